@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the newt_b200 hot path.  Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A "step" is one pass of one workload over one batch of seeded synthetic input:
+
+    matmul     C = A @ B, bf16, one 8192-row block of A per GPU against a replicated
+               8192x8192 B, launched as the deuteron `@dt.kernel` tile loop (the headline:
+               matmul TFLOP/s at 8192^3; at N GPUs the blocks are rows 8192*r.. of one
+               [8192*N, 8192] A, i.e. the M-sharded configuration at N = 8)
+    softmax    fused row softmax, fp32 [4096, 4096]
+    layernorm  layernorm forward, fp16 [8192, 4096]
+    attention  causal attention forward, fp16 [16, 32, 4096, 128] split by batch*head
+
+Multi-GPU runs shard independent units (row blocks, heads) across ranks; there is no
+collective on the data path, so `scaling` is "weak".  Timing: CUDA events around every
+step on the launching stream, L2 flushed (256 MB write) before each timed step, max over
+ranks.  `--impl reference` times the reference's CPU path (the torch calls its tests use as
+expected values, restated under oracle/) on the host cores instead.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+# --------------------------------------------------------------------------- peaks
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "tflops_burst": float(p["bf16_tflops"]),
+                "tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.device_index), "-lms", "100"],
+                stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- workloads
+
+def _seeded(shape, seed, dtype, scale=1.0, shift=0.0):
+    """Draw on the CPU in fp32 from a seed, scale, round to dtype (identical on every box)."""
+    g = torch.Generator().manual_seed(seed)
+    return _pin((torch.randn(shape, generator=g) * scale + shift).to(dtype))
+
+
+def _pin(t):
+    return t.pin_memory() if torch.cuda.is_available() else t
+
+
+class Workload:
+    name = ""
+    metric = ""
+    unit = ""
+    dtype = ""
+    bound = "hbm"
+    kernels_per_step = 1
+
+    def host_inputs(self, rank, world):  # -> list of pinned CPU tensors
+        raise NotImplementedError
+
+    def to_device(self, host):  # -> device state used by step()
+        raise NotImplementedError
+
+    def step(self, dev):
+        raise NotImplementedError
+
+    def result(self, dev):  # tensor read back in the e2e loop
+        raise NotImplementedError
+
+    def units_per_step(self):  # per rank, in the metric's base unit (bytes or flop)
+        raise NotImplementedError
+
+    def cpu_sample(self, host):  # -> (callable, units processed by it, description)
+        raise NotImplementedError
+
+    def config(self, world):
+        raise NotImplementedError
+
+
+class SoftmaxWorkload(Workload):
+    name, metric, unit, dtype, bound = "softmax", "softmax_hbm_gbs", "GB/s", "f32", "hbm"
+    M, N = 4096, 4096
+
+    def host_inputs(self, rank, world):
+        return [_seeded((self.M, self.N), 1 + 1000 * rank, torch.float32)]
+
+    def to_device(self, host):
+        x = host[0].cuda(non_blocking=True)
+        return {"x": x, "out": torch.empty_like(x)}
+
+    def step(self, dev):
+        from newt_b200.runtime import kernels
+        x, out = dev["x"], dev["out"]
+        kernels.softmax_f32(x, out, self.M, self.N, x.stride(0), out.stride(0))
+
+    def result(self, dev):
+        return dev["out"]
+
+    def units_per_step(self):
+        return 2 * self.M * self.N * 4  # bytes read + written (benchmarks/bench.py:208 of the reference)
+
+    def cpu_sample(self, host):
+        from oracle import torch_ref
+        x = host[0]
+        return (lambda: torch_ref.softmax(x)), self.units_per_step(), "full [4096,4096] fp32"
+
+    def config(self, world):
+        return {"workload": "fused row softmax fp32 [4096,4096] per GPU", "rows": self.M,
+                "cols": self.N, "parallelism": f"replicas x{world}", "l2": "flushed between steps"}
+
+
+class LayerNormWorkload(Workload):
+    name, metric, unit, dtype, bound = "layernorm", "layernorm_hbm_gbs", "GB/s", "f16", "hbm"
+    M, N = 8192, 4096
+
+    def host_inputs(self, rank, world):
+        return [_seeded((self.M, self.N), 2 + 1000 * rank, torch.float16),
+                _seeded((self.N,), 21, torch.float16, 0.1, 1.0),
+                _seeded((self.N,), 22, torch.float16, 0.1, 0.0)]
+
+    def to_device(self, host):
+        x, w, b = (h.cuda(non_blocking=True) for h in host)
+        return {"x": x, "w": w, "b": b, "out": torch.empty_like(x)}
+
+    def step(self, dev):
+        from newt_b200.runtime import kernels
+        x, out = dev["x"], dev["out"]
+        kernels.layernorm(x, dev["w"], dev["b"], out, self.M, self.N, x.stride(0), out.stride(0),
+                          1e-5)
+
+    def result(self, dev):
+        return dev["out"]
+
+    def units_per_step(self):
+        return 2 * self.M * self.N * 2
+
+    def cpu_sample(self, host):
+        from oracle import torch_ref
+        x, w, b = host
+        return (lambda: torch_ref.layernorm(x, w, b)), self.units_per_step(), \
+            "full [8192,4096] fp16 (fp32 math)"
+
+    def config(self, world):
+        return {"workload": "layernorm forward fp16 [8192,4096] per GPU", "rows": self.M,
+                "cols": self.N, "eps": 1e-5, "parallelism": f"replicas x{world}",
+                "l2": "flushed between steps"}
+
+
+WORKLOADS = {w.name: w for w in (SoftmaxWorkload, LayerNormWorkload)}
+DEFAULT_WORKLOAD = "softmax"
+
+
+# --------------------------------------------------------------------------- runners
+
+def _dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def run_reference(args, wl):
+    """Reference arm: the reference's CPU path for the same workload, on the host cores."""
+    rank, world, _ = _dist_env()
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    host = wl.host_inputs(0, 1)
+    fn, units, sample = wl.cpu_sample(host)
+    for _ in range(max(1, min(args.warmup, 2))):
+        fn()
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    scale = 1e9 if wl.unit == "GB/s" else 1e12
+    value = units / sec / scale
+    line = {
+        "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded N(0,1))",
+        "config": wl.config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_gpu(args, wl):
+    import torch.distributed as dist
+
+    rank, world, local = _dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the kernels have no CPU fallback)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    host = wl.host_inputs(rank, world)
+    dev = wl.to_device(host)
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        wl.step(dev)
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+
+    # ---- device-resident timed region: K steps, one event pair per step ------
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        flush.zero_()
+        starts[i].record()
+        wl.step(dev)
+        ends[i].record()
+    barrier()
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    total_ms = sum(step_ms)
+
+    # ---- end-to-end region: pinned host -> device, step, result -> host -------
+    out_host = _pin(torch.empty(wl.result(dev).shape, dtype=wl.result(dev).dtype))
+    h2d = sum(h.numel() * h.element_size() for h in host)
+    d2h = out_host.numel() * out_host.element_size()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_once():
+        d = wl.to_device(host)
+        wl.step(d)
+        out_host.copy_(wl.result(d), non_blocking=True)
+
+    e2e_once()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_once()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    clocks = sampler.stop() if rank == 0 else None
+
+    # max over ranks
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        scale = 1e9 if wl.unit == "GB/s" else 1e12
+        units = wl.units_per_step()
+        value = units * world * args.steps / (total_ms * 1e-3) / scale
+        e2e_value = units * world / (e2e_ms * 1e-3) / scale
+        launch_ms = total_ms / (args.steps * wl.kernels_per_step)
+        achieved = units / wl.kernels_per_step / (launch_ms * 1e-3) / scale
+        peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops_burst"]
+        line = {
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic (seeded N(0,1) drawn on the host, copied to HBM before timing)",
+            "config": wl.config(world),
+            "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": wl.unit,
+                         "frac": achieved / peak, "traffic": None,
+                         "peak_source": peaks["source"] + (" copy bandwidth" if wl.bound == "hbm"
+                                                           else " cuBLAS bf16 burst")},
+            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": args.steps * wl.kernels_per_step,
+            "clocks": clocks,
+            "step_ms": {"min": min(step_ms), "median": statistics.median(step_ms),
+                        "max": max(step_ms)},
+        }
+        if world == 1:
+            torch.set_num_threads(os.cpu_count() or 1)
+            fn, cpu_units, sample = wl.cpu_sample(host)
+            fn()
+            best = float("inf")
+            for _ in range(3):
+                t0 = time.perf_counter()
+                fn()
+                best = min(best, time.perf_counter() - t0)
+            line["cpu_baseline"] = {"value": cpu_units / best / scale, "unit": wl.unit,
+                                    "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="newt_b200", choices=["newt_b200", "reference"])
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]()
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_gpu(args, wl)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,144 @@
+/*
+ * newt_b200 -- C ABI of the sm_100a kernel library behind the newt / deuteron
+ * operator API.
+ *
+ * The reference project (arpitsinghgautam/newt) has no C ABI of its own: its
+ * boundary is `cuLaunchKernel` on a kernel that its compiler generated as text
+ * (newt/runtime/cuda.py:216-234, newt/runtime/jit.py:190-223).  Every entry
+ * point below therefore names the *user-level kernel* of the reference whose
+ * generated code it replaces, and the launcher call it stands in for.
+ *
+ * Conventions
+ *   - all pointers are DEVICE pointers owned by the caller, unless the name
+ *     ends in `_host`;
+ *   - sizes and strides are in ELEMENTS, int64;
+ *   - `stream` is a CUstream / cudaStream_t passed as void* (NULL = default);
+ *   - the return value is 0 on success, else one of NB200_E_*; a message for
+ *     the last failure on the calling thread is available from
+ *     nb200_last_error();
+ *   - nothing here allocates device memory unless its comment says so.
+ */
+#ifndef NEWT_B200_H
+#define NEWT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB200_ABI_VERSION 1
+
+enum nb200_error {
+  NB200_OK = 0,
+  NB200_E_INVALID = 1,     /* bad argument (size, alignment, dtype, config)   */
+  NB200_E_UNSUPPORTED = 2, /* legal request that no kernel here covers yet    */
+  NB200_E_CUDA = 3,        /* CUDA runtime / driver call failed               */
+  NB200_E_DEVICE = 4       /* a kernel reported a bounded-wait expiry         */
+};
+
+enum nb200_dtype {
+  NB200_F32 = 0,
+  NB200_F16 = 1,
+  NB200_BF16 = 2
+};
+
+/* Library / ABI identification.  No reference counterpart. */
+int nb200_abi_version(void);
+const char* nb200_last_error(void);
+
+/* Reads and clears the per-device status word that kernels with bounded waits
+ * (mbarrier / TMEM allocation spins) set when a wait expires.  Synchronises
+ * the device.  Returns 0 and *status = 0 when every kernel finished normally.
+ * Stands where the reference has nothing: a hung kernel there is a hung GPU. */
+int nb200_read_status(uint32_t* status, uint32_t* detail);
+
+/* Sets an integer tuning knob by name (0 = back to the built-in heuristic).
+ * Plays the role of the launch keywords `num_warps` / `num_stages` of the
+ * operator API (newt/runtime/jit.py:169-174) for choices the library would
+ * otherwise make itself:
+ *   "row_tpr"          threads that cooperate on one row (32,128,256,512,1024)
+ *   "row_items"        16-byte vectors each of those threads holds (1,2,4,8)
+ *   "row_ctas_per_sm"  resident CTAs per SM of the persistent row grid       */
+int nb200_set_tuning(const char* key, int value);
+
+/* ---- K0: out = x + y -------------------------------------------------------
+ * Replaces the code generated for `add_kernel`
+ * (examples/01_vector_add.py:14-21; launcher :27-28). fp32, bit-exact. */
+int nb200_add_f32(const float* x, const float* y, float* out, int64_t n,
+                  void* stream);
+
+/* ---- K1: row softmax -------------------------------------------------------
+ * Replaces the code generated for `softmax_kernel`
+ * (examples/02_fused_softmax.py:15-24; launcher :27-33): per row
+ * max-subtract, expf, sum, true division; fp32 in/out.
+ * `rows` programs, `n` valid columns, row strides in elements. */
+int nb200_softmax_f32(const float* x, float* out, int64_t rows, int64_t n,
+                      int64_t stride_x, int64_t stride_out, void* stream);
+
+/* ---- K2: layernorm forward -------------------------------------------------
+ * Replaces the code generated for `layernorm_kernel`
+ * (examples/03_layernorm.py:13-27; launcher :30-36): two-pass statistics in
+ * fp32 (mean, then variance of the centred row), rsqrtf(var + eps),
+ * y = (x - mean) * rstd * w + b, one rounding at the store.
+ * `dtype` is the element type of x, w, b and out (NB200_F32/F16/BF16). */
+int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
+                    int64_t rows, int64_t n, int64_t stride_x,
+                    int64_t stride_out, float eps, int dtype, void* stream);
+
+/* ---- K3 / K4: C = A @ B ----------------------------------------------------
+ * Replaces the code generated for `matmul_kernel`
+ * (examples/04_matmul.py:14-45, benchmarks/bench.py:90-108) and for the
+ * deuteron tile loop (examples/deuteron/01_matmul.py:12-18), i.e. what
+ * `nl.dot` lowers to (newt/compiler/codegen.py:2174-2418).
+ * A is [M,K] with row stride lda, B is [K,N] with row stride ldb, C is [M,N]
+ * with row stride ldc; innermost strides are 1.  fp16 or bf16 inputs, fp32
+ * accumulation in tensor memory, one rounding to `dtype` at the store.
+ *
+ * The config mirrors the launch knobs of the operator API: the tile comes
+ * from the kernel's BLOCK_M/BLOCK_N/BLOCK_K constexprs, `stages` from
+ * `num_stages` (depth of the TMA/mbarrier ring), `cta_pair` selects 2-CTA
+ * tcgen05 (cluster of two CTAs sharing one 256-row MMA).  Zero fields mean
+ * "library default". */
+typedef struct nb200_gemm_config {
+  int32_t block_m; /* 128 (one CTA) or 256 (CTA pair)                        */
+  int32_t block_n; /* 64, 128 or 256                                         */
+  int32_t block_k; /* 64                                                     */
+  int32_t stages;  /* 2..8; clamped to what fits in 227 KB of shared memory  */
+  int32_t cta_pair;/* 0 or 1                                                 */
+  int32_t reserved[3];
+} nb200_gemm_config;
+
+int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n,
+               int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int dtype,
+               const nb200_gemm_config* config, void* stream);
+
+/* Returns 0 when (dtype, shape, strides, pointers, config) can run on the
+ * TMA/tcgen05 path, else NB200_E_* with the reason in nb200_last_error().
+ * Launches nothing; lets an autotuner discard configurations analytically
+ * (the reference discards them by catching launch failures,
+ * newt/runtime/autotuner.py:76-81). */
+int nb200_gemm_check(const void* a, const void* b, const void* c, int64_t m,
+                     int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                     int64_t ldc, int dtype, const nb200_gemm_config* config);
+
+/* ---- K5: fused attention forward -------------------------------------------
+ * Replaces the code generated for `attention_kernel`
+ * (examples/05_fused_attention.py:14-48), extended to batch x heads and an
+ * optional causal mask: O = softmax(scale * Q K^T [+ causal]) V with an fp32
+ * online softmax; P is rounded to the input dtype before the PV product, as
+ * the reference does at :43.
+ * Q,O are [batch*heads, seq_q, d]; K,V are [batch*heads, seq_kv, d]; the
+ * three strides of each tensor are (head stride, row stride, 1). d = 64/128. */
+int nb200_attention_fwd(const void* q, const void* k, const void* v, void* o,
+                        int64_t batch_heads, int64_t seq_q, int64_t seq_kv,
+                        int64_t d, int64_t q_head_stride, int64_t q_row_stride,
+                        int64_t k_head_stride, int64_t k_row_stride,
+                        int64_t v_head_stride, int64_t v_row_stride,
+                        int64_t o_head_stride, int64_t o_row_stride,
+                        float scale, int causal, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEWT_B200_H */

@@ -1,0 +1,50 @@
+// Shared host/device helpers of the newt_b200 kernel library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/newt_b200.h"
+
+namespace nb200 {
+
+// ---- host side -------------------------------------------------------------
+
+// Records a printf-style message for nb200_last_error() on this thread and
+// returns `code`, so call sites read `return fail(NB200_E_INVALID, "...")`.
+int fail(int code, const char* fmt, ...);
+int cuda_check(cudaError_t e, const char* what);
+
+struct DeviceInfo {
+  int device;
+  int sm_count;
+  int max_smem_optin;
+};
+// Properties of the current device (cached per device ordinal).
+const DeviceInfo& device_info();
+
+// Integer knobs set through nb200_set_tuning(); returns `dflt` when unset (0).
+int tuning(const char* key, int dflt);
+
+// Per-device status words written by kernels whose bounded waits expire.
+// [0] = first error code (0 = none), [1] = detail (role / barrier / tile).
+unsigned int* device_status_ptr();
+
+static inline int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- device side -----------------------------------------------------------
+
+// Error codes stored in the status word.
+enum : unsigned int {
+  ST_OK = 0,
+  ST_WAIT_TMA_FULL = 1,   // MMA warp waited for a TMA stage that never landed
+  ST_WAIT_SMEM_EMPTY = 2, // TMA warp waited for a stage the MMA never released
+  ST_WAIT_ACC_FULL = 3,   // epilogue waited for an accumulator never committed
+  ST_WAIT_ACC_EMPTY = 4,  // MMA warp waited for an accumulator never drained
+  ST_TMEM_ALLOC = 5,      // tcgen05.alloc did not succeed within the retry cap
+  ST_WAIT_OTHER = 6
+};
+
+}  // namespace nb200

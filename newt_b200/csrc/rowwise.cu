@@ -1,0 +1,451 @@
+// Row programs of the newt operator API as hand-written sm_100a kernels:
+//   K0  out = x + y                      (examples/01_vector_add.py:14-21)
+//   K1  fused row softmax, fp32          (examples/02_fused_softmax.py:15-24)
+//   K2  layernorm forward                (examples/03_layernorm.py:13-27)
+//
+// One template serves K1 and K2.  A row is held entirely in registers: every
+// thread owns ITEMS 16-byte vectors, interleaved so that a warp reads 512
+// contiguous bytes per load instruction (the reference reaches the same access
+// shape through a runtime-checked fast path, newt/compiler/codegen.py:1631-1680).
+// TPR threads cooperate on one row (32 = one row per warp, no shared memory;
+// more = one row per CTA with a two-level shuffle + shared-memory reduction),
+// RPB rows are packed per CTA.  The grid is persistent: it is sized to the
+// number of CTAs the device can hold and each CTA walks rows with a stride,
+// loading the next row's vectors before it reduces the current one, so the
+// reductions of one row overlap the HBM latency of the next.
+//
+// All of this is HBM-bound streaming work; nothing here uses tensor cores.
+
+#include "common.cuh"
+
+namespace nb200 {
+namespace {
+
+constexpr int kWarp = 32;
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static constexpr int kPerVec = 4;
+  __device__ static float to_f32(float v) { return v; }
+  __device__ static float from_f32(float v) { return v; }
+};
+template <>
+struct Elem<__half> {
+  static constexpr int kPerVec = 8;
+  __device__ static float to_f32(__half v) { return __half2float(v); }
+  __device__ static __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int kPerVec = 8;
+  __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+// One 16-byte vector of T, addressable both ways.
+template <typename T>
+union alignas(16) Vec {
+  uint4 raw;
+  T e[Elem<T>::kPerVec];
+};
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_stream(void* p, uint4 v) {
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Loads the vector that covers columns [col, col + kPerVec) of a row.  Lanes
+// past `n` get `fill`.  `vec_ok` says the row base is 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ Vec<T> load_vec(const T* row, int col, int n, bool vec_ok, T fill) {
+  constexpr int E = Elem<T>::kPerVec;
+  Vec<T> v;
+  if (vec_ok && col + E <= n) {
+    v.raw = ld_stream(row + col);
+  } else {
+#pragma unroll
+    for (int j = 0; j < E; ++j) v.e[j] = (col + j < n) ? row[col + j] : fill;
+  }
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void store_vec(T* row, int col, int n, bool vec_ok, const Vec<T>& v) {
+  constexpr int E = Elem<T>::kPerVec;
+  if (vec_ok && col + E <= n) {
+    st_stream(row + col, v.raw);
+  } else {
+#pragma unroll
+    for (int j = 0; j < E; ++j)
+      if (col + j < n) row[col + j] = v.e[j];
+  }
+}
+
+struct SumOp {
+  __device__ static float apply(float a, float b) { return a + b; }
+};
+struct MaxOp {
+  __device__ static float apply(float a, float b) { return fmaxf(a, b); }
+};
+
+// Reduction over the TPR threads of one row.  For TPR > 32 the per-warp
+// results meet in `slot` (one float per warp of the row); callers alternate
+// between two slots so one __syncthreads per reduction is enough.
+template <class Op, int TPR>
+__device__ __forceinline__ float row_reduce(float v, float* slot) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if constexpr (TPR > kWarp) {
+    constexpr int W = TPR / kWarp;
+    const int warp = threadIdx.x / kWarp;
+    if ((threadIdx.x & 31) == 0) slot[warp] = v;
+    __syncthreads();
+    v = slot[0];
+#pragma unroll
+    for (int w = 1; w < W; ++w) v = Op::apply(v, slot[w]);
+  }
+  return v;
+}
+
+enum class RowKind { Softmax, LayerNorm };
+
+struct RowParams {
+  const void* x;
+  const void* w;
+  const void* b;
+  void* out;
+  int rows;
+  int n;
+  int64_t stride_x;
+  int64_t stride_out;
+  float eps;
+  int wb_in_smem;  // layernorm: weight/bias vectors staged once per CTA in shared memory
+};
+
+// Register budget: a thread keeps two raw rows' worth of vectors (current and
+// prefetched), 4 registers each.  Up to 4 vectors per thread that fits in 64
+// registers, i.e. 1024 resident threads per SM, each with 64 bytes of loads in
+// flight: 64 KB per SM, above the ~35 KB that HBM latency x bandwidth needs.
+template <int ITEMS, int THREADS>
+struct RowOccupancy {
+  static constexpr int kMinBlocks = ((ITEMS <= 4 ? 1024 : 512) / THREADS) > 0
+                                        ? ((ITEMS <= 4 ? 1024 : 512) / THREADS)
+                                        : 1;
+};
+
+template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB>
+__global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS, TPR * RPB>::kMinBlocks)
+    row_kernel(RowParams p) {
+  constexpr int E = Elem<T>::kPerVec;
+  constexpr int W = TPR > kWarp ? TPR / kWarp : 1;
+  __shared__ float red[2][W];
+  extern __shared__ uint4 wb_smem[];  // [2][ITEMS][TPR] when p.wb_in_smem
+  static_assert(TPR == kWarp || RPB == 1, "rows share a CTA only in row-per-warp mode");
+
+  const int lane_in_row = threadIdx.x % TPR;
+  const int row_in_cta = threadIdx.x / TPR;
+  const int n = p.n;
+  const T* x = static_cast<const T*>(p.x);
+  T* out = static_cast<T*>(p.out);
+  const T fill = Elem<T>::from_f32(KIND == RowKind::Softmax ? -INFINITY : 0.0f);
+  const T* w = static_cast<const T*>(p.w);
+  const T* b = static_cast<const T*>(p.b);
+  bool w_ok = false, b_ok = false;
+
+  if constexpr (KIND == RowKind::LayerNorm) {
+    w_ok = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    b_ok = (reinterpret_cast<uintptr_t>(b) & 15) == 0;
+    if (p.wb_in_smem) {
+      if (row_in_cta == 0) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const int col = (i * TPR + lane_in_row) * E;
+          wb_smem[i * TPR + lane_in_row] = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f)).raw;
+          wb_smem[(ITEMS + i) * TPR + lane_in_row] =
+              load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f)).raw;
+        }
+      }
+      __syncthreads();
+    }
+  }
+
+  const int step = gridDim.x * RPB;
+  int row = blockIdx.x * RPB + row_in_cta;
+  Vec<T> cur[ITEMS], nxt[ITEMS];
+  if (row < p.rows) {
+    const T* xr = x + (int64_t)row * p.stride_x;
+    const bool ok = (reinterpret_cast<uintptr_t>(xr) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) cur[i] = load_vec<T>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
+  }
+
+  // With TPR > 32 every thread of the CTA works on the same row, so the loop
+  // condition is uniform and the __syncthreads inside row_reduce is safe.
+  for (; row < p.rows; row += step) {
+    // put the next row's loads in flight before reducing this one
+    const int next = row + step;
+    if (next < p.rows) {
+      const T* xr = x + (int64_t)next * p.stride_x;
+      const bool ok = (reinterpret_cast<uintptr_t>(xr) & 15) == 0;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+        nxt[i] = load_vec<T>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
+    }
+
+    T* orow = out + (int64_t)row * p.stride_out;
+    const bool out_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
+
+    if constexpr (KIND == RowKind::Softmax) {
+      static_assert(KIND != RowKind::Softmax || sizeof(T) == 4, "softmax rows are fp32");
+      float m = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+        for (int j = 0; j < E; ++j) m = fmaxf(m, Elem<T>::to_f32(cur[i].e[j]));
+      m = row_reduce<MaxOp, TPR>(m, red[0]);
+      float s = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const float e = expf(Elem<T>::to_f32(cur[i].e[j]) - m);  // masked lanes: exp(-inf) = 0
+          cur[i].e[j] = Elem<T>::from_f32(e);
+          s += e;
+        }
+      s = row_reduce<SumOp, TPR>(s, red[1]);
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+#pragma unroll
+        for (int j = 0; j < E; ++j)
+          cur[i].e[j] = Elem<T>::from_f32(Elem<T>::to_f32(cur[i].e[j]) / s);
+        store_vec<T>(orow, (i * TPR + lane_in_row) * E, n, out_ok, cur[i]);
+      }
+    } else {
+      const float fn = (float)n;
+      float s = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+        for (int j = 0; j < E; ++j) s += Elem<T>::to_f32(cur[i].e[j]);  // masked lanes hold 0
+      const float mean = row_reduce<SumOp, TPR>(s, red[0]) / fn;
+      float q = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const int col = (i * TPR + lane_in_row) * E + j;
+          const float d = col < n ? Elem<T>::to_f32(cur[i].e[j]) - mean : 0.0f;
+          q += d * d;
+        }
+      const float var = row_reduce<SumOp, TPR>(q, red[1]) / fn;
+      const float rstd = rsqrtf(var + p.eps);
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int col = (i * TPR + lane_in_row) * E;
+        Vec<T> wv, bv, o;
+        if (p.wb_in_smem) {
+          wv.raw = wb_smem[i * TPR + lane_in_row];
+          bv.raw = wb_smem[(ITEMS + i) * TPR + lane_in_row];
+        } else {
+          wv = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
+          bv = load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
+        }
+#pragma unroll
+        for (int j = 0; j < E; ++j)
+          o.e[j] = Elem<T>::from_f32((Elem<T>::to_f32(cur[i].e[j]) - mean) * rstd *
+                                         Elem<T>::to_f32(wv.e[j]) +
+                                     Elem<T>::to_f32(bv.e[j]));
+        store_vec<T>(orow, col, n, out_ok, o);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) cur[i] = nxt[i];
+  }
+}
+
+// ---- K0 --------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ x,
+                                                      const float* __restrict__ y,
+                                                      float* __restrict__ out, int64_t n,
+                                                      int vec_ok) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    const int64_t nvec = n / 4;
+    // two vectors per thread per trip keeps 64 bytes in flight per operand
+    for (int64_t i = tid; i < nvec; i += 2 * nthreads) {
+      const int64_t i2 = i + nthreads;
+      uint4 a0 = ld_stream(x + 4 * i), b0 = ld_stream(y + 4 * i);
+      uint4 a1, b1;
+      if (i2 < nvec) {
+        a1 = ld_stream(x + 4 * i2);
+        b1 = ld_stream(y + 4 * i2);
+      }
+      uint4 r;
+      r.x = __float_as_uint(__uint_as_float(a0.x) + __uint_as_float(b0.x));
+      r.y = __float_as_uint(__uint_as_float(a0.y) + __uint_as_float(b0.y));
+      r.z = __float_as_uint(__uint_as_float(a0.z) + __uint_as_float(b0.z));
+      r.w = __float_as_uint(__uint_as_float(a0.w) + __uint_as_float(b0.w));
+      st_stream(out + 4 * i, r);
+      if (i2 < nvec) {
+        r.x = __float_as_uint(__uint_as_float(a1.x) + __uint_as_float(b1.x));
+        r.y = __float_as_uint(__uint_as_float(a1.y) + __uint_as_float(b1.y));
+        r.z = __float_as_uint(__uint_as_float(a1.z) + __uint_as_float(b1.z));
+        r.w = __float_as_uint(__uint_as_float(a1.w) + __uint_as_float(b1.w));
+        st_stream(out + 4 * i2, r);
+      }
+    }
+    for (int64_t i = nvec * 4 + tid; i < n; i += nthreads) out[i] = x[i] + y[i];
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) out[i] = x[i] + y[i];
+  }
+}
+
+// ---- dispatch ----------------------------------------------------------------
+
+struct RowConfig {
+  int tpr;
+  int items;
+};
+
+// Smallest register tile that holds a row of n elements, 16 bytes per vector.
+bool pick_row_config(int64_t n, int elems_per_vec, RowConfig* cfg) {
+  static const RowConfig table[] = {{32, 1},  {32, 2},  {32, 4},  {32, 8},  {128, 4},
+                                    {256, 4}, {256, 8}, {512, 8}, {1024, 8}};
+  const int force_tpr = tuning("row_tpr", 0), force_items = tuning("row_items", 0);
+  if (force_tpr && force_items) {
+    if ((int64_t)force_tpr * force_items * elems_per_vec < n) return false;
+    *cfg = {force_tpr, force_items};
+    return true;
+  }
+  for (const RowConfig& c : table)
+    if ((int64_t)c.tpr * c.items * elems_per_vec >= n) {
+      *cfg = c;
+      return true;
+    }
+  return false;
+}
+
+template <RowKind KIND, typename T, int ITEMS, int TPR>
+int launch_row(const RowParams& p, cudaStream_t stream) {
+  constexpr int RPB = TPR == kWarp ? 4 : 1;
+  auto kern = row_kernel<KIND, T, ITEMS, TPR, RPB>;
+  const DeviceInfo& dev = device_info();
+  RowParams q = p;
+  size_t smem = 0;
+  if (KIND == RowKind::LayerNorm) {
+    // weight and bias as raw 16-byte vectors, staged once per persistent CTA
+    const size_t want_smem = (size_t)2 * ITEMS * TPR * sizeof(uint4);
+    if (want_smem * RowOccupancy<ITEMS, TPR * RPB>::kMinBlocks <= 160 * 1024 &&
+        want_smem <= 48 * 1024) {
+      smem = want_smem;
+      q.wb_in_smem = 1;
+    }
+  }
+  int per_sm = tuning("row_ctas_per_sm", 0);
+  if (per_sm <= 0) {
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, TPR * RPB, smem);
+    if (e != cudaSuccess) return cuda_check(e, "occupancy query");
+    if (per_sm < 1) per_sm = 1;
+  }
+  int64_t want = cdiv64(p.rows, RPB);
+  int64_t cap = (int64_t)dev.sm_count * per_sm;
+  const int grid = (int)(want < cap ? want : cap);
+  kern<<<grid, TPR * RPB, smem, stream>>>(q);
+  return cuda_check(cudaGetLastError(), "row kernel launch");
+}
+
+template <RowKind KIND, typename T>
+int dispatch_row(const RowParams& p, cudaStream_t stream) {
+  RowConfig c;
+  if (!pick_row_config(p.n, Elem<T>::kPerVec, &c))
+    return fail(NB200_E_UNSUPPORTED,
+                "row of %d elements does not fit the register tile (max %d)", p.n,
+                1024 * 8 * Elem<T>::kPerVec);
+#define NB200_ROW_CASE(TPR_, ITEMS_) \
+  if (c.tpr == TPR_ && c.items == ITEMS_) return launch_row<KIND, T, ITEMS_, TPR_>(p, stream);
+  NB200_ROW_CASE(32, 1)
+  NB200_ROW_CASE(32, 2)
+  NB200_ROW_CASE(32, 4)
+  NB200_ROW_CASE(32, 8)
+  NB200_ROW_CASE(128, 4)
+  NB200_ROW_CASE(128, 8)
+  NB200_ROW_CASE(256, 4)
+  NB200_ROW_CASE(256, 8)
+  NB200_ROW_CASE(512, 2)
+  NB200_ROW_CASE(512, 4)
+  NB200_ROW_CASE(512, 8)
+  NB200_ROW_CASE(1024, 8)
+#undef NB200_ROW_CASE
+  return fail(NB200_E_INVALID, "no row kernel for threads-per-row=%d vectors-per-thread=%d",
+              c.tpr, c.items);
+}
+
+int check_rows(const void* x, const void* out, int64_t rows, int64_t n) {
+  if (rows < 0 || n < 0) return fail(NB200_E_INVALID, "negative size (rows=%lld n=%lld)",
+                                     (long long)rows, (long long)n);
+  if (rows > INT32_MAX || n > INT32_MAX)
+    return fail(NB200_E_INVALID, "rows / n beyond int32 (rows=%lld n=%lld)", (long long)rows,
+                (long long)n);
+  if (rows > 0 && n > 0 && (!x || !out)) return fail(NB200_E_INVALID, "null tensor pointer");
+  return 0;
+}
+
+}  // namespace
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" int nb200_add_f32(const float* x, const float* y, float* out, int64_t n,
+                             void* stream) {
+  if (n < 0) return fail(NB200_E_INVALID, "negative length %lld", (long long)n);
+  if (n == 0) return 0;
+  if (!x || !y || !out) return fail(NB200_E_INVALID, "null tensor pointer");
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                       reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const DeviceInfo& dev = device_info();
+  const int threads = 256;
+  int64_t want = cdiv64(vec_ok ? cdiv64(n, 4) : n, threads * 2);
+  int64_t cap = (int64_t)dev.sm_count * 8;
+  const int grid = (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+  add_f32_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(x, y, out, n, vec_ok);
+  return cuda_check(cudaGetLastError(), "add_f32 launch");
+}
+
+extern "C" int nb200_softmax_f32(const float* x, float* out, int64_t rows, int64_t n,
+                                 int64_t stride_x, int64_t stride_out, void* stream) {
+  if (int rc = check_rows(x, out, rows, n)) return rc;
+  if (rows == 0 || n == 0) return 0;
+  RowParams p{x, nullptr, nullptr, out, (int)rows, (int)n, stride_x, stride_out, 0.0f, 0};
+  return dispatch_row<RowKind::Softmax, float>(p, (cudaStream_t)stream);
+}
+
+extern "C" int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
+                               int64_t rows, int64_t n, int64_t stride_x, int64_t stride_out,
+                               float eps, int dtype, void* stream) {
+  if (int rc = check_rows(x, out, rows, n)) return rc;
+  if (rows == 0 || n == 0) return 0;
+  if (!w || !b) return fail(NB200_E_INVALID, "null weight / bias pointer");
+  RowParams p{x, w, b, out, (int)rows, (int)n, stride_x, stride_out, eps, 0};
+  switch (dtype) {
+    case NB200_F32:
+      return dispatch_row<RowKind::LayerNorm, float>(p, (cudaStream_t)stream);
+    case NB200_F16:
+      return dispatch_row<RowKind::LayerNorm, __half>(p, (cudaStream_t)stream);
+    case NB200_BF16:
+      return dispatch_row<RowKind::LayerNorm, __nv_bfloat16>(p, (cudaStream_t)stream);
+    default:
+      return fail(NB200_E_INVALID, "unknown dtype code %d", dtype);
+  }
+}

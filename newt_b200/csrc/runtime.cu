@@ -1,0 +1,95 @@
+// Host-side plumbing shared by every entry point of the library: error text,
+// device properties, tuning knobs, and the device status word that kernels
+// with bounded waits report into.
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+
+namespace nb200 {
+
+namespace {
+thread_local char g_error[512] = "";
+std::mutex g_mutex;
+std::map<std::string, int> g_tuning;
+std::map<int, DeviceInfo> g_devices;
+
+// Written by kernels (first error wins), read by nb200_read_status().
+__device__ unsigned int g_status[4];
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_check(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return 0;
+  return fail(NB200_E_CUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+const DeviceInfo& device_info() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_devices.find(dev);
+  if (it != g_devices.end()) return it->second;
+  DeviceInfo info{dev, 148, 232448};
+  cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev);
+  cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  return g_devices.emplace(dev, info).first->second;
+}
+
+int tuning(const char* key, int dflt) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_tuning.find(key);
+  return (it == g_tuning.end() || it->second == 0) ? dflt : it->second;
+}
+
+unsigned int* device_status_ptr() {
+  // resolved per call: the symbol has one instance per device context
+  unsigned int* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status) != cudaSuccess) return nullptr;
+  return p;
+}
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" int nb200_abi_version(void) { return NB200_ABI_VERSION; }
+
+extern "C" const char* nb200_last_error(void) { return g_error; }
+
+extern "C" int nb200_set_tuning(const char* key, int value) {
+  if (!key) return fail(NB200_E_INVALID, "null tuning key");
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_tuning[key] = value;
+  return 0;
+}
+
+extern "C" int nb200_read_status(uint32_t* status, uint32_t* detail) {
+  unsigned int host[4] = {0, 0, 0, 0};
+  if (int rc = cuda_check(cudaDeviceSynchronize(), "synchronize before status read")) return rc;
+  if (int rc = cuda_check(cudaMemcpyFromSymbol(host, g_status, sizeof(host)), "status read"))
+    return rc;
+  if (host[0] != 0) {
+    unsigned int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_status, zero, sizeof(zero));
+  }
+  if (status) *status = host[0];
+  if (detail) *detail = host[1];
+  if (host[0] != 0)
+    return fail(NB200_E_DEVICE, "a kernel gave up on a bounded wait (code %u, detail 0x%x)", host[0],
+                host[1]);
+  return 0;
+}

@@ -1,0 +1,76 @@
+"""Tensor-level launchers over the C ABI: torch CUDA tensors in, kernel launch on
+torch's current stream.  These are what the lowering plans of the JIT front end
+call; they add nothing to the arithmetic.  Like the reference launcher
+(newt/runtime/jit.py:190-223) they refuse tensors that are not on the current
+CUDA device and they never allocate.
+"""
+
+import ctypes
+
+import torch
+
+from . import abi
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev_ptr(name, t):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"argument '{name}' must be a CUDA tensor")
+    if t.device.index not in (None, torch.cuda.current_device()):
+        raise ValueError(
+            f"tensor '{name}' is on {t.device} but the current device is "
+            f"cuda:{torch.cuda.current_device()}; newt launches on the current device")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def add_f32(x, y, out, n):
+    abi.check(abi.load().nb200_add_f32(_dev_ptr("x", x), _dev_ptr("y", y), _dev_ptr("out", out),
+                                       int(n), _stream()))
+
+
+def softmax_f32(x, out, rows, n, stride_x, stride_out):
+    abi.check(abi.load().nb200_softmax_f32(_dev_ptr("x", x), _dev_ptr("out", out), int(rows),
+                                           int(n), int(stride_x), int(stride_out), _stream()))
+
+
+def layernorm(x, w, b, out, rows, n, stride_x, stride_out, eps):
+    abi.check(abi.load().nb200_layernorm(
+        _dev_ptr("x", x), _dev_ptr("w", w), _dev_ptr("b", b), _dev_ptr("out", out), int(rows),
+        int(n), int(stride_x), int(stride_out), float(eps), abi.dtype_code(x.dtype), _stream()))
+
+
+def gemm_config(block_m=0, block_n=0, block_k=0, stages=0, cta_pair=0):
+    return abi.GemmConfig(block_m, block_n, block_k, stages, cta_pair)
+
+
+def gemm(a, b, c, m, n, k, lda, ldb, ldc, config=None):
+    cfg = ctypes.byref(config) if config is not None else None
+    abi.check(abi.load().nb200_gemm(_dev_ptr("a", a), _dev_ptr("b", b), _dev_ptr("c", c), int(m),
+                                    int(n), int(k), int(lda), int(ldb), int(ldc),
+                                    abi.dtype_code(a.dtype), cfg, _stream()))
+
+
+def gemm_check(a, b, c, m, n, k, lda, ldb, ldc, config=None):
+    """Returns None if the tcgen05 path can run this problem, else the reason (str)."""
+    cfg = ctypes.byref(config) if config is not None else None
+    rc = abi.load().nb200_gemm_check(_dev_ptr("a", a), _dev_ptr("b", b), _dev_ptr("c", c), int(m),
+                                     int(n), int(k), int(lda), int(ldb), int(ldc),
+                                     abi.dtype_code(a.dtype), cfg)
+    return None if rc == 0 else abi.last_error()
+
+
+def attention_fwd(q, k, v, o, scale, causal):
+    """q,o: [bh, seq_q, d]; k,v: [bh, seq_kv, d]; innermost stride 1."""
+    bh, sq, d = q.shape
+    skv = k.shape[1]
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o)):
+        if t.stride(2) != 1:
+            raise ValueError(f"attention: '{name}' must have unit stride along head_dim")
+    abi.check(abi.load().nb200_attention_fwd(
+        _dev_ptr("q", q), _dev_ptr("k", k), _dev_ptr("v", v), _dev_ptr("o", o), bh, sq, skv, d,
+        q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+        o.stride(0), o.stride(1), float(scale), int(bool(causal)), abi.dtype_code(q.dtype),
+        _stream()))
