@@ -99,22 +99,38 @@ struct MaxOp {
 };
 
 // Reduction over the TPR threads of one row.  For TPR > 32 the per-warp
-// results meet in `slot` (one float per warp of the row); callers alternate
-// between two slots so one __syncthreads per reduction is enough.
+// results meet in `slot` (one float per warp of the row) behind a named barrier
+// that only the row's own TPR threads join, so several rows can share a CTA.
+// Callers alternate between two slots, which makes one barrier per reduction
+// enough.
 template <class Op, int TPR>
-__device__ __forceinline__ float row_reduce(float v, float* slot) {
+__device__ __forceinline__ float row_reduce(float v, float* slot, int barrier_id) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
   if constexpr (TPR > kWarp) {
     constexpr int W = TPR / kWarp;
-    const int warp = threadIdx.x / kWarp;
-    if ((threadIdx.x & 31) == 0) slot[warp] = v;
-    __syncthreads();
+    const int warp_in_row = (threadIdx.x % TPR) / kWarp;
+    if ((threadIdx.x & 31) == 0) slot[warp_in_row] = v;
+    asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "n"(TPR) : "memory");
     v = slot[0];
 #pragma unroll
     for (int w = 1; w < W; ++w) v = Op::apply(v, slot[w]);
   }
   return v;
+}
+
+// exp(t) for t <= 0 as 2^(t * log2 e) on the special-function unit.  The
+// product is formed with the constant split in two so that the rounding of
+// log2(e) does not grow with |t|; what remains is the rounding of the product
+// itself (half an ulp of |t| * 1.44) and ex2.approx's 2^-22 relative error:
+// below 3e-6 relative for every finite input, against the 1e-5 bar.
+__device__ __forceinline__ float exp_neg(float t) {
+  constexpr float kLog2eHi = 1.44269502162933349609375f;
+  constexpr float kLog2eLo = 1.92596299112661746e-8f;
+  float y = fmaf(t, kLog2eLo, t * kLog2eHi);
+  float r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(y));
+  return r;
 }
 
 enum class RowKind { Softmax, LayerNorm };
@@ -129,32 +145,33 @@ struct RowParams {
   int64_t stride_x;
   int64_t stride_out;
   float eps;
-  int wb_in_smem;  // layernorm: weight/bias vectors staged once per CTA in shared memory
+  int wb_in_smem;  // layernorm: weight/bias staged once per CTA in shared memory as fp32
 };
 
-// Register budget: a thread keeps two raw rows' worth of vectors (current and
-// prefetched), 4 registers each.  Up to 4 vectors per thread that fits in 64
-// registers, i.e. 1024 resident threads per SM, each with 64 bytes of loads in
-// flight: 64 KB per SM, above the ~35 KB that HBM latency x bandwidth needs.
-template <int ITEMS, int THREADS>
+// Register budget: a thread holds one row slice as fp32 values plus the raw
+// vectors of the next row.  With up to 16 values per thread that fits in 64
+// registers (1024 resident threads per SM); 32 values need about 80 (768
+// threads); more get 128 (512 threads).  Every resident thread keeps up to
+// 64 bytes of loads in flight, i.e. 48-64 KB per SM, above the ~35 KB that HBM
+// latency x bandwidth needs.
+template <int VALUES, int THREADS>
 struct RowOccupancy {
-  static constexpr int kMinBlocks = ((ITEMS <= 4 ? 1024 : 512) / THREADS) > 0
-                                        ? ((ITEMS <= 4 ? 1024 : 512) / THREADS)
-                                        : 1;
+  static constexpr int kThreadsPerSm = VALUES <= 16 ? 1024 : (VALUES <= 32 ? 768 : 512);
+  static constexpr int kMinBlocks = kThreadsPerSm / THREADS > 0 ? kThreadsPerSm / THREADS : 1;
 };
 
 template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB>
-__global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS, TPR * RPB>::kMinBlocks)
+__global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVec, TPR * RPB>::kMinBlocks)
     row_kernel(RowParams p) {
   constexpr int E = Elem<T>::kPerVec;
   constexpr int W = TPR > kWarp ? TPR / kWarp : 1;
-  __shared__ float red[2][W];
-  extern __shared__ uint4 wb_smem[];  // [2][ITEMS][TPR] when p.wb_in_smem
-  static_assert(TPR == kWarp || RPB == 1, "rows share a CTA only in row-per-warp mode");
+  __shared__ float red[RPB][2][W];
+  extern __shared__ float4 wb_smem[];  // fp32 w[ITEMS*TPR*E] then b[...] when p.wb_in_smem
 
   const int lane_in_row = threadIdx.x % TPR;
   const int row_in_cta = threadIdx.x / TPR;
   const int n = p.n;
+  const bool full = n == ITEMS * TPR * E;  // no padded lanes: predicates drop out
   const T* x = static_cast<const T*>(p.x);
   T* out = static_cast<T*>(p.out);
   const T fill = Elem<T>::from_f32(KIND == RowKind::Softmax ? -INFINITY : 0.0f);
@@ -166,13 +183,19 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS, TPR * RPB>::kMin
     w_ok = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     b_ok = (reinterpret_cast<uintptr_t>(b) & 15) == 0;
     if (p.wb_in_smem) {
+      float* ws = reinterpret_cast<float*>(wb_smem);
+      float* bs = ws + ITEMS * TPR * E;
       if (row_in_cta == 0) {
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
           const int col = (i * TPR + lane_in_row) * E;
-          wb_smem[i * TPR + lane_in_row] = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f)).raw;
-          wb_smem[(ITEMS + i) * TPR + lane_in_row] =
-              load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f)).raw;
+          const Vec<T> wv = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
+          const Vec<T> bv = load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
+#pragma unroll
+          for (int j = 0; j < E; ++j) {
+            ws[col + j] = Elem<T>::to_f32(wv.e[j]);
+            bs[col + j] = Elem<T>::to_f32(bv.e[j]);
+          }
         }
       }
       __syncthreads();
@@ -181,17 +204,26 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS, TPR * RPB>::kMin
 
   const int step = gridDim.x * RPB;
   int row = blockIdx.x * RPB + row_in_cta;
-  Vec<T> cur[ITEMS], nxt[ITEMS];
+  Vec<T> nxt[ITEMS];
   if (row < p.rows) {
     const T* xr = x + (int64_t)row * p.stride_x;
     const bool ok = (reinterpret_cast<uintptr_t>(xr) & 15) == 0;
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) cur[i] = load_vec<T>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
+    for (int i = 0; i < ITEMS; ++i) nxt[i] = load_vec<T>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
   }
+  float* red0 = red[row_in_cta][0];
+  float* red1 = red[row_in_cta][1];
+  const int bar_id = 1 + row_in_cta;
 
-  // With TPR > 32 every thread of the CTA works on the same row, so the loop
-  // condition is uniform and the __syncthreads inside row_reduce is safe.
+  // The TPR threads of a row always agree on `row`, so the loop condition is
+  // uniform across everyone who joins the row's named barrier.
   for (; row < p.rows; row += step) {
+    float v[ITEMS * E];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+      for (int j = 0; j < E; ++j) v[i * E + j] = Elem<T>::to_f32(nxt[i].e[j]);
+
     // put the next row's loads in flight before reducing this one
     const int next = row + step;
     if (next < p.rows) {
@@ -206,74 +238,96 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS, TPR * RPB>::kMin
     const bool out_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
 
     if constexpr (KIND == RowKind::Softmax) {
-      static_assert(KIND != RowKind::Softmax || sizeof(T) == 4, "softmax rows are fp32");
-      float m = -INFINITY;
+      float m = v[0];
 #pragma unroll
-      for (int i = 0; i < ITEMS; ++i)
-#pragma unroll
-        for (int j = 0; j < E; ++j) m = fmaxf(m, Elem<T>::to_f32(cur[i].e[j]));
-      m = row_reduce<MaxOp, TPR>(m, red[0]);
+      for (int k = 1; k < ITEMS * E; ++k) m = fmaxf(m, v[k]);
+      m = row_reduce<MaxOp, TPR>(m, red0, bar_id);
       float s = 0.0f;
 #pragma unroll
-      for (int i = 0; i < ITEMS; ++i)
-#pragma unroll
-        for (int j = 0; j < E; ++j) {
-          const float e = expf(Elem<T>::to_f32(cur[i].e[j]) - m);  // masked lanes: exp(-inf) = 0
-          cur[i].e[j] = Elem<T>::from_f32(e);
-          s += e;
-        }
-      s = row_reduce<SumOp, TPR>(s, red[1]);
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) {
-#pragma unroll
-        for (int j = 0; j < E; ++j)
-          cur[i].e[j] = Elem<T>::from_f32(Elem<T>::to_f32(cur[i].e[j]) / s);
-        store_vec<T>(orow, (i * TPR + lane_in_row) * E, n, out_ok, cur[i]);
+      for (int k = 0; k < ITEMS * E; ++k) {
+        v[k] = exp_neg(v[k] - m);  // masked lanes hold -inf and give 0
+        s += v[k];
       }
+      s = row_reduce<SumOp, TPR>(s, red1, bar_id);
+      // one reciprocal per row, then a multiply per element: within 1.5 ulp of
+      // the reference's per-element division
+      const float inv = 1.0f / s;
+#pragma unroll
+      for (int k = 0; k < ITEMS * E; ++k) v[k] *= inv;
     } else {
       const float fn = (float)n;
       float s = 0.0f;
 #pragma unroll
-      for (int i = 0; i < ITEMS; ++i)
-#pragma unroll
-        for (int j = 0; j < E; ++j) s += Elem<T>::to_f32(cur[i].e[j]);  // masked lanes hold 0
-      const float mean = row_reduce<SumOp, TPR>(s, red[0]) / fn;
+      for (int k = 0; k < ITEMS * E; ++k) s += v[k];  // masked lanes hold 0
+      const float mean = row_reduce<SumOp, TPR>(s, red0, bar_id) / fn;
       float q = 0.0f;
+      if (full) {
 #pragma unroll
-      for (int i = 0; i < ITEMS; ++i)
-#pragma unroll
-        for (int j = 0; j < E; ++j) {
-          const int col = (i * TPR + lane_in_row) * E + j;
-          const float d = col < n ? Elem<T>::to_f32(cur[i].e[j]) - mean : 0.0f;
-          q += d * d;
+        for (int k = 0; k < ITEMS * E; ++k) {
+          v[k] -= mean;
+          q = fmaf(v[k], v[k], q);
         }
-      const float var = row_reduce<SumOp, TPR>(q, red[1]) / fn;
+      } else {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+          for (int j = 0; j < E; ++j) {
+            const int col = (i * TPR + lane_in_row) * E + j;
+            const float d = col < n ? v[i * E + j] - mean : 0.0f;
+            v[i * E + j] = d;
+            q = fmaf(d, d, q);
+          }
+      }
+      const float var = row_reduce<SumOp, TPR>(q, red1, bar_id) / fn;
       const float rstd = rsqrtf(var + p.eps);
+      if (p.wb_in_smem) {
+        const float4* ws4 = wb_smem;
+        const float4* bs4 = wb_smem + ITEMS * TPR * E / 4;
 #pragma unroll
-      for (int i = 0; i < ITEMS; ++i) {
-        const int col = (i * TPR + lane_in_row) * E;
-        Vec<T> wv, bv, o;
-        if (p.wb_in_smem) {
-          wv.raw = wb_smem[i * TPR + lane_in_row];
-          bv.raw = wb_smem[(ITEMS + i) * TPR + lane_in_row];
-        } else {
-          wv = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
-          bv = load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
+        for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+          for (int j = 0; j < E; j += 4) {
+            const int q4 = ((i * TPR + lane_in_row) * E + j) / 4;
+            const float4 wv = ws4[q4], bv = bs4[q4];
+            v[i * E + j + 0] = fmaf(v[i * E + j + 0] * rstd, wv.x, bv.x);
+            v[i * E + j + 1] = fmaf(v[i * E + j + 1] * rstd, wv.y, bv.y);
+            v[i * E + j + 2] = fmaf(v[i * E + j + 2] * rstd, wv.z, bv.z);
+            v[i * E + j + 3] = fmaf(v[i * E + j + 3] * rstd, wv.w, bv.w);
+          }
+      } else {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const int col = (i * TPR + lane_in_row) * E;
+          const Vec<T> wv = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
+          const Vec<T> bv = load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
+#pragma unroll
+          for (int j = 0; j < E; ++j)
+            v[i * E + j] = fmaf(v[i * E + j] * rstd, Elem<T>::to_f32(wv.e[j]),
+                                Elem<T>::to_f32(bv.e[j]));
         }
-#pragma unroll
-        for (int j = 0; j < E; ++j)
-          o.e[j] = Elem<T>::from_f32((Elem<T>::to_f32(cur[i].e[j]) - mean) * rstd *
-                                         Elem<T>::to_f32(wv.e[j]) +
-                                     Elem<T>::to_f32(bv.e[j]));
-        store_vec<T>(orow, col, n, out_ok, o);
       }
     }
+
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) cur[i] = nxt[i];
+    for (int i = 0; i < ITEMS; ++i) {
+      Vec<T> o;
+#pragma unroll
+      for (int j = 0; j < E; ++j) o.e[j] = Elem<T>::from_f32(v[i * E + j]);
+      store_vec<T>(orow, (i * TPR + lane_in_row) * E, n, out_ok, o);
+    }
   }
 }
 
 // ---- K0 --------------------------------------------------------------------
+
+__device__ __forceinline__ uint4 add4(uint4 a, uint4 b) {
+  uint4 r;
+  r.x = __float_as_uint(__uint_as_float(a.x) + __uint_as_float(b.x));
+  r.y = __float_as_uint(__uint_as_float(a.y) + __uint_as_float(b.y));
+  r.z = __float_as_uint(__uint_as_float(a.z) + __uint_as_float(b.z));
+  r.w = __float_as_uint(__uint_as_float(a.w) + __uint_as_float(b.w));
+  return r;
+}
 
 __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ x,
                                                       const float* __restrict__ y,
@@ -282,28 +336,23 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   if (vec_ok) {
+    constexpr int U = 4;  // vectors per operand per thread per trip: 128 bytes in flight
     const int64_t nvec = n / 4;
-    // two vectors per thread per trip keeps 64 bytes in flight per operand
-    for (int64_t i = tid; i < nvec; i += 2 * nthreads) {
-      const int64_t i2 = i + nthreads;
-      uint4 a0 = ld_stream(x + 4 * i), b0 = ld_stream(y + 4 * i);
-      uint4 a1, b1;
-      if (i2 < nvec) {
-        a1 = ld_stream(x + 4 * i2);
-        b1 = ld_stream(y + 4 * i2);
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x * U; base < nvec;
+         base += nthreads * U) {
+      uint4 a[U], b[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = base + u * blockDim.x + threadIdx.x;
+        if (i < nvec) {
+          a[u] = ld_stream(x + 4 * i);
+          b[u] = ld_stream(y + 4 * i);
+        }
       }
-      uint4 r;
-      r.x = __float_as_uint(__uint_as_float(a0.x) + __uint_as_float(b0.x));
-      r.y = __float_as_uint(__uint_as_float(a0.y) + __uint_as_float(b0.y));
-      r.z = __float_as_uint(__uint_as_float(a0.z) + __uint_as_float(b0.z));
-      r.w = __float_as_uint(__uint_as_float(a0.w) + __uint_as_float(b0.w));
-      st_stream(out + 4 * i, r);
-      if (i2 < nvec) {
-        r.x = __float_as_uint(__uint_as_float(a1.x) + __uint_as_float(b1.x));
-        r.y = __float_as_uint(__uint_as_float(a1.y) + __uint_as_float(b1.y));
-        r.z = __float_as_uint(__uint_as_float(a1.z) + __uint_as_float(b1.z));
-        r.w = __float_as_uint(__uint_as_float(a1.w) + __uint_as_float(b1.w));
-        st_stream(out + 4 * i2, r);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = base + u * blockDim.x + threadIdx.x;
+        if (i < nvec) st_stream(out + 4 * i, add4(a[u], b[u]));
       }
     }
     for (int64_t i = nvec * 4 + tid; i < n; i += nthreads) out[i] = x[i] + y[i];
@@ -337,20 +386,23 @@ bool pick_row_config(int64_t n, int elems_per_vec, RowConfig* cfg) {
   return false;
 }
 
-template <RowKind KIND, typename T, int ITEMS, int TPR>
+template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB>
 int launch_row(const RowParams& p, cudaStream_t stream) {
-  constexpr int RPB = TPR == kWarp ? 4 : 1;
   auto kern = row_kernel<KIND, T, ITEMS, TPR, RPB>;
   const DeviceInfo& dev = device_info();
   RowParams q = p;
   size_t smem = 0;
   if (KIND == RowKind::LayerNorm) {
-    // weight and bias as raw 16-byte vectors, staged once per persistent CTA
-    const size_t want_smem = (size_t)2 * ITEMS * TPR * sizeof(uint4);
-    if (want_smem * RowOccupancy<ITEMS, TPR * RPB>::kMinBlocks <= 160 * 1024 &&
-        want_smem <= 48 * 1024) {
+    // weight and bias as fp32, staged once per persistent CTA
+    const size_t want_smem = (size_t)2 * ITEMS * TPR * Elem<T>::kPerVec * sizeof(float);
+    if (want_smem * RowOccupancy<ITEMS * Elem<T>::kPerVec, TPR * RPB>::kMinBlocks <= 200 * 1024) {
       smem = want_smem;
       q.wb_in_smem = 1;
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return cuda_check(e, "raise dynamic shared memory limit");
+      }
     }
   }
   int per_sm = tuning("row_ctas_per_sm", 0);
@@ -373,23 +425,30 @@ int dispatch_row(const RowParams& p, cudaStream_t stream) {
     return fail(NB200_E_UNSUPPORTED,
                 "row of %d elements does not fit the register tile (max %d)", p.n,
                 1024 * 8 * Elem<T>::kPerVec);
-#define NB200_ROW_CASE(TPR_, ITEMS_) \
-  if (c.tpr == TPR_ && c.items == ITEMS_) return launch_row<KIND, T, ITEMS_, TPR_>(p, stream);
-  NB200_ROW_CASE(32, 1)
-  NB200_ROW_CASE(32, 2)
-  NB200_ROW_CASE(32, 4)
-  NB200_ROW_CASE(32, 8)
-  NB200_ROW_CASE(128, 4)
-  NB200_ROW_CASE(128, 8)
-  NB200_ROW_CASE(256, 4)
-  NB200_ROW_CASE(256, 8)
-  NB200_ROW_CASE(512, 2)
-  NB200_ROW_CASE(512, 4)
-  NB200_ROW_CASE(512, 8)
-  NB200_ROW_CASE(1024, 8)
+  // rows per CTA: 4 when a warp owns a row; 2 for 128-thread rows so that a
+  // 256-thread CTA shares one staged copy of weight and bias
+  const int rpb = tuning("row_rpb", 0);
+#define NB200_ROW_CASE(TPR_, ITEMS_, RPB_)                          \
+  if (c.tpr == TPR_ && c.items == ITEMS_ && (rpb == 0 || rpb == RPB_)) \
+    return launch_row<KIND, T, ITEMS_, TPR_, RPB_>(p, stream);
+  NB200_ROW_CASE(32, 1, 4)
+  NB200_ROW_CASE(32, 2, 4)
+  NB200_ROW_CASE(32, 4, 4)
+  NB200_ROW_CASE(32, 8, 4)
+  NB200_ROW_CASE(128, 4, 2)
+  NB200_ROW_CASE(128, 4, 1)
+  NB200_ROW_CASE(128, 8, 1)
+  NB200_ROW_CASE(256, 2, 1)
+  NB200_ROW_CASE(256, 4, 1)
+  NB200_ROW_CASE(256, 8, 1)
+  NB200_ROW_CASE(512, 2, 1)
+  NB200_ROW_CASE(512, 4, 1)
+  NB200_ROW_CASE(512, 8, 1)
+  NB200_ROW_CASE(1024, 8, 1)
 #undef NB200_ROW_CASE
-  return fail(NB200_E_INVALID, "no row kernel for threads-per-row=%d vectors-per-thread=%d",
-              c.tpr, c.items);
+  return fail(NB200_E_INVALID,
+              "no row kernel for threads-per-row=%d vectors-per-thread=%d rows-per-cta=%d", c.tpr,
+              c.items, rpb);
 }
 
 int check_rows(const void* x, const void* out, int64_t rows, int64_t n) {
