@@ -66,25 +66,28 @@ __device__ __forceinline__ void st_stream(void* p, uint4 v) {
 
 // Loads the vector that covers columns [col, col + kPerVec) of a row.  Lanes
 // past `n` get `fill`.  `vec_ok` says the row base is 16-byte aligned.
-template <typename T>
+// FAST is the launch-time promise that every row base is 16-byte aligned and
+// that n is a multiple of the vector width, so a vector is either entirely
+// inside the row or entirely padding and no element-wise fallback is compiled.
+template <typename T, bool FAST = false>
 __device__ __forceinline__ Vec<T> load_vec(const T* row, int col, int n, bool vec_ok, T fill) {
   constexpr int E = Elem<T>::kPerVec;
   Vec<T> v;
-  if (vec_ok && col + E <= n) {
+  if ((FAST || vec_ok) && col + E <= n) {
     v.raw = ld_stream(row + col);
   } else {
 #pragma unroll
-    for (int j = 0; j < E; ++j) v.e[j] = (col + j < n) ? row[col + j] : fill;
+    for (int j = 0; j < E; ++j) v.e[j] = (!FAST && col + j < n) ? row[col + j] : fill;
   }
   return v;
 }
 
-template <typename T>
+template <typename T, bool FAST = false>
 __device__ __forceinline__ void store_vec(T* row, int col, int n, bool vec_ok, const Vec<T>& v) {
   constexpr int E = Elem<T>::kPerVec;
-  if (vec_ok && col + E <= n) {
+  if ((FAST || vec_ok) && col + E <= n) {
     st_stream(row + col, v.raw);
-  } else {
+  } else if constexpr (!FAST) {
 #pragma unroll
     for (int j = 0; j < E; ++j)
       if (col + j < n) row[col + j] = v.e[j];
@@ -160,13 +163,13 @@ struct RowOccupancy {
   static constexpr int kMinBlocks = kThreadsPerSm / THREADS > 0 ? kThreadsPerSm / THREADS : 1;
 };
 
-template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB>
+template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB, bool FAST>
 __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVec, TPR * RPB>::kMinBlocks)
     row_kernel(RowParams p) {
   constexpr int E = Elem<T>::kPerVec;
   constexpr int W = TPR > kWarp ? TPR / kWarp : 1;
   __shared__ float red[RPB][2][W];
-  extern __shared__ float4 wb_smem[];  // fp32 w[ITEMS*TPR*E] then b[...] when p.wb_in_smem
+  extern __shared__ float4 wb_smem[];  // fp32 weight then bias, as float4 [ITEMS][E/4][TPR] each
 
   const int lane_in_row = threadIdx.x % TPR;
   const int row_in_cta = threadIdx.x / TPR;
@@ -183,18 +186,22 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
     w_ok = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     b_ok = (reinterpret_cast<uintptr_t>(b) & 15) == 0;
     if (p.wb_in_smem) {
-      float* ws = reinterpret_cast<float*>(wb_smem);
-      float* bs = ws + ITEMS * TPR * E;
+      // consecutive threads own consecutive float4 slots: no bank conflicts
+      float4* ws4 = wb_smem;
+      float4* bs4 = wb_smem + ITEMS * (E / 4) * TPR;
       if (row_in_cta == 0) {
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
           const int col = (i * TPR + lane_in_row) * E;
-          const Vec<T> wv = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
-          const Vec<T> bv = load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
+          const Vec<T> wv = load_vec<T, FAST>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
+          const Vec<T> bv = load_vec<T, FAST>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
 #pragma unroll
-          for (int j = 0; j < E; ++j) {
-            ws[col + j] = Elem<T>::to_f32(wv.e[j]);
-            bs[col + j] = Elem<T>::to_f32(bv.e[j]);
+          for (int h = 0; h < E / 4; ++h) {
+            const int slot = (i * (E / 4) + h) * TPR + lane_in_row;
+            ws4[slot] = make_float4(Elem<T>::to_f32(wv.e[4 * h]), Elem<T>::to_f32(wv.e[4 * h + 1]),
+                                    Elem<T>::to_f32(wv.e[4 * h + 2]), Elem<T>::to_f32(wv.e[4 * h + 3]));
+            bs4[slot] = make_float4(Elem<T>::to_f32(bv.e[4 * h]), Elem<T>::to_f32(bv.e[4 * h + 1]),
+                                    Elem<T>::to_f32(bv.e[4 * h + 2]), Elem<T>::to_f32(bv.e[4 * h + 3]));
           }
         }
       }
@@ -209,7 +216,8 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
     const T* xr = x + (int64_t)row * p.stride_x;
     const bool ok = (reinterpret_cast<uintptr_t>(xr) & 15) == 0;
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) nxt[i] = load_vec<T>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
+    for (int i = 0; i < ITEMS; ++i)
+      nxt[i] = load_vec<T, FAST>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
   }
   float* red0 = red[row_in_cta][0];
   float* red1 = red[row_in_cta][1];
@@ -231,7 +239,7 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
       const bool ok = (reinterpret_cast<uintptr_t>(xr) & 15) == 0;
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i)
-        nxt[i] = load_vec<T>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
+        nxt[i] = load_vec<T, FAST>(xr, (i * TPR + lane_in_row) * E, n, ok, fill);
     }
 
     T* orow = out + (int64_t)row * p.stride_out;
@@ -272,7 +280,8 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
         for (int i = 0; i < ITEMS; ++i)
 #pragma unroll
           for (int j = 0; j < E; ++j) {
-            const int col = (i * TPR + lane_in_row) * E + j;
+            // FAST: a vector is all row or all padding, one test per vector
+            const int col = (i * TPR + lane_in_row) * E + (FAST ? 0 : j);
             const float d = col < n ? v[i * E + j] - mean : 0.0f;
             v[i * E + j] = d;
             q = fmaf(d, d, q);
@@ -282,12 +291,12 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
       const float rstd = rsqrtf(var + p.eps);
       if (p.wb_in_smem) {
         const float4* ws4 = wb_smem;
-        const float4* bs4 = wb_smem + ITEMS * TPR * E / 4;
+        const float4* bs4 = wb_smem + ITEMS * (E / 4) * TPR;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
 #pragma unroll
           for (int j = 0; j < E; j += 4) {
-            const int q4 = ((i * TPR + lane_in_row) * E + j) / 4;
+            const int q4 = (i * (E / 4) + j / 4) * TPR + lane_in_row;
             const float4 wv = ws4[q4], bv = bs4[q4];
             v[i * E + j + 0] = fmaf(v[i * E + j + 0] * rstd, wv.x, bv.x);
             v[i * E + j + 1] = fmaf(v[i * E + j + 1] * rstd, wv.y, bv.y);
@@ -298,8 +307,8 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
           const int col = (i * TPR + lane_in_row) * E;
-          const Vec<T> wv = load_vec<T>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
-          const Vec<T> bv = load_vec<T>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
+          const Vec<T> wv = load_vec<T, FAST>(w, col, n, w_ok, Elem<T>::from_f32(0.0f));
+          const Vec<T> bv = load_vec<T, FAST>(b, col, n, b_ok, Elem<T>::from_f32(0.0f));
 #pragma unroll
           for (int j = 0; j < E; ++j)
             v[i * E + j] = fmaf(v[i * E + j] * rstd, Elem<T>::to_f32(wv.e[j]),
@@ -313,7 +322,7 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
       Vec<T> o;
 #pragma unroll
       for (int j = 0; j < E; ++j) o.e[j] = Elem<T>::from_f32(v[i * E + j]);
-      store_vec<T>(orow, (i * TPR + lane_in_row) * E, n, out_ok, o);
+      store_vec<T, FAST>(orow, (i * TPR + lane_in_row) * E, n, out_ok, o);
     }
   }
 }
@@ -386,9 +395,9 @@ bool pick_row_config(int64_t n, int elems_per_vec, RowConfig* cfg) {
   return false;
 }
 
-template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB>
-int launch_row(const RowParams& p, cudaStream_t stream) {
-  auto kern = row_kernel<KIND, T, ITEMS, TPR, RPB>;
+template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB, bool FAST>
+int launch_row_variant(const RowParams& p, cudaStream_t stream) {
+  auto kern = row_kernel<KIND, T, ITEMS, TPR, RPB, FAST>;
   const DeviceInfo& dev = device_info();
   RowParams q = p;
   size_t smem = 0;
@@ -416,6 +425,24 @@ int launch_row(const RowParams& p, cudaStream_t stream) {
   const int grid = (int)(want < cap ? want : cap);
   kern<<<grid, TPR * RPB, smem, stream>>>(q);
   return cuda_check(cudaGetLastError(), "row kernel launch");
+}
+
+// FAST needs 16-byte aligned row bases for every tensor and whole vectors only.
+template <typename T>
+bool rows_are_vector_friendly(const RowParams& p) {
+  constexpr int E = Elem<T>::kPerVec;
+  auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (p.n % E || p.stride_x % E || p.stride_out % E) return false;
+  if (!aligned(p.x) || !aligned(p.out)) return false;
+  if (p.w && (!aligned(p.w) || !aligned(p.b))) return false;
+  return true;
+}
+
+template <RowKind KIND, typename T, int ITEMS, int TPR, int RPB>
+int launch_row(const RowParams& p, cudaStream_t stream) {
+  if (rows_are_vector_friendly<T>(p) && !tuning("row_force_slow", 0))
+    return launch_row_variant<KIND, T, ITEMS, TPR, RPB, true>(p, stream);
+  return launch_row_variant<KIND, T, ITEMS, TPR, RPB, false>(p, stream);
 }
 
 template <RowKind KIND, typename T>
