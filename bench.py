@@ -161,9 +161,8 @@ class SoftmaxWorkload(Workload):
         return {"x": x, "out": torch.empty_like(x)}
 
     def step(self, dev):
-        from newt_b200.runtime import kernels
-        x, out = dev["x"], dev["out"]
-        kernels.softmax_f32(x, out, self.M, self.N, x.stride(0), out.stride(0))
+        from newt_b200 import examples
+        examples.softmax(dev["x"], dev["out"])     # @newt.jit softmax_kernel[(M,)](...)
 
     def result(self, dev):
         return dev["out"]
@@ -195,10 +194,8 @@ class LayerNormWorkload(Workload):
         return {"x": x, "w": w, "b": b, "out": torch.empty_like(x)}
 
     def step(self, dev):
-        from newt_b200.runtime import kernels
-        x, out = dev["x"], dev["out"]
-        kernels.layernorm(x, dev["w"], dev["b"], out, self.M, self.N, x.stride(0), out.stride(0),
-                          1e-5)
+        from newt_b200 import examples
+        examples.layernorm(dev["x"], dev["w"], dev["b"], 1e-5, dev["out"])   # @newt.jit kernel
 
     def result(self, dev):
         return dev["out"]
@@ -218,8 +215,57 @@ class LayerNormWorkload(Workload):
                 "l2": "flushed between steps"}
 
 
-WORKLOADS = {w.name: w for w in (SoftmaxWorkload, LayerNormWorkload)}
-DEFAULT_WORKLOAD = "softmax"
+class MatmulWorkload(Workload):
+    """bf16 C = A @ B through the deuteron tile loop; one 8192-row block of A per GPU."""
+
+    name, metric, unit, dtype, bound = "matmul", "matmul_tflops", "TFLOP/s", "bf16", "tensor"
+    M = N = K = 8192
+    CPU_ROWS = 1024
+
+    def __init__(self):
+        from newt_b200 import examples
+
+        self.kernel = examples.tile_matmul   # the @dt.kernel tile loop; first call autotunes
+
+    def host_inputs(self, rank, world):
+        scale = 1.0 / self.K ** 0.5
+        return [_seeded((self.M, self.K), 40 + rank, torch.bfloat16, scale),   # block `rank` of A
+                _seeded((self.K, self.N), 4, torch.bfloat16, scale)]           # B, same on every rank
+
+    def to_device(self, host):
+        a, b = (h.cuda(non_blocking=True) for h in host)
+        return {"a": a, "b": b, "out": torch.empty(self.M, self.N, device="cuda",
+                                                   dtype=torch.bfloat16)}
+
+    def step(self, dev):
+        self.kernel(dev["a"], dev["b"], dev["out"])
+
+    def result(self, dev):
+        return dev["out"]
+
+    def units_per_step(self):
+        return 2 * self.M * self.N * self.K
+
+    def cpu_sample(self, host):
+        from oracle import torch_ref
+        a, b = host
+        rows = a[:self.CPU_ROWS]
+        out = torch.empty(self.CPU_ROWS, self.N, dtype=torch.bfloat16)
+        return (lambda: torch_ref.deuteron_matmul(rows, b, out)), \
+            2 * self.CPU_ROWS * self.N * self.K, \
+            f"{self.CPU_ROWS} of the block's 8192 rows (eager tile loop, fp32 accumulate)"
+
+    def config(self, world):
+        return {"workload": "bf16 matmul, one [8192,8192] block of A per GPU x B [8192,8192] "
+                            "(deuteron @dt.kernel tile loop, fp32 accumulate)",
+                "m_per_gpu": self.M, "n": self.N, "k": self.K, "global_m": self.M * world,
+                "parallelism": f"A row-blocks over {world} GPU(s), B replicated, no collective",
+                "l2": "flushed between steps",
+                "tile": dict(self.kernel.best_config or {})}
+
+
+WORKLOADS = {w.name: w for w in (MatmulWorkload, SoftmaxWorkload, LayerNormWorkload)}
+DEFAULT_WORKLOAD = "matmul"
 
 
 # --------------------------------------------------------------------------- runners

@@ -1,0 +1,119 @@
+"""`@jit` kernels of examples/01-04 of the reference and their launch wrappers."""
+
+import torch
+
+import newt_b200 as newt
+import newt_b200.language as nl
+
+
+@newt.jit
+def add_kernel(x_ptr, y_ptr, out_ptr, n, BLOCK: nl.constexpr):
+    pid = nl.program_id(0)
+    offs = pid * BLOCK + nl.arange(0, BLOCK)
+    mask = offs < n
+    x = nl.load(x_ptr + offs, mask=mask)
+    y = nl.load(y_ptr + offs, mask=mask)
+    nl.store(out_ptr + offs, x + y, mask=mask)
+
+
+def add(x, y, out=None):
+    """examples/01_vector_add.py:24-29"""
+    out = torch.empty_like(x) if out is None else out
+    n = x.numel()
+    add_kernel[lambda meta: (newt.cdiv(n, meta["BLOCK"]),)](x, y, out, n, BLOCK=4096)
+    return out
+
+
+@newt.jit
+def softmax_kernel(x_ptr, out_ptr, N, stride, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=float("-inf"))
+    x = x - nl.max(x, axis=0)
+    num = nl.exp(x)
+    den = nl.sum(num, axis=0)
+    nl.store(out_ptr + row * stride + cols, num / den, mask=mask)
+
+
+def softmax(x, out=None):
+    """examples/02_fused_softmax.py:27-33"""
+    m, n = x.shape
+    out = torch.empty_like(x) if out is None else out
+    block = newt.next_power_of_2(n)
+    softmax_kernel[(m,)](x, out, n, x.stride(0), BLOCK_N=block,
+                         num_warps=4 if block < 4096 else 8)
+    return out
+
+
+@newt.jit
+def layernorm_kernel(x_ptr, w_ptr, b_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=0.0)
+    mean = nl.sum(x, axis=0) / N
+    diff = nl.where(mask, x - mean, 0.0)
+    var = nl.sum(diff * diff, axis=0) / N
+    rstd = nl.rsqrt(var + eps)
+    w = nl.load(w_ptr + cols, mask=mask)
+    b = nl.load(b_ptr + cols, mask=mask)
+    y = (x - mean) * rstd * w + b
+    nl.store(out_ptr + row * stride + cols, y, mask=mask)
+
+
+def layernorm(x, w, b, eps=1e-5, out=None):
+    """examples/03_layernorm.py:30-36"""
+    m, n = x.shape
+    out = torch.empty_like(x) if out is None else out
+    layernorm_kernel[(m,)](x, w, b, out, n, x.stride(0), eps,
+                           BLOCK_N=newt.next_power_of_2(n), num_warps=8)
+    return out
+
+
+# Tile / pipeline choices for sm_100a: 128-row tcgen05 MMAs, 64..256 columns, 64-element
+# K slabs per TMA stage, ring depth as num_stages.
+@newt.autotune(
+    configs=[
+        newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=4),
+        newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=3),
+        newt.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_warps=4, num_stages=6),
+        newt.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_warps=4, num_stages=4),
+        newt.Config({"BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64}, num_warps=4, num_stages=8),
+    ],
+    key=["M", "N", "K"],
+)
+@newt.jit
+def matmul_kernel(a_ptr, b_ptr, c_ptr, M, N, K,
+                  sam, sak, sbk, sbn, scm, scn,
+                  BLOCK_M: nl.constexpr, BLOCK_N: nl.constexpr, BLOCK_K: nl.constexpr):
+    pid_m = nl.program_id(0)
+    pid_n = nl.program_id(1)
+    offs_m = pid_m * BLOCK_M + nl.arange(0, BLOCK_M)
+    offs_n = pid_n * BLOCK_N + nl.arange(0, BLOCK_N)
+    offs_k = nl.arange(0, BLOCK_K)
+    a_ptrs = a_ptr + offs_m[:, None] * sam + offs_k[None, :] * sak
+    b_ptrs = b_ptr + offs_k[:, None] * sbk + offs_n[None, :] * sbn
+    acc = nl.zeros((BLOCK_M, BLOCK_N), dtype=nl.float32)
+    for k in range(nl.cdiv(K, BLOCK_K)):
+        a_mask = (offs_m[:, None] < M) & (offs_k[None, :] < K - k * BLOCK_K)
+        b_mask = (offs_k[:, None] < K - k * BLOCK_K) & (offs_n[None, :] < N)
+        a = nl.load(a_ptrs, mask=a_mask, other=0.0)
+        b = nl.load(b_ptrs, mask=b_mask, other=0.0)
+        acc = nl.dot(a, b, acc)
+        a_ptrs += BLOCK_K * sak
+        b_ptrs += BLOCK_K * sbk
+    c_ptrs = c_ptr + offs_m[:, None] * scm + offs_n[None, :] * scn
+    c_mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+    nl.store(c_ptrs, acc.to(c_ptr.dtype.element_ty), mask=c_mask)
+
+
+def matmul(a, b, c=None):
+    """examples/04_matmul.py:48-56"""
+    m, k = a.shape
+    _, n = b.shape
+    c = torch.empty(m, n, device=a.device, dtype=a.dtype) if c is None else c
+    grid = lambda meta: (newt.cdiv(m, meta["BLOCK_M"]), newt.cdiv(n, meta["BLOCK_N"]))  # noqa: E731
+    matmul_kernel[grid](a, b, c, m, n, k, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+                        c.stride(0), c.stride(1))
+    return c

@@ -1,0 +1,735 @@
+"""Lowering: traced kernel graph -> launch plan on a hand-written sm_100a kernel.
+
+The reference lowers every kernel through one generic emitter
+(newt/compiler/codegen.py).  This backend instead owns a small set of
+hand-written kernels (libnewt_b200.so) and recognises the programs they
+implement:
+
+    elementwise add          examples/01_vector_add.py:14-21
+    fused row softmax        examples/02_fused_softmax.py:15-24
+    layernorm forward        examples/03_layernorm.py:13-27
+    matmul K loop (nl.dot)   examples/04_matmul.py:14-45, benchmarks/bench.py:90-108,
+                             and the text deuteron generates (deuteron/codegen.py:104-175)
+    flash attention loop     examples/05_fused_attention.py:14-48 (+ batch*heads, causal)
+
+Recognition is structural (on the expression graph, not on source text) and
+every quantity a kernel needs -- extents, strides, which argument plays which
+role -- is recovered from the graph as a polynomial in the runtime arguments
+and evaluated at launch.  A program that matches none of them raises
+CompileError naming what is missing; nothing falls back to another backend.
+"""
+
+from .. import types as tp
+from .affine import Analyzer, NotAffine, Poly
+from .trace import CompileError, Node
+
+
+class Unmatched(Exception):
+    """Internal: this recogniser does not apply (reason for diagnostics)."""
+
+
+# --------------------------------------------------------------------------- patterns
+
+class Cap:
+    """Pattern wildcard: binds a name to whatever node stands there; a name used
+    twice must bind the same node."""
+
+    def __init__(self, name, pred=None):
+        self.name = name
+        self.pred = pred
+
+
+class Pat:
+    def __init__(self, op, args, **attrs):
+        self.op = op
+        self.args = args
+        self.attrs = attrs
+
+
+def p_bin(fn, a, b):
+    return Pat("bin", [a, b], fn=fn)
+
+
+def p_math(fn, x):
+    return Pat("math", [x], fn=fn)
+
+
+def p_reduce(fn, x):
+    return Pat("reduce", [x], fn=fn)
+
+
+def p_const(value):
+    return Pat("const", [value])
+
+
+def match(pat, node, caps):
+    if isinstance(pat, Cap):
+        if pat.name in caps:
+            return caps[pat.name] is node
+        if pat.pred is not None and not pat.pred(node):
+            return False
+        caps[pat.name] = node
+        return True
+    if isinstance(pat, Pat):
+        if not isinstance(node, Node) or node.op != pat.op:
+            return False
+        attrs = dict(node.attrs)
+        for k, v in pat.attrs.items():
+            if attrs.get(k) != v:
+                return False
+        if len(pat.args) != len(node.args):
+            return False
+        return all(match(p, a, caps) for p, a in zip(pat.args, node.args))
+    # literal
+    if isinstance(node, Node):
+        return False
+    if isinstance(pat, float) and isinstance(node, (int, float)):
+        return float(node) == pat or (pat != pat and node != node)
+    return pat == node
+
+
+def match_commutative(fn, pa, pb, node, caps):
+    """bin(fn, pa, pb) with the operands in either order."""
+    for x, y in ((pa, pb), (pb, pa)):
+        trial = dict(caps)
+        if match(p_bin(fn, x, y), node, trial):
+            caps.clear()
+            caps.update(trial)
+            return True
+    return False
+
+
+# --------------------------------------------------------------------------- helpers
+
+def _param_only(poly):
+    return all(a[0] == "param" for a in poly.atoms())
+
+
+def _compile_int(poly):
+    """Host function args_dict -> int for a polynomial in runtime parameters."""
+    if not _param_only(poly):
+        raise Unmatched(f"quantity {poly!r} depends on more than runtime arguments")
+    c = poly.const_value()
+    if c is not None:
+        return lambda a, _c=c: _c
+    return eval("lambda a: " + poly.to_python("a"))  # noqa: S307 - generated from a Poly
+
+
+def _param_name(node):
+    if isinstance(node, Node) and node.op == "param":
+        return dict(node.attrs)["name"]
+    return None
+
+
+def _top_level_stores(trace):
+    return [e for e in trace.effects if e[0] == "store"]
+
+
+def _loops(trace):
+    return [e[1] for e in trace.effects if e[0] == "for"]
+
+
+class RowAccess:
+    """A 1-D pointer block `base + row_offset(pid) + (ax0 + c)`: one contiguous
+    row per program."""
+
+    def __init__(self, an, ptr, rank1_only=True):
+        if len(ptr.shape) != 1:
+            raise Unmatched("not a 1-D pointer block")
+        self.base, poly = an.pointer(ptr)
+        qr = poly.coeff_of(("ax", 0))
+        if qr is None:
+            raise Unmatched("non-linear column index")
+        q, r = qr
+        if q.const_value() != 1:
+            raise Unmatched("columns are not unit-stride")
+        if r.has_kind("ax", "iter", "carried"):
+            raise Unmatched("row offset depends on more than the program id")
+        self.pid_axes = sorted(a[1] for a in r.atoms() if a[0] == "pid")
+        self.offset = r  # polynomial in pid + params
+
+
+def _mask_bound_1d(an, mask, index_poly):
+    """For mask == (index < bound) returns the polynomial `bound - (index - ax0)`,
+    i.e. the number of valid columns counted from ax0 = 0; `index_poly` is the
+    element index the pointers use (without base offset)."""
+    if mask is None:
+        return None
+    if mask.op != "cmp":
+        raise Unmatched("mask is not a single comparison")
+    fn = dict(mask.attrs)["fn"]
+    a, b = mask.args
+    try:
+        pa, pb = an._aligned(a, b, len(mask.shape))
+    except NotAffine as e:
+        raise Unmatched(f"mask is not affine ({e})")
+    if fn == "lt":
+        d = pa - pb          # d < 0
+    elif fn == "gt":
+        d = pb - pa
+    else:
+        raise Unmatched(f"mask comparison '{fn}'")
+    qr = d.coeff_of(("ax", 0))
+    if qr is None or qr[0].const_value() != 1:
+        raise Unmatched("mask does not bound the column index")
+    rest = qr[1]            # ax0 + rest < 0  ->  ax0 < -rest
+    return -rest
+
+
+# --------------------------------------------------------------------------- plans
+
+class Plan:
+    """What one specialization of a kernel does at launch."""
+
+    kind = ""
+    entry = ""       # C-ABI entry point the plan calls
+
+    def launch(self, grid, args):
+        raise NotImplementedError
+
+    def describe(self):
+        return f"{self.kind} -> {self.entry}"
+
+
+def _split_row_offset(off, what):
+    """off = pid0 * stride + const  (polynomials in runtime params)."""
+    qr = off.coeff_of(("pid", 0))
+    if qr is None:
+        raise Unmatched(f"{what}: row offset is not linear in program_id(0)")
+    stride, const = qr
+    if not _param_only(stride) or not _param_only(const):
+        raise Unmatched(f"{what}: row offset uses more than program_id(0) and arguments")
+    return stride, const
+
+
+class SoftmaxPlan(Plan):
+    kind, entry = "row softmax", "nb200_softmax_f32"
+
+    def __init__(self, x, out, n, block, sx, cx, so, co):
+        self.x, self.out, self.block = x, out, block
+        self.n, self.sx, self.cx, self.so, self.co = map(_compile_int, (n, sx, cx, so, co))
+
+    def launch(self, grid, args):
+        from ..runtime import kernels
+
+        rows = grid[0]
+        n = min(self.n(args), self.block)
+        if rows <= 0 or n <= 0:
+            return
+        x, out = args[self.x], args[self.out]
+        cx, co = self.cx(args), self.co(args)
+        if cx:
+            x = x.reshape(-1)[cx:] if x.is_contiguous() else _offset_view(x, cx)
+        if co:
+            out = out.reshape(-1)[co:] if out.is_contiguous() else _offset_view(out, co)
+        kernels.softmax_f32(x, out, rows, n, self.sx(args), self.so(args))
+
+
+class LayerNormPlan(Plan):
+    kind, entry = "layernorm forward", "nb200_layernorm"
+
+    def __init__(self, x, w, b, out, eps, n, block, sx, so):
+        self.x, self.w, self.b, self.out, self.eps, self.block = x, w, b, out, eps, block
+        self.n, self.sx, self.so = map(_compile_int, (n, sx, so))
+
+    def launch(self, grid, args):
+        from ..runtime import kernels
+
+        rows = grid[0]
+        n = min(self.n(args), self.block)
+        if rows <= 0 or n <= 0:
+            return
+        eps = args[self.eps] if isinstance(self.eps, str) else self.eps
+        kernels.layernorm(args[self.x], args[self.w], args[self.b], args[self.out], rows, n,
+                          self.sx(args), self.so(args), eps)
+
+
+class AddPlan(Plan):
+    kind, entry = "elementwise add", "nb200_add_f32"
+
+    def __init__(self, x, y, out, n, block):
+        self.x, self.y, self.out, self.block = x, y, out, block
+        self.n = _compile_int(n) if n is not None else None
+
+    def launch(self, grid, args):
+        from ..runtime import kernels
+
+        covered = grid[0] * self.block
+        n = covered if self.n is None else min(self.n(args), covered)
+        if n <= 0:
+            return
+        kernels.add_f32(args[self.x], args[self.y], args[self.out], n)
+
+
+def _offset_view(t, elems):
+    import torch
+
+    return torch.as_strided(t, (t.numel() - elems,), (1,), t.storage_offset() + elems)
+
+
+# --------------------------------------------------------------------------- row recognisers
+
+def _single_store(trace, what):
+    if _loops(trace):
+        raise Unmatched(f"{what}: kernel has a runtime loop")
+    stores = _top_level_stores(trace)
+    if len(stores) != 1:
+        raise Unmatched(f"{what}: expected exactly one store, found {len(stores)}")
+    return stores[0]
+
+
+def lower_add(trace, an):
+    _, ptr, value, mask, _ = _single_store(trace, "add")
+    x, y = Cap("x"), Cap("y")
+    caps = {}
+    if not match(p_bin("add", Pat("load", [x, Cap("mx"), Cap("ox")]),
+                       Pat("load", [y, Cap("my"), Cap("oy")])), value, caps):
+        raise Unmatched("add: stored value is not load(x) + load(y)")
+    if caps["mx"] is not mask or caps["my"] is not mask:
+        raise Unmatched("add: loads and store use different masks")
+    accs = [RowAccess(an, p) for p in (caps["x"], caps["y"], ptr)]
+    block = ptr.shape[0]
+    for acc, nm in zip(accs, "xyo"):
+        if acc.offset != accs[0].offset:
+            raise Unmatched("add: operands are addressed differently")
+    stride, const = _split_row_offset(accs[0].offset, "add")
+    if stride.const_value() != block or not const.is_zero():
+        raise Unmatched("add: programs do not tile the vector contiguously")
+    for node in (caps["x"], caps["y"], ptr):
+        if node.dtype.element != tp.float32:
+            raise Unmatched("add: only float32 vectors have a kernel")
+    n = None
+    if mask is not None:
+        bound = _mask_bound_1d(an, mask, None)   # ax0 < bound, bound = n - pid0*BLOCK
+        n = bound + Poly.atom(("pid", 0)) * Poly.const(block)
+        if not _param_only(n):
+            raise Unmatched("add: mask is not `offsets < n`")
+    return AddPlan(accs[0].base, accs[1].base, accs[2].base, n, block)
+
+
+def _row_common(an, ptr_x, ptr_o, mask, what):
+    ax, ao = RowAccess(an, ptr_x), RowAccess(an, ptr_o)
+    block = ptr_x.shape[0]
+    sx, cx = _split_row_offset(ax.offset, what)
+    so, co = _split_row_offset(ao.offset, what)
+    n = Poly.const(block)
+    if mask is not None:
+        n = _mask_bound_1d(an, mask, None)
+        if not _param_only(n):
+            raise Unmatched(f"{what}: column mask is not `cols < N`")
+    return ax, ao, block, sx, cx, so, co, n
+
+
+def lower_softmax(trace, an):
+    _, ptr, value, mask, _ = _single_store(trace, "softmax")
+    x = Cap("x", lambda n: isinstance(n, Node) and n.op == "load")
+    shifted = p_bin("sub", x, p_reduce("max", x))
+    num = p_math("exp", shifted)
+    caps = {}
+    if not match(p_bin("div", num, p_reduce("sum", num)), value, caps):
+        raise Unmatched("softmax: stored value is not exp(x - max(x)) / sum(exp(x - max(x)))")
+    load = caps["x"]
+    ptr_x, lmask, other = load.args
+    if lmask is not mask:
+        raise Unmatched("softmax: load and store use different masks")
+    if lmask is not None and other != float("-inf"):
+        raise Unmatched("softmax: masked lanes must load -inf")
+    if load.dtype != tp.float32 or ptr.dtype.element != tp.float32:
+        raise Unmatched("softmax: only float32 rows have a kernel")
+    ax, ao, block, sx, cx, so, co, n = _row_common(an, ptr_x, ptr, mask, "softmax")
+    return SoftmaxPlan(ax.base, ao.base, n, block, sx, cx, so, co)
+
+
+def lower_layernorm(trace, an):
+    _, ptr, value, mask, _ = _single_store(trace, "layernorm")
+    is_load = lambda n: isinstance(n, Node) and n.op == "load"  # noqa: E731
+    x, w, b = Cap("x", is_load), Cap("w", is_load), Cap("b", is_load)
+    count, eps = Cap("count"), Cap("eps")
+    mean = p_bin("div", p_reduce("sum", x), count)
+    centred = p_bin("sub", x, mean)
+    diff_masked = Pat("where", [Cap("wmask"), centred, p_const(0.0)])
+    caps = {}
+    ok = False
+    for diff in (diff_masked, centred):
+        var = p_bin("div", p_reduce("sum", p_bin("mul", diff, diff)), count)
+        rstd = p_math("rsqrt", p_bin("add", var, eps))
+        trial = {}
+        if match(p_bin("add", p_bin("mul", p_bin("mul", centred, rstd), w), b), value, trial):
+            caps, ok = trial, True
+            break
+    if not ok:
+        raise Unmatched("layernorm: stored value is not (x - mean) * rsqrt(var + eps) * w + b "
+                        "with two-pass statistics")
+    lx, lw, lb = caps["x"], caps["w"], caps["b"]
+    if "wmask" in caps and caps["wmask"] is not mask:
+        raise Unmatched("layernorm: variance mask differs from the load mask")
+    if "wmask" not in caps and mask is not None:
+        raise Unmatched("layernorm: padded lanes are not masked out of the variance")
+    for ld in (lx, lw, lb):
+        if ld.args[1] is not mask:
+            raise Unmatched("layernorm: loads use different masks")
+    if lx.args[2] not in (None, 0.0, 0):
+        raise Unmatched("layernorm: masked lanes of x must load 0")
+    dt = lx.dtype
+    if dt not in (tp.float32, tp.float16, tp.bfloat16) or lw.dtype != dt or lb.dtype != dt \
+            or ptr.dtype.element != dt:
+        raise Unmatched("layernorm: x, w, b and out must share one of float32/float16/bfloat16")
+    ax, ao, block, sx, cx, so, co, n = _row_common(an, lx.args[0], ptr, mask, "layernorm")
+    if not cx.is_zero() or not co.is_zero():
+        raise Unmatched("layernorm: constant pointer offsets are not supported")
+    for ld, nm in ((lw, "w"), (lb, "b")):
+        acc = RowAccess(an, ld.args[0])
+        if not acc.offset.is_zero():
+            raise Unmatched(f"layernorm: {nm} must be indexed by the column only")
+    # the divisor of both statistics must be the row length
+    cnt = caps["count"]
+    try:
+        cnt_poly = an.poly(cnt)
+    except NotAffine:
+        raise Unmatched("layernorm: divisor is not an integer count")
+    if cnt_poly != n:
+        raise Unmatched("layernorm: statistics are not divided by the row length")
+    e = caps["eps"]
+    if _param_name(e) is not None:
+        eps = _param_name(e)
+    elif isinstance(e, Node) and e.op == "const":
+        eps = float(e.args[0])
+    else:
+        raise Unmatched("layernorm: eps must be an argument or a literal")
+    lwb = RowAccess(an, lw.args[0]).base, RowAccess(an, lb.args[0]).base
+    return LayerNormPlan(ax.base, lwb[0], lwb[1], ao.base, eps, n, block, sx, so)
+
+
+# --------------------------------------------------------------------------- scalar expressions
+
+_PY_OPS = {"add": "({0} + {1})", "sub": "({0} - {1})", "mul": "({0} * {1})",
+           "floordiv": "({0} // {1})", "div": "({0} // {1})", "mod": "({0} % {1})",
+           "cdiv": "(-(-{0} // {1}))", "min": "min({0}, {1})", "max": "max({0}, {1})"}
+
+
+def _scalar_source(v):
+    """Python source for an integer scalar of the graph, over the dict `a` of
+    runtime arguments."""
+    if isinstance(v, bool) or not isinstance(v, (int, Node)):
+        raise Unmatched(f"cannot evaluate {v!r} on the host")
+    if isinstance(v, int):
+        return repr(v)
+    if v.shape != () or not v.dtype.is_int:
+        raise Unmatched("loop bounds must be integer scalars")
+    if v.op == "const":
+        return repr(v.args[0])
+    if v.op == "param":
+        return f"a[{dict(v.attrs)['name']!r}]"
+    if v.op == "neg":
+        return f"(-{_scalar_source(v.args[0])})"
+    if v.op == "cast":
+        return _scalar_source(v.args[0])
+    if v.op == "bin":
+        fn = dict(v.attrs)["fn"]
+        if fn in _PY_OPS:
+            return _PY_OPS[fn].format(_scalar_source(v.args[0]), _scalar_source(v.args[1]))
+    raise Unmatched(f"loop bound uses '{v.op}', which the host cannot evaluate")
+
+
+def _compile_scalar(v):
+    return eval("lambda a: " + _scalar_source(v))  # noqa: S307 - generated from the graph
+
+
+def _trip_count_fn(loop):
+    lo, hi, step = (_compile_scalar(x) for x in (loop.lo, loop.hi, loop.step))
+    return lambda a: max(0, -(-(hi(a) - lo(a)) // step(a))) if step(a) > 0 else 0
+
+
+# --------------------------------------------------------------------------- 2-D tiles
+
+class TileAccess:
+    """A 2-D pointer block  base + idx0 * s0 + idx1 * s1  where each index is
+    `ax_d + (program id | loop iteration) * BLOCK_d`."""
+
+    def __init__(self, an, ptr, what):
+        if len(ptr.shape) != 2:
+            raise Unmatched(f"{what}: not a 2-D pointer block")
+        self.shape = ptr.shape
+        try:
+            self.base, poly = an.pointer(ptr)
+        except NotAffine as e:
+            raise Unmatched(f"{what}: pointer block is not affine ({e})")
+        qr0 = poly.coeff_of(("ax", 0))
+        qr1 = qr0[1].coeff_of(("ax", 1)) if qr0 else None
+        if qr0 is None or qr1 is None:
+            raise Unmatched(f"{what}: pointer block is not linear in its indices")
+        self.stride = [qr0[0], qr1[0]]
+        rest = qr1[1]
+        for s in self.stride:
+            if not _param_only(s) or s.is_zero():
+                raise Unmatched(f"{what}: strides must be runtime arguments or constants")
+        # distribute the remaining terms (pid / iter multiples) over the two dims
+        self.origin = [Poly(), Poly()]   # index offset of each dim, in elements of that dim
+        const = Poly()
+        for atom in sorted(rest.atoms(), key=repr):
+            if atom[0] == "param":
+                continue
+            if atom[0] not in ("pid", "iter"):
+                raise Unmatched(f"{what}: offset depends on {atom}")
+        leftovers = rest
+        for atom in sorted({a for a in rest.atoms() if a[0] in ("pid", "iter")}, key=repr):
+            q, leftovers = leftovers.coeff_of(atom)
+            placed = False
+            # prefer the dim whose stride is not the constant 1 (dividing by 1 always works)
+            order = sorted((0, 1), key=lambda d: self.stride[d].const_value() == 1)
+            for d in order:
+                blocks = q.divide_by(self.stride[d])
+                if blocks is not None and blocks.const_value() is not None:
+                    self.origin[d] = self.origin[d] + Poly.atom(atom) * blocks
+                    placed = True
+                    break
+            if not placed:
+                raise Unmatched(f"{what}: {atom} does not step by whole blocks")
+        if not leftovers.is_zero():
+            raise Unmatched(f"{what}: constant pointer offsets are not supported")
+
+    def step_of(self, d, kind):
+        """(atom, blocks) if dim d advances with exactly one atom of `kind`."""
+        terms = [(m, c) for m, c in self.origin[d].terms.items()]
+        if len(terms) != 1 or len(terms[0][0]) != 1 or terms[0][0][0][0] != kind:
+            return None
+        return terms[0][0][0], terms[0][1]
+
+
+def _split_and(mask):
+    if mask is None:
+        return []
+    if mask.op == "bin" and dict(mask.attrs)["fn"] == "and":
+        return _split_and(mask.args[0]) + _split_and(mask.args[1])
+    return [mask]
+
+
+def _comparison(an, term, what):
+    """(fn, lhs - rhs) of a mask term, seen through x[:, None] / x[None, :]."""
+    if term.op == "expand":
+        fn, d = _comparison(an, term.args[0], what)
+        axis = dict(term.attrs)["axis"]
+        return fn, d.map_atoms(lambda a: Poly.atom(("ax", a[1] + 1))
+                               if a[0] == "ax" and a[1] >= axis else None)
+    if term.op == "broadcast":
+        fn, d = _comparison(an, term.args[0], what)
+        k = len(term.shape) - len(term.args[0].shape)
+        return fn, d.map_atoms(lambda a: Poly.atom(("ax", a[1] + k)) if a[0] == "ax" else None)
+    if term.op != "cmp":
+        raise Unmatched(f"{what}: mask term is not a comparison")
+    try:
+        pa, pb = an._aligned(term.args[0], term.args[1], len(term.shape))
+    except NotAffine as e:
+        raise Unmatched(f"{what}: mask is not affine ({e})")
+    return dict(term.attrs)["fn"], pa - pb
+
+
+def _tile_bounds(an, mask, tile, what):
+    """Per-dimension extent polynomials implied by a mask built from
+    `index_d < bound_d` comparisons; checks that index_d is the tile's own."""
+    bounds = {}
+    for term in _split_and(mask):
+        fn, d = _comparison(an, term, what)
+        if len(term.shape) < 2:
+            d = d.map_atoms(lambda a, k=2 - len(term.shape): Poly.atom(("ax", a[1] + k))
+                            if a[0] == "ax" else None)
+        if fn == "gt":
+            d = -d
+        elif fn != "lt":
+            raise Unmatched(f"{what}: mask comparison '{fn}'")
+        dims = [k for k in (0, 1) if ("ax", k) in d.atoms()]
+        if len(dims) != 1:
+            raise Unmatched(f"{what}: a mask term must bound exactly one index")
+        k = dims[0]
+        q, rest = d.coeff_of(("ax", k))
+        if q.const_value() != 1:
+            raise Unmatched(f"{what}: mask index is scaled")
+        moving = Poly({m: c for m, c in rest.terms.items()
+                       if any(a[0] != "param" for a in m)})
+        bound = -(rest - moving)
+        if moving != tile.origin[k]:
+            raise Unmatched(f"{what}: mask bounds a different index than the pointers use")
+        bounds.setdefault(k, []).append(bound)
+    return bounds
+
+
+def _extent_fn(what, *bound_lists):
+    """Host function for an extent named by one or more masks.  All masks must
+    agree at launch: a kernel that loads with one extent and stores with another
+    is not the matmul this backend implements."""
+    polys = []
+    for bl in bound_lists:
+        for p in bl or []:
+            if p not in polys:
+                polys.append(p)
+    if not polys:
+        return None
+    fns = [_compile_int(p) for p in polys]
+    if len(fns) == 1:
+        return fns[0]
+
+    def extent(a):
+        vals = {f(a) for f in fns}
+        if len(vals) != 1:
+            raise CompileError(f"matmul: masks give different {what} extents {sorted(vals)}")
+        return vals.pop()
+
+    return extent
+
+
+# --------------------------------------------------------------------------- GEMM
+
+class GemmPlan(Plan):
+    kind, entry = "matmul K loop", "nb200_gemm"
+
+    def __init__(self):
+        self.a = self.b = self.c = None
+        self.block = (0, 0, 0)
+        self.pid_m = self.pid_n = 0
+        self.m_bound = self.n_bound = self.k_bound = None
+        self.trips = None
+        self.lda = self.ldb = self.ldc = None
+        self.inner = ()
+        self.num_stages = 3
+
+    def _extents(self, grid, args):
+        bm, bn, bk = self.block
+        gm = grid[self.pid_m] if self.pid_m < len(grid) else 1
+        gn = grid[self.pid_n] if self.pid_n < len(grid) else 1
+        m, n, k = gm * bm, gn * bn, self.trips(args) * bk
+        if self.m_bound is not None:
+            m = min(m, self.m_bound(args))
+        if self.n_bound is not None:
+            n = min(n, self.n_bound(args))
+        if self.k_bound is not None:
+            k = min(k, self.k_bound(args))
+        return max(m, 0), max(n, 0), max(k, 0)
+
+    def hardware_key(self):
+        """What distinguishes this plan on the device: the tcgen05 tile is picked by
+        BLOCK_N (when it is a tile the kernel has) and the ring depth by num_stages."""
+        bn = self.block[1] if self.block[1] in (64, 128, 256) else 0
+        return ("gemm", bn, self.num_stages)
+
+    def config(self):
+        from ..runtime import kernels
+
+        _, bn, stages = self.hardware_key()
+        return kernels.gemm_config(block_n=bn, stages=stages)
+
+    def launch(self, grid, args):
+        from ..runtime import kernels
+
+        m, n, k = self._extents(grid, args)
+        if m == 0 or n == 0:
+            return
+        for name, fn in self.inner:
+            if fn(args) != 1:
+                raise CompileError(
+                    f"matmul: '{name}' is not unit-stride along its fast dimension "
+                    f"(stride {fn(args)}); transposed operands have no sm_100a kernel yet")
+        kernels.gemm(args[self.a], args[self.b], args[self.c], m, n, k, self.lda(args),
+                     self.ldb(args), self.ldc(args), self.config())
+
+
+def lower_gemm(trace, an, num_stages):
+    loops = _loops(trace)
+    stores = _top_level_stores(trace)
+    if len(loops) != 1 or len(stores) != 1:
+        raise Unmatched("matmul: expected one K loop followed by one store")
+    loop = loops[0]
+    if loop.effects:
+        raise Unmatched("matmul: the K loop has side effects")
+    acc_name = None
+    for name, (ph, init, nxt) in loop.carried.items():
+        if nxt.op == "dot":
+            if acc_name is not None:
+                raise Unmatched("matmul: two accumulators")
+            acc_name = name
+        elif ("carried", loop.uid, name) not in an.closed_forms:
+            raise Unmatched(f"matmul: loop-carried '{name}' is neither the accumulator nor an "
+                            f"induction")
+    if acc_name is None:
+        raise Unmatched("matmul: no `acc = nl.dot(a, b, acc)` in the loop")
+    ph, init, dot = loop.carried[acc_name]
+    a, b, acc_in = dot.args
+    if acc_in is not ph:
+        raise Unmatched("matmul: nl.dot does not accumulate into the carried block")
+    if not (init.op == "full" and init.args[0] == 0):
+        raise Unmatched("matmul: accumulator does not start at zero")
+    for name, v in (("a", a), ("b", b)):
+        if v.op != "load":
+            raise Unmatched(f"matmul: operand {name} of nl.dot is not loaded directly from memory")
+        if v.args[1] is not None and v.args[2] not in (None, 0, 0.0):
+            raise Unmatched(f"matmul: masked lanes of {name} must read 0")
+    if a.dtype not in (tp.float16, tp.bfloat16):
+        raise Unmatched(f"matmul: {a.dtype.name} operands have no tcgen05 kernel yet")
+
+    _, c_ptr, c_val, c_mask, _ = stores[0]
+    out = c_val.args[0] if c_val.op == "cast" else c_val
+    at = dict(out.attrs)
+    if out.op != "loopout" or at.get("loop") != loop.uid or at.get("name") != acc_name:
+        raise Unmatched("matmul: the stored value is not the accumulator (fused epilogues are "
+                        "not supported yet)")
+    if c_ptr.dtype.element != a.dtype:
+        raise Unmatched("matmul: output dtype differs from the operand dtype")
+
+    ta = TileAccess(an, a.args[0], "matmul A")
+    tb = TileAccess(an, b.args[0], "matmul B")
+    tc = TileAccess(an, c_ptr, "matmul C")
+    bm, bk = ta.shape
+    bk2, bn = tb.shape
+    it = ("iter", loop.uid)
+    if ta.step_of(1, "iter") != (it, bk) or tb.step_of(0, "iter") != (it, bk):
+        raise Unmatched("matmul: A and B do not advance by BLOCK_K per iteration")
+    sm, sn = ta.step_of(0, "pid"), tb.step_of(1, "pid")
+    if sm is None or sn is None or sm[1] != bm or sn[1] != bn or sm[0] == sn[0]:
+        raise Unmatched("matmul: program ids do not tile M and N by BLOCK_M / BLOCK_N")
+    if tc.step_of(0, "pid") != sm or tc.step_of(1, "pid") != sn:
+        raise Unmatched("matmul: C is not addressed by the same (row, column) blocks")
+
+    ba = _tile_bounds(an, a.args[1], ta, "matmul A")
+    bb = _tile_bounds(an, b.args[1], tb, "matmul B")
+    bc = _tile_bounds(an, c_mask, tc, "matmul C")
+
+    plan = GemmPlan()
+    plan.a, plan.b, plan.c = ta.base, tb.base, tc.base
+    plan.block = (bm, bn, bk)
+    plan.pid_m, plan.pid_n = sm[0][1], sn[0][1]
+    plan.m_bound = _extent_fn("M", ba.get(0), bc.get(0))
+    plan.n_bound = _extent_fn("N", bb.get(1), bc.get(1))
+    plan.k_bound = _extent_fn("K", ba.get(1), bb.get(0))
+    plan.trips = _trip_count_fn(loop)
+    plan.lda, plan.ldb, plan.ldc = (_compile_int(t.stride[0]) for t in (ta, tb, tc))
+    plan.inner = tuple((nm, _compile_int(t.stride[1])) for nm, t in
+                       ((ta.base, ta), (tb.base, tb), (tc.base, tc)))
+    plan.num_stages = num_stages
+    return plan
+
+
+# --------------------------------------------------------------------------- driver
+
+_RECOGNISERS = []
+
+
+def lower(trace, num_warps=4, num_stages=3):
+    """Picks the launch plan for a traced kernel or raises CompileError."""
+    an = Analyzer(trace)
+    an.resolve_inductions()
+    reasons = []
+    attempts = [("add", lambda: lower_add(trace, an)),
+                ("softmax", lambda: lower_softmax(trace, an)),
+                ("layernorm", lambda: lower_layernorm(trace, an)),
+                ("matmul", lambda: lower_gemm(trace, an, num_stages))]
+    attempts += [(n, (lambda f=f: f(trace, an, num_stages))) for n, f in _RECOGNISERS]
+    for name, attempt in attempts:
+        try:
+            return attempt()
+        except Unmatched as e:
+            reasons.append(str(e))
+        except NotAffine as e:
+            reasons.append(f"{name}: address arithmetic is not affine ({e})")
+    raise CompileError(
+        f"{trace.name}: no sm_100a kernel implements this program yet (generic lowering of "
+        f"the block language is not part of this backend).  Closest matches:\n  - "
+        + "\n  - ".join(reasons))

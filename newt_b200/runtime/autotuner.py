@@ -1,0 +1,127 @@
+"""`@autotune` / `@heuristics`, with the interface of newt/runtime/autotuner.py.
+
+`Config(kwargs, num_warps=4, num_stages=1)` and `.best_config`, the cache key
+(values of `key` arguments plus the dtypes of all tensor arguments, :36-52) and
+the handling of `reset_to_zero` (:72-73, 89-92) are as in the reference.  One
+thing is stricter: a configuration is first asked whether it *can* run
+(`JITFunction.specialize` + the plan's own `check`), and one that cannot is
+dropped without being launched -- the reference finds invalid configurations by
+launching them and catching the failure (:76-81), which on a shared GPU can
+poison the context.
+"""
+
+from ..frontend.trace import CompileError
+
+
+class Config:
+    def __init__(self, kwargs, num_warps=4, num_stages=1):
+        self.kwargs = dict(kwargs)
+        self.num_warps = num_warps
+        self.num_stages = num_stages
+
+    def all_kwargs(self):
+        out = dict(self.kwargs)
+        out["num_warps"] = self.num_warps
+        out["num_stages"] = self.num_stages
+        return out
+
+    def __repr__(self):
+        body = ", ".join(f"{k}={v}" for k, v in self.kwargs.items())
+        return f"Config({body}, num_warps={self.num_warps}, num_stages={self.num_stages})"
+
+
+def _bound_args(jitfn, args, kwargs):
+    bound = dict(zip(jitfn.param_names, args))
+    bound.update(kwargs)
+    for name, default in getattr(jitfn, "defaults", {}).items():
+        bound.setdefault(name, default)
+    return bound
+
+
+class Autotuner:
+    def __init__(self, jitfn, configs, key, reset_to_zero=None, warmup=5, rep=20):
+        self.jitfn = jitfn
+        self.configs = list(configs)
+        self.key = list(key)
+        self.reset_to_zero = list(reset_to_zero or [])
+        self.warmup, self.rep = warmup, rep
+        self.cache = {}
+        self.best_config = None
+        self.timings = {}
+        self.param_names = jitfn.param_names
+        self.__name__ = getattr(jitfn, "__name__", "kernel")
+
+    def __getitem__(self, grid):
+        return lambda *args, **kwargs: self._run(grid, args, kwargs)
+
+    def _cache_key(self, bound):
+        import torch
+
+        vals = []
+        for k in self.key:
+            v = bound.get(k)
+            vals.append(tuple(v.shape) if hasattr(v, "shape") else v)
+        vals.extend(str(v.dtype) for v in bound.values() if isinstance(v, torch.Tensor))
+        return tuple(vals)
+
+    def _tune(self, grid, args, kwargs, bound):
+        from ..testing import do_bench
+
+        results, last_error = [], None
+        for cfg in self.configs:
+            call_kwargs = {**kwargs, **cfg.all_kwargs()}
+
+            def run(call_kwargs=call_kwargs):
+                for name in self.reset_to_zero:
+                    bound[name].zero_()
+                self.jitfn[grid](*args, **call_kwargs)
+
+            try:
+                run()  # compiles; invalid configurations raise before any launch
+                ms = do_bench(run, warmup=self.warmup, rep=self.rep)
+            except (CompileError, ValueError, RuntimeError) as e:
+                last_error = e
+                continue
+            results.append((ms, cfg))
+        if not results:
+            raise RuntimeError(f"autotune: no valid config for {self.__name__}") from last_error
+        results.sort(key=lambda r: r[0])
+        self.timings = {repr(c): ms for ms, c in results}
+        return results[0][1]
+
+    def _run(self, grid, args, kwargs):
+        bound = _bound_args(self.jitfn, args, kwargs)
+        key = self._cache_key(bound)
+        best = self.cache.get(key)
+        if best is None:
+            best = self._tune(grid, args, kwargs, bound)
+            self.cache[key] = best
+            for name in self.reset_to_zero:  # tuning dirtied the accumulation buffers
+                bound[name].zero_()
+        self.best_config = best
+        self.jitfn[grid](*args, **{**kwargs, **best.all_kwargs()})
+
+
+def autotune(configs, key, reset_to_zero=None):
+    return lambda jitfn: Autotuner(jitfn, configs, key, reset_to_zero)
+
+
+class Heuristics:
+    def __init__(self, jitfn, values):
+        self.jitfn = jitfn
+        self.values = dict(values)
+        self.param_names = jitfn.param_names
+        self.__name__ = getattr(jitfn, "__name__", "kernel")
+
+    def __getitem__(self, grid):
+        def runner(*args, **kwargs):
+            bound = _bound_args(self.jitfn, args, kwargs)
+            for name, fn in self.values.items():
+                kwargs[name] = fn(bound)
+            return self.jitfn[grid](*args, **kwargs)
+
+        return runner
+
+
+def heuristics(values):
+    return lambda jitfn: Heuristics(jitfn, values)

@@ -1,0 +1,201 @@
+"""`@jit`: compile-on-first-launch wrapper with the launch protocol of the reference.
+
+Everything a caller can observe is kept as newt/runtime/jit.py has it:
+`kernel[grid](*args, **kwargs)`; `grid` a tuple, an int or a callable of
+`meta = runtime args | constexprs | {"num_warps"}` (:210-219); reserved
+keywords `num_warps` (power of two <= 32) and `num_stages` (1..8) (:169-174);
+TypeError for binding problems (:104-120, 129-144), ValueError for a tensor on
+another device (:195-199); an empty grid is a no-op (:220-221); a bare call
+raises (:93-97); one specialization per (constexprs, argument types,
+num_warps, num_stages) (:177-183).
+
+What differs is what a specialization *is*: the kernel body is traced into an
+expression graph (frontend/trace.py) and lowered to a launch plan on one of the
+hand-written sm_100a kernels of libnewt_b200.so (frontend/lower.py).  There is
+no other backend; a body no plan covers raises CompileError.
+"""
+
+import ast
+import functools
+import inspect
+import os
+import textwrap
+
+from .. import types as tp
+from ..frontend import lower as _lower
+from ..frontend.trace import CompileError, trace_kernel
+
+
+def _is_constexpr_annotation(ann):
+    from .. import language as nl
+
+    if ann is nl.constexpr or isinstance(ann, nl.constexpr):
+        return True
+    return isinstance(ann, str) and "constexpr" in ann
+
+
+class CompiledKernel:
+    """One specialization: its trace (for inspection) and its launch plan."""
+
+    def __init__(self, name, trace, plan, num_warps, num_stages, param_names):
+        self.name = name
+        self.trace = trace
+        self.plan = plan
+        self.num_warps = num_warps
+        self.num_stages = num_stages
+        self.param_names = param_names
+
+
+class JITFunction:
+    def __init__(self, fn):
+        functools.update_wrapper(self, fn)
+        self.fn = fn
+        source = textwrap.dedent(inspect.getsource(fn))
+        tree = ast.parse(source)
+        self.fndef = next(n for n in tree.body if isinstance(n, ast.FunctionDef))
+        params = inspect.signature(fn).parameters
+        self.param_names = list(params)
+        self.constexpr_names = [n for n, p in params.items()
+                                if _is_constexpr_annotation(p.annotation)]
+        self._constexpr_set = frozenset(self.constexpr_names)
+        self.defaults = {n: p.default for n, p in params.items()
+                         if p.default is not inspect.Parameter.empty}
+        self.cache = {}
+
+    def __getitem__(self, grid):
+        return functools.partial(self._run, grid)
+
+    def __call__(self, *args, **kwargs):
+        raise RuntimeError(
+            f"@newt.jit kernel '{self.fn.__name__}' must be launched with a grid: "
+            f"kernel[grid](...)")
+
+    # ---- argument handling -------------------------------------------------------
+
+    def _bind(self, args, kwargs):
+        names = self.param_names
+        if len(args) > len(names):
+            raise TypeError(f"{self.fn.__name__}() takes {len(names)} arguments "
+                            f"but {len(args)} were given")
+        bound = dict(zip(names, args))
+        unknown = []
+        for k, v in kwargs.items():
+            if k not in self.defaults and k not in names:
+                unknown.append(k)
+            elif k in bound:
+                raise TypeError(f"duplicate argument {k}")
+            else:
+                bound[k] = v
+        if unknown:
+            raise TypeError(f"unknown kernel arguments: {unknown}")
+        for k, v in self.defaults.items():
+            bound.setdefault(k, v)
+        missing = [n for n in names if n not in bound]
+        if missing:
+            raise TypeError(f"missing kernel arguments: {missing}")
+        return bound
+
+    @staticmethod
+    def _type_of(name, val):
+        import torch
+
+        if isinstance(val, torch.Tensor):
+            if not val.is_cuda:
+                raise TypeError(f"argument '{name}' must be a CUDA tensor")
+            elem = tp.TORCH_TO_NEWT.get(str(val.dtype))
+            if elem is None:
+                raise TypeError(f"unsupported tensor dtype {val.dtype} for '{name}'")
+            return tp.pointer_type(elem)
+        if isinstance(val, bool):
+            return tp.int1
+        if isinstance(val, int):
+            if not -(2 ** 63) <= val < 2 ** 63:
+                raise TypeError(f"integer argument '{name}'={val} does not fit int64")
+            return tp.int32 if -(2 ** 31) <= val < 2 ** 31 else tp.int64
+        if isinstance(val, float):
+            return tp.float32
+        raise TypeError(f"unsupported kernel argument type {type(val)} for '{name}'")
+
+    # ---- compile -------------------------------------------------------------------
+
+    def _compile(self, constexprs, runtime_types, num_warps, num_stages):
+        trace = trace_kernel(self.fndef, self.fn.__globals__, runtime_types, constexprs, num_warps)
+        plan = _lower.lower(trace, num_warps=num_warps, num_stages=num_stages)
+        if os.environ.get("NEWT_DEBUG"):
+            print(f"=== newt_b200: {self.fn.__name__} -> {plan.describe()} "
+                  f"(warps={num_warps}, stages={num_stages}) ===")
+            print(trace.dump())
+        return CompiledKernel(self.fn.__name__, trace, plan, num_warps, num_stages,
+                              [n for n in self.param_names if n not in self._constexpr_set])
+
+    def specialize(self, *args, **kwargs):
+        """Compiles (or fetches) the specialization these arguments select, without
+        launching; returns the CompiledKernel.  Tensors may be replaced by
+        `pointer_type` objects, so plans can be inspected without a GPU."""
+        num_warps = kwargs.pop("num_warps", 4)
+        num_stages = kwargs.pop("num_stages", 3)
+        bound = self._bind(args, kwargs)
+        return self._specialization(bound, num_warps, num_stages)[0]
+
+    def _specialization(self, bound, num_warps, num_stages):
+        if num_warps not in (1, 2, 4, 8, 16, 32):
+            raise ValueError(f"num_warps must be a power of two <= 32, got {num_warps}")
+        if not isinstance(num_stages, int) or not 1 <= num_stages <= 8:
+            raise ValueError(f"num_stages must be in 1..8, got {num_stages}")
+        cset = self._constexpr_set
+        constexprs = {n: bound[n] for n in self.constexpr_names}
+        runtime_types = {}
+        for n in self.param_names:
+            if n not in cset:
+                v = bound[n]
+                runtime_types[n] = v if isinstance(v, (tp.pointer_type, tp.dtype)) \
+                    else self._type_of(n, v)
+        key = (tuple(sorted((k, repr(v)) for k, v in constexprs.items())),
+               tuple((n, t.name) for n, t in runtime_types.items()), num_warps, num_stages)
+        compiled = self.cache.get(key)
+        if compiled is None:
+            compiled = self._compile(constexprs, runtime_types, num_warps, num_stages)
+            self.cache[key] = compiled
+        return compiled, constexprs, runtime_types
+
+    # ---- launch --------------------------------------------------------------------
+
+    def _run(self, grid, *args, **kwargs):
+        import torch
+
+        num_warps = kwargs.pop("num_warps", 4)
+        num_stages = kwargs.pop("num_stages", 3)
+        bound = self._bind(args, kwargs)
+        compiled, constexprs, runtime_types = self._specialization(bound, num_warps, num_stages)
+
+        current = None
+        for name, t in runtime_types.items():
+            if isinstance(t, tp.pointer_type):
+                v = bound[name]
+                if current is None:
+                    current = torch.cuda.current_device()
+                if v.device.index not in (None, current):
+                    raise ValueError(
+                        f"tensor '{name}' is on {v.device} but the current device is "
+                        f"cuda:{current}; newt launches on the current device")
+
+        if callable(grid):
+            meta = {n: bound[n] for n in self.param_names}
+            meta["num_warps"] = num_warps
+            g = grid(meta)
+        else:
+            g = grid
+        if isinstance(g, int):
+            g = (g,)
+        g = tuple(int(x) for x in g)
+        if len(g) > 3:
+            raise ValueError(f"grids have at most 3 dimensions, got {g}")
+        if any(x <= 0 for x in g):
+            return
+        compiled.plan.launch(g, bound)
+
+
+def jit(fn=None):
+    if fn is None:
+        return jit
+    return JITFunction(fn)

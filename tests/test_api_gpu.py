@@ -1,0 +1,214 @@
+"""GPU: the operator API end to end -- `@jit` kernels launched with the reference's
+protocol, `@autotune`, `@heuristics`, `@dt.kernel` -- with results checked against the
+CPU oracle.  Shapes follow the reference's own tests (tests/test_vector_add.py,
+test_softmax_layernorm.py, test_matmul.py, test_deuteron.py, test_review_fixes.py)."""
+
+import pytest
+import torch
+
+import newt_b200 as newt
+import newt_b200.deuteron as dt
+import newt_b200.language as nl
+from newt_b200.runtime import abi
+from oracle import cport, torch_ref
+
+import ref_kernels as rk
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("n", [1024, 1 << 20, 12345])
+def test_vector_add_bit_exact(n):
+    x, y = _rand(n, 1), _rand(n, 2)
+    xd, yd = x.cuda(), y.cuda()
+    out = torch.empty_like(xd)
+    grid = lambda meta: (newt.cdiv(n, meta["BLOCK"]),)  # noqa: E731
+    rk.add_kernel[grid](xd, yd, out, n, BLOCK=4096)
+    assert torch.equal(out.cpu(), cport.add_f32(x, y))
+
+
+@pytest.mark.parametrize("m,n", [(8, 128), (128, 1024), (32, 781), (4096, 2500)])
+def test_softmax_kernel(m, n):
+    x = _rand((m, n), 3)
+    xd = x.cuda()
+    out = torch.empty_like(xd)
+    block = newt.next_power_of_2(n)
+    rk.softmax_kernel[(m,)](xd, out, n, xd.stride(0), BLOCK_N=block,
+                            num_warps=4 if block < 4096 else 8)
+    torch.testing.assert_close(out.cpu(), torch_ref.softmax(x), rtol=1e-5, atol=1e-9)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("m,n", [(8, 128), (64, 2048), (16, 300)])
+def test_layernorm_kernel(dtype, m, n):
+    x, w, b = _rand((m, n), 4, dtype), _rand(n, 5, dtype), _rand(n, 6, dtype)
+    xd = x.cuda()
+    out = torch.empty_like(xd)
+    rk.layernorm_kernel[(m,)](xd, w.cuda(), b.cuda(), out, n, xd.stride(0), 1e-5,
+                              BLOCK_N=newt.next_power_of_2(n), num_warps=8)
+    ref = torch_ref.layernorm(x, w, b)
+    if dtype == torch.float32:
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-3, atol=1e-4)
+    else:
+        assert torch_ref.rel_frobenius(out.cpu().float(), ref) <= 1e-2
+
+
+def _run_matmul(kernel, m, n, k, dtype, bm=64, bn=64, bk=32, ld_pad=0, **kw):
+    a = _rand((m, k + ld_pad), 7, dtype, 0.5)[:, :k]
+    b = _rand((k, n + ld_pad), 8, dtype, 0.5)[:, :n]
+    ad, bd = a.cuda(), b.cuda()
+    ad = torch.as_strided(ad, (m, k), (k + ld_pad, 1)) if ld_pad else ad
+    a_dev = torch.empty(m, k + ld_pad, device="cuda", dtype=dtype)[:, :k]
+    a_dev.copy_(a)
+    b_dev = torch.empty(k, n + ld_pad, device="cuda", dtype=dtype)[:, :n]
+    b_dev.copy_(b)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    grid = (newt.cdiv(m, bm), newt.cdiv(n, bn))
+    kernel[grid](a_dev, b_dev, c, m, n, k, a_dev.stride(0), a_dev.stride(1), b_dev.stride(0),
+                 b_dev.stride(1), c.stride(0), c.stride(1), BLOCK_M=bm, BLOCK_N=bn, BLOCK_K=bk, **kw)
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    return a.contiguous(), b.contiguous(), c.cpu()
+
+
+@pytest.mark.parametrize("m,n,k,pad", [(64, 64, 32, 0), (256, 256, 128, 0), (300, 200, 100, 4),
+                                       (129, 264, 72, 0)])
+def test_matmul_fp16(m, n, k, pad):
+    # (300, 200, 100): the reference's ragged case; row pitch padded to a multiple of 8
+    # elements, which is what TMA needs
+    a, b, c = _run_matmul(rk.matmul_kernel, m, n, k, torch.float16, ld_pad=pad)
+    ref = torch_ref.matmul(a, b)
+    assert torch_ref.rel_frobenius(c.float(), ref) <= 1e-2
+    torch.testing.assert_close(c.float(), ref.half().float(), rtol=1e-2, atol=1e-2)
+    if m * n * k <= 256 * 256 * 128:
+        torch.testing.assert_close(c.float(), cport.matmul(a, b).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_matmul_bf16_and_tiles():
+    for bn, stages in ((64, 2), (128, 3), (256, 4)):
+        a, b, c = _run_matmul(rk.matmul_kernel, 256, 512, 192, torch.bfloat16, bm=128, bn=bn,
+                              bk=64, num_stages=stages)
+        assert torch_ref.rel_frobenius(c.float(), torch_ref.matmul(a, b)) <= 1e-2
+
+
+def test_matmul_unmasked_kernel():
+    a, b, c = _run_matmul(rk.matmul_kernel_unmasked, 256, 256, 128, torch.float16, bm=128,
+                          bn=128, bk=64)
+    assert torch_ref.rel_frobenius(c.float(), torch_ref.matmul(a, b)) <= 1e-2
+
+
+def test_matmul_unaligned_pitch_is_reported_not_faulted():
+    a = torch.zeros(64, 100, device="cuda", dtype=torch.float16)   # pitch 200 B: not TMA-legal
+    b = torch.zeros(100, 64, device="cuda", dtype=torch.float16)
+    c = torch.zeros(64, 64, device="cuda", dtype=torch.float16)
+    with pytest.raises(abi.UnsupportedError, match="multiple of 8"):
+        rk.matmul_kernel[(1, 1)](a, b, c, 64, 64, 100, 100, 1, 64, 1, 64, 1,
+                                 BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+
+
+def test_autotune_picks_a_config_and_caches_it():
+    tuned = newt.autotune(
+        configs=[newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_stages=4),
+                 newt.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_stages=4),
+                 newt.Config({"BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64}, num_stages=3)],
+        key=["M", "N", "K"])(rk.matmul_kernel)
+    m = n = k = 512
+    a, b = _rand((m, k), 9, torch.float16, 0.5), _rand((k, n), 10, torch.float16, 0.5)
+    ad, bd = a.cuda(), b.cuda()
+    c = torch.empty(m, n, device="cuda", dtype=torch.float16)
+    grid = lambda meta: (newt.cdiv(m, meta["BLOCK_M"]), newt.cdiv(n, meta["BLOCK_N"]))  # noqa: E731
+    for _ in range(2):
+        tuned[grid](ad, bd, c, m, n, k, k, 1, n, 1, n, 1)
+    assert tuned.best_config in tuned.configs and len(tuned.cache) == 1
+    assert torch_ref.rel_frobenius(c.cpu().float(), torch_ref.matmul(a, b)) <= 1e-2
+
+
+def test_heuristics_and_grid_meta():
+    seen = {}
+    h = newt.heuristics({"BLOCK": lambda args: 256 if args["n"] < 1000 else 1024})(rk.add_kernel)
+    n = 700
+    x, y = _rand(n, 11).cuda(), _rand(n, 12).cuda()
+    out = torch.empty_like(x)
+
+    def grid(meta):
+        seen.update(meta)
+        return (newt.cdiv(meta["n"], meta["BLOCK"]),)
+
+    h[grid](x, y, out, n)
+    assert seen["BLOCK"] == 256 and seen["n"] == n and seen["num_warps"] == 4
+    assert torch.equal(out, x + y)
+
+
+def test_zero_grid_is_noop_and_wrong_device_type():
+    x = torch.ones(16, device="cuda")
+    out = torch.zeros(16, device="cuda")
+    rk.add_kernel[(0,)](x, x, out, 16, BLOCK=16)
+    assert out.sum().item() == 0
+
+
+def test_autotune_reset_to_zero_first_call():
+    calls = []
+
+    class FakeJit:
+        param_names = ["x", "n"]
+        defaults = {}
+        __name__ = "fake"
+
+        def __getitem__(self, grid):
+            def run(x, n, **kw):
+                calls.append(float(x.sum().item()))
+                x += 1
+            return run
+
+    tuner = newt.Autotuner(FakeJit(), [newt.Config({}), newt.Config({})], key=["n"],
+                           reset_to_zero=["x"], warmup=0, rep=1)
+    x = torch.zeros(4, device="cuda")
+    tuner[(1,)](x, 4)
+    assert x.sum().item() == 4.0      # buffer was cleared after tuning, then one real run
+    assert all(c == 0.0 for c in calls)  # every timed call started from zero
+
+
+# ---- deuteron ---------------------------------------------------------------------
+
+@dt.kernel(config={"BLOCK_TILE_M": 128, "BLOCK_TILE_N": 128, "BLOCK_TILE_K": 64, "num_stages": 4})
+def dt_matmul_fixed(x, y, out):
+    for tile_m, tile_n in dt.tile([x.shape[0], y.shape[1]]):
+        acc = dt.zeros([tile_m, tile_n], dtype=dt.float32)
+        for tile_k in dt.tile(x.shape[1]):
+            acc += x[tile_m, tile_k] @ y[tile_k, tile_n]
+        out[tile_m, tile_n] = acc
+
+
+@dt.kernel
+def dt_matmul_tuned(x, y, out):
+    for tile_m, tile_n in dt.tile([x.shape[0], y.shape[1]]):
+        acc = dt.zeros([tile_m, tile_n], dtype=dt.float32)
+        for tile_k in dt.tile(x.shape[1]):
+            acc += x[tile_m, tile_k] @ y[tile_k, tile_n]
+        out[tile_m, tile_n] = acc
+
+
+def test_deuteron_matmul_fixed_config():
+    x, y = _rand((512, 384), 13, torch.float16, 0.5), _rand((384, 256), 14, torch.float16, 0.5)
+    out = torch.empty(512, 256, device="cuda", dtype=torch.float16)
+    dt_matmul_fixed(x.cuda(), y.cuda(), out)
+    assert torch_ref.rel_frobenius(out.cpu().float(), torch_ref.matmul(x, y)) <= 1e-2
+
+
+def test_deuteron_matmul_autotuned_bf16(tmp_path, monkeypatch):
+    monkeypatch.setenv("DEUTERON_CACHE_DIR", str(tmp_path))
+    x, y = _rand((1024, 768), 15, torch.bfloat16, 0.5), _rand((768, 512), 16, torch.bfloat16, 0.5)
+    xd, yd = x.cuda(), y.cuda()
+    out = torch.empty(1024, 512, device="cuda", dtype=torch.bfloat16)
+    dt_matmul_tuned(xd, yd, out)
+    assert torch_ref.rel_frobenius(out.cpu().float(), torch_ref.matmul(x, y)) <= 1e-2
+    best = dt_matmul_tuned.best_config
+    assert best["BLOCK_TILE_N"] in (64, 128, 256) and (tmp_path / "configs.json").exists()
+    ref = torch.empty_like(out)
+    dt_matmul_tuned.ref(xd, yd, ref)          # eager oracle on the device
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)

@@ -1,0 +1,200 @@
+"""CPU: the front end, without a GPU -- tracing, affine analysis and which launch
+plan each hot-path kernel lowers to (the reference's GPU-free tests check the
+structure of generated text the same way, tests/test_codegen_cpu.py:22-76)."""
+
+import pytest
+import torch
+
+import newt_b200 as newt
+import newt_b200.deuteron as dt
+import newt_b200.language as nl
+from newt_b200 import types as tp
+from newt_b200.frontend import lower
+
+import ref_kernels as rk
+
+P = tp.pointer_type
+F32, F16, BF16 = P(tp.float32), P(tp.float16), P(tp.bfloat16)
+
+
+def test_softmax_lowers_to_row_kernel():
+    c = rk.softmax_kernel.specialize(F32, F32, 781, 1001, BLOCK_N=1024)
+    assert isinstance(c.plan, lower.SoftmaxPlan) and c.plan.entry == "nb200_softmax_f32"
+    a = dict(N=781, stride=1001)
+    assert (c.plan.n(a), c.plan.sx(a), c.plan.so(a), c.plan.block) == (781, 1001, 1001, 1024)
+
+
+@pytest.mark.parametrize("ptr", [F32, F16, BF16])
+def test_layernorm_lowers_to_row_kernel(ptr):
+    c = rk.layernorm_kernel.specialize(ptr, ptr, ptr, ptr, 300, 320, 1e-5, BLOCK_N=512)
+    assert isinstance(c.plan, lower.LayerNormPlan)
+    assert c.plan.eps == "eps" and c.plan.n(dict(N=300, stride=320)) == 300
+
+
+def test_add_lowers_to_vector_kernel():
+    c = rk.add_kernel.specialize(F32, F32, F32, 12345, BLOCK=4096)
+    assert isinstance(c.plan, lower.AddPlan) and c.plan.n(dict(n=12345)) == 12345
+
+
+@pytest.mark.parametrize("kernel,extents", [(rk.matmul_kernel, (300, 200, 104)),
+                                            (rk.matmul_kernel_unmasked, (320, 256, 96))])
+def test_matmul_lowers_to_tcgen05_gemm(kernel, extents):
+    c = kernel.specialize(F16, F16, F16, 300, 200, 104, 104, 1, 200, 1, 200, 1,
+                          BLOCK_M=64, BLOCK_N=64, BLOCK_K=32, num_stages=4)
+    p = c.plan
+    assert isinstance(p, lower.GemmPlan) and p.entry == "nb200_gemm"
+    a = dict(M=300, N=200, K=104, sam=104, sak=1, sbk=200, sbn=1, scm=200, scn=1)
+    assert p._extents((5, 4), a) == extents
+    assert (p.lda(a), p.ldb(a), p.ldc(a)) == (104, 200, 200)
+    assert (p.pid_m, p.pid_n) == (0, 1) and p.hardware_key() == ("gemm", 64, 4)
+    assert (p.a, p.b, p.c) == ("a_ptr", "b_ptr", "c_ptr")
+
+
+def test_pointer_walk_is_resolved_as_induction():
+    c = rk.matmul_kernel.specialize(F16, F16, F16, 64, 64, 64, 64, 1, 64, 1, 64, 1,
+                                    BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    from newt_b200.frontend.affine import Analyzer
+    an = Analyzer(c.trace)
+    an.resolve_inductions()
+    loop = c.trace.loops[0]
+    assert ("carried", loop.uid, "a_ptrs") in an.closed_forms
+    assert ("carried", loop.uid, "b_ptrs") in an.closed_forms
+    assert ("carried", loop.uid, "acc") not in an.closed_forms
+
+
+def test_transposed_operand_is_refused_at_launch_time():
+    c = rk.matmul_kernel.specialize(F16, F16, F16, 64, 64, 64, 1, 64, 64, 1, 64, 1,
+                                    BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    a = dict(M=64, N=64, K=64, sam=1, sak=64, sbk=64, sbn=1, scm=64, scn=1)
+    assert dict(c.plan.inner)["a_ptr"](a) == 64   # launch() raises CompileError on this
+
+
+def test_unrecognised_program_raises_compile_error():
+    @newt.jit
+    def scale(x_ptr, out_ptr, n, BLOCK: nl.constexpr):
+        offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        nl.store(out_ptr + offs, nl.load(x_ptr + offs, mask=offs < n) * 2.0, mask=offs < n)
+
+    with pytest.raises(newt.CompileError, match="no sm_100a kernel"):
+        scale.specialize(F32, F32, 100, BLOCK=128)
+
+
+def test_language_errors_are_compile_errors():
+    @newt.jit
+    def bad_arange(x_ptr, BLOCK: nl.constexpr):
+        nl.store(x_ptr + nl.arange(0, 100), 0.0)
+
+    with pytest.raises(newt.CompileError, match="power of two"):
+        bad_arange.specialize(F32, BLOCK=1)
+
+    @newt.jit
+    def bad_dot(a_ptr, b_ptr, BLOCK: nl.constexpr):
+        o = nl.arange(0, 16)
+        a = nl.load(a_ptr + o[:, None] * 16 + o[None, :])
+        b = nl.load(b_ptr + o[:, None] * 16 + o[None, :])
+        nl.store(a_ptr + o[:, None] * 16 + o[None, :], nl.dot(a, b))
+
+    with pytest.raises(newt.CompileError, match="share a dtype"):
+        bad_dot.specialize(F16, BF16, BLOCK=1)
+
+    @newt.jit
+    def block_condition(x_ptr, BLOCK: nl.constexpr):
+        o = nl.arange(0, BLOCK)
+        if o < 3:
+            nl.store(x_ptr + o, 0.0)
+
+    with pytest.raises(newt.CompileError, match="nl.where"):
+        block_condition.specialize(F32, BLOCK=8)
+
+
+def test_launch_protocol_errors_need_no_gpu():
+    with pytest.raises(RuntimeError, match="must be launched with a grid"):
+        rk.add_kernel(1, 2, 3, 4)
+    with pytest.raises(TypeError, match="unknown kernel arguments"):
+        rk.add_kernel.specialize(F32, F32, F32, 10, BLOCK=64, bogus=1)
+    with pytest.raises(TypeError, match="missing kernel arguments"):
+        rk.add_kernel.specialize(F32, F32, F32, 10)
+    with pytest.raises(TypeError, match="takes 5 arguments"):
+        rk.add_kernel.specialize(F32, F32, F32, 10, 64, 7)
+    with pytest.raises(ValueError, match="num_warps"):
+        rk.add_kernel.specialize(F32, F32, F32, 10, BLOCK=64, num_warps=3)
+    with pytest.raises(ValueError, match="num_stages"):
+        rk.add_kernel.specialize(F32, F32, F32, 10, BLOCK=64, num_stages=9)
+    with pytest.raises(TypeError, match="must be a CUDA tensor"):
+        rk.add_kernel[(1,)](torch.zeros(4), torch.zeros(4), torch.zeros(4), 4, BLOCK=64)
+
+
+def test_specialization_cache_keys():
+    k = rk.add_kernel
+    n0 = len(k.cache)
+    k.specialize(F32, F32, F32, 10, BLOCK=256)
+    k.specialize(F32, F32, F32, 99, BLOCK=256)          # same types: reused
+    assert len(k.cache) == n0 + 1
+    k.specialize(F32, F32, F32, 2 ** 40, BLOCK=256)     # int64 argument: new specialization
+    k.specialize(F32, F32, F32, 10, BLOCK=512)          # new constexpr
+    assert len(k.cache) == n0 + 3
+
+
+def test_constexpr_host_arithmetic_and_helpers():
+    c = nl.constexpr(8)
+    assert (c * 2).value == 16 and (2 * c).value == 16 and (c // 3).value == 2 and int(c) == 8
+    assert newt.cdiv(10, 3) == 4 and newt.next_power_of_2(781) == 1024
+    assert newt.next_power_of_2(1) == 1 and newt.next_power_of_2(1024) == 1024
+
+
+def test_type_rules():
+    assert tp.promote(tp.float16, tp.bfloat16) == tp.float32
+    assert tp.promote(tp.int32, tp.float16) == tp.float16
+    assert tp.promote(tp.int32, tp.int64) == tp.int64
+    assert tp.broadcast_shapes((4, 1), (1, 8)) == (4, 8)
+    with pytest.raises(TypeError):
+        tp.broadcast_shapes((4,), (8,))
+    assert P(tp.float16).element_ty == tp.float16
+
+
+# ---- deuteron -------------------------------------------------------------------
+
+@dt.kernel
+def dt_matmul(x, y, out):
+    for tile_m, tile_n in dt.tile([x.shape[0], y.shape[1]]):
+        acc = dt.zeros([tile_m, tile_n], dtype=dt.float32)
+        for tile_k in dt.tile(x.shape[1]):
+            acc += x[tile_m, tile_k] @ y[tile_k, tile_n]
+        out[tile_m, tile_n] = acc
+
+
+def test_deuteron_source_and_plan():
+    x, y = torch.randn(300, 104).bfloat16(), torch.randn(104, 200).bfloat16()
+    out = torch.empty(300, 200).bfloat16()
+    src = dt_matmul.to_newt_source(x, y, out)
+    assert "def matmul_newt(x_ptr, x_d0, x_d1, x_s0, x_s1, y_ptr" not in src  # named after the fn
+    assert "def dt_matmul_newt(x_ptr, x_d0, x_d1, x_s0, x_s1, y_ptr, y_d0, y_d1, y_s0, y_s1, " \
+           "out_ptr, out_d0, out_d1, out_s0, out_s1, BLOCK_TILE_M: nl.constexpr" in src
+    assert "acc = nl.dot(" in src and "for _i_tile_k in range(0, nl.cdiv(x_d1, BLOCK_TILE_K)):" in src
+    ks = dt_matmul._source_for((x, y, out))
+    cfg = dt.Config(BLOCK_TILE_M=128, BLOCK_TILE_N=256, BLOCK_TILE_K=64, num_stages=4)
+    grid, pos, kw = dt_matmul._call_parts(ks, (x, y, out), cfg)
+    assert grid == (3, 1)
+    typed = [BF16 if torch.is_tensor(a) else a for a in pos]
+    plan = dt_matmul._jit.specialize(*typed, **kw).plan
+    args = dict(zip(dt_matmul._jit.param_names, pos))
+    assert isinstance(plan, lower.GemmPlan) and plan.hardware_key() == ("gemm", 256, 4)
+    assert plan._extents(grid, args) == (300, 200, 104)
+
+
+def test_deuteron_eager_reference_runs_on_host_tensors():
+    x, y = torch.randn(64, 48).half(), torch.randn(48, 32).half()
+    out = torch.empty(64, 32).half()
+    dt_matmul.ref(x, y, out)   # the reference's eager mode cannot do this: its accumulator is pinned to CUDA
+    torch.testing.assert_close(out.float(), x.float() @ y.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_deuteron_trace_errors():
+    @dt.kernel
+    def bad(x, out):
+        y = x
+        for t in dt.tile(x.shape[0]):
+            out[t] = x[t]
+
+    with pytest.raises(dt.TraceError, match="top level"):
+        bad.to_newt_source(torch.zeros(4), torch.zeros(4))

@@ -140,3 +140,89 @@ def test_layernorm_config2_shape_fp16():
     b = (0.1 * torch.randn(n, generator=g)).half()
     got = _layernorm(_dev(x), _dev(w), _dev(b)).cpu()
     assert torch_ref.rel_frobenius(got.float(), torch_ref.layernorm(x, w, b)) <= 1e-2
+
+
+# ---- K3 / K4 ------------------------------------------------------------------
+
+def _gemm(a, b, block_n=0, stages=0):
+    m, k = a.shape
+    n = b.shape[1]
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=a.dtype)
+    kernels.gemm(a, b, c, m, n, k, a.stride(0), b.stride(0), c.stride(0),
+                 kernels.gemm_config(block_n=block_n, stages=stages))
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    return c
+
+
+def test_gemm_golden(golden):
+    for name in ("f16", "bf16"):
+        for case in golden.cases(f"matmul_{name}"):
+            p = f"matmul_{name}/{case}"
+            a, b = golden.get(p + "/a"), golden.get(p + "/b")
+            m, k = a.shape
+            n = b.shape[1]
+            # TMA wants row pitches that are multiples of 8 elements: pad the pitch, not the data
+            kp, np_ = -(-k // 8) * 8, -(-n // 8) * 8
+            ad = torch.zeros(m, kp, device="cuda", dtype=a.dtype)[:, :k]
+            bd = torch.zeros(k, np_, device="cuda", dtype=a.dtype)[:, :n]
+            ad.copy_(a)
+            bd.copy_(b)
+            got = _gemm(ad, bd).cpu()
+            assert torch_ref.rel_frobenius(got.float(), golden.get(p + "/expected_f32")) <= 1e-2
+            tol = 1e-2 if name == "f16" else 2e-2
+            torch.testing.assert_close(got.float(), golden.get(p + "/expected_eager").float(),
+                                       rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (128, 64, 64), (130, 72, 200), (257, 520, 136),
+                                   (1024, 1024, 1024)])
+def test_gemm_vs_oracle(dtype, block_n, m, n, k):
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype)
+    b = torch.randn(k, n, generator=g).to(dtype)
+    got = _gemm(a.cuda(), b.cuda(), block_n).cpu()
+    assert torch_ref.rel_frobenius(got.float(), torch_ref.matmul(a, b)) <= 1e-2
+    if m * n * k <= 130 * 72 * 200:
+        want = cport.matmul(a, b)
+        assert torch_ref.rel_frobenius(got.float(), want.float()) <= 4e-3
+
+
+def test_gemm_linearity_at_full_size():
+    # size-independent property at the benchmark size: (A1 + A2) @ B == A1 @ B + A2 @ B
+    # up to rounding, and a spot-checked block against the fp32 oracle
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a1 = (torch.randn(n, n, device="cuda", generator=g) / n ** 0.5).half()
+    a2 = (torch.randn(n, n, device="cuda", generator=g) / n ** 0.5).half()
+    b = torch.randn(n, n, device="cuda", generator=g).half()
+    c1, c2, c12 = _gemm(a1, b), _gemm(a2, b), _gemm((a1.float() + a2.float()).half(), b)
+    err = ((c1.float() + c2.float() - c12.float()).norm() / c12.float().norm()).item()
+    assert err <= 2e-3
+    rows = slice(4096 - 64, 4096 + 64)
+    ref = a1[rows].float().cpu() @ b.float().cpu()
+    assert torch_ref.rel_frobenius(c1[rows].cpu().float(), ref) <= 1e-2
+
+
+def test_gemm_empty_and_k_zero():
+    a = torch.zeros(0, 64, device="cuda", dtype=torch.float16)
+    b = torch.zeros(64, 64, device="cuda", dtype=torch.float16)
+    _gemm(a, b)
+    a = torch.zeros(16, 0, device="cuda", dtype=torch.float16)
+    b = torch.zeros(0, 16, device="cuda", dtype=torch.float16)
+    c = torch.ones(16, 16, device="cuda", dtype=torch.float16)
+    kernels.gemm(a, b, c, 16, 16, 0, 8, 16, 16)
+    assert c.abs().sum().item() == 0
+
+
+def test_gemm_check_rejects_without_launching():
+    a = torch.zeros(64, 100, device="cuda", dtype=torch.float16)
+    b = torch.zeros(100, 64, device="cuda", dtype=torch.float16)
+    c = torch.zeros(64, 64, device="cuda", dtype=torch.float16)
+    assert "multiple of 8" in kernels.gemm_check(a, b, c, 64, 64, 100, 100, 64, 64)
+    assert kernels.gemm_check(a, b, c, 64, 64, 96, 104, 64, 64) is None
+    af = torch.zeros(64, 64, device="cuda")
+    with pytest.raises(abi.UnsupportedError):
+        kernels.gemm(af, af, af, 64, 64, 64, 64, 64, 64)
