@@ -59,13 +59,14 @@ def test_layernorm_kernel(dtype, m, n):
 
 
 def _run_matmul(kernel, m, n, k, dtype, bm=64, bn=64, bk=32, ld_pad=0, **kw):
-    a = _rand((m, k + ld_pad), 7, dtype, 0.5)[:, :k]
-    b = _rand((k, n + ld_pad), 8, dtype, 0.5)[:, :n]
-    ad, bd = a.cuda(), b.cuda()
-    ad = torch.as_strided(ad, (m, k), (k + ld_pad, 1)) if ld_pad else ad
-    a_dev = torch.empty(m, k + ld_pad, device="cuda", dtype=dtype)[:, :k]
+    a = _rand((m, k), 7, dtype, 0.5)
+    b = _rand((k, n), 8, dtype, 0.5)
+    # ld_pad: keep the data ragged but make the row pitch a multiple of 8 elements (TMA)
+    ka = -(-k // 8) * 8 if ld_pad else k
+    na = -(-n // 8) * 8 if ld_pad else n
+    a_dev = torch.empty(m, ka, device="cuda", dtype=dtype)[:, :k]
     a_dev.copy_(a)
-    b_dev = torch.empty(k, n + ld_pad, device="cuda", dtype=dtype)[:, :n]
+    b_dev = torch.empty(k, na, device="cuda", dtype=dtype)[:, :n]
     b_dev.copy_(b)
     c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
     grid = (newt.cdiv(m, bm), newt.cdiv(n, bn))
@@ -73,7 +74,7 @@ def _run_matmul(kernel, m, n, k, dtype, bm=64, bn=64, bk=32, ld_pad=0, **kw):
                  b_dev.stride(1), c.stride(0), c.stride(1), BLOCK_M=bm, BLOCK_N=bn, BLOCK_K=bk, **kw)
     torch.cuda.synchronize()
     assert abi.read_status() == (0, 0)
-    return a.contiguous(), b.contiguous(), c.cpu()
+    return a, b, c.cpu()
 
 
 @pytest.mark.parametrize("m,n,k,pad", [(64, 64, 32, 0), (256, 256, 128, 0), (300, 200, 100, 4),
