@@ -120,11 +120,15 @@ def _pin(t):
 
 
 class Workload:
+    def __init__(self, small=False, autotune=True):
+        pass
+
     name = ""
     metric = ""
     unit = ""
     dtype = ""
     bound = "hbm"
+    scaling = "weak"
     kernels_per_step = 1
 
     def host_inputs(self, rank, world):  # -> list of pinned CPU tensors
@@ -222,10 +226,16 @@ class MatmulWorkload(Workload):
     M = N = K = 8192
     CPU_ROWS = 1024
 
-    def __init__(self):
+    def __init__(self, small=False, autotune=True):
         from newt_b200 import examples
 
         self.kernel = examples.tile_matmul   # the @dt.kernel tile loop; first call autotunes
+        if not autotune:                     # profiling runs: skip the search, use a fixed tile
+            import newt_b200.deuteron as dt
+            self.kernel = dt.Kernel(examples.tile_matmul.fn, config={
+                "BLOCK_TILE_M": 128, "BLOCK_TILE_N": 256, "BLOCK_TILE_K": 64, "num_stages": 4})
+        if small:                            # profiler-sized case: 160 MB of operands, > L2
+            self.N = self.K = 4096
 
     def host_inputs(self, rank, world):
         scale = 1.0 / self.K ** 0.5
@@ -264,7 +274,57 @@ class MatmulWorkload(Workload):
                 "tile": dict(self.kernel.best_config or {})}
 
 
-WORKLOADS = {w.name: w for w in (MatmulWorkload, SoftmaxWorkload, LayerNormWorkload)}
+class AttentionWorkload(Workload):
+    """Causal attention forward, fp16 [16, 32, 4096, 128]; the 512 (batch, head) pairs are
+    split evenly over the ranks, so this workload scales strongly (fixed total work)."""
+
+    name, metric, unit, dtype, bound = "attention", "attention_tflops", "TFLOP/s", "f16", "tensor"
+    scaling = "strong"
+    B, H, S, D = 16, 32, 4096, 128
+    CPU_HEADS = 8
+
+    def __init__(self, small=False, autotune=True):
+        if small:                            # profiler-sized case: 2 x 32 heads, 256 MB of q/k/v/o
+            self.B = 2
+
+    def host_inputs(self, rank, world):
+        self.heads = max(1, self.B * self.H // world)
+        first = rank * self.heads
+        # one seed per (tensor, rank shard): shards are independent, no exchange needed
+        return [_seeded((self.heads, self.S, self.D), 500 + 10 * first + t, torch.float16)
+                for t in range(3)]
+
+    def to_device(self, host):
+        q, k, v = (h.cuda(non_blocking=True) for h in host)
+        return {"q": q, "k": k, "v": v, "out": torch.empty_like(q)}
+
+    def step(self, dev):
+        from newt_b200 import examples
+        examples.attention(dev["q"], dev["k"], dev["v"], causal=True, out=dev["out"])
+
+    def result(self, dev):
+        return dev["out"]
+
+    def units_per_step(self):
+        return 4 * self.heads * self.S * self.S * self.D // 2   # causal convention: half the square
+
+    def cpu_sample(self, host):
+        from oracle import torch_ref
+        q, k, v = (h[:self.CPU_HEADS] for h in host)
+        scale = 1.0 / self.D ** 0.5
+        return (lambda: torch_ref.attention(q, k, v, scale, True)), \
+            4 * self.CPU_HEADS * self.S * self.S * self.D // 2, \
+            f"{self.CPU_HEADS} of the 512 (batch, head) pairs, F.scaled_dot_product_attention fp32"
+
+    def config(self, world):
+        return {"workload": "causal attention forward fp16 [16,32,4096,128], scale 1/sqrt(128)",
+                "batch": self.B, "heads": self.H, "seq_len": self.S, "head_dim": self.D,
+                "parallelism": f"batch*head over {world} GPU(s), no collective",
+                "l2": "flushed between steps"}
+
+
+WORKLOADS = {w.name: w for w in (MatmulWorkload, SoftmaxWorkload, LayerNormWorkload,
+                                 AttentionWorkload)}
 DEFAULT_WORKLOAD = "matmul"
 
 
@@ -298,7 +358,7 @@ def run_reference(args, wl):
     line = {
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": wl.scaling,
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded N(0,1))",
         "config": wl.config(args.gpus),
         "cpu_baseline": {"value": value, "unit": wl.unit, "cores": torch.get_num_threads(),
@@ -393,10 +453,10 @@ def run_gpu(args, wl):
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": wl.scaling,
             "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic (seeded N(0,1) drawn on the host, copied to HBM before timing)",
-            "config": wl.config(world),
+            "config": dict(wl.config(world), **({"small": True} if args.small else {})),
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": wl.unit,
                          "frac": achieved / peak, "traffic": None,
                          "peak_source": peaks["source"] + (" copy bandwidth" if wl.bound == "hbm"
@@ -433,8 +493,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="newt_b200", choices=["newt_b200", "reference"])
+    ap.add_argument("--small", action="store_true",
+                    help="profiler-sized variant of the workload (never a reported number)")
+    ap.add_argument("--no-autotune", action="store_true",
+                    help="fixed tile configuration instead of the first-call search")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]()
+    wl = WORKLOADS[args.workload](small=args.small, autotune=not args.no_autotune)
     if args.impl == "reference":
         run_reference(args, wl)
     else:

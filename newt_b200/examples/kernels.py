@@ -117,3 +117,69 @@ def matmul(a, b, c=None):
     matmul_kernel[grid](a, b, c, m, n, k, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
                         c.stride(0), c.stride(1))
     return c
+
+
+# examples/05_fused_attention.py:14-48 of the reference, with a batch*head grid axis and an
+# optional causal mask (both written with operations that example already uses).
+@newt.jit
+def attention_kernel(q_ptr, k_ptr, v_ptr, o_ptr, M, N, scale,
+                     sqh, sqm, sqd, skh, skn, skd, svh, svn, svd, soh, som, sod,
+                     BLOCK_M: nl.constexpr, BLOCK_N: nl.constexpr, D: nl.constexpr,
+                     CAUSAL: nl.constexpr):
+    pid = nl.program_id(0)
+    head = nl.program_id(1)
+    offs_m = pid * BLOCK_M + nl.arange(0, BLOCK_M)
+    offs_d = nl.arange(0, D)
+    qmask = offs_m[:, None] < M
+    q = nl.load(q_ptr + head * sqh + offs_m[:, None] * sqm + offs_d[None, :] * sqd,
+                mask=qmask, other=0.0)                                  # [BM, D]
+
+    m_i = nl.full((BLOCK_M,), float("-inf"), dtype=nl.float32)         # row maxes
+    l_i = nl.zeros((BLOCK_M,), dtype=nl.float32)                       # row sums
+    acc = nl.zeros((BLOCK_M, D), dtype=nl.float32)                     # output acc
+
+    hi = N
+    if CAUSAL:
+        hi = nl.minimum(N, (pid + 1) * BLOCK_M)                        # skip blocks above the diagonal
+    for start_n in range(0, hi, BLOCK_N):
+        offs_n = start_n + nl.arange(0, BLOCK_N)
+        nmask = offs_n[:, None] < N
+        k = nl.load(k_ptr + head * skh + offs_n[:, None] * skn + offs_d[None, :] * skd,
+                    mask=nmask, other=0.0)                              # [BN, D]
+        qk = nl.dot(q, nl.trans(k)) * scale                            # [BM, BN]
+        keep = offs_n[None, :] < N
+        if CAUSAL:
+            keep = keep & (offs_n[None, :] <= offs_m[:, None])
+        qk = nl.where(keep, qk, float("-inf"))
+        m_new = nl.maximum(m_i, nl.max(qk, axis=1))
+        alpha = nl.exp(m_i - m_new)
+        p = nl.exp(qk - m_new[:, None])
+        l_i = l_i * alpha + nl.sum(p, axis=1)
+        acc = acc * alpha[:, None]
+        v = nl.load(v_ptr + head * svh + offs_n[:, None] * svn + offs_d[None, :] * svd,
+                    mask=nmask, other=0.0)                              # [BN, D]
+        acc = nl.dot(p.to(q_ptr.dtype.element_ty), v, acc)
+        m_i = m_new
+
+    acc = acc / l_i[:, None]
+    nl.store(o_ptr + head * soh + offs_m[:, None] * som + offs_d[None, :] * sod, acc, mask=qmask)
+
+
+def attention(q, k, v, causal=False, out=None, BLOCK_M=128, BLOCK_N=128, num_warps=4):
+    """q, k, v: [batch*heads, seq, head_dim] (or [batch, heads, seq, head_dim] contiguous)."""
+    if q.dim() == 4:
+        b, h, s, d = q.shape
+        o = attention(q.reshape(b * h, s, d), k.reshape(b * h, -1, d), v.reshape(b * h, -1, d),
+                      causal, None if out is None else out.reshape(b * h, s, d), BLOCK_M, BLOCK_N,
+                      num_warps)
+        return o.reshape(b, h, s, d)
+    bh, m, d = q.shape
+    n = k.shape[1]
+    o = torch.empty_like(q) if out is None else out
+    grid = (newt.cdiv(m, BLOCK_M), bh)
+    attention_kernel[grid](q, k, v, o, m, n, 1.0 / d ** 0.5,
+                           q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1),
+                           k.stride(2), v.stride(0), v.stride(1), v.stride(2), o.stride(0),
+                           o.stride(1), o.stride(2), BLOCK_M=BLOCK_M, BLOCK_N=BLOCK_N, D=d,
+                           CAUSAL=bool(causal), num_warps=num_warps)
+    return o

@@ -446,10 +446,11 @@ class TileAccess:
     """A 2-D pointer block  base + idx0 * s0 + idx1 * s1  where each index is
     `ax_d + (program id | loop iteration) * BLOCK_d`."""
 
-    def __init__(self, an, ptr, what):
+    def __init__(self, an, ptr, what, allow_batch=False):
         if len(ptr.shape) != 2:
             raise Unmatched(f"{what}: not a 2-D pointer block")
         self.shape = ptr.shape
+        self.batch = None    # (("pid", axis), stride polynomial) of a leading batch/head index
         try:
             self.base, poly = an.pointer(ptr)
         except NotAffine as e:
@@ -483,6 +484,10 @@ class TileAccess:
                     self.origin[d] = self.origin[d] + Poly.atom(atom) * blocks
                     placed = True
                     break
+            if not placed and allow_batch and atom[0] == "pid" and self.batch is None \
+                    and _param_only(q):
+                self.batch = (atom, q)
+                placed = True
             if not placed:
                 raise Unmatched(f"{what}: {atom} does not step by whole blocks")
         if not leftovers.is_zero():
@@ -707,6 +712,216 @@ def lower_gemm(trace, an, num_stages):
     return plan
 
 
+# --------------------------------------------------------------------------- attention
+
+class AttentionPlan(Plan):
+    kind, entry = "flash attention loop", "nb200_attention_fwd"
+
+    def __init__(self):
+        self.q = self.k = self.v = self.o = None
+        self.block_m = 0
+        self.pid_m = 0
+        self.pid_head = None
+        self.seq_q = self.seq_kv = None
+        self.d = 0
+        self.scale = None          # parameter name or float
+        self.causal = False
+        self.strides = {}          # tensor -> (head stride fn | None, row stride fn, inner stride fn)
+
+    def launch(self, grid, args):
+        import torch
+
+        from ..runtime import kernels
+
+        gm = grid[self.pid_m] if self.pid_m < len(grid) else 1
+        bh = 1
+        if self.pid_head is not None:
+            bh = grid[self.pid_head] if self.pid_head < len(grid) else 1
+        seq_q = gm * self.block_m
+        if self.seq_q is not None:
+            seq_q = min(seq_q, self.seq_q(args))
+        seq_kv = self.seq_kv(args)
+        if seq_q <= 0 or bh <= 0:
+            return
+        scale = args[self.scale] if isinstance(self.scale, str) else self.scale
+        views = {}
+        for name, seq in ((self.q, seq_q), (self.k, seq_kv), (self.v, seq_kv), (self.o, seq_q)):
+            hs, rs, inner = self.strides[name]
+            if inner(args) != 1:
+                raise CompileError(f"attention: '{name}' is not unit-stride along head_dim")
+            # a single head needs no head stride; give TMA the natural one
+            head_stride = hs(args) if hs is not None else rs(args) * seq
+            views[name] = torch.as_strided(args[name], (bh, seq, self.d),
+                                           (head_stride, rs(args), 1),
+                                           args[name].storage_offset())
+        kernels.attention_fwd(views[self.q], views[self.k], views[self.v], views[self.o], scale,
+                              self.causal)
+
+
+def _carried_by_placeholder(loop):
+    return {ph.uid: (name, init, nxt) for name, (ph, init, nxt) in loop.carried.items()}
+
+
+def lower_attention(trace, an, num_stages):
+    loops, stores = _loops(trace), _top_level_stores(trace)
+    if len(loops) != 1 or len(stores) != 1:
+        raise Unmatched("attention: expected one KV loop followed by one store")
+    loop = loops[0]
+    if loop.effects:
+        raise Unmatched("attention: the KV loop has side effects")
+    by_ph = _carried_by_placeholder(loop)
+    accs = [(n, v) for n, v in loop.carried.items() if v[2].op == "dot"]
+    if len(accs) != 1 or len(loop.carried) != 3:
+        raise Unmatched("attention: the loop must carry exactly (m_i, l_i, acc)")
+    acc_name, (acc_ph, acc_init, pv) = accs[0]
+
+    neg_inf = float("-inf")
+    q, k, v = (Cap(n, lambda x: isinstance(x, Node) and x.op == "load") for n in "qkv")
+    qkm = Pat("where", [Cap("keep"), p_bin("mul", Pat("dot", [q, Pat("trans", [k]), None]),
+                                             Cap("scale")), p_const(neg_inf)])
+    m_ph = Cap("m_ph", lambda x: isinstance(x, Node) and x.op == "carried")
+    m_new = p_bin("max", m_ph, Pat("reduce", [qkm], fn="max", axis=1))
+    alpha = p_math("exp", p_bin("sub", m_ph, m_new))
+    prob = p_math("exp", p_bin("sub", qkm, Pat("expand", [m_new], axis=1)))
+    pv_pat = Pat("dot", [Pat("cast", [prob]), v,
+                         p_bin("mul", Cap("acc_ph"), Pat("expand", [alpha], axis=1))])
+    caps = {}
+    if not match(pv_pat, pv, caps):
+        raise Unmatched("attention: the accumulator update is not "
+                        "dot(exp(qk - m_new).to(dtype), v, acc * exp(m_i - m_new))")
+    if caps["acc_ph"] is not acc_ph:
+        raise Unmatched("attention: the rescaled block is not the carried accumulator")
+    m_name, m_init, m_next = by_ph[caps["m_ph"].uid]
+    l_entries = [(n, v) for n, v in loop.carried.items() if n not in (acc_name, m_name)]
+    l_name, (l_ph, l_init, l_next) = l_entries[0]
+    c2 = dict(caps)
+    if not match(m_new, m_next, c2):
+        raise Unmatched("attention: m_i is not updated to maximum(m_i, max(qk))")
+    c3 = dict(caps)
+    c3["l_ph"] = l_ph
+    if not match(p_bin("add", p_bin("mul", Cap("l_ph"), alpha),
+                       Pat("reduce", [prob], fn="sum", axis=1)), l_next, c3):
+        raise Unmatched("attention: l_i is not updated to l_i * alpha + sum(p)")
+    if not (m_init.op == "full" and m_init.args[0] == neg_inf and l_init.op == "full"
+            and l_init.args[0] == 0 and acc_init.op == "full" and acc_init.args[0] == 0):
+        raise Unmatched("attention: running state must start at (-inf, 0, 0)")
+
+    _, o_ptr, o_val, o_mask, _ = stores[0]
+    want = p_bin("div", Pat("loopout", [], loop=loop.uid, name=acc_name),
+                 Pat("expand", [Pat("loopout", [], loop=loop.uid, name=l_name)], axis=1))
+    if not match(want, o_val, {}):
+        raise Unmatched("attention: the stored value is not acc / l_i")
+
+    ql, kl, vl = caps["q"], caps["k"], caps["v"]
+    dt = ql.dtype
+    if dt not in (tp.float16, tp.bfloat16) or kl.dtype != dt or vl.dtype != dt \
+            or o_ptr.dtype.element != dt or pv.args[0].dtype != dt:
+        raise Unmatched("attention: q, k, v, p and out must share float16 or bfloat16")
+    for ld, nm in ((ql, "q"), (kl, "k"), (vl, "v")):
+        if ld.args[1] is not None and ld.args[2] not in (None, 0, 0.0):
+            raise Unmatched(f"attention: masked lanes of {nm} must read 0")
+
+    tq = TileAccess(an, ql.args[0], "attention Q", allow_batch=True)
+    tk = TileAccess(an, kl.args[0], "attention K", allow_batch=True)
+    tv = TileAccess(an, vl.args[0], "attention V", allow_batch=True)
+    to = TileAccess(an, o_ptr, "attention O", allow_batch=True)
+    bm, d = tq.shape
+    bn = tk.shape[0]
+    if tk.shape[1] != d or tv.shape != (bn, d) or to.shape != (bm, d):
+        raise Unmatched("attention: tile shapes are inconsistent")
+    if d not in (64, 128):
+        raise Unmatched(f"attention: head_dim {d} has no kernel (64 and 128 only)")
+    it = ("iter", loop.uid)
+    sm = tq.step_of(0, "pid")
+    if sm is None or sm[1] != bm or to.step_of(0, "pid") != sm:
+        raise Unmatched("attention: program_id does not tile the query rows by BLOCK_M")
+    for t, nm in ((tk, "K"), (tv, "V")):
+        if t.step_of(0, "iter") != (it, bn):
+            raise Unmatched(f"attention: {nm} does not advance by BLOCK_N rows per iteration")
+    for t in (tq, tk, tv, to):
+        if not t.origin[1].is_zero():
+            raise Unmatched("attention: head_dim must be addressed from 0")
+    heads = {t.batch[0] for t in (tq, tk, tv, to) if t.batch is not None}
+    if len(heads) > 1 or (heads and any(t.batch is None for t in (tq, tk, tv, to))):
+        raise Unmatched("attention: q, k, v and out must share one batch*head index")
+
+    # masks: key bound and causal term
+    kv_bounds, causal = [], False
+    for term in _split_and(caps["keep"]):
+        fn, dpoly = _comparison(an, term, "attention mask")
+        if len(term.shape) < 2:
+            raise Unmatched("attention: score mask is not 2-D")
+        has0, has1 = ("ax", 0) in dpoly.atoms(), ("ax", 1) in dpoly.atoms()
+        if has1 and not has0 and fn == "lt":
+            qd, rest = dpoly.coeff_of(("ax", 1))
+            moving = Poly({m: c for m, c in rest.terms.items() if any(a[0] != "param" for a in m)})
+            if qd.const_value() != 1 or moving != tk.origin[0]:
+                raise Unmatched("attention: key mask bounds a different index than K uses")
+            kv_bounds.append(-(rest - moving))
+        elif has0 and has1:
+            # offs_n[None, :] <= offs_m[:, None]   (or the mirrored >=)
+            expect = Poly.atom(("ax", 1)) + tk.origin[0] - Poly.atom(("ax", 0)) - tq.origin[0]
+            if (fn == "le" and dpoly == expect) or (fn == "ge" and dpoly == -expect):
+                causal = True
+            else:
+                raise Unmatched("attention: only the causal mask `key index <= query index` "
+                                "is supported")
+        else:
+            raise Unmatched("attention: unsupported score mask term")
+    if len(kv_bounds) != 1:
+        raise Unmatched("attention: scores must be masked by `key index < N` exactly once")
+    seq_kv = kv_bounds[0]
+    kb = _tile_bounds(an, kl.args[1], tk, "attention K").get(0, [seq_kv])
+    vb = _tile_bounds(an, vl.args[1], tv, "attention V").get(0, [seq_kv])
+    if any(b != seq_kv for b in kb + vb):
+        raise Unmatched("attention: K/V load masks and the score mask disagree on N")
+    qb = _tile_bounds(an, ql.args[1], tq, "attention Q").get(0, [])
+    ob = _tile_bounds(an, o_mask, to, "attention O").get(0, [])
+
+    # loop range: 0 .. N step BLOCK_N, or 0 .. min(N, (pid + 1) * BLOCK_M) when causal
+    try:
+        if an.poly(loop.lo) != Poly.const(0) or an.poly(loop.step) != Poly.const(bn):
+            raise Unmatched("attention: the KV loop must be range(0, hi, BLOCK_N)")
+    except NotAffine:
+        raise Unmatched("attention: the KV loop bounds are not affine")
+    hi_ok = False
+    hi = loop.hi
+    try:
+        hi_ok = an.poly(hi) == seq_kv
+    except NotAffine:
+        pass
+    if not hi_ok and causal and isinstance(hi, Node) and hi.op == "bin" \
+            and dict(hi.attrs)["fn"] == "min":
+        diag = (Poly.atom(sm[0]) + Poly.const(1)) * Poly.const(bm)
+        try:
+            sides = [an.poly(x) for x in hi.args]
+            hi_ok = seq_kv in sides and diag in sides
+        except NotAffine:
+            pass
+    if not hi_ok:
+        raise Unmatched("attention: the KV loop must cover keys [0, N) (or stop at the "
+                        "diagonal block when causal)")
+
+    sc = caps["scale"]
+    plan = AttentionPlan()
+    if _param_name(sc) is not None:
+        plan.scale = _param_name(sc)
+    elif isinstance(sc, Node) and sc.op == "const":
+        plan.scale = float(sc.args[0])
+    else:
+        raise Unmatched("attention: scale must be an argument or a literal")
+    plan.q, plan.k, plan.v, plan.o = tq.base, tk.base, tv.base, to.base
+    plan.block_m, plan.d, plan.causal = bm, d, causal
+    plan.pid_m = sm[0][1]
+    plan.pid_head = next(iter(heads))[1] if heads else None
+    plan.seq_q = _extent_fn("query", qb, ob)
+    plan.seq_kv = _compile_int(seq_kv)
+    for t in (tq, tk, tv, to):
+        plan.strides[t.base] = (_compile_int(t.batch[1]) if t.batch else None,
+                                _compile_int(t.stride[0]), _compile_int(t.stride[1]))
+    return plan
+
+
 # --------------------------------------------------------------------------- driver
 
 _RECOGNISERS = []
@@ -720,7 +935,8 @@ def lower(trace, num_warps=4, num_stages=3):
     attempts = [("add", lambda: lower_add(trace, an)),
                 ("softmax", lambda: lower_softmax(trace, an)),
                 ("layernorm", lambda: lower_layernorm(trace, an)),
-                ("matmul", lambda: lower_gemm(trace, an, num_stages))]
+                ("matmul", lambda: lower_gemm(trace, an, num_stages)),
+                ("attention", lambda: lower_attention(trace, an, num_stages))]
     attempts += [(n, (lambda f=f: f(trace, an, num_stages))) for n, f in _RECOGNISERS]
     for name, attempt in attempts:
         try:

@@ -90,3 +90,34 @@ def matmul_kernel_unmasked(a_ptr, b_ptr, c_ptr, M, N, K, sam, sak, sbk, sbn, scm
         b_ptrs += BLOCK_K * sbk
     c_ptrs = c_ptr + offs_m[:, None] * scm + offs_n[None, :] * scn
     nl.store(c_ptrs, acc.to(nl.float16))
+
+
+@newt.jit
+def attention_kernel_2d(q_ptr, k_ptr, v_ptr, o_ptr, M, N, scale,
+                        sqm, sqd, skn, skd, svn, svd, som, sod,
+                        BLOCK_M: nl.constexpr, BLOCK_N: nl.constexpr, D: nl.constexpr):
+    # examples/05_fused_attention.py:14-48 as shipped: single head, non-causal
+    pid = nl.program_id(0)
+    offs_m = pid * BLOCK_M + nl.arange(0, BLOCK_M)
+    offs_d = nl.arange(0, D)
+    qmask = offs_m[:, None] < M
+    q = nl.load(q_ptr + offs_m[:, None] * sqm + offs_d[None, :] * sqd, mask=qmask, other=0.0)
+    m_i = nl.full((BLOCK_M,), float("-inf"), dtype=nl.float32)
+    l_i = nl.zeros((BLOCK_M,), dtype=nl.float32)
+    acc = nl.zeros((BLOCK_M, D), dtype=nl.float32)
+    for start_n in range(0, N, BLOCK_N):
+        offs_n = start_n + nl.arange(0, BLOCK_N)
+        nmask = offs_n[:, None] < N
+        k = nl.load(k_ptr + offs_n[:, None] * skn + offs_d[None, :] * skd, mask=nmask, other=0.0)
+        qk = nl.dot(q, nl.trans(k)) * scale
+        qk = nl.where(offs_n[None, :] < N, qk, float("-inf"))
+        m_new = nl.maximum(m_i, nl.max(qk, axis=1))
+        alpha = nl.exp(m_i - m_new)
+        p = nl.exp(qk - m_new[:, None])
+        l_i = l_i * alpha + nl.sum(p, axis=1)
+        acc = acc * alpha[:, None]
+        v = nl.load(v_ptr + offs_n[:, None] * svn + offs_d[None, :] * svd, mask=nmask, other=0.0)
+        acc = nl.dot(p.to(nl.float16), v, acc)
+        m_i = m_new
+    acc = acc / l_i[:, None]
+    nl.store(o_ptr + offs_m[:, None] * som + offs_d[None, :] * sod, acc, mask=qmask)

@@ -174,6 +174,37 @@ def test_autotune_reset_to_zero_first_call():
     assert all(c == 0.0 for c in calls)  # every timed call started from zero
 
 
+def test_attention_example_as_shipped():
+    # examples/05_fused_attention.py:66-80: M = N = 1024, D = 64, fp16, single head, vs SDPA
+    m = n = 1024
+    d = 64
+    q, k, v = (_rand((m, d), s, torch.float16) for s in (21, 22, 23))
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.empty_like(qd)
+    rk.attention_kernel_2d[(newt.cdiv(m, 64),)](
+        qd, kd, vd, o, m, n, 1.0 / d ** 0.5, qd.stride(0), qd.stride(1), kd.stride(0),
+        kd.stride(1), vd.stride(0), vd.stride(1), o.stride(0), o.stride(1),
+        BLOCK_M=64, BLOCK_N=64, D=d, num_warps=4)
+    ref = torch_ref.attention(q[None], k[None], v[None], 1.0 / d ** 0.5)[0]
+    assert (o.cpu().float() - ref).abs().max().item() < 2e-2      # the example's own bar
+    assert torch_ref.rel_frobenius(o.cpu().float(), ref) <= 1e-2
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_attention_batched(causal, dtype):
+    from newt_b200 import examples
+
+    b, h, s, d = 2, 3, 640, 128
+    q, k, v = (_rand((b, h, s, d), sd, dtype) for sd in (24, 25, 26))
+    o = examples.attention(q.cuda(), k.cuda(), v.cuda(), causal=causal)
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    ref = torch_ref.attention(q.reshape(b * h, s, d), k.reshape(b * h, s, d),
+                              v.reshape(b * h, s, d), 1.0 / d ** 0.5, causal)
+    assert torch_ref.rel_frobenius(o.cpu().reshape(b * h, s, d).float(), ref) <= 1e-2
+
+
 # ---- deuteron ---------------------------------------------------------------------
 
 @dt.kernel(config={"BLOCK_TILE_M": 128, "BLOCK_TILE_N": 128, "BLOCK_TILE_K": 64, "num_stages": 4})

@@ -50,6 +50,27 @@ def test_matmul_lowers_to_tcgen05_gemm(kernel, extents):
     assert (p.a, p.b, p.c) == ("a_ptr", "b_ptr", "c_ptr")
 
 
+def test_attention_lowers_to_fused_kernel():
+    from newt_b200 import examples
+
+    strides = [524288, 128, 1] * 4
+    a = dict(zip(["sqh", "sqm", "sqd", "skh", "skn", "skd", "svh", "svn", "svd", "soh", "som",
+                  "sod"], strides), M=4000, N=4096, scale=0.088)
+    for causal in (False, True):
+        c = examples.attention_kernel.specialize(F16, F16, F16, F16, 4000, 4096, 0.088, *strides,
+                                                 BLOCK_M=128, BLOCK_N=64, D=128, CAUSAL=causal)
+        p = c.plan
+        assert isinstance(p, lower.AttentionPlan) and p.entry == "nb200_attention_fwd"
+        assert (p.causal, p.pid_m, p.pid_head, p.d, p.scale) == (causal, 0, 1, 128, "scale")
+        assert p.seq_q(a) == 4000 and p.seq_kv(a) == 4096
+        assert [f(a) for f in p.strides["k_ptr"]] == [524288, 128, 1]
+    # the reference's example as shipped: one head, no causal mask, D = 64
+    c = rk.attention_kernel_2d.specialize(F16, F16, F16, F16, 1024, 1024, 0.125, 64, 1, 64, 1, 64,
+                                          1, 64, 1, BLOCK_M=64, BLOCK_N=64, D=64)
+    assert isinstance(c.plan, lower.AttentionPlan)
+    assert c.plan.pid_head is None and not c.plan.causal and c.plan.d == 64
+
+
 def test_pointer_walk_is_resolved_as_induction():
     c = rk.matmul_kernel.specialize(F16, F16, F16, 64, 64, 64, 64, 1, 64, 1, 64, 1,
                                     BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)

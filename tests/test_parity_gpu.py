@@ -226,3 +226,80 @@ def test_gemm_check_rejects_without_launching():
     af = torch.zeros(64, 64, device="cuda")
     with pytest.raises(abi.UnsupportedError):
         kernels.gemm(af, af, af, 64, 64, 64, 64, 64, 64)
+
+
+# ---- K5 -------------------------------------------------------------------------
+
+def _attention(q, k, v, causal, scale=None):
+    o = torch.full(q.shape, float("nan"), device="cuda", dtype=q.dtype)
+    kernels.attention_fwd(q, k, v, o, scale or 1.0 / q.shape[-1] ** 0.5, causal)
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    return o
+
+
+def test_attention_golden(golden):
+    for case in golden.cases("attention"):
+        p = f"attention/{case}"
+        q, k, v = (golden.get(f"{p}/{n}") for n in "qkv")
+        got = _attention(q.cuda(), k.cuda(), v.cuda(), case.startswith("causal")).cpu()
+        assert torch_ref.rel_frobenius(got.float(), golden.get(p + "/expected_f32")) <= 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("bh,sq,skv,d", [(1, 1, 1, 64), (2, 128, 128, 128), (3, 200, 333, 128),
+                                         (2, 333, 333, 64), (1, 100, 700, 128), (2, 513, 129, 64)])
+def test_attention_vs_oracle(dtype, causal, bh, sq, skv, d):
+    g = torch.Generator().manual_seed(bh + sq * 3 + skv * 5 + d)
+    q, k, v = (torch.randn(bh, s, d, generator=g).to(dtype) for s in (sq, skv, skv))
+    got = _attention(q.cuda(), k.cuda(), v.cuda(), causal).cpu()
+    scale = 1.0 / d ** 0.5
+    # the C oracle follows the reference's loop literally (P rounded to the input type)
+    want = cport.attention(q, k, v, scale, causal=causal, block_n=128)
+    assert torch_ref.rel_frobenius(got.float(), want.float()) <= (4e-3 if dtype == torch.float16
+                                                                    else 1.6e-2)
+    if not (causal and sq > skv):   # SDPA leaves rows with no visible key undefined
+        assert torch_ref.rel_frobenius(got.float(), torch_ref.attention(q, k, v, scale, causal)) <= 1e-2
+
+
+def test_attention_strided_heads_and_rows():
+    # q, k, v as slices of one packed [bh, s, 3 * d] projection output
+    bh, s, d = 4, 384, 128
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(bh, s, 3 * d, generator=g).half()
+    dev = qkv.cuda()
+    q, k, v = dev[..., :d], dev[..., d:2 * d], dev[..., 2 * d:]
+    got = _attention(q, k, v, True).cpu()
+    ref = torch_ref.attention(qkv[..., :d], qkv[..., d:2 * d], qkv[..., 2 * d:], 1 / d ** 0.5, True)
+    assert torch_ref.rel_frobenius(got.float(), ref) <= 1e-2
+
+
+def test_attention_rows_sum_property_at_config_size():
+    # with V = ones every output element is exactly sum(p)/l = 1 up to rounding, at any size
+    bh, s, d = 8, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(bh, s, d, device="cuda", generator=g).half()
+    k = torch.randn(bh, s, d, device="cuda", generator=g).half()
+    v = torch.ones(bh, s, d, device="cuda", dtype=torch.float16)
+    o = _attention(q, k, v, True)
+    assert (o.float() - 1.0).abs().max().item() <= 2e-3
+    # and one head against the fp32 oracle
+    v = torch.randn(bh, s, d, device="cuda", generator=g).half()
+    o = _attention(q, k, v, True)
+    ref = torch_ref.attention(q[:1].cpu(), k[:1].cpu(), v[:1].cpu(), 1 / d ** 0.5, True)
+    assert torch_ref.rel_frobenius(o[:1].cpu().float(), ref) <= 1e-2
+
+
+def test_attention_argument_errors():
+    q = torch.zeros(1, 16, 96, device="cuda", dtype=torch.float16)
+    with pytest.raises(abi.UnsupportedError, match="head_dim"):
+        kernels.attention_fwd(q, q, q, q, 0.1, False)
+    q = torch.zeros(1, 16, 64, device="cuda", dtype=torch.float32)
+    with pytest.raises(TypeError):
+        kernels.attention_fwd(q, q, q, q, 0.1, False)
+    q = torch.zeros(1, 16, 64, device="cuda", dtype=torch.float16)
+    e = torch.zeros(1, 0, 64, device="cuda", dtype=torch.float16)
+    with pytest.raises(abi.KernelLibraryError, match="empty key"):
+        kernels.attention_fwd(q, e, e, q, 0.1, False)
+    kernels.attention_fwd(e, q, q, e, 0.1, False)   # no queries: nothing to do
