@@ -330,6 +330,24 @@ DEFAULT_WORKLOAD = "matmul"
 
 # --------------------------------------------------------------------------- runners
 
+def max_over_ranks(values, world, device):
+    """Element-wise maximum of a list of floats over all ranks (the job is as slow as its
+    slowest rank); identity for a single process."""
+    if world <= 1:
+        return list(values)
+    import torch.distributed as dist
+
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def job_throughput(units_per_rank_step, world, steps, total_ms, unit):
+    """Whole-job value: the units all ranks processed divided by the slowest rank's time."""
+    scale = 1e9 if unit == "GB/s" else 1e12
+    return units_per_rank_step * world * steps / (total_ms * 1e-3) / scale
+
+
 def _dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -435,18 +453,14 @@ def run_gpu(args, wl):
 
     clocks = sampler.stop() if rank == 0 else None
 
-    # max over ranks
-    if world > 1:
-        t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms = t.tolist()
+    total_ms, e2e_ms = max_over_ranks([total_ms, e2e_ms], world, "cuda")
 
     if rank == 0:
         peaks = measured_peaks()
         scale = 1e9 if wl.unit == "GB/s" else 1e12
         units = wl.units_per_step()
-        value = units * world * args.steps / (total_ms * 1e-3) / scale
-        e2e_value = units * world / (e2e_ms * 1e-3) / scale
+        value = job_throughput(units, world, args.steps, total_ms, wl.unit)
+        e2e_value = job_throughput(units, world, 1, e2e_ms, wl.unit)
         launch_ms = total_ms / (args.steps * wl.kernels_per_step)
         achieved = units / wl.kernels_per_step / (launch_ms * 1e-3) / scale
         peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops_burst"]

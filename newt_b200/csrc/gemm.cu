@@ -298,7 +298,8 @@ int check_problem(const void* a, const void* b, const void* c, int64_t m, int64_
   if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
     return fail(NB200_E_INVALID, "gemm: extent beyond int32");
   if (m == 0 || n == 0) return 0;
-  if (!a || !b || !c) return fail(NB200_E_INVALID, "gemm: null tensor pointer");
+  if (!c || (k > 0 && (!a || !b))) return fail(NB200_E_INVALID, "gemm: null tensor pointer");
+  if (k == 0) return 0;  // C is cleared; A and B are never read
   if (lda < k || ldb < n || ldc < n)
     return fail(NB200_E_INVALID, "gemm: row stride smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
                 (long long)lda, (long long)ldb, (long long)ldc);
