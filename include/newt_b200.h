@@ -103,9 +103,9 @@ int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
  * "library default". */
 typedef struct nb200_gemm_config {
   int32_t block_m; /* 128 (one CTA) or 256 (CTA pair)                        */
-  int32_t block_n; /* 64, 128 or 256                                         */
+  int32_t block_n; /* 64, 128 or 256 (256 only for a CTA pair)               */
   int32_t block_k; /* 64                                                     */
-  int32_t stages;  /* 2..8; clamped to what fits in 227 KB of shared memory  */
+  int32_t stages;  /* 1..8; snapped to a depth that fits 227 KB of shared mem */
   int32_t cta_pair;/* 0 or 1                                                 */
   int32_t reserved[3];
 } nb200_gemm_config;

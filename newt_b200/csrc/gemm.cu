@@ -251,11 +251,215 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// ---- CTA-pair variant: 256 x 256 output tile per cluster of two CTAs ---------------
+//
+// Each CTA of the pair loads its own 128 rows of A and its own 128 columns of B (no
+// multicast), so a stage costs 32 KB per CTA instead of 48 KB and the ring can be 6-7
+// deep; the leader CTA issues one tcgen05.mma.cta_group::2 (M = 256) that reads both
+// CTAs' shared memory and accumulates 128 rows in each CTA's tensor memory.
+// Barriers: `full` lives in the leader and counts one arrival + bytes from each CTA's
+// producer; `empty` and `acc_full` exist in both CTAs and the leader commits to each;
+// `acc_empty` lives in the leader and collects the epilogue warps of both CTAs.
+template <int STAGES, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                     const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  constexpr int BN = 256;                                // cluster tile width
+  constexpr uint32_t kABytes = kBlockM * kBlockK * 2;    // this CTA's 128 rows of A: 16 KB
+  constexpr uint32_t kBSlab = kBlockK * 64 * 2;          // 64 columns of B: 8 KB
+  constexpr uint32_t kBBytes = kBSlab * 2;               // this CTA's 128 columns of B
+  constexpr uint32_t kStageBytes = kABytes + kBBytes;    // 32 KB
+  constexpr uint32_t kTmemCols = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile uint32_t abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const WaitCtx ctx{&abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 2);    // one producer arrival per CTA (leader's copy is used)
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&acc_full_bar[b]), 1);
+      mbar_init(smem_u32(&acc_empty_bar[b]), 8);  // four epilogue warps in each CTA
+    }
+    mbar_init_fence();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc_pair(smem_u32(&tmem_slot), kTmemCols);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
+  const int num_tiles = m_blocks2 * p.n_blocks;
+  const int first = cluster_id_x(), step = cluster_count_x();
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first; tile < num_tiles && ok; tile += step) {
+        int mb, nb;
+        tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
+        const int row0 = mb * 2 * kBlockM + rank * kBlockM;
+        const int col0 = nb * BN + rank * (BN / 2);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
+          if (!ok) break;
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          mbar_arrive_expect_tx_cluster(bar, kStageBytes);
+          tma_load_2d_pair(a_dst, &tmap_a, kb * kBlockK, row0, bar);
+          tma_load_2d_pair(a_dst + kABytes, &tmap_b, col0, kb * kBlockK, bar);
+          tma_load_2d_pair(a_dst + kABytes + kBSlab, &tmap_b, col0 + 64, kb * kBlockK, bar);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && leader) {
+      constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
+      constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(smem_u32(&acc_empty_bar[buf]), acc_phase ^ 1, ctx, ST_WAIT_ACC_EMPTY, tile);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, ST_WAIT_TMA_FULL, tile);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint64_t a_desc = with_address(kADesc, a_addr);
+          const uint64_t b_desc = with_address(kBDesc, a_addr + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / 16; ++kk)
+            mma_f16_ss_pair(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
+                            p.idesc, (kb | kk) != 0 ? 1u : 0u);
+          // the slot is free in both CTAs once these MMAs retire
+          mma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
+          mma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) {
+          mma_commit_pair(map_to_cta(smem_u32(&acc_full_bar[buf]), 0));
+          mma_commit_pair(map_to_cta(smem_u32(&acc_full_bar[buf]), 1));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue: this CTA's 128 rows of the 256-row tile ----------------
+    const int quarter = warp & 3;
+    using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    OutT* c = static_cast<OutT*>(p.c);
+    int it = 0;
+    bool ok = true;
+    for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
+      int mb, nb;
+      tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = mb * 2 * kBlockM + rank * kBlockM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+      OutT* crow = c + (long long)row * p.ldc;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col0 = nb * BN + c0;
+        if (col0 >= p.n) break;
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        if (row < p.m) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            uint32_t packed[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const float lo = __uint_as_float(r[g * 8 + 2 * h]);
+              const float hi = __uint_as_float(r[g * 8 + 2 * h + 1]);
+              if constexpr (BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                packed[h] = *reinterpret_cast<uint32_t*>(&v);
+              } else {
+                __half2 v = __floats2half2_rn(lo, hi);
+                packed[h] = *reinterpret_cast<uint32_t*>(&v);
+              }
+            }
+            if (p.c_vec_ok && col + 8 <= p.n) {
+              *reinterpret_cast<uint4*>(crow + col) =
+                  make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            } else {
+              const OutT* e = reinterpret_cast<const OutT*>(packed);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col + j < p.n) crow[col + j] = e[j];
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[buf]), 0));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  cluster_sync_all();   // nobody leaves while the other CTA may still touch its barriers or tiles
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ---- host ----------------------------------------------------------------------
 
 struct Resolved {
   int block_n;
   int stages;
+  bool pair;
 };
 
 int smem_bytes_for(int block_n, int stages) {
@@ -265,9 +469,23 @@ int smem_bytes_for(int block_n, int stages) {
 int resolve_config(const nb200_gemm_config* cfg, int64_t n, Resolved* out) {
   int bm = cfg ? cfg->block_m : 0, bn = cfg ? cfg->block_n : 0, bk = cfg ? cfg->block_k : 0;
   int stages = cfg ? cfg->stages : 0;
-  if (cfg && cfg->cta_pair) return fail(NB200_E_UNSUPPORTED, "cta_pair tiles are not built yet");
+  const bool pair = cfg && (cfg->cta_pair || bm == 2 * kBlockM);
+  out->pair = pair;
+  if (pair) {
+    if (bm != 0 && bm != 2 * kBlockM)
+      return fail(NB200_E_INVALID, "block_m=%d: a CTA pair computes 256-row tiles", bm);
+    if (bn != 0 && bn != 256)
+      return fail(NB200_E_INVALID, "block_n=%d: CTA-pair tiles are 256 columns wide", bn);
+    if (bk != 0 && bk != kBlockK)
+      return fail(NB200_E_INVALID, "block_k=%d: the TMA ring moves 64-element K slabs", bk);
+    if (stages != 0 && (stages < 1 || stages > 8))
+      return fail(NB200_E_INVALID, "stages=%d: supported 1..8", stages);
+    out->block_n = 256;
+    out->stages = stages == 0 ? 6 : (stages >= 7 ? 7 : (stages >= 6 ? 6 : (stages >= 5 ? 5 : 4)));
+    return 0;
+  }
   if (bm != 0 && bm != kBlockM)
-    return fail(NB200_E_INVALID, "block_m=%d: this kernel's MMA tile is 128 rows", bm);
+    return fail(NB200_E_INVALID, "block_m=%d: MMA tiles are 128 rows (256 for a CTA pair)", bm);
   if (bk != 0 && bk != kBlockK)
     return fail(NB200_E_INVALID, "block_k=%d: the TMA ring moves 64-element K slabs", bk);
   if (bn == 0) bn = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
@@ -330,6 +548,38 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bo
     kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
   }
   return cuda_check(cudaGetLastError(), "gemm launch");
+}
+
+template <int STAGES>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool bf16,
+                cudaStream_t stream) {
+  const int smem = STAGES * (kBlockM * kBlockK * 2 + kBlockK * 128 * 2) + 1024;
+  const void* kern = bf16 ? (const void*)gemm_pair_kernel<STAGES, true>
+                          : (const void*)gemm_pair_kernel<STAGES, false>;
+  if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
+    return cuda_check(e, "gemm pair smem attribute");
+  cudaLaunchConfig_t lc = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.blockDim = dim3(kThreads);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  // as many pairs as the device can hold at once, never more than there are tiles
+  lc.gridDim = dim3(2);
+  int clusters = 0;
+  if (cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, kern, &lc))
+    return cuda_check(e, "cluster occupancy query");
+  if (clusters < 1) return fail(NB200_E_CUDA, "gemm: the device cannot host a CTA pair");
+  const long long tiles = (long long)cdiv64(p.m, 2 * kBlockM) * p.n_blocks;
+  if (tiles < clusters) clusters = (int)tiles;
+  lc.gridDim = dim3(2 * clusters);
+  void* args[3] = {(void*)&ta, (void*)&tb, (void*)&p};
+  return cuda_check(cudaLaunchKernelExC(&lc, kern, args), "gemm pair launch");
 }
 
 }  // namespace
@@ -423,11 +673,19 @@ extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int6
   p.n_blocks = (int)cdiv64(n, cfg.block_n);
   p.k_blocks = (int)cdiv64(k, kBlockK);
   const bool bf16 = dtype == NB200_BF16;
-  p.idesc = sm100::instr_desc_f16(kBlockM, cfg.block_n, bf16, false, true);
+  p.idesc = sm100::instr_desc_f16(cfg.pair ? 2 * kBlockM : kBlockM, cfg.block_n, bf16, false, true);
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * 2) % 16 == 0) ? 1 : 0;
   p.status = device_status_ptr();
   if (!p.status) return fail(NB200_E_CUDA, "gemm: device status word is not addressable");
 
+  if (cfg.pair) {
+    switch (cfg.stages) {
+      case 4: return launch_pair<4>(ta, tb, p, bf16, stream);
+      case 5: return launch_pair<5>(ta, tb, p, bf16, stream);
+      case 6: return launch_pair<6>(ta, tb, p, bf16, stream);
+      default: return launch_pair<7>(ta, tb, p, bf16, stream);
+    }
+  }
   const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
   const int sms = device_info().sm_count;
   const int grid = (int)(tiles < sms ? tiles : sms);

@@ -215,7 +215,7 @@ class Kernel:
             # tcgen05 tiles: 128-row MMAs, 64..256 columns, 64-element K slabs per TMA stage
             space = {name: [64, 128, 256] for name in ks.tunable}
             space["num_warps"] = [4]
-            space["num_stages"] = [2, 3, 4, 6]
+            space["num_stages"] = [2, 3, 4, 6, 7]
         else:
             space = {name: [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048]
                      for name in ks.tunable}

@@ -71,10 +71,13 @@ def layernorm(x, w, b, eps=1e-5, out=None):
     return out
 
 
-# Tile / pipeline choices for sm_100a: 128-row tcgen05 MMAs, 64..256 columns, 64-element
-# K slabs per TMA stage, ring depth as num_stages.
+# Tile / pipeline choices for sm_100a: 128-row tcgen05 MMAs (256 rows = a CTA pair), 64..256
+# columns, 64-element K slabs per TMA stage, ring depth as num_stages.
 @newt.autotune(
     configs=[
+        newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=7),
+        newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=6),
+        newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=5),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=4),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=3),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_warps=4, num_stages=6),

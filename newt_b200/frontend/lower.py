@@ -611,15 +611,20 @@ class GemmPlan(Plan):
         return max(m, 0), max(n, 0), max(k, 0)
 
     def hardware_key(self):
-        """What distinguishes this plan on the device: the tcgen05 tile is picked by
-        BLOCK_N (when it is a tile the kernel has) and the ring depth by num_stages."""
-        bn = self.block[1] if self.block[1] in (64, 128, 256) else 0
-        return ("gemm", bn, self.num_stages)
+        """What distinguishes this plan on the device: BLOCK_M = BLOCK_N = 256 asks for the
+        CTA-pair kernel (one 256-row tcgen05 MMA over two SMs); otherwise the tcgen05 tile is
+        picked by BLOCK_N (when it is a tile the kernel has); num_stages is the ring depth."""
+        bm, bn, _ = self.block
+        if bm == 256 and bn == 256:
+            return ("gemm-pair", 256, self.num_stages)
+        return ("gemm", bn if bn in (64, 128, 256) else 0, self.num_stages)
 
     def config(self):
         from ..runtime import kernels
 
-        _, bn, stages = self.hardware_key()
+        kind, bn, stages = self.hardware_key()
+        if kind == "gemm-pair":
+            return kernels.gemm_config(block_m=256, block_n=256, stages=stages, cta_pair=1)
         return kernels.gemm_config(block_n=bn, stages=stages)
 
     def launch(self, grid, args):

@@ -190,6 +190,22 @@ def test_gemm_vs_oracle(dtype, block_n, m, n, k):
         assert torch_ref.rel_frobenius(got.float(), want.float()) <= 4e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("stages", [4, 6, 7])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (130, 72, 200), (700, 1000, 328),
+                                   (2048, 2048, 2048)])
+def test_gemm_cta_pair_vs_oracle(dtype, stages, m, n, k):
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k + 1)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype).cuda()
+    b = torch.randn(k, n, generator=g).to(dtype).cuda()
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    kernels.gemm(a, b, c, m, n, k, k, n, n,
+                 kernels.gemm_config(block_m=256, block_n=256, stages=stages, cta_pair=1))
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    assert torch_ref.rel_frobenius(c.cpu().float(), torch_ref.matmul(a.cpu(), b.cpu())) <= 1e-2
+
+
 def test_gemm_linearity_at_full_size():
     # size-independent property at the benchmark size: (A1 + A2) @ B == A1 @ B + A2 @ B
     # up to rounding, and a spot-checked block against the fp32 oracle
