@@ -231,11 +231,16 @@ class MatmulWorkload(Workload):
 
         self.kernel = examples.tile_matmul   # the @dt.kernel tile loop; first call autotunes
         if not autotune:                     # profiling runs: skip the search, use a fixed tile
-            import newt_b200.deuteron as dt
-            self.kernel = dt.Kernel(examples.tile_matmul.fn, config={
-                "BLOCK_TILE_M": 128, "BLOCK_TILE_N": 256, "BLOCK_TILE_K": 64, "num_stages": 4})
+            self.use_tile(128, 256, 64, 4)
         if small:                            # profiler-sized case: 160 MB of operands, > L2
             self.N = self.K = 4096
+
+    def use_tile(self, bm, bn, bk, stages):
+        import newt_b200.deuteron as dt
+        from newt_b200 import examples
+
+        self.kernel = dt.Kernel(examples.tile_matmul.fn, config={
+            "BLOCK_TILE_M": bm, "BLOCK_TILE_N": bn, "BLOCK_TILE_K": bk, "num_stages": stages})
 
     def host_inputs(self, rank, world):
         scale = 1.0 / self.K ** 0.5
@@ -511,8 +516,18 @@ def main():
                     help="profiler-sized variant of the workload (never a reported number)")
     ap.add_argument("--no-autotune", action="store_true",
                     help="fixed tile configuration instead of the first-call search")
+    ap.add_argument("--tile", default="128,256,64,4",
+                    help="BLOCK_M,BLOCK_N,BLOCK_K,num_stages used with --no-autotune (matmul)")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=INT",
+                    help="library tuning knob (nb200_set_tuning), e.g. attn_variant=2")
     args = ap.parse_args()
+    for item in args.tune:
+        from newt_b200.runtime import abi
+        key, _, val = item.partition("=")
+        abi.set_tuning(key, int(val))
     wl = WORKLOADS[args.workload](small=args.small, autotune=not args.no_autotune)
+    if args.no_autotune and isinstance(wl, MatmulWorkload):
+        wl.use_tile(*(int(v) for v in args.tile.split(",")))
     if args.impl == "reference":
         run_reference(args, wl)
     else:

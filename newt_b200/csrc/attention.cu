@@ -349,6 +349,345 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// ---- two Q tiles per CTA ---------------------------------------------------------
+//
+// Same algorithm, scheduled for overlap: a CTA owns 256 query rows as two 128-row tiles
+// X = 0, 1, each with its own S/P and O regions of tensor memory (4 x 128 columns) and its
+// own group of four softmax warps.  The MMA warp interleaves the two tiles,
+//     S_0(0) S_1(0) | PV_0(j) S_0(j+1) PV_1(j) S_1(j+1) | ...
+// so while group 0 works on S_0(j+1) the tensor core runs PV_1(j) and S_1(j+1), and the two
+// softmax groups (two warps per SM sub-partition) hide each other's latencies.  S_X(j+1) is
+// issued right after PV_X(j): MMAs of one thread execute in order, so it cannot overtake the
+// read of P_X(j) that shares its columns.  K and V blocks are loaded once for both tiles.
+constexpr int kThreads2 = 320;   // TMA warp, MMA warp, 2 x 4 softmax warps
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads2, 1)
+    attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                     const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  constexpr int STAGES = 2;
+  constexpr int kChunks = D / 64;
+  constexpr uint32_t kChunkBytes = 128 * 128;
+  constexpr uint32_t kTileBytes = kChunks * kChunkBytes;
+  constexpr uint32_t kTmemCols = 512;
+  // tensor memory: S/P of tile X at X*128, O of tile X at 256 + X*128
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+  __shared__ uint64_t s_full[2], p_full[2], pv_done[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile uint32_t abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem_base;                       // two Q tiles
+  const uint32_t k_smem = q_smem + 2 * kTileBytes;
+  const uint32_t v_smem = k_smem + STAGES * kTileBytes;
+  const WaitCtx ctx{&abort_flag, p.status};
+
+  const int n_q_pairs = (p.n_q_tiles + 1) / 2;
+  const int head = blockIdx.x / n_q_pairs;
+  const int q_pair = n_q_pairs - 1 - (blockIdx.x % n_q_pairs);   // heaviest causal work first
+  const int q0 = q_pair * 2 * kTileM;
+  // KV blocks each tile needs
+  int nblk[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int qx = q0 + x * kTileM;
+    int kv_end = p.seq_kv;
+    if (p.causal) kv_end = min(kv_end, qx + kTileM);
+    nblk[x] = qx < p.seq_q ? (kv_end + kTileN - 1) / kTileN : 0;
+  }
+  const int n_max = max(nblk[0], nblk[1]);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&q_full), 1);
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&k_full[s]), 1);
+      mbar_init(smem_u32(&k_empty[s]), 1);
+      mbar_init(smem_u32(&v_full[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), 1);
+    }
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(smem_u32(&s_full[x]), 1);
+      mbar_init(smem_u32(&p_full[x]), 4);
+      mbar_init(smem_u32(&pv_done[x]), 1);
+    }
+    mbar_init_fence();
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(smem_u32(&q_full), 2 * kTileBytes);   // rows past seq_q are zero-filled
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_3d(q_smem + x * kTileBytes + c * kChunkBytes, &tmap_q, c * 64,
+                      q0 + x * kTileM, head, smem_u32(&q_full));
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int slot = j % STAGES;
+        const uint32_t par = (j / STAGES) & 1;
+        ok = mbar_wait(smem_u32(&k_empty[slot]), par ^ 1, ctx, ST_ATTN_K_EMPTY, j);
+        if (!ok) break;
+        mbar_arrive_expect_tx(smem_u32(&k_full[slot]), kTileBytes);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_3d(k_smem + slot * kTileBytes + c * kChunkBytes, &tmap_k, c * 64, j * kTileN,
+                      head, smem_u32(&k_full[slot]));
+        ok = mbar_wait(smem_u32(&v_empty[slot]), par ^ 1, ctx, ST_ATTN_V_EMPTY, j);
+        if (!ok) break;
+        mbar_arrive_expect_tx(smem_u32(&v_full[slot]), kTileBytes);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_3d(v_smem + slot * kTileBytes + c * kChunkBytes, &tmap_v, c * 64, j * kTileN,
+                      head, smem_u32(&v_full[slot]));
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint64_t kKMajor = smem_desc_sw128(16, 1024);
+      constexpr uint64_t kVDesc = smem_desc_sw128(kChunkBytes, 1024);
+      bool ok = mbar_wait(smem_u32(&q_full), 0, ctx, ST_ATTN_Q, 0);
+
+      // S_x(j) = Q_x K_j^T into tile x's S columns; the caller has waited for K_j
+      auto issue_s = [&](int x, int j) {
+        const uint32_t kb = k_smem + (j % STAGES) * kTileBytes;
+        const uint32_t qb = q_smem + x * kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          mma_f16_ss(tmem_base + x * kTileN, with_address(kKMajor, qb + off),
+                     with_address(kKMajor, kb + off), p.idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&s_full[x]));
+      };
+
+      if (ok && n_max > 0) {
+        ok = mbar_wait(smem_u32(&k_full[0]), 0, ctx, ST_ATTN_K_FULL, 0);
+        if (ok) {
+          tc_fence_after_sync();
+          if (nblk[0] > 0) issue_s(0, 0);
+          if (nblk[1] > 0) issue_s(1, 0);
+          mma_commit(smem_u32(&k_empty[0]));
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int slot = j % STAGES;
+        const bool more = j + 1 < n_max;
+        bool have_v = false, have_k = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (j >= nblk[x]) continue;
+          ok = mbar_wait(smem_u32(&p_full[x]), j & 1, ctx, ST_ATTN_P_FULL, j);
+          if (ok && !have_v) {
+            ok = mbar_wait(smem_u32(&v_full[slot]), (j / STAGES) & 1, ctx, ST_ATTN_V_FULL, j);
+            have_v = true;
+          }
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t vb = v_smem + slot * kTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < kTileN / 16; ++kk)
+            mma_f16_ts(tmem_base + 2 * kTileN + x * kTileN, tmem_base + x * kTileN + kk * 8,
+                       with_address(kVDesc, vb + kk * 2048), p.idesc_pv, (j | kk) != 0 ? 1u : 0u);
+          mma_commit(smem_u32(&pv_done[x]));
+          if (j + 1 < nblk[x]) {
+            if (!have_k) {
+              ok = mbar_wait(smem_u32(&k_full[(j + 1) % STAGES]), ((j + 1) / STAGES) & 1, ctx,
+                             ST_ATTN_K_FULL, j + 1);
+              have_k = true;
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            issue_s(x, j + 1);   // ordered after PV_x(j), which reads the columns it overwrites
+          }
+        }
+        if (!ok) break;
+        mma_commit(smem_u32(&v_empty[slot]));
+        if (more) mma_commit(smem_u32(&k_empty[(j + 1) % STAGES]));
+      }
+    }
+  } else {
+    // ---------------- softmax + epilogue: group x owns tile x, one thread per row ----------------
+    using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const int x = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int qx = q0 + x * kTileM;
+    const int row = qx + quarter * 32 + lane;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_base + x * kTileN;
+    const uint32_t o_tmem = tmem_base + lane_base + 2 * kTileN + x * kTileN;
+    const int n_blocks = nblk[x];
+    const float c = p.scale_log2;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+
+    for (int j = 0; j < n_blocks; ++j) {
+      ok = mbar_wait(smem_u32(&s_full[x]), j & 1, ctx, ST_ATTN_S_FULL, j);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int kv0 = j * kTileN;
+      const bool edge = (p.causal && kv0 + kTileN - 1 > qx) || (kv0 + kTileN > p.seq_kv);
+      const int limit = p.causal ? min(row, p.seq_kv - 1) : p.seq_kv - 1;  // last visible column
+
+      // pass 1: row maximum, 64 columns at a time
+      float mx = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t s[2][32];
+        tmem_ld_32x32(s_tmem + h * 64, s[0]);
+        tmem_ld_32x32(s_tmem + h * 64 + 32, s[1]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(s[q][i]);
+            if (edge && kv0 + h * 64 + q * 32 + i > limit) v = -INFINITY;
+            mx = fmaxf(mx, v);
+          }
+      }
+      const float m_new = fmaxf(m_run, mx * c);
+      const bool need = (m_new - m_run > kRescaleThreshold) && (m_new > -INFINITY);
+      if (j == 0) {
+        if (need) m_run = m_new;
+      } else if (__any_sync(0xffffffffu, need)) {
+        float alpha = 1.0f;
+        if (need) {
+          alpha = exp2_approx(m_run - m_new);
+          m_run = m_new;
+          l_run *= alpha;
+        }
+        ok = mbar_wait(smem_u32(&pv_done[x]), (j - 1) & 1, ctx, ST_ATTN_PV_DONE, j);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int q = 0; q < D / 32; ++q) {
+          uint32_t o[32];
+          tmem_ld_32x32(o_tmem + q * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(o_tmem + q * 32, o);
+        }
+      }
+      const float m_use = m_run > -INFINITY ? m_run : 0.0f;
+
+      // pass 2: exponentials, row sum, P written over the S columns already consumed
+      float sum = 0.0f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t s[2][32];
+        tmem_ld_32x32(s_tmem + h * 64, s[0]);
+        tmem_ld_32x32(s_tmem + h * 64 + 32, s[1]);
+        tmem_ld_wait();
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float a = __uint_as_float(s[i / 16][(2 * i) % 32]);
+          float b = __uint_as_float(s[i / 16][(2 * i) % 32 + 1]);
+          if (edge) {
+            if (kv0 + h * 64 + 2 * i > limit) a = -INFINITY;
+            if (kv0 + h * 64 + 2 * i + 1 > limit) b = -INFINITY;
+          }
+          const float pa = exp2_approx(fmaf(a, c, -m_use));
+          const float pb = exp2_approx(fmaf(b, c, -m_use));
+          sum += pa + pb;
+          if constexpr (BF16) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb);
+            pk[i] = *reinterpret_cast<uint32_t*>(&v);
+          } else {
+            __half2 v = __floats2half2_rn(pa, pb);
+            pk[i] = *reinterpret_cast<uint32_t*>(&v);
+          }
+        }
+        tmem_st_32x32(s_tmem + h * 32, pk);
+      }
+      l_run += sum;
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&p_full[x]));
+    }
+
+    if (ok && n_blocks > 0) {
+      ok = mbar_wait(smem_u32(&pv_done[x]), (n_blocks - 1) & 1, ctx, ST_ATTN_PV_DONE, n_blocks);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && n_blocks > 0) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l_run;
+      OutT* orow = static_cast<OutT*>(p.o) + (long long)head * p.o_head_stride +
+                   (long long)row * p.o_row_stride;
+      const bool vec = ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
+#pragma unroll
+      for (int q = 0; q < D / 32; ++q) {
+        uint32_t o[32];
+        tmem_ld_32x32(o_tmem + q * 32, o);
+        tmem_ld_wait();
+        if (row < p.seq_q) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const float lo = __uint_as_float(o[g * 8 + 2 * h]) * inv;
+              const float hi = __uint_as_float(o[g * 8 + 2 * h + 1]) * inv;
+              if constexpr (BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                packed[h] = *reinterpret_cast<uint32_t*>(&v);
+              } else {
+                __half2 v = __floats2half2_rn(lo, hi);
+                packed[h] = *reinterpret_cast<uint32_t*>(&v);
+              }
+            }
+            OutT* dst = orow + q * 32 + g * 8;
+            if (vec) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            } else {
+              const OutT* e = reinterpret_cast<const OutT*>(packed);
+#pragma unroll
+              for (int t = 0; t < 8; ++t) dst[t] = e[t];
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // ---- host ----------------------------------------------------------------------
 
 template <int D, int STAGES>
@@ -363,6 +702,20 @@ int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
     return cuda_check(cudaGetLastError(), "attention launch");
   };
   return bf16 ? go(attn_fwd_kernel<D, STAGES, true>) : go(attn_fwd_kernel<D, STAGES, false>);
+}
+
+template <int D>
+int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                 const AttnParams& p, bool bf16, cudaStream_t stream) {
+  const int smem = (2 + 2 * 2) * (D / 64) * 128 * 128 + 1024;   // two Q tiles, 2-deep K and V rings
+  const int grid = p.bh * ((p.n_q_tiles + 1) / 2);
+  auto go = [&](auto kern) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_check(e, "attention smem attribute");
+    kern<<<grid, kThreads2, smem, stream>>>(tq, tk, tv, p);
+    return cuda_check(cudaGetLastError(), "attention launch");
+  };
+  return bf16 ? go(attn_fwd2_kernel<D, true>) : go(attn_fwd2_kernel<D, false>);
 }
 
 int encode_qkv_map(CUtensorMap* map, const void* base, int64_t bh, int64_t seq, int64_t d,
@@ -430,6 +783,13 @@ extern "C" int nb200_attention_fwd(const void* q, const void* k, const void* v, 
   if ((int64_t)p.bh * p.n_q_tiles > INT32_MAX)
     return fail(NB200_E_INVALID, "attention: too many tiles for one launch");
 
+  // "attn_variant" = 2 selects the two-tile kernel; the one-tile kernel is the default (it is
+  // the faster of the two as measured so far)
+  const int variant = tuning("attn_variant", 0);
+  if (variant == 2) {
+    if (d == 128) return launch_attn2<128>(tq, tk, tv, p, bf16, stream);
+    return launch_attn2<64>(tq, tk, tv, p, bf16, stream);
+  }
   const int stages = tuning("attn_stages", 0);
   if (d == 128) {
     if (stages == 3) return launch_attn<128, 3>(tq, tk, tv, p, bf16, stream);
