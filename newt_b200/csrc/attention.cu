@@ -53,16 +53,25 @@ enum : unsigned int {
   ST_ATTN_S_FULL, ST_ATTN_P_FULL, ST_ATTN_PV_DONE
 };
 
-template <int D, int STAGES, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+// COMPACT: one S buffer, one-deep K and V rings, 256 TMEM columns and at most 168 registers,
+// so that two CTAs share an SM: each CTA is then a plain serial pipeline (S_j, softmax_j,
+// PV_j) and the overlap of tensor core and softmax comes from the neighbour CTA, which also
+// hides the per-CTA prologue and epilogue.
+template <int D, int STAGES, bool BF16, bool COMPACT>
+__global__ void __launch_bounds__(kThreads, COMPACT ? 2 : 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
   constexpr int kChunks = D / 64;                       // 64-element (128-byte) column chunks
   constexpr uint32_t kChunkBytes = 128 * 128;           // 128 rows x 128 B
   constexpr uint32_t kTileBytes = kChunks * kChunkBytes;  // one Q, K or V tile
-  constexpr uint32_t kSCol0 = 0, kSCol1 = kTileN, kOCol = 2 * kTileN;
-  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kSCol0 = 0, kSCol1 = COMPACT ? 0 : kTileN;
+  constexpr uint32_t kOCol = COMPACT ? kTileN : 2 * kTileN;
+  constexpr uint32_t kTmemCols = COMPACT ? 256 : 512;
+  static_assert(!COMPACT || STAGES == 1, "the compact variant keeps one K and one V tile");
+  // block j uses S buffer j % 2 (or the only one) for the (j / 2)-th (or j-th) time
+  auto buf_of = [](int j) { return COMPACT ? 0 : (j & 1); };
+  auto par_of = [](int j) { return uint32_t(COMPACT ? (j & 1) : ((j >> 1) & 1)); };
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
@@ -152,12 +161,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = mbar_wait(smem_u32(&q_full), 0, ctx, ST_ATTN_Q, 0);
 
       auto issue_s = [&](int j) -> bool {
-        const int slot = j % STAGES, buf = j & 1;
+        const int slot = j % STAGES, buf = buf_of(j);
         if (!mbar_wait(smem_u32(&k_full[slot]), (j / STAGES) & 1, ctx, ST_ATTN_K_FULL, j))
           return false;
-        // S buffer `buf` was last read (as P) by the PV product of block j-2
-        if (j >= 2 &&
-            !mbar_wait(smem_u32(&pv_done[buf]), ((j - 2) >> 1) & 1, ctx, ST_ATTN_PV_DONE, j))
+        // S buffer `buf` was last read (as P) by the PV product of block j-2; with a single
+        // buffer that product was issued just before this one and MMAs run in issue order
+        if (!COMPACT && j >= 2 &&
+            !mbar_wait(smem_u32(&pv_done[buf]), par_of(j - 2), ctx, ST_ATTN_PV_DONE, j))
           return false;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (buf ? kSCol1 : kSCol0);
@@ -173,14 +183,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         return true;
       };
 
-      if (ok) ok = issue_s(0);
+      if (ok && !COMPACT) ok = issue_s(0);
       for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks) {
+        if (COMPACT) {
+          ok = issue_s(j);
+          if (!ok) break;
+        } else if (j + 1 < n_blocks) {
           ok = issue_s(j + 1);   // overlaps the softmax of block j
           if (!ok) break;
         }
-        const int slot = j % STAGES, buf = j & 1;
-        ok = mbar_wait(smem_u32(&p_full[buf]), (j >> 1) & 1, ctx, ST_ATTN_P_FULL, j) &&
+        const int slot = j % STAGES, buf = buf_of(j);
+        ok = mbar_wait(smem_u32(&p_full[buf]), par_of(j), ctx, ST_ATTN_P_FULL, j) &&
              mbar_wait(smem_u32(&v_full[slot]), (j / STAGES) & 1, ctx, ST_ATTN_V_FULL, j);
         if (!ok) break;
         tc_fence_after_sync();
@@ -207,8 +220,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
 
     for (int j = 0; j < n_blocks; ++j) {
-      const int buf = j & 1;
-      ok = mbar_wait(smem_u32(&s_full[buf]), (j >> 1) & 1, ctx, ST_ATTN_S_FULL, j);
+      const int buf = buf_of(j);
+      ok = mbar_wait(smem_u32(&s_full[buf]), par_of(j), ctx, ST_ATTN_S_FULL, j);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
@@ -228,11 +241,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int i = 0; i < 32; ++i)
             if (kv0 + q * 32 + i > limit) s[q][i] = __float_as_uint(-INFINITY);
       }
-      float mx = -INFINITY;
+      // four independent chains of three-input maxima: the row maximum in 16 dependent steps
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int q = 0; q < 4; ++q)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[q][i]));
+        for (int i = 0; i < 32; i += 2)
+          mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(s[q][i]),
+                                   __uint_as_float(s[q][i + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_run, mx * c);
       // rows past seq_q (and nothing else) can be fully masked; keep them finite
       const bool need = (m_new - m_run > kRescaleThreshold) && (m_new > -INFINITY);
@@ -246,8 +263,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           l_run *= alpha;
         }
         // O holds the products up to block j-1: wait for that PV to retire, then rescale
-        const int pb = (j - 1) & 1;
-        ok = mbar_wait(smem_u32(&pv_done[pb]), ((j - 1) >> 1) & 1, ctx, ST_ATTN_PV_DONE, j);
+        const int pb = buf_of(j - 1);
+        ok = mbar_wait(smem_u32(&pv_done[pb]), par_of(j - 1), ctx, ST_ATTN_PV_DONE, j);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
@@ -262,7 +279,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       const float m_use = m_run > -INFINITY ? m_run : 0.0f;
-      float sum = 0.0f;
+      // two scores per fma / add (packed fp32), four partial sums
+      const unsigned long long c2 = pack2(c, c), negm2 = pack2(-m_use, -m_use);
+      unsigned long long sum2[2] = {0ull, 0ull};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {   // 64 scores -> 32 packed columns per store
         uint32_t pk[32];
@@ -270,9 +289,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < 32; ++i) {
           const float a = __uint_as_float(s[2 * h + i / 16][(2 * i) % 32]);
           const float b = __uint_as_float(s[2 * h + i / 16][(2 * i) % 32 + 1]);
-          const float pa = exp2_approx(fmaf(a, c, -m_use));
-          const float pb2 = exp2_approx(fmaf(b, c, -m_use));
-          sum += pa + pb2;
+          float ta, tb;
+          unpack2(fma2(pack2(a, b), c2, negm2), ta, tb);
+          const float pa = exp2_approx(ta);
+          const float pb2 = exp2_approx(tb);
+          sum2[i & 1] = add2(sum2[i & 1], pack2(pa, pb2));
           if constexpr (BF16) {
             __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb2);
             pk[i] = *reinterpret_cast<uint32_t*>(&v);
@@ -283,7 +304,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tmem_st_32x32(s_tmem + h * 32, pk);
       }
-      l_run += sum;
+      float s0, s1, s2, s3;
+      unpack2(sum2[0], s0, s1);
+      unpack2(sum2[1], s2, s3);
+      l_run += (s0 + s1) + (s2 + s3);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -291,8 +315,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     if (ok && n_blocks > 0) {
-      const int lb = (n_blocks - 1) & 1;
-      ok = mbar_wait(smem_u32(&pv_done[lb]), ((n_blocks - 1) >> 1) & 1, ctx, ST_ATTN_PV_DONE,
+      const int lb = buf_of(n_blocks - 1);
+      ok = mbar_wait(smem_u32(&pv_done[lb]), par_of(n_blocks - 1), ctx, ST_ATTN_PV_DONE,
                      n_blocks);
       ok = __all_sync(0xffffffffu, ok);
     }
@@ -690,7 +714,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
 
 // ---- host ----------------------------------------------------------------------
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool COMPACT = false>
 int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                 const AttnParams& p, bool bf16, cudaStream_t stream) {
   const int smem = (1 + 2 * STAGES) * (D / 64) * 128 * 128 + 1024;
@@ -701,7 +725,8 @@ int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
     kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
     return cuda_check(cudaGetLastError(), "attention launch");
   };
-  return bf16 ? go(attn_fwd_kernel<D, STAGES, true>) : go(attn_fwd_kernel<D, STAGES, false>);
+  return bf16 ? go(attn_fwd_kernel<D, STAGES, true, COMPACT>)
+              : go(attn_fwd_kernel<D, STAGES, false, COMPACT>);
 }
 
 template <int D>
@@ -789,6 +814,10 @@ extern "C" int nb200_attention_fwd(const void* q, const void* k, const void* v, 
   if (variant == 2) {
     if (d == 128) return launch_attn2<128>(tq, tk, tv, p, bf16, stream);
     return launch_attn2<64>(tq, tk, tv, p, bf16, stream);
+  }
+  if (variant == 3) {   // two compact CTAs per SM
+    if (d == 128) return launch_attn<128, 1, true>(tq, tk, tv, p, bf16, stream);
+    return launch_attn<64, 1, true>(tq, tk, tv, p, bf16, stream);
   }
   const int stages = tuning("attn_stages", 0);
   if (d == 128) {

@@ -257,9 +257,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 // multicast), so a stage costs 32 KB per CTA instead of 48 KB and the ring can be 6-7
 // deep; the leader CTA issues one tcgen05.mma.cta_group::2 (M = 256) that reads both
 // CTAs' shared memory and accumulates 128 rows in each CTA's tensor memory.
-// Barriers: `full` lives in the leader and counts one arrival + bytes from each CTA's
-// producer; `empty` and `acc_full` exist in both CTAs and the leader commits to each;
-// `acc_empty` lives in the leader and collects the epilogue warps of both CTAs.
+// Barriers: `full` lives in the leader; the leader's producer announces the bytes of both
+// CTAs' copies and every copy (cta_group::2 form) reports its bytes there, so nothing but
+// the copies themselves crosses to the other SM per stage (a remote release-arrive per
+// stage capped the ring at one slot per ~0.8 us).  `empty` and `acc_full` exist in both
+// CTAs and the leader commits to each; `acc_empty` lives in the leader and collects the
+// epilogue warps of both CTAs, once per tile.
 template <int STAGES, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -286,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     abort_flag = 0;
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 2);    // one producer arrival per CTA (leader's copy is used)
+      mbar_init(smem_u32(&full_bar[s]), 1);    // the leader's copy is the one in use
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
 #pragma unroll
@@ -328,7 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!ok) break;
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
-          mbar_arrive_expect_tx_cluster(bar, kStageBytes);
+          if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * kStageBytes);
           tma_load_2d_pair(a_dst, &tmap_a, kb * kBlockK, row0, bar);
           tma_load_2d_pair(a_dst + kABytes, &tmap_b, col0, kb * kBlockK, bar);
           tma_load_2d_pair(a_dst + kABytes + kBSlab, &tmap_b, col0 + 64, kb * kBlockK, bar);
