@@ -9,9 +9,10 @@
 //
 // Here one CTA owns a 128-row Q tile of one (batch, head):
 //   warp 0      TMA producer: Q once, then K and V blocks of 128 rows into two rings
-//   warp 1      MMA issuer:   S_j = Q K_j^T (operands in shared memory, S in tensor
-//               memory) and O += P_j V_j (P read from tensor memory, V from shared
-//               memory as an MN-major operand, so no transpose of V is ever made)
+//   warp 1      MMA issuer:   S_j = Q K_j^T (Q read from tensor memory, where the softmax
+//               warps copy it once; K from shared memory; S in tensor memory) and
+//               O += P_j V_j (P read from tensor memory, V from shared memory as an
+//               MN-major operand, so no transpose of V is ever made)
 //   warps 2..5  softmax: thread t owns row t of the tile -- a TMEM lane -- so row
 //               max and row sum are plain register loops, no shuffles.  P_j is
 //               written back over S_j as packed 16-bit pairs.
@@ -53,29 +54,24 @@ enum : unsigned int {
   ST_ATTN_S_FULL, ST_ATTN_P_FULL, ST_ATTN_PV_DONE
 };
 
-// COMPACT: one S buffer, one-deep K and V rings, 256 TMEM columns and at most 168 registers,
-// so that two CTAs share an SM: each CTA is then a plain serial pipeline (S_j, softmax_j,
-// PV_j) and the overlap of tensor core and softmax comes from the neighbour CTA, which also
-// hides the per-CTA prologue and epilogue.
-template <int D, int STAGES, bool BF16, bool COMPACT>
-__global__ void __launch_bounds__(kThreads, COMPACT ? 2 : 1)
+template <int D, int STAGES, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
   constexpr int kChunks = D / 64;                       // 64-element (128-byte) column chunks
   constexpr uint32_t kChunkBytes = 128 * 128;           // 128 rows x 128 B
   constexpr uint32_t kTileBytes = kChunks * kChunkBytes;  // one Q, K or V tile
-  constexpr uint32_t kSCol0 = 0, kSCol1 = COMPACT ? 0 : kTileN;
-  constexpr uint32_t kOCol = COMPACT ? kTileN : 2 * kTileN;
-  constexpr uint32_t kTmemCols = COMPACT ? 256 : 512;
-  static_assert(!COMPACT || STAGES == 1, "the compact variant keeps one K and one V tile");
-  // block j uses S buffer j % 2 (or the only one) for the (j / 2)-th (or j-th) time
-  auto buf_of = [](int j) { return COMPACT ? 0 : (j & 1); };
-  auto par_of = [](int j) { return uint32_t(COMPACT ? (j & 1) : ((j >> 1) & 1)); };
+  constexpr uint32_t kSCol0 = 0, kSCol1 = kTileN, kOCol = 2 * kTileN;
+  constexpr uint32_t kQCol = kOCol + kTileN;   // Q as packed 16-bit pairs: D / 2 columns
+  constexpr uint32_t kTmemCols = 512;
+  // block j uses S buffer j % 2 for the (j / 2)-th time
+  auto buf_of = [](int j) { return j & 1; };
+  auto par_of = [](int j) { return uint32_t((j >> 1) & 1); };
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-  __shared__ uint64_t s_full[2], p_full[2], pv_done[2];
+  __shared__ uint64_t s_full[2], p_full[2], pv_done[2], q_tmem_full;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile uint32_t abort_flag;
 
@@ -97,6 +93,7 @@ __global__ void __launch_bounds__(kThreads, COMPACT ? 2 : 1)
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(smem_u32(&q_full), 1);
+    mbar_init(smem_u32(&q_tmem_full), 4);
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&k_full[s]), 1);
@@ -158,24 +155,25 @@ __global__ void __launch_bounds__(kThreads, COMPACT ? 2 : 1)
       // 64 columns of D.  V tile: MN-major, 64-column slabs kChunkBytes apart.
       constexpr uint64_t kKMajor = smem_desc_sw128(16, 1024);
       constexpr uint64_t kVDesc = smem_desc_sw128(kChunkBytes, 1024);
-      bool ok = mbar_wait(smem_u32(&q_full), 0, ctx, ST_ATTN_Q, 0);
+      // Q is read from tensor memory (copied there by the softmax warps): S = Q K^T then
+      // costs shared-memory bandwidth for K only.  This kernel is bound by that bandwidth.
+      bool ok = mbar_wait(smem_u32(&q_tmem_full), 0, ctx, ST_ATTN_Q, 0);
+      if (ok) tc_fence_after_sync();
 
       auto issue_s = [&](int j) -> bool {
         const int slot = j % STAGES, buf = buf_of(j);
         if (!mbar_wait(smem_u32(&k_full[slot]), (j / STAGES) & 1, ctx, ST_ATTN_K_FULL, j))
           return false;
-        // S buffer `buf` was last read (as P) by the PV product of block j-2; with a single
-        // buffer that product was issued just before this one and MMAs run in issue order
-        if (!COMPACT && j >= 2 &&
-            !mbar_wait(smem_u32(&pv_done[buf]), par_of(j - 2), ctx, ST_ATTN_PV_DONE, j))
-          return false;
+        // S buffer `buf` was last read (as P) by the PV product of block j-2.  That product was issued by this thread before this point and MMAs execute
+        // in issue order, so no wait is needed -- and waiting for its completion here kept the
+        // softmax warps idle for ~500 cycles per block.
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (buf ? kSCol1 : kSCol0);
         const uint32_t kb = k_smem + slot * kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_f16_ss(d_tmem, with_address(kKMajor, q_smem + off), with_address(kKMajor, kb + off),
+          mma_f16_ts(d_tmem, tmem_base + kQCol + kk * 8, with_address(kKMajor, kb + off),
                      p.idesc_qk, kk != 0 ? 1u : 0u);
         }
         mma_commit(smem_u32(&k_empty[slot]));
@@ -183,12 +181,9 @@ __global__ void __launch_bounds__(kThreads, COMPACT ? 2 : 1)
         return true;
       };
 
-      if (ok && !COMPACT) ok = issue_s(0);
+      if (ok) ok = issue_s(0);
       for (int j = 0; j < n_blocks && ok; ++j) {
-        if (COMPACT) {
-          ok = issue_s(j);
-          if (!ok) break;
-        } else if (j + 1 < n_blocks) {
+        if (j + 1 < n_blocks) {
           ok = issue_s(j + 1);   // overlaps the softmax of block j
           if (!ok) break;
         }
@@ -219,7 +214,32 @@ __global__ void __launch_bounds__(kThreads, COMPACT ? 2 : 1)
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
 
-    for (int j = 0; j < n_blocks; ++j) {
+    // Q tile: shared memory (TMA layout: rows of 128 B, 16-byte units XOR-swizzled with the
+    // row index) -> this thread's row of tensor memory, as the A operand of S = Q K^T
+    ok = mbar_wait(smem_u32(&q_full), 0, ctx, ST_ATTN_Q, 1);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const int r = quarter * 32 + lane;
+#pragma unroll
+      for (int ch = 0; ch < kChunks; ++ch) {
+        uint32_t qreg[32];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint32_t addr = q_smem + ch * kChunkBytes + r * 128 + ((u ^ (r & 7)) << 4);
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(qreg[4 * u]), "=r"(qreg[4 * u + 1]), "=r"(qreg[4 * u + 2]),
+                         "=r"(qreg[4 * u + 3])
+                       : "r"(addr));
+        }
+        tmem_st_32x32(tmem_base + lane_base + kQCol + ch * 32, qreg);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&q_tmem_full));
+    }
+
+    for (int j = 0; j < n_blocks && ok; ++j) {
       const int buf = buf_of(j);
       ok = mbar_wait(smem_u32(&s_full[buf]), par_of(j), ctx, ST_ATTN_S_FULL, j);
       ok = __all_sync(0xffffffffu, ok);
@@ -714,7 +734,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
 
 // ---- host ----------------------------------------------------------------------
 
-template <int D, int STAGES, bool COMPACT = false>
+template <int D, int STAGES>
 int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                 const AttnParams& p, bool bf16, cudaStream_t stream) {
   const int smem = (1 + 2 * STAGES) * (D / 64) * 128 * 128 + 1024;
@@ -725,8 +745,7 @@ int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
     kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
     return cuda_check(cudaGetLastError(), "attention launch");
   };
-  return bf16 ? go(attn_fwd_kernel<D, STAGES, true, COMPACT>)
-              : go(attn_fwd_kernel<D, STAGES, false, COMPACT>);
+  return bf16 ? go(attn_fwd_kernel<D, STAGES, true>) : go(attn_fwd_kernel<D, STAGES, false>);
 }
 
 template <int D>
@@ -814,10 +833,6 @@ extern "C" int nb200_attention_fwd(const void* q, const void* k, const void* v, 
   if (variant == 2) {
     if (d == 128) return launch_attn2<128>(tq, tk, tv, p, bf16, stream);
     return launch_attn2<64>(tq, tk, tv, p, bf16, stream);
-  }
-  if (variant == 3) {   // two compact CTAs per SM
-    if (d == 128) return launch_attn<128, 1, true>(tq, tk, tv, p, bf16, stream);
-    return launch_attn<64, 1, true>(tq, tk, tv, p, bf16, stream);
   }
   const int stages = tuning("attn_stages", 0);
   if (d == 128) {
