@@ -102,11 +102,12 @@ int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
  * from the kernel's BLOCK_M/BLOCK_N/BLOCK_K constexprs, `stages` from
  * `num_stages` (depth of the TMA/mbarrier ring), `cta_pair` selects 2-CTA
  * tcgen05 (cluster of two CTAs sharing one 256-row MMA).  Zero fields mean
- * "library default". */
+ * "library default": CTA pairs with 128-element K slots when the problem has
+ * at least one 256x256 tile per pair of SMs, single-CTA 128xN tiles otherwise. */
 typedef struct nb200_gemm_config {
   int32_t block_m; /* 128 (one CTA) or 256 (CTA pair)                        */
   int32_t block_n; /* 64, 128 or 256 (256 only for a CTA pair)               */
-  int32_t block_k; /* 64                                                     */
+  int32_t block_k; /* 64; a CTA pair also takes 128 (default) and 192        */
   int32_t stages;  /* 1..8; snapped to a depth that fits 227 KB of shared mem */
   int32_t cta_pair;/* 0 or 1                                                 */
   int32_t reserved[3];

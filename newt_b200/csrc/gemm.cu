@@ -263,7 +263,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 // stage capped the ring at one slot per ~0.8 us).  `empty` and `acc_full` exist in both
 // CTAs and the leader commits to each; `acc_empty` lives in the leader and collects the
 // epilogue warps of both CTAs, once per tile.
-template <int STAGES, bool BF16>
+// KSUB 64-element K slabs share one ring slot (one barrier round trip and one pair of
+// commits per slot).
+template <int STAGES, int KSUB, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
@@ -271,7 +273,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr uint32_t kABytes = kBlockM * kBlockK * 2;    // this CTA's 128 rows of A: 16 KB
   constexpr uint32_t kBSlab = kBlockK * 64 * 2;          // 64 columns of B: 8 KB
   constexpr uint32_t kBBytes = kBSlab * 2;               // this CTA's 128 columns of B
-  constexpr uint32_t kStageBytes = kABytes + kBBytes;    // 32 KB
+  constexpr uint32_t kSlabBytes = kABytes + kBBytes;     // 32 KB per 64 elements of K
+  constexpr uint32_t kStageBytes = KSUB * kSlabBytes;
   constexpr uint32_t kTmemCols = 2 * BN;
 
   extern __shared__ uint8_t smem_raw[];
@@ -314,6 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
   const int num_tiles = m_blocks2 * p.n_blocks;
   const int first = cluster_id_x(), step = cluster_count_x();
+  const int k_rounds = (p.k_blocks + KSUB - 1) / KSUB;
 
   if (warp == 0) {
     // ---------------- TMA producer (one per CTA) ----------------
@@ -326,15 +330,19 @@ __global__ void __launch_bounds__(kThreads, 1)
         tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
         const int row0 = mb * 2 * kBlockM + rank * kBlockM;
         const int col0 = nb * BN + rank * (BN / 2);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = 0; kb < k_rounds; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
           if (!ok) break;
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          const uint32_t a_dst = smem_base + stage * kStageBytes;
           if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * kStageBytes);
-          tma_load_2d_pair(a_dst, &tmap_a, kb * kBlockK, row0, bar);
-          tma_load_2d_pair(a_dst + kABytes, &tmap_b, col0, kb * kBlockK, bar);
-          tma_load_2d_pair(a_dst + kABytes + kBSlab, &tmap_b, col0 + 64, kb * kBlockK, bar);
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {   // slabs past K are zero-filled by the tensor map
+            const uint32_t a_dst = smem_base + stage * kStageBytes + sub * kSlabBytes;
+            const int k0 = (kb * KSUB + sub) * kBlockK;
+            tma_load_2d_pair(a_dst, &tmap_a, k0, row0, bar);
+            tma_load_2d_pair(a_dst + kABytes, &tmap_b, col0, k0, bar);
+            tma_load_2d_pair(a_dst + kABytes + kBSlab, &tmap_b, col0 + 64, k0, bar);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -358,17 +366,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = 0; kb < k_rounds; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint64_t a_desc = with_address(kADesc, a_addr);
-          const uint64_t b_desc = with_address(kBDesc, a_addr + kABytes);
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / 16; ++kk)
-            mma_f16_ss_pair(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
-                            p.idesc, (kb | kk) != 0 ? 1u : 0u);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const uint32_t a_addr = smem_base + stage * kStageBytes + sub * kSlabBytes;
+            const uint64_t a_desc = with_address(kADesc, a_addr);
+            const uint64_t b_desc = with_address(kBDesc, a_addr + kABytes);
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / 16; ++kk)
+              mma_f16_ss_pair(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
+                              p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
+          }
           // the slot is free in both CTAs once these MMAs retire
           mma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
           mma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
@@ -461,6 +472,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 struct Resolved {
   int block_n;
+  int block_k;
   int stages;
   bool pair;
 };
@@ -469,22 +481,30 @@ int smem_bytes_for(int block_n, int stages) {
   return stages * (kBlockM * kBlockK * 2 + kBlockK * block_n * 2) + 1024;
 }
 
-int resolve_config(const nb200_gemm_config* cfg, int64_t n, Resolved* out) {
+int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, Resolved* out) {
   int bm = cfg ? cfg->block_m : 0, bn = cfg ? cfg->block_n : 0, bk = cfg ? cfg->block_k : 0;
   int stages = cfg ? cfg->stages : 0;
-  const bool pair = cfg && (cfg->cta_pair || bm == 2 * kBlockM);
+  bool pair = cfg && (cfg->cta_pair || bm == 2 * kBlockM);
+  if (!cfg || (bm == 0 && bn == 0 && bk == 0 && !cfg->cta_pair)) {
+    // library default: CTA pairs once they fill the machine (74 pairs), else single CTAs
+    pair = cdiv64(m, 2 * kBlockM) * cdiv64(n, 256) >= device_info().sm_count / 2;
+  }
   out->pair = pair;
   if (pair) {
     if (bm != 0 && bm != 2 * kBlockM)
       return fail(NB200_E_INVALID, "block_m=%d: a CTA pair computes 256-row tiles", bm);
     if (bn != 0 && bn != 256)
       return fail(NB200_E_INVALID, "block_n=%d: CTA-pair tiles are 256 columns wide", bn);
-    if (bk != 0 && bk != kBlockK)
-      return fail(NB200_E_INVALID, "block_k=%d: the TMA ring moves 64-element K slabs", bk);
+    if (bk != 0 && bk != kBlockK && bk != 2 * kBlockK && bk != 3 * kBlockK)
+      return fail(NB200_E_INVALID,
+                  "block_k=%d: a CTA-pair ring slot holds 64, 128 or 192 elements of K", bk);
+    out->block_k = bk == 0 ? 2 * kBlockK : bk;
     if (stages != 0 && (stages < 1 || stages > 8))
       return fail(NB200_E_INVALID, "stages=%d: supported 1..8", stages);
     out->block_n = 256;
-    out->stages = stages == 0 ? 6 : (stages >= 7 ? 7 : (stages >= 6 ? 6 : (stages >= 5 ? 5 : 4)));
+    // ring depth: 3 slots of 128 K-elements, 2 of 192, 4..7 of 64
+    out->stages = out->block_k == 128 ? 3 : (out->block_k == 192 ? 2 :
+                  (stages == 0 ? 6 : (stages >= 7 ? 7 : (stages >= 6 ? 6 : (stages >= 5 ? 5 : 4)))));
     return 0;
   }
   if (bm != 0 && bm != kBlockM)
@@ -507,6 +527,7 @@ int resolve_config(const nb200_gemm_config* cfg, int64_t n, Resolved* out) {
     }
   stages = pick;
   out->block_n = bn;
+  out->block_k = kBlockK;
   out->stages = stages;
   return 0;
 }
@@ -553,12 +574,12 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bo
   return cuda_check(cudaGetLastError(), "gemm launch");
 }
 
-template <int STAGES>
+template <int STAGES, int KSUB>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool bf16,
                 cudaStream_t stream) {
-  const int smem = STAGES * (kBlockM * kBlockK * 2 + kBlockK * 128 * 2) + 1024;
-  const void* kern = bf16 ? (const void*)gemm_pair_kernel<STAGES, true>
-                          : (const void*)gemm_pair_kernel<STAGES, false>;
+  const int smem = STAGES * KSUB * (kBlockM * kBlockK * 2 + kBlockK * 128 * 2) + 1024;
+  const void* kern = bf16 ? (const void*)gemm_pair_kernel<STAGES, KSUB, true>
+                          : (const void*)gemm_pair_kernel<STAGES, KSUB, false>;
   if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
     return cuda_check(e, "gemm pair smem attribute");
   cudaLaunchConfig_t lc = {};
@@ -637,7 +658,7 @@ extern "C" int nb200_gemm_check(const void* a, const void* b, const void* c, int
                                 const nb200_gemm_config* config) {
   if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype)) return rc;
   Resolved r;
-  return resolve_config(config, n, &r);
+  return resolve_config(config, m, n, &r);
 }
 
 extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
@@ -646,7 +667,7 @@ extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int6
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype)) return rc;
   Resolved cfg;
-  if (int rc = resolve_config(config, n, &cfg)) return rc;
+  if (int rc = resolve_config(config, m, n, &cfg)) return rc;
   if (m == 0 || n == 0) return 0;
   if (k == 0)  // empty reduction: the accumulator is its zero initial value
     return cuda_check(cudaMemset2DAsync(c, (size_t)ldc * 2, 0, (size_t)n * 2, (size_t)m, stream),
@@ -682,11 +703,13 @@ extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int6
   if (!p.status) return fail(NB200_E_CUDA, "gemm: device status word is not addressable");
 
   if (cfg.pair) {
+    if (cfg.block_k == 128) return launch_pair<3, 2>(ta, tb, p, bf16, stream);
+    if (cfg.block_k == 192) return launch_pair<2, 3>(ta, tb, p, bf16, stream);
     switch (cfg.stages) {
-      case 4: return launch_pair<4>(ta, tb, p, bf16, stream);
-      case 5: return launch_pair<5>(ta, tb, p, bf16, stream);
-      case 6: return launch_pair<6>(ta, tb, p, bf16, stream);
-      default: return launch_pair<7>(ta, tb, p, bf16, stream);
+      case 4: return launch_pair<4, 1>(ta, tb, p, bf16, stream);
+      case 5: return launch_pair<5, 1>(ta, tb, p, bf16, stream);
+      case 6: return launch_pair<6, 1>(ta, tb, p, bf16, stream);
+      default: return launch_pair<7, 1>(ta, tb, p, bf16, stream);
     }
   }
   const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;

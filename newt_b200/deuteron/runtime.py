@@ -212,7 +212,8 @@ class Kernel:
 
     def _space(self, ks):
         if self._has_dot(ks):
-            # tcgen05 tiles: 128-row MMAs, 64..256 columns, 64-element K slabs per TMA stage
+            # tcgen05 tiles: 128-row MMAs (256 rows = a CTA pair), 64..256 columns, 64- or
+            # 128-element K slabs per TMA ring slot
             space = {name: [64, 128, 256] for name in ks.tunable}
             space["num_warps"] = [4]
             space["num_stages"] = [2, 3, 4, 6, 7]

@@ -611,21 +611,24 @@ class GemmPlan(Plan):
         return max(m, 0), max(n, 0), max(k, 0)
 
     def hardware_key(self):
-        """What distinguishes this plan on the device: BLOCK_M = BLOCK_N = 256 asks for the
-        CTA-pair kernel (one 256-row tcgen05 MMA over two SMs); otherwise the tcgen05 tile is
-        picked by BLOCK_N (when it is a tile the kernel has); num_stages is the ring depth."""
-        bm, bn, _ = self.block
+        """What distinguishes this plan on the device.  BLOCK_M = BLOCK_N = 256 asks for the
+        CTA-pair kernel (one 256-row tcgen05 MMA over two SMs) whose ring slot holds BLOCK_K
+        = 64, 128 or 192 elements; otherwise the tcgen05 tile is picked by BLOCK_N (when it
+        is a tile the kernel has); num_stages is the ring depth."""
+        bm, bn, bk = self.block
         if bm == 256 and bn == 256:
-            return ("gemm-pair", 256, self.num_stages)
+            bk = bk if bk in (64, 128, 192) else 128
+            return ("gemm-pair", bk, self.num_stages if bk == 64 else 0)
         return ("gemm", bn if bn in (64, 128, 256) else 0, self.num_stages)
 
     def config(self):
         from ..runtime import kernels
 
-        kind, bn, stages = self.hardware_key()
+        kind, x, stages = self.hardware_key()
         if kind == "gemm-pair":
-            return kernels.gemm_config(block_m=256, block_n=256, stages=stages, cta_pair=1)
-        return kernels.gemm_config(block_n=bn, stages=stages)
+            return kernels.gemm_config(block_m=256, block_n=256, block_k=x, stages=stages,
+                                       cta_pair=1)
+        return kernels.gemm_config(block_n=x, stages=stages)
 
     def launch(self, grid, args):
         from ..runtime import kernels

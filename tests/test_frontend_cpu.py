@@ -71,6 +71,14 @@ def test_attention_lowers_to_fused_kernel():
     assert c.plan.pid_head is None and not c.plan.causal and c.plan.d == 64
 
 
+def test_matmul_block_256_selects_the_cta_pair_kernel():
+    c = rk.matmul_kernel.specialize(F16, F16, F16, 512, 512, 512, 512, 1, 512, 1, 512, 1,
+                                    BLOCK_M=256, BLOCK_N=256, BLOCK_K=128, num_stages=3)
+    assert c.plan.hardware_key() == ("gemm-pair", 128, 0)
+    cfg = c.plan.config()
+    assert (cfg.block_m, cfg.block_n, cfg.block_k, cfg.cta_pair) == (256, 256, 128, 1)
+
+
 def test_pointer_walk_is_resolved_as_induction():
     c = rk.matmul_kernel.specialize(F16, F16, F16, 64, 64, 64, 64, 1, 64, 1, 64, 1,
                                     BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
