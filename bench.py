@@ -357,7 +357,7 @@ def job_throughput(units_per_rank_step, world, steps, total_ms, unit):
 # summarised under profiles/.  softmax and layernorm were captured at full size; matmul and
 # attention on the --small case and scaled by operand bytes (x2.4) resp. head count (x8).
 NCU_TRAFFIC_BYTES = {"softmax": 82.3e6, "layernorm": 83.1e6, "matmul": 2.4 * 209.7e6,
-                     "attention": 8 * 255.2e6}
+                     "attention": 255.2e6 / 64}   # attention: per (batch, head) pair
 
 
 def _dist_env():
@@ -485,7 +485,8 @@ def run_gpu(args, wl):
             "config": dict(wl.config(world), **({"small": True} if args.small else {})),
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": wl.unit,
                          "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES.get(wl.name) if not args.small else None,
+                         "traffic": None if args.small else NCU_TRAFFIC_BYTES[wl.name] *
+                         (wl.heads if wl.name == "attention" else 1),
                          "peak_source": peaks["source"] + (" copy bandwidth" if wl.bound == "hbm"
                                                            else " cuBLAS bf16 burst")},
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d,
