@@ -202,8 +202,29 @@ def _split_row_offset(off, what):
     return stride, const
 
 
+def _row_hardware_key(plan):
+    """Row kernels pick their own threads-per-row and vectors-per-thread from the row length:
+    every block / warp configuration of the source runs the same device code."""
+    return (plan.entry,)
+
+
+def _rows_of(plan, grid, args):
+    """Rows a row-kernel launch covers: one per program, or BLOCK rows per program clipped
+    by the row mask for the 2-D (tile) spelling."""
+    rows = grid[0] * plan.rows_per_program
+    if plan.row_bound is not None:
+        rows = min(rows, plan.row_bound(args))
+    for name, fn in plan.unit_strides:
+        if fn(args) != 1:
+            raise CompileError(f"{plan.kind}: '{name}' is not unit-stride along the row "
+                               f"(stride {fn(args)})")
+    return rows
+
+
 class SoftmaxPlan(Plan):
     kind, entry = "row softmax", "nb200_softmax_f32"
+    rows_per_program, row_bound, unit_strides = 1, None, ()
+    hardware_key = _row_hardware_key
 
     def __init__(self, x, out, n, block, sx, cx, so, co):
         self.x, self.out, self.block = x, out, block
@@ -212,7 +233,7 @@ class SoftmaxPlan(Plan):
     def launch(self, grid, args):
         from ..runtime import kernels
 
-        rows = grid[0]
+        rows = _rows_of(self, grid, args)
         n = min(self.n(args), self.block)
         if rows <= 0 or n <= 0:
             return
@@ -227,6 +248,8 @@ class SoftmaxPlan(Plan):
 
 class LayerNormPlan(Plan):
     kind, entry = "layernorm forward", "nb200_layernorm"
+    rows_per_program, row_bound, unit_strides = 1, None, ()
+    hardware_key = _row_hardware_key
 
     def __init__(self, x, w, b, out, eps, n, block, sx, so):
         self.x, self.w, self.b, self.out, self.eps, self.block = x, w, b, out, eps, block
@@ -235,7 +258,7 @@ class LayerNormPlan(Plan):
     def launch(self, grid, args):
         from ..runtime import kernels
 
-        rows = grid[0]
+        rows = _rows_of(self, grid, args)
         n = min(self.n(args), self.block)
         if rows <= 0 or n <= 0:
             return
@@ -398,6 +421,115 @@ def lower_layernorm(trace, an):
         raise Unmatched("layernorm: eps must be an argument or a literal")
     lwb = RowAccess(an, lw.args[0]).base, RowAccess(an, lb.args[0]).base
     return LayerNormPlan(ax.base, lwb[0], lwb[1], ao.base, eps, n, block, sx, so)
+
+
+# --------------------------------------------------------------------------- row programs as 2-D tiles
+#
+# deuteron writes softmax and layernorm over [BLOCK_M rows, whole row] tiles with axis-1
+# reductions and masks propagated into them (deuteron/codegen.py:382-410 of the reference):
+#     m = nl.max(nl.where(mask, row, -inf), axis=1);  e = nl.exp(row - m[:, None]);  ...
+# The same row kernels serve them; a program then covers BLOCK_M rows.
+
+def _row_tile(an, ptr, mask, what):
+    """(TileAccess, row-extent fn, column-extent polynomial) of a [rows, whole-row] tile."""
+    t = TileAccess(an, ptr, what)
+    step = t.step_of(0, "pid")
+    if step is None or step[0] != ("pid", 0) or step[1] != t.shape[0] or not t.origin[1].is_zero():
+        raise Unmatched(f"{what}: programs must tile the rows by BLOCK and span whole rows")
+    bounds = _tile_bounds(an, mask, t, what)
+    if len(bounds.get(1, [])) != 1:
+        raise Unmatched(f"{what}: the row length must be given by one column mask")
+    return t, _extent_fn("row", bounds.get(0)), bounds[1][0]
+
+
+def _finish_tile_plan(plan, tx, to, row_fns, extra_unit=()):
+    plan.rows_per_program = tx.shape[0]
+    plan.row_bound = _extent_fn("row", *[[]]) if not row_fns else (
+        lambda a, fns=row_fns: min(f(a) for f in fns))
+    plan.unit_strides = tuple((t.base, _compile_int(t.stride[1])) for t in (tx, to)) + \
+        tuple(extra_unit)
+    return plan
+
+
+def lower_softmax_tile(trace, an):
+    _, ptr, value, omask, _ = _single_store(trace, "tile softmax")
+    row = Cap("row", lambda n: isinstance(n, Node) and n.op == "load")
+    m1 = Cap("mask")
+    neg_inf = float("-inf")
+    rmax = Pat("reduce", [Pat("where", [m1, row, p_const(neg_inf)])], fn="max", axis=1)
+    e = p_math("exp", p_bin("sub", row, Pat("expand", [rmax], axis=1)))
+    den = Pat("reduce", [Pat("where", [m1, e, p_const(0.0)])], fn="sum", axis=1)
+    caps = {}
+    if not match(p_bin("div", e, Pat("expand", [den], axis=1)), value, caps):
+        raise Unmatched("tile softmax: stored value is not exp(row - max) / sum(exp(row - max)) "
+                        "with masked axis-1 reductions")
+    load = caps["row"]
+    if load.args[1] is not caps["mask"]:
+        raise Unmatched("tile softmax: reductions are masked differently from the load")
+    if load.dtype != tp.float32 or ptr.dtype.element != tp.float32:
+        raise Unmatched("tile softmax: only float32 rows have a kernel")
+    tx, rows_x, n_x = _row_tile(an, load.args[0], load.args[1], "tile softmax input")
+    to, rows_o, n_o = _row_tile(an, ptr, omask, "tile softmax output")
+    if tx.shape != to.shape:
+        raise Unmatched("tile softmax: input and output tiles differ")
+    zero = Poly()
+    plan = SoftmaxPlan(tx.base, to.base, n_x, tx.shape[1], tx.stride[0], zero, to.stride[0], zero)
+    n_out = _compile_int(n_o)
+    n_in = plan.n
+    plan.n = lambda a: min(n_in(a), n_out(a))
+    return _finish_tile_plan(plan, tx, to, [f for f in (rows_x, rows_o) if f is not None])
+
+
+def lower_layernorm_tile(trace, an):
+    _, ptr, value, omask, _ = _single_store(trace, "tile layernorm")
+    is_load = lambda n: isinstance(n, Node) and n.op == "load"  # noqa: E731
+    row, w, b = Cap("row", is_load), Cap("w", is_load), Cap("b", is_load)
+    m1, count, eps = Cap("mask"), Cap("count"), Cap("eps")
+    mean = p_bin("div", Pat("reduce", [Pat("where", [m1, row, p_const(0.0)])], fn="sum", axis=1),
+                 count)
+    diff = p_bin("sub", row, Pat("expand", [mean], axis=1))
+    var = p_bin("div", Pat("reduce", [Pat("where", [m1, p_bin("mul", diff, diff), p_const(0.0)])],
+                           fn="sum", axis=1), count)
+    rstd = p_math("rsqrt", p_bin("add", var, eps))
+    caps = {}
+    if not match(p_bin("add", p_bin("mul", p_bin("mul", diff, Pat("expand", [rstd], axis=1)), w),
+                       b), value, caps):
+        raise Unmatched("tile layernorm: stored value is not (row - mean) * rsqrt(var + eps) * w "
+                        "+ b with masked two-pass statistics")
+    lx, lw, lb = caps["row"], caps["w"], caps["b"]
+    if lx.args[1] is not caps["mask"]:
+        raise Unmatched("tile layernorm: reductions are masked differently from the load")
+    dt = lx.dtype
+    if dt not in (tp.float32, tp.float16, tp.bfloat16) or lw.dtype != dt or lb.dtype != dt \
+            or ptr.dtype.element != dt:
+        raise Unmatched("tile layernorm: x, w, b and out must share one of "
+                        "float32/float16/bfloat16")
+    tx, rows_x, n_x = _row_tile(an, lx.args[0], lx.args[1], "tile layernorm input")
+    to, rows_o, n_o = _row_tile(an, ptr, omask, "tile layernorm output")
+    try:
+        if an.poly(caps["count"]) != n_x:
+            raise Unmatched("tile layernorm: statistics are not divided by the row length")
+    except NotAffine:
+        raise Unmatched("tile layernorm: divisor is not an integer count")
+    extra = []
+    for ld, nm in ((lw, "w"), (lb, "b")):
+        if len(ld.shape) != 1:
+            raise Unmatched(f"tile layernorm: {nm} must be a 1-D load over the row")
+        base, poly = an.pointer(ld.args[0])
+        q, r = poly.coeff_of(("ax", 0))
+        if not r.is_zero() or not _param_only(q):
+            raise Unmatched(f"tile layernorm: {nm} must be indexed by the column only")
+        extra.append((base, _compile_int(q)))
+    e = caps["eps"]
+    if _param_name(e) is not None:
+        eps_v = _param_name(e)
+    elif isinstance(e, Node) and e.op == "const":
+        eps_v = float(e.args[0])
+    else:
+        raise Unmatched("tile layernorm: eps must be an argument or a literal")
+    plan = LayerNormPlan(tx.base, extra[0][0], extra[1][0], to.base, eps_v, n_x, tx.shape[1],
+                         tx.stride[0], to.stride[0])
+    return _finish_tile_plan(plan, tx, to, [f for f in (rows_x, rows_o) if f is not None], extra)
 
 
 # --------------------------------------------------------------------------- scalar expressions
@@ -943,6 +1075,8 @@ def lower(trace, num_warps=4, num_stages=3):
     attempts = [("add", lambda: lower_add(trace, an)),
                 ("softmax", lambda: lower_softmax(trace, an)),
                 ("layernorm", lambda: lower_layernorm(trace, an)),
+                ("tile softmax", lambda: lower_softmax_tile(trace, an)),
+                ("tile layernorm", lambda: lower_layernorm_tile(trace, an)),
                 ("matmul", lambda: lower_gemm(trace, an, num_stages)),
                 ("attention", lambda: lower_attention(trace, an, num_stages))]
     attempts += [(n, (lambda f=f: f(trace, an, num_stages))) for n, f in _RECOGNISERS]

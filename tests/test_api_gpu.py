@@ -244,3 +244,42 @@ def test_deuteron_matmul_autotuned_bf16(tmp_path, monkeypatch):
     ref = torch.empty_like(out)
     dt_matmul_tuned.ref(xd, yd, ref)          # eager oracle on the device
     torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+@dt.kernel
+def dt_softmax(x, out):
+    for tile_m in dt.tile(x.shape[0]):
+        row = x[tile_m, :]
+        m = row.amax(1)
+        e = dt.exp(row - m[:, None])
+        s = e.sum(1)
+        out[tile_m, :] = e / s[:, None]
+
+
+@dt.kernel
+def dt_layernorm(x, w, b, out, eps):
+    for tile_m in dt.tile(x.shape[0]):
+        row = x[tile_m, :]
+        mean = row.sum(1) / x.shape[1]
+        diff = row - mean[:, None]
+        var = (diff * diff).sum(1) / x.shape[1]
+        rstd = dt.rsqrt(var + eps)
+        out[tile_m, :] = diff * rstd[:, None] * w[:] + b[:]
+
+
+def test_deuteron_softmax_non_pow2_columns(tmp_path, monkeypatch):
+    # tests/test_deuteron.py:64-71 of the reference: 1000 x 777
+    monkeypatch.setenv("DEUTERON_CACHE_DIR", str(tmp_path))
+    x = _rand((1000, 777), 31)
+    out = torch.empty(1000, 777, device="cuda")
+    dt_softmax(x.cuda(), out)
+    torch.testing.assert_close(out.cpu(), torch_ref.softmax(x), rtol=1e-5, atol=1e-9)
+
+
+def test_deuteron_layernorm(tmp_path, monkeypatch):
+    # examples/deuteron/03_layernorm.py: 4096 x 1500 fp32, err < 1e-3
+    monkeypatch.setenv("DEUTERON_CACHE_DIR", str(tmp_path))
+    x, w, b = _rand((512, 1500), 32), _rand(1500, 33), _rand(1500, 34)
+    out = torch.empty(512, 1500, device="cuda")
+    dt_layernorm(x.cuda(), w.cuda(), b.cuda(), out, 1e-5)
+    assert (out.cpu() - torch_ref.layernorm(x, w, b)).abs().max().item() < 1e-3

@@ -211,6 +211,48 @@ def test_deuteron_source_and_plan():
     assert plan._extents(grid, args) == (300, 200, 104)
 
 
+@dt.kernel
+def dt_softmax(x, out):
+    for tile_m in dt.tile(x.shape[0]):
+        row = x[tile_m, :]
+        m = row.amax(1)
+        e = dt.exp(row - m[:, None])
+        s = e.sum(1)
+        out[tile_m, :] = e / s[:, None]
+
+
+@dt.kernel
+def dt_layernorm(x, w, b, out, eps):
+    for tile_m in dt.tile(x.shape[0]):
+        row = x[tile_m, :]
+        mean = row.sum(1) / x.shape[1]
+        diff = row - mean[:, None]
+        var = (diff * diff).sum(1) / x.shape[1]
+        rstd = dt.rsqrt(var + eps)
+        out[tile_m, :] = diff * rstd[:, None] * w[:] + b[:]
+
+
+def _plan_of(kernel, args, cfg, ptr):
+    ks = kernel._source_for(args)
+    grid, pos, kw = kernel._call_parts(ks, args, cfg)
+    plan = kernel._jit.specialize(*[ptr if torch.is_tensor(a) else a for a in pos], **kw).plan
+    return plan, grid, dict(zip(kernel._jit.param_names, pos))
+
+
+def test_deuteron_row_programs_lower_to_row_kernels():
+    # examples/deuteron/02_softmax.py and 03_layernorm.py: [BLOCK_M, whole row] tiles
+    x, out = torch.randn(1000, 777), torch.empty(1000, 777)
+    plan, grid, a = _plan_of(dt_softmax, (x, out), dt.Config(BLOCK_TILE_M=4), F32)
+    assert isinstance(plan, lower.SoftmaxPlan) and grid == (250,)
+    assert (plan.n(a), plan.rows_per_program, plan.row_bound(a), plan.sx(a)) == (777, 4, 1000, 777)
+    w, b = torch.randn(777), torch.randn(777)
+    plan, grid, a = _plan_of(dt_layernorm, (x, w, b, out, 1e-5), dt.Config(BLOCK_TILE_M=2), F32)
+    assert isinstance(plan, lower.LayerNormPlan) and plan.eps == "eps"
+    assert (plan.x, plan.w, plan.b, plan.out) == ("x_ptr", "w_ptr", "b_ptr", "out_ptr")
+    assert plan.n(a) == 777 and plan.rows_per_program == 2 and plan.hardware_key() == \
+        ("nb200_layernorm",)
+
+
 def test_deuteron_eager_reference_runs_on_host_tensors():
     x, y = torch.randn(64, 48).half(), torch.randn(48, 32).half()
     out = torch.empty(64, 32).half()
