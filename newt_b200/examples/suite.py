@@ -1,0 +1,108 @@
+"""Benchmark suite over the sizes the reference publishes (benchmarks/bench.py:170-300 and
+benchmarks/results.md of the reference): vector add, fused softmax, layernorm, fp16 matmul,
+plus causal attention, each next to the torch call on the same tensors.
+
+    python -m newt_b200.examples.suite [--quick] [--kernel add|softmax|layernorm|matmul|attention]
+
+Clock and metric definitions are the reference's: `do_bench` (median, L2 flushed between
+reps); GB/s = bytes read + written / t; TFLOP/s = 2*M*N*K / t.  Prints markdown tables.
+"""
+
+import argparse
+
+import torch
+
+from .. import testing
+from . import kernels as K
+
+
+def _row(name, size, ours_ms, torch_ms, unit_per_ms):
+    ours, ref = unit_per_ms / ours_ms, unit_per_ms / torch_ms
+    return f"| {name} | {size} | {ours:.1f} | {ref:.1f} | {ours / ref:.2f} |"
+
+
+def bench_add(quick):
+    out = ["| kernel | n | newt_b200 GB/s | torch GB/s | ratio |", "|---|---|---|---|---|"]
+    for n in ([1 << 20, 1 << 24] if quick else [1 << 20, 1 << 24, 1 << 26, 1 << 27]):
+        x, y = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+        o = torch.empty_like(x)
+        a = testing.do_bench(lambda: K.add(x, y, o))
+        b = testing.do_bench(lambda: torch.add(x, y, out=o))
+        out.append(_row("add fp32", n, a, b, 3 * n * 4 / 1e6))
+    return out
+
+
+def bench_softmax(quick):
+    out = ["| kernel | M x N | newt_b200 GB/s | torch GB/s | ratio |", "|---|---|---|---|---|"]
+    for n in ([1024, 4096] if quick else [1024, 4096, 8192, 16384]):
+        x = torch.randn(4096, n, device="cuda")
+        o = torch.empty_like(x)
+        a = testing.do_bench(lambda: K.softmax(x, o))
+        b = testing.do_bench(lambda: torch.softmax(x, -1, out=o))
+        out.append(_row("softmax fp32", f"4096x{n}", a, b, 2 * 4096 * n * 4 / 1e6))
+    return out
+
+
+def bench_layernorm(quick):
+    out = ["| kernel | M x N | newt_b200 GB/s | torch GB/s | ratio |", "|---|---|---|---|---|"]
+    cases = [(torch.float32, 4096, n) for n in ([1024, 4096] if quick else [1024, 2048, 4096, 8192])]
+    cases.append((torch.float16, 8192, 4096))
+    for dt, m, n in cases:
+        x = torch.randn(m, n, device="cuda").to(dt)
+        w, b_ = torch.randn(n, device="cuda").to(dt), torch.randn(n, device="cuda").to(dt)
+        o = torch.empty_like(x)
+        a = testing.do_bench(lambda: K.layernorm(x, w, b_, 1e-5, o))
+        b = testing.do_bench(lambda: torch.nn.functional.layer_norm(x, (n,), w, b_, 1e-5))
+        out.append(_row(f"layernorm {str(dt)[6:]}", f"{m}x{n}", a, b, 2 * m * n * x.element_size() / 1e6))
+    return out
+
+
+def bench_matmul(quick):
+    out = ["| kernel | M=N=K | newt_b200 TFLOP/s | torch TFLOP/s | ratio |", "|---|---|---|---|---|"]
+    for dt in (torch.float16, torch.bfloat16):
+        for n in ([1024, 4096] if quick else [1024, 2048, 4096, 8192]):
+            a_ = (torch.randn(n, n, device="cuda") / n ** 0.5).to(dt)
+            b_ = (torch.randn(n, n, device="cuda") / n ** 0.5).to(dt)
+            c = torch.empty(n, n, device="cuda", dtype=dt)
+            a = testing.do_bench(lambda: K.matmul(a_, b_, c))     # first call autotunes
+            b = testing.do_bench(lambda: torch.matmul(a_, b_, out=c))
+            row = _row(f"matmul {str(dt)[6:]}", n, a, b, 2 * n ** 3 / 1e9)
+            out.append(row + f" <!-- {K.matmul_kernel.best_config} -->")
+    return out
+
+
+def bench_attention(quick):
+    out = ["| kernel | B x H x S x D | newt_b200 TFLOP/s | torch SDPA TFLOP/s | ratio |",
+           "|---|---|---|---|---|"]
+    for causal in (True, False):
+        for b, h, s, d in ([(4, 32, 4096, 128)] if quick else [(16, 32, 4096, 128), (4, 32, 8192, 128),
+                                                                (16, 32, 2048, 64)]):
+            q, k, v = (torch.randn(b, h, s, d, device="cuda").half() for _ in range(3))
+            o = torch.empty_like(q)
+            flop = 4 * b * h * s * s * d * (0.5 if causal else 1.0)
+            a = testing.do_bench(lambda: K.attention(q, k, v, causal, o), warmup=3, rep=10)
+            t = testing.do_bench(lambda: torch.nn.functional.scaled_dot_product_attention(
+                q, k, v, is_causal=causal), warmup=3, rep=10)
+            out.append(_row(f"attention fp16 {'causal' if causal else 'full'}", f"{b}x{h}x{s}x{d}",
+                            a, t, flop / 1e9))
+    return out
+
+
+SUITES = {"add": bench_add, "softmax": bench_softmax, "layernorm": bench_layernorm,
+          "matmul": bench_matmul, "attention": bench_attention}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--kernel", choices=sorted(SUITES))
+    args = ap.parse_args()
+    print(f"device: {torch.cuda.get_device_name()}  torch {torch.__version__}\n")
+    for name in ([args.kernel] if args.kernel else list(SUITES)):
+        print(f"### {name}\n")
+        print("\n".join(SUITES[name](args.quick)))
+        print()
+
+
+if __name__ == "__main__":
+    main()
