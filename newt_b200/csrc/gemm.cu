@@ -139,7 +139,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop and waits; one elected lane issues, so the warp's
+    // control flow stays uniform and descriptors live in uniform registers.
+    {
+      const bool elected = elect_one();
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int tile) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, tile));
+      };
       // A: K-major, 8-row groups 1024 B apart.  B: MN-major, 8-row K groups
       // 1024 B apart, 64-column slabs kBSlab apart.
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
@@ -151,12 +157,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        ok = mbar_wait(smem_u32(&acc_empty_bar[buf]), acc_phase ^ 1, ctx, ST_WAIT_ACC_EMPTY, tile);
+        ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, ST_WAIT_TMA_FULL, tile);
+          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
@@ -165,16 +171,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int kk = 0; kk < kBlockK / 16; ++kk) {
             // +32 B along K inside A's swizzle row; +16 K-rows (2048 B) inside B's slab
-            mma_f16_ss(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
-                       p.idesc, (kb | kk) != 0 ? 1u : 0u);
+            if (elected)
+              mma_f16_ss(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
+                         p.idesc, (kb | kk) != 0 ? 1u : 0u);
           }
-          mma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these MMAs retire
+          if (elected) mma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these retire
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) mma_commit(smem_u32(&acc_full_bar[buf]));
+        if (ok && elected) mma_commit(smem_u32(&acc_full_bar[buf]));
+        __syncwarp();
       }
     }
   } else {
@@ -351,8 +360,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer (leader CTA only) ----------------
-    if (lane == 0 && leader) {
+    // ---------------- MMA issuer (leader CTA only; whole warp, elected lane issues) --------
+    if (leader) {
+      const bool elected = elect_one();
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int tile) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, tile));
+      };
+      // the barriers the commits signal, in each CTA's window of the cluster address space
+      // (barrier i of an array is 8 bytes after barrier i-1 there as well)
+      const uint32_t empty0 = map_to_cta(smem_u32(&empty_bar[0]), 0);
+      const uint32_t empty1 = map_to_cta(smem_u32(&empty_bar[0]), 1);
+      const uint32_t acc_full0 = map_to_cta(smem_u32(&acc_full_bar[0]), 0);
+      const uint32_t acc_full1 = map_to_cta(smem_u32(&acc_full_bar[0]), 1);
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
       constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
       int stage = 0;
@@ -362,12 +381,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        ok = mbar_wait(smem_u32(&acc_empty_bar[buf]), acc_phase ^ 1, ctx, ST_WAIT_ACC_EMPTY, tile);
+        ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < k_rounds; ++kb) {
-          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, ST_WAIT_TMA_FULL, tile);
+          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
@@ -377,21 +396,26 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t b_desc = with_address(kBDesc, a_addr + kABytes);
 #pragma unroll
             for (int kk = 0; kk < kBlockK / 16; ++kk)
-              mma_f16_ss_pair(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
-                              p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
+              if (elected)
+                mma_f16_ss_pair(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
+                                p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
           }
           // the slot is free in both CTAs once these MMAs retire
-          mma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
-          mma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (elected) {
+            mma_commit_pair(empty0 + stage * 8);
+            mma_commit_pair(empty1 + stage * 8);
+          }
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) {
-          mma_commit_pair(map_to_cta(smem_u32(&acc_full_bar[buf]), 0));
-          mma_commit_pair(map_to_cta(smem_u32(&acc_full_bar[buf]), 1));
+        if (ok && elected) {
+          mma_commit_pair(acc_full0 + buf * 8);
+          mma_commit_pair(acc_full1 + buf * 8);
         }
+        __syncwarp();
       }
     }
   } else {
