@@ -12,15 +12,16 @@
 //   warp 1      issues S_j = Q K_j^T (operands in shared memory, S in tensor memory)
 //   warp 2      issues O += P_j V_j (P read from tensor memory, V from shared memory as an
 //               MN-major operand, so no transpose of V is ever made)
-//   warps 3..   softmax: a thread owns half of a row of the tile -- a TMEM lane -- so row
-//               max and row sum are register loops plus one exchange through shared
-//               memory per block.  P_j is written back over S_j as packed 16-bit pairs.
+//   warps 3..6  softmax: thread t owns row t of the tile -- a TMEM lane -- so row max and
+//               row sum are plain register loops, no shuffles.  P_j is written back over
+//               S_j as packed 16-bit pairs.
 // S is triple-buffered: S_{j+1} and S_{j+2} are computed while the softmax warps work on
 // S_j, and each MMA warp's instruction stream (waits, eight MMAs, one commit per block)
 // is shorter than the tensor core's time for the block.  Every commit serves two waiters:
 // "S_j complete" also frees K slot j, "PV_j retired" also frees V slot j and S/P buffer j.
-// The output accumulator is only rescaled when the running maximum moves by more than
-// 2^8 (the rescale is exact in effect: the final division by l_i undoes whatever
+// The exponentials of a block use the reference maximum known before the block; the block's
+// own maximum is taken in the same loop and moves the reference afterwards, and only when it
+// is more than 2^8 above it (exact in effect: the final division by l_i undoes whatever
 // reference point the exponentials used).
 // Scores are kept in the log2 domain: p = 2^(s * scale * log2(e) - m).
 //
@@ -39,10 +40,10 @@ using namespace sm100;
 constexpr int kTileM = 128;   // Q rows per CTA = TMEM lanes
 constexpr int kTileN = 128;   // KV rows per block
 constexpr int kRing = 3;      // depth of the K ring, the V ring and the S/P buffers
-constexpr int kSplit = 2;     // softmax threads per query row
-constexpr int kWarpTma = 0, kWarpQK = 1, kWarpPV = 2, kWarpSoftmax = 3;   // then 4 * kSplit softmax warps
-constexpr int kThreads = 32 * (kWarpSoftmax + 4 * kSplit);
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kWarpTma = 0, kWarpQK = 1, kWarpPV = 2;   // warps 3..6: softmax, one row per thread
+constexpr int kThreads = 224;
+constexpr float kRescaleThreshold = 8.0f;    // log2 units: move the reference before the next block
+constexpr float kOverflowThreshold = 14.0f;  // log2 units: redo the block (2^14 still fits 16 bits)
 
 struct AttnParams {
   void* o;
@@ -68,7 +69,6 @@ struct AttnShared {
   uint64_t s_full[kRing], p_full[kRing], pv_done[kRing];
   uint32_t tmem_slot;
   uint32_t abort_flag;
-  int row_max[3][kTileM];   // block row maxima as ordered integers, combined with atomicMax
 };
 
 template <int D, bool BF16>
@@ -98,8 +98,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* p_full = sh.p_full;
   uint64_t* pv_done = sh.pv_done;
   volatile uint32_t& abort_flag = sh.abort_flag;
-  // the threads of a row add up their partial sums through the (by then idle) K ring
-  float (*row_sum)[kTileM] = reinterpret_cast<float (*)[kTileM]>(smem_raw + kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t q_smem = smem_u32(smem_raw);
@@ -120,7 +118,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (p.causal) kv_end = min(kv_end, q0 + kTileM);
   const int n_blocks = (kv_end + kTileN - 1) / kTileN;
 
-  for (int i = threadIdx.x; i < 3 * kTileM; i += kThreads) (&sh.row_max[0][0])[i] = INT_MIN;
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(smem_u32(&q_full), 1);
@@ -129,7 +126,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(smem_u32(&k_full[x]), 1);
       mbar_init(smem_u32(&v_full[x]), 1);
       mbar_init(smem_u32(&s_full[x]), 1);
-      mbar_init(smem_u32(&p_full[x]), 4 * kSplit);   // one arrival per softmax warp
+      mbar_init(smem_u32(&p_full[x]), 4);   // one arrival per softmax warp
       mbar_init(smem_u32(&pv_done[x]), 1);
     }
     mbar_init_fence();
@@ -235,123 +232,134 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
     }
   } else {
-    // ---------------- softmax + epilogue: kSplit threads per row ----------------
-    // Warps w, w + 4, ... own the same 32 rows (a warp may only touch the TMEM lanes
-    // 32 * (w % 4) ...) and 128 / kSplit of the columns each, so every scheduler of the SM
-    // has kSplit softmax warps.  The threads of a row combine their partial row maximum
-    // through shared memory once per block and so keep identical running maxima; row sums
-    // stay partial until the end.
+    // ---------------- softmax + epilogue: one thread per row ----------------
+    // Thread t of the four warps owns row t of the tile -- a TMEM lane -- so row maximum and
+    // row sum are register loops.  The exponentials of a block use the reference maximum
+    // m_run known before the block; the block's own maximum is taken in the same loop (ALU
+    // work in the shadow of the special-function unit, which is the unit that bounds this
+    // loop) and acts afterwards:
+    //   - if it exceeds m_run by more than 2^14 (always in the first block, where m_run is
+    //     -inf; otherwise rare) the probabilities could overflow 16 bits: the reference moves
+    //     and the block is exponentiated again;
+    //   - if it exceeds m_run by more than 2^8 the reference moves before the next block.
+    // Moving the reference rescales O and l_i by 2^(old - new); the final division by l_i
+    // undoes whatever reference the exponentials used, so laziness costs no accuracy.
     using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-    constexpr int kCols = kTileN / kSplit;    // columns of S per thread
-    constexpr int kOCols = D / kSplit;        // columns of O per thread
-    const int quarter = warp & 3;
-    const int part = (warp - kWarpSoftmax) >> 2;          // which columns of S and of O
-    const int r = quarter * 32 + lane;                    // row of the tile = TMEM lane
-    const int row = q0 + r;
+    const int quarter = warp & 3;   // the TMEM lanes a warp may touch: 32 * (warp % 4)
+    const int row = q0 + quarter * 32 + lane;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const uint32_t row_bar = 1 + quarter;                 // named barrier of the row's warps
     const float c = p.scale_log2;
     float m_run = -INFINITY, l_run = 0.0f;
+    float m_seen = -INFINITY;       // largest scaled score met so far (>= m_run)
     bool ok = true;
-    int synced = 0;                                       // named-barrier rounds completed
-    const int sync_rounds = n_blocks > 0 ? n_blocks + 1 : 0;
 
+    // Moves the reference of the lanes with `move` set to m_seen.  O holds the products up
+    // to block j-1 (nothing for j = 0): wait for that PV to retire, then rescale the row.
+    auto move_reference = [&](bool move, int j) -> bool {
+      float alpha = 1.0f;
+      if (move) {
+        alpha = exp2_approx(m_run - m_seen);   // 0 when m_run is -inf
+        m_run = m_seen;
+        l_run *= alpha;
+      }
+      if (j == 0) return true;
+      const int pb = slot_of(j - 1);
+      bool good = mbar_wait(smem_u32(&pv_done[pb]), par_of(j - 1), ctx, ST_ATTN_PV_DONE, j);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int q = 0; q < D / 32; ++q) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_base + lane_base + kOCol + q * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st_32x32(tmem_base + lane_base + kOCol + q * 32, o);
+      }
+      return true;
+    };
+
+    bool s_ready = false;   // answer to an early, non-blocking look at the next block's barrier
     for (int j = 0; j < n_blocks && ok; ++j) {
       const int buf = slot_of(j);
-      ok = mbar_wait(smem_u32(&s_full[buf]), par_of(j), ctx, ST_ATTN_S_FULL, j);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, s_ready)) {
+        ok = mbar_wait(smem_u32(&s_full[buf]), par_of(j), ctx, ST_ATTN_S_FULL, j);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
       tc_fence_after_sync();
       const uint32_t s_tmem = tmem_base + lane_base + buf * kTileN;
-      uint32_t s[kCols];
-      tmem_ld_cols(s_tmem + part * kCols, s);
+      uint32_t s[4][32];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tmem_ld_32x32(s_tmem + q * 32, s[q]);
       tmem_ld_wait();
 
-      const int kv0 = j * kTileN + part * kCols;   // first column this thread sees
-      const bool edge = (p.causal && j * kTileN + kTileN - 1 > q0) || (j * kTileN + kTileN > p.seq_kv);
+      const int kv0 = j * kTileN;
+      const bool edge = (p.causal && kv0 + kTileN - 1 > q0) || (kv0 + kTileN > p.seq_kv);
       if (edge) {
         const int limit = p.causal ? min(row, p.seq_kv - 1) : p.seq_kv - 1;  // last visible column
 #pragma unroll
-        for (int i = 0; i < kCols; ++i)
-          if (kv0 + i > limit) s[i] = __float_as_uint(-INFINITY);
-      }
-      // four independent chains of three-input maxima
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        for (int q = 0; q < 4; ++q)
 #pragma unroll
-      for (int i = 0; i < kCols; i += 2)
-        mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // Combine with the other threads of the row: floats compare like the signed integers
-      // `bits ^ ((bits >> 31) & 0x7fffffff)`.  Three slots in rotation; the slot of block j+2
-      // is reset after this block's barrier, i.e. after its last readers (block j-1) and
-      // before the barrier that precedes its next writers.
-      {
-        const int bits = __float_as_int(mx);
-        atomicMax(&sh.row_max[j % 3][r], bits ^ ((bits >> 31) & 0x7fffffff));
-        named_barrier_sync(row_bar, 32 * kSplit);
-        ++synced;
-        const int key = sh.row_max[j % 3][r];
-        mx = __int_as_float(key ^ ((key >> 31) & 0x7fffffff));
-        if (part == 0) sh.row_max[(j + 2) % 3][r] = INT_MIN;
+          for (int i = 0; i < 32; ++i)
+            if (kv0 + q * 32 + i > limit) s[q][i] = __float_as_uint(-INFINITY);
       }
-      if (abort_flag) {
-        ok = false;
-        break;
-      }
-      const float m_new = fmaxf(m_run, mx * c);
-      // rows past seq_q (and nothing else) can be fully masked; keep them finite
-      const bool need = (m_new - m_run > kRescaleThreshold) && (m_new > -INFINITY);
-      if (j == 0) {
-        if (need) m_run = m_new;
-      } else if (__any_sync(0xffffffffu, need)) {
-        float alpha = 1.0f;
-        if (need) {
-          alpha = exp2_approx(m_run - m_new);
-          m_run = m_new;
-          l_run *= alpha;
-        }
-        // O holds the products up to block j-1: wait for that PV to retire, then rescale
-        // this thread's columns of the row
-        const int pb = slot_of(j - 1);
-        ok = mbar_wait(smem_u32(&pv_done[pb]), par_of(j - 1), ctx, ST_ATTN_PV_DONE, j);
-        ok = __all_sync(0xffffffffu, ok);
+      // the reference the previous block asked for (comparisons with -inf - -inf are false)
+      if (__any_sync(0xffffffffu, m_seen - m_run > kRescaleThreshold)) {
+        ok = move_reference(m_seen - m_run > kRescaleThreshold, j);
         if (!ok) break;
-        tc_fence_after_sync();
-        uint32_t o[kOCols];
-        const uint32_t o_tmem = tmem_base + lane_base + kOCol + part * kOCols;
-        tmem_ld_cols(o_tmem, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < kOCols; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st_cols(o_tmem, o);
       }
-      const float m_use = m_run > -INFINITY ? m_run : 0.0f;
-      // two scores per fma / add (packed fp32), four partial sums
-      const unsigned long long c2 = pack2(c, c), negm2 = pack2(-m_use, -m_use);
-      unsigned long long sum2[2] = {0ull, 0ull};
-      uint32_t pk[kCols / 2];   // the probabilities as packed 16-bit pairs
+
+      // S runs ahead of the softmax, so the next block is usually complete by now: ask while
+      // the exponentials hide the round trip to the barrier
+      s_ready = j + 1 < n_blocks &&
+                mbar_test_wait(smem_u32(&s_full[slot_of(j + 1)]), par_of(j + 1));
+      float block_sum = 0.0f;
+#pragma unroll 1
+      for (int pass = 0; pass < 2; ++pass) {
+        const float m_use = m_run > -INFINITY ? m_run : 0.0f;
+        // two scores per fma / add (packed fp32), four partial sums, four chains of maxima
+        const unsigned long long c2 = pack2(c, c), negm2 = pack2(-m_use, -m_use);
+        unsigned long long sum2[2] = {0ull, 0ull};
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < kCols / 2; ++i) {
-        const float a = __uint_as_float(s[2 * i]);
-        const float b = __uint_as_float(s[2 * i + 1]);
-        float ta, tb;
-        unpack2(fma2(pack2(a, b), c2, negm2), ta, tb);
-        const float pa = exp2_approx(ta);
-        const float pb2 = exp2_approx(tb);
-        sum2[i & 1] = add2(sum2[i & 1], pack2(pa, pb2));
-        if constexpr (BF16) {
-          __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb2);
-          pk[i] = *reinterpret_cast<uint32_t*>(&v);
-        } else {
-          __half2 v = __floats2half2_rn(pa, pb2);
-          pk[i] = *reinterpret_cast<uint32_t*>(&v);
+        for (int h = 0; h < 2; ++h) {   // 64 scores -> 32 packed columns per store
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float a = __uint_as_float(s[2 * h + i / 16][(2 * i) % 32]);
+            const float b = __uint_as_float(s[2 * h + i / 16][(2 * i) % 32 + 1]);
+            float ta, tb;
+            unpack2(fma2(pack2(a, b), c2, negm2), ta, tb);
+            const float pa = exp2_approx(ta);
+            const float pb2 = exp2_approx(tb);
+            mx4[i & 3] = max3(mx4[i & 3], a, b);
+            sum2[i & 1] = add2(sum2[i & 1], pack2(pa, pb2));
+            if constexpr (BF16) {
+              __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb2);
+              pk[i] = *reinterpret_cast<uint32_t*>(&v);
+            } else {
+              __half2 v = __floats2half2_rn(pa, pb2);
+              pk[i] = *reinterpret_cast<uint32_t*>(&v);
+            }
+          }
+          tmem_st_32x32(s_tmem + h * 32, pk);
         }
+        float s0, s1, s2, s3;
+        unpack2(sum2[0], s0, s1);
+        unpack2(sum2[1], s2, s3);
+        block_sum = (s0 + s1) + (s2 + s3);
+        m_seen = fmaxf(m_seen, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c);
+        // rows past seq_q (and nothing else) can be fully masked: -inf - -inf compares false
+        const bool again = m_seen - m_run > kOverflowThreshold;
+        if (pass == 1 || !__any_sync(0xffffffffu, again)) break;
+        tmem_st_wait();   // the stores of this pass are replaced by the next one's
+        ok = move_reference(again, j);
+        if (!ok) break;
       }
-      tmem_st_cols(s_tmem + part * (kCols / 2), pk);
-      float s0, s1, s2, s3;
-      unpack2(sum2[0], s0, s1);
-      unpack2(sum2[1], s2, s3);
-      l_run += (s0 + s1) + (s2 + s3);
+      if (!ok) break;
+      l_run += block_sum;
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -365,50 +373,44 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok && n_blocks > 0) {
-      // the row sum is the sum of the threads' partial sums
-      row_sum[part][r] = l_run;
-      named_barrier_sync(row_bar, 32 * kSplit);
-      ++synced;
-      l_run = row_sum[0][r];
-#pragma unroll
-      for (int t = 1; t < kSplit; ++t) l_run += row_sum[t][r];
       tc_fence_after_sync();
       const float inv = 1.0f / l_run;
       OutT* orow = static_cast<OutT*>(p.o) + (long long)head * p.o_head_stride +
-                   (long long)row * p.o_row_stride + part * kOCols;
+                   (long long)row * p.o_row_stride;
       const bool vec = ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
-      uint32_t o[kOCols];
-      tmem_ld_cols(tmem_base + lane_base + kOCol + part * kOCols, o);
-      tmem_ld_wait();
-      if (row < p.seq_q) {
 #pragma unroll
-        for (int g = 0; g < kOCols / 8; ++g) {
-          uint32_t packed[4];
+      for (int q = 0; q < D / 32; ++q) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_base + lane_base + kOCol + q * 32, o);
+        tmem_ld_wait();
+        if (row < p.seq_q) {
 #pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const float lo = __uint_as_float(o[g * 8 + 2 * h]) * inv;
-            const float hi = __uint_as_float(o[g * 8 + 2 * h + 1]) * inv;
-            if constexpr (BF16) {
-              __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-              packed[h] = *reinterpret_cast<uint32_t*>(&v);
-            } else {
-              __half2 v = __floats2half2_rn(lo, hi);
-              packed[h] = *reinterpret_cast<uint32_t*>(&v);
+          for (int g = 0; g < 4; ++g) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const float lo = __uint_as_float(o[g * 8 + 2 * h]) * inv;
+              const float hi = __uint_as_float(o[g * 8 + 2 * h + 1]) * inv;
+              if constexpr (BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                packed[h] = *reinterpret_cast<uint32_t*>(&v);
+              } else {
+                __half2 v = __floats2half2_rn(lo, hi);
+                packed[h] = *reinterpret_cast<uint32_t*>(&v);
+              }
             }
-          }
-          OutT* dst = orow + g * 8;
-          if (vec) {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          } else {
-            const OutT* e = reinterpret_cast<const OutT*>(packed);
+            OutT* dst = orow + q * 32 + g * 8;
+            if (vec) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            } else {
+              const OutT* e = reinterpret_cast<const OutT*>(packed);
 #pragma unroll
-            for (int t = 0; t < 8; ++t) dst[t] = e[t];
+              for (int t = 0; t < 8; ++t) dst[t] = e[t];
+            }
           }
         }
       }
     }
-    // a warp that gave up early must not leave the others waiting at the named barrier
-    for (; synced < sync_rounds; ++synced) named_barrier_arrive(row_bar, 32 * kSplit);
   }
 
   tc_fence_before_sync();

@@ -52,6 +52,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking: has the phase with this parity completed?  Issued early, its latency hides
+// behind other work; a false answer only means "ask again with mbar_wait".
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // What a role needs to give up cleanly: the CTA-wide abort flag and the
 // device status word.
 struct WaitCtx {
@@ -82,14 +96,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
                                           unsigned int code, unsigned int detail) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, ctx, code, detail);
-}
-
-// Named barriers 1..15 (0 is __syncthreads): `threads` threads take part, as whole warps.
-__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {
-  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // True in exactly one lane of a converged warp.  Issuing MMAs under this predicate (rather than
@@ -312,15 +318,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, int x,
-                                                 int y, int z, uint32_t cluster_bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3, %4}], [%5];"
-      :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(cluster_bar)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot),
                "r"(cols)
@@ -342,18 +339,6 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc
       "\n\t}"
       :
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-// Same with the A operand in tensor memory: each CTA reads its own 128 lanes at `a_tmem`.
-__device__ __forceinline__ void mma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                                uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;"
-      "\n\t}"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
 // Arrives on one barrier (anywhere in the cluster) once the pair's MMAs issued so far retire.

@@ -280,6 +280,29 @@ def test_attention_vs_oracle(dtype, causal, bh, sq, skv, d):
         assert torch_ref.rel_frobenius(got.float(), torch_ref.attention(q, k, v, scale, causal)) <= 1e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("step", [3.0, 12.0, 40.0])
+def test_attention_rising_and_falling_scores(dtype, step):
+    # The row maximum climbs by `step` (natural-log units) per 128-key block and then falls
+    # again: small steps stay below every threshold, medium ones move the reference between
+    # blocks, large ones force a block to be exponentiated again with a new reference.
+    bh, s, d = 2, 1024, 128
+    g = torch.Generator().manual_seed(int(step))
+    q = torch.randn(bh, s, d, generator=g)
+    k = torch.randn(bh, s, d, generator=g) * 0.05
+    v = torch.randn(bh, s, d, generator=g)
+    q[..., 0] = 1.0
+    block = torch.arange(s) // 128
+    level = torch.minimum(block, 7 - block).float() * step     # 0, 1, 2, 3, 3, 2, 1, 0 steps
+    k[..., 0] = level * d ** 0.5                               # score offset = level after scaling
+    q, k, v = (t.to(dtype) for t in (q, k, v))
+    for causal in (False, True):
+        got = _attention(q.cuda(), k.cuda(), v.cuda(), causal).cpu()
+        want = torch_ref.attention(q, k, v, 1.0 / d ** 0.5, causal)
+        assert torch.isfinite(got.float()).all()
+        assert torch_ref.rel_frobenius(got.float(), want) <= 1e-2
+
+
 def test_attention_strided_heads_and_rows():
     # q, k, v as slices of one packed [bh, s, 3 * d] projection output
     bh, s, d = 4, 384, 128
