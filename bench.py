@@ -419,8 +419,8 @@ def job_throughput(units_per_rank_step, world, steps, total_ms, unit):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/.  softmax and layernorm were captured at full size; matmul and
 # attention on the --small case and scaled by operand bytes (x2.4) resp. head count (x8).
-NCU_TRAFFIC_BYTES = {"softmax": 82.3e6, "layernorm": 83.1e6, "matmul": 2.4 * 209.7e6,
-                     "attention": 255.2e6 / 64}   # attention: per (batch, head) pair
+NCU_TRAFFIC_BYTES = {"softmax": 82.3e6, "layernorm": 83.1e6, "matmul": 2.4 * 212.9e6,
+                     "attention": 252.1e6 / 64}   # attention: per (batch, head) pair
 
 
 def _dist_env():
@@ -590,7 +590,7 @@ def main():
     ap.add_argument("--tile", default="256,256,128,3",
                     help="BLOCK_M,BLOCK_N,BLOCK_K,num_stages used with --no-autotune (matmul)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=INT",
-                    help="library tuning knob (nb200_set_tuning), e.g. attn_variant=2")
+                    help="library tuning knob (nb200_set_tuning), e.g. row_tpr=256")
     args = ap.parse_args()
     for item in args.tune:
         from newt_b200.runtime import abi

@@ -60,9 +60,7 @@ int nb200_read_status(uint32_t* status, uint32_t* detail);
  *   "row_tpr"          threads that cooperate on one row (32,128,256,512,1024)
  *   "row_items"        16-byte vectors each of those threads holds (1,2,4,8)
  *   "row_ctas_per_sm"  resident CTAs per SM of the persistent row grid
- *   "row_rpb"          rows that share one CTA (1, 2 or 4)
- *   "attn_variant"     2 = two 128-row Q tiles per CTA (default: one tile per CTA)
- *   "attn_stages"      K/V ring depth of the one-tile attention kernel (2, 3) */
+ *   "row_rpb"          rows that share one CTA (1, 2 or 4) */
 int nb200_set_tuning(const char* key, int value);
 
 /* ---- K0: out = x + y -------------------------------------------------------
