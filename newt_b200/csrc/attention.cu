@@ -40,10 +40,10 @@ using namespace sm100;
 constexpr int kTileM = 128;   // Q rows per CTA = TMEM lanes
 constexpr int kTileN = 128;   // KV rows per block
 constexpr int kRing = 3;      // depth of the K ring, the V ring and the S/P buffers
-constexpr int kWarpTma = 0, kWarpQK = 1, kWarpPV = 2;   // warps 3..6: softmax, one row per thread
-constexpr int kThreads = 224;
-constexpr float kRescaleThreshold = 8.0f;    // log2 units: move the reference before the next block
-constexpr float kOverflowThreshold = 14.0f;  // log2 units: redo the block (2^14 still fits 16 bits)
+constexpr int kWarpTma = 0, kWarpQK = 1, kWarpPV = 2, kWarpSoftmax = 3;   // 3..10: two softmax groups
+constexpr int kThreads = 32 * (kWarpSoftmax + 8);
+constexpr int kMaxSlots = 3;  // block maxima in flight between the two softmax groups
+constexpr float kRescaleThreshold = 8.0f;    // log2 units: how far a row maximum may run ahead of the reference
 
 struct AttnParams {
   void* o;
@@ -57,18 +57,28 @@ struct AttnParams {
 
 enum : unsigned int {
   ST_ATTN_Q = 16, ST_ATTN_K_FULL, ST_ATTN_K_EMPTY, ST_ATTN_V_FULL, ST_ATTN_V_EMPTY,
-  ST_ATTN_S_FULL, ST_ATTN_P_FULL, ST_ATTN_PV_DONE, ST_ATTN_LAYOUT
+  ST_ATTN_S_FULL, ST_ATTN_P_FULL, ST_ATTN_PV_DONE, ST_ATTN_LAYOUT, ST_ATTN_MAX_DONE, ST_ATTN_O_FREE,
+  ST_ATTN_SUM
 };
 
-// What a CTA keeps in shared memory besides the tiles.
+// What a CTA keeps in shared memory besides the tiles.  Blocks are counted over the whole
+// life of the CTA (g = 0, 1, ... across its tiles); block g uses slot g % 3 of the K ring, the
+// V ring and the S/P buffers, and slot g % 3 of the block maxima.
 //   s_full[x]:  S of the block in slot x is complete (softmax may read it, K slot x is free)
-//   p_full[x]:  P of that block is in tensor memory (one arrival per softmax warp)
+//   p_full[x]:  P of that block is in tensor memory (one arrival per warp of its softmax group)
 //   pv_done[x]: its PV product has retired (V slot x and S/P buffer x are free, O is current)
+//   q_free:     every S product of the tile has retired (the Q tile may be overwritten)
+//   o_free:     the epilogue has read O (the next tile's first PV product may overwrite it)
 struct AttnShared {
-  uint64_t q_full, k_full[kRing], v_full[kRing];
+  uint64_t q_full, q_free, o_free, sum_done, sum_read;
+  uint64_t k_full[kRing], v_full[kRing];
   uint64_t s_full[kRing], p_full[kRing], pv_done[kRing];
+  uint64_t max_done[kMaxSlots];          // block_max[x] is published (one arrival per warp of a group)
   uint32_t tmem_slot;
   uint32_t abort_flag;
+  float block_max[kMaxSlots][kTileM];    // scaled row maxima of the blocks in flight
+  float2 row_part[kTileM];               // (partial row sum, its reference) of the group that
+                                         // does not close the tile
 };
 
 template <int D, bool BF16>
@@ -82,16 +92,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   // tensor memory: three S/P buffers of 128 columns and the output accumulator = 512 columns
   constexpr uint32_t kOCol = kRing * kTileN;
   constexpr uint32_t kTmemCols = 512;
-  // block j uses slot j % 3 (of the K ring, the V ring and the S/P buffers) for the (j / 3)-th time
-  auto slot_of = [](int j) { return j % kRing; };
-  auto par_of = [](int j) { return uint32_t((j / kRing) & 1); };
+  auto slot_of = [](int g) { return g % kRing; };
+  auto par_of = [](int g) { return uint32_t((g / kRing) & 1); };
 
   // Everything in shared memory is carved from the dynamic allocation (no static part, so
   // the 128-byte-swizzled tiles start on the 1024-byte boundary the allocation starts on):
-  // Q tile, K ring, V ring, then the barriers and the exchange buffer.
+  // Q tile, K ring, V ring, then the barriers and the exchange buffers.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   AttnShared& sh = *reinterpret_cast<AttnShared*>(smem_raw + (1 + 2 * kRing) * kTileBytes);
-  uint64_t& q_full = sh.q_full;
   uint64_t* k_full = sh.k_full;
   uint64_t* v_full = sh.v_full;
   uint64_t* s_full = sh.s_full;
@@ -110,25 +118,43 @@ __global__ void __launch_bounds__(kThreads, 1)
     return;
   }
 
-  // heaviest causal tiles of a head first; tiles of one head are adjacent so its K/V stay in L2
-  const int head = blockIdx.x / p.n_q_tiles;
-  const int q_tile = p.n_q_tiles - 1 - (blockIdx.x % p.n_q_tiles);
-  const int q0 = q_tile * kTileM;
-  int kv_end = p.seq_kv;
-  if (p.causal) kv_end = min(kv_end, q0 + kTileM);
-  const int n_blocks = (kv_end + kTileN - 1) / kTileN;
+  // The grid is persistent: CTA b takes the tiles b, b + gridDim.x, ... of a list that runs
+  // head by head (so the K/V of the few heads in flight stay in L2) and, inside a head, from
+  // the last Q tile to the first (causal tiles get shorter).  gridDim.x is odd, so a CTA
+  // meets every tile length equally often.  Going from one tile to the next costs no
+  // start-up: the next Q and K blocks are loaded and the next S products issued while the
+  // softmax groups finish the current tile.
+  const int num_tiles = p.bh * p.n_q_tiles;
+  struct Tile {
+    int head, q0, n_blocks;
+  };
+  auto tile_at = [&](int t) {
+    Tile tile;
+    tile.head = t / p.n_q_tiles;
+    tile.q0 = (p.n_q_tiles - 1 - t % p.n_q_tiles) * kTileM;
+    int kv_end = p.seq_kv;
+    if (p.causal) kv_end = min(kv_end, tile.q0 + kTileM);
+    tile.n_blocks = (kv_end + kTileN - 1) / kTileN;
+    return tile;
+  };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    mbar_init(smem_u32(&q_full), 1);
+    mbar_init(smem_u32(&sh.q_full), 1);
+    mbar_init(smem_u32(&sh.q_free), 1);
+    mbar_init(smem_u32(&sh.o_free), 4);     // one arrival per warp of the group that closes a tile
+    mbar_init(smem_u32(&sh.sum_done), 4);   // ... of the other group
+    mbar_init(smem_u32(&sh.sum_read), 4);
 #pragma unroll
     for (int x = 0; x < kRing; ++x) {
       mbar_init(smem_u32(&k_full[x]), 1);
       mbar_init(smem_u32(&v_full[x]), 1);
       mbar_init(smem_u32(&s_full[x]), 1);
-      mbar_init(smem_u32(&p_full[x]), 4);   // one arrival per softmax warp
+      mbar_init(smem_u32(&p_full[x]), 4);   // one arrival per warp of the block's softmax group
       mbar_init(smem_u32(&pv_done[x]), 1);
     }
+#pragma unroll
+    for (int x = 0; x < kMaxSlots; ++x) mbar_init(smem_u32(&sh.max_done[x]), 4);
     mbar_init_fence();
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
@@ -144,8 +170,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = sh.tmem_slot;
 
   // a whole warp waits (so that its control flow stays uniform); false = give up
-  auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int j) -> bool {
-    return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, j));
+  auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int g) -> bool {
+    return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, g));
   };
   // Q and K tiles: K-major, rows of 128 B, 8-row groups 1024 B apart, one 16 KB chunk per
   // 64 columns of D.  V tile: MN-major, 64-column slabs kChunkBytes apart.
@@ -155,186 +181,244 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == kWarpTma) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      mbar_arrive_expect_tx(smem_u32(&q_full), kTileBytes);
+      bool ok = true;
+      int g0 = 0;   // blocks of the tiles before this one
+      for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const Tile tile = tile_at(t);
+        // K slot x is free once the S product that read it is complete, V slot x once the PV
+        // product is: the barriers the MMA warps commit to anyway.
+        auto load = [&](const CUtensorMap* map, uint32_t ring, uint64_t* free_bar,
+                        uint64_t* full_bar, unsigned int code, int j) -> bool {
+          const int g = g0 + j, x = slot_of(g);
+          if (!mbar_wait(smem_u32(&free_bar[x]), par_of(g) ^ 1, ctx, code, g)) return false;
+          mbar_arrive_expect_tx(smem_u32(&full_bar[x]), kTileBytes);
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c)
-        tma_load_3d(q_smem + c * kChunkBytes, &tmap_q, c * 64, q0, head, smem_u32(&q_full));
-      // K slot x is free once the S product that read it is complete, V slot x once the PV
-      // product is: the barriers the MMA warps commit to anyway.  K runs a whole ring ahead
-      // of V because S = Q K^T is issued blocks before the PV product of the same block.
-      auto load = [&](const CUtensorMap* map, uint32_t ring, uint64_t* free_bar, uint64_t* full_bar,
-                      unsigned int code, int j) -> bool {
-        const int x = slot_of(j);
-        if (!mbar_wait(smem_u32(&free_bar[x]), par_of(j) ^ 1, ctx, code, j)) return false;
-        mbar_arrive_expect_tx(smem_u32(&full_bar[x]), kTileBytes);
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_3d(ring + x * kTileBytes + c * kChunkBytes, map, c * 64, j * kTileN, tile.head,
+                        smem_u32(&full_bar[x]));
+          return true;
+        };
+        // the Q tile is free once the previous tile's S products have all retired
+        ok = mbar_wait(smem_u32(&sh.q_free), (it & 1) ^ 1, ctx, ST_ATTN_Q, it);
+        if (!ok) break;
+        mbar_arrive_expect_tx(smem_u32(&sh.q_full), kTileBytes);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c)
-          tma_load_3d(ring + x * kTileBytes + c * kChunkBytes, map, c * 64, j * kTileN, head,
-                      smem_u32(&full_bar[x]));
-        return true;
-      };
-      bool ok = true;
-      for (int j = 0; j < kRing && j < n_blocks && ok; ++j)
-        ok = load(&tmap_k, k_smem, s_full, k_full, ST_ATTN_K_EMPTY, j);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        ok = load(&tmap_v, v_smem, pv_done, v_full, ST_ATTN_V_EMPTY, j);
-        if (ok && j + kRing < n_blocks)
-          ok = load(&tmap_k, k_smem, s_full, k_full, ST_ATTN_K_EMPTY, j + kRing);
+          tma_load_3d(q_smem + c * kChunkBytes, &tmap_q, c * 64, tile.q0, tile.head,
+                      smem_u32(&sh.q_full));
+        // K runs a whole ring ahead of V because S = Q K^T is issued blocks before the PV
+        // product of the same block
+        for (int j = 0; j < kRing && j < tile.n_blocks && ok; ++j)
+          ok = load(&tmap_k, k_smem, s_full, k_full, ST_ATTN_K_EMPTY, j);
+        for (int j = 0; j < tile.n_blocks && ok; ++j) {
+          ok = load(&tmap_v, v_smem, pv_done, v_full, ST_ATTN_V_EMPTY, j);
+          if (ok && j + kRing < tile.n_blocks)
+            ok = load(&tmap_k, k_smem, s_full, k_full, ST_ATTN_K_EMPTY, j + kRing);
+        }
+        g0 += tile.n_blocks;
       }
     }
   } else if (warp == kWarpQK) {
-    // ---------------- issuer of S_j = Q K_j^T ----------------
+    // ---------------- issuer of S = Q K^T ----------------
     // The whole warp walks the loop and waits; one elected lane issues, so addresses and
     // descriptors stay in uniform registers.  Two issuing warps (this one and the PV warp)
     // because one thread's instruction stream -- waits, sixteen MMAs and the commits of a
     // block -- took longer than the tensor core needs for the block.
     const bool elected = elect_one();
-    bool ok = wait_all(&q_full, 0, ST_ATTN_Q, 0);
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      const int x = slot_of(j);
-      // S/P buffer x was read (as P) by the PV product of block j-3
-      ok = wait_all(&pv_done[x], par_of(j) ^ 1, ST_ATTN_PV_DONE, j) &&
-           wait_all(&k_full[x], par_of(j), ST_ATTN_K_FULL, j);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + x * kTileN;
-      const uint32_t kb = k_smem + x * kTileBytes;
+    bool ok = true;
+    int g0 = 0;
+    for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+      const Tile tile = tile_at(t);
+      ok = wait_all(&sh.q_full, it & 1, ST_ATTN_Q, it);
+      for (int j = 0; j < tile.n_blocks && ok; ++j) {
+        const int g = g0 + j, x = slot_of(g);
+        // S/P buffer x was read (as P) by the PV product of block g-3
+        ok = wait_all(&pv_done[x], par_of(g) ^ 1, ST_ATTN_PV_DONE, g) &&
+             wait_all(&k_full[x], par_of(g), ST_ATTN_K_FULL, g);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + x * kTileN;
+        const uint32_t kb = k_smem + x * kTileBytes;
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-        const uint64_t qd = with_address(kKMajor, q_smem + off);
-        const uint64_t kd = with_address(kKMajor, kb + off);
-        if (elected) mma_f16_ss(d_tmem, qd, kd, p.idesc_qk, kk != 0 ? 1u : 0u);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          const uint64_t qd = with_address(kKMajor, q_smem + off);
+          const uint64_t kd = with_address(kKMajor, kb + off);
+          if (elected) mma_f16_ss(d_tmem, qd, kd, p.idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        if (elected) {
+          mma_commit(smem_u32(&s_full[x]));
+          if (j == tile.n_blocks - 1) mma_commit(smem_u32(&sh.q_free));
+        }
+        __syncwarp();
       }
-      if (elected) mma_commit(smem_u32(&s_full[x]));
-      __syncwarp();
+      g0 += tile.n_blocks;
     }
   } else if (warp == kWarpPV) {
-    // ---------------- issuer of O += P_j V_j ----------------
+    // ---------------- issuer of O += P V ----------------
     const bool elected = elect_one();
     bool ok = true;
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      const int x = slot_of(j);
-      ok = wait_all(&v_full[x], par_of(j), ST_ATTN_V_FULL, j) &&
-           wait_all(&p_full[x], par_of(j), ST_ATTN_P_FULL, j);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t p_tmem = tmem_base + x * kTileN;
-      const uint32_t vb = v_smem + x * kTileBytes;
+    int g0 = 0;
+    for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+      const Tile tile = tile_at(t);
+      // the first product of a tile overwrites O: the previous tile's epilogue must have read it
+      ok = wait_all(&sh.o_free, (it & 1) ^ 1, ST_ATTN_O_FREE, it);
+      for (int j = 0; j < tile.n_blocks && ok; ++j) {
+        const int g = g0 + j, x = slot_of(g);
+        ok = wait_all(&v_full[x], par_of(g), ST_ATTN_V_FULL, g) &&
+             wait_all(&p_full[x], par_of(g), ST_ATTN_P_FULL, g);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t p_tmem = tmem_base + x * kTileN;
+        const uint32_t vb = v_smem + x * kTileBytes;
 #pragma unroll
-      for (int kk = 0; kk < kTileN / 16; ++kk) {
-        // 16 K-elements of P = 8 packed columns; 16 KV rows of V = 2048 B
-        const uint64_t vd = with_address(kVDesc, vb + kk * 2048);
-        if (elected)
-          mma_f16_ts(tmem_base + kOCol, p_tmem + kk * 8, vd, p.idesc_pv, (j | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < kTileN / 16; ++kk) {
+          // 16 K-elements of P = 8 packed columns; 16 KV rows of V = 2048 B
+          const uint64_t vd = with_address(kVDesc, vb + kk * 2048);
+          if (elected)
+            mma_f16_ts(tmem_base + kOCol, p_tmem + kk * 8, vd, p.idesc_pv, (j | kk) != 0 ? 1u : 0u);
+        }
+        if (elected) mma_commit(smem_u32(&pv_done[x]));
+        __syncwarp();
       }
-      if (elected) mma_commit(smem_u32(&pv_done[x]));
-      __syncwarp();
+      g0 += tile.n_blocks;
     }
   } else {
-    // ---------------- softmax + epilogue: one thread per row ----------------
-    // Thread t of the four warps owns row t of the tile -- a TMEM lane -- so row maximum and
-    // row sum are register loops.  The exponentials of a block use the reference maximum
-    // m_run known before the block; the block's own maximum is taken in the same loop (ALU
-    // work in the shadow of the special-function unit, which is the unit that bounds this
-    // loop) and acts afterwards:
-    //   - if it exceeds m_run by more than 2^14 (always in the first block, where m_run is
-    //     -inf; otherwise rare) the probabilities could overflow 16 bits: the reference moves
-    //     and the block is exponentiated again;
-    //   - if it exceeds m_run by more than 2^8 the reference moves before the next block.
-    // Moving the reference rescales O and l_i by 2^(old - new); the final division by l_i
-    // undoes whatever reference the exponentials used, so laziness costs no accuracy.
+    // ---------------- softmax + epilogue: two groups of four warps, alternating blocks ------
+    // Group g (warps 3+4g .. 6+4g) handles the KV blocks n of a tile with n % 2 == g; in both
+    // groups thread t owns row t of the tile -- a TMEM lane -- so row maximum and row sum are
+    // register loops.  With one group, a scheduler's only softmax warp could not overlap its
+    // own phases (TMEM load + row maximum on the ALU, then 128 exponentials per row on the
+    // special-function unit, which is the unit that bounds this loop); with two, one group's
+    // maxima run under the other's exponentials.
+    //
+    // Both groups must scale P against the same reference maximum R_n, because O is one
+    // accumulator.  R_n follows a rule that every thread of a row can replay from the block
+    // maxima alone:  M_n = max(M_{n-1}, max of block n),  R_n = M_n if M_n - R_{n-1} > 2^8
+    // (or nothing seen yet), else R_{n-1}.  A thread publishes its block maximum in shared
+    // memory; the thread of the other group reads it one block later (the barrier it waits
+    // on is normally complete).  The group whose block changes the reference rescales O after
+    // the previous PV product has retired.  Each group keeps its own partial row sum, in
+    // terms of the last reference it used; the two are combined at the end of the tile.
+    // P never exceeds 2^8, and the final division by l_i undoes whatever reference was used.
     using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     const int quarter = warp & 3;   // the TMEM lanes a warp may touch: 32 * (warp % 4)
-    const int row = q0 + quarter * 32 + lane;
+    const int group = (warp - kWarpSoftmax) >> 2;
+    const int r = quarter * 32 + lane;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const float c = p.scale_log2;
-    float m_run = -INFINITY, l_run = 0.0f;
-    float m_seen = -INFINITY;       // largest scaled score met so far (>= m_run)
     bool ok = true;
+    int g0 = 0;
+    int first = 0;   // the group that takes the even blocks of this tile
+    for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+      const Tile tile = tile_at(t);
+      const int row = tile.q0 + r;
+      // The group of the last block closes the tile (combines the row sums, stores O); the
+      // other one goes straight on to block 0 of the next tile.
+      const int closer = (tile.n_blocks - 1 + first) & 1;
+      float m_all = -INFINITY;    // M: largest scaled score of the blocks replayed so far
+      float ref = -INFINITY;      // R of the last block replayed
+      float l_part = 0.0f;        // this group's part of the row sum ...
+      float l_ref = -INFINITY;    // ... in terms of this reference
+      auto advance = [&](float block_max) {   // the rule above
+        m_all = fmaxf(m_all, block_max);
+        if (m_all - ref > kRescaleThreshold) ref = m_all;   // false while m_all is -inf
+      };
+      auto max_of = [&](int g, unsigned int code) -> bool {   // replays block g (of the other group)
+        bool good = mbar_wait(smem_u32(&sh.max_done[g % kMaxSlots]), (g / kMaxSlots) & 1, ctx, code, g);
+        good = __all_sync(0xffffffffu, good);
+        if (good) advance(sh.block_max[g % kMaxSlots][r]);
+        return good;
+      };
 
-    // Moves the reference of the lanes with `move` set to m_seen.  O holds the products up
-    // to block j-1 (nothing for j = 0): wait for that PV to retire, then rescale the row.
-    auto move_reference = [&](bool move, int j) -> bool {
-      float alpha = 1.0f;
-      if (move) {
-        alpha = exp2_approx(m_run - m_seen);   // 0 when m_run is -inf
-        m_run = m_seen;
-        l_run *= alpha;
-      }
-      if (j == 0) return true;
-      const int pb = slot_of(j - 1);
-      bool good = mbar_wait(smem_u32(&pv_done[pb]), par_of(j - 1), ctx, ST_ATTN_PV_DONE, j);
-      good = __all_sync(0xffffffffu, good);
-      if (!good) return false;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int q = 0; q < D / 32; ++q) {
-        uint32_t o[32];
-        tmem_ld_32x32(tmem_base + lane_base + kOCol + q * 32, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st_32x32(tmem_base + lane_base + kOCol + q * 32, o);
-      }
-      return true;
-    };
-
-    bool s_ready = false;   // answer to an early, non-blocking look at the next block's barrier
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      const int buf = slot_of(j);
-      if (!__all_sync(0xffffffffu, s_ready)) {
-        ok = mbar_wait(smem_u32(&s_full[buf]), par_of(j), ctx, ST_ATTN_S_FULL, j);
+      for (int n = group ^ first; n < tile.n_blocks && ok; n += 2) {
+        const int g = g0 + n, buf = slot_of(g);
+        ok = mbar_wait(smem_u32(&s_full[buf]), par_of(g), ctx, ST_ATTN_S_FULL, g);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-      }
-      tc_fence_after_sync();
-      const uint32_t s_tmem = tmem_base + lane_base + buf * kTileN;
-      uint32_t s[4][32];
+        tc_fence_after_sync();
+        const uint32_t s_tmem = tmem_base + lane_base + buf * kTileN;
+        const int kv0 = n * kTileN;
+        const bool edge = (p.causal && kv0 + kTileN - 1 > tile.q0) || (kv0 + kTileN > p.seq_kv);
+        const int limit = p.causal ? min(row, p.seq_kv - 1) : p.seq_kv - 1;   // last visible column
+        // 64 scores of the row at a time (S stays in tensor memory between the two passes)
+        auto fetch = [&](int h, uint32_t (&s)[2][32]) {
+          tmem_ld_32x32(s_tmem + h * 64, s[0]);
+          tmem_ld_32x32(s_tmem + h * 64 + 32, s[1]);
+          tmem_ld_wait();
+          if (edge) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) tmem_ld_32x32(s_tmem + q * 32, s[q]);
-      tmem_ld_wait();
+            for (int q = 0; q < 2; ++q)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (kv0 + h * 64 + q * 32 + i > limit) s[q][i] = __float_as_uint(-INFINITY);
+          }
+        };
 
-      const int kv0 = j * kTileN;
-      const bool edge = (p.causal && kv0 + kTileN - 1 > q0) || (kv0 + kTileN > p.seq_kv);
-      if (edge) {
-        const int limit = p.causal ? min(row, p.seq_kv - 1) : p.seq_kv - 1;  // last visible column
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (kv0 + q * 32 + i > limit) s[q][i] = __float_as_uint(-INFINITY);
-      }
-      // the reference the previous block asked for (comparisons with -inf - -inf are false)
-      if (__any_sync(0xffffffffu, m_seen - m_run > kRescaleThreshold)) {
-        ok = move_reference(m_seen - m_run > kRescaleThreshold, j);
-        if (!ok) break;
-      }
-
-      // S runs ahead of the softmax, so the next block is usually complete by now: ask while
-      // the exponentials hide the round trip to the barrier
-      s_ready = j + 1 < n_blocks &&
-                mbar_test_wait(smem_u32(&s_full[slot_of(j + 1)]), par_of(j + 1));
-      float block_sum = 0.0f;
-#pragma unroll 1
-      for (int pass = 0; pass < 2; ++pass) {
-        const float m_use = m_run > -INFINITY ? m_run : 0.0f;
-        // two scores per fma / add (packed fp32), four partial sums, four chains of maxima
-        const unsigned long long c2 = pack2(c, c), negm2 = pack2(-m_use, -m_use);
-        unsigned long long sum2[2] = {0ull, 0ull};
+        // ---- pass 1: the block's row maximum, published for the other group ----
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t s[2][32];
+          fetch(h, s);
+#pragma unroll
+          for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(s[q][i]),
+                                       __uint_as_float(s[q][i + 1]));
+        }
+        const float block_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c;
+        sh.block_max[g % kMaxSlots][r] = block_max;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.max_done[g % kMaxSlots]));
+
+        // ---- replay the rule over block n-1 (the other group's) and block n ----
+        if (n > 0) {
+          ok = max_of(g - 1, ST_ATTN_MAX_DONE);
+          if (!ok) break;
+        }
+        const float ref_before = ref;   // R_{n-1}
+        advance(block_max);
+        if (n > 0 && __any_sync(0xffffffffu, ref != ref_before)) {
+          // O holds the products up to block n-1 in terms of R_{n-1}
+          ok = mbar_wait(smem_u32(&pv_done[slot_of(g - 1)]), par_of(g - 1), ctx, ST_ATTN_PV_DONE, g);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const float alpha = ref != ref_before ? exp2_approx(ref_before - ref) : 1.0f;
+#pragma unroll
+          for (int q = 0; q < D / 32; ++q) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_base + lane_base + kOCol + q * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tmem_base + lane_base + kOCol + q * 32, o);
+          }
+        }
+        if (l_ref != ref) {   // two blocks of references may have passed
+          l_part *= l_ref > -INFINITY ? exp2_approx(l_ref - ref) : 0.0f;
+          l_ref = ref;
+        }
+
+        // ---- pass 2: P = 2^(S * scale - R_n), packed over the scores already consumed ----
+        const float m_use = ref > -INFINITY ? ref : 0.0f;   // rows past seq_q see nothing at all
+        const unsigned long long c2 = pack2(c, c), negm2 = pack2(-m_use, -m_use);
+        unsigned long long sum2[2] = {0ull, 0ull};
+#pragma unroll
         for (int h = 0; h < 2; ++h) {   // 64 scores -> 32 packed columns per store
+          uint32_t s[2][32];
+          fetch(h, s);
           uint32_t pk[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float a = __uint_as_float(s[2 * h + i / 16][(2 * i) % 32]);
-            const float b = __uint_as_float(s[2 * h + i / 16][(2 * i) % 32 + 1]);
+            const float a = __uint_as_float(s[i / 16][(2 * i) % 32]);
+            const float b = __uint_as_float(s[i / 16][(2 * i) % 32 + 1]);
             float ta, tb;
             unpack2(fma2(pack2(a, b), c2, negm2), ta, tb);
             const float pa = exp2_approx(ta);
             const float pb2 = exp2_approx(tb);
-            mx4[i & 3] = max3(mx4[i & 3], a, b);
             sum2[i & 1] = add2(sum2[i & 1], pack2(pa, pb2));
             if constexpr (BF16) {
               __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb2);
@@ -344,38 +428,48 @@ __global__ void __launch_bounds__(kThreads, 1)
               pk[i] = *reinterpret_cast<uint32_t*>(&v);
             }
           }
+          // columns [32h, 32h+32) of the buffer: scores 0..63 / 64..127 were read above
           tmem_st_32x32(s_tmem + h * 32, pk);
         }
         float s0, s1, s2, s3;
         unpack2(sum2[0], s0, s1);
         unpack2(sum2[1], s2, s3);
-        block_sum = (s0 + s1) + (s2 + s3);
-        m_seen = fmaxf(m_seen, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c);
-        // rows past seq_q (and nothing else) can be fully masked: -inf - -inf compares false
-        const bool again = m_seen - m_run > kOverflowThreshold;
-        if (pass == 1 || !__any_sync(0xffffffffu, again)) break;
-        tmem_st_wait();   // the stores of this pass are replaced by the next one's
-        ok = move_reference(again, j);
-        if (!ok) break;
+        l_part += (s0 + s1) + (s2 + s3);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));
       }
       if (!ok) break;
-      l_run += block_sum;
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));
-    }
 
-    if (ok && n_blocks > 0) {
-      const int lb = slot_of(n_blocks - 1);
-      ok = mbar_wait(smem_u32(&pv_done[lb]), par_of(n_blocks - 1), ctx, ST_ATTN_PV_DONE,
-                     n_blocks);
+      g0 += tile.n_blocks;
+      first = closer ^ 1;
+      if (group != closer) {
+        // hand the partial sum over (the previous hand-over must have been read)
+        ok = mbar_wait(smem_u32(&sh.sum_read), (it & 1) ^ 1, ctx, ST_ATTN_SUM, it);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        sh.row_part[r] = make_float2(l_part, l_ref);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.sum_done));
+        continue;
+      }
+      // ---- close the tile: O is complete once the last PV product has retired ----
+      const int g_last = g0 - 1;
+      ok = mbar_wait(smem_u32(&pv_done[slot_of(g_last)]), par_of(g_last), ctx, ST_ATTN_PV_DONE, g_last) &&
+           mbar_wait(smem_u32(&sh.sum_done), it & 1, ctx, ST_ATTN_SUM, it);
       ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok && n_blocks > 0) {
+      if (!ok) break;
       tc_fence_after_sync();
-      const float inv = 1.0f / l_run;
-      OutT* orow = static_cast<OutT*>(p.o) + (long long)head * p.o_head_stride +
+      // this group's sum is in terms of the last reference, which is the one O is in;
+      // references only ever rise, so the other group's is not above it
+      const float2 other = sh.row_part[r];
+      const float inv =
+          1.0f / (l_part + (other.y > -INFINITY ? other.x * exp2_approx(other.y - ref) : 0.0f));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh.sum_read));
+
+      OutT* orow = static_cast<OutT*>(p.o) + (long long)tile.head * p.o_head_stride +
                    (long long)row * p.o_row_stride;
       const bool vec = ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
 #pragma unroll
@@ -383,14 +477,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t o[32];
         tmem_ld_32x32(tmem_base + lane_base + kOCol + q * 32, o);
         tmem_ld_wait();
+        if (q == D / 32 - 1) {
+          // O is in registers: the next tile's first PV product may overwrite it
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh.o_free));
+        }
         if (row < p.seq_q) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int gq = 0; gq < 4; ++gq) {
             uint32_t packed[4];
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-              const float lo = __uint_as_float(o[g * 8 + 2 * h]) * inv;
-              const float hi = __uint_as_float(o[g * 8 + 2 * h + 1]) * inv;
+              const float lo = __uint_as_float(o[gq * 8 + 2 * h]) * inv;
+              const float hi = __uint_as_float(o[gq * 8 + 2 * h + 1]) * inv;
               if constexpr (BF16) {
                 __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
                 packed[h] = *reinterpret_cast<uint32_t*>(&v);
@@ -399,13 +499,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 packed[h] = *reinterpret_cast<uint32_t*>(&v);
               }
             }
-            OutT* dst = orow + q * 32 + g * 8;
+            OutT* dst = orow + q * 32 + gq * 8;
             if (vec) {
               *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             } else {
               const OutT* e = reinterpret_cast<const OutT*>(packed);
 #pragma unroll
-              for (int t = 0; t < 8; ++t) dst[t] = e[t];
+              for (int tt = 0; tt < 8; ++tt) dst[tt] = e[tt];
             }
           }
         }
@@ -431,7 +531,11 @@ template <int D>
 int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                 const AttnParams& p, bool bf16, cudaStream_t stream) {
   const int smem = (1 + 2 * kRing) * (D / 64) * 128 * 128 + (int)sizeof(AttnShared);
-  const int grid = p.bh * p.n_q_tiles;
+  // persistent: one CTA per SM, an odd number of them (see the kernel), never more than tiles
+  int grid = device_info().sm_count;
+  if (grid % 2 == 0) --grid;
+  const long long tiles = (long long)p.bh * p.n_q_tiles;
+  if (tiles < grid) grid = (int)tiles;
   auto go = [&](auto kern) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_check(e, "attention smem attribute");

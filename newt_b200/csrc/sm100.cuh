@@ -98,6 +98,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   return mbar_wait_slow(bar, parity, ctx, code, detail);
 }
 
+// Named barriers 1..15 (0 is __syncthreads): `threads` threads take part, as whole warps;
+// `arrive` counts toward the barrier without waiting for it.
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // True in exactly one lane of a converged warp.  Issuing MMAs under this predicate (rather than
 // inside a `lane == 0` branch) keeps the warp's control flow uniform, so descriptors and
 // addresses stay in uniform registers.

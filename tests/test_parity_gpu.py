@@ -329,6 +329,23 @@ def test_attention_rows_sum_property_at_config_size():
     o = _attention(q, k, v, True)
     ref = torch_ref.attention(q[:1].cpu(), k[:1].cpu(), v[:1].cpu(), 1 / d ** 0.5, True)
     assert torch_ref.rel_frobenius(o[:1].cpu().float(), ref) <= 1e-2
+    # and the last head: its tiles are the second and third ones a persistent CTA works on
+    ref = torch_ref.attention(q[-1:].cpu(), k[-1:].cpu(), v[-1:].cpu(), 1 / d ** 0.5, True)
+    assert torch_ref.rel_frobenius(o[-1:].cpu().float(), ref) <= 1e-2
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_many_short_tiles(causal):
+    # 600 Q tiles of one to three KV blocks: every CTA walks several tiles, with tiles of one
+    # block (only one softmax group has work) and tile boundaries at every ring position
+    bh, sq, skv, d = 200, 384, 300, 64
+    g = torch.Generator().manual_seed(23)
+    q, k, v = (torch.randn(bh, s, d, generator=g).half() for s in (sq, skv, skv))
+    got = _attention(q.cuda(), k.cuda(), v.cuda(), causal).cpu()
+    want = torch_ref.attention(q, k, v, 1.0 / d ** 0.5, causal)
+    if causal:   # rows past the last key see every key
+        want[:, skv:] = torch_ref.attention(q[:, skv:], k, v, 1.0 / d ** 0.5, False)
+    assert torch_ref.rel_frobenius(got.float(), want) <= 1e-2
 
 
 def test_attention_argument_errors():
