@@ -7,22 +7,23 @@
 // both dots are staged synchronously and the accumulator round-trips through
 // shared memory every iteration (newt/compiler/codegen.py:1824-1852, 719-776).
 //
-// Here one CTA owns a 128-row Q tile of one (batch, head):
-//   warp 0      TMA producer: Q once, then K and V blocks of 128 rows into two rings of three
-//   warp 1      issues S_j = Q K_j^T (operands in shared memory, S in tensor memory)
-//   warp 2      issues O += P_j V_j (P read from tensor memory, V from shared memory as an
-//               MN-major operand, so no transpose of V is ever made)
-//   warps 3..6  softmax: thread t owns row t of the tile -- a TMEM lane -- so row max and
-//               row sum are plain register loops, no shuffles.  P_j is written back over
-//               S_j as packed 16-bit pairs.
-// S is triple-buffered: S_{j+1} and S_{j+2} are computed while the softmax warps work on
-// S_j, and each MMA warp's instruction stream (waits, eight MMAs, one commit per block)
-// is shorter than the tensor core's time for the block.  Every commit serves two waiters:
-// "S_j complete" also frees K slot j, "PV_j retired" also frees V slot j and S/P buffer j.
-// The exponentials of a block use the reference maximum known before the block; the block's
-// own maximum is taken in the same loop and moves the reference afterwards, and only when it
-// is more than 2^8 above it (exact in effect: the final division by l_i undoes whatever
-// reference point the exponentials used).
+// Here a persistent CTA per SM walks 128-row Q tiles of (batch, head) pairs:
+//   warp 0       TMA producer: Q per tile, K and V blocks of 128 rows into two rings of three
+//   warp 1       issues S = Q K^T (operands in shared memory, S in tensor memory)
+//   warp 2       issues O += P V (P read from tensor memory, V from shared memory as an
+//                MN-major operand, so no transpose of V is ever made)
+//   warps 3..10  softmax: two groups of four warps take alternate KV blocks; in both, thread
+//                t owns row t of the tile -- a TMEM lane -- so row max and row sum are plain
+//                register loops, no shuffles.  P is written back over S as packed 16-bit
+//                pairs.  The group of a tile's last block stores O; the other one is by
+//                then on the next tile.
+// S is triple-buffered and runs two blocks ahead of the softmax, and each MMA warp's
+// instruction stream (waits, eight MMAs, one commit per block) is shorter than the tensor
+// core's time for the block.  Every commit serves two waiters: "S complete" also frees the
+// K slot, "PV retired" also frees the V slot and the S/P buffer.
+// The reference maximum that P is scaled against only moves when a block maximum is more than
+// 2^8 above it (exact in effect: the final division by l_i undoes whatever reference point
+// the exponentials used); the softmax section states the rule both groups follow.
 // Scores are kept in the log2 domain: p = 2^(s * scale * log2(e) - m).
 //
 // Causal tiles skip the KV blocks above the diagonal and mask only the diagonal
@@ -324,19 +325,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         m_all = fmaxf(m_all, block_max);
         if (m_all - ref > kRescaleThreshold) ref = m_all;   // false while m_all is -inf
       };
-      auto max_of = [&](int g, unsigned int code) -> bool {   // replays block g (of the other group)
-        bool good = mbar_wait(smem_u32(&sh.max_done[g % kMaxSlots]), (g / kMaxSlots) & 1, ctx, code, g);
-        good = __all_sync(0xffffffffu, good);
-        if (good) advance(sh.block_max[g % kMaxSlots][r]);
-        return good;
-      };
 
+      bool s_ready = false;   // answer to an early, non-blocking look at the next block's barrier
       for (int n = group ^ first; n < tile.n_blocks && ok; n += 2) {
         const int g = g0 + n, buf = slot_of(g);
-        ok = mbar_wait(smem_u32(&s_full[buf]), par_of(g), ctx, ST_ATTN_S_FULL, g);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
+        if (!__all_sync(0xffffffffu, s_ready)) {
+          ok = mbar_wait(smem_u32(&s_full[buf]), par_of(g), ctx, ST_ATTN_S_FULL, g);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
         tc_fence_after_sync();
+        // the other group's maximum of block n-1 is usually published by now: ask while the
+        // first pass hides the round trip to the barrier
+        const bool max_ready =
+            n > 0 && mbar_test_wait(smem_u32(&sh.max_done[(g - 1) % kMaxSlots]), ((g - 1) / kMaxSlots) & 1);
         const uint32_t s_tmem = tmem_base + lane_base + buf * kTileN;
         const int kv0 = n * kTileN;
         const bool edge = (p.causal && kv0 + kTileN - 1 > tile.q0) || (kv0 + kTileN > p.seq_kv);
@@ -357,12 +359,20 @@ __global__ void __launch_bounds__(kThreads, 1)
 
         // ---- pass 1: the block's row maximum, published for the other group ----
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        {
+          uint32_t s[4][32];   // the whole row at once: nothing else is live in this pass
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t s[2][32];
-          fetch(h, s);
+          for (int q = 0; q < 4; ++q) tmem_ld_32x32(s_tmem + q * 32, s[q]);
+          tmem_ld_wait();
+          if (edge) {
 #pragma unroll
-          for (int q = 0; q < 2; ++q)
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (kv0 + q * 32 + i > limit) s[q][i] = __float_as_uint(-INFINITY);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
 #pragma unroll
             for (int i = 0; i < 32; i += 2)
               mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(s[q][i]),
@@ -375,8 +385,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 
         // ---- replay the rule over block n-1 (the other group's) and block n ----
         if (n > 0) {
-          ok = max_of(g - 1, ST_ATTN_MAX_DONE);
-          if (!ok) break;
+          if (!__all_sync(0xffffffffu, max_ready)) {
+            ok = mbar_wait(smem_u32(&sh.max_done[(g - 1) % kMaxSlots]), ((g - 1) / kMaxSlots) & 1, ctx,
+                           ST_ATTN_MAX_DONE, g);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+          }
+          advance(sh.block_max[(g - 1) % kMaxSlots][r]);
         }
         const float ref_before = ref;   // R_{n-1}
         advance(block_max);
@@ -402,6 +417,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           l_ref = ref;
         }
 
+        // S runs ahead of the softmax, so this group's next block is usually complete by now
+        s_ready = n + 2 < tile.n_blocks &&
+                  mbar_test_wait(smem_u32(&s_full[slot_of(g + 2)]), par_of(g + 2));
         // ---- pass 2: P = 2^(S * scale - R_n), packed over the scores already consumed ----
         const float m_use = ref > -INFINITY ? ref : 0.0f;   // rows past seq_q see nothing at all
         const unsigned long long c2 = pack2(c, c), negm2 = pack2(-m_use, -m_use);
