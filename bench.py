@@ -420,7 +420,7 @@ def job_throughput(units_per_rank_step, world, steps, total_ms, unit):
 # summarised under profiles/.  softmax and layernorm were captured at full size; matmul and
 # attention on the --small case and scaled by operand bytes (x2.4) resp. head count (x8).
 NCU_TRAFFIC_BYTES = {"softmax": 82.3e6, "layernorm": 83.1e6, "matmul": 2.4 * 212.9e6,
-                     "attention": 252.1e6 / 64}   # attention: per (batch, head) pair
+                     "attention": 251.4e6 / 64}   # attention: per (batch, head) pair
 
 
 def _dist_env():

@@ -119,20 +119,25 @@ __global__ void __launch_bounds__(kThreads, 1)
     return;
   }
 
-  // The grid is persistent: CTA b takes the tiles b, b + gridDim.x, ... of a list that runs
-  // head by head (so the K/V of the few heads in flight stay in L2) and, inside a head, from
-  // the last Q tile to the first (causal tiles get shorter).  gridDim.x is odd, so a CTA
-  // meets every tile length equally often.  Going from one tile to the next costs no
-  // start-up: the next Q and K blocks are loaded and the next S products issued while the
-  // softmax groups finish the current tile.
+  // The grid is persistent.  The tile list runs head by head (so the K/V of the few heads in
+  // flight stay in L2) and, inside a head, alternates between the ends: last Q tile, first,
+  // last but one, second, ...  CTA b takes the pairs of neighbours b, b + gridDim.x, ... of
+  // that list, so with a causal mask every pair costs the same number of KV blocks and the
+  // CTAs finish together.  Going from one tile to the next costs no start-up: the next Q and
+  // K blocks are loaded and the next S products issued while the softmax groups finish the
+  // current tile.
   const int num_tiles = p.bh * p.n_q_tiles;
+  auto nth_tile = [&](int it) {   // index in the list of the it-th tile of this CTA
+    return 2 * (int(blockIdx.x) + (it >> 1) * int(gridDim.x)) + (it & 1);
+  };
   struct Tile {
     int head, q0, n_blocks;
   };
   auto tile_at = [&](int t) {
     Tile tile;
     tile.head = t / p.n_q_tiles;
-    tile.q0 = (p.n_q_tiles - 1 - t % p.n_q_tiles) * kTileM;
+    const int k = t % p.n_q_tiles;
+    tile.q0 = ((k & 1) ? (k >> 1) : p.n_q_tiles - 1 - (k >> 1)) * kTileM;
     int kv_end = p.seq_kv;
     if (p.causal) kv_end = min(kv_end, tile.q0 + kTileM);
     tile.n_blocks = (kv_end + kTileN - 1) / kTileN;
@@ -184,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       bool ok = true;
       int g0 = 0;   // blocks of the tiles before this one
-      for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int it = 0, t = nth_tile(0); t < num_tiles && ok; ++it, t = nth_tile(it)) {
         const Tile tile = tile_at(t);
         // K slot x is free once the S product that read it is complete, V slot x once the PV
         // product is: the barriers the MMA warps commit to anyway.
@@ -228,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool elected = elect_one();
     bool ok = true;
     int g0 = 0;
-    for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+    for (int it = 0, t = nth_tile(0); t < num_tiles && ok; ++it, t = nth_tile(it)) {
       const Tile tile = tile_at(t);
       ok = wait_all(&sh.q_full, it & 1, ST_ATTN_Q, it);
       for (int j = 0; j < tile.n_blocks && ok; ++j) {
@@ -260,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool elected = elect_one();
     bool ok = true;
     int g0 = 0;
-    for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+    for (int it = 0, t = nth_tile(0); t < num_tiles && ok; ++it, t = nth_tile(it)) {
       const Tile tile = tile_at(t);
       // the first product of a tile overwrites O: the previous tile's epilogue must have read it
       ok = wait_all(&sh.o_free, (it & 1) ^ 1, ST_ATTN_O_FREE, it);
@@ -311,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
     int g0 = 0;
     int first = 0;   // the group that takes the even blocks of this tile
-    for (int t = blockIdx.x, it = 0; t < num_tiles && ok; t += gridDim.x, ++it) {
+    for (int it = 0, t = nth_tile(0); t < num_tiles && ok; ++it, t = nth_tile(it)) {
       const Tile tile = tile_at(t);
       const int row = tile.q0 + r;
       // The group of the last block closes the tile (combines the row sums, stores O); the
@@ -549,11 +554,10 @@ template <int D>
 int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                 const AttnParams& p, bool bf16, cudaStream_t stream) {
   const int smem = (1 + 2 * kRing) * (D / 64) * 128 * 128 + (int)sizeof(AttnShared);
-  // persistent: one CTA per SM, an odd number of them (see the kernel), never more than tiles
+  // persistent: one CTA per SM, never more than there are pairs of tiles
   int grid = device_info().sm_count;
-  if (grid % 2 == 0) --grid;
-  const long long tiles = (long long)p.bh * p.n_q_tiles;
-  if (tiles < grid) grid = (int)tiles;
+  const long long pairs = ((long long)p.bh * p.n_q_tiles + 1) / 2;
+  if (pairs < grid) grid = (int)pairs;
   auto go = [&](auto kern) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_check(e, "attention smem attribute");
