@@ -95,6 +95,10 @@ int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
  * A is [M,K] with row stride lda, B is [K,N] with row stride ldb, C is [M,N]
  * with row stride ldc; innermost strides are 1.  fp16 or bf16 inputs, fp32
  * accumulation in tensor memory, one rounding to `dtype` at the store.
+ * fp32 inputs run as tf32 with an fp32 result, as `nl.dot` does for fp32 blocks
+ * (newt/language.py:165-167, newt/compiler/codegen.py:2195-2197); the tensor core
+ * reads tf32 operands K-major only, so they go through nb200_gemm_bt or
+ * nb200_gemm_tf32 below and nb200_gemm itself rejects NB200_F32.
  *
  * The config mirrors the launch knobs of the operator API: the tile comes
  * from the kernel's BLOCK_M/BLOCK_N/BLOCK_K constexprs, `stages` from
@@ -105,7 +109,7 @@ int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
 typedef struct nb200_gemm_config {
   int32_t block_m; /* 128 (one CTA) or 256 (CTA pair)                        */
   int32_t block_n; /* 64, 128 or 256 (256 only for a CTA pair)               */
-  int32_t block_k; /* 64; a CTA pair also takes 128 (default) and 192        */
+  int32_t block_k; /* 64; a CTA pair also takes 128 (default) and 192 (fp32: 32 / 64 / 96) */
   int32_t stages;  /* 1..8; snapped to a depth that fits 227 KB of shared mem */
   int32_t cta_pair;/* 0 or 1                                                 */
   int32_t reserved[3];
@@ -115,11 +119,30 @@ int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n,
                int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int dtype,
                const nb200_gemm_config* config, void* stream);
 
+/* The same product with B given transposed: `bt` is [N,K] with row stride ldbt, i.e. what
+ * `nl.dot(a, nl.trans(bt_tile))` computes (nl.trans: newt/compiler/codegen.py:1824-1852) or a
+ * matmul_kernel called with stride_bk = 1.  All three dtypes. */
+int nb200_gemm_bt(const void* a, const void* bt, void* c, int64_t m, int64_t n,
+                  int64_t k, int64_t lda, int64_t ldbt, int64_t ldc, int dtype,
+                  const nb200_gemm_config* config, void* stream);
+
+/* fp32 C = A @ B with B as [K,N] (the layout of tests/test_matmul.py:67-70 and of
+ * bench_matmul_tf32, benchmarks/bench.py:291-294): B is first transposed into `workspace`, a
+ * caller-owned device buffer of at least nb200_gemm_tf32_workspace_bytes(n, k) bytes, 16-byte
+ * aligned, which the call may overwrite completely; then the product runs as nb200_gemm_bt.
+ * The transposing pass moves 8 bytes per element of B. */
+int64_t nb200_gemm_tf32_workspace_bytes(int64_t n, int64_t k);
+int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n,
+                    int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                    const nb200_gemm_config* config, void* workspace,
+                    int64_t workspace_bytes, void* stream);
+
 /* Returns 0 when (dtype, shape, strides, pointers, config) can run on the
  * TMA/tcgen05 path, else NB200_E_* with the reason in nb200_last_error().
  * Launches nothing; lets an autotuner discard configurations analytically
  * (the reference discards them by catching launch failures,
- * newt/runtime/autotuner.py:76-81). */
+ * newt/runtime/autotuner.py:76-81).  For NB200_F32 it answers for nb200_gemm_tf32 (B as
+ * [K,N], any pitch). */
 int nb200_gemm_check(const void* a, const void* b, const void* c, int64_t m,
                      int64_t n, int64_t k, int64_t lda, int64_t ldb,
                      int64_t ldc, int dtype, const nb200_gemm_config* config);

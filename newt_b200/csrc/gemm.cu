@@ -1,4 +1,5 @@
-// C = A @ B for 16-bit inputs on the 5th-generation tensor cores (K3 / K4).
+// C = A @ B on the 5th-generation tensor cores (K3 / K4): fp16 / bf16 inputs, and fp32 inputs
+// as tf32 (what `nl.dot` does for fp32 blocks, newt/compiler/codegen.py:2195-2197).
 //
 // This is what `nl.dot` inside a K loop lowers to.  The reference stages
 // operands with cp.async into an XOR-swizzled ring and multiplies with
@@ -11,7 +12,10 @@
 //   * one thread issues tcgen05.mma (M = 128, N = BLOCK_N, K = 16 per
 //     instruction) reading both operands through shared-memory descriptors;
 //     A is [M,K] row-major  -> K-major operand,
-//     B is [K,N] row-major  -> MN-major operand (no transpose pass needed);
+//     B is [K,N] row-major  -> MN-major operand (no transpose pass needed), or is handed
+//     over transposed, [N,K] -> K-major operand.  tf32 operands are read K-major only (an
+//     MN-major B gives zeros), so an fp32 B as [K,N] goes through a transposing pass into a
+//     caller-provided workspace first (nb200_gemm_tf32);
 //   * the fp32 accumulator lives in tensor memory, double-buffered, so the
 //     epilogue of tile i (tcgen05.ld -> round -> store) overlaps the MMAs of
 //     tile i+1;
@@ -38,7 +42,74 @@ namespace {
 using namespace sm100;
 
 constexpr int kBlockM = 128;
-constexpr int kBlockK = 64;     // 64 16-bit elements = one 128-byte swizzle row
+// fp32 operands run as tf32 (kind::tf32 reads the upper 19 bits of each word): everything
+// below is laid out in 128-byte rows, so a row holds 32 K-elements instead of 64, a slab of B
+// 32 columns instead of 64, and one MMA consumes 8 K-elements instead of 16 -- the same 32
+// bytes.  Stage sizes, descriptor strides along K of A and the MMA count do not change.
+template <int DT>
+struct Elem {
+  static constexpr int kBytes = DT == NB200_F32 ? 4 : 2;
+  static constexpr int kPerRow = 128 / kBytes;   // K elements per stage = columns per slab of B
+  using Out = typename std::conditional<DT == NB200_F32, float,
+              typename std::conditional<DT == NB200_BF16, __nv_bfloat16, __half>::type>::type;
+};
+template <int DT>
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
+                                       uint32_t acc) {
+  if constexpr (DT == NB200_F32) mma_tf32_ss(d, a, b, idesc, acc);
+  else mma_f16_ss(d, a, b, idesc, acc);
+}
+template <int DT>
+__device__ __forceinline__ void mma_ss_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
+                                            uint32_t acc) {
+  if constexpr (DT == NB200_F32) mma_tf32_ss_pair(d, a, b, idesc, acc);
+  else mma_f16_ss_pair(d, a, b, idesc, acc);
+}
+// 32 accumulator columns of one row -> global memory, one rounding (none for fp32)
+template <int DT>
+__device__ __forceinline__ void store_chunk(typename Elem<DT>::Out* crow, int col0, int n,
+                                            bool vec_ok, const uint32_t (&r)[32]) {
+  using OutT = typename Elem<DT>::Out;
+  if constexpr (DT == NB200_F32) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {   // 4 columns = 16 bytes per group
+      const int col = col0 + g * 4;
+      if (vec_ok && col + 4 <= n) {
+        *reinterpret_cast<uint4*>(crow + col) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (col + j < n) crow[col + j] = __uint_as_float(r[g * 4 + j]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {   // 8 columns = 16 bytes per group
+      const int col = col0 + g * 8;
+      uint32_t packed[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float lo = __uint_as_float(r[g * 8 + 2 * h]);
+        const float hi = __uint_as_float(r[g * 8 + 2 * h + 1]);
+        if constexpr (DT == NB200_BF16) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+          packed[h] = *reinterpret_cast<uint32_t*>(&v);
+        } else {
+          __half2 v = __floats2half2_rn(lo, hi);
+          packed[h] = *reinterpret_cast<uint32_t*>(&v);
+        }
+      }
+      if (vec_ok && col + 8 <= n) {
+        *reinterpret_cast<uint4*>(crow + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      } else {
+        const OutT* e = reinterpret_cast<const OutT*>(packed);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col + j < n) crow[col + j] = e[j];
+      }
+    }
+  }
+}
 constexpr int kThreads = 192;
 constexpr int kGroupM = 8;      // row-blocks per L2 band of the tile order
 
@@ -49,6 +120,7 @@ struct GemmParams {
   int m_blocks, n_blocks, k_blocks;
   uint32_t idesc;
   int c_vec_ok;  // C base and row pitch are 16-byte aligned
+  int b_kmajor;  // B is given transposed ([N, K], K contiguous); always so for tf32
   unsigned int* status;
 };
 
@@ -64,13 +136,15 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
   *nb = in_band / rows;
 }
 
-template <int BN, int STAGES, bool BF16>
+template <int BN, int STAGES, int DT>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  constexpr uint32_t kABytes = kBlockM * kBlockK * 2;   // 16 KB
-  constexpr uint32_t kBSlab = kBlockK * 64 * 2;         // one 64-column slab of B: 8 KB
-  constexpr uint32_t kBBytes = kBSlab * (BN / 64);
+  constexpr int kBK = Elem<DT>::kPerRow;                // K elements per stage
+  constexpr int kSlab = Elem<DT>::kPerRow;              // columns of B per slab
+  constexpr uint32_t kABytes = kBlockM * 128;           // 16 KB
+  constexpr uint32_t kBSlab = kBK * 128;                // one slab of B: 8 KB (4 KB for tf32)
+  constexpr uint32_t kBBytes = kBSlab * (BN / kSlab);
   constexpr uint32_t kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators, BN fp32 columns each
 
@@ -109,6 +183,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = tmem_slot;
 
   const int num_tiles = p.m_blocks * p.n_blocks;
+  // The tensor core takes tf32 operands K-major only (an MN-major B gives zeros), so fp32
+  // always comes with B transposed; for 16-bit types it is the caller's choice.
+  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -125,11 +202,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t bar = smem_u32(&full_bar[stage]);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           mbar_arrive_expect_tx(bar, kStageBytes);
-          tma_load_2d(a_dst, &tmap_a, kb * kBlockK, mb * kBlockM, bar);
+          tma_load_2d(a_dst, &tmap_a, kb * kBK, mb * kBlockM, bar);
+          if (b_kmajor) {   // BN rows of B^T, one 128-byte row of K each
+            tma_load_2d(a_dst + kABytes, &tmap_b, kb * kBK, nb * BN, bar);
+          } else {
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_2d(a_dst + kABytes + j * kBSlab, &tmap_b, nb * BN + j * 64, kb * kBlockK,
-                        bar);
+            for (int j = 0; j < BN / kSlab; ++j)
+              tma_load_2d(a_dst + kABytes + j * kBSlab, &tmap_b, nb * BN + j * kSlab, kb * kBK, bar);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -150,6 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       // 1024 B apart, 64-column slabs kBSlab apart.
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
       constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
+      const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -167,12 +248,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_fence_after_sync();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
           const uint64_t a_desc = with_address(kADesc, a_addr);
-          const uint64_t b_desc = with_address(kBDesc, a_addr + kABytes);
+          const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / 16; ++kk) {
-            // +32 B along K inside A's swizzle row; +16 K-rows (2048 B) inside B's slab
+          for (int kk = 0; kk < 4; ++kk) {
+            // +32 B along K inside a K-major swizzle row; + a quarter of the stage's K-rows
+            // (128 B each) inside an MN-major slab of B
             if (elected)
-              mma_f16_ss(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
+              mma_ss<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
                          p.idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           if (elected) mma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these retire
@@ -189,7 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    using OutT = typename Elem<DT>::Out;
     OutT* c = static_cast<OutT*>(p.c);
     int it = 0;
     bool ok = true;
@@ -212,34 +294,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
-        if (row < p.m) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {  // 8 columns = 16 bytes per group
-            const int col = col0 + g * 8;
-            uint32_t packed[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const float lo = __uint_as_float(r[g * 8 + 2 * h]);
-              const float hi = __uint_as_float(r[g * 8 + 2 * h + 1]);
-              if constexpr (BF16) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-                packed[h] = *reinterpret_cast<uint32_t*>(&v);
-              } else {
-                __half2 v = __floats2half2_rn(lo, hi);
-                packed[h] = *reinterpret_cast<uint32_t*>(&v);
-              }
-            }
-            if (p.c_vec_ok && col + 8 <= p.n) {
-              *reinterpret_cast<uint4*>(crow + col) =
-                  make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            } else {
-              const OutT* e = reinterpret_cast<const OutT*>(packed);
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (col + j < p.n) crow[col + j] = e[j];
-            }
-          }
-        }
+        if (row < p.m) store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -274,14 +329,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 // epilogue warps of both CTAs, once per tile.
 // KSUB 64-element K slabs share one ring slot (one barrier round trip and one pair of
 // commits per slot).
-template <int STAGES, int KSUB, bool BF16>
+template <int STAGES, int KSUB, int DT>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   constexpr int BN = 256;                                // cluster tile width
-  constexpr uint32_t kABytes = kBlockM * kBlockK * 2;    // this CTA's 128 rows of A: 16 KB
-  constexpr uint32_t kBSlab = kBlockK * 64 * 2;          // 64 columns of B: 8 KB
-  constexpr uint32_t kBBytes = kBSlab * 2;               // this CTA's 128 columns of B
+  constexpr int kBK = Elem<DT>::kPerRow;                 // K elements per 128-byte row
+  constexpr int kSlab = Elem<DT>::kPerRow;               // columns of B per slab
+  constexpr uint32_t kABytes = kBlockM * 128;            // this CTA's 128 rows of A: 16 KB
+  constexpr uint32_t kBSlab = kBK * 128;                 // one slab of B: 8 KB (4 KB for tf32)
+  constexpr uint32_t kBBytes = kBSlab * (128 / kSlab);   // this CTA's 128 columns of B
   constexpr uint32_t kSlabBytes = kABytes + kBBytes;     // 32 KB per 64 elements of K
   constexpr uint32_t kStageBytes = KSUB * kSlabBytes;
   constexpr uint32_t kTmemCols = 2 * BN;
@@ -323,6 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
 
+  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;   // see gemm_kernel
   const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
   const int num_tiles = m_blocks2 * p.n_blocks;
   const int first = cluster_id_x(), step = cluster_count_x();
@@ -347,10 +405,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {   // slabs past K are zero-filled by the tensor map
             const uint32_t a_dst = smem_base + stage * kStageBytes + sub * kSlabBytes;
-            const int k0 = (kb * KSUB + sub) * kBlockK;
+            const int k0 = (kb * KSUB + sub) * kBK;
             tma_load_2d_pair(a_dst, &tmap_a, k0, row0, bar);
-            tma_load_2d_pair(a_dst + kABytes, &tmap_b, col0, k0, bar);
-            tma_load_2d_pair(a_dst + kABytes + kBSlab, &tmap_b, col0 + 64, k0, bar);
+            if (b_kmajor) {   // this CTA's 128 rows of B^T
+              tma_load_2d_pair(a_dst + kABytes, &tmap_b, k0, col0, bar);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 128 / kSlab; ++j)
+                tma_load_2d_pair(a_dst + kABytes + j * kBSlab, &tmap_b, col0 + j * kSlab, k0, bar);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -374,6 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t acc_full1 = map_to_cta(smem_u32(&acc_full_bar[0]), 1);
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
       constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
+      const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -393,11 +457,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int sub = 0; sub < KSUB; ++sub) {
             const uint32_t a_addr = smem_base + stage * kStageBytes + sub * kSlabBytes;
             const uint64_t a_desc = with_address(kADesc, a_addr);
-            const uint64_t b_desc = with_address(kBDesc, a_addr + kABytes);
+            const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
 #pragma unroll
-            for (int kk = 0; kk < kBlockK / 16; ++kk)
+            for (int kk = 0; kk < 4; ++kk)
               if (elected)
-                mma_f16_ss_pair(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
+                mma_ss_pair<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
                                 p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
           }
           // the slot is free in both CTAs once these MMAs retire
@@ -421,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ---------------- epilogue: this CTA's 128 rows of the 256-row tile ----------------
     const int quarter = warp & 3;
-    using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    using OutT = typename Elem<DT>::Out;
     OutT* c = static_cast<OutT*>(p.c);
     int it = 0;
     bool ok = true;
@@ -444,34 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
-        if (row < p.m) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + g * 8;
-            uint32_t packed[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const float lo = __uint_as_float(r[g * 8 + 2 * h]);
-              const float hi = __uint_as_float(r[g * 8 + 2 * h + 1]);
-              if constexpr (BF16) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-                packed[h] = *reinterpret_cast<uint32_t*>(&v);
-              } else {
-                __half2 v = __floats2half2_rn(lo, hi);
-                packed[h] = *reinterpret_cast<uint32_t*>(&v);
-              }
-            }
-            if (p.c_vec_ok && col + 8 <= p.n) {
-              *reinterpret_cast<uint4*>(crow + col) =
-                  make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            } else {
-              const OutT* e = reinterpret_cast<const OutT*>(packed);
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (col + j < p.n) crow[col + j] = e[j];
-            }
-          }
-        }
+        if (row < p.m) store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -501,11 +538,14 @@ struct Resolved {
   bool pair;
 };
 
-int smem_bytes_for(int block_n, int stages) {
-  return stages * (kBlockM * kBlockK * 2 + kBlockK * block_n * 2) + 1024;
+int smem_bytes_for(int block_n, int stages) {   // a stage is 128 bytes of K for every row and column
+  return stages * (kBlockM * 128 + 128 * block_n) + 1024;
 }
 
-int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, Resolved* out) {
+// `row_k`: K elements per 128-byte row (64 for 16-bit operands, 32 for tf32); block_k is
+// resolved in elements of the operand type.
+int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, int row_k, Resolved* out) {
+  const int kBlockK = row_k;
   int bm = cfg ? cfg->block_m : 0, bn = cfg ? cfg->block_n : 0, bk = cfg ? cfg->block_k : 0;
   int stages = cfg ? cfg->stages : 0;
   bool pair = cfg && (cfg->cta_pair || bm == 2 * kBlockM);
@@ -521,20 +561,21 @@ int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, Resolved*
       return fail(NB200_E_INVALID, "block_n=%d: CTA-pair tiles are 256 columns wide", bn);
     if (bk != 0 && bk != kBlockK && bk != 2 * kBlockK && bk != 3 * kBlockK)
       return fail(NB200_E_INVALID,
-                  "block_k=%d: a CTA-pair ring slot holds 64, 128 or 192 elements of K", bk);
+                  "block_k=%d: a CTA-pair ring slot holds %d, %d or %d elements of K", bk, kBlockK,
+                  2 * kBlockK, 3 * kBlockK);
     out->block_k = bk == 0 ? 2 * kBlockK : bk;
     if (stages != 0 && (stages < 1 || stages > 8))
       return fail(NB200_E_INVALID, "stages=%d: supported 1..8", stages);
     out->block_n = 256;
     // ring depth: 3 slots of 128 K-elements, 2 of 192, 4..7 of 64
-    out->stages = out->block_k == 128 ? 3 : (out->block_k == 192 ? 2 :
+    out->stages = out->block_k == 2 * kBlockK ? 3 : (out->block_k == 3 * kBlockK ? 2 :
                   (stages == 0 ? 6 : (stages >= 7 ? 7 : (stages >= 6 ? 6 : (stages >= 5 ? 5 : 4)))));
     return 0;
   }
   if (bm != 0 && bm != kBlockM)
     return fail(NB200_E_INVALID, "block_m=%d: MMA tiles are 128 rows (256 for a CTA pair)", bm);
   if (bk != 0 && bk != kBlockK)
-    return fail(NB200_E_INVALID, "block_k=%d: the TMA ring moves 64-element K slabs", bk);
+    return fail(NB200_E_INVALID, "block_k=%d: the TMA ring moves %d-element K slabs", bk, kBlockK);
   if (bn == 0) bn = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
   if (bn != 64 && bn != 128 && bn != 256)
     return fail(NB200_E_INVALID, "block_n=%d: supported 64, 128, 256", bn);
@@ -557,53 +598,55 @@ int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, Resolved*
 }
 
 int check_problem(const void* a, const void* b, const void* c, int64_t m, int64_t n, int64_t k,
-                  int64_t lda, int64_t ldb, int64_t ldc, int dtype) {
-  if (dtype != NB200_F16 && dtype != NB200_BF16)
-    return fail(NB200_E_UNSUPPORTED, "gemm: dtype code %d (fp16 and bf16 only)", dtype);
+                  int64_t lda, int64_t ldb, int64_t ldc, int dtype, bool b_kmajor) {
+  if (dtype != NB200_F16 && dtype != NB200_BF16 && dtype != NB200_F32)
+    return fail(NB200_E_UNSUPPORTED, "gemm: dtype code %d (fp16, bf16, and fp32 as tf32)", dtype);
+  const int eb = dtype == NB200_F32 ? 4 : 2;
   if (m < 0 || n < 0 || k < 0) return fail(NB200_E_INVALID, "gemm: negative extent");
   if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
     return fail(NB200_E_INVALID, "gemm: extent beyond int32");
   if (m == 0 || n == 0) return 0;
   if (!c || (k > 0 && (!a || !b))) return fail(NB200_E_INVALID, "gemm: null tensor pointer");
   if (k == 0) return 0;  // C is cleared; A and B are never read
-  if (lda < k || ldb < n || ldc < n)
+  if (dtype == NB200_F32 && !b_kmajor)
+    return fail(NB200_E_UNSUPPORTED,
+                "gemm: fp32 operands run as tf32, which the tensor core reads K-major only: pass B "
+                "transposed (nb200_gemm_bt) or let nb200_gemm_tf32 transpose it into a workspace");
+  if (lda < k || ldb < (b_kmajor ? k : n) || ldc < n)
     return fail(NB200_E_INVALID, "gemm: row stride smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
                 (long long)lda, (long long)ldb, (long long)ldc);
   // TMA: 16-byte aligned base and row pitch
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
     return fail(NB200_E_UNSUPPORTED, "gemm: A and B must be 16-byte aligned for TMA");
-  if ((lda * 2) % 16 || (ldb * 2) % 16)
+  if ((lda * eb) % 16 || (ldb * eb) % 16)
     return fail(NB200_E_UNSUPPORTED,
-                "gemm: row pitch of A (%lld) and B (%lld) elements must be a multiple of 8 for TMA",
-                (long long)lda, (long long)ldb);
+                "gemm: row pitch of A (%lld) and B (%lld) elements must be a multiple of %d for TMA",
+                (long long)lda, (long long)ldb, 16 / eb);
   return 0;
 }
 
 template <int BN, int STAGES>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool bf16, int grid,
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype, int grid,
            cudaStream_t stream) {
   const int smem = smem_bytes_for(BN, STAGES);
-  auto set = [&](auto kern) {
-    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  auto go = [&](auto kern) {
+    if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
+      return cuda_check(e, "gemm smem attribute");
+    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+    return cuda_check(cudaGetLastError(), "gemm launch");
   };
-  if (bf16) {
-    auto kern = gemm_kernel<BN, STAGES, true>;
-    if (cudaError_t e = set(kern)) return cuda_check(e, "gemm smem attribute");
-    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
-  } else {
-    auto kern = gemm_kernel<BN, STAGES, false>;
-    if (cudaError_t e = set(kern)) return cuda_check(e, "gemm smem attribute");
-    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
-  }
-  return cuda_check(cudaGetLastError(), "gemm launch");
+  if (dtype == NB200_BF16) return go(gemm_kernel<BN, STAGES, NB200_BF16>);
+  if (dtype == NB200_F32) return go(gemm_kernel<BN, STAGES, NB200_F32>);
+  return go(gemm_kernel<BN, STAGES, NB200_F16>);
 }
 
 template <int STAGES, int KSUB>
-int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool bf16,
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype,
                 cudaStream_t stream) {
-  const int smem = STAGES * KSUB * (kBlockM * kBlockK * 2 + kBlockK * 128 * 2) + 1024;
-  const void* kern = bf16 ? (const void*)gemm_pair_kernel<STAGES, KSUB, true>
-                          : (const void*)gemm_pair_kernel<STAGES, KSUB, false>;
+  const int smem = STAGES * KSUB * (kBlockM * 128 + 128 * 128) + 1024;
+  const void* kern = dtype == NB200_BF16 ? (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_BF16>
+                     : dtype == NB200_F32 ? (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_F32>
+                                          : (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_F16>;
   if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
     return cuda_check(e, "gemm pair smem attribute");
   cudaLaunchConfig_t lc = {};
@@ -641,6 +684,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 int encode_tensor_map_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                             const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode_tensor_map(out, base, 2, rank, dims, strides_bytes, box);
+}
+
+int encode_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int rank,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
   static EncodeTiledFn encode = nullptr;
   static std::mutex mu;
   {
@@ -663,8 +711,9 @@ int encode_tensor_map_16bit(CUtensorMap* out, const void* base, int rank, const 
     es[i] = 1;
   }
   for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
-  // the 16-bit payload is moved as raw bits; the element type only sets the size
-  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, (cuuint32_t)rank,
+  // the payload is moved as raw bits; the element type only sets the size
+  CUresult r = encode(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                      (cuuint32_t)rank,
                       const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -680,35 +729,50 @@ using namespace nb200;
 extern "C" int nb200_gemm_check(const void* a, const void* b, const void* c, int64_t m, int64_t n,
                                 int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int dtype,
                                 const nb200_gemm_config* config) {
-  if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype)) return rc;
+  if (dtype == NB200_F32) {
+    // as nb200_gemm_tf32 will see it: B replaced by its transposed copy in the workspace
+    if (k > 0 && m > 0 && n > 0 && (!b || ldb < n))
+      return fail(NB200_E_INVALID, "gemm: B is null or its row stride is smaller than the row");
+    if (int rc = check_problem(a, a, c, m, n, k, lda, (k + 3) / 4 * 4, ldc, dtype, true)) return rc;
+  } else if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype, false)) {
+    return rc;
+  }
   Resolved r;
-  return resolve_config(config, m, n, &r);
+  return resolve_config(config, m, n, dtype == NB200_F32 ? 32 : 64, &r);
 }
 
-extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                          int64_t lda, int64_t ldb, int64_t ldc, int dtype,
-                          const nb200_gemm_config* config, void* stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype)) return rc;
+namespace nb200 {
+// C = A @ B with B given either as [K, N] (b_kmajor = false) or transposed as [N, K].
+int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
+              int64_t ldb, int64_t ldc, int dtype, const nb200_gemm_config* config, bool b_kmajor,
+              cudaStream_t stream) {
+  if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype, b_kmajor)) return rc;
+  const int eb = dtype == NB200_F32 ? 4 : 2;   // bytes per element
+  const int row_k = 128 / eb;                  // K elements per 128-byte row = columns per slab of B
   Resolved cfg;
-  if (int rc = resolve_config(config, m, n, &cfg)) return rc;
+  if (int rc = resolve_config(config, m, n, row_k, &cfg)) return rc;
   if (m == 0 || n == 0) return 0;
   if (k == 0)  // empty reduction: the accumulator is its zero initial value
-    return cuda_check(cudaMemset2DAsync(c, (size_t)ldc * 2, 0, (size_t)n * 2, (size_t)m, stream),
+    return cuda_check(cudaMemset2DAsync(c, (size_t)ldc * eb, 0, (size_t)n * eb, (size_t)m, stream),
                       "gemm k=0 clear");
 
   CUtensorMap ta, tb;
   {
     const uint64_t dims[2] = {(uint64_t)k, (uint64_t)m};
-    const uint64_t strides[1] = {(uint64_t)lda * 2};
-    const uint32_t box[2] = {(uint32_t)kBlockK, (uint32_t)kBlockM};
-    if (int rc = encode_tensor_map_16bit(&ta, a, 2, dims, strides, box)) return rc;
+    const uint64_t strides[1] = {(uint64_t)lda * eb};
+    const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)kBlockM};
+    if (int rc = encode_tensor_map(&ta, a, eb, 2, dims, strides, box)) return rc;
   }
-  {
+  if (b_kmajor) {   // rows of B^T: one box per CTA and stage
+    const uint64_t dims[2] = {(uint64_t)k, (uint64_t)n};
+    const uint64_t strides[1] = {(uint64_t)ldb * eb};
+    const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)(cfg.pair ? 128 : cfg.block_n)};
+    if (int rc = encode_tensor_map(&tb, b, eb, 2, dims, strides, box)) return rc;
+  } else {
     const uint64_t dims[2] = {(uint64_t)n, (uint64_t)k};
-    const uint64_t strides[1] = {(uint64_t)ldb * 2};
-    const uint32_t box[2] = {64u, (uint32_t)kBlockK};
-    if (int rc = encode_tensor_map_16bit(&tb, b, 2, dims, strides, box)) return rc;
+    const uint64_t strides[1] = {(uint64_t)ldb * eb};
+    const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)row_k};
+    if (int rc = encode_tensor_map(&tb, b, eb, 2, dims, strides, box)) return rc;
   }
 
   GemmParams p;
@@ -719,21 +783,24 @@ extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int6
   p.k = (int)k;
   p.m_blocks = (int)cdiv64(m, kBlockM);
   p.n_blocks = (int)cdiv64(n, cfg.block_n);
-  p.k_blocks = (int)cdiv64(k, kBlockK);
-  const bool bf16 = dtype == NB200_BF16;
-  p.idesc = sm100::instr_desc_f16(cfg.pair ? 2 * kBlockM : kBlockM, cfg.block_n, bf16, false, true);
-  p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * 2) % 16 == 0) ? 1 : 0;
+  p.k_blocks = (int)cdiv64(k, row_k);
+  const int mma_m = cfg.pair ? 2 * kBlockM : kBlockM;
+  p.idesc = dtype == NB200_F32
+                ? sm100::instr_desc_tf32(mma_m, cfg.block_n, false, false)
+                : sm100::instr_desc_f16(mma_m, cfg.block_n, dtype == NB200_BF16, false, !b_kmajor);
+  p.b_kmajor = b_kmajor ? 1 : 0;
+  p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * eb) % 16 == 0) ? 1 : 0;
   p.status = device_status_ptr();
   if (!p.status) return fail(NB200_E_CUDA, "gemm: device status word is not addressable");
 
   if (cfg.pair) {
-    if (cfg.block_k == 128) return launch_pair<3, 2>(ta, tb, p, bf16, stream);
-    if (cfg.block_k == 192) return launch_pair<2, 3>(ta, tb, p, bf16, stream);
+    if (cfg.block_k == 2 * row_k) return launch_pair<3, 2>(ta, tb, p, dtype, stream);
+    if (cfg.block_k == 3 * row_k) return launch_pair<2, 3>(ta, tb, p, dtype, stream);
     switch (cfg.stages) {
-      case 4: return launch_pair<4, 1>(ta, tb, p, bf16, stream);
-      case 5: return launch_pair<5, 1>(ta, tb, p, bf16, stream);
-      case 6: return launch_pair<6, 1>(ta, tb, p, bf16, stream);
-      default: return launch_pair<7, 1>(ta, tb, p, bf16, stream);
+      case 4: return launch_pair<4, 1>(ta, tb, p, dtype, stream);
+      case 5: return launch_pair<5, 1>(ta, tb, p, dtype, stream);
+      case 6: return launch_pair<6, 1>(ta, tb, p, dtype, stream);
+      default: return launch_pair<7, 1>(ta, tb, p, dtype, stream);
     }
   }
   const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
@@ -741,7 +808,7 @@ extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int6
   const int grid = (int)(tiles < sms ? tiles : sms);
 
 #define NB200_GEMM_CASE(BN_, ST_) \
-  if (cfg.block_n == BN_ && cfg.stages == ST_) return launch<BN_, ST_>(ta, tb, p, bf16, grid, stream);
+  if (cfg.block_n == BN_ && cfg.stages == ST_) return launch<BN_, ST_>(ta, tb, p, dtype, grid, stream);
   NB200_GEMM_CASE(256, 4)
   NB200_GEMM_CASE(256, 3)
   NB200_GEMM_CASE(256, 2)
@@ -756,4 +823,83 @@ extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int6
 #undef NB200_GEMM_CASE
   return fail(NB200_E_UNSUPPORTED, "gemm: no kernel instance for block_n=%d stages=%d",
               cfg.block_n, cfg.stages);
+}
+
+namespace {
+
+// dst[n][k] = src[k][n] for fp32: 32 x 32 tiles through shared memory, coalesced on both sides.
+// HBM-bound: 8 bytes per element.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                            int rows, int cols, long long ld_src, long long ld_dst) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[i][threadIdx.x] = src[(long long)r * ld_src + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (c < cols && r < rows) dst[(long long)c * ld_dst + r] = tile[threadIdx.x][i];
+  }
+}
+
+}  // namespace
+
+// Row pitch (elements) of the transposed copy of a [K, N] fp32 matrix: K rounded up to the
+// 16 bytes TMA wants.
+int64_t tf32_workspace_pitch(int64_t k) { return (k + 3) / 4 * 4; }
+
+// B [K, N] -> workspace [N, pitch]; then the K-major GEMM.
+int gemm_tf32_via(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
+                  int64_t ldb, int64_t ldc, const nb200_gemm_config* config, void* workspace,
+                  cudaStream_t stream) {
+  if (m < 0 || n < 0 || k < 0) return fail(NB200_E_INVALID, "gemm: negative extent");
+  if (n > INT32_MAX || k > INT32_MAX) return fail(NB200_E_INVALID, "gemm: extent beyond int32");
+  const int64_t pitch = tf32_workspace_pitch(k);
+  if (m > 0 && n > 0 && k > 0) {
+    if (!b) return fail(NB200_E_INVALID, "gemm: null tensor pointer");
+    if (ldb < n) return fail(NB200_E_INVALID, "gemm: row stride of B smaller than the row");
+    const dim3 grid((unsigned)cdiv64(n, 32), (unsigned)cdiv64(k, 32));
+    if (grid.y > 65535u) return fail(NB200_E_INVALID, "gemm: K too large for the transposing pass");
+    transpose_f32_kernel<<<grid, dim3(32, 8), 0, stream>>>(static_cast<const float*>(b),
+                                                           static_cast<float*>(workspace), (int)k,
+                                                           (int)n, ldb, pitch);
+    if (int rc = cuda_check(cudaGetLastError(), "transpose launch")) return rc;
+  }
+  return gemm_impl(a, workspace, c, m, n, k, lda, pitch, ldc, NB200_F32, config, true, stream);
+}
+
+}  // namespace nb200
+
+extern "C" int nb200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                          int64_t lda, int64_t ldb, int64_t ldc, int dtype,
+                          const nb200_gemm_config* config, void* stream) {
+  return gemm_impl(a, b, c, m, n, k, lda, ldb, ldc, dtype, config, false,
+                   static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nb200_gemm_bt(const void* a, const void* bt, void* c, int64_t m, int64_t n, int64_t k,
+                             int64_t lda, int64_t ldbt, int64_t ldc, int dtype,
+                             const nb200_gemm_config* config, void* stream) {
+  return gemm_impl(a, bt, c, m, n, k, lda, ldbt, ldc, dtype, config, true,
+                   static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t nb200_gemm_tf32_workspace_bytes(int64_t n, int64_t k) {
+  return n < 0 || k < 0 ? 0 : n * tf32_workspace_pitch(k) * 4;
+}
+
+extern "C" int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                               int64_t lda, int64_t ldb, int64_t ldc, const nb200_gemm_config* config,
+                               void* workspace, int64_t workspace_bytes, void* stream) {
+  if (m > 0 && n > 0 && k > 0) {
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15))
+      return fail(NB200_E_INVALID, "gemm_tf32: the workspace must be a 16-byte aligned device buffer");
+    if (workspace_bytes < nb200_gemm_tf32_workspace_bytes(n, k))
+      return fail(NB200_E_INVALID, "gemm_tf32: workspace of %lld bytes, %lld needed",
+                  (long long)workspace_bytes, (long long)nb200_gemm_tf32_workspace_bytes(n, k));
+  }
+  return gemm_tf32_via(a, b, c, m, n, k, lda, ldb, ldc, config, workspace,
+                       static_cast<cudaStream_t>(stream));
 }

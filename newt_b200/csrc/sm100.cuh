@@ -178,6 +178,17 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// The same for fp32 operands read as tf32 (8 K-elements per instruction).
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem]; one thread issues.
 __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
                                            uint32_t idesc, uint32_t accumulate) {
@@ -350,6 +361,17 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+__device__ __forceinline__ void mma_tf32_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;"
+      "\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
 // Arrives on one barrier (anywhere in the cluster) once the pair's MMAs issued so far retire.
 __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -383,6 +405,11 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(int m, int n, bool bf16, b
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
          ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+// The same for kind::tf32 (A and B format 2 = tf32).
+__host__ __device__ constexpr uint32_t instr_desc_tf32(int m, int n, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
 // three-input maximum and packed two-wide fp32 arithmetic (one issue slot for two values)
@@ -424,6 +451,8 @@ __device__ __forceinline__ float exp2_approx(float x) {
 // Encodes a tiled 16-bit tensor map with 128-byte swizzle and zero fill.
 // dims/strides are given innermost first; `strides_bytes` has rank-1 entries.
 // Returns 0 or an NB200_E_* code (message recorded).
+int encode_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int rank,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
 int encode_tensor_map_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                             const uint64_t* strides_bytes, const uint32_t* box);
 

@@ -1,8 +1,8 @@
 """Benchmark suite over the sizes the reference publishes (benchmarks/bench.py:170-300 and
 benchmarks/results.md of the reference): vector add, fused softmax, layernorm, fp16 matmul,
-plus causal attention, each next to the torch call on the same tensors.
+fp32/tf32 matmul, plus causal attention, each next to the torch call on the same tensors.
 
-    python -m newt_b200.examples.suite [--quick] [--kernel add|softmax|layernorm|matmul|attention]
+    python -m newt_b200.examples.suite [--quick] [--kernel add|softmax|layernorm|matmul|matmul_tf32|attention]
 
 Clock and metric definitions are the reference's: `do_bench` (median, L2 flushed between
 reps); GB/s = bytes read + written / t; TFLOP/s = 2*M*N*K / t.  Prints markdown tables.
@@ -71,6 +71,26 @@ def bench_matmul(quick):
     return out
 
 
+def bench_matmul_tf32(quick):
+    """fp32 operands, tf32 product (benchmarks/bench.py:291-294: torch runs with allow_tf32).
+    Our time includes the pass that transposes B for the tensor core."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    out = ["| kernel | M=N=K | newt_b200 TFLOP/s | torch TFLOP/s | ratio |", "|---|---|---|---|---|"]
+    try:
+        for n in ([1024, 4096] if quick else [1024, 2048, 4096, 8192]):
+            a_ = torch.randn(n, n, device="cuda") / n ** 0.5
+            b_ = torch.randn(n, n, device="cuda") / n ** 0.5
+            c = torch.empty(n, n, device="cuda")
+            a = testing.do_bench(lambda: K.matmul(a_, b_, c))     # first call autotunes
+            b = testing.do_bench(lambda: torch.matmul(a_, b_, out=c))
+            row = _row("matmul fp32/tf32", n, a, b, 2 * n ** 3 / 1e9)
+            out.append(row + f" <!-- {K.matmul_kernel.best_config} -->")
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    return out
+
+
 def bench_attention(quick):
     out = ["| kernel | B x H x S x D | newt_b200 TFLOP/s | torch SDPA TFLOP/s | ratio |",
            "|---|---|---|---|---|"]
@@ -89,7 +109,7 @@ def bench_attention(quick):
 
 
 SUITES = {"add": bench_add, "softmax": bench_softmax, "layernorm": bench_layernorm,
-          "matmul": bench_matmul, "attention": bench_attention}
+          "matmul": bench_matmul, "matmul_tf32": bench_matmul_tf32, "attention": bench_attention}
 
 
 def main():

@@ -728,6 +728,7 @@ class GemmPlan(Plan):
         self.lda = self.ldb = self.ldc = None
         self.inner = ()
         self.num_stages = 3
+        self.row_k = 64   # K elements per 128-byte row: 64 for fp16/bf16, 32 for fp32 (run as tf32)
 
     def _extents(self, grid, args):
         bm, bn, bk = self.block
@@ -745,12 +746,14 @@ class GemmPlan(Plan):
     def hardware_key(self):
         """What distinguishes this plan on the device.  BLOCK_M = BLOCK_N = 256 asks for the
         CTA-pair kernel (one 256-row tcgen05 MMA over two SMs) whose ring slot holds BLOCK_K
-        = 64, 128 or 192 elements; otherwise the tcgen05 tile is picked by BLOCK_N (when it
-        is a tile the kernel has); num_stages is the ring depth."""
+        = one, two or three 128-byte rows of K (64, 128, 192 elements of fp16/bf16; 32, 64, 96
+        of fp32); otherwise the tcgen05 tile is picked by BLOCK_N (when it is a tile the
+        kernel has); num_stages is the ring depth."""
         bm, bn, bk = self.block
         if bm == 256 and bn == 256:
-            bk = bk if bk in (64, 128, 192) else 128
-            return ("gemm-pair", bk, self.num_stages if bk == 64 else 0)
+            rk = self.row_k
+            bk = bk if bk in (rk, 2 * rk, 3 * rk) else 2 * rk
+            return ("gemm-pair", bk, self.num_stages if bk == rk else 0)
         return ("gemm", bn if bn in (64, 128, 256) else 0, self.num_stages)
 
     def config(self):
@@ -768,13 +771,25 @@ class GemmPlan(Plan):
         m, n, k = self._extents(grid, args)
         if m == 0 or n == 0:
             return
-        for name, fn in self.inner:
-            if fn(args) != 1:
+        inner = {name: fn(args) for name, fn in self.inner}
+        lda, ldb, ldc = self.lda(args), self.ldb(args), self.ldc(args)
+        for name in (self.a, self.c):
+            if inner[name] != 1:
                 raise CompileError(
                     f"matmul: '{name}' is not unit-stride along its fast dimension "
-                    f"(stride {fn(args)}); transposed operands have no sm_100a kernel yet")
-        kernels.gemm(args[self.a], args[self.b], args[self.c], m, n, k, self.lda(args),
-                     self.ldb(args), self.ldc(args), self.config())
+                    f"(stride {inner[name]}); only B may be passed transposed")
+        a, b, c = args[self.a], args[self.b], args[self.c]
+        if inner[self.b] != 1:
+            # B[k, n] at k * 1 + n * stride: the caller handed over B^T, which is what the
+            # tensor core wants anyway
+            if ldb != 1:
+                raise CompileError(
+                    f"matmul: '{self.b}' has strides ({ldb}, {inner[self.b]}); one of them must be 1")
+            kernels.gemm_bt(a, b, c, m, n, k, lda, inner[self.b], ldc, self.config())
+        elif self.row_k == 32:
+            kernels.gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, self.config())
+        else:
+            kernels.gemm(a, b, c, m, n, k, lda, ldb, ldc, self.config())
 
 
 def lower_gemm(trace, an, num_stages):
@@ -807,8 +822,8 @@ def lower_gemm(trace, an, num_stages):
             raise Unmatched(f"matmul: operand {name} of nl.dot is not loaded directly from memory")
         if v.args[1] is not None and v.args[2] not in (None, 0, 0.0):
             raise Unmatched(f"matmul: masked lanes of {name} must read 0")
-    if a.dtype not in (tp.float16, tp.bfloat16):
-        raise Unmatched(f"matmul: {a.dtype.name} operands have no tcgen05 kernel yet")
+    if a.dtype not in (tp.float16, tp.bfloat16, tp.float32):
+        raise Unmatched(f"matmul: {a.dtype.name} operands have no tcgen05 kernel")
 
     _, c_ptr, c_val, c_mask, _ = stores[0]
     out = c_val.args[0] if c_val.op == "cast" else c_val
@@ -849,6 +864,7 @@ def lower_gemm(trace, an, num_stages):
     plan.inner = tuple((nm, _compile_int(t.stride[1])) for nm, t in
                        ((ta.base, ta), (tb.base, tb), (tc.base, tc)))
     plan.num_stages = num_stages
+    plan.row_k = 32 if a.dtype == tp.float32 else 64
     return plan
 
 

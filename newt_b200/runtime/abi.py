@@ -55,6 +55,11 @@ SIGNATURES = {
                                        ctypes.c_float, ctypes.c_int, _vp]),
     "nb200_gemm": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                   ctypes.c_int, ctypes.POINTER(GemmConfig), _vp]),
+    "nb200_gemm_bt": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
+                                     ctypes.c_int, ctypes.POINTER(GemmConfig), _vp]),
+    "nb200_gemm_tf32_workspace_bytes": (ctypes.c_int64, [_i64, _i64]),
+    "nb200_gemm_tf32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
+                                       ctypes.POINTER(GemmConfig), _vp, _i64, _vp]),
     "nb200_gemm_check": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                         ctypes.c_int, ctypes.POINTER(GemmConfig)]),
     "nb200_attention_fwd": (ctypes.c_int, [_vp, _vp, _vp, _vp] + [_i64] * 12 +

@@ -53,6 +53,36 @@ def gemm(a, b, c, m, n, k, lda, ldb, ldc, config=None):
                                     abi.dtype_code(a.dtype), cfg, _stream()))
 
 
+def gemm_bt(a, bt, c, m, n, k, lda, ldbt, ldc, config=None):
+    """C = A @ B with B given transposed: bt is [N, K] with row stride ldbt."""
+    cfg = ctypes.byref(config) if config is not None else None
+    abi.check(abi.load().nb200_gemm_bt(_dev_ptr("a", a), _dev_ptr("b", bt), _dev_ptr("c", c), int(m),
+                                       int(n), int(k), int(lda), int(ldbt), int(ldc),
+                                       abi.dtype_code(a.dtype), cfg, _stream()))
+
+
+_tf32_workspaces = {}   # device index -> uint8 tensor, grown on demand
+
+
+def gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, config=None):
+    """fp32 C = A @ B (tf32 product, fp32 accumulation) with B as [K, N].  The tensor core
+    reads tf32 operands K-major only, so B is transposed into a workspace first.  The workspace
+    is a torch tensor kept per device and grown when a larger B comes along; work queued on
+    other streams that still uses it is the caller's to order, as with any reused buffer."""
+    import torch
+
+    need = int(abi.load().nb200_gemm_tf32_workspace_bytes(int(n), int(k)))
+    dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+    ws = _tf32_workspaces.get(dev)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=a.device)
+        _tf32_workspaces[dev] = ws
+    cfg = ctypes.byref(config) if config is not None else None
+    abi.check(abi.load().nb200_gemm_tf32(_dev_ptr("a", a), _dev_ptr("b", b), _dev_ptr("c", c), int(m),
+                                         int(n), int(k), int(lda), int(ldb), int(ldc), cfg,
+                                         ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream()))
+
+
 def gemm_check(a, b, c, m, n, k, lda, ldb, ldc, config=None):
     """Returns None if the tcgen05 path can run this problem, else the reason (str)."""
     cfg = ctypes.byref(config) if config is not None else None

@@ -122,6 +122,17 @@ def main(ref_root):
         out[key + "/q"], out[key + "/k"], out[key + "/v"] = _np(q), _np(k), _np(v)
         out[key + "/expected_f32"] = _np(exp)
 
+    # fp32 matmul, the case of tests/test_matmul.py:67-70 (nl.dot on fp32 runs as tf32 on the
+    # device; the test's expected value is the fp32 product, within rtol = atol = 1e-2).
+    # Appended last so that the draws above keep their values.
+    a, b = randn(128, 128, dtype=torch.float32, scale=0.5), randn(128, 128, dtype=torch.float32, scale=0.5)
+    eager = torch.empty(128, 128, dtype=torch.float32)
+    ex_mm.matmul.ref(a, b, eager)
+    key = "matmul_f32/128x128x128"
+    out[key + "/a"], out[key + "/b"] = _np(a), _np(b)
+    out[key + "/expected_eager"] = _np(eager)
+    out[key + "/expected_f32"] = _np(a @ b)
+
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

@@ -90,6 +90,38 @@ def test_matmul_fp16(m, n, k, pad):
         torch.testing.assert_close(c.float(), cport.matmul(a, b).float(), rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("m,n,k,bm,bn,bk,pad", [(128, 128, 128, 64, 64, 32, 0),   # tests/test_matmul.py:67-70
+                                               (300, 200, 100, 64, 64, 32, 4),
+                                               (512, 768, 160, 128, 256, 32, 0),
+                                               (512, 512, 256, 256, 256, 64, 0)])   # CTA pair
+def test_matmul_fp32_runs_as_tf32(m, n, k, bm, bn, bk, pad):
+    # nl.dot on fp32 blocks is a tf32 product with fp32 accumulation (newt/language.py:165-167)
+    a, b, c = _run_matmul(rk.matmul_kernel, m, n, k, torch.float32, bm=bm, bn=bn, bk=bk, ld_pad=pad)
+    ref = a.double() @ b.double()
+    torch.testing.assert_close(c.double(), ref, rtol=1e-2, atol=1e-2)      # the reference's bar
+    assert torch_ref.rel_frobenius(c, ref) <= 2e-3                         # tf32 inputs: ~2^-11 each
+    if m * n * k <= 512 * 768 * 160:
+        # the oracle rounds the operands to tf32 as the reference does; the tensor core drops
+        # the low mantissa bits instead, so the two differ by rounding of the operands only
+        assert torch_ref.rel_frobenius(c, cport.matmul(a, b)) <= 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_matmul_with_b_transposed(dtype):
+    # the same kernel text, called with B^T in memory: stride_bk = 1, stride_bn = row pitch
+    m, n, k = 192, 320, 136
+    a = _rand((m, k), 21, dtype, 0.5)
+    b = _rand((k, n), 22, dtype, 0.5)
+    bt = b.t().contiguous().cuda()            # [n, k], pitch 136: a multiple of 8
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    rk.matmul_kernel[(newt.cdiv(m, 64), newt.cdiv(n, 64))](
+        a.cuda(), bt, c, m, n, k, k, 1, 1, k, n, 1, BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    assert torch_ref.rel_frobenius(c.cpu().float(), a.double() @ b.double()) <= (
+        2e-3 if dtype == torch.float32 else 1e-2)
+
+
 def test_matmul_bf16_and_tiles():
     for bn, stages in ((64, 2), (128, 3), (256, 4)):
         a, b, c = _run_matmul(rk.matmul_kernel, 256, 512, 192, torch.bfloat16, bm=128, bn=bn,

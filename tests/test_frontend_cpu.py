@@ -91,11 +91,22 @@ def test_pointer_walk_is_resolved_as_induction():
     assert ("carried", loop.uid, "acc") not in an.closed_forms
 
 
-def test_transposed_operand_is_refused_at_launch_time():
+def test_transposed_operands_are_told_apart_at_launch_time():
     c = rk.matmul_kernel.specialize(F16, F16, F16, 64, 64, 64, 1, 64, 64, 1, 64, 1,
                                     BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
-    a = dict(M=64, N=64, K=64, sam=1, sak=64, sbk=64, sbn=1, scm=64, scn=1)
-    assert dict(c.plan.inner)["a_ptr"](a) == 64   # launch() raises CompileError on this
+    a = dict(M=64, N=64, K=64, sam=1, sak=64, sbk=1, sbn=64, scm=64, scn=1)
+    inner = dict(c.plan.inner)
+    assert inner["a_ptr"](a) == 64   # A transposed: launch() raises CompileError on this
+    assert inner["b_ptr"](a) == 64 and c.plan.ldb(a) == 1   # B transposed: goes to nb200_gemm_bt
+
+
+def test_fp32_matmul_lowers_to_the_tf32_plan():
+    c = rk.matmul_kernel.specialize(F32, F32, F32, 128, 128, 128, 128, 1, 128, 1, 128, 1,
+                                    BLOCK_M=256, BLOCK_N=256, BLOCK_K=32)
+    assert c.plan.row_k == 32 and c.plan.hardware_key() == ("gemm-pair", 32, 3)
+    c = rk.matmul_kernel.specialize(F32, F32, F32, 128, 128, 128, 128, 1, 128, 1, 128, 1,
+                                    BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    assert c.plan.hardware_key() == ("gemm", 64, 3)
 
 
 def test_unrecognised_program_raises_compile_error():

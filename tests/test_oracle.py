@@ -52,6 +52,25 @@ def test_matmul_matches_reference(golden, name):
                                    rtol=tol, atol=tol)
 
 
+def test_matmul_f32_follows_the_tf32_path(golden):
+    p = "matmul_f32/128x128x128"
+    a, b = golden.get(p + "/a"), golden.get(p + "/b")
+    got = cport.matmul(a, b)
+    # the reference's own bar for nl.dot on fp32 (tests/test_matmul.py:67-70)
+    torch.testing.assert_close(got, golden.get(p + "/expected_f32"), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(got, golden.get(p + "/expected_eager"), rtol=1e-2, atol=1e-2)
+    # operands rounded to 10 mantissa bits, products and sums in fp32
+    def tf32(x):
+        u = x.view(torch.int32)
+        return ((u + 0x1000) & ~0x1fff).view(torch.float32)
+    want = torch.zeros(128, 128)
+    ar, br = tf32(a), tf32(b)
+    for kk in range(128):
+        want += ar[:, kk:kk + 1] * br[kk:kk + 1, :]
+    assert torch.equal(got, want)
+    assert 1e-5 < torch_ref.rel_frobenius(got, golden.get(p + "/expected_f32")) < 2e-3
+
+
 def test_attention_matches_sdpa(golden):
     for case in golden.cases("attention"):
         p = f"attention/{case}"

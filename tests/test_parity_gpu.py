@@ -148,8 +148,9 @@ def _gemm(a, b, block_n=0, stages=0):
     m, k = a.shape
     n = b.shape[1]
     c = torch.full((m, n), float("nan"), device="cuda", dtype=a.dtype)
-    kernels.gemm(a, b, c, m, n, k, a.stride(0), b.stride(0), c.stride(0),
-                 kernels.gemm_config(block_n=block_n, stages=stages))
+    run = kernels.gemm_tf32 if a.dtype == torch.float32 else kernels.gemm
+    run(a, b, c, m, n, k, a.stride(0), b.stride(0), c.stride(0),
+        kernels.gemm_config(block_n=block_n, stages=stages))
     torch.cuda.synchronize()
     assert abi.read_status() == (0, 0)
     return c
@@ -188,6 +189,71 @@ def test_gemm_vs_oracle(dtype, block_n, m, n, k):
     if m * n * k <= 130 * 72 * 200:
         want = cport.matmul(a, b)
         assert torch_ref.rel_frobenius(got.float(), want.float()) <= 4e-3
+
+
+def test_gemm_f32_golden_runs_as_tf32(golden):
+    p = "matmul_f32/128x128x128"
+    a, b = golden.get(p + "/a"), golden.get(p + "/b")
+    got = _gemm(a.cuda(), b.cuda()).cpu()
+    # the reference's bar for nl.dot on fp32 blocks (tests/test_matmul.py:67-70)
+    torch.testing.assert_close(got, golden.get(p + "/expected_f32"), rtol=1e-2, atol=1e-2)
+    assert torch_ref.rel_frobenius(got, cport.matmul(a, b)) <= 2e-3
+
+
+@pytest.mark.parametrize("config", [dict(block_n=64), dict(block_n=128), dict(block_n=256, stages=2),
+                                    dict(block_m=256, block_n=256),
+                                    dict(block_m=256, block_n=256, block_k=32, stages=5),
+                                    dict(block_m=256, block_n=256, block_k=96)])
+@pytest.mark.parametrize("m,n,k", [(1, 4, 4), (128, 64, 32), (130, 72, 200), (257, 520, 132),
+                                   (1024, 1024, 1024)])
+def test_gemm_tf32_vs_oracle(config, m, n, k):
+    g = torch.Generator().manual_seed(m * 5 + n * 3 + k)
+    a = torch.randn(m, k, generator=g) / k ** 0.5
+    b = torch.randn(k, n, generator=g)
+    c = torch.full((m, n), float("nan"), device="cuda")
+    kernels.gemm_tf32(a.cuda(), b.cuda(), c, m, n, k, k, n, n, kernels.gemm_config(**config))
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    got = c.cpu()
+    ref = a.double() @ b.double()
+    assert torch_ref.rel_frobenius(got, ref) <= 2e-3
+    if m * n * k <= 130 * 72 * 200:
+        assert torch_ref.rel_frobenius(got, cport.matmul(a, b)) <= 2e-3
+    # exact where tf32 is exact: small integers
+    ai = torch.randint(-8, 9, (m, k), generator=g).float()
+    bi = torch.randint(-8, 9, (k, n), generator=g).float()
+    kernels.gemm_tf32(ai.cuda(), bi.cuda(), c, m, n, k, k, n, n, kernels.gemm_config(**config))
+    torch.cuda.synchronize()
+    assert torch.equal(c.cpu(), ai @ bi)
+
+
+def test_gemm_tf32_rules():
+    a = torch.zeros(64, 102, device="cuda")   # pitch 408 B: not a multiple of 16
+    b = torch.zeros(102, 66, device="cuda")   # B goes through the transposing pass: any pitch
+    c = torch.zeros(64, 64, device="cuda")
+    assert "multiple of 4" in kernels.gemm_check(a, b, c, 64, 64, 102, 102, 66, 64)
+    assert kernels.gemm_check(a, b, c, 64, 64, 100, 104, 66, 64) is None
+    with pytest.raises(abi.UnsupportedError, match="K-major"):
+        kernels.gemm(a, b, c, 64, 64, 100, 104, 66, 64)      # fp32 with B as [K, N]: not this entry
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("config", [dict(block_n=64), dict(block_n=256), dict(block_m=256, block_n=256)])
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (130, 72, 200), (700, 1000, 328)])
+def test_gemm_bt_vs_oracle(dtype, config, m, n, k):
+    # B handed over transposed ([N, K]); the pitch of B^T is padded to what TMA needs
+    g = torch.Generator().manual_seed(m + n * 3 + k * 7)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype)
+    b = torch.randn(k, n, generator=g).to(dtype)
+    bt = torch.zeros(n, k + 8, dtype=dtype)[:, :k]
+    bt.copy_(b.t())
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    btd = bt.cuda() if bt.is_contiguous() else torch.zeros(n, k + 8, dtype=dtype, device="cuda")[:, :k].copy_(bt)
+    kernels.gemm_bt(a.cuda(), btd, c, m, n, k, k, btd.stride(0), n, kernels.gemm_config(**config))
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    tol = 2e-3 if dtype == torch.float32 else 1e-2
+    assert torch_ref.rel_frobenius(c.cpu().float(), a.double() @ b.double()) <= tol
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
