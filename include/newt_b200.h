@@ -137,6 +137,25 @@ int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n,
                     const nb200_gemm_config* config, void* workspace,
                     int64_t workspace_bytes, void* stream);
 
+/* nb200_gemm_tf32 for callers that cannot bring a workspace.  (No counterpart in the
+ * reference, whose generated kernels never need scratch memory.)  A drop-in behind the
+ * reference's launcher is such a caller: `JITFunction._run` hands a kernel nothing but the
+ * user's own tensors and scalars (newt/runtime/jit.py:166-223) and the package allocates no
+ * device memory of its own, so there is no allocator to ask; the same goes for a host that has
+ * given all device memory to its own pool, where a cudaMalloc from a plug-in fails or stalls
+ * the device.  The transposed copy of B goes into a 4 MiB array inside the library image
+ * (held by every GPU that loads the library until the process exits), so the product is
+ * limited to n * round_up(k, 4) <= 1048576 (e.g. 1024 x 1024); larger ones are refused with
+ * NB200_E_UNSUPPORTED and the limit in the message.  The call allocates nothing.  Its first
+ * call on a device looks up the array's device address (once per device; make that first
+ * call outside any stream capture).  All calls on a device share the array and each
+ * overwrites what the last one left there -- nothing in it needs clearing, the product reads
+ * only what its own transposing pass wrote -- so two calls that overlap on the GPU (different
+ * streams, no dependency between them) race; calls on one stream are ordered and safe. */
+int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int64_t m, int64_t n,
+                           int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                           const nb200_gemm_config* config, void* stream);
+
 /* Returns 0 when (dtype, shape, strides, pointers, config) can run on the
  * TMA/tcgen05 path, else NB200_E_* with the reason in nb200_last_error().
  * Launches nothing; lets an autotuner discard configurations analytically

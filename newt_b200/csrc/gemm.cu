@@ -903,3 +903,58 @@ extern "C" int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m,
   return gemm_tf32_via(a, b, c, m, n, k, lda, ldb, ldc, config, workspace,
                        static_cast<cudaStream_t>(stream));
 }
+
+// ---- the same product for callers that have no workspace to give ---------------------
+//
+// Scratch for the transposed copy of B, inside the library image: 4 MiB on every GPU that
+// loads the library, for as long as the process lives.
+#define NB200_TF32_STATIC_FLOATS (1 << 20)
+static __device__ __align__(256) float g_tf32_static_scratch[NB200_TF32_STATIC_FLOATS];
+
+namespace nb200 {
+namespace {
+
+// Device address of the scratch array on the current device.  The array's name means
+// something only to device code; host code has to ask the runtime where it lives, once per
+// device and with that device current.
+float* tf32_static_scratch(int* rc) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static float* address[kMaxDevices] = {};
+  *rc = 0;
+  int dev = -1;
+  if ((*rc = cuda_check(cudaGetDevice(&dev), "current device")) != 0) return nullptr;
+  if (dev < 0 || dev >= kMaxDevices) {
+    *rc = fail(NB200_E_UNSUPPORTED, "gemm_tf32_static: device index %d beyond %d", dev, kMaxDevices - 1);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!address[dev]) {
+    void* ptr = nullptr;
+    if ((*rc = cuda_check(cudaGetSymbolAddress(&ptr, g_tf32_static_scratch),
+                          "address of the static tf32 scratch")) != 0)
+      return nullptr;
+    address[dev] = static_cast<float*>(ptr);
+  }
+  return address[dev];
+}
+
+}  // namespace
+}  // namespace nb200
+
+extern "C" int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int64_t m, int64_t n,
+                                      int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                                      const nb200_gemm_config* config, void* stream) {
+  if (m < 0 || n < 0 || k < 0) return fail(NB200_E_INVALID, "gemm: negative extent");
+  const int64_t need = n * tf32_workspace_pitch(k);   // floats of the transposed copy
+  if (m > 0 && n > 0 && k > 0 && need > NB200_TF32_STATIC_FLOATS)
+    return fail(NB200_E_UNSUPPORTED,
+                "gemm_tf32_static: B transposed needs %lld floats, the built-in scratch holds %d "
+                "(n * round_up(k, 4) <= 1048576); use nb200_gemm_tf32 with a workspace",
+                (long long)need, NB200_TF32_STATIC_FLOATS);
+  int rc = 0;
+  float* scratch = tf32_static_scratch(&rc);
+  if (rc) return rc;
+  return gemm_tf32_via(a, b, c, m, n, k, lda, ldb, ldc, config, scratch,
+                       static_cast<cudaStream_t>(stream));
+}
