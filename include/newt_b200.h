@@ -145,7 +145,8 @@ int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n,
  * given all device memory to its own pool, where a cudaMalloc from a plug-in fails or stalls
  * the device.  The transposed copy of B goes into a 4 MiB array inside the library image
  * (held by every GPU that loads the library until the process exits), so the product is
- * limited to n * round_up(k, 4) <= 1048576 (e.g. 1024 x 1024); larger ones are refused with
+ * limited to n * round_up(k, 4) <= 1048576 (e.g. 1024 x 1024; a k that is a multiple of 8192
+ * counts 32 more, see nb200_gemm_tf32_workspace_bytes); larger ones are refused with
  * NB200_E_UNSUPPORTED and the limit in the message.  The call allocates nothing.  Its first
  * call on a device looks up the array's device address (once per device; make that first
  * call outside any stream capture).  All calls on a device share the array and each

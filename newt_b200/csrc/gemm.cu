@@ -827,28 +827,59 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
 
 namespace {
 
-// dst[n][k] = src[k][n] for fp32: 32 x 32 tiles through shared memory, coalesced on both sides.
-// HBM-bound: 8 bytes per element.
+// dst[n][k] = src[k][n] for fp32: 64 x 64 tiles through shared memory, 16-byte accesses on
+// both sides where the tile is whole and the pitches allow it, element by element at the
+// ragged edges.  HBM-bound: 8 bytes per element.
 __global__ void __launch_bounds__(256) transpose_f32_kernel(const float* __restrict__ src, float* __restrict__ dst,
-                                                            int rows, int cols, long long ld_src, long long ld_dst) {
-  __shared__ float tile[32][33];
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  for (int i = threadIdx.y; i < 32; i += 8) {
-    const int r = r0 + i, c = c0 + threadIdx.x;
-    if (r < rows && c < cols) tile[i][threadIdx.x] = src[(long long)r * ld_src + c];
+                                                            int rows, int cols, long long ld_src, long long ld_dst,
+                                                            int vec_ok) {
+  __shared__ float tile[64][65];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads
+  const bool whole = vec_ok && r0 + 64 <= rows && c0 + 64 <= cols;
+  if (whole) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty + 16 * i;
+      const float4 v = *reinterpret_cast<const float4*>(src + (long long)(r0 + r) * ld_src + c0 + 4 * tx);
+      tile[r][4 * tx] = v.x;
+      tile[r][4 * tx + 1] = v.y;
+      tile[r][4 * tx + 2] = v.z;
+      tile[r][4 * tx + 3] = v.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+      const int r = i >> 6, c = i & 63;
+      if (r0 + r < rows && c0 + c < cols) tile[r][c] = src[(long long)(r0 + r) * ld_src + c0 + c];
+    }
   }
   __syncthreads();
-  for (int i = threadIdx.y; i < 32; i += 8) {
-    const int c = c0 + i, r = r0 + threadIdx.x;
-    if (c < cols && r < rows) dst[(long long)c * ld_dst + r] = tile[threadIdx.x][i];
+  if (whole) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = ty + 16 * i;   // a source column = a destination row
+      const float4 v = make_float4(tile[4 * tx][c], tile[4 * tx + 1][c], tile[4 * tx + 2][c],
+                                   tile[4 * tx + 3][c]);
+      *reinterpret_cast<float4*>(dst + (long long)(c0 + c) * ld_dst + r0 + 4 * tx) = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+      const int c = i >> 6, r = i & 63;
+      if (r0 + r < rows && c0 + c < cols) dst[(long long)(c0 + c) * ld_dst + r0 + r] = tile[r][c];
+    }
   }
 }
 
 }  // namespace
 
 // Row pitch (elements) of the transposed copy of a [K, N] fp32 matrix: K rounded up to the
-// 16 bytes TMA wants.
-int64_t tf32_workspace_pitch(int64_t k) { return (k + 3) / 4 * 4; }
+// 16 bytes TMA wants -- and 128 bytes more when that makes rows a multiple of 32 KB apart, where
+// the transposing pass would write all of a tile's 64 rows into the same few DRAM channels
+// (measured at K = 8192: 2.1 TB/s instead of 5 TB/s).
+int64_t tf32_workspace_pitch(int64_t k) {
+  const int64_t pitch = (k + 3) / 4 * 4;
+  return pitch % 8192 == 0 && pitch > 0 ? pitch + 32 : pitch;
+}
 
 // B [K, N] -> workspace [N, pitch]; then the K-major GEMM.
 int gemm_tf32_via(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
@@ -860,11 +891,13 @@ int gemm_tf32_via(const void* a, const void* b, void* c, int64_t m, int64_t n, i
   if (m > 0 && n > 0 && k > 0) {
     if (!b) return fail(NB200_E_INVALID, "gemm: null tensor pointer");
     if (ldb < n) return fail(NB200_E_INVALID, "gemm: row stride of B smaller than the row");
-    const dim3 grid((unsigned)cdiv64(n, 32), (unsigned)cdiv64(k, 32));
+    const dim3 grid((unsigned)cdiv64(n, 64), (unsigned)cdiv64(k, 64));
     if (grid.y > 65535u) return fail(NB200_E_INVALID, "gemm: K too large for the transposing pass");
-    transpose_f32_kernel<<<grid, dim3(32, 8), 0, stream>>>(static_cast<const float*>(b),
-                                                           static_cast<float*>(workspace), (int)k,
-                                                           (int)n, ldb, pitch);
+    const int vec_ok = (reinterpret_cast<uintptr_t>(b) & 15) == 0 && ldb % 4 == 0 &&
+                       (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;   // pitch % 4 == 0 always
+    transpose_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(b),
+                                                   static_cast<float*>(workspace), (int)k, (int)n, ldb,
+                                                   pitch, vec_ok);
     if (int rc = cuda_check(cudaGetLastError(), "transpose launch")) return rc;
   }
   return gemm_impl(a, workspace, c, m, n, k, lda, pitch, ldc, NB200_F32, config, true, stream);
@@ -950,7 +983,8 @@ extern "C" int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int
   if (m > 0 && n > 0 && k > 0 && need > NB200_TF32_STATIC_FLOATS)
     return fail(NB200_E_UNSUPPORTED,
                 "gemm_tf32_static: B transposed needs %lld floats, the built-in scratch holds %d "
-                "(n * round_up(k, 4) <= 1048576); use nb200_gemm_tf32 with a workspace",
+                "(n * round_up(k, 4) <= 1048576, a k that is a multiple of 8192 counting 32 more); "
+                "use nb200_gemm_tf32 with a workspace",
                 (long long)need, NB200_TF32_STATIC_FLOATS);
   int rc = 0;
   float* scratch = tf32_static_scratch(&rc);
