@@ -15,11 +15,14 @@ implement:
 Recognition is structural (on the expression graph, not on source text) and
 every quantity a kernel needs -- extents, strides, which argument plays which
 role -- is recovered from the graph as a polynomial in the runtime arguments
-and evaluated at launch.  A program that matches none of them raises
-CompileError naming what is missing; nothing falls back to another backend.
+and evaluated at launch.  A program that matches none of them and is plain block
+arithmetic -- no runtime loop, no reduction, no dot -- is turned into CUDA text and
+compiled at run time (pointwise.py, PointwisePlan); anything else raises CompileError
+naming what is missing.  Nothing falls back to another backend or to the CPU.
 """
 
 from .. import types as tp
+from . import pointwise
 from .affine import Analyzer, NotAffine, Poly
 from .trace import CompileError, Node
 
@@ -1083,6 +1086,32 @@ def lower_attention(trace, an, num_stages):
 _RECOGNISERS = []
 
 
+class PointwisePlan(Plan):
+    """A loop-free, reduction-free program: generated CUDA, compiled by NVRTC for sm_100a on
+    first launch, one CUDA block per program instance (frontend/pointwise.py)."""
+
+    kind, entry = "block arithmetic", "run-time compiled kernel (NVRTC, sm_100a)"
+
+    def __init__(self, trace, num_warps):
+        self.num_warps = num_warps
+        self.source, self.kernel_name, self.params = pointwise.generate(trace, num_warps)
+        self._kernel = None
+
+    def hardware_key(self):
+        return ("pointwise", self.kernel_name, self.num_warps)
+
+    def launch(self, grid, args):
+        import torch
+
+        from ..runtime import nvrtc
+
+        if self._kernel is None:
+            self._kernel = nvrtc.Kernel(nvrtc.compile_cubin(self.source, self.kernel_name + ".cu"),
+                                        self.kernel_name)
+        self._kernel.launch(grid, self.num_warps * 32, pointwise.marshal(self.params, args),
+                            torch.cuda.current_stream().cuda_stream)
+
+
 def lower(trace, num_warps=4, num_stages=3):
     """Picks the launch plan for a traced kernel or raises CompileError."""
     an = Analyzer(trace)
@@ -1103,7 +1132,13 @@ def lower(trace, num_warps=4, num_stages=3):
             reasons.append(str(e))
         except NotAffine as e:
             reasons.append(f"{name}: address arithmetic is not affine ({e})")
+    # not one of the tuned programs: block arithmetic without loops or reductions is compiled
+    # at run time
+    try:
+        return PointwisePlan(trace, num_warps)
+    except pointwise.Unsupported as e:
+        reasons.append(f"generic elementwise lowering: {e}")
     raise CompileError(
-        f"{trace.name}: no sm_100a kernel implements this program yet (generic lowering of "
-        f"the block language is not part of this backend).  Closest matches:\n  - "
+        f"{trace.name}: no sm_100a kernel implements this program yet (the generic lowering "
+        f"covers loop-free, reduction-free block arithmetic only).  Closest matches:\n  - "
         + "\n  - ".join(reasons))

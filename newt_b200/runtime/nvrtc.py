@@ -1,0 +1,133 @@
+"""Run-time compilation of generated CUDA for sm_100a: NVRTC -> cubin -> module -> launch.
+
+The five hot programs run through the prebuilt library; programs outside them that are pure
+block arithmetic (newt_b200/frontend/pointwise.py) are compiled here, the way the reference
+compiles everything (newt/runtime/cuda.py:124-154 `compile_cuda`, :177-234 `Kernel`): NVRTC
+with `--gpu-architecture=sm_100a`, the cubin loaded with the driver API and launched on
+torch's current stream.  libnvrtc and libcuda are bound with ctypes; nothing here touches the
+device until a kernel is launched.
+"""
+
+import ctypes
+import os
+import threading
+
+_lock = threading.Lock()
+_nvrtc = None
+_cuda = None
+
+
+class NVRTCError(RuntimeError):
+    """Compilation failed; the message carries the log and the numbered source
+    (newt/runtime/jit.py:58-61 does the same)."""
+
+
+class CUDAError(RuntimeError):
+    pass
+
+
+def _load_nvrtc():
+    global _nvrtc
+    if _nvrtc is None:
+        last = None
+        for name in ("libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so",
+                     "libnvrtc.so.13"):
+            try:
+                _nvrtc = ctypes.CDLL(name)
+                break
+            except OSError as e:
+                last = e
+        if _nvrtc is None:
+            raise NVRTCError(f"libnvrtc is not loadable: {last}")
+    return _nvrtc
+
+
+def _load_cuda():
+    global _cuda
+    if _cuda is None:
+        try:
+            _cuda = ctypes.CDLL("libcuda.so.1")
+        except OSError as e:
+            raise CUDAError(f"libcuda.so.1 is not loadable (no NVIDIA driver?): {e}") from e
+    return _cuda
+
+
+def _numbered(source):
+    return "\n".join(f"{i + 1:4d} | {line}" for i, line in enumerate(source.splitlines()))
+
+
+def compile_cubin(source, name="kernel.cu", arch="sm_100a", extra_opts=()):
+    """CUDA C++ text -> cubin bytes for `arch`.  Works without a GPU."""
+    lib = _load_nvrtc()
+    prog = ctypes.c_void_p()
+    rc = lib.nvrtcCreateProgram(ctypes.byref(prog), source.encode(), name.encode(), 0, None, None)
+    if rc != 0:
+        raise NVRTCError(f"nvrtcCreateProgram failed with code {rc}")
+    try:
+        include = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
+        opts = [f"--gpu-architecture={arch}", "--std=c++17", "-lineinfo", f"-I{include}",
+                *extra_opts]
+        arr = (ctypes.c_char_p * len(opts))(*[o.encode() for o in opts])
+        rc = lib.nvrtcCompileProgram(prog, len(opts), arr)
+        if rc != 0:
+            size = ctypes.c_size_t()
+            lib.nvrtcGetProgramLogSize(prog, ctypes.byref(size))
+            log = ctypes.create_string_buffer(size.value or 1)
+            lib.nvrtcGetProgramLog(prog, log)
+            raise NVRTCError(f"NVRTC could not compile {name}:\n{log.value.decode(errors='replace')}\n"
+                             f"{_numbered(source)}")
+        size = ctypes.c_size_t()
+        if lib.nvrtcGetCUBINSize(prog, ctypes.byref(size)) != 0 or size.value == 0:
+            raise NVRTCError(f"NVRTC produced no cubin for {arch}")
+        cubin = ctypes.create_string_buffer(size.value)
+        if lib.nvrtcGetCUBIN(prog, cubin) != 0:
+            raise NVRTCError("nvrtcGetCUBIN failed")
+        return cubin.raw
+    finally:
+        lib.nvrtcDestroyProgram(ctypes.byref(prog))
+
+
+def _check(rc, what):
+    if rc != 0:
+        msg = ctypes.c_char_p()
+        _load_cuda().cuGetErrorString(rc, ctypes.byref(msg))
+        raise CUDAError(f"{what} failed: {msg.value.decode() if msg.value else rc}")
+
+
+class Kernel:
+    """One function of a cubin, loaded per device on first launch."""
+
+    def __init__(self, cubin, func_name):
+        self.cubin = cubin
+        self.func_name = func_name
+        self._functions = {}   # device index -> CUfunction
+
+    def _function(self):
+        import torch
+
+        dev = torch.cuda.current_device()
+        fn = self._functions.get(dev)
+        if fn is None:
+            with _lock:
+                fn = self._functions.get(dev)
+                if fn is None:
+                    torch.cuda.init()
+                    torch.zeros(1, device=f"cuda:{dev}")   # makes the primary context current
+                    cu = _load_cuda()
+                    module = ctypes.c_void_p()
+                    _check(cu.cuModuleLoadData(ctypes.byref(module), self.cubin), "cuModuleLoadData")
+                    fn = ctypes.c_void_p()
+                    _check(cu.cuModuleGetFunction(ctypes.byref(fn), module, self.func_name.encode()),
+                           "cuModuleGetFunction")
+                    self._functions[dev] = fn
+        return fn
+
+    def launch(self, grid, block, args, stream):
+        """`args`: ctypes values in parameter order; `stream`: a CUstream handle (int)."""
+        cu = _load_cuda()
+        fn = self._function()
+        g = tuple(grid) + (1,) * (3 - len(grid))
+        ptrs = (ctypes.c_void_p * len(args))(*[ctypes.cast(ctypes.pointer(a), ctypes.c_void_p)
+                                               for a in args])
+        _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], block, 1, 1, 0, ctypes.c_void_p(stream),
+                                 ptrs, None), f"launch of {self.func_name}")

@@ -315,3 +315,99 @@ def test_deuteron_layernorm(tmp_path, monkeypatch):
     out = torch.empty(512, 1500, device="cuda")
     dt_layernorm(x.cuda(), w.cuda(), b.cuda(), out, 1e-5)
     assert (out.cpu() - torch_ref.layernorm(x, w, b)).abs().max().item() < 1e-3
+
+
+# ---- block arithmetic outside the tuned programs: generated CUDA, compiled at run time ----
+
+@newt.jit
+def pw_gelu_residual(x_ptr, y_ptr, out_ptr, n, BLOCK: nl.constexpr):
+    offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+    m = offs < n
+    v = nl.load(x_ptr + offs, mask=m, other=0.0)
+    inner = 0.7978845608028654 * (v + 0.044715 * v * v * v)
+    g = 0.5 * v * (1.0 + nl.tanh(inner))
+    nl.store(out_ptr + offs, g + nl.load(y_ptr + offs, mask=m), mask=m)
+
+
+@newt.jit
+def pw_bias_relu_2d(x_ptr, b_ptr, out_ptr, M, N, sx, so, BM: nl.constexpr, BN: nl.constexpr):
+    rm = nl.program_id(0) * BM + nl.arange(0, BM)
+    rn = nl.program_id(1) * BN + nl.arange(0, BN)
+    mask = (rm[:, None] < M) & (rn[None, :] < N)
+    x = nl.load(x_ptr + rm[:, None] * sx + rn[None, :], mask=mask, other=0.0)
+    b = nl.load(b_ptr + rn, mask=rn < N, other=0.0)
+    nl.store(out_ptr + rm[:, None] * so + rn[None, :], nl.maximum(x + b[None, :], 0.0), mask=mask)
+
+
+@newt.jit
+def pw_mixed(x_ptr, i_ptr, f_out, i_out, n, alpha, BLOCK: nl.constexpr):
+    offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+    m = offs < n
+    x = nl.load(x_ptr + offs, mask=m, other=1.0)
+    k = nl.load(i_ptr + offs, mask=m, other=0)
+    y = nl.where(k % 3 == 0, nl.exp(-nl.abs(x)) * alpha, nl.sqrt(nl.abs(x)) / (1.0 + nl.sigmoid(x)))
+    nl.store(f_out + offs, y.to(nl.float16), mask=m)
+    nl.store(i_out + offs, (k * 7 + offs) // 5 - (k >> 1), mask=m)
+
+
+def test_generated_elementwise_fp32():
+    n = 100_003
+    x, y = _rand((n,), 31), _rand((n,), 32)
+    out = torch.full((n,), float("nan"), device="cuda")
+    pw_gelu_residual[(newt.cdiv(n, 1024),)](x.cuda(), y.cuda(), out, n, BLOCK=1024)
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.gelu(x.double(), approximate="tanh") + y.double()
+    torch.testing.assert_close(out.cpu().double(), ref, rtol=2e-6, atol=2e-6)
+
+
+def test_generated_elementwise_fp16_2d_broadcast_is_bit_exact():
+    m, n = 300, 517
+    x, b = _rand((m, n), 33, torch.float16), _rand((n,), 34, torch.float16)
+    xd = torch.zeros(m, n + 3, device="cuda", dtype=torch.float16)[:, :n]   # a row pitch that is not n
+    xd.copy_(x)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float16)
+    pw_bias_relu_2d[(newt.cdiv(m, 32), newt.cdiv(n, 64))](xd, b.cuda(), out, m, n, xd.stride(0),
+                                                           out.stride(0), BM=32, BN=64, num_warps=8)
+    torch.cuda.synchronize()
+    # every fp16 operation is one fp32 operation rounded to fp16, which is what torch does on CPU
+    assert torch.equal(out.cpu(), torch.relu(x + b[None, :]))
+
+
+def test_generated_elementwise_mixed_types_two_stores():
+    n = 5000
+    x = _rand((n,), 35)
+    k = torch.randint(-1000, 1000, (n,), generator=torch.Generator().manual_seed(36), dtype=torch.int32)
+    f_out = torch.full((n,), float("nan"), device="cuda", dtype=torch.float16)
+    i_out = torch.full((n,), -1, device="cuda", dtype=torch.int32)
+    pw_mixed[(newt.cdiv(n, 256),)](x.cuda(), k.cuda(), f_out, i_out, n, 0.25, BLOCK=256)
+    torch.cuda.synchronize()
+    xd = x.double()
+    # `%`, `//` and `>>` are C's on int32 (truncating division), as in the reference's lowering
+    c_mod = torch.fmod(k, 3)
+    want_f = torch.where(c_mod == 0, torch.exp(-xd.abs()) * 0.25,
+                         xd.abs().sqrt() / (1.0 + torch.sigmoid(xd)))
+    torch.testing.assert_close(f_out.cpu().double(), want_f, rtol=2e-3, atol=1e-6)
+    t = k * 7 + torch.arange(n, dtype=torch.int32)
+    want_i = torch.div(t, 5, rounding_mode="trunc") - (k >> 1)
+    assert torch.equal(i_out.cpu(), want_i.to(torch.int32))
+
+
+@dt.kernel
+def dt_fused_gelu_residual(x, y, out):
+    # examples/deuteron/04_fused_ops.py of the reference
+    for t in dt.tile(x.shape[0]):
+        v = x[t]
+        inner = 0.7978845608028654 * (v + 0.044715 * v * v * v)
+        g = 0.5 * v * (1.0 + dt.tanh(inner))
+        out[t] = g + y[t]
+
+
+def test_deuteron_fused_elementwise_chain(tmp_path, monkeypatch):
+    monkeypatch.setenv("DEUTERON_CACHE_DIR", str(tmp_path))
+    n = 1 << 18
+    x, y = _rand((n,), 37), _rand((n,), 38)
+    out = torch.full((n,), float("nan"), device="cuda")
+    dt_fused_gelu_residual(x.cuda(), y.cuda(), out)
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.gelu(x.double(), approximate="tanh") + y.double()
+    assert (out.cpu().double() - ref).abs().max().item() < 1e-5     # the example's own bar

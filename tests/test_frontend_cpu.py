@@ -111,12 +111,56 @@ def test_fp32_matmul_lowers_to_the_tf32_plan():
 
 def test_unrecognised_program_raises_compile_error():
     @newt.jit
+    def block_sum(x_ptr, out_ptr, n, BLOCK: nl.constexpr):     # a reduction that is no tuned program
+        offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        x = nl.load(x_ptr + offs, mask=offs < n, other=0.0)
+        nl.store(out_ptr + nl.program_id(0), nl.sum(x * x, axis=0))
+
+    with pytest.raises(newt.CompileError, match="no sm_100a kernel"):
+        block_sum.specialize(F32, F32, 100, BLOCK=128)
+
+
+def test_block_arithmetic_is_compiled_at_run_time():
+    from newt_b200.frontend.lower import PointwisePlan
+    from newt_b200.runtime import nvrtc
+
+    @newt.jit
     def scale(x_ptr, out_ptr, n, BLOCK: nl.constexpr):
         offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
         nl.store(out_ptr + offs, nl.load(x_ptr + offs, mask=offs < n) * 2.0, mask=offs < n)
 
-    with pytest.raises(newt.CompileError, match="no sm_100a kernel"):
-        scale.specialize(F32, F32, 100, BLOCK=128)
+    @newt.jit
+    def bias_relu(x_ptr, b_ptr, out_ptr, M, N, sx, so, BM: nl.constexpr, BN: nl.constexpr):
+        rm = nl.program_id(0) * BM + nl.arange(0, BM)
+        rn = nl.program_id(1) * BN + nl.arange(0, BN)
+        mask = (rm[:, None] < M) & (rn[None, :] < N)
+        x = nl.load(x_ptr + rm[:, None] * sx + rn[None, :], mask=mask, other=0.0)
+        b = nl.load(b_ptr + rn, mask=rn < N, other=0.0)
+        y = nl.where(x + b[None, :] > 0.0, x + b[None, :], 0.0)
+        nl.store(out_ptr + rm[:, None] * so + rn[None, :], nl.sigmoid(y).to(nl.float32), mask=mask)
+
+    for kernel, spec, kw in ((scale, (F32, F32, 100), dict(BLOCK=128)),
+                             (bias_relu, (F16, F16, F32, 100, 200, 200, 200), dict(BM=16, BN=64))):
+        c = kernel.specialize(*spec, **kw)
+        assert isinstance(c.plan, PointwisePlan)
+        assert f'extern "C" __global__ void __launch_bounds__(128) {c.plan.kernel_name}(' in c.plan.source
+        # fp16 arithmetic is done in fp32 and rounded back after every operation
+        if kernel is bias_relu:
+            assert "__float2half_rn((__half2float(" in c.plan.source
+        cubin = nvrtc.compile_cubin(c.plan.source, c.plan.kernel_name + ".cu")   # needs no GPU
+        assert cubin[:4] == b"\x7fELF"
+
+
+def test_block_arithmetic_refuses_what_it_could_get_wrong():
+    @newt.jit
+    def read_after_write(x_ptr, y_ptr, n, BLOCK: nl.constexpr):
+        offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        x = nl.load(x_ptr + offs, mask=offs < n)
+        nl.store(x_ptr + offs, x + 1.0, mask=offs < n)
+        nl.store(y_ptr + offs, x, mask=offs < n)      # x must be the value from before the first store
+
+    with pytest.raises(newt.CompileError, match="read after the program stored to it"):
+        read_after_write.specialize(F32, F32, 100, BLOCK=128)
 
 
 def test_language_errors_are_compile_errors():
