@@ -25,6 +25,26 @@ def add(x, y, out=None):
 
 
 @newt.jit
+def gelu_residual_kernel(x_ptr, y_ptr, out_ptr, n, BLOCK: nl.constexpr):
+    """out = gelu(x) + y, tanh approximation: the chain of examples/deuteron/04_fused_ops.py
+    written against the block language.  Not one of the tuned programs: it goes through the
+    generic elementwise lowering."""
+    offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+    mask = offs < n
+    v = nl.load(x_ptr + offs, mask=mask, other=0.0)
+    inner = 0.7978845608028654 * (v + 0.044715 * v * v * v)
+    g = 0.5 * v * (1.0 + nl.tanh(inner))
+    nl.store(out_ptr + offs, g + nl.load(y_ptr + offs, mask=mask, other=0.0), mask=mask)
+
+
+def gelu_residual(x, y, out=None, BLOCK=2048, num_warps=8):
+    out = torch.empty_like(x) if out is None else out
+    n = x.numel()
+    gelu_residual_kernel[(newt.cdiv(n, BLOCK),)](x, y, out, n, BLOCK=BLOCK, num_warps=num_warps)
+    return out
+
+
+@newt.jit
 def softmax_kernel(x_ptr, out_ptr, N, stride, BLOCK_N: nl.constexpr):
     row = nl.program_id(0)
     cols = nl.arange(0, BLOCK_N)

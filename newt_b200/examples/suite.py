@@ -2,7 +2,7 @@
 benchmarks/results.md of the reference): vector add, fused softmax, layernorm, fp16 matmul,
 fp32/tf32 matmul, plus causal attention, each next to the torch call on the same tensors.
 
-    python -m newt_b200.examples.suite [--quick] [--kernel add|softmax|layernorm|matmul|matmul_tf32|attention]
+    python -m newt_b200.examples.suite [--quick] [--kernel add|fused|softmax|layernorm|matmul|matmul_tf32|attention]
 
 Clock and metric definitions are the reference's: `do_bench` (median, L2 flushed between
 reps); GB/s = bytes read + written / t; TFLOP/s = 2*M*N*K / t.  Prints markdown tables.
@@ -29,6 +29,19 @@ def bench_add(quick):
         a = testing.do_bench(lambda: K.add(x, y, o))
         b = testing.do_bench(lambda: torch.add(x, y, out=o))
         out.append(_row("add fp32", n, a, b, 3 * n * 4 / 1e6))
+    return out
+
+
+def bench_fused(quick):
+    """gelu(x) + y in one generated kernel against the two torch launches
+    (examples/deuteron/04_fused_ops.py); bytes = 3 * n * 4."""
+    out = ["| kernel | n | newt_b200 GB/s | torch GB/s | ratio |", "|---|---|---|---|---|"]
+    for n in ([1 << 22, 1 << 26] if quick else [1 << 20, 1 << 22, 1 << 24, 1 << 26]):
+        x, y = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+        o = torch.empty_like(x)
+        a = testing.do_bench(lambda: K.gelu_residual(x, y, o))
+        b = testing.do_bench(lambda: torch.add(torch.nn.functional.gelu(x, approximate="tanh"), y, out=o))
+        out.append(_row("gelu+residual fp32", n, a, b, 3 * n * 4 / 1e6))
     return out
 
 
@@ -108,7 +121,7 @@ def bench_attention(quick):
     return out
 
 
-SUITES = {"add": bench_add, "softmax": bench_softmax, "layernorm": bench_layernorm,
+SUITES = {"add": bench_add, "fused": bench_fused, "softmax": bench_softmax, "layernorm": bench_layernorm,
           "matmul": bench_matmul, "matmul_tf32": bench_matmul_tf32, "attention": bench_attention}
 
 

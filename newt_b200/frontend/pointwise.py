@@ -297,6 +297,7 @@ def generate(trace, num_warps):
         guard = _emit(body, mask, _operand_dims(shape, dims, mask.shape)) if mask is not None else None
         lines = []
         if shape:
+            lines.append("#pragma unroll 8")
             lines.append(f"for (int e = threadIdx.x; e < {numel}; e += {threads}) {{")
             lines.append("  int r = e;")
             for d in range(len(shape) - 1, 0, -1):
@@ -312,7 +313,11 @@ def generate(trace, num_warps):
         chunks.append("\n  ".join(lines))
 
     params = [(name, node.dtype) for name, node in trace.params.items()]
-    decl = ", ".join(f"{t.ctype} {name}" for name, t in params)
+    # Elements are independent, so the loads of several iterations may be issued before the
+    # stores of earlier ones; `__restrict__` says so (a tensor passed under two names is still
+    # fine as long as element i is only read for element i, as in any in-place elementwise call).
+    decl = ", ".join(f"{t.ctype} __restrict__ {name}" if isinstance(t, tp.pointer_type)
+                     else f"{t.ctype} {name}" for name, t in params)
     body_text = "\n  __syncthreads();\n  ".join(chunks)
     digest = hashlib.sha1((decl + body_text).encode()).hexdigest()[:8]
     kernel_name = f"{trace.name}_{digest}"
