@@ -15,8 +15,8 @@ implement:
 Recognition is structural (on the expression graph, not on source text) and
 every quantity a kernel needs -- extents, strides, which argument plays which
 role -- is recovered from the graph as a polynomial in the runtime arguments
-and evaluated at launch.  A program that matches none of them and is plain block
-arithmetic -- no runtime loop, no reduction, no dot -- is turned into CUDA text and
+and evaluated at launch.  A program that matches none of them and has no runtime loop
+and no dot -- block arithmetic, reductions included -- is turned into CUDA text and
 compiled at run time (pointwise.py, PointwisePlan); anything else raises CompileError
 naming what is missing.  Nothing falls back to another backend or to the CPU.
 """
@@ -1087,7 +1087,7 @@ _RECOGNISERS = []
 
 
 class PointwisePlan(Plan):
-    """A loop-free, reduction-free program: generated CUDA, compiled by NVRTC for sm_100a on
+    """A loop-free program without dots: generated CUDA, compiled by NVRTC for sm_100a on
     first launch, one CUDA block per program instance (frontend/pointwise.py)."""
 
     kind, entry = "block arithmetic", "run-time compiled kernel (NVRTC, sm_100a)"
@@ -1140,5 +1140,5 @@ def lower(trace, num_warps=4, num_stages=3):
         reasons.append(f"generic elementwise lowering: {e}")
     raise CompileError(
         f"{trace.name}: no sm_100a kernel implements this program yet (the generic lowering "
-        f"covers loop-free, reduction-free block arithmetic only).  Closest matches:\n  - "
+        f"covers programs without runtime loops and dots only).  Closest matches:\n  - "
         + "\n  - ".join(reasons))

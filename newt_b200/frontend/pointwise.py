@@ -1,12 +1,13 @@
-"""Generic lowering of loop-free, reduction-free block programs to CUDA text.
+"""Generic lowering of loop-free block programs to CUDA text.
 
-Everything the block language can say without `for`, `nl.dot` or a reduction is arithmetic
-on blocks of compile-time shape: loads through pointer blocks, broadcasting, elementwise math,
-`nl.where`, casts, masked stores.  Such a program needs no tuned kernel -- it is bound by HBM
-and every output element depends on a fixed expression of loaded elements -- so it is
-compiled at run time, like the reference compiles all programs: one CUDA block of
-`num_warps * 32` threads per program instance; for each `nl.store`, the threads stride over
-the elements of the stored block and evaluate the expression for their element.
+Everything the block language can say without a runtime `for` or `nl.dot` is arithmetic on
+blocks of compile-time shape: loads through pointer blocks, broadcasting, elementwise math,
+`nl.where`, casts, `nl.sum / max / min`, masked stores.  Such a program needs no tuned kernel
+-- it is bound by HBM -- so it is compiled at run time, like the reference compiles all
+programs: one CUDA block of `num_warps * 32` threads per program instance; for each `nl.store`,
+the threads stride over the elements of the stored block and evaluate the expression for their
+element.  A reduction is computed first, by the whole block, into shared memory, and read from
+there by the expressions that use it.
 
 Numerics follow the reference's elementwise rules (newt/compiler/codegen.py:1196-1284,
 2011-2030): fp16 / bf16 operations are computed in fp32 and rounded back after every
@@ -89,9 +90,10 @@ _CMP = {"lt": "<", "le": "<=", "gt": ">", "ge": ">=", "eq": "==", "ne": "!="}
 class _Body:
     """Statements that compute one element of one store."""
 
-    def __init__(self):
+    def __init__(self, reduced=None):
         self.lines = []
         self.memo = {}
+        self.reduced = reduced if reduced is not None else {}   # reduce node uid -> (array, shape)
 
     def var(self, dt, expr):
         name = f"v{len(self.lines)}"
@@ -236,18 +238,145 @@ def _emit_new(body, node, dims):
         else:
             raise Unsupported(f"operator '{fn}'")
         return body.var(dt, _convert(f"({expr})", cd, dt))
+    if op == "reduce":
+        slot = body.reduced.get(node.uid)
+        if slot is None:
+            raise Unsupported("a reduction inside a reduction's own operand chain was not materialised")
+        name, shape = slot
+        index = "0"
+        for d, extent in enumerate(shape):
+            index = f"({index} * {extent} + {dims[d]})"
+        return f"{name}[{index}]"
     raise Unsupported(f"'{op}' has no elementwise lowering")
 
 
-def _reads_from(node, seen, out):
-    """Names of the pointer parameters that `node`'s value loads from."""
+def _reads_from(node, seen, out, reduces=None):
+    """Names of the pointer parameters that `node`'s value loads from (and, in `reduces`, the
+    reductions it goes through)."""
     if not isinstance(node, Node) or node.uid in seen:
         return
     seen.add(node.uid)
     if node.op == "load":
         out.add(_base_param(node.args[0]))
+    if node.op == "reduce" and reduces is not None:
+        reduces[node.uid] = node
     for a in node.args:
-        _reads_from(a, seen, out)
+        _reads_from(a, seen, out, reduces)
+
+
+_REDUCE_HELPERS = """
+// Block-wide fold of one value per thread; the result is valid in thread 0.  OP: 0 sum, 1 max, 2 min.
+template <int OP, typename T> __device__ __forceinline__ T nb_fold(T a, T b) {
+  if (OP == 0) return a + b;
+  if (OP == 1) return a > b ? a : b;
+  return a < b ? a : b;
+}
+template <> __device__ __forceinline__ float nb_fold<1, float>(float a, float b) { return fmaxf(a, b); }
+template <> __device__ __forceinline__ float nb_fold<2, float>(float a, float b) { return fminf(a, b); }
+template <> __device__ __forceinline__ double nb_fold<1, double>(double a, double b) { return fmax(a, b); }
+template <> __device__ __forceinline__ double nb_fold<2, double>(double a, double b) { return fmin(a, b); }
+template <int OP, typename T> __device__ __forceinline__ T nb_block_reduce(T v, T* scratch) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v = nb_fold<OP, T>(v, __shfl_xor_sync(0xffffffffu, v, s));
+  const int warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  __syncthreads();                       // scratch may still be read by the previous round
+  if ((threadIdx.x & 31) == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    v = scratch[threadIdx.x < warps ? threadIdx.x : 0];
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+      const T other = __shfl_xor_sync(0xffffffffu, v, s);
+      if ((threadIdx.x ^ s) < warps && threadIdx.x < warps) v = nb_fold<OP, T>(v, other);
+    }
+  }
+  return v;
+}
+"""
+
+_REDUCE_OPS = {"sum": 0, "max": 1, "min": 2}
+
+
+def _reduce_init(fn, dt):
+    if fn == "sum":
+        return _literal(0, dt)
+    if dt.is_floating:
+        return _literal(float("-inf") if fn == "max" else float("inf"), dt)
+    bits = dt.itemsize * 8
+    if dt.kind == "u":
+        return _literal(0 if fn == "max" else 2 ** bits - 1, dt)
+    lo, hi = -(2 ** (bits - 1)), 2 ** (bits - 1) - 1
+    # INT_MIN has no literal of its own
+    return f"(({dt.ctype})({lo + 1}{'LL' if bits == 64 else ''} - 1))" if fn == "max" else _literal(hi, dt)
+
+
+def _materialise_reduce(node, name, threads, reduced):
+    """Statements that leave the result of reduction `node` in the shared array `name`."""
+    at = dict(node.attrs)
+    fn, axis = at["fn"], at["axis"]
+    if fn not in _REDUCE_OPS:
+        raise Unsupported(f"reduction '{fn}'")
+    x = node.args[0]
+    dt = node.dtype
+    shape = x.shape
+    if axis is None:                   # everything into one value
+        out_shape, length = (), 1
+        for s in shape:
+            length *= s
+    else:
+        out_shape, length = node.shape, shape[axis]
+    outs = 1
+    for s in out_shape:
+        outs *= s
+    body = _Body(reduced)
+    # index of x for output element (j0, j1, ...) and position k along the reduced extent
+    if axis is None:
+        xdims, pre, rem = [], [], "k"
+        for d in range(len(shape) - 1, 0, -1):
+            pre.append(f"const int x{d} = {rem} % {shape[d]};")
+            pre.append(f"const int y{d} = {rem} / {shape[d]};")
+            rem = f"y{d}"
+        pre.append(f"const int x0 = {rem};")
+        xdims = tuple(f"x{d}" for d in range(len(shape)))
+    else:
+        pre = []
+        js = [f"j{d}" for d in range(len(out_shape))]
+        xdims = tuple(js[:axis] + ["k"] + js[axis:])
+    val = _convert(_emit(body, x, xdims), x.dtype, dt)
+    op = _REDUCE_OPS[fn]
+    init = _reduce_init(fn, dt)
+    inner = pre + body.lines + [f"acc = nb_fold<{op}, {dt.ctype}>(acc, {val});"]
+    lines = []
+    decompose = []
+    rem = "o"
+    for d in range(len(out_shape) - 1, 0, -1):
+        decompose.append(f"const int j{d} = {rem} % {out_shape[d]};")
+        decompose.append(f"const int p{d} = {rem} / {out_shape[d]};")
+        rem = f"p{d}"
+    if out_shape:
+        decompose.append(f"const int j0 = {rem};")
+    if outs >= threads:
+        # enough results for every thread to fold one of its own, serially
+        lines.append(f"for (int o = threadIdx.x; o < {outs}; o += {threads}) {{")
+        lines += ["  " + ln for ln in decompose]
+        lines.append(f"  {dt.ctype} acc = {init};")
+        lines.append(f"  for (int k = 0; k < {length}; ++k) {{")
+        lines += ["    " + ln for ln in inner]
+        lines.append("  }")
+        lines.append(f"  {name}[o] = acc;")
+        lines.append("}")
+    else:
+        # few results: the whole block folds each of them together
+        lines.append(f"for (int o = 0; o < {outs}; ++o) {{")
+        lines += ["  " + ln for ln in decompose]
+        lines.append(f"  {dt.ctype} acc = {init};")
+        lines.append(f"  for (int k = threadIdx.x; k < {length}; k += {threads}) {{")
+        lines += ["    " + ln for ln in inner]
+        lines.append("  }")
+        lines.append(f"  acc = nb_block_reduce<{op}, {dt.ctype}>(acc, reinterpret_cast<{dt.ctype}*>(nb_scratch));")
+        lines.append(f"  if (threadIdx.x == 0) {name}[o] = acc;")
+        lines.append("}")
+    return "\n  ".join(lines), outs * dt.itemsize
 
 
 def _base_param(ptr):
@@ -273,10 +402,29 @@ def generate(trace, num_warps):
     threads = num_warps * THREADS_PER_WARP
     written = set()
     chunks = []
+    reduced = {}        # reduce node uid -> (shared array, result shape)
+    shared_decls = []
+    shared_bytes = 0
     for _, ptr, value, mask, _lineno in stores:
         reads = set()
+        reduces = {}
         for n in (value, mask, ptr):
-            _reads_from(n, set(), reads)
+            _reads_from(n, set(), reads, reduces)
+        # Reductions are materialised in shared memory, in the order they were written (node ids
+        # are in program order, so an inner reduction comes before the one that uses it).
+        for uid in sorted(reduces):
+            if uid in reduced:
+                continue
+            node = reduces[uid]
+            name = f"nb_r{len(reduced)}"
+            text, nbytes = _materialise_reduce(node, name, threads, reduced)
+            shared_bytes += nbytes
+            if shared_bytes > 40 * 1024:
+                raise Unsupported("the reductions' results do not fit in shared memory")
+            outs = max(nbytes // node.dtype.itemsize, 1)
+            shared_decls.append(f"__shared__ {node.dtype.ctype} {name}[{outs}];")
+            reduced[uid] = (name, () if dict(node.attrs)["axis"] is None else node.shape)
+            chunks.append(text)
         # Loads are evaluated inside the statement that uses them, i.e. after earlier stores of
         # the program; the source program read them before.  Refuse the programs where that
         # could differ.
@@ -289,7 +437,7 @@ def generate(trace, num_warps):
         numel = 1
         for s in shape:
             numel *= s
-        body = _Body()
+        body = _Body(reduced)
         dims = tuple(f"i{d}" for d in range(len(shape)))
         p = _emit(body, ptr, dims)
         val = _convert(_emit(body, value, _operand_dims(shape, dims, value.shape)), value.dtype,
@@ -319,10 +467,15 @@ def generate(trace, num_warps):
     decl = ", ".join(f"{t.ctype} __restrict__ {name}" if isinstance(t, tp.pointer_type)
                      else f"{t.ctype} {name}" for name, t in params)
     body_text = "\n  __syncthreads();\n  ".join(chunks)
+    helpers = ""
+    if reduced:
+        helpers = _REDUCE_HELPERS
+        shared_decls.insert(0, "__shared__ unsigned long long nb_scratch[32];")
+        body_text = "\n  ".join(shared_decls) + "\n  " + body_text
     digest = hashlib.sha1((decl + body_text).encode()).hexdigest()[:8]
     kernel_name = f"{trace.name}_{digest}"
     source = (
-        "#include <cuda_fp16.h>\n#include <cuda_bf16.h>\n\n"
+        "#include <cuda_fp16.h>\n#include <cuda_bf16.h>\n" + helpers + "\n"
         f"extern \"C\" __global__ void __launch_bounds__({threads}) {kernel_name}({decl}) {{\n  "
         f"{body_text}\n}}\n")
     return source, kernel_name, params

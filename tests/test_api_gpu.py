@@ -411,3 +411,70 @@ def test_deuteron_fused_elementwise_chain(tmp_path, monkeypatch):
     torch.cuda.synchronize()
     ref = torch.nn.functional.gelu(x.double(), approximate="tanh") + y.double()
     assert (out.cpu().double() - ref).abs().max().item() < 1e-5     # the example's own bar
+
+
+@newt.jit
+def pw_rmsnorm(x_ptr, w_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=0.0).to(nl.float32)
+    ms = nl.sum(x * x, axis=0) / N
+    y = x * nl.rsqrt(ms + eps) * nl.load(w_ptr + cols, mask=mask, other=0.0)
+    nl.store(out_ptr + row * stride + cols, y, mask=mask)
+
+
+@newt.jit
+def pw_log_softmax(x_ptr, out_ptr, N, stride, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=float("-inf"))
+    z = x - nl.max(x, axis=0)
+    nl.store(out_ptr + row * stride + cols, z - nl.log(nl.sum(nl.exp(z), axis=0)), mask=mask)
+
+
+@newt.jit
+def pw_tile_stats(x_ptr, colmax_ptr, rowsum_ptr, total_ptr, M, N, sx, BM: nl.constexpr, BN: nl.constexpr):
+    # one program per BN columns, walking BM rows: column maxima, and per program row sums + a total
+    pid = nl.program_id(0)
+    rn = pid * BN + nl.arange(0, BN)
+    rm = nl.arange(0, BM)
+    mask = (rm[:, None] < M) & (rn[None, :] < N)
+    x = nl.load(x_ptr + rm[:, None] * sx + rn[None, :], mask=mask, other=float("-inf"))
+    nl.store(colmax_ptr + rn, nl.max(x, axis=0), mask=rn < N)
+    z = nl.where(mask, x, 0.0)
+    nl.store(rowsum_ptr + pid * BM + rm, nl.sum(z, axis=1))
+    nl.store(total_ptr + pid, nl.sum(z))
+
+
+def test_generated_row_reductions():
+    m, n = 37, 1000
+    x, w = _rand((m, n), 41, torch.float16), _rand((n,), 42, torch.float16)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float16)
+    pw_rmsnorm[(m,)](x.cuda(), w.cuda(), out, n, n, 1e-6, BLOCK_N=1024, num_warps=8)
+    xf = x.float()
+    ref = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert torch_ref.rel_frobenius(out.cpu().float(), ref) <= 1e-3
+    xs = _rand((m, n), 43)
+    outs = torch.full((m, n), float("nan"), device="cuda")
+    pw_log_softmax[(m,)](xs.cuda(), outs, n, n, BLOCK_N=1024)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(outs.cpu(), torch.log_softmax(xs, -1), rtol=1e-5, atol=1e-5)
+
+
+def test_generated_reductions_over_2d_blocks():
+    m, n, bm, bn = 50, 300, 64, 128
+    x = _rand((m, n), 44)
+    progs = newt.cdiv(n, bn)
+    colmax = torch.full((n,), float("nan"), device="cuda")
+    rowsum = torch.full((progs, bm), float("nan"), device="cuda")
+    total = torch.full((progs,), float("nan"), device="cuda")
+    pw_tile_stats[(progs,)](x.cuda(), colmax, rowsum, total, m, n, n, BM=bm, BN=bn)
+    torch.cuda.synchronize()
+    assert torch.equal(colmax.cpu(), x.max(0).values)                       # max is exact
+    xp = torch.zeros(bm, progs * bn)
+    xp[:m, :n] = x
+    want_rows = xp.view(bm, progs, bn).sum(-1).t()
+    torch.testing.assert_close(rowsum.cpu(), want_rows, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(total.cpu(), want_rows.sum(-1), rtol=1e-5, atol=1e-4)

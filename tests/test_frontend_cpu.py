@@ -111,13 +111,35 @@ def test_fp32_matmul_lowers_to_the_tf32_plan():
 
 def test_unrecognised_program_raises_compile_error():
     @newt.jit
-    def block_sum(x_ptr, out_ptr, n, BLOCK: nl.constexpr):     # a reduction that is no tuned program
+    def strided_sum(x_ptr, out_ptr, n, steps, BLOCK: nl.constexpr):   # a runtime loop that is no tuned program
         offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
-        x = nl.load(x_ptr + offs, mask=offs < n, other=0.0)
-        nl.store(out_ptr + nl.program_id(0), nl.sum(x * x, axis=0))
+        acc = nl.zeros((BLOCK,), dtype=nl.float32)
+        for i in range(steps):
+            acc += nl.load(x_ptr + i * n + offs, mask=offs < n, other=0.0)
+        nl.store(out_ptr + offs, acc, mask=offs < n)
 
     with pytest.raises(newt.CompileError, match="no sm_100a kernel"):
-        block_sum.specialize(F32, F32, 100, BLOCK=128)
+        strided_sum.specialize(F32, F32, 100, 4, BLOCK=128)
+
+
+def test_reductions_outside_the_tuned_programs_are_compiled_at_run_time():
+    from newt_b200.frontend.lower import PointwisePlan
+    from newt_b200.runtime import nvrtc
+
+    @newt.jit
+    def rmsnorm(x_ptr, w_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
+        row = nl.program_id(0)
+        cols = nl.arange(0, BLOCK_N)
+        mask = cols < N
+        x = nl.load(x_ptr + row * stride + cols, mask=mask, other=0.0).to(nl.float32)
+        ms = nl.sum(x * x, axis=0) / N
+        y = x * nl.rsqrt(ms + eps) * nl.load(w_ptr + cols, mask=mask, other=0.0)
+        nl.store(out_ptr + row * stride + cols, y, mask=mask)
+
+    c = rmsnorm.specialize(F16, F16, F16, 1000, 1024, 1e-6, BLOCK_N=1024)
+    assert isinstance(c.plan, PointwisePlan)
+    assert "nb_block_reduce<0, float>" in c.plan.source and "__shared__ float nb_r0[1];" in c.plan.source
+    assert nvrtc.compile_cubin(c.plan.source, "rmsnorm.cu")[:4] == b"\x7fELF"
 
 
 def test_block_arithmetic_is_compiled_at_run_time():
