@@ -1125,6 +1125,8 @@ def lower(trace, num_warps=4, num_stages=3):
                 ("matmul", lambda: lower_gemm(trace, an, num_stages)),
                 ("attention", lambda: lower_attention(trace, an, num_stages))]
     attempts += [(n, (lambda f=f: f(trace, an, num_stages))) for n, f in _RECOGNISERS]
+    if any(e[0] == "atomic" for e in trace.effects):
+        attempts = []        # none of the tuned programs updates memory atomically
     for name, attempt in attempts:
         try:
             return attempt()

@@ -159,6 +159,20 @@ def _emit_new(body, node, dims):
         return _emit(body, child, dims[:axis] + dims[axis + 1:])
     if op == "trans":
         return _emit(body, node.args[0], (dims[1], dims[0]))
+    if op == "reshape":
+        # same elements in row-major order: linear index here -> indices of the operand
+        child = node.args[0]
+        lin = "0"
+        for d, extent in enumerate(node.shape):
+            lin = f"({lin} * {extent} + {dims[d]})"
+        lin = body.var(tp.int32, lin)
+        cdims, rem = [], lin
+        for d in range(len(child.shape) - 1, 0, -1):
+            cdims.append(body.var(tp.int32, f"{rem} % {child.shape[d]}"))
+            rem = body.var(tp.int32, f"{rem} / {child.shape[d]}")
+        if child.shape:
+            cdims.append(rem)
+        return _emit(body, child, tuple(reversed(cdims)))
     if op == "cast":
         x = node.args[0]
         return body.var(dt, _convert(sub(x), x.dtype, dt))
@@ -224,9 +238,12 @@ def _emit_new(body, node, dims):
         elif fn == "mod":
             expr = f"{x} % {y}" if cd.is_int else f"{'fmod' if cd == tp.float64 else 'fmodf'}({x}, {y})"
         elif fn == "pow":
-            if cd.is_int:
-                raise Unsupported("integer ** with a runtime exponent")
-            expr = f"{'pow' if cd == tp.float64 else 'powf'}({x}, {y})"
+            if b.op == "const" and b.args[0] == 2:     # x ** 2 is x * x (codegen.py:1254-1256)
+                expr = f"{x} * {x}"
+            elif cd.is_int:
+                raise Unsupported("integer ** needs the constant exponent 2")
+            else:
+                expr = f"{'pow' if cd == tp.float64 else 'powf'}({x}, {y})"
         elif fn in ("max", "min"):
             if cd.is_int:
                 expr = f"({x} {'>' if fn == 'max' else '<'} {y} ? {x} : {y})"
@@ -295,6 +312,19 @@ template <int OP, typename T> __device__ __forceinline__ T nb_block_reduce(T v, 
 """
 
 _REDUCE_OPS = {"sum": 0, "max": 1, "min": 2}
+
+_ATOMIC_MAX_F32 = """
+// atomicMax has no float overload: compare-and-swap until the stored value is not smaller
+__device__ __forceinline__ void nb_atomic_max_f32(float* address, float value) {
+  int* as_int = reinterpret_cast<int*>(address);
+  int seen = *as_int;
+  while (__int_as_float(seen) < value) {
+    const int before = seen;
+    seen = atomicCAS(as_int, before, __float_as_int(value));
+    if (seen == before) break;
+  }
+}
+"""
 
 
 def _reduce_init(fn, dt):
@@ -393,7 +423,7 @@ def generate(trace, num_warps):
         raise Unsupported("the program has a runtime loop")
     stores = []
     for eff in trace.effects:
-        if eff[0] != "store":
+        if eff[0] not in ("store", "atomic"):
             raise Unsupported(f"effect '{eff[0]}'")
         stores.append(eff)
     if not stores:
@@ -405,7 +435,10 @@ def generate(trace, num_warps):
     reduced = {}        # reduce node uid -> (shared array, result shape)
     shared_decls = []
     shared_bytes = 0
-    for _, ptr, value, mask, _lineno in stores:
+    uses_atomic_max_f32 = False
+    for eff in stores:
+        _, ptr, value, mask, _lineno = eff[:5]
+        atomic = eff[5] if eff[0] == "atomic" else None
         reads = set()
         reduces = {}
         for n in (value, mask, ptr):
@@ -455,7 +488,24 @@ def generate(trace, num_warps):
         else:
             lines.append("if (threadIdx.x == 0) {")
         lines += ["  " + ln for ln in body.lines]
-        store = f"*{p} = {val};"
+        elem = ptr.dtype.element
+        if atomic is None:
+            store = f"*{p} = {val};"
+        elif atomic == "add":
+            if elem == tp.int64:
+                store = f"atomicAdd(reinterpret_cast<unsigned long long*>({p}), (unsigned long long)({val}));"
+            elif elem.name in ("float32", "float64", "float16", "bfloat16", "int32", "uint32"):
+                store = f"atomicAdd({p}, {val});"
+            else:
+                raise Unsupported(f"nl.atomic_add on {elem.name}")
+        else:
+            if elem == tp.float32:
+                uses_atomic_max_f32 = True
+                store = f"nb_atomic_max_f32({p}, {val});"
+            elif elem.name in ("int32", "uint32", "int64"):
+                store = f"atomicMax({p}, {val});"
+            else:
+                raise Unsupported(f"nl.atomic_max on {elem.name}")
         lines.append(f"  if ({guard}) {store}" if guard else f"  {store}")
         lines.append("}")
         chunks.append("\n  ".join(lines))
@@ -468,8 +518,10 @@ def generate(trace, num_warps):
                      else f"{t.ctype} {name}" for name, t in params)
     body_text = "\n  __syncthreads();\n  ".join(chunks)
     helpers = ""
+    if uses_atomic_max_f32:
+        helpers += _ATOMIC_MAX_F32
     if reduced:
-        helpers = _REDUCE_HELPERS
+        helpers += _REDUCE_HELPERS
         shared_decls.insert(0, "__shared__ unsigned long long nb_scratch[32];")
         body_text = "\n  ".join(shared_decls) + "\n  " + body_text
     digest = hashlib.sha1((decl + body_text).encode()).hexdigest()[:8]

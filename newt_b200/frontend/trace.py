@@ -78,6 +78,7 @@ class Trace:
     def __init__(self, name):
         self.name = name
         self.effects = []        # ("store", ptr, value, mask, lineno) | ("for", Loop)
+                                 # | ("atomic", ptr, value, mask, lineno, "add" | "max")
         self.loops = []
         self.params = {}         # runtime parameter name -> Node
         self.constexprs = {}
@@ -603,6 +604,30 @@ class Tracer(ast.NodeVisitor):
             self.err(where, f"cannot store a {value.shape} block through {pointer.shape} pointers")
         mask = self._mask_arg(where, mask, pointer.shape)
         self.effects.append(("store", pointer, value, mask, getattr(where, "lineno", 0)))
+
+    def _atomic(self, where, fn, pointer, value, mask):
+        """nl.atomic_add / nl.atomic_max: a side effect, no value (newt/compiler/codegen.py:
+        1750-1800).  Through a scalar pointer it is one update per program and takes a scalar."""
+        if not isinstance(pointer, Node) or not pointer.is_pointer:
+            self.err(where, f"nl.atomic_{fn} needs a pointer or a block of pointers")
+        value = _unwrap_constexpr(value)
+        if not isinstance(value, Node):
+            value = self.as_node(value, pointer.dtype.element, where)
+        mask = self._mask_arg(where, mask, pointer.shape)
+        if pointer.shape == () and value.shape != ():
+            self.err(where, "scalar-pointer atomic with a block value; reduce it first")
+        try:
+            if tp.broadcast_shapes(value.shape, pointer.shape) != pointer.shape:
+                raise TypeError
+        except TypeError:
+            self.err(where, f"cannot apply a {value.shape} block through {pointer.shape} pointers")
+        self.effects.append(("atomic", pointer, value, mask, getattr(where, "lineno", 0), fn))
+
+    def b_atomic_add(self, where, pointer, value, mask=None):
+        self._atomic(where, "add", pointer, value, mask)
+
+    def b_atomic_max(self, where, pointer, value, mask=None):
+        self._atomic(where, "max", pointer, value, mask)
 
     def b_expand_dims(self, where, x, axis):
         axis = _unwrap_constexpr(axis)
