@@ -15,10 +15,10 @@ implement:
 Recognition is structural (on the expression graph, not on source text) and
 every quantity a kernel needs -- extents, strides, which argument plays which
 role -- is recovered from the graph as a polynomial in the runtime arguments
-and evaluated at launch.  A program that matches none of them and has no runtime loop
-and no dot -- block arithmetic, reductions included -- is turned into CUDA text and
-compiled at run time (pointwise.py, PointwisePlan); anything else raises CompileError
-naming what is missing.  Nothing falls back to another backend or to the CPU.
+and evaluated at launch.  A program that matches none of them -- block arithmetic,
+reductions, runtime loops, dots on shapes no tensor-core tile takes -- is turned into CUDA
+text and compiled at run time (pointwise.py, PointwisePlan); what that lowering refuses too
+raises CompileError naming what is missing.  Nothing falls back to another backend or to the CPU.
 """
 
 from .. import types as tp
@@ -768,7 +768,30 @@ class GemmPlan(Plan):
                                        cta_pair=1)
         return kernels.gemm_config(block_n=x, stages=stages)
 
+    generic = None      # set by lower(): builds the run-time compiled plan of the same program
+
     def launch(self, grid, args):
+        """Tensor-core kernel when the operands are laid out so that bulk tensor copies can
+        fetch them (unit stride along the rows, 16-byte pitches and bases); otherwise the same
+        program through the generic lowering, on the CUDA cores."""
+        from ..runtime import abi
+
+        if self._generic_plan is None:
+            try:
+                return self._launch_tensor_core(grid, args)
+            except (CompileError, abi.UnsupportedError) as e:
+                if self.generic is None:
+                    raise
+                try:
+                    self._generic_plan = self.generic()
+                except CompileError as second:
+                    raise CompileError(f"{e}; and the generic lowering does not take the program "
+                                       f"either: {second}") from e
+        self._generic_plan.launch(grid, args)
+
+    _generic_plan = None
+
+    def _launch_tensor_core(self, grid, args):
         from ..runtime import kernels
 
         m, n, k = self._extents(grid, args)
@@ -1087,14 +1110,15 @@ _RECOGNISERS = []
 
 
 class PointwisePlan(Plan):
-    """A loop-free program without dots: generated CUDA, compiled by NVRTC for sm_100a on
-    first launch, one CUDA block per program instance (frontend/pointwise.py)."""
+    """A program that is none of the tuned ones: generated CUDA, compiled by NVRTC for sm_100a
+    on first launch, one CUDA block per program instance (frontend/pointwise.py)."""
 
     kind, entry = "block arithmetic", "run-time compiled kernel (NVRTC, sm_100a)"
 
     def __init__(self, trace, num_warps):
         self.num_warps = num_warps
-        self.source, self.kernel_name, self.params = pointwise.generate(trace, num_warps)
+        self.source, self.kernel_name, self.params, self.shared_bytes = \
+            pointwise.generate(trace, num_warps)
         self._kernel = None
 
     def hardware_key(self):
@@ -1109,7 +1133,7 @@ class PointwisePlan(Plan):
             self._kernel = nvrtc.Kernel(nvrtc.compile_cubin(self.source, self.kernel_name + ".cu"),
                                         self.kernel_name)
         self._kernel.launch(grid, self.num_warps * 32, pointwise.marshal(self.params, args),
-                            torch.cuda.current_stream().cuda_stream)
+                            torch.cuda.current_stream().cuda_stream, self.shared_bytes)
 
 
 def lower(trace, num_warps=4, num_stages=3):
@@ -1127,20 +1151,28 @@ def lower(trace, num_warps=4, num_stages=3):
     attempts += [(n, (lambda f=f: f(trace, an, num_stages))) for n, f in _RECOGNISERS]
     if any(e[0] == "atomic" for e in trace.effects):
         attempts = []        # none of the tuned programs updates memory atomically
+    def generic():
+        try:
+            return PointwisePlan(trace, num_warps)
+        except pointwise.Unsupported as e:
+            raise CompileError(f"{trace.name}: {e}") from e
+
     for name, attempt in attempts:
         try:
-            return attempt()
+            plan = attempt()
+            if isinstance(plan, GemmPlan):
+                plan.generic = generic
+            return plan
         except Unmatched as e:
             reasons.append(str(e))
         except NotAffine as e:
             reasons.append(f"{name}: address arithmetic is not affine ({e})")
-    # not one of the tuned programs: block arithmetic without loops or reductions is compiled
-    # at run time
+    # not one of the tuned programs: compiled at run time by the generic lowering
     try:
         return PointwisePlan(trace, num_warps)
     except pointwise.Unsupported as e:
-        reasons.append(f"generic elementwise lowering: {e}")
+        reasons.append(f"generic lowering: {e}")
     raise CompileError(
         f"{trace.name}: no sm_100a kernel implements this program yet (the generic lowering "
-        f"covers programs without runtime loops and dots only).  Closest matches:\n  - "
+        f"refused it as well).  Closest matches:\n  - "
         + "\n  - ".join(reasons))

@@ -1,19 +1,31 @@
-"""Generic lowering of loop-free block programs to CUDA text.
+"""Generic lowering of block programs to CUDA text.
 
-Everything the block language can say without a runtime `for` or `nl.dot` is arithmetic on
-blocks of compile-time shape: loads through pointer blocks, broadcasting, elementwise math,
-`nl.where`, casts, `nl.sum / max / min`, masked stores.  Such a program needs no tuned kernel
--- it is bound by HBM -- so it is compiled at run time, like the reference compiles all
-programs: one CUDA block of `num_warps * 32` threads per program instance; for each `nl.store`,
-the threads stride over the elements of the stored block and evaluate the expression for their
-element.  A reduction is computed first, by the whole block, into shared memory, and read from
-there by the expressions that use it.
+Everything the block language can say that is not one of the tuned programs -- arithmetic on
+blocks of compile-time shape, loads through pointer blocks, broadcasting, `nl.where`, casts,
+`nl.sum / max / min`, atomics, masked stores, runtime `for` / `while` loops, `nl.dot` on shapes
+or layouts no tensor-core tile takes -- is compiled at run time, like the reference compiles
+all programs: one CUDA block of `num_warps * 32` threads per program instance.
+
+* For each `nl.store` (or atomic) the threads stride over the elements of the stored block and
+  evaluate the expression for their element, on demand, from the leaves.
+* A reduction is computed first, by the whole block, into shared memory, and read from there.
+* A runtime loop that only computes (no store, no reduction that changes per iteration) is run
+  privately by each thread for the element it is working on: carried values are registers.
+* Any other runtime loop is a C loop that all threads run together: carried scalars are
+  registers (every thread computes the same value), a carried block that moves by one scalar
+  per iteration (`ptrs += BLOCK_K * stride`) is its first value plus a running offset, other
+  carried blocks live in shared memory and are updated in place when element e only reads
+  element e, through a staging copy otherwise.
+* `nl.dot` is summed per output element on the CUDA cores (fp32 accumulation; fp32 operands
+  rounded to tf32 first).  The matmul and attention programs never come here unless their
+  operands are laid out so that bulk tensor copies cannot fetch them.
 
 Numerics follow the reference's elementwise rules (newt/compiler/codegen.py:1196-1284,
 2011-2030): fp16 / bf16 operations are computed in fp32 and rounded back after every
 operation; Python constants were already given the dtype of the block they meet by the
 tracer; integer `/` is C division; math functions are the precise single-precision ones
-(`expf`, `rsqrtf`, ...), no fast-math.
+(`expf`, `rsqrtf`, ...), no fast-math.  Control flow follows newt/compiler/codegen.py:993-1105
+(`visit_For`, `visit_While`, `visit_If`, `visit_Break`, `visit_Continue`).
 """
 
 import ctypes
@@ -87,16 +99,70 @@ _INFIX = {"add": "+", "sub": "-", "mul": "*", "and": "&", "or": "|", "xor": "^",
 _CMP = {"lt": "<", "le": "<=", "gt": ">", "ge": ">=", "eq": "==", "ne": "!="}
 
 
-class _Body:
-    """Statements that compute one element of one store."""
+class _Context:
+    """What all statement lists of one kernel share."""
 
-    def __init__(self, reduced=None):
+    def __init__(self, trace, threads):
+        self.loops = {loop.uid: loop for loop in trace.loops}
+        self.live = _live_names(trace)
+        self.threads = threads
+        self.reduced = {}      # reduce node uid -> (shared array, result shape)
+        self.final = {}        # (loop uid, carried name) -> where a finished block-level loop left it
+        self.depends = {}      # (node uid, loop uid) -> bool
+        self.pure = {}         # loop uid -> bool
+        self.helpers = set()
+        self.arrays = []       # (name, dtype, count, byte offset) in shared memory
+        self.shared_bytes = 0
+        self.counter = 0
+
+    def fresh(self, prefix="v"):
+        self.counter += 1
+        return f"{prefix}{self.counter}"
+
+    def alloc(self, dt, count, prefix):
+        """A shared-memory array of `count` elements; returns its name."""
+        name = f"{prefix}{len(self.arrays)}"
+        offset = (self.shared_bytes + 15) // 16 * 16
+        size = 8 if isinstance(dt, tp.pointer_type) else dt.itemsize
+        self.shared_bytes = offset + max(count, 1) * size
+        if self.shared_bytes > _SHARED_LIMIT:
+            raise Unsupported(f"the blocks kept across iterations and the reductions need "
+                              f"{self.shared_bytes} bytes of shared memory; a CTA has {_SHARED_LIMIT}")
+        self.arrays.append((name, dt, count, offset))
+        return name
+
+    def shared_declarations(self):
+        """Declarations of the shared arrays, and the dynamic shared memory to launch with."""
+        if not self.arrays and "reduce" not in self.helpers:
+            return [], 0
+        lines = ["__shared__ unsigned long long nb_scratch[32];"]
+        dynamic = 0
+        if self.arrays:
+            if self.shared_bytes + 256 <= _STATIC_SHARED_LIMIT:
+                lines.append(f"__shared__ __align__(16) unsigned char nb_shared[{self.shared_bytes}];")
+            else:
+                lines.append("extern __shared__ __align__(16) unsigned char nb_shared[];")
+                dynamic = self.shared_bytes
+        for name, dt, _, offset in self.arrays:
+            lines.append(f"{dt.ctype}* const {name} = reinterpret_cast<{dt.ctype}*>(nb_shared + {offset});")
+        return lines, dynamic
+
+
+class _Body:
+    """Statements that compute one element of one store (or one pass of a loop body)."""
+
+    def __init__(self, ctx, loop_state=None):
+        self.ctx = ctx
         self.lines = []
         self.memo = {}
-        self.reduced = reduced if reduced is not None else {}   # reduce node uid -> (array, shape)
+        self.reduced = ctx.reduced
+        # (loop uid, carried name) -> variable holding its current value; (loop uid, None) -> the
+        # loop variable
+        self.loop_state = dict(loop_state or {})
+        self.loop_final = {}    # (loop uid, name) -> offset form left by a loop emitted in this body
 
     def var(self, dt, expr):
-        name = f"v{len(self.lines)}"
+        name = self.ctx.fresh()
         if isinstance(dt, tp.pointer_type):
             self.lines.append(f"{dt.ctype} const {name} = {expr};")
         else:
@@ -255,30 +321,317 @@ def _emit_new(body, node, dims):
         else:
             raise Unsupported(f"operator '{fn}'")
         return body.var(dt, _convert(f"({expr})", cd, dt))
+    if op == "loopvar":
+        name = body.loop_state.get((at["loop"], None))
+        if name is None:
+            raise Unsupported("a loop variable is used outside its loop")
+        return name
+    if op == "carried":
+        st = body.loop_state.get((at["loop"], at["name"]))
+        if st is None:
+            raise Unsupported(f"loop-carried '{at['name']}' is used outside its loop")
+        return _state_value(body, st, node, dims)
+    if op == "loopout":
+        key = (at["loop"], at["name"])
+        st = body.ctx.final.get(key) or body.loop_final.get(key)
+        if st is not None:
+            return _state_value(body, st, node, dims)
+        hit = body.memo.get(("loopout",) + key + (dims,))
+        return hit if hit is not None else _emit_loop(body, node, dims)
+    if op == "dot":
+        return _emit_dot(body, node, dims)
     if op == "reduce":
         slot = body.reduced.get(node.uid)
         if slot is None:
             raise Unsupported("a reduction inside a reduction's own operand chain was not materialised")
         name, shape = slot
-        index = "0"
-        for d, extent in enumerate(shape):
-            index = f"({index} * {extent} + {dims[d]})"
-        return f"{name}[{index}]"
+        return f"{name}[{_linear(dims, shape)}]"
     raise Unsupported(f"'{op}' has no elementwise lowering")
 
 
-def _reads_from(node, seen, out, reduces=None):
-    """Names of the pointer parameters that `node`'s value loads from (and, in `reduces`, the
-    reductions it goes through)."""
-    if not isinstance(node, Node) or node.uid in seen:
-        return
-    seen.add(node.uid)
-    if node.op == "load":
-        out.add(_base_param(node.args[0]))
-    if node.op == "reduce" and reduces is not None:
-        reduces[node.uid] = node
-    for a in node.args:
-        _reads_from(a, seen, out, reduces)
+# ---- the expression graph, seen through loops -------------------------------------------
+
+_ELEMENTWISE = ("bin", "math", "where", "cast", "neg", "not", "inv", "cmp", "ptradd", "ptrsub")
+
+
+def _effect_roots(eff):
+    return [x for x in eff[1:4] if isinstance(x, Node)]
+
+
+def _live_names(trace):
+    """(loop uid, name) of the carried values something reads: a store, a loop bound or
+    condition, or the next value of another live name.  The tracer lists every name a loop
+    body assigns as carried; the ones that are only ever overwritten (`cols = start + offs`)
+    are dropped here."""
+    loops = {loop.uid: loop for loop in trace.loops}
+    live, todo = set(), []
+
+    def scan(roots):
+        seen = set()
+        stack = [r for r in roots if isinstance(r, Node)]
+        while stack:
+            n = stack.pop()
+            if n.uid in seen:
+                continue
+            seen.add(n.uid)
+            if n.op in ("carried", "loopout"):
+                at = dict(n.attrs)
+                key = (at["loop"], at["name"])
+                if key not in live:
+                    live.add(key)
+                    todo.append(key)
+            stack += [a for a in n.args if isinstance(a, Node)]
+
+    def scan_effects(effects):
+        for eff in effects:
+            if eff[0] in ("for", "while"):
+                scan([eff[1].lo, eff[1].hi, eff[1].step, eff[1].cond])
+                scan_effects(eff[1].effects)
+            else:
+                scan(_effect_roots(eff))
+
+    scan_effects(trace.effects)
+    while todo:
+        uid, name = todo.pop()
+        _, init, nxt = loops[uid].carried[name]
+        scan([init, nxt])
+    return live
+
+
+def _carried(ctx, loop):
+    """The live carried names of a loop, in a fixed order: name -> (placeholder, init, next)."""
+    return {name: loop.carried[name] for name in sorted(loop.carried) if (loop.uid, name) in ctx.live}
+
+
+def _outside_roots(ctx, loop):
+    """What a loop evaluates before its first iteration."""
+    return [x for x in [init for (_, init, _) in _carried(ctx, loop).values()] +
+            [loop.lo, loop.hi, loop.step] if isinstance(x, Node)]
+
+
+def _inside_roots(ctx, loop):
+    """What a loop evaluates every iteration, nested loops included."""
+    roots = [nxt for (_, _, nxt) in _carried(ctx, loop).values()]
+    if loop.cond is not None:
+        roots.append(loop.cond)
+    for eff in loop.effects:
+        if eff[0] in ("for", "while"):
+            roots += _outside_roots(ctx, eff[1]) + _inside_roots(ctx, eff[1])
+        else:
+            roots += _effect_roots(eff)
+    return roots
+
+
+def _walk(ctx, roots, visit):
+    """Depth-first over the nodes below `roots`; a loop result leads into the loop's own
+    expressions.  `visit(node)` returning False stops the descent below that node."""
+    seen = set()
+    todo = [r for r in roots if isinstance(r, Node)]
+    while todo:
+        n = todo.pop()
+        if n.uid in seen:
+            continue
+        seen.add(n.uid)
+        if visit(n) is False:
+            continue
+        todo += [a for a in n.args if isinstance(a, Node)]
+        if n.op == "loopout":
+            loop = ctx.loops[dict(n.attrs)["loop"]]
+            todo += _outside_roots(ctx, loop) + _inside_roots(ctx, loop)
+
+
+def _depends(ctx, node, loop_uid):
+    """Does `node` change from one iteration of loop `loop_uid` to the next?"""
+    key = (node.uid, loop_uid)
+    hit = ctx.depends.get(key)
+    if hit is None:
+        found = []
+
+        def visit(n):
+            if n.op in ("carried", "loopvar") and dict(n.attrs)["loop"] == loop_uid:
+                found.append(n)
+            return not found
+
+        _walk(ctx, [node], visit)
+        hit = ctx.depends[key] = bool(found)
+    return hit
+
+
+def _carried_below(ctx, roots, loop_uid):
+    """Names of loop `loop_uid`'s carried values that `roots` read."""
+    out = set()
+
+    def visit(n):
+        if n.op == "carried" and dict(n.attrs)["loop"] == loop_uid:
+            out.add(dict(n.attrs)["name"])
+
+    _walk(ctx, roots, visit)
+    return out
+
+
+def _nested(loop):
+    out = []
+    for eff in loop.effects:
+        if eff[0] in ("for", "while"):
+            out += [eff[1]] + _nested(eff[1])
+    return out
+
+
+def _has_effects(loop):
+    return any(eff[0] in ("store", "atomic") or (eff[0] in ("for", "while") and _has_effects(eff[1]))
+               for eff in loop.effects)
+
+
+def _is_pure(ctx, loop):
+    """A pure loop neither touches memory nor needs the whole block to work together inside an
+    iteration, so each thread can run it privately for the element it is computing."""
+    hit = ctx.pure.get(loop.uid)
+    if hit is None:
+        hit = not _has_effects(loop) and all(_is_pure(ctx, n) for n in _nested(loop))
+        if hit:
+            reduces = []
+            _walk(ctx, _inside_roots(ctx, loop), lambda n: reduces.append(n) if n.op == "reduce" else None)
+            hit = not any(_depends(ctx, r, loop.uid) for r in reduces)
+        ctx.pure[loop.uid] = hit
+    return hit
+
+
+def _induction(ph, nxt):
+    """A carried block that moves by the same scalar for all of its elements each iteration
+    (`ptrs += BLOCK_K * stride`, `offs += BLOCK`): returns (step node, '+' or '-'), else None.
+    Such a block is kept as its initial value plus one running scalar."""
+    if ph.shape == ():
+        return None
+    step, sign = None, "+"
+    if nxt.op in ("ptradd", "ptrsub") and nxt.args[0] is ph:
+        step, sign = nxt.args[1], "+" if nxt.op == "ptradd" else "-"
+    elif nxt.op == "bin" and ph.dtype.is_int and nxt.dtype == ph.dtype:
+        fn = dict(nxt.attrs)["fn"]
+        if fn == "add" and nxt.args[0] is ph:
+            step = nxt.args[1]
+        elif fn == "add" and nxt.args[1] is ph:
+            step = nxt.args[0]
+        elif fn == "sub" and nxt.args[0] is ph:
+            step, sign = nxt.args[1], "-"
+    while step is not None and step.op in ("splat", "broadcast") and step.args[0].shape == ():
+        step = step.args[0]
+    if step is None or step.shape != () or not step.dtype.is_int:
+        return None
+    return step, sign
+
+
+def _linear(dims, shape):
+    index = "0"
+    for d, extent in enumerate(shape):
+        index = f"({index} * {extent} + {dims[d]})"
+    return index
+
+
+def _state_value(body, st, node, dims):
+    """The current value of a loop-carried name for the element `dims`."""
+    if isinstance(st, str):
+        return st                                   # a register: per element, or a scalar
+    if st[0] == "ind":
+        _, init, off = st
+        base = _emit(body, init, _operand_dims(node.shape, dims, init.shape))
+        if node.is_pointer:
+            return body.var(node.dtype, f"{base} + {off}")
+        return body.var(node.dtype, f"({node.dtype.ctype})({base} + {off})")
+    _, array, shape = st                            # a block kept in shared memory
+    return f"{array}[{_linear(dims, shape)}]"
+
+
+def _emit_dot(body, node, dims):
+    """One element of `nl.dot(a, b, acc)` on the CUDA cores: the tuned tensor-core kernels take
+    the matmul and attention programs; a dot anywhere else (small tiles, odd shapes, fused
+    epilogues) is summed here in fp32, fp32 operands rounded to tf32 first as the tensor core
+    would (newt/compiler/codegen.py:2174-2201)."""
+    a, b, acc = node.args
+    ctx = body.ctx
+    i, j = dims
+    d = ctx.fresh("d")
+    first = _emit(body, acc, dims) if acc is not None else "0.0f"
+    body.lines.append(f"float {d} = {first};")
+    kk = ctx.fresh("kk")
+    inner = _Body(ctx, body.loop_state)
+    x = _convert(_emit(inner, a, (i, kk)), a.dtype, _F32)
+    y = _convert(_emit(inner, b, (kk, j)), b.dtype, _F32)
+    if a.dtype == _F32:
+        ctx.helpers.add("tf32")
+        x, y = f"nb_tf32({x})", f"nb_tf32({y})"
+    inner.lines.append(f"{d} = fmaf({x}, {y}, {d});")
+    body.lines.append(f"for (int {kk} = 0; {kk} < {a.shape[1]}; ++{kk}) {{")
+    body.lines += ["  " + ln for ln in inner.lines]
+    body.lines.append("}")
+    return d
+
+
+def _emit_loop(body, node, dims):
+    """The value a pure runtime loop leaves in one of its carried names, for one element: the
+    carried values this one depends on become local variables, updated in a C loop.  Each thread
+    walks the loop for its own element, so carried blocks need no storage of their own."""
+    ctx = body.ctx
+    at = dict(node.attrs)
+    loop = ctx.loops[at["loop"]]
+    if not _is_pure(ctx, loop):
+        raise Unsupported("the result of a loop that has not run yet")
+    want = at["name"]
+    names, todo = set(), [want]
+    while todo:
+        name = todo.pop()
+        if name in names:
+            continue
+        names.add(name)
+        todo += sorted(_carried_below(ctx, [loop.carried[name][2], loop.cond], loop.uid) - names)
+    names = sorted(names)
+    state, dims_of, steps = {}, {}, {}
+    for name in names:
+        ph, init, nxt = loop.carried[name]
+        steps[name] = _induction(ph, nxt)
+        if steps[name] is not None:
+            off = ctx.fresh("off")
+            body.lines.append(f"long long {off} = 0;")
+            state[(loop.uid, name)] = ("ind", init, off)
+            continue
+        if len(ph.shape) > len(node.shape) or any(
+                a not in (1, b) for a, b in zip(reversed(ph.shape), reversed(node.shape))):
+            raise Unsupported(f"loop-carried '{name}' {ph.shape} does not broadcast to '{want}' {node.shape}")
+        dims_of[name] = _operand_dims(node.shape, dims, ph.shape)
+        first = _emit(body, init, _operand_dims(ph.shape, dims_of[name], init.shape))
+        var = ctx.fresh("c")
+        body.lines.append(f"{ph.dtype.ctype} {var} = {first if ph.is_pointer else _convert(first, init.dtype, ph.dtype)};")
+        state[(loop.uid, name)] = var
+    inner_state = dict(body.loop_state)
+    inner_state.update(state)
+    if loop.kind == "for":
+        lo, hi, step = (_emit(body, b, ()) if isinstance(b, Node) else str(int(b))
+                        for b in (loop.lo, loop.hi, loop.step))
+        iv = ctx.fresh("k")
+        inner_state[(loop.uid, None)] = iv
+        body.lines.append(f"for (int {iv} = {lo}; ({step}) > 0 ? {iv} < {hi} : {iv} > {hi}; {iv} += {step}) {{")
+    else:
+        body.lines.append("for (;;) {")
+    inner = _Body(ctx, inner_state)
+    if loop.kind == "while":
+        inner.lines.append(f"if (!({_emit(inner, loop.cond, ())})) break;")
+    updates = []
+    for name in names:
+        ph, _, nxt = loop.carried[name]
+        if steps[name] is not None:
+            step, sign = steps[name]
+            tmp = inner.var(tp.int64, f"(long long)({_emit(inner, step, ())})")
+            updates.append(f"{state[(loop.uid, name)][2]} {sign}= {tmp};")
+            continue
+        value = _emit(inner, nxt, _operand_dims(ph.shape, dims_of[name], nxt.shape))
+        tmp = inner.var(ph.dtype, value if ph.is_pointer else _convert(value, nxt.dtype, ph.dtype))
+        updates.append(f"{state[(loop.uid, name)]} = {tmp};")
+    body.lines += ["  " + ln for ln in inner.lines + updates]
+    body.lines.append("}")
+    for name in names:     # the other carried values are now known for these indices as well
+        if steps[name] is None:
+            body.memo[("loopout", loop.uid, name, dims_of[name])] = state[(loop.uid, name)]
+    body.loop_final.update({k: v for k, v in state.items() if not isinstance(v, str)})
+    return _state_value(body, state[(loop.uid, want)], node, dims)
 
 
 _REDUCE_HELPERS = """
@@ -340,7 +693,7 @@ def _reduce_init(fn, dt):
     return f"(({dt.ctype})({lo + 1}{'LL' if bits == 64 else ''} - 1))" if fn == "max" else _literal(hi, dt)
 
 
-def _materialise_reduce(node, name, threads, reduced):
+def _materialise_reduce(node, name, threads, ctx, state=None):
     """Statements that leave the result of reduction `node` in the shared array `name`."""
     at = dict(node.attrs)
     fn, axis = at["fn"], at["axis"]
@@ -358,7 +711,7 @@ def _materialise_reduce(node, name, threads, reduced):
     outs = 1
     for s in out_shape:
         outs *= s
-    body = _Body(reduced)
+    body = _Body(ctx, state)
     # index of x for output element (j0, j1, ...) and position k along the reduced extent
     if axis is None:
         xdims, pre, rem = [], [], "k"
@@ -385,8 +738,8 @@ def _materialise_reduce(node, name, threads, reduced):
         rem = f"p{d}"
     if out_shape:
         decompose.append(f"const int j0 = {rem};")
-    if outs >= threads:
-        # enough results for every thread to fold one of its own, serially
+    if outs >= threads or length < 2 * threads:
+        # enough results for every thread to fold one of its own, or too few terms to share out
         lines.append(f"for (int o = threadIdx.x; o < {outs}; o += {threads}) {{")
         lines += ["  " + ln for ln in decompose]
         lines.append(f"  {dt.ctype} acc = {init};")
@@ -406,79 +759,71 @@ def _materialise_reduce(node, name, threads, reduced):
         lines.append(f"  acc = nb_block_reduce<{op}, {dt.ctype}>(acc, reinterpret_cast<{dt.ctype}*>(nb_scratch));")
         lines.append(f"  if (threadIdx.x == 0) {name}[o] = acc;")
         lines.append("}")
-    return "\n  ".join(lines), outs * dt.itemsize
+    return lines
 
 
-def _base_param(ptr):
-    while ptr.op in ("ptradd", "ptrsub", "broadcast", "expand", "splat", "trans"):
-        ptr = ptr.args[0]
+def _base_param(ptr, loops=None):
+    """The pointer argument a pointer value walks from (a pointer carried by a loop starts at
+    its initial value)."""
+    while True:
+        if ptr.op in ("ptradd", "ptrsub", "broadcast", "expand", "splat", "trans", "reshape"):
+            ptr = ptr.args[0]
+        elif ptr.op in ("carried", "loopout") and loops is not None:
+            at = dict(ptr.attrs)
+            ptr = loops[at["loop"]].carried[at["name"]][1]
+        else:
+            break
     if ptr.op != "param":
         raise Unsupported("a pointer that is not derived from a kernel argument")
     return dict(ptr.attrs)["name"]
 
 
-def generate(trace, num_warps):
-    """Returns (cuda_source, kernel_name, [(param name, dtype or pointer_type)])."""
-    if trace.loops:
-        raise Unsupported("the program has a runtime loop")
-    stores = []
-    for eff in trace.effects:
-        if eff[0] not in ("store", "atomic"):
-            raise Unsupported(f"effect '{eff[0]}'")
-        stores.append(eff)
-    if not stores:
-        raise Unsupported("the program stores nothing")
+_TF32_HELPER = """
+// fp32 operands of nl.dot are rounded to tf32 (10 explicit mantissa bits, ties away from zero)
+__device__ __forceinline__ float nb_tf32(float x) {
+  unsigned r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+"""
 
-    threads = num_warps * THREADS_PER_WARP
-    written = set()
-    chunks = []
-    reduced = {}        # reduce node uid -> (shared array, result shape)
-    shared_decls = []
-    shared_bytes = 0
-    uses_atomic_max_f32 = False
-    for eff in stores:
-        _, ptr, value, mask, _lineno = eff[:5]
-        atomic = eff[5] if eff[0] == "atomic" else None
-        reads = set()
-        reduces = {}
-        for n in (value, mask, ptr):
-            _reads_from(n, set(), reads, reduces)
-        # Reductions are materialised in shared memory, in the order they were written (node ids
-        # are in program order, so an inner reduction comes before the one that uses it).
-        for uid in sorted(reduces):
-            if uid in reduced:
-                continue
-            node = reduces[uid]
-            name = f"nb_r{len(reduced)}"
-            text, nbytes = _materialise_reduce(node, name, threads, reduced)
-            shared_bytes += nbytes
-            if shared_bytes > 40 * 1024:
-                raise Unsupported("the reductions' results do not fit in shared memory")
-            outs = max(nbytes // node.dtype.itemsize, 1)
-            shared_decls.append(f"__shared__ {node.dtype.ctype} {name}[{outs}];")
-            reduced[uid] = (name, () if dict(node.attrs)["axis"] is None else node.shape)
-            chunks.append(text)
-        # Loads are evaluated inside the statement that uses them, i.e. after earlier stores of
-        # the program; the source program read them before.  Refuse the programs where that
-        # could differ.
-        clash = reads & written
-        if clash:
-            raise Unsupported(f"'{sorted(clash)[0]}' is read after the program stored to it")
-        written.add(_base_param(ptr))
+_STATIC_SHARED_LIMIT = 48 * 1024
+_SHARED_LIMIT = 227 * 1024
 
-        shape = ptr.shape
+
+class _Scheduler:
+    """Writes the block-level statements of a kernel: one element loop per store, atomic or
+    reduction, and a C loop run by all threads together for every runtime loop that stores or
+    reduces inside its body.  In such a loop carried scalars are registers (every thread
+    computes the same value), carried blocks that only move by a scalar are an offset, and the
+    other carried blocks live in shared memory."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+        self.live = set()          # reductions whose shared array holds the current value
+
+    # -- pieces ---------------------------------------------------------------------------
+
+    def scalar(self, expr, state):
+        """Statements + C expression of a scalar, evaluated by every thread."""
+        if not isinstance(expr, Node):
+            return [], str(int(expr))
+        body = _Body(self.ctx, state)
+        return body.lines, _emit(body, expr, ())
+
+    def element_loop(self, shape, state, finish):
+        """`finish(body, dims)` appends the statement(s) done for each element of `shape`."""
+        threads = self.ctx.threads
         numel = 1
         for s in shape:
             numel *= s
-        body = _Body(reduced)
+        body = _Body(self.ctx, state)
         dims = tuple(f"i{d}" for d in range(len(shape)))
-        p = _emit(body, ptr, dims)
-        val = _convert(_emit(body, value, _operand_dims(shape, dims, value.shape)), value.dtype,
-                       ptr.dtype.element)
-        guard = _emit(body, mask, _operand_dims(shape, dims, mask.shape)) if mask is not None else None
+        finish(body, dims)
         lines = []
         if shape:
-            lines.append("#pragma unroll 8")
+            if not any(ln.lstrip().startswith("for (") for ln in body.lines):
+                lines.append("#pragma unroll 8")
             lines.append(f"for (int e = threadIdx.x; e < {numel}; e += {threads}) {{")
             lines.append("  int r = e;")
             for d in range(len(shape) - 1, 0, -1):
@@ -488,27 +833,284 @@ def generate(trace, num_warps):
         else:
             lines.append("if (threadIdx.x == 0) {")
         lines += ["  " + ln for ln in body.lines]
+        lines.append("}")
+        lines.append("__syncthreads();")
+        return lines
+
+    def fill(self, array, shape, value, state, dt):
+        """array[e] = value(e) for a block kept in shared memory."""
+        def finish(body, dims):
+            v = _emit(body, value, _operand_dims(shape, dims, value.shape))
+            v = v if isinstance(dt, tp.pointer_type) else _convert(v, value.dtype, dt)
+            body.lines.append(f"{array}[{_linear(dims, shape)}] = {v};")
+        return self.element_loop(shape, state, finish)
+
+    def need(self, roots, state, only=None):
+        """Materialises the reductions below `roots` that are not current, innermost first."""
+        ctx = self.ctx
+        found = {}
+
+        def visit(n):
+            if n.op == "reduce":
+                found[n.uid] = n
+            if n.op == "loopout" and (dict(n.attrs)["loop"], dict(n.attrs)["name"]) in ctx.final:
+                return False          # that loop has run; its result is read, not recomputed
+            return True
+
+        _walk(ctx, roots, visit)
+        lines = []
+        for uid in sorted(found):      # node ids follow program order: operands come first
+            node = found[uid]
+            if uid in self.live or (only is not None and not only(node)):
+                continue
+            if uid not in ctx.reduced:
+                outs = 1
+                for s in (node.shape if dict(node.attrs)["axis"] is not None else ()):
+                    outs *= s
+                name = ctx.alloc(node.dtype, outs, "nb_r")
+                ctx.reduced[uid] = (name, () if dict(node.attrs)["axis"] is None else node.shape)
+            ctx.helpers.add("reduce")
+            lines += _materialise_reduce(node, ctx.reduced[uid][0], ctx.threads, ctx, state)
+            lines.append("__syncthreads();")
+            self.live.add(uid)
+        return lines
+
+    def store(self, eff, state):
+        ctx = self.ctx
+        _, ptr, value, mask, _lineno = eff[:5]
+        atomic = eff[5] if eff[0] == "atomic" else None
         elem = ptr.dtype.element
-        if atomic is None:
-            store = f"*{p} = {val};"
-        elif atomic == "add":
-            if elem == tp.int64:
-                store = f"atomicAdd(reinterpret_cast<unsigned long long*>({p}), (unsigned long long)({val}));"
-            elif elem.name in ("float32", "float64", "float16", "bfloat16", "int32", "uint32"):
-                store = f"atomicAdd({p}, {val});"
-            else:
-                raise Unsupported(f"nl.atomic_add on {elem.name}")
-        else:
-            if elem == tp.float32:
-                uses_atomic_max_f32 = True
-                store = f"nb_atomic_max_f32({p}, {val});"
+        shape = ptr.shape
+
+        def finish(body, dims):
+            p = _emit(body, ptr, dims)
+            val = _convert(_emit(body, value, _operand_dims(shape, dims, value.shape)), value.dtype, elem)
+            guard = _emit(body, mask, _operand_dims(shape, dims, mask.shape)) if mask is not None else None
+            if atomic is None:
+                stmt = f"*{p} = {val};"
+            elif atomic == "add":
+                if elem == tp.int64:
+                    stmt = f"atomicAdd(reinterpret_cast<unsigned long long*>({p}), (unsigned long long)({val}));"
+                elif elem.name in ("float32", "float64", "float16", "bfloat16", "int32", "uint32"):
+                    stmt = f"atomicAdd({p}, {val});"
+                else:
+                    raise Unsupported(f"nl.atomic_add on {elem.name}")
+            elif elem == tp.float32:
+                ctx.helpers.add("atomic_max_f32")
+                stmt = f"nb_atomic_max_f32({p}, {val});"
             elif elem.name in ("int32", "uint32", "int64"):
-                store = f"atomicMax({p}, {val});"
+                stmt = f"atomicMax({p}, {val});"
             else:
                 raise Unsupported(f"nl.atomic_max on {elem.name}")
-        lines.append(f"  if ({guard}) {store}" if guard else f"  {store}")
-        lines.append("}")
-        chunks.append("\n  ".join(lines))
+            body.lines.append(f"if ({guard}) {stmt}" if guard else stmt)
+
+        return self.need(_effect_roots(eff), state) + self.element_loop(shape, state, finish)
+
+    # -- statements -----------------------------------------------------------------------
+
+    def run(self, effects, state):
+        lines = []
+        for eff in effects:
+            if eff[0] in ("for", "while"):
+                if not _is_pure(self.ctx, eff[1]):     # a pure loop is emitted where its results are used
+                    lines += self.block_loop(eff[1], state)
+            elif eff[0] in ("store", "atomic"):
+                lines += self.store(eff, state)
+            else:
+                raise Unsupported(f"effect '{eff[0]}'")
+        return lines
+
+    def block_loop(self, loop, state):
+        ctx = self.ctx
+        out = self.need(_outside_roots(ctx, loop), state)
+        inside = _inside_roots(ctx, loop)
+        varying = [loop.uid] + [n.uid for n in _nested(loop)]
+        # reductions the body uses but does not change are done once, before the loop
+        out += self.need(inside, state, only=lambda r: not any(_depends(ctx, r, u) for u in varying))
+        inner = dict(state)
+        scalars, inductions, blocks = [], [], []
+        carried = _carried(ctx, loop)
+        for name, (ph, init, nxt) in carried.items():
+            key = (loop.uid, name)
+            step = _induction(ph, nxt)
+            if ph.shape == ():
+                lines, v = self.scalar(init, state)
+                var = ctx.fresh("c")
+                out += lines + [f"{ph.dtype.ctype} {var} = {v if ph.is_pointer else _convert(v, init.dtype, ph.dtype)};"]
+                inner[key] = var
+                scalars.append(name)
+            elif step is not None:
+                off = ctx.fresh("off")
+                out.append(f"long long {off} = 0;")
+                inner[key] = ("ind", init, off)
+                inductions.append((name, step))
+            else:
+                numel = 1
+                for s in ph.shape:
+                    numel *= s
+                array = ctx.alloc(ph.dtype, numel, "nb_c")
+                inner[key] = ("smem", array, ph.shape)
+                out += self.fill(array, ph.shape, init, state, ph.dtype)
+                blocks.append(name)
+        if loop.kind == "for":
+            bounds = []
+            for b in (loop.lo, loop.hi, loop.step):
+                lines, v = self.scalar(b, state)
+                out += lines
+                bounds.append(v)
+            lo, hi, step = bounds
+            iv = ctx.fresh("k")
+            inner[(loop.uid, None)] = iv
+            out.append(f"for (int {iv} = {lo}; ({step}) > 0 ? {iv} < {hi} : {iv} > {hi}; {iv} += {step}) {{")
+        else:
+            out.append("for (;;) {")
+        live_outside = set(self.live)
+        body = []
+        if loop.kind == "while":
+            body += self.need([loop.cond], inner)
+            lines, v = self.scalar(loop.cond, inner)
+            body += lines + [f"if (!({v})) break;"]
+        body += self.run(loop.effects, inner)
+        # next values: everything is computed from this iteration's state before any of it changes
+        body += self.need([nxt for (_, _, nxt) in carried.values()], inner)
+        assigns = []
+        for name in scalars:
+            ph, _, nxt = loop.carried[name]
+            lines, v = self.scalar(nxt, inner)
+            tmp = ctx.fresh("t")
+            decl = f"{ph.dtype.ctype} const {tmp}" if ph.is_pointer else f"const {ph.dtype.ctype} {tmp}"
+            body += lines + [f"{decl} = {v if ph.is_pointer else _convert(v, nxt.dtype, ph.dtype)};"]
+            assigns.append(f"{inner[(loop.uid, name)]} = {tmp};")
+        for name, (step, sign) in inductions:
+            lines, v = self.scalar(step, inner)
+            tmp = ctx.fresh("t")
+            body += lines + [f"const long long {tmp} = (long long)({v});"]
+            assigns.append(f"{inner[(loop.uid, name)][2]} {sign}= {tmp};")
+        reads = {name: _carried_below(ctx, [loop.carried[name][2]], loop.uid) & set(blocks)
+                 for name in blocks}
+        copies = []
+        for name in blocks:
+            ph, _, nxt = loop.carried[name]
+            _, array, shape = inner[(loop.uid, name)]
+            in_place = _same_index_only(ctx, nxt, ph) and \
+                not any(name in reads[other] for other in blocks if other != name)
+            if in_place:       # element e is read and written by the same thread only
+                body += self.fill(array, shape, nxt, inner, ph.dtype)
+                continue
+            numel = 1
+            for s in shape:
+                numel *= s
+            staged = ctx.alloc(ph.dtype, numel, "nb_n")
+            body += self.fill(staged, shape, nxt, inner, ph.dtype)
+            copies += [f"for (int e = threadIdx.x; e < {numel}; e += {ctx.threads}) {array}[e] = {staged}[e];"]
+        if copies:
+            body += copies + ["__syncthreads();"]
+        body += assigns
+        out += ["  " + ln for ln in body]
+        out.append("}")
+        self.live = live_outside
+        for name in carried:
+            ctx.final[(loop.uid, name)] = inner[(loop.uid, name)]
+        return out
+
+
+def _same_index_only(ctx, root, ph):
+    """True when element e of `root` reads the carried block `ph` at element e only."""
+    memo = {}
+
+    def go(n, same):
+        if n is ph:
+            return same
+        if n.op == "reduce":
+            return True      # materialised before the update starts, read from its own array
+        key = (n.uid, same)
+        if key in memo:
+            return memo[key]
+        memo[key] = True
+        ok = True
+        children = [(a, same and a.shape == n.shape and
+                     (n.op in _ELEMENTWISE or (n.op == "dot" and i == 2)))
+                    for i, a in enumerate(n.args) if isinstance(a, Node)]
+        if n.op == "loopout":
+            loop = ctx.loops[dict(n.attrs)["loop"]]
+            children += [(r, False) for r in _outside_roots(ctx, loop) + _inside_roots(ctx, loop)]
+        for a, child_same in children:
+            if not go(a, child_same):
+                ok = False
+                break
+        memo[key] = ok
+        return ok
+
+    return go(root, True)
+
+
+def _check_order(ctx, effects, written):
+    """Loads are evaluated inside the statement that uses them, i.e. possibly after stores that
+    the source program placed later.  Refuses the programs where that could change a result:
+    a tensor read by a statement after another statement stored to it."""
+
+    def loads(roots):
+        out = set()
+        _walk(ctx, roots, lambda n: out.add(_base_param(n.args[0], ctx.loops)) if n.op == "load" else None)
+        return out
+
+    def in_place(eff):
+        """A statement may read the tensor it stores to only through the very pointers it
+        stores through (x[i] = f(x[i])): any other element may already be overwritten by
+        another thread."""
+        target = _base_param(eff[1], ctx.loops)
+
+        def visit(n):
+            if n.op == "load" and n.args[0] is not eff[1] and _base_param(n.args[0], ctx.loops) == target:
+                raise Unsupported(f"'{target}' is stored to and read at other elements by one statement")
+
+        _walk(ctx, _effect_roots(eff), visit)
+
+    def groups(loop):
+        """(roots, written parameter or None) for everything a loop evaluates per iteration."""
+        out = [([nxt for (_, _, nxt) in _carried(ctx, loop).values()] + [loop.cond], None)]
+        for eff in loop.effects:
+            if eff[0] in ("for", "while"):
+                out += [(_outside_roots(ctx, eff[1]), None)] + groups(eff[1])
+            else:
+                in_place(eff)
+                out.append((_effect_roots(eff), _base_param(eff[1], ctx.loops)))
+        return out
+
+    for eff in effects:
+        if eff[0] in ("for", "while"):
+            loop = eff[1]
+            if _is_pure(ctx, loop):
+                continue
+            parts = [(_outside_roots(ctx, loop), None)] + groups(loop)
+            reads = [loads(roots) for roots, _ in parts]
+            for i, (_, target) in enumerate(parts):
+                clash = set().union(*reads) & written
+                if clash:
+                    raise Unsupported(f"'{sorted(clash)[0]}' is read after the program stored to it")
+                if target is not None and any(target in r for j, r in enumerate(reads) if j != i):
+                    raise Unsupported(f"'{target}' is stored to and read by different statements "
+                                      f"of a runtime loop")
+            written |= {t for _, t in parts if t is not None}
+        else:
+            in_place(eff)
+            clash = loads(_effect_roots(eff)) & written
+            if clash:
+                raise Unsupported(f"'{sorted(clash)[0]}' is read after the program stored to it")
+            written.add(_base_param(eff[1], ctx.loops))
+
+
+def generate(trace, num_warps):
+    """Returns (cuda_source, kernel_name, [(param name, dtype or pointer_type)], bytes of
+    dynamic shared memory)."""
+    ctx = _Context(trace, num_warps * THREADS_PER_WARP)
+    if not any(eff[0] in ("store", "atomic") or (eff[0] in ("for", "while") and _has_effects(eff[1]))
+               for eff in trace.effects):
+        raise Unsupported("the program stores nothing")
+    _check_order(ctx, trace.effects, set())
+    lines = _Scheduler(ctx).run(trace.effects, {})
+    while lines and lines[-1] == "__syncthreads();":
+        lines.pop()
 
     params = [(name, node.dtype) for name, node in trace.params.items()]
     # Elements are independent, so the loads of several iterations may be issued before the
@@ -516,21 +1118,22 @@ def generate(trace, num_warps):
     # fine as long as element i is only read for element i, as in any in-place elementwise call).
     decl = ", ".join(f"{t.ctype} __restrict__ {name}" if isinstance(t, tp.pointer_type)
                      else f"{t.ctype} {name}" for name, t in params)
-    body_text = "\n  __syncthreads();\n  ".join(chunks)
     helpers = ""
-    if uses_atomic_max_f32:
+    if "atomic_max_f32" in ctx.helpers:
         helpers += _ATOMIC_MAX_F32
-    if reduced:
+    if "tf32" in ctx.helpers:
+        helpers += _TF32_HELPER
+    if "reduce" in ctx.helpers:
         helpers += _REDUCE_HELPERS
-        shared_decls.insert(0, "__shared__ unsigned long long nb_scratch[32];")
-        body_text = "\n  ".join(shared_decls) + "\n  " + body_text
+    shared, dynamic = ctx.shared_declarations()
+    body_text = "\n  ".join(shared + lines)
     digest = hashlib.sha1((decl + body_text).encode()).hexdigest()[:8]
     kernel_name = f"{trace.name}_{digest}"
     source = (
         "#include <cuda_fp16.h>\n#include <cuda_bf16.h>\n" + helpers + "\n"
-        f"extern \"C\" __global__ void __launch_bounds__({threads}) {kernel_name}({decl}) {{\n  "
+        f"extern \"C\" __global__ void __launch_bounds__({ctx.threads}) {kernel_name}({decl}) {{\n  "
         f"{body_text}\n}}\n")
-    return source, kernel_name, params
+    return source, kernel_name, params, dynamic
 
 
 _CTYPES = {"int1": ctypes.c_bool, "int8": ctypes.c_int8, "uint8": ctypes.c_uint8,

@@ -63,9 +63,11 @@ class Node:
 class Loop:
     """A `for v in range(lo, hi, step)` whose bounds are not all compile-time."""
 
-    def __init__(self, uid, lo, hi, step, lineno):
+    def __init__(self, uid, lo, hi, step, lineno, kind="for"):
         self.uid = uid
+        self.kind = kind         # "for" (range) or "while"
         self.lo, self.hi, self.step = lo, hi, step
+        self.cond = None         # while: scalar bool Node over the carried placeholders
         self.lineno = lineno
         self.var = None          # Node 'loopvar'
         self.carried = {}        # name -> (placeholder Node, init, next)
@@ -107,6 +109,15 @@ _HOST_CALLS = {"float": float, "int": int, "bool": bool, "min": min, "max": max,
                "len": len, "tuple": tuple, "list": list, "range": range, "isinstance": isinstance}
 
 
+class _PromoteScalar(Exception):
+    """Internal: a Python number is changed inside a runtime loop; trace the loop again with
+    it as a typed scalar."""
+
+    def __init__(self, name):
+        super().__init__(name)
+        self.name = name
+
+
 def _unwrap_constexpr(v):
     from .. import language as nl
 
@@ -124,6 +135,8 @@ class Tracer(ast.NodeVisitor):
         self.effects = self.trace.effects
         self.num_warps = num_warps
         self._loop_ids = 0
+        self._pred = None        # scalar bool Node: condition of the enclosing runtime `if`s
+        self._depth = 0          # enclosing loops; names the `break`/`continue` flags in env
         for name, val in constexprs.items():
             self.env[name] = _unwrap_constexpr(val)
         for name, t in runtime_types.items():
@@ -148,10 +161,68 @@ class Tracer(ast.NodeVisitor):
         return hit
 
     def run(self):
-        body = self.fndef.body
-        for stmt in body:
-            self.visit(stmt)
+        self._block(self.fndef.body)
         return self.trace
+
+    # ---- break / continue ------------------------------------------------------
+    #
+    # Each enclosing loop has two flags in the environment, "\0brk<depth>" and "\0cont<depth>"
+    # (names no source can spell): False, True, or a scalar bool node once a `break` or
+    # `continue` ran under a runtime condition.  They are ordinary variables, so the merge at
+    # the end of a runtime `if` turns `if c: break` into `brk = where(c, True, brk)`.  While a
+    # flag is a node the rest of the iteration still runs, with memory accesses masked and
+    # assignments keeping the old value where the flag is set.
+
+    def _flag(self, kind, depth=None):
+        return f"\0{kind}{self._depth if depth is None else depth}"
+
+    def _skip(self, where=None):
+        """True / False / node: are the statements that follow skipped?"""
+        acc = False
+        for depth in range(1, self._depth + 1):
+            for kind in ("brk", "cont"):
+                f = self.env.get(self._flag(kind, depth), False)
+                if f is True:
+                    return True
+                if isinstance(f, Node):
+                    acc = f if acc is False else self.binop("or", acc, f, where)
+        return acc
+
+    def _block(self, stmts):
+        for stmt in stmts:
+            if self._skip(stmt) is True:
+                return
+            self.visit(stmt)
+
+    def _jump(self, node, kind):
+        if self._depth == 0:
+            self.err(node, f"`{'break' if kind == 'brk' else 'continue'}` outside a loop")
+        skip = self._skip(node)
+        name = self._flag(kind)
+        if skip is False:
+            self.env[name] = True
+        else:       # taken only where the iteration is still live
+            live = self.node("not", (skip,), (), (), tp.int1)
+            self.env[name] = self.binop("or", self.env.get(name, False), live, node)
+
+    def visit_Break(self, node):
+        self._jump(node, "brk")
+
+    def visit_Continue(self, node):
+        self._jump(node, "cont")
+
+    @staticmethod
+    def _own_jumps(body, kind):
+        """Does `body` hold a break/continue that belongs to this loop (not to a nested one)?"""
+        todo = list(body)
+        while todo:
+            n = todo.pop()
+            if isinstance(n, kind):
+                return True
+            if isinstance(n, (ast.For, ast.While)):
+                continue
+            todo += list(ast.iter_child_nodes(n))
+        return False
 
     # ---- value helpers ---------------------------------------------------------
 
@@ -248,14 +319,32 @@ class Tracer(ast.NodeVisitor):
     def visit_Pass(self, node):
         pass
 
+    def visit_Assert(self, node):
+        pass  # host-level asserts are ignored on the device (newt/compiler/codegen.py:1104-1105)
+
     def visit_Return(self, node):
         if node.value is not None:
             self.err(node, "kernels cannot return a value")
         self.err(node, "early `return` is not supported by the sm_100a front end yet")
 
+    def _bind(self, name, value, where):
+        """`name = value`, keeping the old value where a conditional break/continue has already
+        ended the iteration."""
+        skip = self._skip(where)
+        old = self.env.get(name)
+        if isinstance(skip, Node) and old is not None and old is not value:
+            scalar = (Node, int, float, bool)
+            if not isinstance(old, scalar) or not isinstance(_unwrap_constexpr(value), scalar):
+                self.err(where, f"'{name}' is a compile-time object assigned after a conditional "
+                                f"break/continue")
+            if isinstance(old, Node) and old.is_pointer or isinstance(value, Node) and value.is_pointer:
+                self.err(where, f"pointer '{name}' is assigned after a conditional break/continue")
+            value = self.b_where(where, skip, old, value)
+        self.env[name] = value
+
     def _assign(self, target, value, where):
         if isinstance(target, ast.Name):
-            self.env[target.id] = value
+            self._bind(target.id, value, where)
         elif isinstance(target, (ast.Tuple, ast.List)):
             if not isinstance(value, (tuple, list)) or len(value) != len(target.elts):
                 self.err(where, "cannot unpack: shapes of target and value differ")
@@ -282,19 +371,59 @@ class Tracer(ast.NodeVisitor):
         op = _BINOPS.get(type(node.op))
         if op is None:
             self.err(node, f"unsupported operator {type(node.op).__name__}")
-        self.env[node.target.id] = self.binop(op, cur, self.eval(node.value), node)
+        self._bind(node.target.id, self.binop(op, cur, self.eval(node.value), node), node)
 
     def visit_If(self, node):
         cond = _unwrap_constexpr(self.eval(node.test))
         if isinstance(cond, Node):
             if cond.shape != ():
                 self.err(node, "`if` on a block: use nl.where for elementwise selection")
-            self.err(node, "`if` on a runtime scalar is not supported by the sm_100a front end yet")
-        for stmt in (node.body if cond else node.orelse):
-            self.visit(stmt)
+            return self._runtime_if(node, cond)
+        self._block(node.body if cond else node.orelse)
+
+    def _runtime_if(self, node, cond):
+        """`if` on a runtime scalar, by if-conversion: both arms are traced, loads, stores and
+        atomics inside them are masked by the (negated) condition, and every name the arms
+        leave different is merged with a select.  All programs of a grid run the same
+        instructions either way; only the taken arm touches memory."""
+        if cond.dtype != tp.int1:
+            cond = self.compare("ne", cond, 0, node)
+        before = dict(self.env)
+        outer = self._pred
+
+        def arm(stmts, c):
+            self.env = dict(before)
+            self._pred = c if outer is None else self.binop("and", outer, c, node)
+            self._block(stmts)
+            return self.env
+
+        then_env = arm(node.body, cond)
+        else_env = arm(node.orelse, self.node("not", (cond,), (), (), tp.int1))
+        self._pred = outer
+        merged = dict(before)
+        for name in sorted(set(then_env) | set(else_env)):
+            a, b = then_env.get(name, before.get(name)), else_env.get(name, before.get(name))
+            if a is b:
+                merged[name] = a
+                continue
+            if a is None or b is None:
+                merged.pop(name, None)       # defined in one arm only: unusable afterwards
+                continue
+            if not isinstance(a, (Node, int, float, bool)) or not isinstance(b, (Node, int, float, bool)):
+                if a == b:
+                    merged[name] = a
+                    continue
+                self.err(node, f"'{name}' is bound to different compile-time objects in the two "
+                               f"arms of a runtime `if`")
+            if isinstance(a, Node) and a.is_pointer or isinstance(b, Node) and b.is_pointer:
+                self.err(node, f"'{name}': a runtime `if` cannot choose between pointers")
+            merged[name] = self.b_where(node, cond, a, b)
+        self.env = merged
 
     def visit_While(self, node):
-        self.err(node, "`while` is not supported by the sm_100a front end yet")
+        if node.orelse:
+            self.err(node, "while/else is not supported")
+        self._retry_promoting(node, lambda promote: self._symbolic_loop(node, None, None, None, promote))
 
     def visit_For(self, node):
         if node.orelse:
@@ -313,26 +442,63 @@ class Tracer(ast.NodeVisitor):
             if isinstance(b, Node) and (b.shape != () or not b.dtype.is_int):
                 self.err(node, "range() bounds must be integer scalars")
         if not any(isinstance(b, Node) for b in (lo, hi, step)):
-            for i in range(lo, hi, step):     # compile-time loop: unrolled
+            self._depth += 1                  # compile-time loop: unrolled
+            brk, cont = self._flag("brk"), self._flag("cont")
+            self.env[brk] = False
+            for i in range(lo, hi, step):
+                if self.env[brk] is True:
+                    break
                 self.env[node.target.id] = i
-                for stmt in node.body:
-                    self.visit(stmt)
+                self.env[cont] = False
+                self._block(node.body)
+            # a flag that became a node has done its work: every later assignment and access
+            # of the loop was guarded by it
+            self.env.pop(cont, None)
+            self.env.pop(brk, None)
+            self._depth -= 1
             return
-        self._symbolic_loop(node, lo, hi, step)
+        self._retry_promoting(node, lambda promote: self._symbolic_loop(node, lo, hi, step, promote))
 
-    def _symbolic_loop(self, node, lo, hi, step):
+    def _retry_promoting(self, node, trace_loop):
+        """Traces a runtime loop; a Python number that the body changes is made a typed scalar
+        of the program and the loop is traced again (`s = 0; for i in range(n): s += i`)."""
+        promote = set()
+        while True:
+            env, n_eff, n_loops = dict(self.env), len(self.effects), len(self.trace.loops)
+            effects, depth, pred = self.effects, self._depth, self._pred
+            try:
+                return trace_loop(promote)
+            except _PromoteScalar as e:
+                if e.name in promote:
+                    raise
+                promote.add(e.name)
+                self.env, self.effects, self._depth, self._pred = env, effects, depth, pred
+                del self.effects[n_eff:]
+                del self.trace.loops[n_loops:]
+
+    def _symbolic_loop(self, node, lo, hi, step, promote=()):
         self._loop_ids += 1
-        loop = Loop(self._loop_ids, lo, hi, step, node.lineno)
+        is_while = isinstance(node, ast.While)
+        loop = Loop(self._loop_ids, lo, hi, step, node.lineno, "while" if is_while else "for")
         self.trace.loops.append(loop)
         assigned = set()
         for sub in node.body:
             for n in ast.walk(sub):
                 if isinstance(n, ast.Name) and isinstance(n.ctx, ast.Store):
                     assigned.add(n.id)
-        assigned.discard(node.target.id)
+        if not is_while:
+            assigned.discard(node.target.id)
+        self._depth += 1
+        brk, cont = self._flag("brk"), self._flag("cont")
+        self.env[brk] = False
+        if self._own_jumps(node.body, ast.Break):
+            self.env[brk] = self.as_node(False)     # carried: a break also ends later iterations
+            assigned.add(brk)
         placeholders = {}
         for name in sorted(assigned):
             init = self.env.get(name)
+            if name in promote and isinstance(init, (int, float)) and not isinstance(init, bool):
+                init = self.as_node(init, None, node)
             if isinstance(init, Node):
                 ph = self.node("carried", (), (("loop", loop.uid), ("name", name)), init.shape,
                                init.dtype)
@@ -340,16 +506,32 @@ class Tracer(ast.NodeVisitor):
                 self.env[name] = ph
             elif name in self.env:
                 placeholders[name] = (None, init)
-        loop.var = self.node("loopvar", (), (("loop", loop.uid),), (), tp.int32)
-        self.env[node.target.id] = loop.var
+        if is_while:
+            cond = _unwrap_constexpr(self.eval(node.test))
+            if not isinstance(cond, Node):
+                self.err(node, "`while` on a compile-time condition: " +
+                         ("it would never end" if cond else "the body never runs; remove it"))
+            if cond.shape != ():
+                self.err(node, "`while` on a block: the condition must be a scalar")
+            loop.cond = cond if cond.dtype == tp.int1 else self.compare("ne", cond, 0, node)
+            if isinstance(self.env[brk], Node):
+                loop.cond = self.binop("and", loop.cond,
+                                       self.node("not", (self.env[brk],), (), (), tp.int1), node)
+        else:
+            loop.var = self.node("loopvar", (), (("loop", loop.uid),), (), tp.int32)
+            self.env[node.target.id] = loop.var
         outer_effects, self.effects = self.effects, loop.effects
-        for stmt in node.body:
-            self.visit(stmt)
+        self.env[cont] = False
+        self._block(node.body)
         self.effects = outer_effects
+        self.env.pop(cont, None)
+        self._depth -= 1
         for name, (ph, init) in placeholders.items():
             nxt = self.env[name]
             if ph is None:
                 if nxt is not init and nxt != init:
+                    if isinstance(init, (int, float)) and not isinstance(init, bool):
+                        raise _PromoteScalar(name)
                     self.err(node, f"'{name}' is a compile-time value changed inside a runtime loop")
                 continue
             if nxt is ph:
@@ -369,7 +551,8 @@ class Tracer(ast.NodeVisitor):
             loop.carried[name] = (ph, init, nxt)
             self.env[name] = self.node("loopout", (), (("loop", loop.uid), ("name", name)),
                                        init.shape, init.dtype)
-        self.effects.append(("for", loop))
+        self.env.pop(brk, None)
+        self.effects.append(("while" if is_while else "for", loop))
 
     # ---- expressions -----------------------------------------------------------------
 
@@ -565,7 +748,7 @@ class Tracer(ast.NodeVisitor):
     def b_load(self, where, pointer, mask=None, other=None):
         if not isinstance(pointer, Node) or not pointer.is_pointer:
             self.err(where, "nl.load needs a pointer or a block of pointers")
-        mask = self._mask_arg(where, mask, pointer.shape)
+        mask = self._predicated(where, self._mask_arg(where, mask, pointer.shape))
         elem = pointer.dtype.element
         other = _unwrap_constexpr(other)
         if other is not None and not isinstance(other, Node):
@@ -591,6 +774,12 @@ class Tracer(ast.NodeVisitor):
             self.err(where, f"mask shape {mask.shape} does not broadcast to {tuple(shape)}")
         return mask
 
+    def _predicated(self, where, mask):
+        """Inside the arm of a runtime `if`, memory is only touched where the arm is taken."""
+        if self._pred is None:
+            return mask
+        return self._pred if mask is None else self.binop("and", mask, self._pred, where)
+
     def b_store(self, where, pointer, value, mask=None):
         if not isinstance(pointer, Node) or not pointer.is_pointer:
             self.err(where, "nl.store needs a pointer or a block of pointers")
@@ -602,7 +791,7 @@ class Tracer(ast.NodeVisitor):
                 raise TypeError
         except TypeError:
             self.err(where, f"cannot store a {value.shape} block through {pointer.shape} pointers")
-        mask = self._mask_arg(where, mask, pointer.shape)
+        mask = self._predicated(where, self._mask_arg(where, mask, pointer.shape))
         self.effects.append(("store", pointer, value, mask, getattr(where, "lineno", 0)))
 
     def _atomic(self, where, fn, pointer, value, mask):
@@ -613,7 +802,7 @@ class Tracer(ast.NodeVisitor):
         value = _unwrap_constexpr(value)
         if not isinstance(value, Node):
             value = self.as_node(value, pointer.dtype.element, where)
-        mask = self._mask_arg(where, mask, pointer.shape)
+        mask = self._predicated(where, self._mask_arg(where, mask, pointer.shape))
         if pointer.shape == () and value.shape != ():
             self.err(where, "scalar-pointer atomic with a block value; reduce it first")
         try:

@@ -101,6 +101,7 @@ class Kernel:
         self.cubin = cubin
         self.func_name = func_name
         self._functions = {}   # device index -> CUfunction
+        self._shared = {}      # device index -> dynamic shared memory the function is opted in for
 
     def _function(self):
         import torch
@@ -122,12 +123,20 @@ class Kernel:
                     self._functions[dev] = fn
         return fn
 
-    def launch(self, grid, block, args, stream):
-        """`args`: ctypes values in parameter order; `stream`: a CUstream handle (int)."""
+    def launch(self, grid, block, args, stream, shared_bytes=0):
+        """`args`: ctypes values in parameter order; `stream`: a CUstream handle (int);
+        `shared_bytes`: dynamic shared memory (above 48 KB the function is opted in first)."""
+        import torch
+
         cu = _load_cuda()
         fn = self._function()
+        dev = torch.cuda.current_device()
+        if shared_bytes > 48 * 1024 and self._shared.get(dev, 0) < shared_bytes:
+            # CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES = 8
+            _check(cu.cuFuncSetAttribute(fn, 8, ctypes.c_int(shared_bytes)), "cuFuncSetAttribute")
+            self._shared[dev] = shared_bytes
         g = tuple(grid) + (1,) * (3 - len(grid))
         ptrs = (ctypes.c_void_p * len(args))(*[ctypes.cast(ctypes.pointer(a), ctypes.c_void_p)
                                                for a in args])
-        _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], block, 1, 1, 0, ctypes.c_void_p(stream),
+        _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], block, 1, 1, shared_bytes, ctypes.c_void_p(stream),
                                  ptrs, None), f"launch of {self.func_name}")

@@ -111,15 +111,31 @@ def test_fp32_matmul_lowers_to_the_tf32_plan():
 
 def test_unrecognised_program_raises_compile_error():
     @newt.jit
-    def strided_sum(x_ptr, out_ptr, n, steps, BLOCK: nl.constexpr):   # a runtime loop that is no tuned program
+    def shift_through_memory(x_ptr, tmp_ptr, out_ptr, BLOCK: nl.constexpr):
+        # elements travel between threads through memory the program itself wrote: the generic
+        # lowering evaluates loads where they are used and refuses what that could reorder
+        offs = nl.arange(0, BLOCK)
+        nl.store(tmp_ptr + offs, nl.load(x_ptr + offs) * 2)
+        nl.store(out_ptr + offs, nl.load(tmp_ptr + (offs + 1) % BLOCK))
+
+    with pytest.raises(newt.CompileError, match="no sm_100a kernel"):
+        shift_through_memory.specialize(F32, F32, F32, BLOCK=128)
+
+
+def test_runtime_loop_outside_the_tuned_programs_is_compiled_at_run_time():
+    from newt_b200.frontend.lower import PointwisePlan
+
+    @newt.jit
+    def strided_sum(x_ptr, out_ptr, n, steps, BLOCK: nl.constexpr):
         offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
         acc = nl.zeros((BLOCK,), dtype=nl.float32)
         for i in range(steps):
             acc += nl.load(x_ptr + i * n + offs, mask=offs < n, other=0.0)
         nl.store(out_ptr + offs, acc, mask=offs < n)
 
-    with pytest.raises(newt.CompileError, match="no sm_100a kernel"):
-        strided_sum.specialize(F32, F32, 100, 4, BLOCK=128)
+    c = strided_sum.specialize(F32, F32, 100, 4, BLOCK=128)
+    assert isinstance(c.plan, PointwisePlan)
+    assert "for (int k" in c.plan.source
 
 
 def test_reductions_outside_the_tuned_programs_are_compiled_at_run_time():
@@ -138,7 +154,7 @@ def test_reductions_outside_the_tuned_programs_are_compiled_at_run_time():
 
     c = rmsnorm.specialize(F16, F16, F16, 1000, 1024, 1e-6, BLOCK_N=1024)
     assert isinstance(c.plan, PointwisePlan)
-    assert "nb_block_reduce<0, float>" in c.plan.source and "__shared__ float nb_r0[1];" in c.plan.source
+    assert "nb_block_reduce<0, float>" in c.plan.source and "float* const nb_r0" in c.plan.source
     assert nvrtc.compile_cubin(c.plan.source, "rmsnorm.cu")[:4] == b"\x7fELF"
 
 

@@ -1,0 +1,98 @@
+"""Control flow and dots outside the tuned kernels, without a GPU: every program of
+tests/generic_programs.py lowers to generated CUDA and NVRTC compiles it for sm_100a."""
+
+import pytest
+import torch
+
+import generic_programs as gp
+import newt_b200 as newt
+import newt_b200.language as nl
+from newt_b200 import types as tp
+from newt_b200.frontend.lower import GemmPlan, PointwisePlan
+from newt_b200.runtime import nvrtc
+
+
+def _specialize(name):
+    kernel, _grid, args, meta, _checks = gp.build(name, "cpu")
+    types = [tp.pointer_type(tp.TORCH_TO_NEWT[str(a.dtype)]) if isinstance(a, torch.Tensor) else a
+             for a in args]
+    return kernel.specialize(*types, **meta)
+
+
+@pytest.mark.parametrize("name", sorted(gp.CASES))
+def test_program_lowers_and_compiles(name):
+    plan = _specialize(name).plan
+    if isinstance(plan, GemmPlan):      # picked at launch by the operands' pitches
+        plan = plan.generic()
+    assert isinstance(plan, PointwisePlan)
+    cubin = nvrtc.compile_cubin(plan.source, name + ".cu")
+    assert len(cubin) > 1000
+
+
+def test_pure_loops_stay_in_registers():
+    """A loop that only computes is run by each thread for its own element: no shared memory,
+    no barrier; a walking pointer block is its first value plus one running offset."""
+    plan = _specialize("weighted_tiles").plan
+    assert "__syncthreads" not in plan.source and "nb_shared" not in plan.source
+    assert "long long off" in plan.source
+    plan = _specialize("ragged_matmul").plan.generic()
+    assert "nb_shared" not in plan.source and "fmaf(" in plan.source
+
+
+def test_loops_that_reduce_run_block_wide():
+    plan = _specialize("running_softmax_stats").plan
+    assert "nb_block_reduce" in plan.source or "nb_fold" in plan.source
+    assert plan.source.count("for (int k") >= 1 and "__syncthreads" in plan.source
+    plan = _specialize("small_head_attention").plan
+    assert "nb_c0" in plan.source          # the accumulator block lives in shared memory
+
+
+def test_names_only_overwritten_in_a_loop_are_not_carried():
+    plan = _specialize("tiled_layernorm").plan
+    assert isinstance(plan, PointwisePlan)
+
+
+def test_break_under_a_runtime_condition_ends_a_while_loop():
+    src = _specialize("capped_growth").plan.source
+    assert "for (;;)" in src and "break;" in src
+
+
+def test_control_flow_errors():
+    F32 = tp.pointer_type(tp.float32)
+
+    @newt.jit
+    def block_condition(x_ptr, BLOCK: nl.constexpr):
+        x = nl.load(x_ptr + nl.arange(0, BLOCK))
+        if x > 0:
+            nl.store(x_ptr + nl.arange(0, BLOCK), x)
+
+    with pytest.raises(newt.CompileError, match="nl.where"):
+        block_condition.specialize(F32, BLOCK=64)
+
+    @newt.jit
+    def pointer_choice(x_ptr, y_ptr, flag, BLOCK: nl.constexpr):
+        p = x_ptr
+        if flag == 1:
+            p = y_ptr
+        nl.store(p + nl.arange(0, BLOCK), 1.0)
+
+    with pytest.raises(newt.CompileError, match="pointers"):
+        pointer_choice.specialize(F32, F32, 1, BLOCK=64)
+
+    @newt.jit
+    def endless(x_ptr, BLOCK: nl.constexpr):
+        while True:
+            nl.store(x_ptr + nl.arange(0, BLOCK), 1.0)
+
+    with pytest.raises(newt.CompileError, match="never end"):
+        endless.specialize(F32, BLOCK=64)
+
+    @newt.jit
+    def stored_then_read(x_ptr, n, BLOCK: nl.constexpr):
+        offs = nl.arange(0, BLOCK)
+        for t in range(n):                     # each pass reads what the pass before stored
+            x = nl.load(x_ptr + offs + t)
+            nl.store(x_ptr + offs + t + 1, x)
+
+    with pytest.raises(newt.CompileError, match="stored to"):
+        stored_then_read.specialize(F32, 4, BLOCK=64)
