@@ -352,7 +352,20 @@ class _Emitter:
                 self.fail(node, "cannot resolve negative axis; use a non-negative one")
             axis += base.ndim
         if method == "mean":
-            self.fail(node, "mean() is not supported yet; use .sum(axis) / explicit size")
+            # sum over the valid lanes divided by their number (the reference leaves mean()
+            # out, deuteron/codegen.py:412-413): padded lanes count for nothing
+            arg = "" if axis is None else f", axis={axis}"
+            if base.mask:
+                total = f"nl.sum(nl.where({base.mask}, {base.code}, 0.0){arg})"
+                count = (f"nl.sum(nl.broadcast_to(nl.where({base.mask}, 1.0, 0.0), "
+                         f"({base.code}).shape){arg})")
+            else:
+                total = f"nl.sum({base.code}{arg})"
+                if base.ndim <= 0:
+                    self.fail(node, "mean() of a value whose rank is not known")
+                dims = range(base.ndim) if axis is None else [axis]
+                count = " * ".join(f"({base.code}).shape[{d}]" for d in dims)
+            return Value(f"({total} / ({count}))", None, 0 if axis is None else max(0, base.ndim - 1))
         fn, identity = dl.REDUCTIONS[method]
         inner = f"nl.where({base.mask}, {base.code}, {identity})" if base.mask else base.code
         arg = "" if axis is None else f", axis={axis}"

@@ -393,14 +393,14 @@ def _live_names(trace):
     scan_effects(trace.effects)
     while todo:
         uid, name = todo.pop()
-        _, init, nxt = loops[uid].carried[name]
+        _, init, nxt = loops[uid].values[name]
         scan([init, nxt])
     return live
 
 
 def _carried(ctx, loop):
     """The live carried names of a loop, in a fixed order: name -> (placeholder, init, next)."""
-    return {name: loop.carried[name] for name in sorted(loop.carried) if (loop.uid, name) in ctx.live}
+    return {name: triple for name, triple in sorted(loop.values.items()) if (loop.uid, name) in ctx.live}
 
 
 def _outside_roots(ctx, loop):
@@ -582,11 +582,11 @@ def _emit_loop(body, node, dims):
         if name in names:
             continue
         names.add(name)
-        todo += sorted(_carried_below(ctx, [loop.carried[name][2], loop.cond], loop.uid) - names)
+        todo += sorted(_carried_below(ctx, [loop.values[name][2], loop.cond], loop.uid) - names)
     names = sorted(names)
     state, dims_of, steps = {}, {}, {}
     for name in names:
-        ph, init, nxt = loop.carried[name]
+        ph, init, nxt = loop.values[name]
         steps[name] = _induction(ph, nxt)
         if steps[name] is not None:
             off = ctx.fresh("off")
@@ -616,7 +616,7 @@ def _emit_loop(body, node, dims):
         inner.lines.append(f"if (!({_emit(inner, loop.cond, ())})) break;")
     updates = []
     for name in names:
-        ph, _, nxt = loop.carried[name]
+        ph, _, nxt = loop.values[name]
         if steps[name] is not None:
             step, sign = steps[name]
             tmp = inner.var(tp.int64, f"(long long)({_emit(inner, step, ())})")
@@ -770,7 +770,7 @@ def _base_param(ptr, loops=None):
             ptr = ptr.args[0]
         elif ptr.op in ("carried", "loopout") and loops is not None:
             at = dict(ptr.attrs)
-            ptr = loops[at["loop"]].carried[at["name"]][1]
+            ptr = loops[at["loop"]].values[at["name"]][1]
         else:
             break
     if ptr.op != "param":
@@ -975,7 +975,7 @@ class _Scheduler:
         body += self.need([nxt for (_, _, nxt) in carried.values()], inner)
         assigns = []
         for name in scalars:
-            ph, _, nxt = loop.carried[name]
+            ph, _, nxt = loop.values[name]
             lines, v = self.scalar(nxt, inner)
             tmp = ctx.fresh("t")
             decl = f"{ph.dtype.ctype} const {tmp}" if ph.is_pointer else f"const {ph.dtype.ctype} {tmp}"
@@ -986,11 +986,11 @@ class _Scheduler:
             tmp = ctx.fresh("t")
             body += lines + [f"const long long {tmp} = (long long)({v});"]
             assigns.append(f"{inner[(loop.uid, name)][2]} {sign}= {tmp};")
-        reads = {name: _carried_below(ctx, [loop.carried[name][2]], loop.uid) & set(blocks)
+        reads = {name: _carried_below(ctx, [loop.values[name][2]], loop.uid) & set(blocks)
                  for name in blocks}
         copies = []
         for name in blocks:
-            ph, _, nxt = loop.carried[name]
+            ph, _, nxt = loop.values[name]
             _, array, shape = inner[(loop.uid, name)]
             in_place = _same_index_only(ctx, nxt, ph) and \
                 not any(name in reads[other] for other in blocks if other != name)

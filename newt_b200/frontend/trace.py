@@ -71,7 +71,14 @@ class Loop:
         self.lineno = lineno
         self.var = None          # Node 'loopvar'
         self.carried = {}        # name -> (placeholder Node, init, next)
+        self.escaping = {}       # same triples for names first bound inside the body and visible
+                                 # after the loop with their last value (zero when it never ran)
         self.effects = []        # effects issued inside the body
+
+    @property
+    def values(self):
+        """Everything the loop hands on: carried names and names that escape the body."""
+        return {**self.escaping, **self.carried}
 
 
 class Trace:
@@ -552,6 +559,18 @@ class Tracer(ast.NodeVisitor):
             self.env[name] = self.node("loopout", (), (("loop", loop.uid), ("name", name)),
                                        init.shape, init.dtype)
         self.env.pop(brk, None)
+        for name in sorted(assigned):
+            value = self.env.get(name)
+            if name in placeholders or name.startswith("\0") or not isinstance(value, Node) \
+                    or value.is_pointer:
+                continue
+            # first bound inside the body: afterwards it holds the last iteration's value
+            # (the reference declares such names before the loop, newt/compiler/codegen.py:93-157)
+            ph = self.node("carried", (), (("loop", loop.uid), ("name", name)), value.shape, value.dtype)
+            zero = self.node("full", (False if value.dtype == tp.int1 else 0,), (), value.shape, value.dtype)
+            loop.escaping[name] = (ph, zero, value)
+            self.env[name] = self.node("loopout", (), (("loop", loop.uid), ("name", name)),
+                                       value.shape, value.dtype)
         self.effects.append(("while" if is_while else "for", loop))
 
     # ---- expressions -----------------------------------------------------------------

@@ -61,6 +61,7 @@ class JITFunction:
         self.defaults = {n: p.default for n, p in params.items()
                          if p.default is not inspect.Parameter.empty}
         self.cache = {}
+        self._fast = {}      # cheap per-launch key -> (CompiledKernel, names of the tensor arguments)
 
     def __getitem__(self, grid):
         return functools.partial(self._run, grid)
@@ -166,14 +167,42 @@ class JITFunction:
         num_warps = kwargs.pop("num_warps", 4)
         num_stages = kwargs.pop("num_stages", 3)
         bound = self._bind(args, kwargs)
-        compiled, constexprs, runtime_types = self._specialization(bound, num_warps, num_stages)
+        # Launches of a specialization seen before skip type inference: the key holds the
+        # constexpr values and, per runtime argument, what its type is inferred from (the torch
+        # dtype, int32 vs int64 by value, float) -- newt/runtime/jit.py:99-144 keys the same way.
+        cset = self._constexpr_set
+        parts = []
+        for n in self.param_names:
+            v = bound[n]
+            if n in cset:
+                parts.append(v)
+            else:
+                tv = type(v)
+                if tv is int:
+                    parts.append(32 if -2147483648 <= v < 2147483648 else 64)
+                elif tv is float or tv is bool:
+                    parts.append(tv)
+                else:
+                    parts.append(getattr(v, "dtype", tv))
+        try:
+            key = (tuple(parts), num_warps, num_stages)
+            hit = self._fast.get(key)
+        except TypeError:          # an unhashable constexpr value
+            key, hit = None, None
+        if hit is None:
+            compiled, _, runtime_types = self._specialization(bound, num_warps, num_stages)
+            tensors = [n for n, t in runtime_types.items() if isinstance(t, tp.pointer_type)]
+            if key is not None and all(isinstance(bound[n], torch.Tensor) for n in tensors):
+                self._fast[key] = (compiled, tensors)
+        else:
+            compiled, tensors = hit
 
-        current = None
-        for name, t in runtime_types.items():
-            if isinstance(t, tp.pointer_type):
+        if tensors:
+            current = torch.cuda.current_device()
+            for name in tensors:
                 v = bound[name]
-                if current is None:
-                    current = torch.cuda.current_device()
+                if not v.is_cuda:
+                    raise TypeError(f"argument '{name}' must be a CUDA tensor")
                 if v.device.index not in (None, current):
                     raise ValueError(
                         f"tensor '{name}' is on {v.device} but the current device is "

@@ -419,6 +419,102 @@ def _small_head_attention(dev):
         [(o, want, 5e-3, 5e-3)], (4,)
 
 
+# ---- names, pointers and masks across control flow ---------------------------------------------
+
+@newt.jit
+def last_value(x_ptr, y_ptr, n, BLOCK: nl.constexpr):
+    offs = nl.arange(0, BLOCK)
+    for i in range(n):
+        t = nl.load(x_ptr + offs) + i      # first bound inside the loop, read after it
+    nl.store(y_ptr + offs, t)
+
+
+def _last_value(dev):
+    x = _draw(64, 30)
+    y = torch.empty(64, device=dev)
+    return (x.to(dev), y, 3), dict(BLOCK=64), [(y, x + 2, 0, 0)]
+
+
+@newt.jit
+def switch_source(a_ptr, b_ptr, out_ptr, n, BLOCK: nl.constexpr):
+    offs = nl.arange(0, BLOCK)
+    p = a_ptr + offs
+    for i in range(n):
+        nl.store(out_ptr + i * BLOCK + offs, nl.load(p))
+        p = b_ptr + offs                   # a carried pointer block that changes its tensor
+
+
+def _switch_source(dev):
+    a = _draw(64, 31)
+    b = _draw(64, 32)
+    out = torch.empty(192, device=dev)
+    return (a.to(dev), b.to(dev), out, 3), dict(BLOCK=64), [(out, torch.cat([a, b, b]), 0, 0)]
+
+
+@newt.jit
+def count_large(x_ptr, y_ptr, BLOCK: nl.constexpr):
+    offs = nl.arange(0, BLOCK)
+    big = nl.load(x_ptr + offs) > 100.0
+    nl.store(y_ptr, nl.max(big).to(nl.int32))
+    nl.store(y_ptr + 1, nl.sum(big).to(nl.int32))
+
+
+def _count_large(dev):
+    x = torch.zeros(256)
+    x[[3, 77, 130, 255]] = 500.0
+    y = torch.empty(2, device=dev, dtype=torch.int32)
+    return (x.to(dev), y), dict(BLOCK=256), [(y, torch.tensor([1, 4], dtype=torch.int32), 0, 0)]
+
+
+@newt.jit
+def bound_in_both_arms(x_ptr, y_ptr, flag, BLOCK: nl.constexpr):
+    offs = nl.arange(0, BLOCK)
+    if flag == 1:
+        t = nl.load(x_ptr + offs) * 2
+    else:
+        t = nl.load(x_ptr + offs) * 3
+    nl.store(y_ptr + offs, t)
+
+
+def _bound_in_both_arms(flag):
+    def build(dev):
+        x = _draw(64, 33)
+        y = torch.empty(64, device=dev)
+        return (x.to(dev), y, flag), dict(BLOCK=64), [(y, x * (2 if flag == 1 else 3), 0, 0)]
+    return build
+
+
+@newt.jit
+def fill_from_other_tensor(p_ptr, q_ptr, y_ptr, n, BLOCK: nl.constexpr):
+    offs = nl.arange(0, BLOCK)
+    spare = nl.load(q_ptr + offs)
+    nl.store(y_ptr + offs, nl.load(p_ptr + offs, mask=offs < n, other=spare))
+
+
+def _fill_from_other_tensor(dev):
+    p = _draw(64, 34)
+    q = _draw(64, 35)
+    y = torch.empty(64, device=dev)
+    want = torch.where(torch.arange(64) < 9, p, q)
+    return (p.to(dev), q.to(dev), y, 9), dict(BLOCK=64), [(y, want, 0, 0)]
+
+
+@newt.jit
+def small_types(a_ptr, h_ptr, oa_ptr, oh_ptr, BLOCK: nl.constexpr):
+    offs = nl.arange(0, BLOCK)
+    nl.store(oa_ptr + offs, nl.load(a_ptr + offs) + 200)     # the constant becomes uint8: wraps
+    nl.store(oh_ptr + offs, nl.load(h_ptr + offs) * 0.1)     # the constant becomes fp16
+
+
+def _small_types(dev):
+    a = torch.arange(64, dtype=torch.uint8) * 3
+    h = _draw(64, 36, torch.float16)
+    oa = torch.empty(64, device=dev, dtype=torch.uint8)
+    oh = torch.empty(64, device=dev, dtype=torch.float32)
+    want_h = (h * torch.tensor(0.1, dtype=torch.float16)).float()
+    return (a.to(dev), h.to(dev), oa, oh), dict(BLOCK=64), [(oa, a + 200, 0, 0), (oh, want_h, 0, 0)]
+
+
 CASES = {
     "weighted_tiles": (weighted_tiles, _weighted_tiles),
     "sum_of_cubes": (sum_of_cubes, _sum_of_cubes),
@@ -430,6 +526,13 @@ CASES = {
     "two_way_then": (two_way, _two_way(1)),
     "two_way_else": (two_way, _two_way(0)),
     "two_way_both": (two_way, _two_way(9)),
+    "last_value": (last_value, _last_value),
+    "switch_source": (switch_source, _switch_source),
+    "count_large": (count_large, _count_large),
+    "bound_in_both_arms_then": (bound_in_both_arms, _bound_in_both_arms(1)),
+    "bound_in_both_arms_else": (bound_in_both_arms, _bound_in_both_arms(0)),
+    "fill_from_other_tensor": (fill_from_other_tensor, _fill_from_other_tensor),
+    "small_types": (small_types, _small_types),
     "scale_tiles": (scale_tiles, _scale_tiles),
     "running_softmax_stats": (running_softmax_stats, _running_softmax_stats),
     "tiled_layernorm": (tiled_layernorm, _tiled_layernorm),

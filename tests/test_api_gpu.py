@@ -420,6 +420,38 @@ def test_deuteron_fused_elementwise_chain(tmp_path, monkeypatch):
     assert (out.cpu().double() - ref).abs().max().item() < 1e-5     # the example's own bar
 
 
+@dt.kernel
+def dt_center_rows(x, out):
+    for tile_m in dt.tile(x.shape[0]):
+        row = x[tile_m, :]
+        out[tile_m, :] = row - row.mean(1)[:, None]
+
+
+@dt.kernel(config={"BLOCK_TILE_M": 32, "BLOCK_TILE_N": 64})
+def dt_scale_by_mean(x, out):
+    for tile_m, tile_n in dt.tile([x.shape[0], x.shape[1]]):
+        block = x[tile_m, tile_n]
+        out[tile_m, tile_n] = block / block.mean()
+
+
+def test_deuteron_mean(tmp_path, monkeypatch):
+    """mean() over the valid lanes of a tile: along an axis of ragged rows, and over a whole
+    tile (every tile here is full, so each is scaled by its own mean)."""
+    monkeypatch.setenv("DEUTERON_CACHE_DIR", str(tmp_path))
+    x = _rand((37, 777), 41)
+    out = torch.full((37, 777), float("nan"), device="cuda")
+    dt_center_rows(x.cuda(), out)
+    torch.testing.assert_close(out.cpu(), x - x.mean(1, keepdim=True), rtol=1e-5, atol=1e-5)
+    x = _rand((64, 128), 42).abs() + 1.0
+    out = torch.full((64, 128), float("nan"), device="cuda")
+    dt_scale_by_mean(x.cuda(), out)
+    want = x.clone()
+    for i in range(0, 64, 32):
+        for j in range(0, 128, 64):
+            want[i:i + 32, j:j + 64] /= x[i:i + 32, j:j + 64].mean()
+    torch.testing.assert_close(out.cpu(), want, rtol=1e-5, atol=1e-6)
+
+
 @newt.jit
 def pw_rmsnorm(x_ptr, w_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
     row = nl.program_id(0)

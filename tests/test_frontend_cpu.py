@@ -346,6 +346,27 @@ def test_deuteron_row_programs_lower_to_row_kernels():
         ("nb200_layernorm",)
 
 
+@dt.kernel
+def dt_center_rows(x, out):
+    for tile_m in dt.tile(x.shape[0]):
+        row = x[tile_m, :]
+        out[tile_m, :] = row - row.mean(1)[:, None]
+
+
+def test_deuteron_mean_counts_valid_lanes_only():
+    # mean() is what the reference leaves out (deuteron/codegen.py:412-413)
+    from newt_b200.runtime import nvrtc
+
+    x, out = torch.randn(10, 77), torch.empty(10, 77)
+    src = dt_center_rows.to_newt_source(x, out)
+    assert "nl.where(mask_tile_m[:, None] & mask_full0[None, :], 1.0, 0.0)" in src
+    plan, grid, _ = _plan_of(dt_center_rows, (x, out), dt.Config(BLOCK_TILE_M=4), F32)
+    assert isinstance(plan, lower.PointwisePlan) and grid == (3,)
+    assert nvrtc.compile_cubin(plan.source, "center_rows.cu")[:4] == b"\x7fELF"
+    dt_center_rows.ref(x, out)
+    torch.testing.assert_close(out, x - x.mean(1, keepdim=True))
+
+
 def test_deuteron_eager_reference_runs_on_host_tensors():
     x, y = torch.randn(64, 48).half(), torch.randn(48, 32).half()
     out = torch.empty(64, 32).half()
