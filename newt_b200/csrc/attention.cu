@@ -559,8 +559,7 @@ int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   const long long pairs = ((long long)p.bh * p.n_q_tiles + 1) / 2;
   if (pairs < grid) grid = (int)pairs;
   auto go = [&](auto kern) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return cuda_check(e, "attention smem attribute");
+    if (int rc = prepare_kernel((const void*)kern, smem)) return rc;
     kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
     return cuda_check(cudaGetLastError(), "attention launch");
   };

@@ -32,6 +32,14 @@ int tuning(const char* key, int dflt);
 // [0] = first error code (0 = none), [1] = detail (role / barrier / tile).
 unsigned int* device_status_ptr();
 
+// Opts `kernel` in for `smem_bytes` of dynamic shared memory, once per device and size (the
+// attribute call costs microseconds; a launch-bound GEMM should not pay it every time).
+int prepare_kernel(const void* kernel, int smem_bytes);
+
+// How many clusters of the launch described by `config` fit on the device at once
+// (cudaOccupancyMaxActiveClusters, remembered per device, kernel and shared-memory size).
+int cluster_capacity(const void* kernel, const cudaLaunchConfig_t* config, int* clusters);
+
 static inline int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // ---- device side -----------------------------------------------------------

@@ -630,8 +630,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
            cudaStream_t stream) {
   const int smem = smem_bytes_for(BN, STAGES);
   auto go = [&](auto kern) {
-    if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
-      return cuda_check(e, "gemm smem attribute");
+    if (int rc = prepare_kernel((const void*)kern, smem)) return rc;
     kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
     return cuda_check(cudaGetLastError(), "gemm launch");
   };
@@ -647,8 +646,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   const void* kern = dtype == NB200_BF16 ? (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_BF16>
                      : dtype == NB200_F32 ? (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_F32>
                                           : (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_F16>;
-  if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))
-    return cuda_check(e, "gemm pair smem attribute");
+  if (int rc = prepare_kernel(kern, smem)) return rc;
   cudaLaunchConfig_t lc = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -663,8 +661,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   // as many pairs as the device can hold at once, never more than there are tiles
   lc.gridDim = dim3(2);
   int clusters = 0;
-  if (cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, kern, &lc))
-    return cuda_check(e, "cluster occupancy query");
+  if (int rc = cluster_capacity(kern, &lc, &clusters)) return rc;
   if (clusters < 1) return fail(NB200_E_CUDA, "gemm: the device cannot host a CTA pair");
   const long long tiles = (long long)cdiv64(p.m, 2 * kBlockM) * p.n_blocks;
   if (tiles < clusters) clusters = (int)tiles;

@@ -408,9 +408,7 @@ int launch_row_variant(const RowParams& p, cudaStream_t stream) {
       smem = want_smem;
       q.wb_in_smem = 1;
       if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return cuda_check(e, "raise dynamic shared memory limit");
+        if (int rc = prepare_kernel((const void*)kern, (int)smem)) return rc;
       }
     }
   }

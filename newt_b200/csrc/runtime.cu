@@ -56,10 +56,67 @@ int tuning(const char* key, int dflt) {
 }
 
 unsigned int* device_status_ptr() {
-  // resolved per call: the symbol has one instance per device context
+  // the symbol has one instance per device context: resolved once per device
+  static std::map<int, unsigned int*> known;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = known.find(dev);
+  if (it != known.end()) return it->second;
   unsigned int* p = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status) != cudaSuccess) return nullptr;
+  known[dev] = p;
   return p;
+}
+
+namespace {
+struct KernelKey {
+  int device;
+  const void* kernel;
+  int smem;
+  bool operator<(const KernelKey& o) const {
+    if (device != o.device) return device < o.device;
+    if (kernel != o.kernel) return kernel < o.kernel;
+    return smem < o.smem;
+  }
+};
+std::map<KernelKey, int> g_prepared;   // value: cluster capacity, or -1 when not asked yet
+}  // namespace
+
+int prepare_kernel(const void* kernel, int smem_bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const KernelKey key{dev, kernel, smem_bytes};
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_prepared.count(key)) return 0;
+  }
+  if (cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes))
+    return cuda_check(e, "shared-memory attribute");
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_prepared.emplace(key, -1);
+  return 0;
+}
+
+int cluster_capacity(const void* kernel, const cudaLaunchConfig_t* config, int* clusters) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const KernelKey key{dev, kernel, (int)config->dynamicSmemBytes};
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_prepared.find(key);
+    if (it != g_prepared.end() && it->second >= 0) {
+      *clusters = it->second;
+      return 0;
+    }
+  }
+  int count = 0;
+  if (cudaError_t e = cudaOccupancyMaxActiveClusters(&count, kernel, config))
+    return cuda_check(e, "cluster occupancy query");
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_prepared[key] = count;
+  *clusters = count;
+  return 0;
 }
 
 }  // namespace nb200

@@ -762,11 +762,16 @@ class GemmPlan(Plan):
     def config(self):
         from ..runtime import kernels
 
-        kind, x, stages = self.hardware_key()
-        if kind == "gemm-pair":
-            return kernels.gemm_config(block_m=256, block_n=256, block_k=x, stages=stages,
-                                       cta_pair=1)
-        return kernels.gemm_config(block_n=x, stages=stages)
+        if self._config is None:
+            kind, x, stages = self.hardware_key()
+            if kind == "gemm-pair":
+                self._config = kernels.gemm_config(block_m=256, block_n=256, block_k=x,
+                                                   stages=stages, cta_pair=1)
+            else:
+                self._config = kernels.gemm_config(block_n=x, stages=stages)
+        return self._config
+
+    _config = None
 
     generic = None      # set by lower(): builds the run-time compiled plan of the same program
 
@@ -1132,8 +1137,11 @@ class PointwisePlan(Plan):
         if self._kernel is None:
             self._kernel = nvrtc.Kernel(nvrtc.compile_cubin(self.source, self.kernel_name + ".cu"),
                                         self.kernel_name)
+        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        stream = raw(torch.cuda.current_device()) if raw is not None \
+            else torch.cuda.current_stream().cuda_stream
         self._kernel.launch(grid, self.num_warps * 32, pointwise.marshal(self.params, args),
-                            torch.cuda.current_stream().cuda_stream, self.shared_bytes)
+                            stream, self.shared_bytes)
 
 
 def lower(trace, num_warps=4, num_stages=3):

@@ -221,7 +221,18 @@ class JITFunction:
             raise ValueError(f"grids have at most 3 dimensions, got {g}")
         if any(x <= 0 for x in g):
             return
-        compiled.plan.launch(g, bound)
+        if tensors:
+            global _checked_tensors
+            if _checked_tensors is None:
+                from . import kernels
+                _checked_tensors = kernels.checked_tensors()
+            with _checked_tensors:
+                compiled.plan.launch(g, bound)
+        else:
+            compiled.plan.launch(g, bound)
+
+
+_checked_tensors = None
 
 
 def jit(fn=None):

@@ -6,17 +6,37 @@ CUDA device and they never allocate.
 """
 
 import ctypes
+import threading
 
 import torch
 
 from . import abi
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_trust = threading.local()     # .checked: the JIT launcher has verified the tensors of this launch
+
+
 def _stream():
+    if _raw_stream is not None:      # the handle without building a torch.cuda.Stream object
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class checked_tensors:
+    """Inside this block `_dev_ptr` takes tensors as already verified (CUDA, current device):
+    the JIT launcher checks every tensor argument once per launch (runtime/jit.py `_run`)."""
+
+    def __enter__(self):
+        _trust.checked = True
+
+    def __exit__(self, *exc):
+        _trust.checked = False
+
+
 def _dev_ptr(name, t):
+    if getattr(_trust, "checked", False):
+        return ctypes.c_void_p(t.data_ptr())
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise TypeError(f"argument '{name}' must be a CUDA tensor")
     if t.device.index not in (None, torch.cuda.current_device()):
