@@ -490,7 +490,12 @@ def run_gpu(args, wl):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        time.sleep(0.3)      # nvidia-smi needs a few hundred ms to come up
+    barrier()
+    # one more untimed step on every rank: the pause above let the GPU drop to an idle power
+    # state, and the first launch after it pays for the ramp
+    flush.zero_()
+    wl.step(dev)
 
     # ---- device-resident timed region: K steps, one event pair per step ------
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]

@@ -157,6 +157,15 @@ int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int64_t m, int
                            int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
                            const nb200_gemm_config* config, void* stream);
 
+/* dst[r][c] = src[r * row_stride + c * col_stride] for 2- or 4-byte elements (strides and
+ * dst_pitch in elements): copies a matrix given with any two strides -- a row pitch that is
+ * not a multiple of 16 bytes, a misaligned base, a transposed A -- into a row-major buffer
+ * the caller owns, so that nb200_gemm can fetch it.  (No counterpart in the reference, whose
+ * cp.async staging takes any stride, newt/compiler/codegen.py:2560-2654; bulk tensor copies do
+ * not.)  Moves 2 * elem_bytes per element. */
+int nb200_repitch(const void* src, void* dst, int64_t rows, int64_t cols, int64_t row_stride,
+                  int64_t col_stride, int64_t dst_pitch, int elem_bytes, void* stream);
+
 /* Returns 0 when (dtype, shape, strides, pointers, config) can run on the
  * TMA/tcgen05 path, else NB200_E_* with the reason in nb200_last_error().
  * Launches nothing; lets an autotuner discard configurations analytically

@@ -723,6 +723,61 @@ int encode_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int ra
 
 using namespace nb200;
 
+namespace nb200 {
+namespace {
+
+// dst[r][c] = src[r * row_stride + c * col_stride]: a matrix given with any two strides is
+// copied into a row-major one whose pitch bulk tensor copies accept.  64 x 64 tiles through
+// shared memory, walked along whichever source direction is the closer to unit stride, so
+// that both the reads and the writes coalesce.  HBM-bound: 2 * sizeof(T) bytes per element.
+template <typename T>
+__global__ void __launch_bounds__(256) repitch_kernel(const T* __restrict__ src, T* __restrict__ dst,
+                                                      int rows, int cols, long long row_stride,
+                                                      long long col_stride, long long dst_pitch) {
+  __shared__ T tile[64][64 + 4 / sizeof(T)];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const bool along_rows = col_stride > row_stride;     // a transposed source
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int r = along_rows ? (i & 63) : (i >> 6), c = along_rows ? (i >> 6) : (i & 63);
+    if (r0 + r < rows && c0 + c < cols)
+      tile[r][c] = src[(long long)(r0 + r) * row_stride + (long long)(c0 + c) * col_stride];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int r = i >> 6, c = i & 63;
+    if (r0 + r < rows && c0 + c < cols) dst[(long long)(r0 + r) * dst_pitch + c0 + c] = tile[r][c];
+  }
+}
+
+}  // namespace
+}  // namespace nb200
+
+extern "C" int nb200_repitch(const void* src, void* dst, int64_t rows, int64_t cols,
+                             int64_t row_stride, int64_t col_stride, int64_t dst_pitch,
+                             int elem_bytes, void* stream) {
+  if (elem_bytes != 2 && elem_bytes != 4)
+    return fail(NB200_E_UNSUPPORTED, "repitch: elements of %d bytes (2 or 4)", elem_bytes);
+  if (rows < 0 || cols < 0 || rows > INT32_MAX || cols > INT32_MAX)
+    return fail(NB200_E_INVALID, "repitch: extent out of range");
+  if (rows == 0 || cols == 0) return 0;
+  if (!src || !dst) return fail(NB200_E_INVALID, "repitch: null pointer");
+  if (dst_pitch < cols) return fail(NB200_E_INVALID, "repitch: destination pitch smaller than a row");
+  if (row_stride < 0 || col_stride < 0) return fail(NB200_E_UNSUPPORTED, "repitch: negative stride");
+  const long long gx = cdiv64(cols, 64), gy = cdiv64(rows, 64);
+  if (gy > 65535) return fail(NB200_E_UNSUPPORTED, "repitch: more than 65535 * 64 rows");
+  const dim3 grid((unsigned)gx, (unsigned)gy);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (elem_bytes == 2)
+    repitch_kernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(src),
+                                                  static_cast<uint16_t*>(dst), (int)rows, (int)cols,
+                                                  row_stride, col_stride, dst_pitch);
+  else
+    repitch_kernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(src),
+                                                  static_cast<uint32_t*>(dst), (int)rows, (int)cols,
+                                                  row_stride, col_stride, dst_pitch);
+  return cuda_check(cudaGetLastError(), "repitch launch");
+}
+
 extern "C" int nb200_gemm_check(const void* a, const void* b, const void* c, int64_t m, int64_t n,
                                 int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int dtype,
                                 const nb200_gemm_config* config) {

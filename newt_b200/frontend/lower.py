@@ -776,9 +776,10 @@ class GemmPlan(Plan):
     generic = None      # set by lower(): builds the run-time compiled plan of the same program
 
     def launch(self, grid, args):
-        """Tensor-core kernel when the operands are laid out so that bulk tensor copies can
-        fetch them (unit stride along the rows, 16-byte pitches and bases); otherwise the same
-        program through the generic lowering, on the CUDA cores."""
+        """The tensor-core kernel, after copying operands that bulk tensor copies cannot fetch
+        as they lie (see `_launch_tensor_core`); what that path still refuses -- a C that is not
+        unit-stride along its rows -- runs the same program through the generic lowering, on
+        the CUDA cores."""
         from ..runtime import abi
 
         if self._generic_plan is None:
@@ -804,23 +805,35 @@ class GemmPlan(Plan):
             return
         inner = {name: fn(args) for name, fn in self.inner}
         lda, ldb, ldc = self.lda(args), self.ldb(args), self.ldc(args)
-        for name in (self.a, self.c):
-            if inner[name] != 1:
-                raise CompileError(
-                    f"matmul: '{name}' is not unit-stride along its fast dimension "
-                    f"(stride {inner[name]}); only B may be passed transposed")
+        if inner[self.c] != 1:
+            raise CompileError(
+                f"matmul: '{self.c}' is not unit-stride along its fast dimension "
+                f"(stride {inner[self.c]})")
         a, b, c = args[self.a], args[self.b], args[self.c]
-        if inner[self.b] != 1:
+        per16 = 16 // a.element_size()
+
+        def fetchable(t, pitch, unit):      # what a bulk tensor copy needs of an operand
+            return unit == 1 and pitch % per16 == 0 and t.data_ptr() % 16 == 0
+
+        # An operand laid out otherwise (a pitch that is not a multiple of 16 bytes, a
+        # misaligned base, a transposed A) is first copied into a row-major workspace.
+        if not fetchable(a, lda, inner[self.a]):
+            a, lda = kernels.repitched("a", a, m, k, lda, inner[self.a])
+            self.repitched += 1
+        if fetchable(b, inner[self.b], ldb) and inner[self.b] != 1:
             # B[k, n] at k * 1 + n * stride: the caller handed over B^T, which is what the
             # tensor core wants anyway
-            if ldb != 1:
-                raise CompileError(
-                    f"matmul: '{self.b}' has strides ({ldb}, {inner[self.b]}); one of them must be 1")
             kernels.gemm_bt(a, b, c, m, n, k, lda, inner[self.b], ldc, self.config())
-        elif self.row_k == 32:
+            return
+        if not fetchable(b, ldb, inner[self.b]):
+            b, ldb = kernels.repitched("b", b, k, n, ldb, inner[self.b])
+            self.repitched += 1
+        if self.row_k == 32:
             kernels.gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, self.config())
         else:
             kernels.gemm(a, b, c, m, n, k, lda, ldb, ldc, self.config())
+
+    repitched = 0       # how many operands launches of this plan had to copy first
 
 
 def lower_gemm(trace, an, num_stages):

@@ -111,6 +111,7 @@ class _Context:
         self.depends = {}      # (node uid, loop uid) -> bool
         self.pure = {}         # loop uid -> bool
         self.helpers = set()
+        self.staging = set()   # nodes whose shared-memory copy is being written right now
         self.arrays = []       # (name, dtype, count, byte offset) in shared memory
         self.shared_bytes = 0
         self.counter = 0
@@ -183,6 +184,9 @@ def _operand_dims(node_shape, dims, operand_shape):
 def _emit(body, node, dims):
     if not isinstance(node, Node):
         raise Unsupported(f"non-node operand {node!r}")
+    if node.op != "reduce" and node.uid in body.reduced and node.uid not in body.ctx.staging:
+        array, shape = body.reduced[node.uid]     # staged in shared memory by the scheduler
+        return f"{array}[{_linear(dims, shape)}]"
     key = (node.uid, dims)
     hit = body.memo.get(key)
     if hit is not None:
@@ -520,6 +524,14 @@ def _induction(ph, nxt):
     return step, sign
 
 
+def _is_cheap(node):
+    """Loaded (or constant) data, possibly cast or reshuffled: cheaper to fetch again than to
+    stage."""
+    while node.op in ("cast", "trans", "broadcast", "expand", "splat", "reshape"):
+        node = node.args[0]
+    return node.op in ("load", "const", "full", "param", "arange")
+
+
 def _linear(dims, shape):
     index = "0"
     for d, extent in enumerate(shape):
@@ -846,22 +858,49 @@ class _Scheduler:
         return self.element_loop(shape, state, finish)
 
     def need(self, roots, state, only=None):
-        """Materialises the reductions below `roots` that are not current, innermost first."""
+        """Materialises what the expressions below `roots` read from shared memory and is not
+        current: reductions, and operands of `nl.dot` that are computed rather than loaded
+        (attention's P in P @ V) -- a dot reads each operand element once per output column
+        or row, so computing it in place would repeat that work that many times."""
         ctx = self.ctx
         found = {}
-
-        def visit(n):
+        seen = set()
+        todo = [(r, False) for r in roots if isinstance(r, Node)]
+        while todo:
+            n, in_pure = todo.pop()
+            if (n.uid, in_pure) in seen:
+                continue
+            seen.add((n.uid, in_pure))
             if n.op == "reduce":
                 found[n.uid] = n
-            if n.op == "loopout" and (dict(n.attrs)["loop"], dict(n.attrs)["name"]) in ctx.final:
-                return False          # that loop has run; its result is read, not recomputed
-            return True
-
-        _walk(ctx, roots, visit)
+            if n.op == "dot" and not in_pure:
+                for operand in n.args[:2]:
+                    if not _is_cheap(operand):
+                        found[operand.uid] = operand
+            todo += [(a, in_pure) for a in n.args if isinstance(a, Node)]
+            if n.op == "loopout":
+                at = dict(n.attrs)
+                if (at["loop"], at["name"]) in ctx.final:
+                    continue          # that loop has run; its result is read, not recomputed
+                loop = ctx.loops[at["loop"]]
+                # what a pure loop computes from its own state stays in the thread that runs it
+                todo += [(r, in_pure) for r in _outside_roots(ctx, loop)]
+                todo += [(r, True) for r in _inside_roots(ctx, loop)]
         lines = []
         for uid in sorted(found):      # node ids follow program order: operands come first
             node = found[uid]
             if uid in self.live or (only is not None and not only(node)):
+                continue
+            if node.op != "reduce":
+                if uid not in ctx.reduced:
+                    numel = 1
+                    for s in node.shape:
+                        numel *= s
+                    ctx.reduced[uid] = (ctx.alloc(node.dtype, numel, "nb_s"), node.shape)
+                ctx.staging.add(uid)
+                lines += self.fill(ctx.reduced[uid][0], node.shape, node, state, node.dtype)
+                ctx.staging.discard(uid)
+                self.live.add(uid)
                 continue
             if uid not in ctx.reduced:
                 outs = 1

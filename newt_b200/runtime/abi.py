@@ -62,6 +62,7 @@ SIGNATURES = {
                                        ctypes.POINTER(GemmConfig), _vp, _i64, _vp]),
     "nb200_gemm_tf32_static": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                               ctypes.POINTER(GemmConfig), _vp]),
+    "nb200_repitch": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, _vp]),
     "nb200_gemm_check": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                         ctypes.c_int, ctypes.POINTER(GemmConfig)]),
     "nb200_attention_fwd": (ctypes.c_int, [_vp, _vp, _vp, _vp] + [_i64] * 12 +

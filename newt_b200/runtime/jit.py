@@ -62,6 +62,8 @@ class JITFunction:
                          if p.default is not inspect.Parameter.empty}
         self.cache = {}
         self._fast = {}      # cheap per-launch key -> (CompiledKernel, names of the tensor arguments)
+        self._name_set = set(self.param_names)
+        self._is_constexpr = [n in self._constexpr_set for n in self.param_names]
 
     def __getitem__(self, grid):
         return functools.partial(self._run, grid)
@@ -75,6 +77,13 @@ class JITFunction:
 
     def _bind(self, args, kwargs):
         names = self.param_names
+        if not self.defaults and len(args) + len(kwargs) == len(names):
+            # the usual call: every parameter given once, tensors and sizes by position,
+            # constexprs by keyword
+            bound = dict(zip(names, args))
+            bound.update(kwargs)
+            if len(bound) == len(names) and bound.keys() == self._name_set:
+                return bound
         if len(args) > len(names):
             raise TypeError(f"{self.fn.__name__}() takes {len(names)} arguments "
                             f"but {len(args)} were given")
@@ -170,20 +179,10 @@ class JITFunction:
         # Launches of a specialization seen before skip type inference: the key holds the
         # constexpr values and, per runtime argument, what its type is inferred from (the torch
         # dtype, int32 vs int64 by value, float) -- newt/runtime/jit.py:99-144 keys the same way.
-        cset = self._constexpr_set
-        parts = []
-        for n in self.param_names:
-            v = bound[n]
-            if n in cset:
-                parts.append(v)
-            else:
-                tv = type(v)
-                if tv is int:
-                    parts.append(32 if -2147483648 <= v < 2147483648 else 64)
-                elif tv is float or tv is bool:
-                    parts.append(tv)
-                else:
-                    parts.append(getattr(v, "dtype", tv))
+        parts = [v if c else
+                 ((32 if -2147483648 <= v < 2147483648 else 64) if type(v) is int else
+                  (type(v) if type(v) in (float, bool) else getattr(v, "dtype", type(v))))
+                 for v, c in zip(map(bound.__getitem__, self.param_names), self._is_constexpr)]
         try:
             key = (tuple(parts), num_warps, num_stages)
             hit = self._fast.get(key)

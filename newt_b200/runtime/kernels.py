@@ -103,6 +103,29 @@ def gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, config=None):
                                          ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream()))
 
 
+_repitch_workspaces = {}
+
+
+def repitched(slot, t, rows, cols, row_stride, col_stride):
+    """A row-major copy of the [rows, cols] matrix that starts at `t` with the given strides
+    (in elements), in a per-device workspace for `slot` ("a" or "b") that is kept and grown as
+    needed; returns (workspace tensor of t's dtype, pitch in elements).  The pitch is a
+    multiple of 16 bytes, which is what the tensor-core GEMM needs of its operands.  Work
+    queued on other streams that still reads the workspace is the caller's to order."""
+    eb = t.element_size()
+    pitch = -(-int(cols) // (16 // eb)) * (16 // eb)
+    need = max(int(rows) * pitch, 16)
+    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    ws = _repitch_workspaces.get((dev, slot, t.dtype))
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=t.dtype, device=t.device)
+        _repitch_workspaces[(dev, slot, t.dtype)] = ws
+    abi.check(abi.load().nb200_repitch(_dev_ptr(slot, t), ctypes.c_void_p(ws.data_ptr()), int(rows),
+                                       int(cols), int(row_stride), int(col_stride), pitch, eb,
+                                       _stream()))
+    return ws, pitch
+
+
 def gemm_check(a, b, c, m, n, k, lda, ldb, ldc, config=None):
     """Returns None if the tcgen05 path can run this problem, else the reason (str)."""
     cfg = ctypes.byref(config) if config is not None else None

@@ -515,6 +515,70 @@ def _small_types(dev):
     return (a.to(dev), h.to(dev), oa, oh), dict(BLOCK=64), [(oa, a + 200, 0, 0), (oh, want_h, 0, 0)]
 
 
+@newt.jit
+def two_phase_accumulate(a_ptr, b_ptr, o_ptr, K, full, tail, BM: nl.constexpr, BN: nl.constexpr,
+                         BK: nl.constexpr):
+    """Whole k-blocks in one loop, the masked remainder in a second one on the same accumulator
+    and the same walked pointers; the second loop may run zero times."""
+    rm = nl.arange(0, BM)
+    rn = nl.arange(0, BN)
+    rk = nl.arange(0, BK)
+    a_ptrs = a_ptr + rm[:, None] * K + rk[None, :]
+    b_ptrs = b_ptr + rk[:, None] * BN + rn[None, :]
+    acc = nl.zeros((BM, BN), dtype=nl.float32)
+    for _ in range(full):
+        acc = nl.dot(nl.load(a_ptrs), nl.load(b_ptrs), acc)
+        a_ptrs += BK
+        b_ptrs += BK * BN
+    for t in range(tail):
+        live = (t * BK + rk) < (K - full * BK)
+        acc = nl.dot(nl.load(a_ptrs, mask=live[None, :], other=0.0),
+                     nl.load(b_ptrs, mask=live[:, None], other=0.0), acc)
+    nl.store(o_ptr + rm[:, None] * BN + rn[None, :], acc)
+
+
+def _two_phase_accumulate(k):
+    def build(dev):
+        bm, bn, bk = 32, 32, 16
+        a = _draw((bm, k), 40, torch.float16, 0.3)
+        b = _draw((k, bn), 41, torch.float16, 0.3)
+        o = torch.empty(bm, bn, device=dev)
+        full, tail = k // bk, 1 if k % bk else 0
+        return (a.to(dev), b.to(dev), o, k, full, tail), dict(BM=bm, BN=bn, BK=bk), \
+            [(o, a.float() @ b.float(), 1e-4, 1e-4)]
+    return build
+
+
+@newt.jit
+def logging_k_loop(a_ptr, b_ptr, o_ptr, log_ptr, K, BM: nl.constexpr, BN: nl.constexpr,
+                   BK: nl.constexpr):
+    """A store inside the k loop next to the dot: the loop runs block-wide, the accumulator
+    lives in shared memory."""
+    rm = nl.arange(0, BM)
+    rn = nl.arange(0, BN)
+    rk = nl.arange(0, BK)
+    a_ptrs = a_ptr + rm[:, None] * K + rk[None, :]
+    b_ptrs = b_ptr + rk[:, None] * BN + rn[None, :]
+    acc = nl.zeros((BM, BN), dtype=nl.float32)
+    for i in range(K // BK):
+        acc = nl.dot(nl.load(a_ptrs), nl.load(b_ptrs), acc)
+        nl.store(log_ptr + i * BM + rm, rm.to(nl.float32) + i)
+        a_ptrs += BK
+        b_ptrs += BK * BN
+    nl.store(o_ptr + rm[:, None] * BN + rn[None, :], acc)
+
+
+def _logging_k_loop(dev):
+    bm, bn, bk, k = 32, 32, 16, 64
+    a = _draw((bm, k), 42, torch.float16, 0.3)
+    b = _draw((k, bn), 43, torch.float16, 0.3)
+    o = torch.empty(bm, bn, device=dev)
+    log = torch.zeros(k // bk * bm, device=dev)
+    want_log = (torch.arange(bm).float()[None, :] + torch.arange(k // bk).float()[:, None]).reshape(-1)
+    return (a.to(dev), b.to(dev), o, log, k), dict(BM=bm, BN=bn, BK=bk), \
+        [(o, a.float() @ b.float(), 1e-4, 1e-4), (log, want_log, 0, 0)]
+
+
 CASES = {
     "weighted_tiles": (weighted_tiles, _weighted_tiles),
     "sum_of_cubes": (sum_of_cubes, _sum_of_cubes),
@@ -543,6 +607,9 @@ CASES = {
     "ragged_matmul": (ragged_matmul, _ragged_matmul),
     "matmul_bias_relu": (matmul_bias_relu, _matmul_bias_relu),
     "gram_matrix": (gram_matrix, _gram_matrix),
+    "two_phase_accumulate_no_tail": (two_phase_accumulate, _two_phase_accumulate(48)),
+    "two_phase_accumulate_tail": (two_phase_accumulate, _two_phase_accumulate(40)),
+    "logging_k_loop": (logging_k_loop, _logging_k_loop),
     "small_head_attention": (small_head_attention, _small_head_attention),
 }
 

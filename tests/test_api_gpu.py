@@ -135,9 +135,10 @@ def test_matmul_unmasked_kernel():
     assert torch_ref.rel_frobenius(c.float(), torch_ref.matmul(a, b)) <= 1e-2
 
 
-def test_matmul_unaligned_pitch_runs_on_the_generic_path():
+def test_matmul_unaligned_pitch_is_copied_first():
     """A 200-byte pitch is not TMA-legal: the C-ABI call refuses it with a message (no launch
-    is attempted), and the same program then runs through the generic lowering."""
+    is attempted); the `@jit` launch copies such operands into an aligned workspace first
+    (nb200_repitch) and runs the same tensor-core kernel."""
     from newt_b200.runtime import kernels
 
     a = _rand((64, 100), 21, torch.float16, 0.5)

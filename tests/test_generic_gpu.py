@@ -25,16 +25,17 @@ def test_program_matches_torch(name):
             torch.testing.assert_close(got.float(), want.float(), rtol=rtol, atol=atol)
 
 
-def test_ragged_matmul_took_the_generic_path_and_aligned_one_the_tensor_core():
-    """The same program text: operands whose pitches bulk tensor copies cannot fetch run on the
-    CUDA cores, aligned ones on the tcgen05 kernel."""
+def test_ragged_matmul_is_copied_to_a_fetchable_layout_and_runs_on_the_tensor_core():
+    """The same program text: operands whose pitches bulk tensor copies cannot fetch are first
+    copied into an aligned workspace (two operands here), aligned ones are used as they lie."""
     from newt_b200.frontend.lower import GemmPlan
 
     kernel, grid, args, meta, checks = gp.build("ragged_matmul", "cuda")
     compiled = kernel.specialize(*args, **meta)
     assert isinstance(compiled.plan, GemmPlan)
+    before = compiled.plan.repitched
     kernel[grid](*args, **meta)
-    assert compiled.plan._generic_plan is not None
+    assert compiled.plan.repitched == before + 2 and compiled.plan._generic_plan is None
 
     m, n, k = 128, 128, 64
     g = torch.Generator().manual_seed(3)
@@ -42,4 +43,46 @@ def test_ragged_matmul_took_the_generic_path_and_aligned_one_the_tensor_core():
     b = torch.randn(k, n, generator=g).half().cuda()
     c = torch.zeros(m, n, device="cuda", dtype=torch.float16)
     kernel[(1, 1)](a, b, c, m, n, k, k, 1, n, 1, n, 1, BM=128, BN=128, BK=64)
+    assert compiled.plan.repitched == before + 2
     torch.testing.assert_close(c.float().cpu(), (a.float() @ b.float()).cpu(), rtol=2e-3, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_transposed_a_and_odd_sizes_on_the_tensor_core(dtype):
+    """A given transposed, odd M, N, K (rows of 333, 257 and 1001 elements) and a base pointer
+    that is not 16-byte aligned: all three operands' layouts are ones TMA refuses."""
+    import newt_b200 as newt
+    from newt_b200.frontend.lower import GemmPlan
+
+    m, n, k = 333, 257, 1001
+    g = torch.Generator().manual_seed(11)
+    a = (torch.randn(m, k, generator=g) * 0.5).to(dtype)
+    b = (torch.randn(k, n, generator=g) * 0.5).to(dtype)
+    at = a.t().contiguous().cuda()                     # [k, m]: A[i, j] at j * m + i
+    b_store = torch.empty(k * n + 1, device="cuda", dtype=dtype)
+    b_dev = b_store[1:].view(k, n)                     # base off by one element
+    b_dev.copy_(b)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    kernel = gp.ragged_matmul
+    kernel[(newt.cdiv(m, 64), newt.cdiv(n, 64))](at, b_dev, c, m, n, k, 1, m, n, 1, n, 1,
+                                                  BM=64, BN=64, BK=32)
+    torch.cuda.synchronize()
+    plan = kernel.specialize(at, b_dev, c, m, n, k, 1, m, n, 1, n, 1, BM=64, BN=64, BK=32).plan
+    assert isinstance(plan, GemmPlan) and plan._generic_plan is None and plan.repitched >= 2
+    ref = a.double() @ b.double()
+    err = ((c.cpu().double() - ref).norm() / ref.norm()).item()
+    assert err <= (2e-3 if dtype == torch.float32 else 1e-3), err
+
+
+def test_repitch_entry_point_is_bit_exact():
+    """nb200_repitch moves bits: any two strides in, row-major with a 16-byte pitch out."""
+    from newt_b200.runtime import kernels
+
+    for dtype, rows, cols in ((torch.float16, 130, 75), (torch.float32, 65, 200), (torch.bfloat16, 1, 1)):
+        g = torch.Generator().manual_seed(rows)
+        x = torch.randn(rows, cols, generator=g).to(dtype)
+        for src, rs, cs in ((x.cuda(), cols, 1), (x.t().contiguous().cuda(), 1, rows)):
+            ws, pitch = kernels.repitched("a", src, rows, cols, rs, cs)
+            assert pitch % (16 // x.element_size()) == 0 and pitch >= cols
+            got = ws[:rows * pitch].view(rows, pitch)[:, :cols].cpu()
+            assert torch.equal(got, x)
