@@ -96,7 +96,7 @@ def test_transposed_operands_are_told_apart_at_launch_time():
                                     BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
     a = dict(M=64, N=64, K=64, sam=1, sak=64, sbk=1, sbn=64, scm=64, scn=1)
     inner = dict(c.plan.inner)
-    assert inner["a_ptr"](a) == 64   # A transposed: launch() raises CompileError on this
+    assert inner["a_ptr"](a) == 64   # A transposed: copied into a row-major workspace at launch
     assert inner["b_ptr"](a) == 64 and c.plan.ldb(a) == 1   # B transposed: goes to nb200_gemm_bt
 
 
