@@ -731,6 +731,7 @@ class GemmPlan(Plan):
         self.lda = self.ldb = self.ldc = None
         self.inner = ()
         self.num_stages = 3
+        self._derived = {}
         self.row_k = 64   # K elements per 128-byte row: 64 for fp16/bf16, 32 for fp32 (run as tf32)
 
     def _extents(self, grid, args):
@@ -800,11 +801,22 @@ class GemmPlan(Plan):
     def _launch_tensor_core(self, grid, args):
         from ..runtime import kernels
 
-        m, n, k = self._extents(grid, args)
+        # extents and strides are polynomials in the scalar arguments: evaluated once per
+        # distinct (grid, scalars), the usual case being the same call repeated
+        if self._scalars is None:
+            self._scalars = [name for name, v in args.items()
+                             if isinstance(v, (int, float)) and not isinstance(v, bool)]
+        key = (grid, *[args[name] for name in self._scalars])
+        derived = self._derived.get(key)
+        if derived is None:
+            if len(self._derived) >= 256:
+                self._derived.clear()
+            derived = self._derived[key] = (
+                self._extents(grid, args), {name: fn(args) for name, fn in self.inner},
+                self.lda(args), self.ldb(args), self.ldc(args))
+        (m, n, k), inner, lda, ldb, ldc = derived
         if m == 0 or n == 0:
             return
-        inner = {name: fn(args) for name, fn in self.inner}
-        lda, ldb, ldc = self.lda(args), self.ldb(args), self.ldc(args)
         if inner[self.c] != 1:
             raise CompileError(
                 f"matmul: '{self.c}' is not unit-stride along its fast dimension "
@@ -834,6 +846,7 @@ class GemmPlan(Plan):
             kernels.gemm(a, b, c, m, n, k, lda, ldb, ldc, self.config())
 
     repitched = 0       # how many operands launches of this plan had to copy first
+    _scalars = None     # names of the scalar arguments, found at the first launch
 
 
 def lower_gemm(trace, an, num_stages):

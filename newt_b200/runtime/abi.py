@@ -115,10 +115,15 @@ def read_status():
     return st.value, det.value
 
 
-def dtype_code(torch_dtype):
-    import torch
+_dtype_codes = {}
 
-    table = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
-    if torch_dtype not in table:
+
+def dtype_code(torch_dtype):
+    if not _dtype_codes:
+        import torch
+
+        _dtype_codes.update({torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16})
+    code = _dtype_codes.get(torch_dtype)
+    if code is None:
         raise TypeError(f"dtype {torch_dtype} has no kernel in libnewt_b200")
-    return table[torch_dtype]
+    return code
