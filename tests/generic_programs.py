@@ -579,6 +579,27 @@ def _logging_k_loop(dev):
         [(o, a.float() @ b.float(), 1e-4, 1e-4), (log, want_log, 0, 0)]
 
 
+@newt.jit
+def dot_row_sums(a_ptr, b_ptr, o_ptr, M: nl.constexpr, N: nl.constexpr, K: nl.constexpr):
+    """A dot whose result goes through elementwise arithmetic and a reduction before the store."""
+    rm = nl.arange(0, M)
+    rn = nl.arange(0, N)
+    rk = nl.arange(0, K)
+    a = nl.load(a_ptr + rm[:, None] * K + rk[None, :])
+    b = nl.load(b_ptr + rk[:, None] * N + rn[None, :])
+    c = nl.dot(a, b) * 2.0 + 1.0
+    nl.store(o_ptr + rm, nl.sum(c, axis=1))
+
+
+def _dot_row_sums(dev):
+    m, n, k = 32, 64, 32
+    a = _draw((m, k), 44, torch.float16, 0.3)
+    b = _draw((k, n), 45, torch.float16, 0.3)
+    o = torch.empty(m, device=dev)
+    return (a.to(dev), b.to(dev), o), dict(M=m, N=n, K=k), \
+        [(o, (a.float() @ b.float() * 2 + 1).sum(1), 1e-4, 1e-4)]
+
+
 CASES = {
     "weighted_tiles": (weighted_tiles, _weighted_tiles),
     "sum_of_cubes": (sum_of_cubes, _sum_of_cubes),
@@ -607,6 +628,7 @@ CASES = {
     "ragged_matmul": (ragged_matmul, _ragged_matmul),
     "matmul_bias_relu": (matmul_bias_relu, _matmul_bias_relu),
     "gram_matrix": (gram_matrix, _gram_matrix),
+    "dot_row_sums": (dot_row_sums, _dot_row_sums),
     "two_phase_accumulate_no_tail": (two_phase_accumulate, _two_phase_accumulate(48)),
     "two_phase_accumulate_tail": (two_phase_accumulate, _two_phase_accumulate(40)),
     "logging_k_loop": (logging_k_loop, _logging_k_loop),
