@@ -600,6 +600,49 @@ def _dot_row_sums(dev):
         [(o, (a.float() @ b.float() * 2 + 1).sum(1), 1e-4, 1e-4)]
 
 
+# ---- launch geometry and compile-time constructs ------------------------------------------------
+
+@newt.jit
+def grid_coordinates(o_ptr, BLOCK: nl.constexpr):
+    """Three grid axes and their extents: program (x, y, z) writes its linear index."""
+    x, y, z = nl.program_id(0), nl.program_id(1), nl.program_id(2)
+    nx, ny = nl.num_programs(0), nl.num_programs(1)
+    lin = (z * ny + y) * nx + x
+    offs = nl.arange(0, BLOCK)
+    nl.store(o_ptr + lin * BLOCK + offs, nl.zeros((BLOCK,), dtype=nl.int32) + lin * 10 + nl.num_programs(2))
+
+
+def _grid_coordinates(dev):
+    gx, gy, gz, block = 3, 4, 2, 32
+    o = torch.full((gx * gy * gz * block,), -1, device=dev, dtype=torch.int32)
+    want = (torch.arange(gx * gy * gz, dtype=torch.int32) * 10 + gz).repeat_interleave(block)
+    return (o,), dict(BLOCK=block), [(o, want, 0, 0)], (gx, gy, gz)
+
+
+@newt.jit
+def chosen_at_compile_time(x_ptr, o_ptr, n, MODE: nl.constexpr, BLOCK: nl.constexpr):
+    """A constexpr branch is pruned: the arm not taken is never traced (it would not lower),
+    a tuple assignment unpacks, a block smaller than the thread count leaves threads idle."""
+    nl.static_assert(BLOCK >= 16, "BLOCK too small")
+    offs, ok = nl.arange(0, BLOCK), nl.arange(0, BLOCK) < n
+    x = nl.load(x_ptr + offs, mask=ok)
+    if MODE == "triple":
+        y = x * 3
+    else:
+        y = nl.no_such_function(x)
+    nl.store(o_ptr + offs, y, mask=ok)
+
+
+def _chosen_at_compile_time(n, block, warps):
+    def build(dev):
+        x = _draw(block, 50)
+        o = torch.full((block,), 5.0, device=dev)
+        want = torch.full((block,), 5.0)
+        want[:n] = x[:n] * 3
+        return (x.to(dev), o, n), dict(MODE="triple", BLOCK=block, num_warps=warps), [(o, want, 0, 0)]
+    return build
+
+
 CASES = {
     "weighted_tiles": (weighted_tiles, _weighted_tiles),
     "sum_of_cubes": (sum_of_cubes, _sum_of_cubes),
@@ -618,6 +661,9 @@ CASES = {
     "bound_in_both_arms_else": (bound_in_both_arms, _bound_in_both_arms(0)),
     "fill_from_other_tensor": (fill_from_other_tensor, _fill_from_other_tensor),
     "small_types": (small_types, _small_types),
+    "grid_coordinates": (grid_coordinates, _grid_coordinates),
+    "pruned_branch_tiny_block": (chosen_at_compile_time, _chosen_at_compile_time(16, 16, 4)),
+    "pruned_branch_one_element": (chosen_at_compile_time, _chosen_at_compile_time(1, 64, 1)),
     "scale_tiles": (scale_tiles, _scale_tiles),
     "running_softmax_stats": (running_softmax_stats, _running_softmax_stats),
     "tiled_layernorm": (tiled_layernorm, _tiled_layernorm),

@@ -60,6 +60,11 @@ def test_break_under_a_runtime_condition_ends_a_while_loop():
 def test_control_flow_errors():
     F32 = tp.pointer_type(tp.float32)
 
+    with pytest.raises(newt.CompileError, match="BLOCK too small"):
+        gp.chosen_at_compile_time.specialize(F32, F32, 4, MODE="triple", BLOCK=8)
+    with pytest.raises(newt.CompileError):       # the other arm is traced when it is the one taken
+        gp.chosen_at_compile_time.specialize(F32, F32, 4, MODE="other", BLOCK=16)
+
     @newt.jit
     def block_condition(x_ptr, BLOCK: nl.constexpr):
         x = nl.load(x_ptr + nl.arange(0, BLOCK))
