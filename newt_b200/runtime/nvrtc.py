@@ -136,7 +136,8 @@ class Kernel:
             _check(cu.cuFuncSetAttribute(fn, 8, ctypes.c_int(shared_bytes)), "cuFuncSetAttribute")
             self._shared[dev] = shared_bytes
         g = tuple(grid) + (1,) * (3 - len(grid))
+        b = (block, 1, 1) if isinstance(block, int) else tuple(block) + (1,) * (3 - len(block))
         ptrs = (ctypes.c_void_p * len(args))(*[ctypes.cast(ctypes.pointer(a), ctypes.c_void_p)
                                                for a in args])
-        _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], block, 1, 1, shared_bytes, ctypes.c_void_p(stream),
+        _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], b[0], b[1], b[2], shared_bytes, ctypes.c_void_p(stream),
                                  ptrs, None), f"launch of {self.func_name}")

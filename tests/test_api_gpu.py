@@ -518,3 +518,26 @@ def test_generated_reductions_over_2d_blocks():
     want_rows = xp.view(bm, progs, bn).sum(-1).t()
     torch.testing.assert_close(rowsum.cpu(), want_rows, rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(total.cpu(), want_rows.sum(-1), rtol=1e-5, atol=1e-4)
+
+
+def test_runtime_cuda_kernel_launches_raw_source():
+    """newt/runtime/cuda.py `compile_cuda` + `Kernel.launch` by name (tests/test_runtime_smoke.py):
+    NVRTC -> cubin -> driver launch on torch tensors, no compiler in between."""
+    import ctypes
+
+    from newt_b200.runtime.cuda import Kernel, compile_cuda
+
+    src = 'extern "C" __global__ void scale_shift(float a, const float* x, const float* y, float* out, int n) {\n' \
+          '  int i = blockIdx.x * blockDim.x + threadIdx.x;\n  if (i < n) out[i] = a * x[i] + y[i];\n}\n'
+    cap = torch.cuda.get_device_capability()
+    k = Kernel(compile_cuda(src, "scale_shift", f"sm_{cap[0]}{cap[1]}"), "scale_shift")
+    n = (1 << 18) + 7
+    x, y = _rand(n, 51), _rand(n, 52)
+    xd, yd = x.cuda(), y.cuda()
+    out = torch.empty_like(xd)
+    k.launch(grid=((n + 255) // 256,), block=(256,),
+             args=[ctypes.c_float(2.5), ctypes.c_void_p(xd.data_ptr()), ctypes.c_void_p(yd.data_ptr()),
+                   ctypes.c_void_p(out.data_ptr()), ctypes.c_int32(n)],
+             stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.cpu(), 2.5 * x + y, rtol=1e-6, atol=1e-6)

@@ -383,3 +383,46 @@ def test_deuteron_trace_errors():
 
     with pytest.raises(dt.TraceError, match="top level"):
         bad.to_newt_source(torch.zeros(4), torch.zeros(4))
+
+
+def test_compile_fn_keeps_the_generator_contract():
+    """newt/compiler/codegen.py:2758-2765 as driven by tests/test_codegen_cpu.py:22-31:
+    (fndef, globals, params, constexprs, num_warps, name) -> (source, shared bytes[, plan])."""
+    import ast
+    import inspect
+    import textwrap
+
+    from newt_b200.compiler import codegen
+    from newt_b200.compiler import types as ctp
+
+    def scaled_add(x_ptr, y_ptr, out_ptr, n, alpha, BLOCK: nl.constexpr):
+        offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        ok = offs < n
+        nl.store(out_ptr + offs, nl.load(x_ptr + offs, mask=ok) * alpha + nl.load(y_ptr + offs, mask=ok),
+                 mask=ok)
+
+    fndef = ast.parse(textwrap.dedent(inspect.getsource(scaled_add))).body[0]
+    fp = ctp.pointer_type(ctp.float32)
+    params = [(n, codegen.Value(codegen.UNIFORM, t, (), n))
+              for n, t in dict(x_ptr=fp, y_ptr=fp, out_ptr=fp, n=ctp.int32, alpha=ctp.float32).items()]
+    src, smem, plan = codegen.compile_fn(fndef, globals(), params, {"BLOCK": 1024}, 4, "k")
+    assert "__launch_bounds__(128)" in src and "blockIdx.x" in src and "__restrict__" in src
+    assert smem == 0 and isinstance(plan, lower.PointwisePlan) and 'void __launch_bounds__(128) k_' in src
+
+    fndef = ast.parse(textwrap.dedent(inspect.getsource(rk.add_kernel.fn))).body[-1]
+    params = [("x_ptr", fp), ("y_ptr", fp), ("out_ptr", fp), ("n", ctp.int32)]
+    src, smem, plan = codegen.compile_fn(fndef, rk.add_kernel.fn.__globals__, params, {"BLOCK": 4096})
+    assert isinstance(plan, lower.AddPlan) and "nb200_add_f32" in src and smem == 0
+
+
+def test_runtime_cuda_compiles_raw_source_without_a_gpu():
+    from newt_b200.runtime.cuda import Kernel, NVRTCError, compile_cuda
+
+    src = 'extern "C" __global__ void saxpy(float a, const float* x, float* y, int n) {\n' \
+          '  int i = blockIdx.x * blockDim.x + threadIdx.x;\n  if (i < n) y[i] = a * x[i] + y[i];\n}\n'
+    cubin = compile_cuda(src, "saxpy", "sm_100")
+    assert cubin[:4] == b"\x7fELF"
+    k = Kernel(cubin, "saxpy", shared_bytes=0)      # loading is deferred to the first launch
+    assert k.func_name == "saxpy"
+    with pytest.raises(NVRTCError, match="saxpy.cu"):
+        compile_cuda(src.replace("int i", "int i i"), "saxpy")
