@@ -1161,8 +1161,8 @@ class PointwisePlan(Plan):
         from ..runtime import nvrtc
 
         if self._kernel is None:
-            self._kernel = nvrtc.Kernel(nvrtc.compile_cubin(self.source, self.kernel_name + ".cu"),
-                                        self.kernel_name)
+            self._kernel = nvrtc.Kernel(
+                nvrtc.compile_cubin_cached(self.source, self.kernel_name + ".cu"), self.kernel_name)
         raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         stream = raw(torch.cuda.current_device()) if raw is not None \
             else torch.cuda.current_stream().cuda_stream

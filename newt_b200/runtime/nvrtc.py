@@ -87,6 +87,58 @@ def compile_cubin(source, name="kernel.cu", arch="sm_100a", extra_opts=()):
         lib.nvrtcDestroyProgram(ctypes.byref(prog))
 
 
+def cache_dir():
+    """Where compiled cubins are kept between processes: $NEWT_CACHE_DIR, else ~/.newt/cache
+    (the reference's convention, newt/runtime/jit.py:21-24); None if it cannot be created."""
+    d = os.environ.get("NEWT_CACHE_DIR") or os.path.join(os.path.expanduser("~"), ".newt", "cache")
+    try:
+        os.makedirs(d, exist_ok=True)
+    except OSError:
+        return None
+    return d
+
+
+def _nvrtc_version():
+    major, minor = ctypes.c_int(), ctypes.c_int()
+    if _load_nvrtc().nvrtcVersion(ctypes.byref(major), ctypes.byref(minor)) != 0:
+        return "?"
+    return f"{major.value}.{minor.value}"
+
+
+def compile_cubin_cached(source, name="kernel.cu", arch="sm_100a", extra_opts=()):
+    """`compile_cubin` behind a disk cache keyed by the source text, the architecture, the
+    options and the NVRTC version (newt/runtime/jit.py:50-66 keeps cubins the same way).  The
+    source is stored next to the cubin for inspection.  Files are written to a temporary name
+    and renamed, so concurrent processes (one per GPU) never read a partial cubin; a cache
+    that cannot be read or written is skipped, not an error."""
+    import hashlib
+    import tempfile
+
+    d = cache_dir()
+    if d is None:
+        return compile_cubin(source, name, arch, extra_opts)
+    key = hashlib.sha256("\0".join([source, arch, *extra_opts, _nvrtc_version(), "b200-1"]).encode()
+                         ).hexdigest()[:32]
+    path = os.path.join(d, f"{key}.cubin")
+    try:
+        with open(path, "rb") as f:
+            cubin = f.read()
+        if cubin[:4] == b"\x7fELF":
+            return cubin
+    except OSError:
+        pass
+    cubin = compile_cubin(source, name, arch, extra_opts)
+    for suffix, payload in ((".cubin", cubin), (".cu", source.encode())):
+        try:
+            fd, tmp = tempfile.mkstemp(dir=d, suffix=".tmp")
+            with os.fdopen(fd, "wb") as f:
+                f.write(payload)
+            os.replace(tmp, os.path.join(d, key + suffix))
+        except OSError:
+            break
+    return cubin
+
+
 def _check(rc, what):
     if rc != 0:
         msg = ctypes.c_char_p()

@@ -426,3 +426,23 @@ def test_runtime_cuda_compiles_raw_source_without_a_gpu():
     assert k.func_name == "saxpy"
     with pytest.raises(NVRTCError, match="saxpy.cu"):
         compile_cuda(src.replace("int i", "int i i"), "saxpy")
+
+
+def test_cubins_are_cached_on_disk(tmp_path, monkeypatch):
+    from newt_b200.runtime import nvrtc
+
+    monkeypatch.setenv("NEWT_CACHE_DIR", str(tmp_path))
+    src = 'extern "C" __global__ void twice(float* x) { x[threadIdx.x] *= 2.0f; }\n'
+    first = nvrtc.compile_cubin_cached(src, "twice.cu")
+    files = sorted(p.suffix for p in tmp_path.iterdir())
+    assert files == [".cu", ".cubin"] and first[:4] == b"\x7fELF"
+    calls = []
+    monkeypatch.setattr(nvrtc, "compile_cubin", lambda *a, **k: calls.append(a) or b"")
+    assert nvrtc.compile_cubin_cached(src, "twice.cu") == first and not calls      # served from disk
+    nvrtc.compile_cubin_cached(src, "twice.cu", arch="sm_100")                     # another key
+    assert len(calls) == 1
+    # a truncated file is not trusted
+    cubin = next(p for p in tmp_path.iterdir() if p.suffix == ".cubin" and p.stat().st_size > 0)
+    cubin.write_bytes(b"junk")
+    nvrtc.compile_cubin_cached(src, "twice.cu")
+    assert len(calls) == 2
