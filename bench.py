@@ -22,6 +22,7 @@ expected values, restated under oracle/) on the host cores instead.
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -482,25 +483,31 @@ def run_gpu(args, wl):
     flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
 
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(max(args.warmup, 3)):
         flush.zero_()
+        w0.record()
         wl.step(dev)
+        w1.record()
     barrier()
+    warm_step_ms = max(w0.elapsed_time(w1), 1e-3)
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)      # nvidia-smi needs a few hundred ms to come up
-    barrier()
-    # one more untimed step on every rank: the pause above let the GPU drop to an idle power
-    # state, and the first launch after it pays for the ramp
-    flush.zero_()
-    wl.step(dev)
 
     # ---- device-resident timed region: K steps, one event pair per step ------
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
+    # Untimed steps on every rank, queued straight ahead of the timed ones: the pause and the
+    # barrier above left the GPU idle, and the first launches after that pay for the ramp (a
+    # 28 us row kernel read 59 us there).  About 0.7 ms of them: one matmul step, a couple of
+    # dozen row-kernel steps.
+    for _ in range(min(32, max(1, math.ceil(0.7 / warm_step_ms)))):
+        flush.zero_()
+        wl.step(dev)
     for i in range(args.steps):
         flush.zero_()
         starts[i].record()
@@ -561,7 +568,7 @@ def run_gpu(args, wl):
             "gpu_launches": args.steps * wl.kernels_per_step,
             "clocks": clocks,
             "step_ms": {"min": min(step_ms), "median": statistics.median(step_ms),
-                        "max": max(step_ms)},
+                        "max": max(step_ms), "slowest": step_ms.index(max(step_ms))},
         }
         if world == 1:
             torch.set_num_threads(os.cpu_count() or 1)
