@@ -157,6 +157,15 @@ int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int64_t m, int
                            int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
                            const nb200_gemm_config* config, void* stream);
 
+/* nb200_gemm / nb200_gemm_bt (b_transposed != 0) for fp16 or bf16 operands with C taking the
+ * fp32 accumulator unrounded: C is float [M, N] with row stride ldc.  What a matmul with an
+ * epilogue fused after its k loop needs (bias, activation, scaling applied to the fp32
+ * accumulator before the one rounding at the store, newt/compiler/codegen.py:1718-1723): the
+ * product runs here, the epilogue reads C. */
+int nb200_gemm_acc32(const void* a, const void* b, float* c, int64_t m, int64_t n, int64_t k,
+                     int64_t lda, int64_t ldb, int64_t ldc, int dtype, int b_transposed,
+                     const nb200_gemm_config* config, void* stream);
+
 /* dst[r][c] = src[r * row_stride + c * col_stride] for 2- or 4-byte elements (strides and
  * dst_pitch in elements): copies a matrix given with any two strides -- a row pitch that is
  * not a multiple of 16 bytes, a misaligned base, a transposed A -- into a row-major buffer

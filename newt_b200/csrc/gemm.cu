@@ -121,6 +121,7 @@ struct GemmParams {
   uint32_t idesc;
   int c_vec_ok;  // C base and row pitch are 16-byte aligned
   int b_kmajor;  // B is given transposed ([N, K], K contiguous); always so for tf32
+  int c_f32;     // 16-bit operands, but C takes the fp32 accumulator unrounded
   unsigned int* status;
 };
 
@@ -294,7 +295,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
-        if (row < p.m) store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
+        if (row < p.m) {
+          if (DT != NB200_F32 && p.c_f32)
+            store_chunk<NB200_F32>(static_cast<float*>(p.c) + (long long)row * p.ldc, col0, p.n,
+                                   p.c_vec_ok != 0, r);
+          else
+            store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -508,7 +515,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
-        if (row < p.m) store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
+        if (row < p.m) {
+          if (DT != NB200_F32 && p.c_f32)
+            store_chunk<NB200_F32>(static_cast<float*>(p.c) + (long long)row * p.ldc, col0, p.n,
+                                   p.c_vec_ok != 0, r);
+          else
+            store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -797,15 +810,16 @@ namespace nb200 {
 // C = A @ B with B given either as [K, N] (b_kmajor = false) or transposed as [N, K].
 int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
               int64_t ldb, int64_t ldc, int dtype, const nb200_gemm_config* config, bool b_kmajor,
-              cudaStream_t stream) {
+              cudaStream_t stream, bool c_f32 = false) {
   if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype, b_kmajor)) return rc;
   const int eb = dtype == NB200_F32 ? 4 : 2;   // bytes per element
   const int row_k = 128 / eb;                  // K elements per 128-byte row = columns per slab of B
   Resolved cfg;
   if (int rc = resolve_config(config, m, n, row_k, &cfg)) return rc;
   if (m == 0 || n == 0) return 0;
+  const int cb = c_f32 ? 4 : eb;                // bytes per element of C
   if (k == 0)  // empty reduction: the accumulator is its zero initial value
-    return cuda_check(cudaMemset2DAsync(c, (size_t)ldc * eb, 0, (size_t)n * eb, (size_t)m, stream),
+    return cuda_check(cudaMemset2DAsync(c, (size_t)ldc * cb, 0, (size_t)n * cb, (size_t)m, stream),
                       "gemm k=0 clear");
 
   CUtensorMap ta, tb;
@@ -841,7 +855,8 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
                 ? sm100::instr_desc_tf32(mma_m, cfg.block_n, false, false)
                 : sm100::instr_desc_f16(mma_m, cfg.block_n, dtype == NB200_BF16, false, !b_kmajor);
   p.b_kmajor = b_kmajor ? 1 : 0;
-  p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * eb) % 16 == 0) ? 1 : 0;
+  p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * cb) % 16 == 0) ? 1 : 0;
+  p.c_f32 = c_f32 ? 1 : 0;
   p.status = device_status_ptr();
   if (!p.status) return fail(NB200_E_CUDA, "gemm: device status word is not addressable");
 
@@ -969,6 +984,16 @@ extern "C" int nb200_gemm_bt(const void* a, const void* bt, void* c, int64_t m, 
                              const nb200_gemm_config* config, void* stream) {
   return gemm_impl(a, bt, c, m, n, k, lda, ldbt, ldc, dtype, config, true,
                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nb200_gemm_acc32(const void* a, const void* b, float* c, int64_t m, int64_t n,
+                                int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int dtype,
+                                int b_transposed, const nb200_gemm_config* config, void* stream) {
+  if (dtype != NB200_F16 && dtype != NB200_BF16)
+    return fail(NB200_E_UNSUPPORTED, "gemm_acc32: fp16 or bf16 operands (fp32 ones already give an "
+                                     "fp32 result through nb200_gemm_tf32 / nb200_gemm_bt)");
+  return gemm_impl(a, b, c, m, n, k, lda, ldb, ldc, dtype, config, b_transposed != 0,
+                   static_cast<cudaStream_t>(stream), true);
 }
 
 extern "C" int64_t nb200_gemm_tf32_workspace_bytes(int64_t n, int64_t k) {

@@ -798,7 +798,8 @@ class GemmPlan(Plan):
 
     _generic_plan = None
 
-    def _launch_tensor_core(self, grid, args):
+    def _launch_tensor_core(self, grid, args, acc32=None):
+        """`acc32`: an fp32 buffer laid out like C that takes the accumulator instead of C."""
         from ..runtime import kernels
 
         # extents and strides are polynomials in the scalar arguments: evaluated once per
@@ -822,6 +823,8 @@ class GemmPlan(Plan):
                 f"matmul: '{self.c}' is not unit-stride along its fast dimension "
                 f"(stride {inner[self.c]})")
         a, b, c = args[self.a], args[self.b], args[self.c]
+        if acc32 is not None:
+            c = acc32
         per16 = 16 // a.element_size()
 
         def fetchable(t, pitch, unit):      # what a bulk tensor copy needs of an operand
@@ -835,13 +838,18 @@ class GemmPlan(Plan):
         if fetchable(b, inner[self.b], ldb) and inner[self.b] != 1:
             # B[k, n] at k * 1 + n * stride: the caller handed over B^T, which is what the
             # tensor core wants anyway
-            kernels.gemm_bt(a, b, c, m, n, k, lda, inner[self.b], ldc, self.config())
+            if acc32 is not None and self.row_k != 32:
+                kernels.gemm_acc32(a, b, c, m, n, k, lda, inner[self.b], ldc, True, self.config())
+            else:
+                kernels.gemm_bt(a, b, c, m, n, k, lda, inner[self.b], ldc, self.config())
             return
         if not fetchable(b, ldb, inner[self.b]):
             b, ldb = kernels.repitched("b", b, k, n, ldb, inner[self.b])
             self.repitched += 1
         if self.row_k == 32:
             kernels.gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, self.config())
+        elif acc32 is not None:
+            kernels.gemm_acc32(a, b, c, m, n, k, lda, ldb, ldc, False, self.config())
         else:
             kernels.gemm(a, b, c, m, n, k, lda, ldb, ldc, self.config())
 
@@ -849,7 +857,10 @@ class GemmPlan(Plan):
     _scalars = None     # names of the scalar arguments, found at the first launch
 
 
-def lower_gemm(trace, an, num_stages):
+def lower_gemm(trace, an, num_stages, epilogue=False):
+    """The matmul k loop.  With `epilogue`, the stored value may be any expression of the
+    accumulator (bias, activation, scaling, a reduction over the tile) and the store may be of
+    any dtype; returns (plan, (loop uid, accumulator name), the store's pointer node) then."""
     loops = _loops(trace)
     stores = _top_level_stores(trace)
     if len(loops) != 1 or len(stores) != 1:
@@ -885,11 +896,13 @@ def lower_gemm(trace, an, num_stages):
     _, c_ptr, c_val, c_mask, _ = stores[0]
     out = c_val.args[0] if c_val.op == "cast" else c_val
     at = dict(out.attrs)
-    if out.op != "loopout" or at.get("loop") != loop.uid or at.get("name") != acc_name:
-        raise Unmatched("matmul: the stored value is not the accumulator (fused epilogues are "
-                        "not supported yet)")
-    if c_ptr.dtype.element != a.dtype:
-        raise Unmatched("matmul: output dtype differs from the operand dtype")
+    plain = out.op == "loopout" and at.get("loop") == loop.uid and at.get("name") == acc_name \
+        and c_ptr.dtype.element == a.dtype
+    if not plain and not epilogue:
+        raise Unmatched("matmul: the stored value is not the accumulator cast to the operand "
+                        "dtype (taken by the matmul-with-epilogue plan)")
+    if plain and epilogue:
+        raise Unmatched("matmul with epilogue: the store is the plain accumulator")
 
     ta = TileAccess(an, a.args[0], "matmul A")
     tb = TileAccess(an, b.args[0], "matmul B")
@@ -922,7 +935,45 @@ def lower_gemm(trace, an, num_stages):
                        ((ta.base, ta), (tb.base, tb), (tc.base, tc)))
     plan.num_stages = num_stages
     plan.row_k = 32 if a.dtype == tp.float32 else 64
+    if epilogue:
+        return plan, (loop.uid, acc_name), c_ptr
     return plan
+
+
+class GemmEpiloguePlan(Plan):
+    """A matmul k loop whose accumulator goes through more arithmetic before the store (bias,
+    activation, scaling, a row reduction): the product runs on the tensor core into an fp32
+    buffer laid out like C (`nb200_gemm_acc32`; fp32 operands: the tf32 entry points), then the
+    rest of the program runs as a generated kernel that reads the accumulator from that buffer
+    (newt/compiler/codegen.py:2420-2451 drains the pipeline before the accumulator is read;
+    here the drain is the end of the first kernel).  Costs one extra pass over C (4 bytes
+    written and read per element) against a kernel with the epilogue inside."""
+
+    kind, entry = "matmul K loop + epilogue", "nb200_gemm_acc32 + run-time compiled kernel"
+
+    def __init__(self, trace, gemm, acc, c_ptr, num_warps):
+        self.gemm = gemm
+        self.epilogue = PointwisePlan(trace, num_warps, {acc: ("nb_acc", c_ptr)})
+        self._buffers = {}
+
+    def hardware_key(self):
+        return ("gemm+epilogue",) + self.gemm.hardware_key() + (self.epilogue.kernel_name,)
+
+    def launch(self, grid, args):
+        import torch
+
+        c = args[self.gemm.c]
+        m, n, _ = self.gemm._extents(grid, args)
+        if m == 0 or n == 0:
+            return
+        ldc = self.gemm.ldc(args)
+        need = (m - 1) * ldc + n
+        dev = c.device.index if c.device.index is not None else torch.cuda.current_device()
+        buf = self._buffers.get(dev)
+        if buf is None or buf.numel() < need:
+            buf = self._buffers[dev] = torch.empty(need, dtype=torch.float32, device=c.device)
+        self.gemm._launch_tensor_core(grid, args, acc32=buf)
+        self.epilogue.launch(grid, {**args, "nb_acc": buf})
 
 
 # --------------------------------------------------------------------------- attention
@@ -1146,10 +1197,10 @@ class PointwisePlan(Plan):
 
     kind, entry = "block arithmetic", "run-time compiled kernel (NVRTC, sm_100a)"
 
-    def __init__(self, trace, num_warps):
+    def __init__(self, trace, num_warps, computed_elsewhere=None):
         self.num_warps = num_warps
         self.source, self.kernel_name, self.params, self.shared_bytes = \
-            pointwise.generate(trace, num_warps)
+            pointwise.generate(trace, num_warps, computed_elsewhere)
         self._kernel = None
 
     def hardware_key(self):
@@ -1170,6 +1221,14 @@ class PointwisePlan(Plan):
                             stream, self.shared_bytes)
 
 
+def _lower_gemm_epilogue(trace, an, num_stages, num_warps):
+    gemm, acc, c_ptr = lower_gemm(trace, an, num_stages, epilogue=True)
+    try:
+        return GemmEpiloguePlan(trace, gemm, acc, c_ptr, num_warps)
+    except pointwise.Unsupported as e:
+        raise Unmatched(f"matmul with epilogue: {e}")
+
+
 def lower(trace, num_warps=4, num_stages=3):
     """Picks the launch plan for a traced kernel or raises CompileError."""
     an = Analyzer(trace)
@@ -1181,6 +1240,7 @@ def lower(trace, num_warps=4, num_stages=3):
                 ("tile softmax", lambda: lower_softmax_tile(trace, an)),
                 ("tile layernorm", lambda: lower_layernorm_tile(trace, an)),
                 ("matmul", lambda: lower_gemm(trace, an, num_stages)),
+                ("matmul with epilogue", lambda: _lower_gemm_epilogue(trace, an, num_stages, num_warps)),
                 ("attention", lambda: lower_attention(trace, an, num_stages))]
     attempts += [(n, (lambda f=f: f(trace, an, num_stages))) for n, f in _RECOGNISERS]
     if any(e[0] == "atomic" for e in trace.effects):

@@ -549,6 +549,13 @@ def _state_value(body, st, node, dims):
         if node.is_pointer:
             return body.var(node.dtype, f"{base} + {off}")
         return body.var(node.dtype, f"({node.dtype.ctype})({base} + {off})")
+    if st[0] == "gmem":
+        # computed by another kernel into a buffer laid out like the tensor `like` walks:
+        # element (dims) sits at the same offset from the buffer's start as like(dims) from
+        # its own base argument
+        _, name, like, base = st
+        where = _emit(body, like, _operand_dims(node.shape, dims, like.shape))
+        return body.var(node.dtype, f"{name}[{where} - {base}]")
     _, array, shape = st                            # a block kept in shared memory
     return f"{array}[{_linear(dims, shape)}]"
 
@@ -1139,10 +1146,21 @@ def _check_order(ctx, effects, written):
             written.add(_base_param(eff[1], ctx.loops))
 
 
-def generate(trace, num_warps):
+def generate(trace, num_warps, computed_elsewhere=None):
     """Returns (cuda_source, kernel_name, [(param name, dtype or pointer_type)], bytes of
-    dynamic shared memory)."""
+    dynamic shared memory).
+
+    `computed_elsewhere`: {(loop uid, carried name): (buffer parameter name, pointer node)} --
+    results of loops that another kernel has already left in device memory (the accumulator of
+    a matmul k loop run on the tensor core).  The generated kernel takes each buffer as one
+    more pointer argument, after the program's own, and reads the value for an element at the
+    offset at which the pointer node addresses its tensor; the loop itself is not emitted."""
     ctx = _Context(trace, num_warps * THREADS_PER_WARP)
+    extra_params = []
+    for (uid, name), (buffer, like) in (computed_elsewhere or {}).items():
+        ph = ctx.loops[uid].values[name][0]
+        ctx.final[(uid, name)] = ("gmem", buffer, like, _base_param(like, ctx.loops))
+        extra_params.append((buffer, tp.pointer_type(ph.dtype)))
     if not any(eff[0] in ("store", "atomic") or (eff[0] in ("for", "while") and _has_effects(eff[1]))
                for eff in trace.effects):
         raise Unsupported("the program stores nothing")
@@ -1151,7 +1169,7 @@ def generate(trace, num_warps):
     while lines and lines[-1] == "__syncthreads();":
         lines.pop()
 
-    params = [(name, node.dtype) for name, node in trace.params.items()]
+    params = [(name, node.dtype) for name, node in trace.params.items()] + extra_params
     # Elements are independent, so the loads of several iterations may be issued before the
     # stores of earlier ones; `__restrict__` says so (a tensor passed under two names is still
     # fine as long as element i is only read for element i, as in any in-place elementwise call).

@@ -62,6 +62,8 @@ SIGNATURES = {
                                        ctypes.POINTER(GemmConfig), _vp, _i64, _vp]),
     "nb200_gemm_tf32_static": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                               ctypes.POINTER(GemmConfig), _vp]),
+    "nb200_gemm_acc32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
+                                        ctypes.c_int, ctypes.c_int, ctypes.POINTER(GemmConfig), _vp]),
     "nb200_repitch": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, _vp]),
     "nb200_gemm_check": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                         ctypes.c_int, ctypes.POINTER(GemmConfig)]),

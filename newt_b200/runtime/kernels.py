@@ -103,6 +103,15 @@ def gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, config=None):
                                          ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream()))
 
 
+def gemm_acc32(a, b, c, m, n, k, lda, ldb, ldc, b_transposed=False, config=None):
+    """fp32 C = A @ B for fp16 / bf16 operands: the accumulator as it is, not rounded."""
+    cfg = ctypes.byref(config) if config is not None else None
+    abi.check(abi.load().nb200_gemm_acc32(_dev_ptr("a", a), _dev_ptr("b", b), _dev_ptr("c", c),
+                                          int(m), int(n), int(k), int(lda), int(ldb), int(ldc),
+                                          abi.dtype_code(a.dtype), 1 if b_transposed else 0, cfg,
+                                          _stream()))
+
+
 _repitch_workspaces = {}
 
 

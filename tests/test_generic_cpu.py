@@ -8,7 +8,7 @@ import generic_programs as gp
 import newt_b200 as newt
 import newt_b200.language as nl
 from newt_b200 import types as tp
-from newt_b200.frontend.lower import GemmPlan, PointwisePlan
+from newt_b200.frontend.lower import GemmEpiloguePlan, GemmPlan, PointwisePlan
 from newt_b200.runtime import nvrtc
 
 
@@ -22,8 +22,11 @@ def _specialize(name):
 @pytest.mark.parametrize("name", sorted(gp.CASES))
 def test_program_lowers_and_compiles(name):
     plan = _specialize(name).plan
-    if isinstance(plan, GemmPlan):      # picked at launch by the operands' pitches
+    if isinstance(plan, GemmPlan):      # what runs if the tensor-core path refuses the operands
         plan = plan.generic()
+    if isinstance(plan, GemmEpiloguePlan):      # tensor-core product + generated epilogue
+        assert "nb_acc[" in plan.epilogue.source and "fmaf(" not in plan.epilogue.source
+        plan = plan.epilogue
     assert isinstance(plan, PointwisePlan)
     cubin = nvrtc.compile_cubin(plan.source, name + ".cu")
     assert len(cubin) > 1000

@@ -86,3 +86,44 @@ def test_repitch_entry_point_is_bit_exact():
             assert pitch % (16 // x.element_size()) == 0 and pitch >= cols
             got = ws[:rows * pitch].view(rows, pitch)[:, :cols].cpu()
             assert torch.equal(got, x)
+
+
+def test_matmul_with_epilogue_runs_the_product_on_the_tensor_core():
+    """Bias and activation after the k loop: the product goes through nb200_gemm_acc32 into an
+    fp32 buffer, the epilogue is a generated kernel reading it; one rounding, at the store."""
+    from newt_b200.frontend.lower import GemmEpiloguePlan
+
+    m, n, k = 512, 768, 256
+    g = torch.Generator().manual_seed(5)
+    a = (torch.randn(m, k, generator=g) * 0.5).bfloat16()
+    b = (torch.randn(k, n, generator=g) * 0.5).bfloat16()
+    bias = torch.randn(n, generator=g)
+    ad, bd, biasd = a.cuda(), b.cuda(), bias.cuda()
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    meta = dict(BM=128, BN=128, BK=64)
+    plan = gp.matmul_bias_relu.specialize(ad, bd, biasd, c, m, n, k, **meta).plan
+    assert isinstance(plan, GemmEpiloguePlan)
+    gp.matmul_bias_relu[(m // 128, n // 128)](ad, bd, biasd, c, m, n, k, **meta)
+    torch.cuda.synchronize()
+    want = torch.relu(a.double() @ b.double() + bias.double())
+    # fp32 accumulation and one bf16 rounding: half an ulp of bf16 (2^-9) plus the sum's error
+    torch.testing.assert_close(c.cpu().double(), want, rtol=2 ** -8, atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("transposed", [False, True])
+def test_gemm_acc32_keeps_the_accumulator(dtype, transposed):
+    from newt_b200.runtime import kernels
+
+    m, n, k = 200, 136, 264
+    g = torch.Generator().manual_seed(6)
+    a = (torch.randn(m, k, generator=g) * 0.5).to(dtype)
+    b = (torch.randn(k, n, generator=g) * 0.5).to(dtype)
+    bd = b.t().contiguous().cuda() if transposed else b.cuda()
+    c = torch.full((m, n + 3), float("nan"), device="cuda")            # a pitch of its own
+    kernels.gemm_acc32(a.cuda(), bd, c, m, n, k, k, k if transposed else n, n + 3, transposed)
+    torch.cuda.synchronize()
+    want = a.double() @ b.double()
+    got = c[:, :n].cpu().double()
+    assert ((got - want).norm() / want.norm()).item() < 1e-6          # fp32 sums of exact products
+    assert torch.isnan(c[:, n:]).all()
