@@ -141,6 +141,39 @@ def matmul(a, b, c=None):
     return c
 
 
+@newt.jit
+def linear_bias_relu_kernel(a_ptr, b_ptr, bias_ptr, c_ptr, M, N, K, sam, sak, sbk, sbn, scm, scn,
+                            BLOCK_M: nl.constexpr, BLOCK_N: nl.constexpr, BLOCK_K: nl.constexpr):
+    """relu(A @ B + bias): the matmul of examples/04_matmul.py:22-45 with an epilogue fused after
+    the k loop (as tests/test_ops.py:458-473 does with arithmetic and a reduction)."""
+    offs_m = nl.program_id(0) * BLOCK_M + nl.arange(0, BLOCK_M)
+    offs_n = nl.program_id(1) * BLOCK_N + nl.arange(0, BLOCK_N)
+    offs_k = nl.arange(0, BLOCK_K)
+    a_ptrs = a_ptr + offs_m[:, None] * sam + offs_k[None, :] * sak
+    b_ptrs = b_ptr + offs_k[:, None] * sbk + offs_n[None, :] * sbn
+    acc = nl.zeros((BLOCK_M, BLOCK_N), dtype=nl.float32)
+    for k in range(nl.cdiv(K, BLOCK_K)):
+        a = nl.load(a_ptrs, mask=(offs_m[:, None] < M) & (offs_k[None, :] < K - k * BLOCK_K), other=0.0)
+        b = nl.load(b_ptrs, mask=(offs_k[:, None] < K - k * BLOCK_K) & (offs_n[None, :] < N), other=0.0)
+        acc = nl.dot(a, b, acc)
+        a_ptrs += BLOCK_K * sak
+        b_ptrs += BLOCK_K * sbk
+    bias = nl.load(bias_ptr + offs_n, mask=offs_n < N, other=0.0)
+    out = nl.maximum(acc + bias[None, :], 0.0)
+    nl.store(c_ptr + offs_m[:, None] * scm + offs_n[None, :] * scn, out.to(c_ptr.dtype.element_ty),
+             mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+
+def linear_bias_relu(a, b, bias, c=None, BLOCK_M=256, BLOCK_N=256, BLOCK_K=64, num_stages=7):
+    m, k = a.shape
+    _, n = b.shape
+    c = torch.empty(m, n, device=a.device, dtype=a.dtype) if c is None else c
+    linear_bias_relu_kernel[(newt.cdiv(m, BLOCK_M), newt.cdiv(n, BLOCK_N))](
+        a, b, bias, c, m, n, k, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0),
+        c.stride(1), BLOCK_M=BLOCK_M, BLOCK_N=BLOCK_N, BLOCK_K=BLOCK_K, num_stages=num_stages)
+    return c
+
+
 # examples/05_fused_attention.py:14-48 of the reference, with a batch*head grid axis and an
 # optional causal mask (both written with operations that example already uses).
 @newt.jit

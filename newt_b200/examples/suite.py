@@ -104,6 +104,21 @@ def bench_matmul_tf32(quick):
     return out
 
 
+def bench_matmul_epilogue(quick):
+    """relu(A @ B + bias) in bf16: tensor-core product into an fp32 buffer plus a generated
+    epilogue kernel, against torch's matmul + add + relu (three launches)."""
+    out = ["| kernel | M=N=K | newt_b200 TFLOP/s | torch TFLOP/s | ratio |", "|---|---|---|---|---|"]
+    for n in ([2048] if quick else [2048, 4096, 8192]):
+        a_ = (torch.randn(n, n, device="cuda") / n ** 0.5).bfloat16()
+        b_ = (torch.randn(n, n, device="cuda") / n ** 0.5).bfloat16()
+        bias = torch.randn(n, device="cuda")
+        c = torch.empty(n, n, device="cuda", dtype=torch.bfloat16)
+        a = testing.do_bench(lambda: K.linear_bias_relu(a_, b_, bias, c))
+        b = testing.do_bench(lambda: torch.relu_(torch.matmul(a_, b_, out=c).add_(bias)))
+        out.append(_row("relu(A@B+bias) bf16", n, a, b, 2 * n ** 3 / 1e9))
+    return out
+
+
 def bench_attention(quick):
     out = ["| kernel | B x H x S x D | newt_b200 TFLOP/s | torch SDPA TFLOP/s | ratio |",
            "|---|---|---|---|---|"]
@@ -122,7 +137,8 @@ def bench_attention(quick):
 
 
 SUITES = {"add": bench_add, "fused": bench_fused, "softmax": bench_softmax, "layernorm": bench_layernorm,
-          "matmul": bench_matmul, "matmul_tf32": bench_matmul_tf32, "attention": bench_attention}
+          "matmul": bench_matmul, "matmul_tf32": bench_matmul_tf32,
+          "matmul_epilogue": bench_matmul_epilogue, "attention": bench_attention}
 
 
 def main():

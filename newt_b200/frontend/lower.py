@@ -953,7 +953,14 @@ class GemmEpiloguePlan(Plan):
 
     def __init__(self, trace, gemm, acc, c_ptr, num_warps):
         self.gemm = gemm
-        self.epilogue = PointwisePlan(trace, num_warps, {acc: ("nb_acc", c_ptr)})
+        # The epilogue streams a BLOCK_M x BLOCK_N tile per program through HBM once; the
+        # kernel's num_warps was chosen for the k loop.  Eight elements per thread keep enough
+        # loads in flight: up to 32 warps for the tiles a tensor-core matmul uses.
+        bm, bn, _ = gemm.block
+        warps = num_warps
+        while warps < 32 and warps * 32 * 8 < bm * bn:
+            warps *= 2
+        self.epilogue = PointwisePlan(trace, warps, {acc: ("nb_acc", c_ptr)})
         self._buffers = {}
 
     def hardware_key(self):
@@ -1207,18 +1214,13 @@ class PointwisePlan(Plan):
         return ("pointwise", self.kernel_name, self.num_warps)
 
     def launch(self, grid, args):
-        import torch
-
-        from ..runtime import nvrtc
+        from ..runtime import kernels, nvrtc
 
         if self._kernel is None:
             self._kernel = nvrtc.Kernel(
                 nvrtc.compile_cubin_cached(self.source, self.kernel_name + ".cu"), self.kernel_name)
-        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
-        stream = raw(torch.cuda.current_device()) if raw is not None \
-            else torch.cuda.current_stream().cuda_stream
         self._kernel.launch(grid, self.num_warps * 32, pointwise.marshal(self.params, args),
-                            stream, self.shared_bytes)
+                            kernels.raw_stream(), self.shared_bytes)
 
 
 def _lower_gemm_epilogue(trace, an, num_stages, num_warps):

@@ -1205,8 +1205,9 @@ def marshal(params, args):
         v = args[name]
         if isinstance(t, tp.pointer_type):
             out.append(ctypes.c_void_p(v.data_ptr()))
-        elif t.name in _CTYPES:
-            out.append(_CTYPES[t.name](v))
         else:
-            raise TypeError(f"argument '{name}': scalars of type {t.name} cannot be passed to a kernel")
+            ctype = _CTYPES.get(t.name)
+            if ctype is None:
+                raise TypeError(f"argument '{name}': scalars of type {t.name} cannot be passed to a kernel")
+            out.append(ctype(v))
     return out

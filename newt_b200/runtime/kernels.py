@@ -17,6 +17,13 @@ _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 _trust = threading.local()     # .checked: the JIT launcher has verified the tensors of this launch
 
 
+def raw_stream():
+    """The current stream of the current device as an integer handle."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
+
+
 def _stream():
     if _raw_stream is not None:      # the handle without building a torch.cuda.Stream object
         return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))

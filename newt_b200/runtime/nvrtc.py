@@ -180,16 +180,15 @@ class Kernel:
         `shared_bytes`: dynamic shared memory (above 48 KB the function is opted in first)."""
         import torch
 
-        cu = _load_cuda()
-        fn = self._function()
+        cu = _cuda or _load_cuda()
         dev = torch.cuda.current_device()
+        fn = self._functions.get(dev) or self._function()
         if shared_bytes > 48 * 1024 and self._shared.get(dev, 0) < shared_bytes:
             # CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES = 8
             _check(cu.cuFuncSetAttribute(fn, 8, ctypes.c_int(shared_bytes)), "cuFuncSetAttribute")
             self._shared[dev] = shared_bytes
         g = tuple(grid) + (1,) * (3 - len(grid))
         b = (block, 1, 1) if isinstance(block, int) else tuple(block) + (1,) * (3 - len(block))
-        ptrs = (ctypes.c_void_p * len(args))(*[ctypes.cast(ctypes.pointer(a), ctypes.c_void_p)
-                                               for a in args])
+        ptrs = (ctypes.c_void_p * len(args))(*map(ctypes.addressof, args))
         _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], b[0], b[1], b[2], shared_bytes, ctypes.c_void_p(stream),
                                  ptrs, None), f"launch of {self.func_name}")
