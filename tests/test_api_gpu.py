@@ -541,3 +541,28 @@ def test_runtime_cuda_kernel_launches_raw_source():
              stream=torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     torch.testing.assert_close(out.cpu(), 2.5 * x + y, rtol=1e-6, atol=1e-6)
+
+
+@dt.kernel(config={"BLOCK_TILE_M": 128, "BLOCK_TILE_N": 128, "BLOCK_TILE_K": 64, "num_stages": 4})
+def dt_linear_relu(x, y, bias, out):
+    for tile_m, tile_n in dt.tile([x.shape[0], y.shape[1]]):
+        acc = dt.zeros([tile_m, tile_n], dtype=dt.float32)
+        for tile_k in dt.tile(x.shape[1]):
+            acc += x[tile_m, tile_k] @ y[tile_k, tile_n]
+        out[tile_m, tile_n] = dt.relu(acc + bias[tile_n][None, :])
+
+
+def test_deuteron_matmul_with_epilogue():
+    """A tile loop whose accumulator goes through bias + relu before the store: the product
+    runs on the tensor core, the epilogue as a generated kernel; checked against the kernel's
+    own eager run and against fp64."""
+    x, y = _rand((300, 200), 61, torch.float16, 0.5), _rand((200, 264), 62, torch.float16, 0.5)
+    bias = _rand((264,), 63)
+    out = torch.full((300, 264), float("nan"), device="cuda", dtype=torch.float16)
+    dt_linear_relu(x.cuda(), y.cuda(), bias.cuda(), out)
+    torch.cuda.synchronize()
+    eager = torch.empty(300, 264, dtype=torch.float16)
+    dt_linear_relu.ref(x, y, bias, eager)
+    want = torch.relu(x.double() @ y.double() + bias.double())
+    torch.testing.assert_close(out.cpu().double(), want, rtol=2 ** -10, atol=2e-3)
+    torch.testing.assert_close(out.cpu().float(), eager.float(), rtol=2e-3, atol=2e-3)

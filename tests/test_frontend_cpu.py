@@ -367,6 +367,33 @@ def test_deuteron_mean_counts_valid_lanes_only():
     torch.testing.assert_close(out, x - x.mean(1, keepdim=True))
 
 
+@dt.kernel
+def dt_linear_relu(x, y, bias, out):
+    for tile_m, tile_n in dt.tile([x.shape[0], y.shape[1]]):
+        acc = dt.zeros([tile_m, tile_n], dtype=dt.float32)
+        for tile_k in dt.tile(x.shape[1]):
+            acc += x[tile_m, tile_k] @ y[tile_k, tile_n]
+        out[tile_m, tile_n] = dt.relu(acc + bias[tile_n][None, :])
+
+
+def test_matmul_with_epilogue_splits_into_product_and_generated_kernel():
+    x, y, bias, out = torch.randn(256, 128).half(), torch.randn(128, 192).half(), torch.randn(192), \
+        torch.empty(256, 192).half()
+    ks = dt_linear_relu._source_for((x, y, bias, out))
+    grid, pos, kw = dt_linear_relu._call_parts(ks, (x, y, bias, out),
+                                               dt.Config(BLOCK_TILE_M=128, BLOCK_TILE_N=64, BLOCK_TILE_K=64))
+    types = [P(tp.TORCH_TO_NEWT[str(a.dtype)]) if torch.is_tensor(a) else a for a in pos]
+    plan = dt_linear_relu._jit.specialize(*types, **kw).plan
+    assert isinstance(plan, lower.GemmEpiloguePlan) and grid == (2, 3)
+    assert isinstance(plan.gemm, lower.GemmPlan) and plan.gemm.c == "out_ptr"
+    src = plan.epilogue.source
+    assert "float* __restrict__ nb_acc" in src and "nb_acc[" in src and "fmaf(" not in src
+    # the plain matmul still takes the one-kernel plan
+    c = rk.matmul_kernel.specialize(F16, F16, F16, 64, 64, 64, 64, 1, 64, 1, 64, 1,
+                                    BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    assert type(c.plan) is lower.GemmPlan
+
+
 def test_deuteron_eager_reference_runs_on_host_tensors():
     x, y = torch.randn(64, 48).half(), torch.randn(48, 32).half()
     out = torch.empty(64, 32).half()
