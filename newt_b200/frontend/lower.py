@@ -961,7 +961,10 @@ class GemmEpiloguePlan(Plan):
         while warps < 32 and warps * 32 * 8 < bm * bn:
             warps *= 2
         self.epilogue = PointwisePlan(trace, warps, {acc: ("nb_acc", c_ptr)})
-        self._buffers = {}
+        self._buffers = {}      # device -> fp32 buffer, kept and grown; launches on one stream
+                                # are ordered, overlapping ones on other streams are the caller's
+        self._whole = lambda: PointwisePlan(trace, num_warps)    # the program in one generated kernel
+        self._whole_plan = None
 
     def hardware_key(self):
         return ("gemm+epilogue",) + self.gemm.hardware_key() + (self.epilogue.kernel_name,)
@@ -969,6 +972,10 @@ class GemmEpiloguePlan(Plan):
     def launch(self, grid, args):
         import torch
 
+        from ..runtime import abi
+
+        if self._whole_plan is not None:
+            return self._whole_plan.launch(grid, args)
         c = args[self.gemm.c]
         m, n, _ = self.gemm._extents(grid, args)
         if m == 0 or n == 0:
@@ -979,7 +986,16 @@ class GemmEpiloguePlan(Plan):
         buf = self._buffers.get(dev)
         if buf is None or buf.numel() < need:
             buf = self._buffers[dev] = torch.empty(need, dtype=torch.float32, device=c.device)
-        self.gemm._launch_tensor_core(grid, args, acc32=buf)
+        try:
+            self.gemm._launch_tensor_core(grid, args, acc32=buf)
+        except (CompileError, abi.UnsupportedError) as e:
+            # a layout the tensor-core path does not take (C not unit-stride along its rows)
+            try:
+                self._whole_plan = self._whole()
+            except pointwise.Unsupported as second:
+                raise CompileError(f"{e}; and the generic lowering does not take the program "
+                                   f"either: {second}") from e
+            return self._whole_plan.launch(grid, args)
         self.epilogue.launch(grid, {**args, "nb_acc": buf})
 
 
