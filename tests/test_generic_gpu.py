@@ -127,3 +127,26 @@ def test_gemm_acc32_keeps_the_accumulator(dtype, transposed):
     got = c[:, :n].cpu().double()
     assert ((got - want).norm() / want.norm()).item() < 1e-6          # fp32 sums of exact products
     assert torch.isnan(c[:, n:]).all()
+
+
+def test_epilogue_matmul_with_a_transposed_result_takes_the_one_kernel_path():
+    """C written with unit stride down its columns: the tensor-core kernels do not store that
+    way, so the whole program (k loop and epilogue) runs as one generated kernel."""
+    from newt_b200.examples import kernels as K
+    from newt_b200.frontend.lower import GemmEpiloguePlan
+
+    m, n, k = 64, 96, 64
+    g = torch.Generator().manual_seed(8)
+    a = (torch.randn(m, k, generator=g) * 0.5).half()
+    b = (torch.randn(k, n, generator=g) * 0.5).half()
+    bias = torch.randn(n, generator=g)
+    ad, bd, biasd = a.cuda(), b.cuda(), bias.cuda()
+    ct = torch.full((n, m), float("nan"), device="cuda", dtype=torch.float16)
+    meta = dict(BLOCK_M=32, BLOCK_N=32, BLOCK_K=32)
+    args = (ad, bd, biasd, ct, m, n, k, k, 1, n, 1, 1, m)
+    K.linear_bias_relu_kernel[(2, 3)](*args, **meta)
+    torch.cuda.synchronize()
+    plan = K.linear_bias_relu_kernel.specialize(*args, **meta).plan
+    assert isinstance(plan, GemmEpiloguePlan) and plan._whole_plan is not None
+    want = torch.relu(a.float() @ b.float() + bias)
+    torch.testing.assert_close(ct.t().cpu().float(), want, rtol=2e-3, atol=2e-3)
