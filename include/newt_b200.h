@@ -149,7 +149,10 @@ int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n,
  * counts 32 more, see nb200_gemm_tf32_workspace_bytes); larger ones are refused with
  * NB200_E_UNSUPPORTED and the limit in the message.  The call allocates nothing.  Its first
  * call on a device looks up the array's device address (once per device; make that first
- * call outside any stream capture).  All calls on a device share the array and each
+ * call outside any stream capture).  The address is remembered per device ordinal, for the
+ * device's primary context (the one the CUDA runtime and torch use): it is not valid after a
+ * cudaDeviceReset, nor for a second context created on the same device through the driver
+ * API.  All calls on a device share the array and each
  * overwrites what the last one left there -- nothing in it needs clearing, the product reads
  * only what its own transposing pass wrote -- so two calls that overlap on the GPU (different
  * streams, no dependency between them) race; calls on one stream are ordered and safe. */

@@ -783,12 +783,15 @@ class GemmPlan(Plan):
         the CUDA cores."""
         from ..runtime import abi
 
-        if self._generic_plan is None:
-            try:
-                return self._launch_tensor_core(grid, args)
-            except (CompileError, abi.UnsupportedError) as e:
-                if self.generic is None:
-                    raise
+        # The choice is made per launch: strides are run-time values of one specialization, so
+        # a launch the tensor core refuses says nothing about the next one.  The generic plan
+        # is compiled at the first refusal and kept for later ones.
+        try:
+            return self._launch_tensor_core(grid, args)
+        except (CompileError, abi.UnsupportedError) as e:
+            if self.generic is None:
+                raise
+            if self._generic_plan is None:
                 try:
                     self._generic_plan = self.generic()
                 except CompileError as second:
@@ -961,8 +964,6 @@ class GemmEpiloguePlan(Plan):
         while warps < 32 and warps * 32 * 8 < bm * bn:
             warps *= 2
         self.epilogue = PointwisePlan(trace, warps, {acc: ("nb_acc", c_ptr)})
-        self._buffers = {}      # device -> fp32 buffer, kept and grown; launches on one stream
-                                # are ordered, overlapping ones on other streams are the caller's
         self._whole = lambda: PointwisePlan(trace, num_warps)    # the program in one generated kernel
         self._whole_plan = None
 
@@ -974,27 +975,26 @@ class GemmEpiloguePlan(Plan):
 
         from ..runtime import abi
 
-        if self._whole_plan is not None:
-            return self._whole_plan.launch(grid, args)
         c = args[self.gemm.c]
         m, n, _ = self.gemm._extents(grid, args)
         if m == 0 or n == 0:
             return
         ldc = self.gemm.ldc(args)
-        need = (m - 1) * ldc + n
-        dev = c.device.index if c.device.index is not None else torch.cuda.current_device()
-        buf = self._buffers.get(dev)
-        if buf is None or buf.numel() < need:
-            buf = self._buffers[dev] = torch.empty(need, dtype=torch.float32, device=c.device)
+        # The fp32 buffer comes from torch's caching allocator per launch: it is allocated,
+        # written and read on the current stream, so launches on different streams never share
+        # one, and the allocator reuses the block on this stream without touching the driver.
+        buf = torch.empty(max((m - 1) * ldc + n, 1), dtype=torch.float32, device=c.device)
         try:
             self.gemm._launch_tensor_core(grid, args, acc32=buf)
         except (CompileError, abi.UnsupportedError) as e:
-            # a layout the tensor-core path does not take (C not unit-stride along its rows)
-            try:
-                self._whole_plan = self._whole()
-            except pointwise.Unsupported as second:
-                raise CompileError(f"{e}; and the generic lowering does not take the program "
-                                   f"either: {second}") from e
+            # a layout the tensor-core path does not take (C not unit-stride along its rows);
+            # decided per launch, the one-kernel plan is compiled once and kept
+            if self._whole_plan is None:
+                try:
+                    self._whole_plan = self._whole()
+                except pointwise.Unsupported as second:
+                    raise CompileError(f"{e}; and the generic lowering does not take the program "
+                                       f"either: {second}") from e
             return self._whole_plan.launch(grid, args)
         self.epilogue.launch(grid, {**args, "nb_acc": buf})
 

@@ -170,24 +170,32 @@ class JITFunction:
 
     # ---- launch --------------------------------------------------------------------
 
+    def _fast_key(self, bound, num_warps, num_stages):
+        """Key under which a launch finds its specialization without type inference: the
+        constexpr values and, per runtime argument, what its type is inferred from (the torch
+        dtype, int32 vs int64 by value, float) -- newt/runtime/jit.py:99-144 keys the same
+        way.  A constexpr is keyed with its type: 2, 2.0 and True compare (and hash) equal in
+        Python but select different specializations (the reference keys on repr, :177-183).
+        None for an unhashable constexpr value."""
+        parts = [(type(v), v) if c else
+                 ((32 if -2147483648 <= v < 2147483648 else 64) if type(v) is int else
+                  (type(v) if type(v) in (float, bool) else getattr(v, "dtype", type(v))))
+                 for v, c in zip(map(bound.__getitem__, self.param_names), self._is_constexpr)]
+        key = (tuple(parts), num_warps, num_stages)
+        try:
+            hash(key)
+        except TypeError:
+            return None
+        return key
+
     def _run(self, grid, *args, **kwargs):
         import torch
 
         num_warps = kwargs.pop("num_warps", 4)
         num_stages = kwargs.pop("num_stages", 3)
         bound = self._bind(args, kwargs)
-        # Launches of a specialization seen before skip type inference: the key holds the
-        # constexpr values and, per runtime argument, what its type is inferred from (the torch
-        # dtype, int32 vs int64 by value, float) -- newt/runtime/jit.py:99-144 keys the same way.
-        parts = [v if c else
-                 ((32 if -2147483648 <= v < 2147483648 else 64) if type(v) is int else
-                  (type(v) if type(v) in (float, bool) else getattr(v, "dtype", type(v))))
-                 for v, c in zip(map(bound.__getitem__, self.param_names), self._is_constexpr)]
-        try:
-            key = (tuple(parts), num_warps, num_stages)
-            hit = self._fast.get(key)
-        except TypeError:          # an unhashable constexpr value
-            key, hit = None, None
+        key = self._fast_key(bound, num_warps, num_stages)
+        hit = self._fast.get(key) if key is not None else None
         if hit is None:
             compiled, _, runtime_types = self._specialization(bound, num_warps, num_stages)
             tensors = [n for n, t in runtime_types.items() if isinstance(t, tp.pointer_type)]

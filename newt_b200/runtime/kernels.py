@@ -2,7 +2,10 @@
 torch's current stream.  These are what the lowering plans of the JIT front end
 call; they add nothing to the arithmetic.  Like the reference launcher
 (newt/runtime/jit.py:190-223) they refuse tensors that are not on the current
-CUDA device and they never allocate.
+CUDA device.  Three of them need scratch memory beside the caller's tensors (the transposed
+copy of an fp32 B, a re-pitched copy of an operand bulk tensor copies cannot fetch): they take it
+from torch's caching allocator per launch, on the current stream, so launches on different
+streams never share a buffer; the others never allocate.
 """
 
 import ctypes
@@ -88,22 +91,13 @@ def gemm_bt(a, bt, c, m, n, k, lda, ldbt, ldc, config=None):
                                        abi.dtype_code(a.dtype), cfg, _stream()))
 
 
-_tf32_workspaces = {}   # device index -> uint8 tensor, grown on demand
-
-
 def gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, config=None):
     """fp32 C = A @ B (tf32 product, fp32 accumulation) with B as [K, N].  The tensor core
     reads tf32 operands K-major only, so B is transposed into a workspace first.  The workspace
-    is a torch tensor kept per device and grown when a larger B comes along; work queued on
-    other streams that still uses it is the caller's to order, as with any reused buffer."""
-    import torch
-
+    is a fresh tensor of torch's caching allocator: allocated and used on the current stream,
+    so the allocator's stream-ordered reuse keeps concurrent launches apart."""
     need = int(abi.load().nb200_gemm_tf32_workspace_bytes(int(n), int(k)))
-    dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
-    ws = _tf32_workspaces.get(dev)
-    if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=a.device)
-        _tf32_workspaces[dev] = ws
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=a.device)
     cfg = ctypes.byref(config) if config is not None else None
     abi.check(abi.load().nb200_gemm_tf32(_dev_ptr("a", a), _dev_ptr("b", b), _dev_ptr("c", c), int(m),
                                          int(n), int(k), int(lda), int(ldb), int(ldc), cfg,
@@ -119,23 +113,15 @@ def gemm_acc32(a, b, c, m, n, k, lda, ldb, ldc, b_transposed=False, config=None)
                                           _stream()))
 
 
-_repitch_workspaces = {}
-
-
 def repitched(slot, t, rows, cols, row_stride, col_stride):
     """A row-major copy of the [rows, cols] matrix that starts at `t` with the given strides
-    (in elements), in a per-device workspace for `slot` ("a" or "b") that is kept and grown as
-    needed; returns (workspace tensor of t's dtype, pitch in elements).  The pitch is a
-    multiple of 16 bytes, which is what the tensor-core GEMM needs of its operands.  Work
-    queued on other streams that still reads the workspace is the caller's to order."""
+    (in elements), as a fresh tensor of torch's caching allocator (allocated and used on the
+    current stream); returns (tensor of t's dtype, pitch in elements).  The pitch is a multiple
+    of 16 bytes, which is what the tensor-core GEMM needs of its operands.  `slot` ("a" or "b")
+    only names the operand in error messages."""
     eb = t.element_size()
     pitch = -(-int(cols) // (16 // eb)) * (16 // eb)
-    need = max(int(rows) * pitch, 16)
-    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
-    ws = _repitch_workspaces.get((dev, slot, t.dtype))
-    if ws is None or ws.numel() < need:
-        ws = torch.empty(need, dtype=t.dtype, device=t.device)
-        _repitch_workspaces[(dev, slot, t.dtype)] = ws
+    ws = torch.empty(max(int(rows) * pitch, 16), dtype=t.dtype, device=t.device)
     abi.check(abi.load().nb200_repitch(_dev_ptr(slot, t), ctypes.c_void_p(ws.data_ptr()), int(rows),
                                        int(cols), int(row_stride), int(col_stride), pitch, eb,
                                        _stream()))

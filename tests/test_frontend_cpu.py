@@ -473,3 +473,24 @@ def test_cubins_are_cached_on_disk(tmp_path, monkeypatch):
     cubin.write_bytes(b"junk")
     nvrtc.compile_cubin_cached(src, "twice.cu")
     assert len(calls) == 2
+
+
+def test_constexpr_values_of_different_types_are_different_specializations():
+    """2, 2.0 and True are equal (and hash alike) in Python; as constexprs they select integer,
+    float and boolean arithmetic, so neither the specialization cache nor the launcher's fast
+    key may fold them together (reference keys on repr: newt/runtime/jit.py:177-183)."""
+    import newt_b200 as newt
+    import newt_b200.language as nl
+
+    @newt.jit
+    def scaled(x_ptr, out_ptr, n, SCALE: nl.constexpr, BLOCK: nl.constexpr):
+        offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        mask = offs < n
+        nl.store(out_ptr + offs, nl.load(x_ptr + offs, mask=mask) * SCALE, mask=mask)
+
+    compiled = [scaled.specialize(F32, F32, 100, SCALE=s, BLOCK=128) for s in (2, 2.0, True)]
+    assert len({id(c) for c in compiled}) == 3 and len(scaled.cache) == 3
+    keys = [scaled._fast_key(scaled._bind((F32, F32, 100), {"SCALE": s, "BLOCK": 128}), 4, 3)
+            for s in (2, 2.0, True)]
+    assert len(set(keys)) == 3
+    assert scaled._fast_key(scaled._bind((F32, F32, 100), {"SCALE": [1], "BLOCK": 128}), 4, 3) is None

@@ -64,6 +64,61 @@ def test_static_scratch_matches_the_workspace_entry_point_twice_in_a_row():
         assert torch_ref.rel_frobenius(got.cpu(), a.double().cpu() @ b.double().cpu()) <= 2e-3
 
 
+def _free_bytes():
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]     # cudaMemGetInfo: what the driver has left
+
+
+def test_static_scratch_allocates_nothing():
+    """The property in the entry point's name: device memory the driver has free, and what
+    torch's allocator holds, are the same before and after calls (the first call on a device
+    only looks up the address of the built-in array)."""
+    g = torch.Generator().manual_seed(78)
+    m, n, k = 256, 512, 768
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).cuda()
+    b = torch.randn(k, n, generator=g).cuda()
+    got = torch.empty(m, n, device="cuda")
+    abi.check(_static(a, b, got))           # first call in a fresh process: address look-up
+    free0, held0, reserved0 = _free_bytes(), torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(3):
+        abi.check(_static(a, b, got))
+    assert _free_bytes() == free0
+    assert torch.cuda.memory_allocated() == held0 and torch.cuda.memory_reserved() == reserved0
+    assert abi.read_status() == (0, 0)
+    assert torch_ref.rel_frobenius(got.cpu(), a.double().cpu() @ b.double().cpu()) <= 2e-3
+
+
+def test_static_scratch_with_a_misaligned_b():
+    """B one element off a 16-byte boundary: the transposing pass reads it element by element."""
+    g = torch.Generator().manual_seed(79)
+    m, n, k = 128, 200, 96
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).cuda()
+    flat = torch.randn(k * n + 1, generator=g).cuda()
+    b = flat[1:].view(k, n)
+    assert b.data_ptr() % 16 == 4
+    got = torch.full((m, n), float("nan"), device="cuda")
+    abi.check(_static(a, b, got))
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    assert torch_ref.rel_frobenius(got.cpu(), a.double().cpu() @ b.double().cpu()) <= 2e-3
+
+
+def test_static_scratch_limit_when_k_is_a_multiple_of_8192():
+    """Such a k is stored with a pitch 32 floats longer, so n = 128 no longer fits, n = 127 does."""
+    k = 8192
+    a = torch.zeros(128, k, device="cuda")
+    for n, fits in ((128, False), (127, True)):
+        b = torch.zeros(k, n, device="cuda")
+        c = torch.full((128, n), 7.0, device="cuda")
+        rc = _static(a, b, c)
+        torch.cuda.synchronize()
+        if fits:
+            abi.check(rc)
+            assert torch.all(c == 0.0)
+        else:
+            assert rc == abi.E_UNSUPPORTED and torch.all(c == 7.0)
+
+
 def test_static_scratch_refuses_what_does_not_fit():
     k, n = 1024, 1028                       # 1028 * 1024 floats: just over the limit
     assert n * k > LIMIT_FLOATS
