@@ -724,7 +724,6 @@ def measure(ctx, args, wl):
     ctx.barrier()
     step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     total_ms = sum(step_ms)
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- parity of the very tensors that were just timed ----------------------
     torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
@@ -753,6 +752,7 @@ def measure(ctx, args, wl):
         rotating_ms = r0.elapsed_time(r1) / reps
         del sets
         floor_ms = protocol_floor_ms(ctx, wl.units_per_step())
+    clocks = sampler.stop() if rank == 0 else None     # sampled over the device-timed regions
 
     # ---- end-to-end region: pinned host -> device, step, result -> host -------
     out_host = _pin(torch.empty(wl.result(dev).shape, dtype=wl.result(dev).dtype))

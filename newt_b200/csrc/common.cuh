@@ -28,6 +28,10 @@ const DeviceInfo& device_info();
 // Integer knobs set through nb200_set_tuning(); returns `dflt` when unset (0).
 int tuning(const char* key, int dflt);
 
+// How long one device-side wait may spin before the kernel gives up, in nanoseconds: the
+// "wait_limit_us" knob of nb200_set_tuning(), 2 s when unset.
+unsigned long long wait_limit_ns();
+
 // Per-device status words written by kernels whose bounded waits expire.
 // [0] = first error code (0 = none), [1] = detail (role / barrier / tile).
 unsigned int* device_status_ptr();

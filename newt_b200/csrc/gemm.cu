@@ -122,6 +122,7 @@ struct GemmParams {
   int c_vec_ok;  // C base and row pitch are 16-byte aligned
   int b_kmajor;  // B is given transposed ([N, K], K contiguous); always so for tf32
   int c_f32;     // 16-bit operands, but C takes the fp32 accumulator unrounded
+  unsigned long long wait_limit_ns;
   unsigned int* status;
 };
 
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1 KB
-  const WaitCtx ctx{&abort_flag, p.status};
+  const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -359,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t rank = cluster_cta_rank();
   const bool leader = rank == 0;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const WaitCtx ctx{&abort_flag, p.status};
+  const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -857,6 +858,7 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   p.b_kmajor = b_kmajor ? 1 : 0;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * cb) % 16 == 0) ? 1 : 0;
   p.c_f32 = c_f32 ? 1 : 0;
+  p.wait_limit_ns = wait_limit_ns();
   p.status = device_status_ptr();
   if (!p.status) return fail(NB200_E_CUDA, "gemm: device status word is not addressable");
 

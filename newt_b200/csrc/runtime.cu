@@ -55,6 +55,10 @@ int tuning(const char* key, int dflt) {
   return (it == g_tuning.end() || it->second == 0) ? dflt : it->second;
 }
 
+unsigned long long wait_limit_ns() {
+  return 1000ull * (unsigned long long)tuning("wait_limit_us", 2000000);
+}
+
 unsigned int* device_status_ptr() {
   // the symbol has one instance per device context: resolved once per device
   static std::map<int, unsigned int*> known;

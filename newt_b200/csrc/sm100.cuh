@@ -2,8 +2,9 @@
 // tcgen05 (tensor memory allocation, MMA issue, commit, TMEM loads) and the
 // shared-memory / instruction descriptors tcgen05.mma consumes.
 //
-// Every wait here is bounded: a spin gives up after kWaitLimitNs, records a
-// code in the per-device status word and tells the rest of the CTA to leave.
+// Every wait here is bounded: a spin gives up after WaitCtx::limit_ns (2 s unless the
+// "wait_limit_us" tuning knob says otherwise), records a code in the per-device status word
+// and tells the rest of the CTA to leave.
 #pragma once
 
 #include <cuda.h>
@@ -12,8 +13,6 @@
 
 namespace nb200 {
 namespace sm100 {
-
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -66,23 +65,24 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// What a role needs to give up cleanly: the CTA-wide abort flag and the
-// device status word.
+// What a role needs to give up cleanly: the CTA-wide abort flag, the device status word and
+// how long one wait may last.
 struct WaitCtx {
   volatile uint32_t* abort_flag;  // shared memory
   unsigned int* status;           // global, 4 words
+  unsigned long long limit_ns;    // per wait
 };
 
 // Waits for the phase with the given parity.  Returns false when the CTA is
 // aborting or when the wait ran out of time (recorded with `code`).
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                            unsigned int code, unsigned int detail) {
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                          unsigned int code, unsigned int detail) {
   const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xff) == 0) {
       if (*ctx.abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > ctx.limit_ns) {
         *ctx.abort_flag = 1;
         if (atomicCAS(&ctx.status[0], 0u, code) == 0u) ctx.status[1] = detail;
         __threadfence();
@@ -92,10 +92,22 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
   }
   return true;
 }
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                                   unsigned int code, unsigned int detail) {
+  return mbar_spin(bar, parity, ctx, code, detail);
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           unsigned int code, unsigned int detail) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, ctx, code, detail);
+}
+// The same with the spin loop in line, for kernels whose warpgroups re-divide the register
+// file (setmaxnreg): ptxas cannot allocate registers for a function call made from a region
+// whose register count was lowered.
+__device__ __forceinline__ bool mbar_wait_nocall(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                                 unsigned int code, unsigned int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_spin(bar, parity, ctx, code, detail);
 }
 
 // Named barriers 1..15 (0 is __syncthreads): `threads` threads take part, as whole warps;

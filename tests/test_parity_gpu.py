@@ -426,3 +426,15 @@ def test_attention_argument_errors():
     with pytest.raises(abi.KernelLibraryError, match="empty key"):
         kernels.attention_fwd(q, e, e, q, 0.1, False)
     kernels.attention_fwd(e, q, q, e, 0.1, False)   # no queries: nothing to do
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("bh,sq,skv,d", [(160, 640, 640, 128), (3, 255, 1000, 128), (5, 129, 257, 64)])
+def test_attention_odd_tile_counts(causal, bh, sq, skv, d):
+    # An odd number of 128-row Q tiles per head (the last pair of a head has one tile only),
+    # fewer than 256 query rows, and several pairs per persistent CTA (160 heads x 3 pairs).
+    g = torch.Generator().manual_seed(bh + sq + skv)
+    q, k, v = (torch.randn(bh, s, d, generator=g).half() for s in (sq, skv, skv))
+    got = _attention(q.cuda(), k.cuda(), v.cuda(), causal).cpu()
+    want = torch_ref.attention(q, k, v, 1.0 / d ** 0.5, causal)
+    assert torch_ref.rel_frobenius(got.float(), want) <= 1e-2
