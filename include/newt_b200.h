@@ -60,8 +60,19 @@ int nb200_read_status(uint32_t* status, uint32_t* detail);
  *   "row_tpr"          threads that cooperate on one row (32,128,256,512,1024)
  *   "row_items"        16-byte vectors each of those threads holds (1,2,4,8)
  *   "row_ctas_per_sm"  resident CTAs per SM of the persistent row grid
- *   "row_rpb"          rows that share one CTA (1, 2 or 4) */
+ *   "row_rpb"          rows that share one CTA (1, 2 or 4)
+ *   "wait_limit_us"    how long one device-side wait (an mbarrier spin of the tensor-core
+ *                      kernels) may last before the kernel gives up, records a code in the
+ *                      status word and returns; 2 000 000 (2 s) when unset */
 int nb200_set_tuning(const char* key, int value);
+
+/* Diagnostic: launches one warp that waits, with the current "wait_limit_us", on a barrier
+ * nothing will ever signal.  The wait runs out, the kernel records status code 6 with
+ * `detail` as given and returns by itself -- nothing traps, nothing spins for ever.  Lets a
+ * caller (and the tests) see the failure path end to end: nb200_read_status() afterwards
+ * reports NB200_E_DEVICE once, then is clean again, and the device stays usable.  No
+ * reference counterpart. */
+int nb200_selftest_wait_timeout(uint32_t detail, void* stream);
 
 /* ---- K0: out = x + y -------------------------------------------------------
  * Replaces the code generated for `add_kernel`

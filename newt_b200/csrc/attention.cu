@@ -16,14 +16,21 @@
 //   warp 1         issues, for both tiles in turn, S_t = Q_t K^T and O_t += P_t V (P read from
 //                  tensor memory, V from shared memory as an MN-major operand: no transpose)
 //   warps 4..7     softmax of tile 0: thread r owns row r -- a TMEM lane -- so row max and
-//   warps 8..11    row sum are register loops, no shuffles (the same for tile 1).  P is
-//                  written over S as packed 16-bit pairs.
+//   warps 8..11    row sum are register loops, no shuffles (the same for tile 1).  The 128
+//                  scores of a row are read from tensor memory once and stay in registers; P
+//                  is written over S as packed 16-bit pairs and handed over in two halves, so
+//                  the first half of the PV product runs under the second half's exponentials.
 //   warps 12..15   epilogue: O_t / l_t -> global, while the softmax warps are already on the
 //                  next pair
+// The warpgroups re-divide the register file (setmaxnreg): 208 registers per softmax thread,
+// 40 and 56 for the others.
 // Tensor memory: S0 | S1 (128 columns each, P_t over the first 64 of S_t) | O0 | O1 = 512.
 // The order in which one thread issues  ... PV_t(j), QK_t(j+1) ...  is the order the tensor core
 // executes them in, so S_t(j+1) lands only after P_t(j) has been read; a softmax group is told
 // "S_t(j) complete" by a commit that also covers PV_t(j-1), so it may rescale O_t right away.
+// One issuer, strictly alternating between the tiles, is what keeps them half a period apart
+// (two issuing warps, one per tile, interleave their products, finish together, and both
+// softmax groups then run -- and wait -- together: measured 25 % slower).
 // The reference maximum that P is scaled against only moves when a block maximum is more than
 // 2^8 above it (exact in effect: the final division by l_i undoes whatever reference point
 // the exponentials used); the row sum is kept in terms of the same reference.

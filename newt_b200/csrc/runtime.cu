@@ -10,7 +10,7 @@
 #include <mutex>
 #include <string>
 
-#include "common.cuh"
+#include "sm100.cuh"
 
 namespace nb200 {
 
@@ -136,6 +136,32 @@ extern "C" int nb200_set_tuning(const char* key, int value) {
   std::lock_guard<std::mutex> lock(g_mutex);
   g_tuning[key] = value;
   return 0;
+}
+
+namespace nb200 {
+namespace {
+// One warp, one barrier that nobody arrives on: the bounded wait runs out and reports.
+__global__ void wait_timeout_kernel(unsigned int* status, unsigned long long limit_ns,
+                                    unsigned int detail) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    sm100::mbar_init(sm100::smem_u32(&bar), 1);
+    sm100::mbar_init_fence();
+  }
+  __syncwarp();
+  const sm100::WaitCtx ctx{&abort_flag, status, limit_ns};
+  sm100::mbar_wait(sm100::smem_u32(&bar), 0, ctx, ST_WAIT_OTHER, detail);
+}
+}  // namespace
+}  // namespace nb200
+
+extern "C" int nb200_selftest_wait_timeout(uint32_t detail, void* stream) {
+  unsigned int* status = device_status_ptr();
+  if (!status) return fail(NB200_E_CUDA, "selftest: device status word is not addressable");
+  wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, wait_limit_ns(), detail);
+  return cuda_check(cudaGetLastError(), "selftest launch");
 }
 
 extern "C" int nb200_read_status(uint32_t* status, uint32_t* detail) {

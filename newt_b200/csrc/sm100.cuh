@@ -450,6 +450,35 @@ __device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigne
   return r;
 }
 
+__device__ __forceinline__ unsigned long long sub2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("sub.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// 2^t for two values at once without the special-function unit: t is split into its nearest
+// integer (adding 1.5 * 2^23 leaves it in the low mantissa bits, from where it is shifted into
+// the exponent field of the result) and a remainder in [-0.5, 0.5], whose power of two is a
+// cubic with a largest relative error of 7.5e-5 (minimax fit).  Arguments are clamped at -125;
+// meant for t <= ~100.  Costs about eleven issue slots on the FMA and integer pipes, none on
+// the unit `ex2.approx` runs on, which is the point: softmax loops are bound by that unit.
+__device__ __forceinline__ void exp2_cubic2(unsigned long long t2, float& pa, float& pb) {
+  const unsigned long long magic2 = pack2(12582912.0f, 12582912.0f);
+  float ta, tb;
+  unpack2(t2, ta, tb);
+  t2 = pack2(fmaxf(ta, -125.0f), fmaxf(tb, -125.0f));
+  const unsigned long long f2 = add2(t2, magic2);
+  const unsigned long long r2 = sub2(t2, sub2(f2, magic2));
+  unsigned long long q2 = fma2(pack2(0.05517146f, 0.05517146f), r2, pack2(0.24261086f, 0.24261086f));
+  q2 = fma2(q2, r2, pack2(0.69326097f, 0.69326097f));
+  q2 = fma2(q2, r2, pack2(0.99992812f, 0.99992812f));
+  float qa, qb, fa, fb;
+  unpack2(q2, qa, qb);
+  unpack2(f2, fa, fb);
+  pa = __uint_as_float(__float_as_uint(qa) + (__float_as_uint(fa) << 23));
+  pb = __uint_as_float(__float_as_uint(qb) + (__float_as_uint(fb) << 23));
+}
+
 __device__ __forceinline__ float exp2_approx(float x) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));

@@ -49,6 +49,7 @@ SIGNATURES = {
     "nb200_read_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32),
                                          ctypes.POINTER(ctypes.c_uint32)]),
     "nb200_set_tuning": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int]),
+    "nb200_selftest_wait_timeout": (ctypes.c_int, [ctypes.c_uint32, _vp]),
     "nb200_add_f32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp]),
     "nb200_softmax_f32": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "nb200_layernorm": (ctypes.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,

@@ -42,3 +42,18 @@ def test_abi_version_and_error_text():
     rc = lib.nb200_softmax_f32(None, None, 4, 4, 4, 4, None)
     assert rc == abi.E_INVALID and "null" in abi.last_error()
     assert lib.nb200_add_f32(None, None, None, 0, None) == 0  # empty input is a no-op
+
+
+def test_status_codes_become_exceptions():
+    """abi.check: 0 passes, NB200_E_UNSUPPORTED has its own type, anything else (a kernel that
+    gave up on a bounded wait reports NB200_E_DEVICE) is a KernelLibraryError with the code."""
+    import pytest
+
+    abi.check(abi.OK)
+    with pytest.raises(abi.UnsupportedError) as e:
+        abi.check(abi.E_UNSUPPORTED)
+    assert e.value.code == abi.E_UNSUPPORTED
+    for code in (abi.E_INVALID, abi.E_CUDA, abi.E_DEVICE):
+        with pytest.raises(abi.KernelLibraryError) as e:
+            abi.check(code)
+        assert e.value.code == code and not isinstance(e.value, abi.UnsupportedError)

@@ -438,3 +438,28 @@ def test_attention_odd_tile_counts(causal, bh, sq, skv, d):
     got = _attention(q.cuda(), k.cuda(), v.cuda(), causal).cpu()
     want = torch_ref.attention(q, k, v, 1.0 / d ** 0.5, causal)
     assert torch_ref.rel_frobenius(got.float(), want) <= 1e-2
+
+
+# ---- bounded waits ----------------------------------------------------------------
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """A kernel waits on a barrier nothing signals, with the limit turned down to 200 us: it
+    returns by itself, the status word says so once, and the next launch is fine."""
+    import ctypes
+
+    lib = abi.load()
+    abi.read_status()                       # start clean
+    abi.set_tuning("wait_limit_us", 200)
+    try:
+        abi.check(lib.nb200_selftest_wait_timeout(0xabc, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        with pytest.raises(abi.KernelLibraryError) as e:
+            abi.read_status()
+        assert e.value.code == abi.E_DEVICE and "code 6" in str(e.value) and "0xabc" in str(e.value)
+    finally:
+        abi.set_tuning("wait_limit_us", 0)  # back to the default
+    assert abi.read_status() == (0, 0)      # reported once, then clear
+    x = torch.randn(64, 1000, device="cuda")
+    out = torch.empty_like(x)
+    kernels.softmax_f32(x, out, 64, 1000, x.stride(0), out.stride(0))
+    torch.testing.assert_close(out, torch.softmax(x, dim=-1), rtol=1e-5, atol=1e-8)
+    assert abi.read_status() == (0, 0)
