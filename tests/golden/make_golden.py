@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 What is recorded, per case, is the seeded input and the reference's own result:
   * `deuteron` eager mode (`Kernel.ref`, deuteron/runtime.py:71-73) of the
@@ -139,4 +139,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of the reference checkout>")
+    main(sys.argv[1])
