@@ -4,51 +4,54 @@
     import newt_b200.language as nl
 
     @newt.jit
-    def add_kernel(x_ptr, y_ptr, out_ptr, n, BLOCK: nl.constexpr):
-        pid = nl.program_id(0)
-        offs = pid * BLOCK + nl.arange(0, BLOCK)
-        mask = offs < n
-        nl.store(out_ptr + offs, nl.load(x_ptr + offs, mask=mask) + nl.load(y_ptr + offs, mask=mask),
-                 mask=mask)
+    def scale_kernel(x_ptr, out_ptr, factor, n, BLOCK: nl.constexpr):
+        lanes = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        inside = lanes < n
+        nl.store(out_ptr + lanes, nl.load(x_ptr + lanes, mask=inside) * factor, mask=inside)
 
-    add_kernel[(newt.cdiv(n, 1024),)](x, y, out, n, BLOCK=1024)
+    scale_kernel[(newt.cdiv(n, 2048),)](x, out, 0.5, n, BLOCK=2048)
 
-The names exported here are the ones newt/__init__.py of the reference exports
-(:18-51).  `install_aliases()` additionally registers this package under the
-module names `newt` and `deuteron`, so kernels written against the reference
-import unchanged.
+Exports the names of newt/__init__.py of the reference (:18-51).  `install_aliases()` also
+registers this package under the module names `newt` and `deuteron`, so kernels written
+against the reference import unchanged.
 """
 
 import sys as _sys
 
 from . import language, testing, types
-from .frontend.trace import CompileError
-from .runtime.autotuner import Autotuner, Config, Heuristics, autotune, heuristics
-from .runtime.jit import JITFunction, jit
+from .frontend import trace as _trace
+from .runtime import autotuner as _autotuner, jit as _jit
 
 __version__ = "0.1.0"
 
+# decorators and the classes behind them
+jit, JITFunction = _jit.jit, _jit.JITFunction
+autotune, heuristics = _autotuner.autotune, _autotuner.heuristics
+Autotuner, Heuristics, Config = _autotuner.Autotuner, _autotuner.Heuristics, _autotuner.Config
+CompileError = _trace.CompileError
+
 
 def cdiv(a, b):
-    return -(-a // b)
+    """Ceiling of a / b for non-negative integers: how many blocks of b cover a."""
+    return (a + b - 1) // b
 
 
 def next_power_of_2(n):
-    n = int(n)
-    return 1 if n <= 1 else 1 << (n - 1).bit_length()
+    """The smallest power of two that is not below n (1 for n <= 1)."""
+    return 1 << max(int(n) - 1, 0).bit_length()
 
 
 def install_aliases():
-    """Makes `import newt`, `import newt.language as nl` and `import deuteron`
-    resolve to this package."""
+    """Registers this package as `newt` (with `newt.language`, `newt.testing`) and its tile
+    language as `deuteron`, unless modules of those names are loaded already."""
     from . import deuteron
 
-    _sys.modules.setdefault("newt", _sys.modules[__name__])
-    _sys.modules.setdefault("newt.language", language)
-    _sys.modules.setdefault("newt.testing", testing)
-    _sys.modules.setdefault("deuteron", deuteron)
+    here = _sys.modules[__name__]
+    for alias, module in (("newt", here), ("newt.language", language), ("newt.testing", testing),
+                          ("deuteron", deuteron)):
+        _sys.modules.setdefault(alias, module)
 
 
-__all__ = ["Autotuner", "CompileError", "Config", "Heuristics", "JITFunction", "__version__",
-           "autotune", "cdiv", "heuristics", "jit", "language", "next_power_of_2", "testing",
-           "install_aliases"]
+__all__ = ("jit", "autotune", "heuristics", "Config", "cdiv", "next_power_of_2", "language",
+           "testing", "JITFunction", "Autotuner", "Heuristics", "CompileError", "install_aliases",
+           "__version__")

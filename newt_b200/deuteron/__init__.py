@@ -1,27 +1,31 @@
-"""deuteron on newt_b200: a PyTorch-like tile DSL compiled to sm_100a kernel launches.
+"""The tile language on top of newt_b200: kernels written over whole tensors and tiles of them,
+compiled to sm_100a launches with tile sizes chosen by a search.
 
     import newt_b200.deuteron as dt
 
     @dt.kernel
-    def matmul(x, y, out):
-        for tile_m, tile_n in dt.tile([x.shape[0], y.shape[1]]):
-            acc = dt.zeros([tile_m, tile_n], dtype=dt.float32)
-            for tile_k in dt.tile(x.shape[1]):
-                acc += x[tile_m, tile_k] @ y[tile_k, tile_n]
-            out[tile_m, tile_n] = acc
+    def row_softmax(x, out):
+        for rows in dt.tile(x.shape[0]):
+            block = x[rows, :]
+            shifted = dt.exp(block - block.amax(1)[:, None])
+            out[rows, :] = shifted / shifted.sum(1)[:, None]
 
-    matmul(x, y, out)                         # trace, autotune, cache, launch
-    matmul.ref(x, y, out)                     # eager PyTorch run of the same body (the oracle)
-    print(matmul.to_newt_source(x, y, out))   # the generated newt kernel
+    row_softmax(x, out)                        # build, pick tile sizes (remembered), launch
+    row_softmax.ref(x, out)                    # the same body as plain PyTorch: the oracle
+    print(row_softmax.to_newt_source(x, out))  # the newt kernel it was turned into
 
-Exports what deuteron/__init__.py of the reference exports (:19-44).
+The public names are those of the reference's `deuteron` package (deuteron/__init__.py:19-44).
 """
 
-from .codegen import TraceError  # noqa: F401
-from .language import (  # noqa: F401
-    EagerTensor, Tile, abs, bfloat16, erf, exp, float16, float32, full, int32, int64, log,
-    maximum, minimum, relu, rsqrt, sigmoid, sqrt, tanh, tile, where, zeros,
-)
-from .runtime import Config, Kernel, kernel  # noqa: F401
+from . import codegen as _codegen, language as _language, runtime as _runtime
 
+TraceError = _codegen.TraceError
+Config, Kernel, kernel = _runtime.Config, _runtime.Kernel, _runtime.kernel
+
+_LANGUAGE_NAMES = ("EagerTensor", "Tile", "tile", "zeros", "full", "where", "maximum", "minimum",
+                   "relu", "exp", "log", "sqrt", "rsqrt", "sigmoid", "tanh", "erf", "abs",
+                   "float32", "float16", "bfloat16", "int32", "int64")
+globals().update({_n: getattr(_language, _n) for _n in _LANGUAGE_NAMES})
+
+__all__ = ["TraceError", "Config", "Kernel", "kernel", *_LANGUAGE_NAMES]
 __version__ = "0.1.0"

@@ -1,55 +1,56 @@
-"""The tile language (`import newt_b200.deuteron as dt`), after deuteron/language.py.
+"""The tile language (`import newt_b200.deuteron as dt`): what a kernel body may call.
 
-Every function here has an eager implementation on torch tensors: calling a
-`@dt.kernel` function with full-size tiles runs it as plain PyTorch.  That eager
-run is the oracle candidate configurations are checked against
-(deuteron/runtime.py:226-231 of the reference) and is exposed as `Kernel.ref`.
+Everything here also works on plain torch tensors, which is what makes a `@dt.kernel`
+function runnable as ordinary PyTorch: called with tiles that span whole dimensions, the
+body computes its result eagerly.  That run is the oracle tile-size candidates are checked
+against and is exposed as `Kernel.ref` (the reference does the same,
+deuteron/language.py:1-8, deuteron/runtime.py:226-231).
 
-One deliberate difference: the reference allocates `dt.zeros` / `dt.full` on a
-hard-coded "cuda" device (deuteron/language.py:83-90), which makes `.ref`
-unusable on host tensors for any kernel with an accumulator.  Here the eager
-allocators follow the device of the tensors the kernel was called with.
+One deliberate difference: the reference allocates `dt.zeros` / `dt.full` on a hard-coded
+"cuda" device (deuteron/language.py:83-90), so `.ref` cannot run on host tensors for any
+kernel with an accumulator.  Here the eager allocators follow the device of the tensors the
+kernel was called with.
 """
 
 import contextlib
 import threading
+from dataclasses import dataclass
 
 import torch
 
-float32 = torch.float32
-float16 = torch.float16
-bfloat16 = torch.bfloat16
-int32 = torch.int32
-int64 = torch.int64
+float32, float16, bfloat16 = torch.float32, torch.float16, torch.bfloat16
+int32, int64 = torch.int32, torch.int64
 
-_eager = threading.local()
+_state = threading.local()
 
 
 @contextlib.contextmanager
 def eager_device(device):
-    """Device that dt.zeros / dt.full allocate on during an eager run."""
-    prev = getattr(_eager, "device", None)
-    _eager.device = device
+    """While active, dt.zeros / dt.full allocate on `device` (None: no preference)."""
+    before = getattr(_state, "device", None)
+    _state.device = device
     try:
         yield
     finally:
-        _eager.device = prev
+        _state.device = before
 
 
-def _alloc_device():
-    dev = getattr(_eager, "device", None)
-    if dev is not None:
-        return dev
-    return torch.device("cuda") if torch.cuda.is_available() else torch.device("cpu")
+def _where_to_allocate():
+    chosen = getattr(_state, "device", None)
+    if chosen is None:
+        chosen = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    return chosen
 
 
+@dataclass
 class Tile:
-    """One tile of an iteration dimension.  Eagerly it spans the whole
-    dimension; compiled it is a BLOCK_<NAME> constexpr with offsets and a mask."""
+    """One tile of an iteration dimension.  In an eager run it is the whole dimension; in the
+    compiled kernel it is BLOCK_<NAME> elements, with offsets and a mask for the ragged end."""
+    size: int
+    name: str = None
 
-    def __init__(self, size, name=None):
-        self.size = int(size)
-        self.name = name
+    def __post_init__(self):
+        self.size = int(self.size)
 
     def as_slice(self):
         return slice(0, self.size)
@@ -58,84 +59,72 @@ class Tile:
         return f"Tile({self.name or '?'}, {self.size})"
 
 
-def _index(idx):
-    idx = idx if isinstance(idx, tuple) else (idx,)
-    return tuple(i.as_slice() if isinstance(i, Tile) else i for i in idx)
+def _as_torch_index(index):
+    parts = index if isinstance(index, tuple) else (index,)
+    return tuple(part.as_slice() if isinstance(part, Tile) else part for part in parts)
+
+
+def _extent(entry):
+    return entry.size if isinstance(entry, Tile) else int(entry)
 
 
 class EagerTensor:
-    """Tensor argument as the eager run sees it: Tile indices act as full slices,
-    loads give plain tensors, stores write through."""
+    """A tensor argument during an eager run: indexing it with tiles reads or writes the
+    spanned region of the real tensor."""
 
     def __init__(self, tensor):
         self._t = tensor
 
-    def __getitem__(self, idx):
-        return self._t[_index(idx)]
+    def __getitem__(self, index):
+        return self._t[_as_torch_index(index)]
 
-    def __setitem__(self, idx, value):
-        self._t[_index(idx)] = value
+    def __setitem__(self, index, value):
+        self._t[_as_torch_index(index)] = value
 
-    @property
-    def shape(self):
-        return self._t.shape
-
-    @property
-    def dtype(self):
-        return self._t.dtype
-
-    @property
-    def device(self):
-        return self._t.device
-
-    def size(self, dim=None):
-        return self._t.size() if dim is None else self._t.size(dim)
+    def __getattr__(self, attribute):          # shape, dtype, device, size(), ...
+        return getattr(self._t, attribute)
 
 
-def tile(sizes):
-    """`for t in dt.tile(n)` / `for tm, tn in dt.tile([m, n])`.  The outermost tile
-    loop of a kernel becomes the launch grid, inner ones become loops over
-    tiles; eagerly each yields one full-size tile."""
-    if isinstance(sizes, (list, tuple)):
-        yield tuple(Tile(s) for s in sizes)
+def tile(extents):
+    """`for t in dt.tile(n)` / `for tm, tn in dt.tile([m, n])`.  The outermost tile loop of a
+    kernel becomes its launch grid and inner ones loops over tiles; an eager run gets a single
+    tile per dimension, as long as the dimension."""
+    if isinstance(extents, (list, tuple)):
+        yield tuple(Tile(e) for e in extents)
     else:
-        yield Tile(sizes)
-
-
-def _sizes(shape):
-    return [s.size if isinstance(s, Tile) else int(s) for s in shape]
+        yield Tile(extents)
 
 
 def zeros(shape, dtype=torch.float32):
-    return torch.zeros(_sizes(shape), dtype=dtype, device=_alloc_device())
+    return torch.zeros([_extent(e) for e in shape], dtype=dtype, device=_where_to_allocate())
 
 
 def full(shape, value, dtype=torch.float32):
-    return torch.full(_sizes(shape), value, dtype=dtype, device=_alloc_device())
-
-
-exp, log, sqrt, rsqrt = torch.exp, torch.log, torch.sqrt, torch.rsqrt
-sigmoid, tanh, erf, abs = torch.sigmoid, torch.tanh, torch.erf, torch.abs
-maximum, minimum, where = torch.maximum, torch.minimum, torch.where
+    return torch.full([_extent(e) for e in shape], value, dtype=dtype, device=_where_to_allocate())
 
 
 def relu(x):
     return torch.clamp_min(x, 0)
 
 
-# dt.<name>(args...) -> newt expression over the already generated operand texts
+# the rest of the elementwise vocabulary is torch's own
+for _fn in ("exp", "log", "sqrt", "rsqrt", "sigmoid", "tanh", "erf", "abs", "maximum", "minimum", "where"):
+    globals()[_fn] = getattr(torch, _fn)
+del _fn
+
+
+# dt.<name>(args...) in a compiled kernel -> nl.<function>(args..., *trailing constants)
 ELEMENTWISE = {
-    "exp": "nl.exp({0})", "log": "nl.log({0})", "sqrt": "nl.sqrt({0})",
-    "rsqrt": "nl.rsqrt({0})", "sigmoid": "nl.sigmoid({0})", "tanh": "nl.tanh({0})",
-    "erf": "nl.erf({0})", "abs": "nl.abs({0})", "relu": "nl.maximum({0}, 0.0)",
-    "maximum": "nl.maximum({0}, {1})", "minimum": "nl.minimum({0}, {1})",
-    "where": "nl.where({0}, {1}, {2})",
+    "exp": ("exp", ()), "log": ("log", ()), "sqrt": ("sqrt", ()), "rsqrt": ("rsqrt", ()),
+    "sigmoid": ("sigmoid", ()), "tanh": ("tanh", ()), "erf": ("erf", ()), "abs": ("abs", ()),
+    "relu": ("maximum", (0.0,)),
+    "maximum": ("maximum", ()), "minimum": ("minimum", ()), "where": ("where", ()),
 }
-# tensor method -> (newt reduction, identity that padded lanes must hold)
+# tensor method -> (nl reduction, the identity that padding lanes are given)
 REDUCTIONS = {
-    "sum": ("nl.sum", "0.0"),
-    "max": ("nl.max", "float('-inf')"), "amax": ("nl.max", "float('-inf')"),
-    "min": ("nl.min", "float('inf')"), "amin": ("nl.min", "float('inf')"),
+    "sum": ("sum", 0.0),
+    "max": ("max", float("-inf")), "amax": ("max", float("-inf")),
+    "min": ("min", float("inf")), "amin": ("min", float("inf")),
 }
-DTYPE_NAMES = {torch.float32: "nl.float32", torch.float16: "nl.float16",
-               torch.bfloat16: "nl.bfloat16", torch.int32: "nl.int32", torch.int64: "nl.int64"}
+DTYPE_NAMES = {torch.float32: "float32", torch.float16: "float16", torch.bfloat16: "bfloat16",
+               torch.int32: "int32", torch.int64: "int64"}

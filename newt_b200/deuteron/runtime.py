@@ -1,352 +1,212 @@
-"""`@dt.kernel`: trace -> newt source -> oracle-checked autotune -> launch,
-after deuteron/runtime.py of the reference.
+"""`@dt.kernel`: read the tile function, build its newt kernel, pick tile sizes, launch.
 
-Protocol (reference :1-11, :220-303):
-  1. the kernel function is run *eagerly* on clones of the arguments (full-size
-     tiles = plain PyTorch): the correctness oracle, also exposed as `.ref`;
-  2. newt source is generated once; tile sizes are constexprs;
-  3. candidate configurations are checked against the oracle first and only the
-     correct ones are timed (seeded sample of the space, then up to three rounds
-     of one-step neighbours);
-  4. the winner is remembered per (source, pow2-bucketed shapes, dtypes) in
-     memory and in $DEUTERON_CACHE_DIR/configs.json.
-
-Differences that the sm_100a backend needs: candidates that lower to the same
-hardware configuration are tried once (the tcgen05 kernel's tile is chosen by
-BLOCK of the N dimension and `num_stages` only); a candidate the backend cannot
-run is discarded from its launch plan, before any launch; the cache file is
-written atomically because several ranks tune the same kernel at once.
+A `Kernel` keeps, per argument signature (ranks and dtypes), the newt kernel built from the
+function (`codegen.generate` -> `JITFunction.from_ast`; no source text is executed or parsed
+on the way) and, per shape bucket, the configuration a search chose for it
+(`tuning.Search`, against the eager run of the same function as the oracle).  What callers see
+is what deuteron/runtime.py of the reference offers: calling the kernel, `.ref` (the eager
+PyTorch run), `.to_newt_source`, `.best_config`, `dt.Config`, and the environment switches
+DEUTERON_INTERPRET, DEUTERON_VERBOSE and DEUTERON_CACHE_DIR.
 """
 
 import ast
 import hashlib
 import inspect
-import itertools
-import json
-import linecache
 import os
-import random
-import tempfile
 import textwrap
 
 import torch
 
 from ..frontend.trace import CompileError
-from . import codegen
+from . import codegen, tuning
 from .language import EagerTensor, eager_device
-
-_CACHE_VERSION = "sm100a-1"
-
-
-def _cache_file():
-    d = os.environ.get("DEUTERON_CACHE_DIR") or os.path.join(os.path.expanduser("~"), ".deuteron")
-    os.makedirs(d, exist_ok=True)
-    return os.path.join(d, "configs.json")
+from .tuning import Config  # noqa: F401  (re-exported as dt.Config)
 
 
-def _read_cache():
-    try:
-        with open(_cache_file()) as f:
-            data = json.load(f)
-        return data if isinstance(data, dict) else {}
-    except (OSError, ValueError):
-        return {}
-
-
-def _write_cache(update):
-    path = _cache_file()
-    data = _read_cache()
-    data.update(update)
-    try:
-        fd, tmp = tempfile.mkstemp(dir=os.path.dirname(path), suffix=".tmp")
-        with os.fdopen(fd, "w") as f:
-            json.dump(data, f, indent=1)
-        os.replace(tmp, path)
-    except OSError:
-        pass
-
-
-def _pow2_at_least(n):
+def _bucket(n):
+    """Shapes that round up to the same power of two share a tuned configuration."""
     n = int(n)
     return 1 if n <= 1 else 1 << (n - 1).bit_length()
 
 
-class Config(dict):
+class _Built:
+    """One argument signature of a Kernel: the generated kernel and its jit."""
+
+    def __init__(self, generated):
+        from .. import language as nl
+        import newt_b200
+
+        self.generated = generated
+        self.jit = newt_b200.runtime.jit.JITFunction.from_ast(
+            generated.fndef, {"nl": nl, "newt": newt_b200, "__name__": "newt_b200.deuteron.generated"})
+
     @property
-    def num_warps(self):
-        return self.get("num_warps", 4)
+    def source(self):
+        return self.generated.source
 
 
 class Kernel:
     def __init__(self, fn, config=None, autotune=True, samples=12, verbose=False):
         self.fn = fn
         self.__name__ = fn.__name__
+        self.__doc__ = fn.__doc__
         self.fndef = ast.parse(textwrap.dedent(inspect.getsource(fn))).body[0]
         self.arg_names = [a.arg for a in self.fndef.args.args]
         self.fixed_config = Config(config) if config else None
         self.autotune_enabled = autotune and config is None
         self.samples = samples
         self.verbose = verbose or bool(os.environ.get("DEUTERON_VERBOSE"))
-        self._source = None
-        self._source_sig = None
-        self._jit = None
-        self._configs = {}
+        self._built = {}       # argument signature -> _Built
+        self._chosen = {}      # tuning key -> Config
+        self._last = None
 
-    # ---- public surface -----------------------------------------------------------
+    # ---- what users call ---------------------------------------------------------------------
 
     def __call__(self, *args):
         if os.environ.get("DEUTERON_INTERPRET"):
-            return self._eager(args)
-        ks = self._source_for(args)
-        cfg = self.fixed_config or self._config_for(ks, args)
-        self._launch(ks, args, cfg)
+            return self.ref(*args)
+        built = self.built_for(args)
+        self.launch(built, args, self.fixed_config or self.config_for(built, args))
 
     def ref(self, *args):
-        """The kernel body executed as plain PyTorch on full-size tiles."""
-        return self._eager(args)
+        """The function body run as plain PyTorch on whole-dimension tiles: the oracle."""
+        device = next((a.device for a in args if torch.is_tensor(a)), None)
+        with eager_device(device):
+            return self.fn(*[EagerTensor(a) if torch.is_tensor(a) else a for a in args])
 
     def to_newt_source(self, *args):
-        return self._source_for(args).source
+        return self.built_for(args).source
 
     @property
     def best_config(self):
-        if self._configs:
-            return list(self._configs.values())[-1]
-        return self.fixed_config
+        return self._last if self._last is not None else self.fixed_config
 
-    # ---- eager oracle ----------------------------------------------------------------
+    # ---- building ----------------------------------------------------------------------------------
 
-    def _eager(self, args):
-        device = next((a.device for a in args if torch.is_tensor(a)), None)
-        wrapped = [EagerTensor(a) if torch.is_tensor(a) else a for a in args]
-        with eager_device(device):
-            return self.fn(*wrapped)
-
-    # ---- source ------------------------------------------------------------------------
-
-    def _source_for(self, args):
-        sig = tuple((a.dim(), str(a.dtype)) if torch.is_tensor(a) else type(a).__name__
-                    for a in args)
-        if self._source is None or sig != self._source_sig:
-            ks = codegen.generate(self.fn, self.fndef, args)
-            filename = f"<deuteron:{self.__name__}>"
-            # the jit front end reads kernel text through inspect.getsource
-            linecache.cache[filename] = (len(ks.source), None, ks.source.splitlines(True), filename)
-            scope = {}
-            exec(compile(ks.source, filename, "exec"), scope)  # noqa: S102 - our own generated text
-            self._source, self._source_sig, self._jit = ks, sig, scope[ks.name]
+    def built_for(self, args):
+        signature = tuple((a.dim(), str(a.dtype)) if torch.is_tensor(a) else type(a).__name__
+                          for a in args)
+        built = self._built.get(signature)
+        if built is None:
+            built = self._built[signature] = _Built(codegen.generate(self.fn, self.fndef, args))
             if self.verbose:
-                print(f"=== deuteron: generated newt source for {self.__name__} ===")
-                print(ks.source)
-        return self._source
+                print(f"=== deuteron: newt kernel generated for {self.__name__} ===\n{built.source}")
+        return built
 
-    # ---- launch ---------------------------------------------------------------------------
+    # ---- launching -----------------------------------------------------------------------------------
 
-    def _sizes(self, ks, args):
-        by_name = dict(zip(self.arg_names, args))
-        sizes = {}
-        for kind, name in ks.params:
+    def launch_parts(self, built, args, config):
+        """(grid, positional arguments, keyword arguments) of the newt launch under `config`."""
+        gen = built.generated
+        given = dict(zip(self.arg_names, args))
+        extents = {}
+        for kind, name in gen.params:
             if kind == "tensor":
-                for d, s in enumerate(by_name[name].shape):
-                    sizes[f"{name}_d{d}"] = int(s)
+                extents.update({f"{name}_d{d}": int(n) for d, n in enumerate(given[name].shape)})
             else:
-                sizes[name] = by_name[name]
-        return sizes
+                extents[name] = given[name]
 
-    @staticmethod
-    def _size(sizes, sym):
-        return int(sizes[sym]) if sym in sizes else int(sym)
+        def length(symbol):
+            return int(extents[symbol]) if symbol in extents else int(symbol)
 
-    def _call_parts(self, ks, args, cfg):
-        """(grid, positional args, keyword args) of the newt launch for `cfg`."""
-        by_name = dict(zip(self.arg_names, args))
-        sizes = self._sizes(ks, args)
-        consts = {}
-        for tv in ks.tile_vars:
-            consts[tv.block] = _pow2_at_least(self._size(sizes, tv.size)) if tv.kind == "full" \
-                else cfg[tv.block]
-        grid = tuple(-(-self._size(sizes, tv.size) // consts[tv.block]) for tv in ks.grid_tiles)
-        pos = []
-        for kind, name in ks.params:
-            v = by_name[name]
+        blocks = {axis.block: (_bucket(length(axis.size)) if axis.kind == "full" else config[axis.block])
+                  for axis in gen.tile_vars}
+        grid = tuple(-(-length(axis.size) // blocks[axis.block]) for axis in gen.grid_tiles)
+        positional = []
+        for kind, name in gen.params:
+            value = given[name]
+            positional.append(value)
             if kind == "tensor":
-                pos.append(v)
-                pos.extend(int(s) for s in v.shape)
-                pos.extend(int(s) for s in v.stride())
-            else:
-                pos.append(v)
-        kw = dict(consts, num_warps=cfg.num_warps, num_stages=cfg.get("num_stages", 3))
-        return grid, pos, kw
+                positional += [int(n) for n in value.shape] + [int(n) for n in value.stride()]
+        keywords = dict(blocks, num_warps=config.num_warps, num_stages=config.get("num_stages", 3))
+        return grid, positional, keywords
 
-    def _launch(self, ks, args, cfg):
-        grid, pos, kw = self._call_parts(ks, args, cfg)
-        self._jit[grid](*pos, **kw)
+    def launch(self, built, args, config):
+        grid, positional, keywords = self.launch_parts(built, args, config)
+        built.jit[grid](*positional, **keywords)
 
-    # ---- configuration ------------------------------------------------------------------------
+    # ---- configurations --------------------------------------------------------------------------------
 
-    def _key(self, ks, args):
-        digest = hashlib.sha256(ks.source.encode()).hexdigest()[:12]
-        shapes = tuple(tuple(_pow2_at_least(s) for s in a.shape) if torch.is_tensor(a) else None
-                       for a in args)
+    def tuning_key(self, built, args):
+        digest = hashlib.sha256(built.source.encode()).hexdigest()[:12]
+        shapes = tuple(tuple(_bucket(n) for n in a.shape) if torch.is_tensor(a) else None for a in args)
         dtypes = tuple(str(a.dtype) if torch.is_tensor(a) else "" for a in args)
-        return f"{_CACHE_VERSION}:{self.__name__}:{digest}:{shapes}:{dtypes}"
+        return f"{tuning.CACHE_VERSION}:{self.__name__}:{digest}:{shapes}:{dtypes}"
 
-    def _config_for(self, ks, args):
-        key = self._key(ks, args)
-        cfg = self._configs.get(key)
-        if cfg is not None:
-            return cfg
-        stored = _read_cache().get(key)
-        if stored is not None:
-            cfg = Config(stored)
-        elif self.autotune_enabled:
-            cfg = self._autotune(ks, args)
-            _write_cache({key: dict(cfg)})
-        else:
-            cfg = self._default_config(ks)
-        self._configs[key] = cfg
-        return cfg
+    def config_for(self, built, args):
+        key = self.tuning_key(built, args)
+        config = self._chosen.get(key)
+        if config is None:
+            config = tuning.ConfigFile.lookup(key)
+            if config is None:
+                space = tuning.search_space(built.generated.tunable, built.generated.has_dot)
+                if self.autotune_enabled:
+                    config = self.search(built, args, space)
+                    tuning.ConfigFile.remember(key, config)
+                else:
+                    config = tuning.middle_of(space)
+            self._chosen[key] = config
+        self._last = config
+        return config
 
-    def _has_dot(self, ks):
-        return "nl.dot(" in ks.source
-
-    def _space(self, ks):
-        if self._has_dot(ks):
-            # tcgen05 tiles: 128-row MMAs (256 rows = a CTA pair), 64..256 columns, 64- or
-            # 128-element K slabs per TMA ring slot
-            space = {name: [64, 128, 256] for name in ks.tunable}
-            space["num_warps"] = [4]
-            space["num_stages"] = [2, 3, 4, 6, 7]
-        else:
-            space = {name: [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048]
-                     for name in ks.tunable}
-            space["num_warps"] = [2, 4, 8]
-        return space
-
-    def _default_config(self, ks):
-        space = self._space(ks)
-        return Config({k: v[len(v) // 2] for k, v in space.items()})
-
-    @staticmethod
-    def _neighbours(cfg, space):
-        out = []
-        for k, options in space.items():
-            i = options.index(cfg[k]) if cfg[k] in options else 0
-            for j in (i - 1, i + 1):
-                if 0 <= j < len(options):
-                    n = Config(cfg)
-                    n[k] = options[j]
-                    out.append(n)
-        return out
-
-    def _plan_key(self, ks, args, cfg):
-        """What the backend will actually run for cfg (None = every cfg distinct);
-        raises if the backend cannot run it."""
-        grid, pos, kw = self._call_parts(ks, args, cfg)
-        compiled = self._jit.specialize(*pos, **kw)
-        fn = getattr(compiled.plan, "hardware_key", None)
-        return fn() if fn else None
-
-    def _autotune(self, ks, args):
+    def search(self, built, args, space):
+        """Times the configurations whose result matches the eager run, on copies of the
+        arguments (the caller's tensors are not touched until the real launch)."""
         from ..testing import do_bench
 
-        space = self._space(ks)
-        keys = list(space)
-        clones = [a.clone() if torch.is_tensor(a) else a for a in args]
-        self._eager(clones)                                   # the oracle
-        by_name = dict(zip(self.arg_names, clones))
-        expected = {p: by_name[p].clone() for p in ks.store_params}
-        work = [a.clone() if torch.is_tensor(a) else a for a in args]
-        outs = {p: dict(zip(self.arg_names, work))[p] for p in ks.store_params}
-        originals = {p: dict(zip(self.arg_names, args))[p] for p in ks.store_params}
-        loose = self._has_dot(ks)
+        gen = built.generated
+        names = self.arg_names
 
-        def tolerance(t):
-            return 2e-2 if (loose or t.dtype in (torch.float16, torch.bfloat16)) else 1e-3
+        def copies():
+            return [a.clone() if torch.is_tensor(a) else a for a in args]
 
-        seen_plans = set()
+        oracle_args = copies()
+        self.ref(*oracle_args)
+        wanted = {name: dict(zip(names, oracle_args))[name] for name in gen.store_params}
+        scratch = copies()
+        outputs = {name: dict(zip(names, scratch))[name] for name in gen.store_params}
+        pristine = {name: dict(zip(names, args))[name] for name in gen.store_params}
 
-        def evaluate(cfg):
-            try:
-                pk = self._plan_key(ks, work, cfg)
-            except (CompileError, ValueError, TypeError, RuntimeError) as e:
-                if self.verbose:
-                    print(f"  {dict(cfg)}: invalid ({str(e)[:80]})")
-                return None
-            if pk is not None:
-                if pk in seen_plans:
-                    return None
-                seen_plans.add(pk)
-            for p, o in outs.items():
-                o.copy_(originals[p])
-            try:
-                self._launch(ks, work, cfg)
-                torch.cuda.synchronize()
-            except (CompileError, ValueError, RuntimeError) as e:
-                if self.verbose:
-                    print(f"  {dict(cfg)}: invalid ({str(e)[:80]})")
-                return None
-            for p, want in expected.items():
-                tol = tolerance(want)
-                if not torch.allclose(outs[p].float(), want.float(), rtol=tol, atol=tol):
-                    if self.verbose:
-                        print(f"  {dict(cfg)}: WRONG RESULT (skipped)")
-                    return None
-            ms = do_bench(lambda: self._launch(ks, work, cfg), warmup=3, rep=10)
+        def say(config, what):
             if self.verbose:
-                print(f"  {dict(cfg)}: {ms:.4f} ms")
+                print(f"  {dict(config)}: {what}")
+
+        def plan_identity(config):
+            _, positional, keywords = self.launch_parts(built, scratch, config)
+            plan = built.jit.specialize(*positional, **keywords).plan
+            describe = getattr(plan, "hardware_key", None)
+            return describe() if describe else None
+
+        def measure(config):
+            for name, out in outputs.items():
+                out.copy_(pristine[name])
+            try:
+                self.launch(built, scratch, config)
+                torch.cuda.synchronize()
+            except (CompileError, ValueError, RuntimeError) as problem:
+                say(config, f"cannot run ({str(problem)[:80]})")
+                return None
+            for name, want in wanted.items():
+                loose = gen.has_dot or want.dtype in (torch.float16, torch.bfloat16)
+                bar = 2e-2 if loose else 1e-3
+                if not torch.allclose(outputs[name].float(), want.float(), rtol=bar, atol=bar):
+                    say(config, "differs from the eager run, dropped")
+                    return None
+            ms = do_bench(lambda: self.launch(built, scratch, config), warmup=3, rep=10)
+            say(config, f"{ms:.4f} ms")
             return ms
 
-        everything = [Config(zip(keys, vals)) for vals in
-                      itertools.product(*[space[k] for k in keys])]
-        if len(everything) > self.samples and self._has_dot(ks):
-            # many candidates share a hardware configuration: keep one of each first
-            distinct, kept = set(), []
-            for cfg in everything:
-                try:
-                    pk = self._plan_key(ks, work, cfg)
-                except (CompileError, ValueError, TypeError, RuntimeError):
-                    continue
-                if pk is None or pk not in distinct:
-                    distinct.add(pk)
-                    kept.append(cfg)
-            everything = kept or everything
-        candidates = everything if len(everything) <= self.samples else \
-            random.Random(0).sample(everything, self.samples)
-
-        tried, results = set(), []
-        for cfg in candidates:
-            tag = frozenset(cfg.items())
-            if tag in tried:
-                continue
-            tried.add(tag)
-            ms = evaluate(cfg)
-            if ms is not None:
-                results.append((ms, cfg))
-        if not results:
-            raise RuntimeError(f"deuteron: no valid config found for {self.__name__} "
-                               f"(try DEUTERON_VERBOSE=1)")
-        best_ms, best = min(results, key=lambda r: r[0])
-        for _ in range(3):
-            improved = False
-            for n in self._neighbours(best, space):
-                tag = frozenset(n.items())
-                if tag in tried:
-                    continue
-                tried.add(tag)
-                ms = evaluate(n)
-                if ms is not None and ms < best_ms:
-                    best_ms, best, improved = ms, n, True
-            if not improved:
-                break
+        best, ms = tuning.Search(space, measure, plan_identity, samples=self.samples).run()
+        if best is None:
+            raise RuntimeError(f"deuteron: no configuration of {self.__name__} both runs and matches "
+                               f"its eager run (DEUTERON_VERBOSE=1 lists what was tried)")
         if self.verbose:
-            print(f"deuteron: {self.__name__} best {dict(best)} = {best_ms:.4f} ms")
+            print(f"deuteron: {self.__name__} -> {dict(best)} ({ms:.4f} ms)")
         return best
 
 
 def kernel(fn=None, *, config=None, autotune=True, samples=12, verbose=False):
-    """@dt.kernel -- compile a tile-DSL function to an autotuned sm_100a kernel launch."""
+    """@dt.kernel -- a tile-language function compiled to an autotuned sm_100a kernel launch."""
     if fn is None:
-        return lambda f: Kernel(f, config=config, autotune=autotune, samples=samples,
-                                verbose=verbose)
+        return lambda f: Kernel(f, config=config, autotune=autotune, samples=samples, verbose=verbose)
     return Kernel(fn)

@@ -46,20 +46,52 @@ class CompiledKernel:
         self.param_names = param_names
 
 
+class _KernelHandle:
+    """Stands where a Python function would for a kernel that only exists as a syntax tree
+    (deuteron builds its kernels that way): a name and the globals its body refers to."""
+
+    def __init__(self, name, fn_globals, doc=None):
+        self.__name__ = self.__qualname__ = name
+        self.__globals__ = fn_globals
+        self.__doc__ = doc
+        self.__module__ = fn_globals.get("__name__", "newt_b200.generated")
+
+
 class JITFunction:
     def __init__(self, fn):
-        functools.update_wrapper(self, fn)
-        self.fn = fn
         source = textwrap.dedent(inspect.getsource(fn))
         tree = ast.parse(source)
-        self.fndef = next(n for n in tree.body if isinstance(n, ast.FunctionDef))
+        fndef = next(n for n in tree.body if isinstance(n, ast.FunctionDef))
         params = inspect.signature(fn).parameters
-        self.param_names = list(params)
-        self.constexpr_names = [n for n, p in params.items()
-                                if _is_constexpr_annotation(p.annotation)]
+        self._setup(fn, fndef, list(params),
+                    [n for n, p in params.items() if _is_constexpr_annotation(p.annotation)],
+                    {n: p.default for n, p in params.items()
+                     if p.default is not inspect.Parameter.empty})
+
+    @classmethod
+    def from_ast(cls, fndef, fn_globals):
+        """A kernel given as an `ast.FunctionDef` (positional parameters, constexprs marked by a
+        `...constexpr` annotation, no defaults) and the globals its names resolve in: what a
+        front end that builds kernels programmatically hands over, with no source text, `exec`
+        or `inspect` in between."""
+        if fndef.args.defaults or fndef.args.kwonlyargs or fndef.args.vararg or fndef.args.kwarg:
+            raise TypeError("from_ast: plain positional parameters only")
+        names = [a.arg for a in fndef.args.args]
+        constexprs = [a.arg for a in fndef.args.args
+                      if a.annotation is not None and "constexpr" in ast.unparse(a.annotation)]
+        self = cls.__new__(cls)
+        self._setup(_KernelHandle(fndef.name, fn_globals, ast.get_docstring(fndef)), fndef, names,
+                    constexprs, {})
+        return self
+
+    def _setup(self, fn, fndef, param_names, constexpr_names, defaults):
+        functools.update_wrapper(self, fn)
+        self.fn = fn
+        self.fndef = fndef
+        self.param_names = param_names
+        self.constexpr_names = constexpr_names
         self._constexpr_set = frozenset(self.constexpr_names)
-        self.defaults = {n: p.default for n, p in params.items()
-                         if p.default is not inspect.Parameter.empty}
+        self.defaults = defaults
         self.cache = {}
         self._fast = {}      # cheap per-launch key -> (CompiledKernel, names of the tensor arguments)
         self._name_set = set(self.param_names)

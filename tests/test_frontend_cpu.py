@@ -293,13 +293,13 @@ def test_deuteron_source_and_plan():
     assert "def dt_matmul_newt(x_ptr, x_d0, x_d1, x_s0, x_s1, y_ptr, y_d0, y_d1, y_s0, y_s1, " \
            "out_ptr, out_d0, out_d1, out_s0, out_s1, BLOCK_TILE_M: nl.constexpr" in src
     assert "acc = nl.dot(" in src and "for _i_tile_k in range(0, nl.cdiv(x_d1, BLOCK_TILE_K)):" in src
-    ks = dt_matmul._source_for((x, y, out))
+    built = dt_matmul.built_for((x, y, out))
     cfg = dt.Config(BLOCK_TILE_M=128, BLOCK_TILE_N=256, BLOCK_TILE_K=64, num_stages=4)
-    grid, pos, kw = dt_matmul._call_parts(ks, (x, y, out), cfg)
+    grid, pos, kw = dt_matmul.launch_parts(built, (x, y, out), cfg)
     assert grid == (3, 1)
     typed = [BF16 if torch.is_tensor(a) else a for a in pos]
-    plan = dt_matmul._jit.specialize(*typed, **kw).plan
-    args = dict(zip(dt_matmul._jit.param_names, pos))
+    plan = built.jit.specialize(*typed, **kw).plan
+    args = dict(zip(built.jit.param_names, pos))
     assert isinstance(plan, lower.GemmPlan) and plan.hardware_key() == ("gemm", 256, 4)
     assert plan._extents(grid, args) == (300, 200, 104)
 
@@ -326,10 +326,10 @@ def dt_layernorm(x, w, b, out, eps):
 
 
 def _plan_of(kernel, args, cfg, ptr):
-    ks = kernel._source_for(args)
-    grid, pos, kw = kernel._call_parts(ks, args, cfg)
-    plan = kernel._jit.specialize(*[ptr if torch.is_tensor(a) else a for a in pos], **kw).plan
-    return plan, grid, dict(zip(kernel._jit.param_names, pos))
+    built = kernel.built_for(args)
+    grid, pos, kw = kernel.launch_parts(built, args, cfg)
+    plan = built.jit.specialize(*[ptr if torch.is_tensor(a) else a for a in pos], **kw).plan
+    return plan, grid, dict(zip(built.jit.param_names, pos))
 
 
 def test_deuteron_row_programs_lower_to_row_kernels():
@@ -379,11 +379,11 @@ def dt_linear_relu(x, y, bias, out):
 def test_matmul_with_epilogue_splits_into_product_and_generated_kernel():
     x, y, bias, out = torch.randn(256, 128).half(), torch.randn(128, 192).half(), torch.randn(192), \
         torch.empty(256, 192).half()
-    ks = dt_linear_relu._source_for((x, y, bias, out))
-    grid, pos, kw = dt_linear_relu._call_parts(ks, (x, y, bias, out),
-                                               dt.Config(BLOCK_TILE_M=128, BLOCK_TILE_N=64, BLOCK_TILE_K=64))
+    built = dt_linear_relu.built_for((x, y, bias, out))
+    grid, pos, kw = dt_linear_relu.launch_parts(built, (x, y, bias, out),
+                                                dt.Config(BLOCK_TILE_M=128, BLOCK_TILE_N=64, BLOCK_TILE_K=64))
     types = [P(tp.TORCH_TO_NEWT[str(a.dtype)]) if torch.is_tensor(a) else a for a in pos]
-    plan = dt_linear_relu._jit.specialize(*types, **kw).plan
+    plan = built.jit.specialize(*types, **kw).plan
     assert isinstance(plan, lower.GemmEpiloguePlan) and grid == (2, 3)
     assert isinstance(plan.gemm, lower.GemmPlan) and plan.gemm.c == "out_ptr"
     src = plan.epilogue.source
@@ -408,7 +408,7 @@ def test_deuteron_trace_errors():
         for t in dt.tile(x.shape[0]):
             out[t] = x[t]
 
-    with pytest.raises(dt.TraceError, match="top level"):
+    with pytest.raises(dt.TraceError, match="top level of a kernel holds tile loops only"):
         bad.to_newt_source(torch.zeros(4), torch.zeros(4))
 
 
