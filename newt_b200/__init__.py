@@ -42,14 +42,22 @@ def next_power_of_2(n):
 
 
 def install_aliases():
-    """Registers this package as `newt` (with `newt.language`, `newt.testing`) and its tile
-    language as `deuteron`, unless modules of those names are loaded already."""
-    from . import deuteron
+    """Registers this package as `newt` and its tile language as `deuteron` -- with the
+    submodules programs written against the reference import by name (`newt.language`,
+    `newt.testing`, `newt.runtime[.jit|.autotuner|.cuda]`, `newt.compiler[.codegen|.types]`) --
+    unless modules of those names are loaded already."""
+    import importlib
 
     here = _sys.modules[__name__]
-    for alias, module in (("newt", here), ("newt.language", language), ("newt.testing", testing),
-                          ("deuteron", deuteron)):
-        _sys.modules.setdefault(alias, module)
+    _sys.modules.setdefault("newt", here)
+    for sub in ("language", "testing", "types", "runtime", "runtime.jit", "runtime.autotuner",
+                "runtime.cuda", "compiler", "compiler.codegen", "deuteron"):
+        module = importlib.import_module(f"{__name__}.{sub}")
+        _sys.modules.setdefault(f"newt.{sub}", module)
+    _sys.modules.setdefault("newt.compiler.types", types)     # where the reference keeps them
+    _sys.modules.setdefault("deuteron", _sys.modules[f"{__name__}.deuteron"])
+    for sub in ("language", "codegen", "runtime"):
+        _sys.modules.setdefault(f"deuteron.{sub}", _sys.modules[f"{__name__}.deuteron.{sub}"])
 
 
 __all__ = ("jit", "autotune", "heuristics", "Config", "cdiv", "next_power_of_2", "language",

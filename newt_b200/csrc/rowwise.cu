@@ -338,6 +338,11 @@ __device__ __forceinline__ uint4 add4(uint4 a, uint4 b) {
   return r;
 }
 
+// U vectors per operand per thread and trip.  PERSISTENT: a grid of as many CTAs as the device
+// holds walks the array with a stride; otherwise every CTA takes one chunk of 256 * U vectors
+// and the hardware scheduler hands out chunks in address order (what keeps DRAM pages open
+// across the three streams).
+template <int U, bool PERSISTENT>
 __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ x,
                                                       const float* __restrict__ y,
                                                       float* __restrict__ out, int64_t n,
@@ -345,10 +350,9 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   if (vec_ok) {
-    constexpr int U = 4;  // vectors per operand per thread per trip: 128 bytes in flight
     const int64_t nvec = n / 4;
-    for (int64_t base = (int64_t)blockIdx.x * blockDim.x * U; base < nvec;
-         base += nthreads * U) {
+    const int64_t stride = PERSISTENT ? nthreads * U : nvec;   // one trip when not persistent
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x * U; base < nvec; base += stride) {
       uint4 a[U], b[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -500,10 +504,26 @@ extern "C" int nb200_add_f32(const float* x, const float* y, float* out, int64_t
                        reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   const DeviceInfo& dev = device_info();
   const int threads = 256;
-  int64_t want = cdiv64(vec_ok ? cdiv64(n, 4) : n, threads * 2);
-  int64_t cap = (int64_t)dev.sm_count * 8;
-  const int grid = (int)(want < cap ? (want < 1 ? 1 : want) : cap);
-  add_f32_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(x, y, out, n, vec_ok);
+  cudaStream_t st = (cudaStream_t)stream;
+  // "add_variant": 0 = default, 1 = persistent x4, 2 = chunked x4, 3 = chunked x8, 4 = persistent x8
+  const int variant = tuning("add_variant", 0);
+  const int64_t cap = (int64_t)dev.sm_count * 8;
+  auto persistent_grid = [&](int u) {
+    const int64_t want = cdiv64(vec_ok ? cdiv64(n, 4) : n, threads * u);
+    return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+  };
+  auto chunked_grid = [&](int u) -> int64_t { return cdiv64(cdiv64(n, 4), threads * u); };
+  if (!vec_ok || variant == 1) {
+    add_f32_kernel<4, true><<<persistent_grid(4), threads, 0, st>>>(x, y, out, n, vec_ok);
+  } else if (variant == 4) {
+    add_f32_kernel<8, true><<<persistent_grid(8), threads, 0, st>>>(x, y, out, n, vec_ok);
+  } else if (variant == 3 && chunked_grid(8) <= INT32_MAX) {
+    add_f32_kernel<8, false><<<(int)chunked_grid(8), threads, 0, st>>>(x, y, out, n, vec_ok);
+  } else if (chunked_grid(4) <= INT32_MAX) {
+    add_f32_kernel<4, false><<<(int)chunked_grid(4), threads, 0, st>>>(x, y, out, n, vec_ok);
+  } else {
+    add_f32_kernel<4, true><<<persistent_grid(4), threads, 0, st>>>(x, y, out, n, vec_ok);
+  }
   return cuda_check(cudaGetLastError(), "add_f32 launch");
 }
 

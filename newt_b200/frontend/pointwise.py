@@ -699,11 +699,18 @@ __device__ __forceinline__ void nb_atomic_max_f32(float* address, float value) {
 """
 
 
+def _read_after_write(clash):
+    return (f"values loaded from '{sorted(clash)[0]}' are consumed after the program stored to it "
+            f"(a load is evaluated where its value is used, so it would see the new contents)")
+
+
 def _reduce_init(fn, dt):
     if fn == "sum":
         return _literal(0, dt)
     if dt.is_floating:
         return _literal(float("-inf") if fn == "max" else float("inf"), dt)
+    if dt == tp.int1:        # max of booleans is "any", min is "all"
+        return "false" if fn == "max" else "true"
     bits = dt.itemsize * 8
     if dt.kind == "u":
         return _literal(0 if fn == "max" else 2 ** bits - 1, dt)
@@ -1133,7 +1140,7 @@ def _check_order(ctx, effects, written):
             for i, (_, target) in enumerate(parts):
                 clash = set().union(*reads) & written
                 if clash:
-                    raise Unsupported(f"'{sorted(clash)[0]}' is read after the program stored to it")
+                    raise Unsupported(_read_after_write(clash))
                 if target is not None and any(target in r for j, r in enumerate(reads) if j != i):
                     raise Unsupported(f"'{target}' is stored to and read by different statements "
                                       f"of a runtime loop")
@@ -1142,7 +1149,7 @@ def _check_order(ctx, effects, written):
             in_place(eff)
             clash = loads(_effect_roots(eff)) & written
             if clash:
-                raise Unsupported(f"'{sorted(clash)[0]}' is read after the program stored to it")
+                raise Unsupported(_read_after_write(clash))
             written.add(_base_param(eff[1], ctx.loops))
 
 

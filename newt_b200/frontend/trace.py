@@ -384,7 +384,8 @@ class Tracer(ast.NodeVisitor):
         cond = _unwrap_constexpr(self.eval(node.test))
         if isinstance(cond, Node):
             if cond.shape != ():
-                self.err(node, "`if` on a block: use nl.where for elementwise selection")
+                self.err(node, "`if` takes a scalar condition, this one is a block: use nl.where for "
+                               "elementwise selection")
             return self._runtime_if(node, cond)
         self._block(node.body if cond else node.orelse)
 

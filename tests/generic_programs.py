@@ -467,6 +467,24 @@ def _count_large(dev):
 
 
 @newt.jit
+def any_and_all(x_ptr, y_ptr, BLOCK: nl.constexpr):
+    """max of booleans is "any", min is "all": the folds must start from false and true."""
+    offs = nl.arange(0, BLOCK)
+    v = nl.load(x_ptr + offs)
+    nl.store(y_ptr, nl.max(v > 100.0).to(nl.int32))       # nothing is: 0
+    nl.store(y_ptr + 1, nl.sum(v > 100.0).to(nl.int32))   # ... counted: 0
+    nl.store(y_ptr + 2, nl.min(v < 100.0).to(nl.int32))   # everything is: 1
+    nl.store(y_ptr + 3, nl.min(v > -1.0).to(nl.int32))    # one is not: 0
+
+
+def _any_and_all(dev):
+    x = torch.zeros(256)
+    x[200] = -5.0
+    y = torch.full((4,), 7, device=dev, dtype=torch.int32)
+    return (x.to(dev), y), dict(BLOCK=256), [(y, torch.tensor([0, 0, 1, 0], dtype=torch.int32), 0, 0)]
+
+
+@newt.jit
 def bound_in_both_arms(x_ptr, y_ptr, flag, BLOCK: nl.constexpr):
     offs = nl.arange(0, BLOCK)
     if flag == 1:
@@ -657,6 +675,7 @@ CASES = {
     "last_value": (last_value, _last_value),
     "switch_source": (switch_source, _switch_source),
     "count_large": (count_large, _count_large),
+    "any_and_all": (any_and_all, _any_and_all),
     "bound_in_both_arms_then": (bound_in_both_arms, _bound_in_both_arms(1)),
     "bound_in_both_arms_else": (bound_in_both_arms, _bound_in_both_arms(0)),
     "fill_from_other_tensor": (fill_from_other_tensor, _fill_from_other_tensor),

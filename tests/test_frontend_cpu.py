@@ -197,7 +197,7 @@ def test_block_arithmetic_refuses_what_it_could_get_wrong():
         nl.store(x_ptr + offs, x + 1.0, mask=offs < n)
         nl.store(y_ptr + offs, x, mask=offs < n)      # x must be the value from before the first store
 
-    with pytest.raises(newt.CompileError, match="read after the program stored to it"):
+    with pytest.raises(newt.CompileError, match="consumed after the program stored to it"):
         read_after_write.specialize(F32, F32, 100, BLOCK=128)
 
 
