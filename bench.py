@@ -724,6 +724,7 @@ def measure(ctx, args, wl):
     ctx.barrier()
     step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     total_ms = sum(step_ms)
+    timed_config = wl.config(world)      # as of the timed steps (later launches may tune other shapes)
 
     # ---- parity of the very tensors that were just timed ----------------------
     torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
@@ -829,7 +830,7 @@ def measure(ctx, args, wl):
         "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": wl.scaling,
         "vs_baseline": None, "dtype": wl.dtype,
         "data": "synthetic (seeded N(0,1) drawn on the host, copied to HBM before timing)",
-        "config": dict(wl.config(world), **({"small": True} if args.small else {})),
+        "config": dict(timed_config, **({"small": True} if args.small else {})),
         "roofline": roofline,
         "e2e": {"value": job_throughput(units, world, 1, e2e_ms, wl.unit), "unit": wl.unit,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,

@@ -30,6 +30,21 @@ class Config:
         return f"Config({body}, num_warps={self.num_warps}, num_stages={self.num_stages})"
 
 
+def _busy_for(fn, seconds):
+    """Keeps the device busy with `fn` for about `seconds` (bounded in calls as well)."""
+    import time
+
+    import torch
+
+    until = time.perf_counter() + seconds
+    for _ in range(100):
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize()
+        if time.perf_counter() >= until:
+            break
+
+
 def _bound_args(jitfn, args, kwargs):
     bound = dict(zip(jitfn.param_names, args))
     bound.update(kwargs)
@@ -68,6 +83,7 @@ class Autotuner:
         from ..testing import do_bench
 
         results, last_error = [], None
+        warmed = False
         for cfg in self.configs:
             call_kwargs = {**kwargs, **cfg.all_kwargs()}
 
@@ -78,6 +94,13 @@ class Autotuner:
 
             try:
                 run()  # compiles; invalid configurations raise before any launch
+                if not warmed:
+                    # The candidates are compared with each other, so they must all be timed in
+                    # the same clock state: a chip that idled takes milliseconds of work to
+                    # reach its boost clock, which the first candidates of a list of short
+                    # kernels would otherwise pay for (and a later, slower one would win).
+                    _busy_for(run, 0.02)
+                    warmed = True
                 ms = do_bench(run, warmup=self.warmup, rep=self.rep)
             except (CompileError, ValueError, RuntimeError) as e:
                 last_error = e
