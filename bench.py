@@ -530,7 +530,7 @@ class AttentionWorkload(Workload):
 
     def traffic_bytes(self):
         # captured on the --small case (64 heads); DRAM traffic grows with the head count
-        return 251.4e6 / 64 * self.heads if (self.S, self.D) == (4096, 128) else None
+        return 246.0e6 / 64 * self.heads if (self.S, self.D) == (4096, 128) else None
 
     def config(self, world):
         return {"workload": "causal attention forward fp16 [16,32,4096,128], scale 1/sqrt(128)",
