@@ -180,6 +180,30 @@ int nb200_gemm_acc32(const void* a, const void* b, float* c, int64_t m, int64_t 
                      int64_t lda, int64_t ldb, int64_t ldc, int dtype, int b_transposed,
                      const nb200_gemm_config* config, void* stream);
 
+/* The host half of nb200_gemm / nb200_gemm_bt without the launch, for a kernel compiled at run
+ * time from the library's own device templates (csrc/gemm_device.cuh) with code of the
+ * caller's spliced into the epilogue -- what the reference does for everything after a k loop
+ * (newt/compiler/codegen.py:1854-1871, tests/test_ops.py:458-474).  Validates the problem as
+ * nb200_gemm does, resolves `config`, encodes the two tensor maps into `tensor_map_a` /
+ * `tensor_map_b` (128 bytes each, 64-byte aligned), fills `params` (the kernels' GemmParams; at
+ * least nb200_gemm_params_bytes() bytes) and says in `launch` which template instance to
+ * compile and how to launch it.  `c_dtype` is the element type of C (any of the three codes);
+ * fp16 / bf16 operands only. */
+typedef struct nb200_gemm_launch {
+  int32_t pair;        /* 1: gemm_pair_body<stages, ksub, ..> in clusters of two; 0: gemm_body<block_n, stages, ..> */
+  int32_t block_n, stages, ksub;
+  int32_t grid, block, cluster; /* CTAs, threads per CTA, CTAs per cluster (1: no cluster) */
+  int32_t smem_bytes;  /* dynamic shared memory per CTA */
+  int32_t nothing;     /* 1: C is empty, nothing to launch */
+  int32_t only_clear;  /* 1: K == 0, C is all zeros and nothing is to be launched */
+  int32_t reserved[6];
+} nb200_gemm_launch;
+int64_t nb200_gemm_params_bytes(void);
+int nb200_gemm_plan(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                    int64_t lda, int64_t ldb, int64_t ldc, int dtype, int c_dtype, int b_transposed,
+                    const nb200_gemm_config* config, void* tensor_map_a, void* tensor_map_b,
+                    void* params, nb200_gemm_launch* launch);
+
 /* dst[r][c] = src[r * row_stride + c * col_stride] for 2- or 4-byte elements (strides and
  * dst_pitch in elements): copies a matrix given with any two strides -- a row pitch that is
  * not a multiple of 16 bytes, a misaligned base, a transposed A -- into a row-major buffer

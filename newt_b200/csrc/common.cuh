@@ -3,13 +3,28 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#ifdef __CUDACC_RTC__
+// Compiled at run time (NVRTC has no host headers): the fixed-width names and the dtype codes
+// of include/newt_b200.h, spelled out.
+typedef unsigned char uint8_t;
+typedef unsigned short uint16_t;
+typedef int int32_t;
+typedef unsigned int uint32_t;
+typedef long long int64_t;
+typedef unsigned long long uint64_t;
+typedef unsigned long long uintptr_t;
+enum { NB200_F32 = 0, NB200_F16 = 1, NB200_BF16 = 2 };
+#else
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "../../include/newt_b200.h"
+#endif
 
 namespace nb200 {
 
+#ifndef __CUDACC_RTC__
 // ---- host side -------------------------------------------------------------
 
 // Records a printf-style message for nb200_last_error() on this thread and
@@ -45,6 +60,7 @@ int prepare_kernel(const void* kernel, int smem_bytes);
 int cluster_capacity(const void* kernel, const cudaLaunchConfig_t* config, int* clusters);
 
 static inline int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+#endif  // !__CUDACC_RTC__
 
 // ---- device side -----------------------------------------------------------
 

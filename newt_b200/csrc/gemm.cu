@@ -32,515 +32,33 @@
 #include <string.h>
 
 #include <mutex>
-#include <type_traits>
 
-#include "sm100.cuh"
+#include "gemm_device.cuh"
 
 namespace nb200 {
 namespace {
 
 using namespace sm100;
 
-constexpr int kBlockM = 128;
-// fp32 operands run as tf32 (kind::tf32 reads the upper 19 bits of each word): everything
-// below is laid out in 128-byte rows, so a row holds 32 K-elements instead of 64, a slab of B
-// 32 columns instead of 64, and one MMA consumes 8 K-elements instead of 16 -- the same 32
-// bytes.  Stage sizes, descriptor strides along K of A and the MMA count do not change.
-template <int DT>
-struct Elem {
-  static constexpr int kBytes = DT == NB200_F32 ? 4 : 2;
-  static constexpr int kPerRow = 128 / kBytes;   // K elements per stage = columns per slab of B
-  using Out = typename std::conditional<DT == NB200_F32, float,
-              typename std::conditional<DT == NB200_BF16, __nv_bfloat16, __half>::type>::type;
-};
-template <int DT>
-__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
-                                       uint32_t acc) {
-  if constexpr (DT == NB200_F32) mma_tf32_ss(d, a, b, idesc, acc);
-  else mma_f16_ss(d, a, b, idesc, acc);
-}
-template <int DT>
-__device__ __forceinline__ void mma_ss_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
-                                            uint32_t acc) {
-  if constexpr (DT == NB200_F32) mma_tf32_ss_pair(d, a, b, idesc, acc);
-  else mma_f16_ss_pair(d, a, b, idesc, acc);
-}
-// 32 accumulator columns of one row -> global memory, one rounding (none for fp32)
-template <int DT>
-__device__ __forceinline__ void store_chunk(typename Elem<DT>::Out* crow, int col0, int n,
-                                            bool vec_ok, const uint32_t (&r)[32]) {
-  using OutT = typename Elem<DT>::Out;
-  if constexpr (DT == NB200_F32) {
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {   // 4 columns = 16 bytes per group
-      const int col = col0 + g * 4;
-      if (vec_ok && col + 4 <= n) {
-        *reinterpret_cast<uint4*>(crow + col) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (col + j < n) crow[col + j] = __uint_as_float(r[g * 4 + j]);
-      }
-    }
-  } else {
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {   // 8 columns = 16 bytes per group
-      const int col = col0 + g * 8;
-      uint32_t packed[4];
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const float lo = __uint_as_float(r[g * 8 + 2 * h]);
-        const float hi = __uint_as_float(r[g * 8 + 2 * h + 1]);
-        if constexpr (DT == NB200_BF16) {
-          __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-          packed[h] = *reinterpret_cast<uint32_t*>(&v);
-        } else {
-          __half2 v = __floats2half2_rn(lo, hi);
-          packed[h] = *reinterpret_cast<uint32_t*>(&v);
-        }
-      }
-      if (vec_ok && col + 8 <= n) {
-        *reinterpret_cast<uint4*>(crow + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      } else {
-        const OutT* e = reinterpret_cast<const OutT*>(packed);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (col + j < n) crow[col + j] = e[j];
-      }
-    }
-  }
-}
-constexpr int kThreads = 192;
-constexpr int kGroupM = 8;      // row-blocks per L2 band of the tile order
+// ---- the kernels built ahead of time: the plain product, every tile and ring depth ------
 
-struct GemmParams {
-  void* c;
-  long long ldc;
-  int m, n, k;
-  int m_blocks, n_blocks, k_blocks;
-  uint32_t idesc;
-  int c_vec_ok;  // C base and row pitch are 16-byte aligned
-  int b_kmajor;  // B is given transposed ([N, K], K contiguous); always so for tf32
-  int c_f32;     // 16-bit operands, but C takes the fp32 accumulator unrounded
-  unsigned long long wait_limit_ns;
-  unsigned int* status;
-};
+using gemm::GemmParams;
+using gemm::kBlockM;
+using gemm::kThreads;
 
-__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int* mb,
-                                            int* nb) {
-  // bands of kGroupM row-blocks; inside a band, column-blocks advance slowest
-  const int band_tiles = kGroupM * n_blocks;
-  const int band = tile / band_tiles;
-  const int first_m = band * kGroupM;
-  const int rows = min(kGroupM, m_blocks - first_m);
-  const int in_band = tile - band * band_tiles;
-  *mb = first_m + in_band % rows;
-  *nb = in_band / rows;
-}
-
-template <int BN, int STAGES, int DT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int STAGES, int DT, int CT>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  constexpr int kBK = Elem<DT>::kPerRow;                // K elements per stage
-  constexpr int kSlab = Elem<DT>::kPerRow;              // columns of B per slab
-  constexpr uint32_t kABytes = kBlockM * 128;           // 16 KB
-  constexpr uint32_t kBSlab = kBK * 128;                // one slab of B: 8 KB (4 KB for tf32)
-  constexpr uint32_t kBBytes = kBSlab * (BN / kSlab);
-  constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators, BN fp32 columns each
-
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
-  __shared__ uint32_t tmem_slot;
-  __shared__ volatile uint32_t abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1 KB
-  const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
-
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
-    }
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&acc_full_bar[b]), 1);
-      mbar_init(smem_u32(&acc_empty_bar[b]), 4);  // one arrival per epilogue warp
-    }
-    mbar_init_fence();
-    prefetch_tensormap(&tmap_a);
-    prefetch_tensormap(&tmap_b);
-  }
-  if (warp == 1) {
-    __syncwarp();
-    tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_slot;
-
-  const int num_tiles = p.m_blocks * p.n_blocks;
-  // The tensor core takes tf32 operands K-major only (an MN-major B gives zeros), so fp32
-  // always comes with B transposed; for 16-bit types it is the caller's choice.
-  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;
-
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int mb, nb;
-        tile_coords(tile, p.m_blocks, p.n_blocks, &mb, &nb);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
-          if (!ok) break;
-          const uint32_t bar = smem_u32(&full_bar[stage]);
-          const uint32_t a_dst = smem_base + stage * kStageBytes;
-          mbar_arrive_expect_tx(bar, kStageBytes);
-          tma_load_2d(a_dst, &tmap_a, kb * kBK, mb * kBlockM, bar);
-          if (b_kmajor) {   // BN rows of B^T, one 128-byte row of K each
-            tma_load_2d(a_dst + kABytes, &tmap_b, kb * kBK, nb * BN, bar);
-          } else {
-#pragma unroll
-            for (int j = 0; j < BN / kSlab; ++j)
-              tma_load_2d(a_dst + kABytes + j * kBSlab, &tmap_b, nb * BN + j * kSlab, kb * kBK, bar);
-          }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    // The whole warp walks the loop and waits; one elected lane issues, so the warp's
-    // control flow stays uniform and descriptors live in uniform registers.
-    {
-      const bool elected = elect_one();
-      auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int tile) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, tile));
-      };
-      // A: K-major, 8-row groups 1024 B apart.  B: MN-major, 8-row K groups
-      // 1024 B apart, 64-column slabs kBSlab apart.
-      constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
-      constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
-      const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
-        const int buf = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
-        ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint64_t a_desc = with_address(kADesc, a_addr);
-          const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            // +32 B along K inside a K-major swizzle row; + a quarter of the stage's K-rows
-            // (128 B each) inside an MN-major slab of B
-            if (elected)
-              mma_ss<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
-                         p.idesc, (kb | kk) != 0 ? 1u : 0u);
-          }
-          if (elected) mma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these retire
-          __syncwarp();
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-        if (ok && elected) mma_commit(smem_u32(&acc_full_bar[buf]));
-        __syncwarp();
-      }
-    }
-  } else {
-    // ---------------- epilogue: TMEM -> registers -> global ----------------
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    using OutT = typename Elem<DT>::Out;
-    OutT* c = static_cast<OutT*>(p.c);
-    int it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
-      int mb, nb;
-      tile_coords(tile, p.m_blocks, p.n_blocks, &mb, &nb);
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const int row = mb * kBlockM + quarter * 32 + lane;
-      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
-      OutT* crow = c + (long long)row * p.ldc;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = nb * BN + c0;
-        if (col0 >= p.n) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (row < p.m) {
-          if (DT != NB200_F32 && p.c_f32)
-            store_chunk<NB200_F32>(static_cast<float*>(p.c) + (long long)row * p.ldc, col0, p.n,
-                                   p.c_vec_ok != 0, r);
-          else
-            store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buf]));
-    }
-  }
-
-  __syncthreads();
-  if (abort_flag) {
-    // give bulk copies that may still be in flight time to land before the
-    // shared memory they target is released
-    for (int i = 0; i < 64; ++i) __nanosleep(2000);
-  }
-  if (warp == 1) {
-    __syncwarp();
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
-  }
+  gemm::gemm_body<BN, STAGES, DT, CT, gemm::NoEpilogue>(tmap_a, tmap_b, p, gemm::NoEpilogueArgs{0});
 }
 
-// ---- CTA-pair variant: 256 x 256 output tile per cluster of two CTAs ---------------
-//
-// Each CTA of the pair loads its own 128 rows of A and its own 128 columns of B (no
-// multicast), so a stage costs 32 KB per CTA instead of 48 KB and the ring can be 6-7
-// deep; the leader CTA issues one tcgen05.mma.cta_group::2 (M = 256) that reads both
-// CTAs' shared memory and accumulates 128 rows in each CTA's tensor memory.
-// Barriers: `full` lives in the leader; the leader's producer announces the bytes of both
-// CTAs' copies and every copy (cta_group::2 form) reports its bytes there, so nothing but
-// the copies themselves crosses to the other SM per stage (a remote release-arrive per
-// stage capped the ring at one slot per ~0.8 us).  `empty` and `acc_full` exist in both
-// CTAs and the leader commits to each; `acc_empty` lives in the leader and collects the
-// epilogue warps of both CTAs, once per tile.
-// KSUB 64-element K slabs share one ring slot (one barrier round trip and one pair of
-// commits per slot).
-template <int STAGES, int KSUB, int DT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int STAGES, int KSUB, int DT, int CT>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  constexpr int BN = 256;                                // cluster tile width
-  constexpr int kBK = Elem<DT>::kPerRow;                 // K elements per 128-byte row
-  constexpr int kSlab = Elem<DT>::kPerRow;               // columns of B per slab
-  constexpr uint32_t kABytes = kBlockM * 128;            // this CTA's 128 rows of A: 16 KB
-  constexpr uint32_t kBSlab = kBK * 128;                 // one slab of B: 8 KB (4 KB for tf32)
-  constexpr uint32_t kBBytes = kBSlab * (128 / kSlab);   // this CTA's 128 columns of B
-  constexpr uint32_t kSlabBytes = kABytes + kBBytes;     // 32 KB per 64 elements of K
-  constexpr uint32_t kStageBytes = KSUB * kSlabBytes;
-  constexpr uint32_t kTmemCols = 2 * BN;
-
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
-  __shared__ uint32_t tmem_slot;
-  __shared__ volatile uint32_t abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_cta_rank();
-  const bool leader = rank == 0;
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
-
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);    // the leader's copy is the one in use
-      mbar_init(smem_u32(&empty_bar[s]), 1);
-    }
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&acc_full_bar[b]), 1);
-      mbar_init(smem_u32(&acc_empty_bar[b]), 8);  // four epilogue warps in each CTA
-    }
-    mbar_init_fence();
-    prefetch_tensormap(&tmap_a);
-    prefetch_tensormap(&tmap_b);
-  }
-  if (warp == 1) {
-    __syncwarp();
-    tmem_alloc_pair(smem_u32(&tmem_slot), kTmemCols);
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
-  tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_slot;
-
-  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;   // see gemm_kernel
-  const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
-  const int num_tiles = m_blocks2 * p.n_blocks;
-  const int first = cluster_id_x(), step = cluster_count_x();
-  const int k_rounds = (p.k_blocks + KSUB - 1) / KSUB;
-
-  if (warp == 0) {
-    // ---------------- TMA producer (one per CTA) ----------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = first; tile < num_tiles && ok; tile += step) {
-        int mb, nb;
-        tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
-        const int row0 = mb * 2 * kBlockM + rank * kBlockM;
-        const int col0 = nb * BN + rank * (BN / 2);
-        for (int kb = 0; kb < k_rounds; ++kb) {
-          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
-          if (!ok) break;
-          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * kStageBytes);
-#pragma unroll
-          for (int sub = 0; sub < KSUB; ++sub) {   // slabs past K are zero-filled by the tensor map
-            const uint32_t a_dst = smem_base + stage * kStageBytes + sub * kSlabBytes;
-            const int k0 = (kb * KSUB + sub) * kBK;
-            tma_load_2d_pair(a_dst, &tmap_a, k0, row0, bar);
-            if (b_kmajor) {   // this CTA's 128 rows of B^T
-              tma_load_2d_pair(a_dst + kABytes, &tmap_b, k0, col0, bar);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 128 / kSlab; ++j)
-                tma_load_2d_pair(a_dst + kABytes + j * kBSlab, &tmap_b, col0 + j * kSlab, k0, bar);
-            }
-          }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer (leader CTA only; whole warp, elected lane issues) --------
-    if (leader) {
-      const bool elected = elect_one();
-      auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int tile) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, tile));
-      };
-      // the barriers the commits signal, in each CTA's window of the cluster address space
-      // (barrier i of an array is 8 bytes after barrier i-1 there as well)
-      const uint32_t empty0 = map_to_cta(smem_u32(&empty_bar[0]), 0);
-      const uint32_t empty1 = map_to_cta(smem_u32(&empty_bar[0]), 1);
-      const uint32_t acc_full0 = map_to_cta(smem_u32(&acc_full_bar[0]), 0);
-      const uint32_t acc_full1 = map_to_cta(smem_u32(&acc_full_bar[0]), 1);
-      constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
-      constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
-      const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      bool ok = true;
-      for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
-        const int buf = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
-        ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_rounds; ++kb) {
-          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
-          if (!ok) break;
-          tc_fence_after_sync();
-#pragma unroll
-          for (int sub = 0; sub < KSUB; ++sub) {
-            const uint32_t a_addr = smem_base + stage * kStageBytes + sub * kSlabBytes;
-            const uint64_t a_desc = with_address(kADesc, a_addr);
-            const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              if (elected)
-                mma_ss_pair<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
-                                p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
-          }
-          // the slot is free in both CTAs once these MMAs retire
-          if (elected) {
-            mma_commit_pair(empty0 + stage * 8);
-            mma_commit_pair(empty1 + stage * 8);
-          }
-          __syncwarp();
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-        if (ok && elected) {
-          mma_commit_pair(acc_full0 + buf * 8);
-          mma_commit_pair(acc_full1 + buf * 8);
-        }
-        __syncwarp();
-      }
-    }
-  } else {
-    // ---------------- epilogue: this CTA's 128 rows of the 256-row tile ----------------
-    const int quarter = warp & 3;
-    using OutT = typename Elem<DT>::Out;
-    OutT* c = static_cast<OutT*>(p.c);
-    int it = 0;
-    bool ok = true;
-    for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
-      int mb, nb;
-      tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const int row = mb * 2 * kBlockM + rank * kBlockM + quarter * 32 + lane;
-      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
-      OutT* crow = c + (long long)row * p.ldc;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = nb * BN + c0;
-        if (col0 >= p.n) break;
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (row < p.m) {
-          if (DT != NB200_F32 && p.c_f32)
-            store_chunk<NB200_F32>(static_cast<float*>(p.c) + (long long)row * p.ldc, col0, p.n,
-                                   p.c_vec_ok != 0, r);
-          else
-            store_chunk<DT>(crow, col0, p.n, p.c_vec_ok != 0, r);
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[buf]), 0));
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (abort_flag) {
-    for (int i = 0; i < 64; ++i) __nanosleep(2000);
-  }
-  cluster_sync_all();   // nobody leaves while the other CTA may still touch its barriers or tiles
-  if (warp == 1) {
-    __syncwarp();
-    tc_fence_after_sync();
-    tmem_dealloc_pair(tmem_base, kTmemCols);
-  }
+  gemm::gemm_pair_body<STAGES, KSUB, DT, CT, gemm::NoEpilogue>(tmap_a, tmap_b, p,
+                                                               gemm::NoEpilogueArgs{0});
 }
 
 // ---- host ----------------------------------------------------------------------
@@ -639,28 +157,56 @@ int check_problem(const void* a, const void* b, const void* c, int64_t m, int64_
   return 0;
 }
 
+// the instance for (operand type, type of C): C is the operand type, or fp32 for 16-bit
+// operands whose accumulator is wanted unrounded
+#define NB200_PICK(KERNEL, ...)                                                              \
+  (dtype == NB200_F32    ? (const void*)KERNEL<__VA_ARGS__, NB200_F32, NB200_F32>            \
+   : dtype == NB200_BF16 ? (c_f32 ? (const void*)KERNEL<__VA_ARGS__, NB200_BF16, NB200_F32>  \
+                                  : (const void*)KERNEL<__VA_ARGS__, NB200_BF16, NB200_BF16>) \
+                         : (c_f32 ? (const void*)KERNEL<__VA_ARGS__, NB200_F16, NB200_F32>   \
+                                  : (const void*)KERNEL<__VA_ARGS__, NB200_F16, NB200_F16>))
+
 template <int BN, int STAGES>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype, int grid,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype, bool c_f32,
+           int grid, cudaStream_t stream) {
   const int smem = smem_bytes_for(BN, STAGES);
-  auto go = [&](auto kern) {
-    if (int rc = prepare_kernel((const void*)kern, smem)) return rc;
-    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
-    return cuda_check(cudaGetLastError(), "gemm launch");
-  };
-  if (dtype == NB200_BF16) return go(gemm_kernel<BN, STAGES, NB200_BF16>);
-  if (dtype == NB200_F32) return go(gemm_kernel<BN, STAGES, NB200_F32>);
-  return go(gemm_kernel<BN, STAGES, NB200_F16>);
+  const void* kern = NB200_PICK(gemm_kernel, BN, STAGES);
+  if (int rc = prepare_kernel(kern, smem)) return rc;
+  void* args[3] = {(void*)&ta, (void*)&tb, (void*)&p};
+  return cuda_check(cudaLaunchKernel(kern, dim3(grid), dim3(kThreads), args, smem, stream), "gemm launch");
 }
+
+// How many clusters of the pair kernel the device holds at once (asked once per device and
+// instance), never more than there are tiles.
+int pair_clusters(const void* kern, int smem, const GemmParams& p, int* clusters) {
+  cudaLaunchConfig_t lc = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.blockDim = dim3(kThreads);
+  lc.dynamicSmemBytes = smem;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  lc.gridDim = dim3(2);
+  if (int rc = cluster_capacity(kern, &lc, clusters)) return rc;
+  if (*clusters < 1) return fail(NB200_E_CUDA, "gemm: the device cannot host a CTA pair");
+  const long long tiles = (long long)cdiv64(p.m, 2 * kBlockM) * p.n_blocks;
+  if (tiles < *clusters) *clusters = (int)tiles;
+  return 0;
+}
+
+int pair_smem_bytes(int stages, int ksub) { return stages * ksub * (kBlockM * 128 + 128 * 128) + 1024; }
 
 template <int STAGES, int KSUB>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype,
-                cudaStream_t stream) {
-  const int smem = STAGES * KSUB * (kBlockM * 128 + 128 * 128) + 1024;
-  const void* kern = dtype == NB200_BF16 ? (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_BF16>
-                     : dtype == NB200_F32 ? (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_F32>
-                                          : (const void*)gemm_pair_kernel<STAGES, KSUB, NB200_F16>;
+                bool c_f32, cudaStream_t stream) {
+  const int smem = pair_smem_bytes(STAGES, KSUB);
+  const void* kern = NB200_PICK(gemm_pair_kernel, STAGES, KSUB);
   if (int rc = prepare_kernel(kern, smem)) return rc;
+  int clusters = 0;
+  if (int rc = pair_clusters(kern, smem, p, &clusters)) return rc;
   cudaLaunchConfig_t lc = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -672,13 +218,6 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   lc.stream = stream;
   lc.attrs = attr;
   lc.numAttrs = 1;
-  // as many pairs as the device can hold at once, never more than there are tiles
-  lc.gridDim = dim3(2);
-  int clusters = 0;
-  if (int rc = cluster_capacity(kern, &lc, &clusters)) return rc;
-  if (clusters < 1) return fail(NB200_E_CUDA, "gemm: the device cannot host a CTA pair");
-  const long long tiles = (long long)cdiv64(p.m, 2 * kBlockM) * p.n_blocks;
-  if (tiles < clusters) clusters = (int)tiles;
   lc.gridDim = dim3(2 * clusters);
   void* args[3] = {(void*)&ta, (void*)&tb, (void*)&p};
   return cuda_check(cudaLaunchKernelExC(&lc, kern, args), "gemm pair launch");
@@ -808,41 +347,51 @@ extern "C" int nb200_gemm_check(const void* a, const void* b, const void* c, int
 }
 
 namespace nb200 {
-// C = A @ B with B given either as [K, N] (b_kmajor = false) or transposed as [N, K].
-int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
-              int64_t ldb, int64_t ldc, int dtype, const nb200_gemm_config* config, bool b_kmajor,
-              cudaStream_t stream, bool c_f32 = false) {
+
+// Everything a launch needs, worked out on the host: the resolved tile configuration, the two
+// tensor maps and the kernel's parameter block.  `c_bytes`: size of an element of C.
+struct PlannedGemm {
+  Resolved cfg;
+  CUtensorMap ta, tb;
+  GemmParams p;
+  int row_k;
+  bool nothing_to_do;   // an empty C
+  bool only_clear;      // K == 0: C is its zero initial value
+};
+
+int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
+              int64_t ldb, int64_t ldc, int dtype, int c_bytes, const nb200_gemm_config* config,
+              bool b_kmajor, PlannedGemm* out) {
   if (int rc = check_problem(a, b, c, m, n, k, lda, ldb, ldc, dtype, b_kmajor)) return rc;
   const int eb = dtype == NB200_F32 ? 4 : 2;   // bytes per element
   const int row_k = 128 / eb;                  // K elements per 128-byte row = columns per slab of B
-  Resolved cfg;
+  out->row_k = row_k;
+  Resolved& cfg = out->cfg;
   if (int rc = resolve_config(config, m, n, row_k, &cfg)) return rc;
-  if (m == 0 || n == 0) return 0;
-  const int cb = c_f32 ? 4 : eb;                // bytes per element of C
-  if (k == 0)  // empty reduction: the accumulator is its zero initial value
-    return cuda_check(cudaMemset2DAsync(c, (size_t)ldc * cb, 0, (size_t)n * cb, (size_t)m, stream),
-                      "gemm k=0 clear");
+  out->nothing_to_do = m == 0 || n == 0;
+  out->only_clear = !out->nothing_to_do && k == 0;
+  if (out->nothing_to_do || out->only_clear) return 0;
 
-  CUtensorMap ta, tb;
   {
     const uint64_t dims[2] = {(uint64_t)k, (uint64_t)m};
     const uint64_t strides[1] = {(uint64_t)lda * eb};
     const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)kBlockM};
-    if (int rc = encode_tensor_map(&ta, a, eb, 2, dims, strides, box)) return rc;
+    if (int rc = encode_tensor_map(&out->ta, a, eb, 2, dims, strides, box)) return rc;
   }
   if (b_kmajor) {   // rows of B^T: one box per CTA and stage
     const uint64_t dims[2] = {(uint64_t)k, (uint64_t)n};
     const uint64_t strides[1] = {(uint64_t)ldb * eb};
     const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)(cfg.pair ? 128 : cfg.block_n)};
-    if (int rc = encode_tensor_map(&tb, b, eb, 2, dims, strides, box)) return rc;
+    if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box)) return rc;
   } else {
     const uint64_t dims[2] = {(uint64_t)n, (uint64_t)k};
     const uint64_t strides[1] = {(uint64_t)ldb * eb};
     const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)row_k};
-    if (int rc = encode_tensor_map(&tb, b, eb, 2, dims, strides, box)) return rc;
+    if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box)) return rc;
   }
 
-  GemmParams p;
+  GemmParams& p = out->p;
+  memset(&p, 0, sizeof(p));
   p.c = c;
   p.ldc = ldc;
   p.m = (int)m;
@@ -856,28 +405,44 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
                 ? sm100::instr_desc_tf32(mma_m, cfg.block_n, false, false)
                 : sm100::instr_desc_f16(mma_m, cfg.block_n, dtype == NB200_BF16, false, !b_kmajor);
   p.b_kmajor = b_kmajor ? 1 : 0;
-  p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * cb) % 16 == 0) ? 1 : 0;
-  p.c_f32 = c_f32 ? 1 : 0;
+  p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * c_bytes) % 16 == 0) ? 1 : 0;
   p.wait_limit_ns = wait_limit_ns();
   p.status = device_status_ptr();
   if (!p.status) return fail(NB200_E_CUDA, "gemm: device status word is not addressable");
+  return 0;
+}
+
+// C = A @ B with B given either as [K, N] (b_kmajor = false) or transposed as [N, K].
+int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
+              int64_t ldb, int64_t ldc, int dtype, const nb200_gemm_config* config, bool b_kmajor,
+              cudaStream_t stream, bool c_f32 = false) {
+  const int cb = (c_f32 || dtype == NB200_F32) ? 4 : 2;   // bytes per element of C
+  PlannedGemm g;
+  if (int rc = plan_gemm(a, b, c, m, n, k, lda, ldb, ldc, dtype, cb, config, b_kmajor, &g)) return rc;
+  if (g.nothing_to_do) return 0;
+  if (g.only_clear)  // empty reduction: the accumulator is its zero initial value
+    return cuda_check(cudaMemset2DAsync(c, (size_t)ldc * cb, 0, (size_t)n * cb, (size_t)m, stream),
+                      "gemm k=0 clear");
+  const Resolved& cfg = g.cfg;
+  const GemmParams& p = g.p;
 
   if (cfg.pair) {
-    if (cfg.block_k == 2 * row_k) return launch_pair<3, 2>(ta, tb, p, dtype, stream);
-    if (cfg.block_k == 3 * row_k) return launch_pair<2, 3>(ta, tb, p, dtype, stream);
+    if (cfg.block_k == 2 * g.row_k) return launch_pair<3, 2>(g.ta, g.tb, p, dtype, c_f32, stream);
+    if (cfg.block_k == 3 * g.row_k) return launch_pair<2, 3>(g.ta, g.tb, p, dtype, c_f32, stream);
     switch (cfg.stages) {
-      case 4: return launch_pair<4, 1>(ta, tb, p, dtype, stream);
-      case 5: return launch_pair<5, 1>(ta, tb, p, dtype, stream);
-      case 6: return launch_pair<6, 1>(ta, tb, p, dtype, stream);
-      default: return launch_pair<7, 1>(ta, tb, p, dtype, stream);
+      case 4: return launch_pair<4, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
+      case 5: return launch_pair<5, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
+      case 6: return launch_pair<6, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
+      default: return launch_pair<7, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
     }
   }
   const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
   const int sms = device_info().sm_count;
   const int grid = (int)(tiles < sms ? tiles : sms);
 
-#define NB200_GEMM_CASE(BN_, ST_) \
-  if (cfg.block_n == BN_ && cfg.stages == ST_) return launch<BN_, ST_>(ta, tb, p, dtype, grid, stream);
+#define NB200_GEMM_CASE(BN_, ST_)                  \
+  if (cfg.block_n == BN_ && cfg.stages == ST_)     \
+    return launch<BN_, ST_>(g.ta, g.tb, p, dtype, c_f32, grid, stream);
   NB200_GEMM_CASE(256, 4)
   NB200_GEMM_CASE(256, 3)
   NB200_GEMM_CASE(256, 2)
@@ -996,6 +561,67 @@ extern "C" int nb200_gemm_acc32(const void* a, const void* b, float* c, int64_t 
                                      "fp32 result through nb200_gemm_tf32 / nb200_gemm_bt)");
   return gemm_impl(a, b, c, m, n, k, lda, ldb, ldc, dtype, config, b_transposed != 0,
                    static_cast<cudaStream_t>(stream), true);
+}
+
+extern "C" int64_t nb200_gemm_params_bytes(void) { return (int64_t)sizeof(gemm::GemmParams); }
+
+extern "C" int nb200_gemm_plan(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                               int64_t lda, int64_t ldb, int64_t ldc, int dtype, int c_dtype,
+                               int b_transposed, const nb200_gemm_config* config, void* tensor_map_a,
+                               void* tensor_map_b, void* params, nb200_gemm_launch* launch) {
+  if (dtype != NB200_F16 && dtype != NB200_BF16)
+    return fail(NB200_E_UNSUPPORTED, "gemm_plan: fp16 or bf16 operands");
+  if (c_dtype != NB200_F16 && c_dtype != NB200_BF16 && c_dtype != NB200_F32)
+    return fail(NB200_E_INVALID, "gemm_plan: unknown dtype code %d for C", c_dtype);
+  if (!tensor_map_a || !tensor_map_b || !params || !launch)
+    return fail(NB200_E_INVALID, "gemm_plan: null output buffer");
+  if ((reinterpret_cast<uintptr_t>(tensor_map_a) | reinterpret_cast<uintptr_t>(tensor_map_b)) & 63)
+    return fail(NB200_E_INVALID, "gemm_plan: tensor maps must be 64-byte aligned");
+  PlannedGemm g;
+  if (int rc = plan_gemm(a, b, c, m, n, k, lda, ldb, ldc, dtype, c_dtype == NB200_F32 ? 4 : 2, config,
+                         b_transposed != 0, &g))
+    return rc;
+  memset(launch, 0, sizeof(*launch));
+  launch->nothing = g.nothing_to_do ? 1 : 0;
+  launch->only_clear = g.only_clear ? 1 : 0;
+  if (g.nothing_to_do || g.only_clear) return 0;
+  memcpy(tensor_map_a, &g.ta, sizeof(CUtensorMap));
+  memcpy(tensor_map_b, &g.tb, sizeof(CUtensorMap));
+  memcpy(params, &g.p, sizeof(g.p));
+  launch->block = kThreads;
+  launch->block_n = g.cfg.block_n;
+  if (g.cfg.pair) {
+    // the instances the library has itself: 3 slots of two K slabs, 2 of three, 4..7 of one
+    int stages = g.cfg.stages, ksub = 1;
+    if (g.cfg.block_k == 2 * g.row_k) stages = 3, ksub = 2;
+    else if (g.cfg.block_k == 3 * g.row_k) stages = 2, ksub = 3;
+    else stages = stages < 4 ? 4 : (stages > 7 ? 7 : stages);
+    launch->pair = 1;
+    launch->stages = stages;
+    launch->ksub = ksub;
+    launch->cluster = 2;
+    launch->smem_bytes = pair_smem_bytes(stages, ksub);
+    // as many pairs as the device holds of the library's own instance of this shape
+    const void* twin = stages == 3 && ksub == 2 ? (const void*)gemm_pair_kernel<3, 2, NB200_BF16, NB200_BF16>
+                     : stages == 2 && ksub == 3 ? (const void*)gemm_pair_kernel<2, 3, NB200_BF16, NB200_BF16>
+                     : stages == 4 ? (const void*)gemm_pair_kernel<4, 1, NB200_BF16, NB200_BF16>
+                     : stages == 5 ? (const void*)gemm_pair_kernel<5, 1, NB200_BF16, NB200_BF16>
+                     : stages == 6 ? (const void*)gemm_pair_kernel<6, 1, NB200_BF16, NB200_BF16>
+                                   : (const void*)gemm_pair_kernel<7, 1, NB200_BF16, NB200_BF16>;
+    if (int rc = prepare_kernel(twin, launch->smem_bytes)) return rc;
+    int clusters = 0;
+    if (int rc = pair_clusters(twin, launch->smem_bytes, g.p, &clusters)) return rc;
+    launch->grid = 2 * clusters;
+    return 0;
+  }
+  launch->stages = g.cfg.stages;
+  launch->ksub = 1;
+  launch->cluster = 1;
+  launch->smem_bytes = smem_bytes_for(g.cfg.block_n, g.cfg.stages);
+  const int64_t tiles = (int64_t)g.p.m_blocks * g.p.n_blocks;
+  const int sms = device_info().sm_count;
+  launch->grid = (int)(tiles < sms ? tiles : sms);
+  return 0;
 }
 
 extern "C" int64_t nb200_gemm_tf32_workspace_bytes(int64_t n, int64_t k) {

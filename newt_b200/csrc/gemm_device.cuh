@@ -1,0 +1,538 @@
+// Device side of C = A @ B on the 5th-generation tensor cores: the two kernels of gemm.cu as
+// function templates, so that the same text is compiled ahead of time (nvcc, the plain product)
+// and at run time (NVRTC, a kernel that brings code of its own to run on the accumulator before
+// the store).  Nothing here needs a host header.
+//
+//   gemm_body<BN, STAGES, DT, CT, EPI>        one CTA per 128 x BN tile
+//   gemm_pair_body<STAGES, KSUB, DT, CT, EPI>  a cluster of two CTAs per 256 x 256 tile
+//
+// DT: operand type code (NB200_F16 / BF16, or F32 run as tf32), CT: type code of C, EPI: the
+// epilogue functor (NoEpilogue for the plain product).  Callers wrap a body in a __global__
+// function with `__launch_bounds__(192, 1)` whose tensor maps are `__grid_constant__`.
+#pragma once
+
+#include "sm100.cuh"
+
+namespace nb200 {
+namespace gemm {
+
+using namespace sm100;
+
+constexpr int kBlockM = 128;
+// fp32 operands run as tf32 (kind::tf32 reads the upper 19 bits of each word): everything
+// below is laid out in 128-byte rows, so a row holds 32 K-elements instead of 64, a slab of B
+// 32 columns instead of 64, and one MMA consumes 8 K-elements instead of 16 -- the same 32
+// bytes.  Stage sizes, descriptor strides along K of A and the MMA count do not change.
+template <int DT>
+struct Elem {
+  static constexpr int kBytes = DT == NB200_F32 ? 4 : 2;
+  static constexpr int kPerRow = 128 / kBytes;   // K elements per stage = columns per slab of B
+};
+template <int DT> struct ElemType { using T = __half; };
+template <> struct ElemType<NB200_F32> { using T = float; };
+template <> struct ElemType<NB200_BF16> { using T = __nv_bfloat16; };
+template <int DT>
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
+                                       uint32_t acc) {
+  if constexpr (DT == NB200_F32) mma_tf32_ss(d, a, b, idesc, acc);
+  else mma_f16_ss(d, a, b, idesc, acc);
+}
+template <int DT>
+__device__ __forceinline__ void mma_ss_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
+                                            uint32_t acc) {
+  if constexpr (DT == NB200_F32) mma_tf32_ss_pair(d, a, b, idesc, acc);
+  else mma_f16_ss_pair(d, a, b, idesc, acc);
+}
+// 32 accumulator columns of one row -> global memory, one rounding (none for fp32)
+template <int DT>
+__device__ __forceinline__ void store_chunk(typename ElemType<DT>::T* crow, int col0, int n,
+                                            bool vec_ok, const uint32_t (&r)[32]) {
+  using OutT = typename ElemType<DT>::T;
+  if constexpr (DT == NB200_F32) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {   // 4 columns = 16 bytes per group
+      const int col = col0 + g * 4;
+      if (vec_ok && col + 4 <= n) {
+        *reinterpret_cast<uint4*>(crow + col) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (col + j < n) crow[col + j] = __uint_as_float(r[g * 4 + j]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {   // 8 columns = 16 bytes per group
+      const int col = col0 + g * 8;
+      uint32_t packed[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float lo = __uint_as_float(r[g * 8 + 2 * h]);
+        const float hi = __uint_as_float(r[g * 8 + 2 * h + 1]);
+        if constexpr (DT == NB200_BF16) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+          packed[h] = *reinterpret_cast<uint32_t*>(&v);
+        } else {
+          __half2 v = __floats2half2_rn(lo, hi);
+          packed[h] = *reinterpret_cast<uint32_t*>(&v);
+        }
+      }
+      if (vec_ok && col + 8 <= n) {
+        *reinterpret_cast<uint4*>(crow + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      } else {
+        const OutT* e = reinterpret_cast<const OutT*>(packed);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col + j < n) crow[col + j] = e[j];
+      }
+    }
+  }
+}
+template <class A, class B> struct std_is_same { static constexpr bool value = false; };
+template <class A> struct std_is_same<A, A> { static constexpr bool value = true; };
+constexpr int kThreads = 192;
+constexpr int kGroupM = 8;      // row-blocks per L2 band of the tile order
+
+struct GemmParams {
+  void* c;
+  long long ldc;
+  int m, n, k;
+  int m_blocks, n_blocks, k_blocks;
+  uint32_t idesc;
+  int c_vec_ok;  // C base and row pitch are 16-byte aligned
+  int b_kmajor;  // B is given transposed ([N, K], K contiguous); always so for tf32
+  unsigned long long wait_limit_ns;
+  unsigned int* status;
+};
+
+// What runs between the accumulator and the store.  `apply` gets 32 consecutive columns of one
+// row of the fp32 accumulator (row `row`, columns `col0`..`col0 + 31` of C; entries past the
+// matrix edge are never stored) and may change them in place: a bias, an activation, a
+// scaling -- the code a kernel has after its k loop (newt/compiler/codegen.py:1854-1871 keeps it
+// in the same kernel too).  The plain product uses NoEpilogue; kernels compiled at run time
+// bring their own functor and its argument struct.
+struct NoEpilogueArgs {
+  int unused;
+};
+struct NoEpilogue {
+  using Args = NoEpilogueArgs;
+  static __device__ __forceinline__ void apply(float (&)[32], int, int, const Args&) {}
+};
+
+// The epilogue of one 32-column chunk: functor, one rounding to C's type, store.
+template <int CT, class EPI>
+__device__ __forceinline__ void finish_chunk(void* c, long long ldc, int row, int col0, int n,
+                                             bool vec_ok, uint32_t (&r)[32],
+                                             const typename EPI::Args& ea) {
+  if constexpr (!std_is_same<EPI, NoEpilogue>::value) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    EPI::apply(v, row, col0, ea);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(v[j]);
+  }
+  using OutT = typename ElemType<CT>::T;
+  store_chunk<CT>(static_cast<OutT*>(c) + (long long)row * ldc, col0, n, vec_ok, r);
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int* mb,
+                                            int* nb) {
+  // bands of kGroupM row-blocks; inside a band, column-blocks advance slowest
+  const int band_tiles = kGroupM * n_blocks;
+  const int band = tile / band_tiles;
+  const int first_m = band * kGroupM;
+  const int rows = min(kGroupM, m_blocks - first_m);
+  const int in_band = tile - band * band_tiles;
+  *mb = first_m + in_band % rows;
+  *nb = in_band / rows;
+}
+
+template <int BN, int STAGES, int DT, int CT, class EPI>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                          const GemmParams& p, const typename EPI::Args& ea) {
+  constexpr int kBK = Elem<DT>::kPerRow;                // K elements per stage
+  constexpr int kSlab = Elem<DT>::kPerRow;              // columns of B per slab
+  constexpr uint32_t kABytes = kBlockM * 128;           // 16 KB
+  constexpr uint32_t kBSlab = kBK * 128;                // one slab of B: 8 KB (4 KB for tf32)
+  constexpr uint32_t kBBytes = kBSlab * (BN / kSlab);
+  constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators, BN fp32 columns each
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile uint32_t abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1 KB
+  const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&acc_full_bar[b]), 1);
+      mbar_init(smem_u32(&acc_empty_bar[b]), 4);  // one arrival per epilogue warp
+    }
+    mbar_init_fence();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int num_tiles = p.m_blocks * p.n_blocks;
+  // The tensor core takes tf32 operands K-major only (an MN-major B gives zeros), so fp32
+  // always comes with B transposed; for 16-bit types it is the caller's choice.
+  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, p.m_blocks, p.n_blocks, &mb, &nb);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&full_bar[stage]);
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          mbar_arrive_expect_tx(bar, kStageBytes);
+          tma_load_2d(a_dst, &tmap_a, kb * kBK, mb * kBlockM, bar);
+          if (b_kmajor) {   // BN rows of B^T, one 128-byte row of K each
+            tma_load_2d(a_dst + kABytes, &tmap_b, kb * kBK, nb * BN, bar);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / kSlab; ++j)
+              tma_load_2d(a_dst + kABytes + j * kBSlab, &tmap_b, nb * BN + j * kSlab, kb * kBK, bar);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    // The whole warp walks the loop and waits; one elected lane issues, so the warp's
+    // control flow stays uniform and descriptors live in uniform registers.
+    {
+      const bool elected = elect_one();
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int tile) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, tile));
+      };
+      // A: K-major, 8-row groups 1024 B apart.  B: MN-major, 8-row K groups
+      // 1024 B apart, 64-column slabs kBSlab apart.
+      constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
+      constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
+      const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint64_t a_desc = with_address(kADesc, a_addr);
+          const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            // +32 B along K inside a K-major swizzle row; + a quarter of the stage's K-rows
+            // (128 B each) inside an MN-major slab of B
+            if (elected)
+              mma_ss<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
+                         p.idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          if (elected) mma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these retire
+          __syncwarp();
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok && elected) mma_commit(smem_u32(&acc_full_bar[buf]));
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(tile, p.m_blocks, p.n_blocks, &mb, &nb);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = mb * kBlockM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col0 = nb * BN + c0;
+        if (col0 >= p.n) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        if (row < p.m) finish_chunk<CT, EPI>(p.c, p.ldc, row, col0, p.n, p.c_vec_ok != 0, r, ea);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buf]));
+    }
+  }
+
+  __syncthreads();
+  if (abort_flag) {
+    // give bulk copies that may still be in flight time to land before the
+    // shared memory they target is released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- CTA-pair variant: 256 x 256 output tile per cluster of two CTAs ---------------
+//
+// Each CTA of the pair loads its own 128 rows of A and its own 128 columns of B (no
+// multicast), so a stage costs 32 KB per CTA instead of 48 KB and the ring can be 6-7
+// deep; the leader CTA issues one tcgen05.mma.cta_group::2 (M = 256) that reads both
+// CTAs' shared memory and accumulates 128 rows in each CTA's tensor memory.
+// Barriers: `full` lives in the leader; the leader's producer announces the bytes of both
+// CTAs' copies and every copy (cta_group::2 form) reports its bytes there, so nothing but
+// the copies themselves crosses to the other SM per stage (a remote release-arrive per
+// stage capped the ring at one slot per ~0.8 us).  `empty` and `acc_full` exist in both
+// CTAs and the leader commits to each; `acc_empty` lives in the leader and collects the
+// epilogue warps of both CTAs, once per tile.
+// KSUB 64-element K slabs share one ring slot (one barrier round trip and one pair of
+// commits per slot).
+template <int STAGES, int KSUB, int DT, int CT, class EPI>
+__device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                               const GemmParams& p, const typename EPI::Args& ea) {
+  constexpr int BN = 256;                                // cluster tile width
+  constexpr int kBK = Elem<DT>::kPerRow;                 // K elements per 128-byte row
+  constexpr int kSlab = Elem<DT>::kPerRow;               // columns of B per slab
+  constexpr uint32_t kABytes = kBlockM * 128;            // this CTA's 128 rows of A: 16 KB
+  constexpr uint32_t kBSlab = kBK * 128;                 // one slab of B: 8 KB (4 KB for tf32)
+  constexpr uint32_t kBBytes = kBSlab * (128 / kSlab);   // this CTA's 128 columns of B
+  constexpr uint32_t kSlabBytes = kABytes + kBBytes;     // 32 KB per 64 elements of K
+  constexpr uint32_t kStageBytes = KSUB * kSlabBytes;
+  constexpr uint32_t kTmemCols = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile uint32_t abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);    // the leader's copy is the one in use
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&acc_full_bar[b]), 1);
+      mbar_init(smem_u32(&acc_empty_bar[b]), 8);  // four epilogue warps in each CTA
+    }
+    mbar_init_fence();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc_pair(smem_u32(&tmem_slot), kTmemCols);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;   // see gemm_kernel
+  const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
+  const int num_tiles = m_blocks2 * p.n_blocks;
+  const int first = cluster_id_x(), step = cluster_count_x();
+  const int k_rounds = (p.k_blocks + KSUB - 1) / KSUB;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first; tile < num_tiles && ok; tile += step) {
+        int mb, nb;
+        tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
+        const int row0 = mb * 2 * kBlockM + rank * kBlockM;
+        const int col0 = nb * BN + rank * (BN / 2);
+        for (int kb = 0; kb < k_rounds; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
+          if (!ok) break;
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * kStageBytes);
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {   // slabs past K are zero-filled by the tensor map
+            const uint32_t a_dst = smem_base + stage * kStageBytes + sub * kSlabBytes;
+            const int k0 = (kb * KSUB + sub) * kBK;
+            tma_load_2d_pair(a_dst, &tmap_a, k0, row0, bar);
+            if (b_kmajor) {   // this CTA's 128 rows of B^T
+              tma_load_2d_pair(a_dst + kABytes, &tmap_b, k0, col0, bar);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 128 / kSlab; ++j)
+                tma_load_2d_pair(a_dst + kABytes + j * kBSlab, &tmap_b, col0 + j * kSlab, k0, bar);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only; whole warp, elected lane issues) --------
+    if (leader) {
+      const bool elected = elect_one();
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, unsigned int code, int tile) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, code, tile));
+      };
+      // the barriers the commits signal, in each CTA's window of the cluster address space
+      // (barrier i of an array is 8 bytes after barrier i-1 there as well)
+      const uint32_t empty0 = map_to_cta(smem_u32(&empty_bar[0]), 0);
+      const uint32_t empty1 = map_to_cta(smem_u32(&empty_bar[0]), 1);
+      const uint32_t acc_full0 = map_to_cta(smem_u32(&acc_full_bar[0]), 0);
+      const uint32_t acc_full1 = map_to_cta(smem_u32(&acc_full_bar[0]), 1);
+      constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
+      constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
+      const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_rounds; ++kb) {
+          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const uint32_t a_addr = smem_base + stage * kStageBytes + sub * kSlabBytes;
+            const uint64_t a_desc = with_address(kADesc, a_addr);
+            const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              if (elected)
+                mma_ss_pair<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
+                                p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
+          }
+          // the slot is free in both CTAs once these MMAs retire
+          if (elected) {
+            mma_commit_pair(empty0 + stage * 8);
+            mma_commit_pair(empty1 + stage * 8);
+          }
+          __syncwarp();
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok && elected) {
+          mma_commit_pair(acc_full0 + buf * 8);
+          mma_commit_pair(acc_full1 + buf * 8);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---------------- epilogue: this CTA's 128 rows of the 256-row tile ----------------
+    const int quarter = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
+      int mb, nb;
+      tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = mb * 2 * kBlockM + rank * kBlockM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col0 = nb * BN + c0;
+        if (col0 >= p.n) break;
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        if (row < p.m) finish_chunk<CT, EPI>(p.c, p.ldc, row, col0, p.n, p.c_vec_ok != 0, r, ea);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[buf]), 0));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  cluster_sync_all();   // nobody leaves while the other CTA may still touch its barriers or tiles
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+
+}  // namespace gemm
+}  // namespace nb200

@@ -7,9 +7,17 @@
 // and tells the rest of the CTA to leave.
 #pragma once
 
-#include <cuda.h>
-
 #include "common.cuh"
+
+#ifdef __CUDACC_RTC__
+// cuda.h needs host headers; all device code needs of it is the size and alignment of a tensor map
+struct alignas(64) CUtensorMap_st {
+  unsigned long long opaque[16];
+};
+typedef CUtensorMap_st CUtensorMap;
+#else
+#include <cuda.h>
+#endif
 
 namespace nb200 {
 namespace sm100 {
@@ -487,6 +495,7 @@ __device__ __forceinline__ float exp2_approx(float x) {
 
 }  // namespace sm100
 
+#ifndef __CUDACC_RTC__
 // ---- host: tensor maps ---------------------------------------------------------
 
 // Encodes a tiled 16-bit tensor map with 128-byte swizzle and zero fill.
@@ -496,5 +505,6 @@ int encode_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int ra
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
 int encode_tensor_map_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                             const uint64_t* strides_bytes, const uint32_t* box);
+#endif  // !__CUDACC_RTC__
 
 }  // namespace nb200

@@ -863,7 +863,8 @@ class GemmPlan(Plan):
 def lower_gemm(trace, an, num_stages, epilogue=False):
     """The matmul k loop.  With `epilogue`, the stored value may be any expression of the
     accumulator (bias, activation, scaling, a reduction over the tile) and the store may be of
-    any dtype; returns (plan, (loop uid, accumulator name), the store's pointer node) then."""
+    any dtype; returns (plan, (loop uid, accumulator name), the store's pointer node, the store
+    effect) then."""
     loops = _loops(trace)
     stores = _top_level_stores(trace)
     if len(loops) != 1 or len(stores) != 1:
@@ -939,42 +940,155 @@ def lower_gemm(trace, an, num_stages, epilogue=False):
     plan.num_stages = num_stages
     plan.row_k = 32 if a.dtype == tp.float32 else 64
     if epilogue:
-        return plan, (loop.uid, acc_name), c_ptr
+        return plan, (loop.uid, acc_name), c_ptr, stores[0]
     return plan
 
 
 class GemmEpiloguePlan(Plan):
     """A matmul k loop whose accumulator goes through more arithmetic before the store (bias,
-    activation, scaling, a row reduction): the product runs on the tensor core into an fp32
-    buffer laid out like C (`nb200_gemm_acc32`; fp32 operands: the tf32 entry points), then the
-    rest of the program runs as a generated kernel that reads the accumulator from that buffer
-    (newt/compiler/codegen.py:2420-2451 drains the pipeline before the accumulator is read;
-    here the drain is the end of the first kernel).  Costs one extra pass over C (4 bytes
-    written and read per element) against a kernel with the epilogue inside."""
+    activation, scaling, another output type, a row reduction).
 
-    kind, entry = "matmul K loop + epilogue", "nb200_gemm_acc32 + run-time compiled kernel"
+    Where that arithmetic is elementwise in the accumulator it is spliced into the tensor-core
+    kernel itself, as the reference keeps everything after a k loop in the same kernel
+    (newt/compiler/codegen.py:1854-1871): the program's own graph is turned into an epilogue
+    functor (frontend/pointwise.py `generate_epilogue`) and the library's device templates
+    (csrc/gemm_device.cuh) are compiled with it by NVRTC, one kernel per tile configuration;
+    the host half of the launch -- checks, tensor maps, parameter block -- stays in the library
+    (`nb200_gemm_plan`).  Nothing but the program's own tensors is touched.
 
-    def __init__(self, trace, gemm, acc, c_ptr, num_warps):
+    What cannot run there (a reduction over the tile, operands bulk tensor copies cannot fetch
+    as they lie) takes two kernels: the product on the tensor core into an fp32 buffer laid out
+    like C (`nb200_gemm_acc32`; fp32 operands: the tf32 entry points), then the rest of the
+    program as a generated kernel that reads the accumulator from that buffer -- one extra pass
+    over C (4 bytes written and read per element)."""
+
+    kind, entry = "matmul K loop + epilogue", "run-time compiled tcgen05 kernel with the epilogue inside"
+
+    def __init__(self, trace, gemm, acc, c_ptr, num_warps, store):
         self.gemm = gemm
-        # The epilogue streams a BLOCK_M x BLOCK_N tile per program through HBM once; the
-        # kernel's num_warps was chosen for the k loop.  Eight elements per thread keep enough
-        # loads in flight: up to 32 warps for the tiles a tensor-core matmul uses.
+        self.fused_source = None
+        self.fused_reason = None
+        try:
+            if gemm.row_k != 64:
+                raise pointwise.Unsupported("fp32 operands go through a transposing pass first")
+            text, self.fused_params = pointwise.generate_epilogue(
+                trace, acc, store, gemm.block[:2], (gemm.pid_m, gemm.pid_n))
+            self.fused_source = text
+            self.c_element = c_ptr.dtype.element
+            if self.c_element not in (tp.float16, tp.bfloat16, tp.float32):
+                raise pointwise.Unsupported(f"C of type {self.c_element.name}")
+        except pointwise.Unsupported as why:
+            self.fused_source, self.fused_reason = None, str(why)
+        self._fused_kernels = {}     # template instance -> nvrtc.Kernel
+        # The two-kernel route.  Its epilogue streams a BLOCK_M x BLOCK_N tile per program through
+        # HBM once; the kernel's num_warps was chosen for the k loop.  Eight elements per thread
+        # keep enough loads in flight: up to 32 warps for the tiles a tensor-core matmul uses.
         bm, bn, _ = gemm.block
         warps = num_warps
         while warps < 32 and warps * 32 * 8 < bm * bn:
             warps *= 2
-        self.epilogue = PointwisePlan(trace, warps, {acc: ("nb_acc", c_ptr)})
+        self._split_args = (trace, warps, {acc: ("nb_acc", c_ptr)})
+        self._epilogue = None
+        if self.fused_source is None:
+            self.epilogue           # compile-time refusals surface when the plan is made
         self._whole = lambda: PointwisePlan(trace, num_warps)    # the program in one generated kernel
         self._whole_plan = None
 
+    @property
+    def epilogue(self):
+        if self._epilogue is None:
+            self._epilogue = PointwisePlan(*self._split_args)
+        return self._epilogue
+
+    def describe(self):
+        if self.fused_source is not None:
+            return "tcgen05 GEMM with the program's epilogue compiled in (NVRTC)"
+        return f"nb200_gemm_acc32 + run-time compiled kernel ({self.fused_reason})"
+
     def hardware_key(self):
-        return ("gemm+epilogue",) + self.gemm.hardware_key() + (self.epilogue.kernel_name,)
+        tail = ("fused",) if self.fused_source is not None else (self.epilogue.kernel_name,)
+        return ("gemm+epilogue",) + self.gemm.hardware_key() + tail
+
+    # ---- one kernel --------------------------------------------------------------------------
+
+    def _fused_kernel(self, launch, dtype_code, c_code):
+        from ..runtime import nvrtc
+
+        key = (launch.pair, launch.block_n, launch.stages, launch.ksub, dtype_code, c_code)
+        kernel = self._fused_kernels.get(key)
+        if kernel is None:
+            codes = {0: "NB200_F32", 1: "NB200_F16", 2: "NB200_BF16"}
+            if launch.pair:
+                body = (f"nb200::gemm::gemm_pair_body<{launch.stages}, {launch.ksub}, {codes[dtype_code]}, "
+                        f"{codes[c_code]}, NbEpilogue>(ta, tb, p, ea);")
+            else:
+                body = (f"nb200::gemm::gemm_body<{launch.block_n}, {launch.stages}, {codes[dtype_code]}, "
+                        f"{codes[c_code]}, NbEpilogue>(ta, tb, p, ea);")
+            name = "nb_gemm_epilogue"
+            source = (
+                f"// device templates {nvrtc.device_headers_digest()}\n"     # part of the cache key
+                '#include "gemm_device.cuh"\n' + self.fused_source +
+                f'\nextern "C" __global__ void __launch_bounds__(192, 1) {name}(\n'
+                "    const __grid_constant__ CUtensorMap ta, const __grid_constant__ CUtensorMap tb,\n"
+                "    const nb200::gemm::GemmParams p, const NbEpilogue::Args ea) {\n"
+                f"  {body}\n}}\n")
+            kernel = nvrtc.Kernel(nvrtc.compile_cubin_cached(source, name + ".cu",
+                                                             extra_opts=(f"-I{nvrtc.device_headers()}",)), name)
+            kernel.source = source
+            self._fused_kernels[key] = kernel
+        return kernel
+
+    def _launch_fused(self, grid, args):
+        """False when this launch's operands need a copy first (the two-kernel route does that)."""
+        import ctypes
+
+        from ..runtime import abi, kernels, nvrtc
+
+        g = self.gemm
+        m, n, k = g._extents(grid, args)
+        if m == 0 or n == 0:
+            return True
+        inner = {name: fn(args) for name, fn in g.inner}
+        lda, ldb, ldc = g.lda(args), g.ldb(args), g.ldc(args)
+        a, b, c = args[g.a], args[g.b], args[g.c]
+        if inner[g.c] != 1 or inner[g.a] != 1:
+            return False
+        b_transposed = inner[g.b] != 1
+        if b_transposed and ldb != 1:
+            return False
+        pitch_b = inner[g.b] if b_transposed else ldb
+        lib = abi.load()
+        tma, tmb = nvrtc.new_tensor_map(), nvrtc.new_tensor_map()
+        params = (ctypes.c_char * int(lib.nb200_gemm_params_bytes()))()
+        launch = abi.GemmLaunch()
+        cfg = g.config()
+        dtype_code, c_code = abi.dtype_code(a.dtype), abi.dtype_code(c.dtype)
+        rc = lib.nb200_gemm_plan(
+            kernels._dev_ptr(g.a, a), kernels._dev_ptr(g.b, b), kernels._dev_ptr(g.c, c), m, n, k, lda,
+            pitch_b, ldc, dtype_code, c_code, 1 if b_transposed else 0, ctypes.byref(cfg),
+            ctypes.byref(tma), ctypes.byref(tmb), ctypes.byref(params), ctypes.byref(launch))
+        if rc == abi.E_UNSUPPORTED:
+            return False          # a pitch or base bulk tensor copies cannot fetch
+        abi.check(rc)
+        if launch.nothing:
+            return True
+        if launch.only_clear:
+            return False          # K == 0: the generated kernel applies the epilogue to zeros
+        kernel = self._fused_kernel(launch, dtype_code, c_code)
+        ea = pointwise.marshal_struct(self.fused_params, args)
+        kernel.launch((launch.grid,), launch.block, [tma, tmb, params, ea], kernels.raw_stream(),
+                      launch.smem_bytes, cluster=launch.cluster if launch.cluster > 1 else None)
+        return True
+
+    # ---- launch -----------------------------------------------------------------------------------
 
     def launch(self, grid, args):
         import torch
 
         from ..runtime import abi
 
+        if self.fused_source is not None and self._launch_fused(grid, args):
+            return
         c = args[self.gemm.c]
         m, n, _ = self.gemm._extents(grid, args)
         if m == 0 or n == 0:
@@ -1240,9 +1354,9 @@ class PointwisePlan(Plan):
 
 
 def _lower_gemm_epilogue(trace, an, num_stages, num_warps):
-    gemm, acc, c_ptr = lower_gemm(trace, an, num_stages, epilogue=True)
+    gemm, acc, c_ptr, store = lower_gemm(trace, an, num_stages, epilogue=True)
     try:
-        return GemmEpiloguePlan(trace, gemm, acc, c_ptr, num_warps)
+        return GemmEpiloguePlan(trace, gemm, acc, c_ptr, num_warps, store)
     except pointwise.Unsupported as e:
         raise Unmatched(f"matmul with epilogue: {e}")
 

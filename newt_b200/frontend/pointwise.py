@@ -115,6 +115,8 @@ class _Context:
         self.arrays = []       # (name, dtype, count, byte offset) in shared memory
         self.shared_bytes = 0
         self.counter = 0
+        self.program_ids = {}  # grid axis -> C expression, when the code does not run one CUDA
+                               # block per program instance
 
     def fresh(self, prefix="v"):
         self.counter += 1
@@ -214,8 +216,11 @@ def _emit_new(body, node, dims):
     if op == "full":
         return _literal(node.args[0], dt)
     if op == "pid":
-        return f"(int)blockIdx.{'xyz'[at['axis']]}"
+        named = body.ctx.program_ids.get(at["axis"])      # an epilogue spliced into another kernel
+        return named if named is not None else f"(int)blockIdx.{'xyz'[at['axis']]}"
     if op == "nprog":
+        if body.ctx.program_ids:
+            raise Unsupported("nl.num_programs in code spliced into the matmul kernel")
         return f"(int)gridDim.{'xyz'[at['axis']]}"
     if op == "arange":
         return f"({int(node.args[0])} + {dims[0]})"
@@ -1198,6 +1203,76 @@ def generate(trace, num_warps, computed_elsewhere=None):
         f"extern \"C\" __global__ void __launch_bounds__({ctx.threads}) {kernel_name}({decl}) {{\n  "
         f"{body_text}\n}}\n")
     return source, kernel_name, params, dynamic
+
+
+def generate_epilogue(trace, accumulator, store, block, axes):
+    """The code a matmul program has after its k loop, as a functor for the tensor-core kernel's
+    epilogue (csrc/gemm_device.cuh `EPI`): `apply` gets 32 consecutive columns of one row of the
+    fp32 accumulator and leaves in them the value the program stores, evaluated element by
+    element exactly as the one-block-per-program kernel would (same graph, same emitter), with
+    the program ids and block indices derived from the element's row and column.
+
+    accumulator: (loop uid, carried name) of the k loop's result; store: the program's store
+    effect; block: (BLOCK_M, BLOCK_N); axes: (grid axis of the row blocks, of the column blocks).
+    Returns (CUDA text defining `struct NbEpilogue`, [(param name, type)] of its Args struct).
+    Raises Unsupported for what cannot run there (reductions over the tile, further loops that
+    store, anything needing shared memory): those programs take the two-kernel route."""
+    ctx = _Context(trace, THREADS_PER_WARP)
+    ctx.final[accumulator] = "nb_acc"
+    ctx.program_ids = {axes[0]: "nb_pid_m", axes[1]: "nb_pid_n"}
+    _, ptr, value, mask, _lineno = store[:5]
+    if len(ptr.shape) != 2:
+        raise Unsupported("the store after the k loop is not a 2-D tile")
+    body = _Body(ctx)
+    dims = ("nb_i", "nb_j")
+    elem = ptr.dtype.element
+    out = _convert(_emit(body, value, _operand_dims(ptr.shape, dims, value.shape)), value.dtype, elem)
+    if ctx.arrays or ctx.helpers:
+        raise Unsupported("the code after the k loop needs shared memory or helper routines")
+    params = [(name, node.dtype) for name, node in trace.params.items()]
+    fields = "\n".join(f"    {t.ctype} {name};" for name, t in params)
+    unpack = "\n".join(f"    {t.ctype} const {name} = nb_a.{name}; (void){name};" if isinstance(t, tp.pointer_type)
+                       else f"    const {t.ctype} {name} = nb_a.{name}; (void){name};" for name, t in params)
+    lines = "\n".join("      " + ln for ln in body.lines)
+    bm, bn = block
+    text = f"""
+struct NbEpilogue {{
+  struct Args {{
+{fields}
+  }};
+  static __device__ __forceinline__ void apply(float (&nb_v)[32], int nb_row, int nb_col0, const Args& nb_a) {{
+{unpack}
+    const int nb_pid_m = nb_row / {bm}, nb_i = nb_row % {bm};
+#pragma unroll
+    for (int nb_k = 0; nb_k < 32; ++nb_k) {{
+      const int nb_col = nb_col0 + nb_k;
+      const int nb_pid_n = nb_col / {bn}, nb_j = nb_col % {bn};
+      const float nb_acc = nb_v[nb_k];
+{lines}
+      nb_v[nb_k] = (float)({out});
+    }}
+  }}
+}};
+"""
+    return text, params
+
+
+def marshal_struct(params, args):
+    """A ctypes structure laid out like the `Args` struct `generate_epilogue` declares."""
+    fields = []
+    for name, t in params:
+        if isinstance(t, tp.pointer_type):
+            fields.append((name, ctypes.c_void_p))
+        else:
+            ctype = _CTYPES.get(t.name)
+            if ctype is None:
+                raise TypeError(f"argument '{name}': scalars of type {t.name} cannot be passed to a kernel")
+            fields.append((name, ctype))
+    packed = type("NbEpilogueArgs", (ctypes.Structure,), {"_fields_": fields})()
+    for name, t in params:
+        v = args[name]
+        setattr(packed, name, v.data_ptr() if isinstance(t, tp.pointer_type) else v)
+    return packed
 
 
 _CTYPES = {"int1": ctypes.c_bool, "int8": ctypes.c_int8, "uint8": ctypes.c_uint8,

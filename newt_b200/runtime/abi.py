@@ -39,6 +39,13 @@ class GemmConfig(ctypes.Structure):
     ]
 
 
+class GemmLaunch(ctypes.Structure):
+    """nb200_gemm_launch: which template instance a run-time compiled GEMM is, and its launch."""
+    _fields_ = [(name, ctypes.c_int32) for name in
+                ("pair", "block_n", "stages", "ksub", "grid", "block", "cluster", "smem_bytes",
+                 "nothing", "only_clear")] + [("reserved", ctypes.c_int32 * 6)]
+
+
 _i64 = ctypes.c_int64
 _vp = ctypes.c_void_p
 
@@ -65,6 +72,10 @@ SIGNATURES = {
                                               ctypes.POINTER(GemmConfig), _vp]),
     "nb200_gemm_acc32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                         ctypes.c_int, ctypes.c_int, ctypes.POINTER(GemmConfig), _vp]),
+    "nb200_gemm_params_bytes": (ctypes.c_int64, []),
+    "nb200_gemm_plan": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int,
+                                       ctypes.c_int, ctypes.c_int, ctypes.POINTER(GemmConfig), _vp, _vp,
+                                       _vp, ctypes.POINTER(GemmLaunch)]),
     "nb200_repitch": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, _vp]),
     "nb200_gemm_check": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                         ctypes.c_int, ctypes.POINTER(GemmConfig)]),

@@ -87,6 +87,32 @@ def compile_cubin(source, name="kernel.cu", arch="sm_100a", extra_opts=()):
         lib.nvrtcDestroyProgram(ctypes.byref(prog))
 
 
+def device_headers():
+    """The folder of the kernel library's device templates (sm100.cuh, gemm_device.cuh): kernels
+    compiled at run time from them get it as an include path."""
+    return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+
+
+_headers_digest = None
+
+
+def device_headers_digest():
+    """Hash of the device templates' text: a kernel compiled from them is stale when they change,
+    although its own source (which only includes them) does not."""
+    global _headers_digest
+    if _headers_digest is None:
+        import hashlib
+
+        h = hashlib.sha256()
+        folder = device_headers()
+        for name in sorted(os.listdir(folder)):
+            if name.endswith(".cuh"):
+                with open(os.path.join(folder, name), "rb") as f:
+                    h.update(f.read())
+        _headers_digest = h.hexdigest()[:16]
+    return _headers_digest
+
+
 def cache_dir():
     """Where compiled cubins are kept between processes: $NEWT_CACHE_DIR, else ~/.newt/cache
     (the reference's convention, newt/runtime/jit.py:21-24); None if it cannot be created."""
@@ -175,9 +201,13 @@ class Kernel:
                     self._functions[dev] = fn
         return fn
 
-    def launch(self, grid, block, args, stream, shared_bytes=0):
-        """`args`: ctypes values in parameter order; `stream`: a CUstream handle (int);
-        `shared_bytes`: dynamic shared memory (above 48 KB the function is opted in first)."""
+    def launch(self, grid, block, args, stream, shared_bytes=0, cluster=None):
+        """`args`: ctypes values in parameter order (structures and raw buffers are passed by
+        value: a `__grid_constant__ CUtensorMap` parameter is what `new_tensor_map` returns); `stream`: a
+        CUstream handle (int); `shared_bytes`: dynamic shared memory (above 48 KB the function
+        is opted in first); `cluster`: thread blocks per cluster along x, for kernels whose
+        CTAs work in clusters (launched through cuLaunchKernelEx with the cluster-dimension
+        attribute)."""
         import torch
 
         cu = _cuda or _load_cuda()
@@ -190,5 +220,56 @@ class Kernel:
         g = tuple(grid) + (1,) * (3 - len(grid))
         b = (block, 1, 1) if isinstance(block, int) else tuple(block) + (1,) * (3 - len(block))
         ptrs = (ctypes.c_void_p * len(args))(*map(ctypes.addressof, args))
-        _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], b[0], b[1], b[2], shared_bytes, ctypes.c_void_p(stream),
-                                 ptrs, None), f"launch of {self.func_name}")
+        if cluster is None:
+            _check(cu.cuLaunchKernel(fn, g[0], g[1], g[2], b[0], b[1], b[2], shared_bytes,
+                                     ctypes.c_void_p(stream), ptrs, None), f"launch of {self.func_name}")
+            return
+        attr = _LaunchAttribute()
+        attr.id = 4                                  # CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION
+        attr.value.cluster_dim[:] = [int(cluster), 1, 1]
+        config = _LaunchConfig(g[0], g[1], g[2], b[0], b[1], b[2], shared_bytes,
+                               ctypes.c_void_p(stream), ctypes.pointer(attr), 1)
+        _check(cu.cuLaunchKernelEx(ctypes.byref(config), fn, ptrs, None),
+               f"cluster launch of {self.func_name}")
+
+
+class _LaunchAttributeValue(ctypes.Union):       # CUlaunchAttributeValue: 64 bytes
+    _fields_ = [("pad", ctypes.c_char * 64), ("cluster_dim", ctypes.c_uint * 3)]
+
+
+class _LaunchAttribute(ctypes.Structure):        # CUlaunchAttribute
+    _fields_ = [("id", ctypes.c_int), ("pad", ctypes.c_char * 4), ("value", _LaunchAttributeValue)]
+
+
+class _LaunchConfig(ctypes.Structure):           # CUlaunchConfig
+    _fields_ = [("grid_x", ctypes.c_uint), ("grid_y", ctypes.c_uint), ("grid_z", ctypes.c_uint),
+                ("block_x", ctypes.c_uint), ("block_y", ctypes.c_uint), ("block_z", ctypes.c_uint),
+                ("shared_bytes", ctypes.c_uint), ("stream", ctypes.c_void_p),
+                ("attrs", ctypes.POINTER(_LaunchAttribute)), ("num_attrs", ctypes.c_uint)]
+
+
+def new_tensor_map():
+    """Storage for a CUtensorMap passed by value: sixteen 64-bit words on a 64-byte boundary
+    (ctypes cannot ask for the alignment, so the words are a view into a larger buffer)."""
+    raw = (ctypes.c_char * 192)()
+    view = (ctypes.c_uint64 * 16).from_buffer(raw, (-ctypes.addressof(raw)) % 64)
+    return view
+
+
+_DATA_TYPES = {1: 0, 2: 1, 4: 2}     # bytes per element -> CU_TENSOR_MAP_DATA_TYPE_UINT8/16/32
+
+
+def encode_tiled(address, elem_bytes, dims, strides_bytes, box, swizzle_128b=True):
+    """cuTensorMapEncodeTiled for a row-major tensor: `dims` innermost first, `strides_bytes` of
+    every dimension but the innermost, `box` the tile a copy moves.  No interleave, zero fill
+    out of range, 256-byte L2 promotion, 128-byte swizzle unless told otherwise."""
+    cu = _load_cuda()
+    rank = len(dims)
+    tmap = new_tensor_map()
+    rc = cu.cuTensorMapEncodeTiled(
+        ctypes.byref(tmap), _DATA_TYPES[elem_bytes], rank, ctypes.c_void_p(address),
+        (ctypes.c_uint64 * rank)(*dims), (ctypes.c_uint64 * max(rank - 1, 1))(*strides_bytes),
+        (ctypes.c_uint32 * rank)(*box), (ctypes.c_uint32 * rank)(*([1] * rank)),
+        0, 3 if swizzle_128b else 0, 2, 0)
+    _check(rc, "cuTensorMapEncodeTiled")
+    return tmap

@@ -7,6 +7,7 @@ import torch
 
 import newt_b200 as newt
 import newt_b200.deuteron as dt
+from newt_b200.examples import kernels as examples_kernels
 import newt_b200.language as nl
 from newt_b200 import types as tp
 from newt_b200.frontend import lower
@@ -374,6 +375,39 @@ def dt_linear_relu(x, y, bias, out):
         for tile_k in dt.tile(x.shape[1]):
             acc += x[tile_m, tile_k] @ y[tile_k, tile_n]
         out[tile_m, tile_n] = dt.relu(acc + bias[tile_n][None, :])
+
+
+def test_matmul_epilogue_is_compiled_into_the_tensor_core_kernel():
+    """relu(acc + bias) after the k loop: the program's own graph becomes an epilogue functor and
+    the library's device templates are compiled with it by NVRTC for sm_100a (no GPU needed)."""
+    import os
+
+    from newt_b200.runtime import abi, nvrtc
+
+    P16 = P(tp.bfloat16)
+    c = examples_kernels.linear_bias_relu_kernel.specialize(
+        P16, P16, P(tp.float32), P16, 512, 512, 512, 512, 1, 512, 1, 512, 1,
+        BLOCK_M=256, BLOCK_N=256, BLOCK_K=64, num_stages=7)
+    plan = c.plan
+    assert isinstance(plan, lower.GemmEpiloguePlan) and plan.fused_source is not None
+    assert "struct NbEpilogue" in plan.fused_source and "fmaxf(" in plan.fused_source
+    assert "nb_pid_n" in plan.fused_source and "blockIdx" not in plan.fused_source
+    assert plan.hardware_key()[-1] == "fused"
+    for launch in (abi.GemmLaunch(pair=1, block_n=256, stages=7, ksub=1),
+                   abi.GemmLaunch(pair=0, block_n=128, stages=4, ksub=1)):
+        kernel = plan._fused_kernel(launch, abi.BF16, abi.BF16)
+        assert kernel.cubin[:4] == b"\x7fELF" and "gemm_device.cuh" in kernel.source
+    # what was compiled: tcgen05 MMAs fed by bulk tensor copies, and no multicast load anywhere
+    text = "".join(open(os.path.join(nvrtc.device_headers(), f)).read()
+                   for f in ("gemm_device.cuh", "sm100.cuh"))
+    assert "tcgen05.mma" in text and "cp.async.bulk.tensor" in text
+    assert ".multicast::cluster" not in text
+    # a reduction over the tile cannot run per element: that program keeps the two-kernel route
+    r = rk.matmul_row_sums.specialize(P(tp.float16), P(tp.float16), P(tp.float32), 128, 128, 128, 128, 1,
+                                      128, 1, BLOCK_M=128, BLOCK_N=128, BLOCK_K=64) \
+        if hasattr(rk, "matmul_row_sums") else None
+    if r is not None:
+        assert isinstance(r.plan, lower.GemmEpiloguePlan) and r.plan.fused_source is None
 
 
 def test_matmul_with_epilogue_splits_into_product_and_generated_kernel():
