@@ -980,6 +980,8 @@ class GemmEpiloguePlan(Plan):
         except pointwise.Unsupported as why:
             self.fused_source, self.fused_reason = None, str(why)
         self._fused_kernels = {}     # template instance -> nvrtc.Kernel
+        self._fused_launches = {}    # (pointers, extents, pitches) -> what nb200_gemm_plan answered
+        self._args_type = None
         # The two-kernel route.  Its epilogue streams a BLOCK_M x BLOCK_N tile per program through
         # HBM once; the kernel's num_warps was chosen for the k loop.  Eight elements per thread
         # keep enough loads in flight: up to 32 warps for the tiles a tensor-core matmul uses.
@@ -1057,25 +1059,38 @@ class GemmEpiloguePlan(Plan):
         if b_transposed and ldb != 1:
             return False
         pitch_b = inner[g.b] if b_transposed else ldb
-        lib = abi.load()
-        tma, tmb = nvrtc.new_tensor_map(), nvrtc.new_tensor_map()
-        params = (ctypes.c_char * int(lib.nb200_gemm_params_bytes()))()
-        launch = abi.GemmLaunch()
-        cfg = g.config()
-        dtype_code, c_code = abi.dtype_code(a.dtype), abi.dtype_code(c.dtype)
-        rc = lib.nb200_gemm_plan(
-            kernels._dev_ptr(g.a, a), kernels._dev_ptr(g.b, b), kernels._dev_ptr(g.c, c), m, n, k, lda,
-            pitch_b, ldc, dtype_code, c_code, 1 if b_transposed else 0, ctypes.byref(cfg),
-            ctypes.byref(tma), ctypes.byref(tmb), ctypes.byref(params), ctypes.byref(launch))
-        if rc == abi.E_UNSUPPORTED:
-            return False          # a pitch or base bulk tensor copies cannot fetch
-        abi.check(rc)
+        # the host half of the launch is a function of the pointers, extents and pitches: the
+        # usual case is the same call repeated, which finds its tensor maps and parameters here
+        key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), a.dtype, c.dtype, m, n, k, lda, pitch_b, ldc,
+               b_transposed)
+        planned = self._fused_launches.get(key)
+        if planned is None:
+            lib = abi.load()
+            tma, tmb = nvrtc.new_tensor_map(), nvrtc.new_tensor_map()
+            params = (ctypes.c_char * int(lib.nb200_gemm_params_bytes()))()
+            launch = abi.GemmLaunch()
+            cfg = g.config()
+            dtype_code, c_code = abi.dtype_code(a.dtype), abi.dtype_code(c.dtype)
+            rc = lib.nb200_gemm_plan(
+                kernels._dev_ptr(g.a, a), kernels._dev_ptr(g.b, b), kernels._dev_ptr(g.c, c), m, n, k,
+                lda, pitch_b, ldc, dtype_code, c_code, 1 if b_transposed else 0, ctypes.byref(cfg),
+                ctypes.byref(tma), ctypes.byref(tmb), ctypes.byref(params), ctypes.byref(launch))
+            if rc == abi.E_UNSUPPORTED:
+                return False          # a pitch or base bulk tensor copies cannot fetch
+            abi.check(rc)
+            kernel = None if (launch.nothing or launch.only_clear) else \
+                self._fused_kernel(launch, dtype_code, c_code)
+            if len(self._fused_launches) >= 64:
+                self._fused_launches.clear()
+            planned = self._fused_launches[key] = (tma, tmb, params, launch, kernel)
+        tma, tmb, params, launch, kernel = planned
         if launch.nothing:
             return True
         if launch.only_clear:
             return False          # K == 0: the generated kernel applies the epilogue to zeros
-        kernel = self._fused_kernel(launch, dtype_code, c_code)
-        ea = pointwise.marshal_struct(self.fused_params, args)
+        if self._args_type is None:
+            self._args_type = pointwise.struct_type(self.fused_params)
+        ea = pointwise.marshal_struct(self.fused_params, args, self._args_type)
         kernel.launch((launch.grid,), launch.block, [tma, tmb, params, ea], kernels.raw_stream(),
                       launch.smem_bytes, cluster=launch.cluster if launch.cluster > 1 else None)
         return True

@@ -1257,8 +1257,8 @@ struct NbEpilogue {{
     return text, params
 
 
-def marshal_struct(params, args):
-    """A ctypes structure laid out like the `Args` struct `generate_epilogue` declares."""
+def struct_type(params):
+    """The ctypes structure laid out like the `Args` struct `generate_epilogue` declares."""
     fields = []
     for name, t in params:
         if isinstance(t, tp.pointer_type):
@@ -1268,7 +1268,12 @@ def marshal_struct(params, args):
             if ctype is None:
                 raise TypeError(f"argument '{name}': scalars of type {t.name} cannot be passed to a kernel")
             fields.append((name, ctype))
-    packed = type("NbEpilogueArgs", (ctypes.Structure,), {"_fields_": fields})()
+    return type("NbEpilogueArgs", (ctypes.Structure,), {"_fields_": fields})
+
+
+def marshal_struct(params, args, struct=None):
+    """An instance of `struct_type(params)` holding this launch's arguments."""
+    packed = (struct or struct_type(params))()
     for name, t in params:
         v = args[name]
         setattr(packed, name, v.data_ptr() if isinstance(t, tp.pointer_type) else v)

@@ -150,3 +150,32 @@ def test_epilogue_matmul_with_a_transposed_result_takes_the_one_kernel_path():
     assert isinstance(plan, GemmEpiloguePlan) and plan._whole_plan is not None
     want = torch.relu(a.float() @ b.float() + bias)
     torch.testing.assert_close(ct.t().cpu().float(), want, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("m,n,k,dtype", [(64, 96, 64, torch.float16), (300, 200, 136, torch.bfloat16),
+                                         (1024, 768, 512, torch.bfloat16),
+                                         (2048, 2048, 1024, torch.float16)])
+def test_epilogue_is_compiled_into_the_tensor_core_kernel(m, n, k, dtype):
+    """bias + relu after the k loop: one launch of the tcgen05 kernel with the program's own
+    epilogue compiled in (ragged edges, the one-CTA and the CTA-pair tiles), no fp32 buffer."""
+    from newt_b200.examples import kernels as K
+    from newt_b200.frontend.lower import GemmEpiloguePlan
+    from newt_b200.runtime import abi
+
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g) * 0.5).to(dtype)
+    b = (torch.randn(k, n, generator=g) * 0.5).to(dtype)
+    bias = torch.randn(n, generator=g)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    K.linear_bias_relu(a.cuda(), b.cuda(), bias.cuda(), c)
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    plans = [r.plan for r in K.linear_bias_relu_kernel.cache.values()
+             if isinstance(r.plan, GemmEpiloguePlan) and r.plan._fused_kernels]
+    assert plans, "the epilogue ran as a second kernel"
+    assert all(p._whole_plan is None for p in plans)
+    want = torch.relu(a.double() @ b.double() + bias.double())
+    got = c.cpu().double()
+    assert not torch.isnan(got).any()
+    tol = 2 ** -8 if dtype == torch.bfloat16 else 2 ** -10
+    assert ((got - want).norm() / want.norm()).item() < tol
