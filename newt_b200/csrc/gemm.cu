@@ -46,11 +46,12 @@ using gemm::GemmParams;
 using gemm::kBlockM;
 using gemm::kThreads;
 
-template <int BN, int STAGES, int DT, int CT>
+template <int BN, int STAGES, int KSUB, int DT, int CT>
 __global__ void __launch_bounds__(gemm::kThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  gemm::gemm_body<BN, STAGES, DT, CT, gemm::NoEpilogue>(tmap_a, tmap_b, p, gemm::NoEpilogueArgs{0});
+  gemm::gemm_body<BN, STAGES, KSUB, DT, CT, gemm::NoEpilogue>(tmap_a, tmap_b, p,
+                                                              gemm::NoEpilogueArgs{0});
 }
 
 template <int STAGES, int KSUB, int DT, int CT>
@@ -70,8 +71,9 @@ struct Resolved {
   bool pair;
 };
 
-int smem_bytes_for(int block_n, int stages) {   // a stage is 128 bytes of K for every row and column
-  return stages * (kBlockM * 128 + 128 * block_n) + 1024;
+// a ring slot holds `ksub` slabs of K: 128 bytes for every row of A and column of B each
+int smem_bytes_for(int block_n, int stages, int ksub) {
+  return stages * ksub * (kBlockM * 128 + 128 * block_n) + 1024 + (int)gemm::kEpilogueStageBytes;
 }
 
 // `row_k`: K elements per 128-byte row (64 for 16-bit operands, 32 for tf32); block_k is
@@ -99,18 +101,27 @@ int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, int row_k
     if (stages != 0 && (stages < 1 || stages > 8))
       return fail(NB200_E_INVALID, "stages=%d: supported 1..8", stages);
     out->block_n = 256;
-    // ring depth: 3 slots of 128 K-elements, 2 of 192, 4..7 of 64
+    // ring depth: 3 slots of 128 K-elements, 2 of 192, 4..6 of 64 (the epilogue's 16 KB of
+    // staging leaves no room for a seventh)
     out->stages = out->block_k == 2 * kBlockK ? 3 : (out->block_k == 3 * kBlockK ? 2 :
-                  (stages == 0 ? 6 : (stages >= 7 ? 7 : (stages >= 6 ? 6 : (stages >= 5 ? 5 : 4)))));
+                  (stages == 0 ? 6 : (stages >= 6 ? 6 : (stages >= 5 ? 5 : 4))));
     return 0;
   }
   if (bm != 0 && bm != kBlockM)
     return fail(NB200_E_INVALID, "block_m=%d: MMA tiles are 128 rows (256 for a CTA pair)", bm);
-  if (bk != 0 && bk != kBlockK)
-    return fail(NB200_E_INVALID, "block_k=%d: the TMA ring moves %d-element K slabs", bk, kBlockK);
   if (bn == 0) bn = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
   if (bn != 64 && bn != 128 && bn != 256)
     return fail(NB200_E_INVALID, "block_n=%d: supported 64, 128, 256", bn);
+  if (bk == 2 * kBlockK && bn != 256) {   // two K slabs per ring slot: half as many copies to issue
+    out->block_n = bn;
+    out->block_k = bk;
+    out->stages = bn == 64 ? 4 : 3;
+    return 0;
+  }
+  if (bk != 0 && bk != kBlockK)
+    return fail(NB200_E_INVALID,
+                "block_k=%d: a ring slot holds %d elements of K (%d too for 64 and 128 columns)", bk,
+                kBlockK, 2 * kBlockK);
   // ring depths with a compiled instance, deepest first (bounded by 227 KB of shared memory)
   static const int depth256[] = {4, 3, 2, 0}, depth128[] = {6, 4, 3, 2, 0}, depth64[] = {8, 6, 4, 2, 0};
   const int* depths = bn == 256 ? depth256 : (bn == 128 ? depth128 : depth64);
@@ -166,11 +177,11 @@ int check_problem(const void* a, const void* b, const void* c, int64_t m, int64_
                          : (c_f32 ? (const void*)KERNEL<__VA_ARGS__, NB200_F16, NB200_F32>   \
                                   : (const void*)KERNEL<__VA_ARGS__, NB200_F16, NB200_F16>))
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KSUB = 1>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype, bool c_f32,
            int grid, cudaStream_t stream) {
-  const int smem = smem_bytes_for(BN, STAGES);
-  const void* kern = NB200_PICK(gemm_kernel, BN, STAGES);
+  const int smem = smem_bytes_for(BN, STAGES, KSUB);
+  const void* kern = NB200_PICK(gemm_kernel, BN, STAGES, KSUB);
   if (int rc = prepare_kernel(kern, smem)) return rc;
   void* args[3] = {(void*)&ta, (void*)&tb, (void*)&p};
   return cuda_check(cudaLaunchKernel(kern, dim3(grid), dim3(kThreads), args, smem, stream), "gemm launch");
@@ -197,7 +208,9 @@ int pair_clusters(const void* kern, int smem, const GemmParams& p, int* clusters
   return 0;
 }
 
-int pair_smem_bytes(int stages, int ksub) { return stages * ksub * (kBlockM * 128 + 128 * 128) + 1024; }
+int pair_smem_bytes(int stages, int ksub) {
+  return stages * ksub * (kBlockM * 128 + 128 * 128) + 1024 + (int)gemm::kEpilogueStageBytes;
+}
 
 template <int STAGES, int KSUB>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype,
@@ -372,22 +385,52 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   out->only_clear = !out->nothing_to_do && k == 0;
   if (out->nothing_to_do || out->only_clear) return 0;
 
-  {
+  // K slabs per ring slot of the pair kernel; the one-CTA kernel's slots hold one
+  const int ksub = cfg.block_k == 2 * row_k ? 2 : cfg.block_k == 3 * row_k ? 3 : 1;
+  const bool whole_k_rows = k % row_k == 0;
+  // A slot wants one copy per operand (see GemmParams::wide_a).  The 3-D views reach past a
+  // ragged edge into the next row, so they are used only where there is no such edge.
+  const bool wide_a = ksub > 1 && whole_k_rows;
+  bool wide_b;
+  if (wide_a) {   // [K / row, M, row]
+    const uint64_t dims[3] = {(uint64_t)row_k, (uint64_t)m, (uint64_t)(k / row_k)};
+    const uint64_t strides[2] = {(uint64_t)lda * eb, 128};
+    const uint32_t box[3] = {(uint32_t)row_k, (uint32_t)kBlockM, (uint32_t)ksub};
+    if (int rc = encode_tensor_map(&out->ta, a, eb, 3, dims, strides, box)) return rc;
+  } else {
     const uint64_t dims[2] = {(uint64_t)k, (uint64_t)m};
     const uint64_t strides[1] = {(uint64_t)lda * eb};
     const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)kBlockM};
     if (int rc = encode_tensor_map(&out->ta, a, eb, 2, dims, strides, box)) return rc;
   }
-  if (b_kmajor) {   // rows of B^T: one box per CTA and stage
-    const uint64_t dims[2] = {(uint64_t)k, (uint64_t)n};
-    const uint64_t strides[1] = {(uint64_t)ldb * eb};
-    const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)(cfg.pair ? 128 : cfg.block_n)};
-    if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box)) return rc;
+  if (b_kmajor) {   // rows of B^T: one box per CTA and K slab
+    const uint32_t rows = (uint32_t)(cfg.pair ? 128 : cfg.block_n);
+    wide_b = wide_a;
+    if (wide_b) {
+      const uint64_t dims[3] = {(uint64_t)row_k, (uint64_t)n, (uint64_t)(k / row_k)};
+      const uint64_t strides[2] = {(uint64_t)ldb * eb, 128};
+      const uint32_t box[3] = {(uint32_t)row_k, rows, (uint32_t)ksub};
+      if (int rc = encode_tensor_map(&out->tb, b, eb, 3, dims, strides, box)) return rc;
+    } else {
+      const uint64_t dims[2] = {(uint64_t)k, (uint64_t)n};
+      const uint64_t strides[1] = {(uint64_t)ldb * eb};
+      const uint32_t box[2] = {(uint32_t)row_k, rows};
+      if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box)) return rc;
+    }
   } else {
-    const uint64_t dims[2] = {(uint64_t)n, (uint64_t)k};
-    const uint64_t strides[1] = {(uint64_t)ldb * eb};
-    const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)row_k};
-    if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box)) return rc;
+    const int slabs = (cfg.pair ? 128 : cfg.block_n) / row_k;   // column slabs per CTA
+    wide_b = n % row_k == 0 && slabs * ksub > 1;
+    if (wide_b) {   // [N / slab, K, slab]
+      const uint64_t dims[3] = {(uint64_t)row_k, (uint64_t)k, (uint64_t)(n / row_k)};
+      const uint64_t strides[2] = {(uint64_t)ldb * eb, 128};
+      const uint32_t box[3] = {(uint32_t)row_k, (uint32_t)(row_k * ksub), (uint32_t)slabs};
+      if (int rc = encode_tensor_map(&out->tb, b, eb, 3, dims, strides, box)) return rc;
+    } else {
+      const uint64_t dims[2] = {(uint64_t)n, (uint64_t)k};
+      const uint64_t strides[1] = {(uint64_t)ldb * eb};
+      const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)row_k};
+      if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box)) return rc;
+    }
   }
 
   GemmParams& p = out->p;
@@ -405,6 +448,8 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
                 ? sm100::instr_desc_tf32(mma_m, cfg.block_n, false, false)
                 : sm100::instr_desc_f16(mma_m, cfg.block_n, dtype == NB200_BF16, false, !b_kmajor);
   p.b_kmajor = b_kmajor ? 1 : 0;
+  p.wide_a = wide_a ? 1 : 0;
+  p.wide_b = wide_b ? 1 : 0;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * c_bytes) % 16 == 0) ? 1 : 0;
   p.wait_limit_ns = wait_limit_ns();
   p.status = device_status_ptr();
@@ -432,14 +477,16 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
     switch (cfg.stages) {
       case 4: return launch_pair<4, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
       case 5: return launch_pair<5, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
-      case 6: return launch_pair<6, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
-      default: return launch_pair<7, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
+      default: return launch_pair<6, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
     }
   }
   const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
   const int sms = device_info().sm_count;
   const int grid = (int)(tiles < sms ? tiles : sms);
 
+  if (cfg.block_k == 2 * g.row_k)
+    return cfg.block_n == 64 ? launch<64, 4, 2>(g.ta, g.tb, p, dtype, c_f32, grid, stream)
+                             : launch<128, 3, 2>(g.ta, g.tb, p, dtype, c_f32, grid, stream);
 #define NB200_GEMM_CASE(BN_, ST_)                  \
   if (cfg.block_n == BN_ && cfg.stages == ST_)     \
     return launch<BN_, ST_>(g.ta, g.tb, p, dtype, c_f32, grid, stream);
@@ -591,11 +638,11 @@ extern "C" int nb200_gemm_plan(const void* a, const void* b, void* c, int64_t m,
   launch->block = kThreads;
   launch->block_n = g.cfg.block_n;
   if (g.cfg.pair) {
-    // the instances the library has itself: 3 slots of two K slabs, 2 of three, 4..7 of one
+    // the instances the library has itself: 3 slots of two K slabs, 2 of three, 4..6 of one
     int stages = g.cfg.stages, ksub = 1;
     if (g.cfg.block_k == 2 * g.row_k) stages = 3, ksub = 2;
     else if (g.cfg.block_k == 3 * g.row_k) stages = 2, ksub = 3;
-    else stages = stages < 4 ? 4 : (stages > 7 ? 7 : stages);
+    else stages = stages < 4 ? 4 : (stages > 6 ? 6 : stages);
     launch->pair = 1;
     launch->stages = stages;
     launch->ksub = ksub;
@@ -606,8 +653,7 @@ extern "C" int nb200_gemm_plan(const void* a, const void* b, void* c, int64_t m,
                      : stages == 2 && ksub == 3 ? (const void*)gemm_pair_kernel<2, 3, NB200_BF16, NB200_BF16>
                      : stages == 4 ? (const void*)gemm_pair_kernel<4, 1, NB200_BF16, NB200_BF16>
                      : stages == 5 ? (const void*)gemm_pair_kernel<5, 1, NB200_BF16, NB200_BF16>
-                     : stages == 6 ? (const void*)gemm_pair_kernel<6, 1, NB200_BF16, NB200_BF16>
-                                   : (const void*)gemm_pair_kernel<7, 1, NB200_BF16, NB200_BF16>;
+                                   : (const void*)gemm_pair_kernel<6, 1, NB200_BF16, NB200_BF16>;
     if (int rc = prepare_kernel(twin, launch->smem_bytes)) return rc;
     int clusters = 0;
     if (int rc = pair_clusters(twin, launch->smem_bytes, g.p, &clusters)) return rc;
@@ -615,9 +661,9 @@ extern "C" int nb200_gemm_plan(const void* a, const void* b, void* c, int64_t m,
     return 0;
   }
   launch->stages = g.cfg.stages;
-  launch->ksub = 1;
+  launch->ksub = g.cfg.block_k == 2 * g.row_k ? 2 : 1;
   launch->cluster = 1;
-  launch->smem_bytes = smem_bytes_for(g.cfg.block_n, g.cfg.stages);
+  launch->smem_bytes = smem_bytes_for(g.cfg.block_n, g.cfg.stages, launch->ksub);
   const int64_t tiles = (int64_t)g.p.m_blocks * g.p.n_blocks;
   const int sms = device_info().sm_count;
   launch->grid = (int)(tiles < sms ? tiles : sms);
@@ -697,3 +743,9 @@ extern "C" int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int
   return gemm_tf32_via(a, b, c, m, n, k, lda, ldb, ldc, config, scratch,
                        static_cast<cudaStream_t>(stream));
 }
+
+#ifdef NB200_GEMM_TRACE
+extern "C" int nb200_debug_gemm_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, nb200::gemm::g_gemm_trace, sizeof(nb200::gemm::g_gemm_trace));
+}
+#endif

@@ -93,6 +93,22 @@ template <class A> struct std_is_same<A, A> { static constexpr bool value = true
 constexpr int kThreads = 192;
 constexpr int kGroupM = 8;      // row-blocks per L2 band of the tile order
 
+// Time stamps of one CTA's roles, for development builds only (-DNB200_GEMM_TRACE; the shipped
+// library and the kernels compiled at run time have none of this).
+#ifdef NB200_GEMM_TRACE
+__device__ long long g_gemm_trace[4][128][2];
+#define GTRACE_DECL int gtrace_n = 0;
+#define GTRACE(role, id, cond)                                               \
+  if (blockIdx.x == NB200_GEMM_TRACE && (cond) && gtrace_n < 128) {          \
+    g_gemm_trace[role][gtrace_n][0] = (id);                                  \
+    g_gemm_trace[role][gtrace_n][1] = clock64();                             \
+    ++gtrace_n;                                                              \
+  }
+#else
+#define GTRACE_DECL
+#define GTRACE(role, id, cond)
+#endif
+
 struct GemmParams {
   void* c;
   long long ldc;
@@ -101,6 +117,13 @@ struct GemmParams {
   uint32_t idesc;
   int c_vec_ok;  // C base and row pitch are 16-byte aligned
   int b_kmajor;  // B is given transposed ([N, K], K contiguous); always so for tf32
+  // One bulk copy costs its issuing thread over a hundred cycles whatever its size, so a ring
+  // slot is filled with as few copies as the shapes allow.  wide_a / wide_b: the tensor map is
+  // the 3-D view [K / row, rows, row] (K-major operands; needs K to be whole 128-byte rows) or
+  // [N / slab, K, slab] (B as [K, N]; needs N to be whole slabs), and one copy brings every K
+  // slab of the slot, or every column slab of B, at once.  Otherwise the maps are 2-D and the
+  // slot is filled slab by slab, zero-filled at the ragged edges.
+  int wide_a, wide_b;
   unsigned long long wait_limit_ns;
   unsigned int* status;
 };
@@ -119,21 +142,85 @@ struct NoEpilogue {
   static __device__ __forceinline__ void apply(float (&)[32], int, int, const Args&) {}
 };
 
-// The epilogue of one 32-column chunk: functor, one rounding to C's type, store.
-template <int CT, class EPI>
-__device__ __forceinline__ void finish_chunk(void* c, long long ldc, int row, int col0, int n,
-                                             bool vec_ok, uint32_t (&r)[32],
-                                             const typename EPI::Args& ea) {
-  if constexpr (!std_is_same<EPI, NoEpilogue>::value) {
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-    EPI::apply(v, row, col0, ea);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(v[j]);
-  }
+// The epilogue of one warp: its 32 rows (tensor-memory lanes) of a BN-column accumulator go
+// to C.  A thread holds one row, so storing from registers would write 16 bytes to each of 32
+// rows per instruction -- half-filled 32-byte sectors, which made the epilogue of a 128 x 256
+// tile take ~4900 cycles.  Instead a pass of 128 bytes of C per row (64 columns of a 16-bit C,
+// 32 of an fp32 C) is rounded, parked in this warp's 4 KB of shared memory (16-byte pieces
+// XOR-swizzled by the row, conflict-free both ways) and written out four whole 128-byte rows
+// per instruction.  Ragged edges and unaligned C take the register path.
+constexpr uint32_t kEpilogueStageBytes = 4 * 32 * 128;   // four epilogue warps
+
+template <int BN, int CT, class EPI>
+__device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ldc, int row0,
+                                           int col_base, int m, int n, bool vec_ok, uint32_t stage,
+                                           int lane, const typename EPI::Args& ea) {
   using OutT = typename ElemType<CT>::T;
-  store_chunk<CT>(static_cast<OutT*>(c) + (long long)row * ldc, col0, n, vec_ok, r);
+  constexpr int kPass = 128 / (int)sizeof(OutT);     // columns per pass
+  constexpr int kPer16 = 16 / (int)sizeof(OutT);     // columns per 16-byte piece
+  const int row = row0 + lane;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += kPass) {
+    const int col0 = col_base + c0;
+    if (col0 >= n) break;   // uniform across the warp
+    uint32_t r[kPass];
+    tmem_ld_cols<kPass>(t_row + c0, r);
+    tmem_ld_wait();
+    if constexpr (!std_is_same<EPI, NoEpilogue>::value) {
+#pragma unroll
+      for (int q = 0; q < kPass / 32; ++q) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[q * 32 + j]);
+        EPI::apply(v, row, col0 + q * 32, ea);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[q * 32 + j] = __float_as_uint(v[j]);
+      }
+    }
+    if (vec_ok && col0 + kPass <= n) {
+      const uint32_t mine = stage + lane * 128;
+#pragma unroll
+      for (int pc = 0; pc < 8; ++pc) {
+        uint32_t w[4];
+        if constexpr (CT == NB200_F32) {
+#pragma unroll
+          for (int h = 0; h < 4; ++h) w[h] = r[pc * 4 + h];
+        } else {
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const float lo = __uint_as_float(r[pc * 8 + 2 * h]);
+            const float hi = __uint_as_float(r[pc * 8 + 2 * h + 1]);
+            if constexpr (CT == NB200_BF16) {
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(lo, hi);
+              w[h] = *reinterpret_cast<uint32_t*>(&v2);
+            } else {
+              __half2 v2 = __floats2half2_rn(lo, hi);
+              w[h] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+          }
+        }
+        st_shared_v4(mine + ((pc ^ (lane & 7)) << 4), w[0], w[1], w[2], w[3]);
+      }
+      __syncwarp();
+      const int pc = lane & 7;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3);
+        uint32_t w0, w1, w2, w3;
+        ld_shared_v4(stage + rr * 128 + ((pc ^ (rr & 7)) << 4), w0, w1, w2, w3);
+        if (row0 + rr < m)
+          *reinterpret_cast<uint4*>(static_cast<OutT*>(c) + (long long)(row0 + rr) * ldc + col0 +
+                                    pc * kPer16) = make_uint4(w0, w1, w2, w3);
+      }
+      __syncwarp();
+    } else if (row < m) {
+      OutT* crow = static_cast<OutT*>(c) + (long long)row * ldc;
+#pragma unroll
+      for (int q = 0; q < kPass / 32; ++q)
+        store_chunk<CT>(crow, col0 + q * 32, n, vec_ok,
+                        *reinterpret_cast<const uint32_t (*)[32]>(&r[q * 32]));
+    }
+  }
 }
 
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int* mb,
@@ -148,15 +235,19 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
   *nb = in_band / rows;
 }
 
-template <int BN, int STAGES, int DT, int CT, class EPI>
+// A ring slot holds KSUB slabs of K (a slab = one 128-byte row of K per row of A and per
+// column of B): first A's KSUB slabs, 16 KB each; then B -- given as [N, K], its KSUB slabs
+// like A's; given as [K, N], column slab after column slab, each with the K rows of all KSUB
+// slabs one after the other.
+template <int BN, int STAGES, int KSUB, int DT, int CT, class EPI>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                           const GemmParams& p, const typename EPI::Args& ea) {
-  constexpr int kBK = Elem<DT>::kPerRow;                // K elements per stage
+  constexpr int kBK = Elem<DT>::kPerRow;                // K elements per slab
   constexpr int kSlab = Elem<DT>::kPerRow;              // columns of B per slab
   constexpr uint32_t kABytes = kBlockM * 128;           // 16 KB
   constexpr uint32_t kBSlab = kBK * 128;                // one slab of B: 8 KB (4 KB for tf32)
   constexpr uint32_t kBBytes = kBSlab * (BN / kSlab);
-  constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kStageBytes = KSUB * (kABytes + kBBytes);
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators, BN fp32 columns each
 
   extern __shared__ uint8_t smem_raw[];
@@ -166,7 +257,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1 KB
+  const uint32_t epi_stage = smem_base + STAGES * kStageBytes;       // behind the ring
   const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
+  GTRACE_DECL
+  GTRACE(0, 0, threadIdx.x == 0)      // kernel entered
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -192,8 +286,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  GTRACE(0, 1, threadIdx.x == 0)      // set up
 
   const int num_tiles = p.m_blocks * p.n_blocks;
+  const int k_rounds = (p.k_blocks + KSUB - 1) / KSUB;
   // The tensor core takes tf32 operands K-major only (an MN-major B gives zeros), so fp32
   // always comes with B transposed; for 16-bit types it is the caller's choice.
   const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;
@@ -207,20 +303,40 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mb, nb;
         tile_coords(tile, p.m_blocks, p.n_blocks, &mb, &nb);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = 0; kb < k_rounds; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
           if (!ok) break;
           const uint32_t bar = smem_u32(&full_bar[stage]);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + KSUB * kABytes;
+          const int slab0 = kb * KSUB;
           mbar_arrive_expect_tx(bar, kStageBytes);
-          tma_load_2d(a_dst, &tmap_a, kb * kBK, mb * kBlockM, bar);
-          if (b_kmajor) {   // BN rows of B^T, one 128-byte row of K each
-            tma_load_2d(a_dst + kABytes, &tmap_b, kb * kBK, nb * BN, bar);
+          if (KSUB > 1 && p.wide_a) {
+            tma_load_3d(a_dst, &tmap_a, 0, mb * kBlockM, slab0, bar);
+          } else {
+#pragma unroll
+            for (int sub = 0; sub < KSUB; ++sub)
+              tma_load_2d(a_dst + sub * kABytes, &tmap_a, (slab0 + sub) * kBK, mb * kBlockM, bar);
+          }
+          if (b_kmajor) {   // BN rows of B^T, laid out like A
+            if (KSUB > 1 && p.wide_b) {
+              tma_load_3d(b_dst, &tmap_b, 0, nb * BN, slab0, bar);
+            } else {
+#pragma unroll
+              for (int sub = 0; sub < KSUB; ++sub)
+                tma_load_2d(b_dst + sub * kBBytes, &tmap_b, (slab0 + sub) * kBK, nb * BN, bar);
+            }
+          } else if (p.wide_b) {   // all column slabs of the tile, KSUB * 64 rows of K each
+            tma_load_3d(b_dst, &tmap_b, 0, slab0 * kBK, nb * (BN / kSlab), bar);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / kSlab; ++j)
-              tma_load_2d(a_dst + kABytes + j * kBSlab, &tmap_b, nb * BN + j * kSlab, kb * kBK, bar);
+#pragma unroll
+              for (int sub = 0; sub < KSUB; ++sub)
+                tma_load_2d(b_dst + (j * KSUB + sub) * kBSlab, &tmap_b, nb * BN + j * kSlab,
+                            (slab0 + sub) * kBK, bar);
           }
+          GTRACE(0, 100 + kb, (kb & 7) == 0)     // copies of k block kb issued
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -240,7 +356,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       // A: K-major, 8-row groups 1024 B apart.  B: MN-major, 8-row K groups
       // 1024 B apart, 64-column slabs kBSlab apart.
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
-      constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
+      constexpr uint64_t kBDesc = smem_desc_sw128(KSUB * kBSlab, 1024);
       const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
       int stage = 0;
       uint32_t phase = 0;
@@ -253,20 +369,26 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = 0; kb < k_rounds; ++kb) {
           ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
           tc_fence_after_sync();
+          GTRACE(1, 100 + kb, elected && (kb & 7) == 0)  // k block kb landed
           const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint64_t a_desc = with_address(kADesc, a_addr);
-          const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
+          const uint32_t b_addr = a_addr + KSUB * kABytes;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            // +32 B along K inside a K-major swizzle row; + a quarter of the stage's K-rows
-            // (128 B each) inside an MN-major slab of B
-            if (elected)
-              mma_ss<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
-                         p.idesc, (kb | kk) != 0 ? 1u : 0u);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const uint64_t a_desc = with_address(kADesc, a_addr + sub * kABytes);
+            const uint64_t b_desc = b_kmajor ? with_address(kADesc, b_addr + sub * kBBytes)
+                                             : with_address(kBDesc, b_addr + sub * kBSlab);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              // +32 B along K inside a K-major swizzle row; + a quarter of a slab's K rows
+              // (128 B each) inside an MN-major slab of B
+              if (elected)
+                mma_ss<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
+                           p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
+            }
           }
           if (elected) mma_commit(smem_u32(&empty_bar[stage]));  // slot reusable once these retire
           __syncwarp();
@@ -276,6 +398,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
           }
         }
         if (ok && elected) mma_commit(smem_u32(&acc_full_bar[buf]));
+        GTRACE(1, 2, elected)           // last product issued
         __syncwarp();
       }
     }
@@ -293,24 +416,19 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = mb * kBlockM + quarter * 32 + lane;
+      GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = nb * BN + c0;
-        if (col0 >= p.n) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (row < p.m) finish_chunk<CT, EPI>(p.c, p.ldc, row, col0, p.n, p.c_vec_ok != 0, r, ea);
-      }
+      drain_rows<BN, CT, EPI>(t_row, p.c, p.ldc, mb * kBlockM + quarter * 32, nb * BN, p.m, p.n,
+                              p.c_vec_ok != 0, epi_stage + quarter * (32 * 128), lane, ea);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buf]));
+      GTRACE(2, 4, threadIdx.x == 64)   // tile stored
     }
   }
 
   __syncthreads();
+  GTRACE(0, 5, threadIdx.x == 0)        // all roles done
   if (abort_flag) {
     // give bulk copies that may still be in flight time to land before the
     // shared memory they target is released
@@ -359,7 +477,10 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
   const uint32_t rank = cluster_cta_rank();
   const bool leader = rank == 0;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t epi_stage = smem_base + STAGES * kStageBytes;       // behind the ring
   const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
+  GTRACE_DECL
+  GTRACE(0, 0, threadIdx.x == 0)      // kernel entered
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -386,6 +507,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
   cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  GTRACE(0, 1, threadIdx.x == 0)      // set up
 
   const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;   // see gemm_kernel
   const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
@@ -409,19 +531,37 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
           if (!ok) break;
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * kStageBytes);
+          // A slot: this CTA's A rows for KSUB slabs of K, then its share of B.  Slabs past K
+          // and rows or columns past the matrix are zero-filled by the tensor maps.
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + KSUB * kABytes;
+          const int slab0 = kb * KSUB;
+          if (p.wide_a) {
+            tma_load_3d_pair(a_dst, &tmap_a, 0, row0, slab0, bar);
+          } else {
 #pragma unroll
-          for (int sub = 0; sub < KSUB; ++sub) {   // slabs past K are zero-filled by the tensor map
-            const uint32_t a_dst = smem_base + stage * kStageBytes + sub * kSlabBytes;
-            const int k0 = (kb * KSUB + sub) * kBK;
-            tma_load_2d_pair(a_dst, &tmap_a, k0, row0, bar);
-            if (b_kmajor) {   // this CTA's 128 rows of B^T
-              tma_load_2d_pair(a_dst + kABytes, &tmap_b, k0, col0, bar);
+            for (int sub = 0; sub < KSUB; ++sub)
+              tma_load_2d_pair(a_dst + sub * kABytes, &tmap_a, (slab0 + sub) * kBK, row0, bar);
+          }
+          if (b_kmajor) {   // this CTA's 128 rows of B^T, laid out like A
+            if (p.wide_b) {
+              tma_load_3d_pair(b_dst, &tmap_b, 0, col0, slab0, bar);
             } else {
 #pragma unroll
-              for (int j = 0; j < 128 / kSlab; ++j)
-                tma_load_2d_pair(a_dst + kABytes + j * kBSlab, &tmap_b, col0 + j * kSlab, k0, bar);
+              for (int sub = 0; sub < KSUB; ++sub)
+                tma_load_2d_pair(b_dst + sub * kBBytes, &tmap_b, (slab0 + sub) * kBK, col0, bar);
             }
+          } else if (p.wide_b) {   // both column slabs, KSUB * 64 rows of K each
+            tma_load_3d_pair(b_dst, &tmap_b, 0, slab0 * kBK, col0 / kSlab, bar);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 128 / kSlab; ++j)
+#pragma unroll
+              for (int sub = 0; sub < KSUB; ++sub)
+                tma_load_2d_pair(b_dst + (j * KSUB + sub) * kBSlab, &tmap_b, col0 + j * kSlab,
+                                 (slab0 + sub) * kBK, bar);
           }
+          GTRACE(0, 100 + kb, (kb & 7) == 0)     // copies of k round kb issued
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -443,7 +583,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       const uint32_t acc_full0 = map_to_cta(smem_u32(&acc_full_bar[0]), 0);
       const uint32_t acc_full1 = map_to_cta(smem_u32(&acc_full_bar[0]), 1);
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
-      constexpr uint64_t kBDesc = smem_desc_sw128(kBSlab, 1024);
+      constexpr uint64_t kBDesc = smem_desc_sw128(KSUB * kBSlab, 1024);   // column slabs of B
       const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
       int stage = 0;
       uint32_t phase = 0;
@@ -460,11 +600,16 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
           ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
           tc_fence_after_sync();
+          GTRACE(1, 100 + kb, elected && (kb & 7) == 0)  // k round kb landed
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint32_t b_addr = a_addr + KSUB * kABytes;
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {
-            const uint32_t a_addr = smem_base + stage * kStageBytes + sub * kSlabBytes;
-            const uint64_t a_desc = with_address(kADesc, a_addr);
-            const uint64_t b_desc = with_address(b_kmajor ? kADesc : kBDesc, a_addr + kABytes);
+            // K-major operands: slab `sub` is a block of its own.  B as [K, N]: a column slab
+            // holds the K rows of all KSUB slabs one after the other.
+            const uint64_t a_desc = with_address(kADesc, a_addr + sub * kABytes);
+            const uint64_t b_desc = b_kmajor ? with_address(kADesc, b_addr + sub * kBBytes)
+                                             : with_address(kBDesc, b_addr + sub * kBSlab);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               if (elected)
@@ -486,6 +631,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
           mma_commit_pair(acc_full0 + buf * 8);
           mma_commit_pair(acc_full1 + buf * 8);
         }
+        GTRACE(1, 2, elected)           // last product issued
         __syncwarp();
       }
     }
@@ -503,20 +649,15 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = mb * 2 * kBlockM + rank * kBlockM + quarter * 32 + lane;
+      GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = nb * BN + c0;
-        if (col0 >= p.n) break;
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (row < p.m) finish_chunk<CT, EPI>(p.c, p.ldc, row, col0, p.n, p.c_vec_ok != 0, r, ea);
-      }
+      drain_rows<BN, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
+                              nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),
+                              lane, ea);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[buf]), 0));
+      GTRACE(2, 4, threadIdx.x == 64)   // tile stored
     }
   }
 
@@ -526,6 +667,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
   }
   cluster_sync_all();   // nobody leaves while the other CTA may still touch its barriers or tiles
+  GTRACE(0, 5, threadIdx.x == 0)        // all roles done
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();

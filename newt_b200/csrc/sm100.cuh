@@ -118,6 +118,19 @@ __device__ __forceinline__ bool mbar_wait_nocall(uint32_t bar, uint32_t parity, 
   return mbar_spin(bar, parity, ctx, code, detail);
 }
 
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c,
+                                             uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+               : "r"(addr)
+               : "memory");
+}
+
 // Named barriers 1..15 (0 is __syncthreads): `threads` threads take part, as whole warps;
 // `arrive` counts toward the barrier without waiting for it.
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
@@ -356,6 +369,15 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       " [%0], [%1, {%2, %3}], [%4];"
       :
       : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, int x,
+                                                 int y, int z, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(cluster_bar)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t cols) {

@@ -37,7 +37,7 @@ def search_space(tunable, has_dot):
     if has_dot:
         space = {name: [64, 128, 256] for name in tunable}
         space["num_warps"] = [4]
-        space["num_stages"] = [2, 3, 4, 6, 7]
+        space["num_stages"] = [2, 3, 4, 5, 6]
     else:
         space = {name: [1 << i for i in range(12)] for name in tunable}
         space["num_warps"] = [2, 4, 8]

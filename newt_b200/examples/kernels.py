@@ -96,12 +96,14 @@ def layernorm(x, w, b, eps=1e-5, out=None):
 @newt.autotune(
     configs=[
         newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 128}, num_warps=4, num_stages=3),
-        newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=7),
+        newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=6),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=4),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=3),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_warps=4, num_stages=6),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 64}, num_warps=4, num_stages=4),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 64}, num_warps=4, num_stages=8),
+        newt.Config({"BLOCK_M": 128, "BLOCK_N": 128, "BLOCK_K": 128}, num_warps=4, num_stages=3),
+        newt.Config({"BLOCK_M": 128, "BLOCK_N": 64, "BLOCK_K": 128}, num_warps=4, num_stages=4),
     ],
     key=["M", "N", "K"],
 )
@@ -164,7 +166,7 @@ def linear_bias_relu_kernel(a_ptr, b_ptr, bias_ptr, c_ptr, M, N, K, sam, sak, sb
              mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
 
 
-def linear_bias_relu(a, b, bias, c=None, BLOCK_M=256, BLOCK_N=256, BLOCK_K=64, num_stages=7):
+def linear_bias_relu(a, b, bias, c=None, BLOCK_M=256, BLOCK_N=256, BLOCK_K=64, num_stages=6):
     m, k = a.shape
     _, n = b.shape
     c = torch.empty(m, n, device=a.device, dtype=a.dtype) if c is None else c

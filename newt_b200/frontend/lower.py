@@ -752,12 +752,16 @@ class GemmPlan(Plan):
         CTA-pair kernel (one 256-row tcgen05 MMA over two SMs) whose ring slot holds BLOCK_K
         = one, two or three 128-byte rows of K (64, 128, 192 elements of fp16/bf16; 32, 64, 96
         of fp32); otherwise the tcgen05 tile is picked by BLOCK_N (when it is a tile the
-        kernel has); num_stages is the ring depth."""
+        kernel has) and num_stages is the ring depth -- except that BLOCK_K = two 128-byte rows
+        with 64 or 128 columns picks the ring whose slots hold two K slabs (half as many copies
+        to issue: what small problems are bound by)."""
         bm, bn, bk = self.block
+        rk = self.row_k
         if bm == 256 and bn == 256:
-            rk = self.row_k
             bk = bk if bk in (rk, 2 * rk, 3 * rk) else 2 * rk
             return ("gemm-pair", bk, self.num_stages if bk == rk else 0)
+        if bk == 2 * rk and bn in (64, 128):
+            return ("gemm-2slab", bn, 0)
         return ("gemm", bn if bn in (64, 128, 256) else 0, self.num_stages)
 
     def config(self):
@@ -768,6 +772,8 @@ class GemmPlan(Plan):
             if kind == "gemm-pair":
                 self._config = kernels.gemm_config(block_m=256, block_n=256, block_k=x,
                                                    stages=stages, cta_pair=1)
+            elif kind == "gemm-2slab":
+                self._config = kernels.gemm_config(block_n=x, block_k=2 * self.row_k)
             else:
                 self._config = kernels.gemm_config(block_n=x, stages=stages)
         return self._config
@@ -1024,7 +1030,8 @@ class GemmEpiloguePlan(Plan):
                 body = (f"nb200::gemm::gemm_pair_body<{launch.stages}, {launch.ksub}, {codes[dtype_code]}, "
                         f"{codes[c_code]}, NbEpilogue>(ta, tb, p, ea);")
             else:
-                body = (f"nb200::gemm::gemm_body<{launch.block_n}, {launch.stages}, {codes[dtype_code]}, "
+                body = (f"nb200::gemm::gemm_body<{launch.block_n}, {launch.stages}, {launch.ksub}, "
+                        f"{codes[dtype_code]}, "
                         f"{codes[c_code]}, NbEpilogue>(ta, tb, p, ea);")
             name = "nb_gemm_epilogue"
             source = (

@@ -273,6 +273,39 @@ def test_gemm_cta_pair_vs_oracle(dtype, block_k, stages, m, n, k):
     assert torch_ref.rel_frobenius(c.cpu().float(), torch_ref.matmul(a.cpu(), b.cpu())) <= 1e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("block_n", [64, 128])
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (128, 128, 128), (130, 72, 200), (300, 192, 320),
+                                   (700, 1000, 328), (1024, 1024, 1024)])
+def test_gemm_two_slab_slots_vs_oracle(dtype, block_n, transposed, m, n, k):
+    """Ring slots of two K slabs (one copy per operand and slot where the shapes allow the wide
+    tensor maps, slab by slab at ragged K or N), B as [K, N] and as [N, K]."""
+    if dtype == torch.float32 and not transposed:
+        pytest.skip("tf32 reads B K-major only")
+    g = torch.Generator().manual_seed(m * 11 + n * 3 + k + block_n)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype)
+    b = torch.randn(k, n, generator=g).to(dtype)
+    kp = (k + 7) // 8 * 8
+    ad = torch.zeros(m, kp, dtype=dtype, device="cuda")[:, :k].copy_(a)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    row_k = 32 if dtype == torch.float32 else 64
+    cfg = kernels.gemm_config(block_n=block_n, block_k=2 * row_k)
+    if transposed:
+        bd = torch.zeros(n, kp, dtype=dtype, device="cuda")[:, :k].copy_(b.t())
+        kernels.gemm_bt(ad, bd, c, m, n, k, kp, kp, n, cfg)
+    else:
+        np_ = (n + 7) // 8 * 8
+        bd = torch.zeros(k, np_, dtype=dtype, device="cuda")[:, :n].copy_(b)
+        kernels.gemm(ad, bd, c, m, n, k, kp, np_, n, cfg)
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    tol = 2e-3 if dtype == torch.float32 else 1e-2
+    got = c.cpu().double()
+    assert not torch.isnan(got).any()
+    assert torch_ref.rel_frobenius(got, a.double() @ b.double()) <= tol
+
+
 def test_gemm_linearity_at_full_size():
     # size-independent property at the benchmark size: (A1 + A2) @ B == A1 @ B + A2 @ B
     # up to rounding, and a spot-checked block against the fp32 oracle
