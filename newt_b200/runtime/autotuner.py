@@ -65,6 +65,9 @@ class Autotuner:
         self.timings = {}
         self.param_names = jitfn.param_names
         self.__name__ = getattr(jitfn, "__name__", "kernel")
+        # where the key's parameters sit in a positional call
+        self._key_at = [self.param_names.index(k) if k in self.param_names else -1
+                        for k in self.key]
 
     def __getitem__(self, grid):
         return lambda *args, **kwargs: self._run(grid, args, kwargs)
@@ -75,8 +78,25 @@ class Autotuner:
         vals = []
         for k in self.key:
             v = bound.get(k)
-            vals.append(tuple(v.shape) if hasattr(v, "shape") else v)
-        vals.extend(str(v.dtype) for v in bound.values() if isinstance(v, torch.Tensor))
+            vals.append(v if type(v) in (int, float, bool) or not hasattr(v, "shape")
+                        else tuple(v.shape))
+        vals.extend(v.dtype for v in bound.values() if isinstance(v, torch.Tensor))
+        return tuple(vals)
+
+    def _positional_key(self, args):
+        """`_cache_key` of a call that gives the key's parameters and every tensor by position
+        (the usual call), without building the name -> value map; None otherwise."""
+        import torch
+
+        n = len(args)
+        vals = []
+        for at in self._key_at:
+            if not 0 <= at < n:
+                return None
+            v = args[at]
+            vals.append(v if type(v) in (int, float, bool) or not hasattr(v, "shape")
+                        else tuple(v.shape))
+        vals.extend(v.dtype for v in args if isinstance(v, torch.Tensor))
         return tuple(vals)
 
     def _tune(self, grid, args, kwargs, bound):
@@ -113,16 +133,32 @@ class Autotuner:
         return results[0][1]
 
     def _run(self, grid, args, kwargs):
-        bound = _bound_args(self.jitfn, args, kwargs)
-        key = self._cache_key(bound)
+        import torch
+
+        key = None
+        if not any(isinstance(v, torch.Tensor) for v in kwargs.values()):
+            key = self._positional_key(args)
+        bound = None
+        if key is None:
+            bound = _bound_args(self.jitfn, args, kwargs)
+            key = self._cache_key(bound)
         best = self.cache.get(key)
         if best is None:
+            bound = bound or _bound_args(self.jitfn, args, kwargs)
             best = self._tune(grid, args, kwargs, bound)
             self.cache[key] = best
             for name in self.reset_to_zero:  # tuning dirtied the accumulation buffers
                 bound[name].zero_()
         self.best_config = best
-        self.jitfn[grid](*args, **{**kwargs, **best.all_kwargs()})
+        chosen = best.__dict__.get("_launch_kwargs")
+        if chosen is None:
+            chosen = best.__dict__["_launch_kwargs"] = best.all_kwargs()
+        merged = {**kwargs, **chosen} if kwargs else chosen
+        direct = getattr(self.jitfn, "_run", None)     # a JITFunction: skip building the partial
+        if direct is not None and not isinstance(self.jitfn, (Autotuner, Heuristics)):
+            direct(grid, *args, **merged)
+        else:
+            self.jitfn[grid](*args, **merged)
 
 
 def autotune(configs, key, reset_to_zero=None):

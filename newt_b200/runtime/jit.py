@@ -223,6 +223,8 @@ class JITFunction:
     def _run(self, grid, *args, **kwargs):
         import torch
 
+        from . import kernels
+
         num_warps = kwargs.pop("num_warps", 4)
         num_stages = kwargs.pop("num_stages", 3)
         bound = self._bind(args, kwargs)
@@ -237,12 +239,12 @@ class JITFunction:
             compiled, tensors = hit
 
         if tensors:
-            current = torch.cuda.current_device()
+            current = kernels.current_device()
             for name in tensors:
                 v = bound[name]
-                if not v.is_cuda:
-                    raise TypeError(f"argument '{name}' must be a CUDA tensor")
-                if v.device.index not in (None, current):
+                if v.get_device() != current:      # -1 for a CPU tensor
+                    if not v.is_cuda:
+                        raise TypeError(f"argument '{name}' must be a CUDA tensor")
                     raise ValueError(
                         f"tensor '{name}' is on {v.device} but the current device is "
                         f"cuda:{current}; newt launches on the current device")
@@ -253,25 +255,21 @@ class JITFunction:
             g = grid(meta)
         else:
             g = grid
-        if isinstance(g, int):
-            g = (g,)
-        g = tuple(int(x) for x in g)
+        if type(g) is not tuple or not all(type(x) is int for x in g):
+            g = (int(g),) if isinstance(g, int) else tuple(int(x) for x in g)
         if len(g) > 3:
             raise ValueError(f"grids have at most 3 dimensions, got {g}")
-        if any(x <= 0 for x in g):
+        if min(g, default=1) <= 0:
             return
         if tensors:
-            global _checked_tensors
-            if _checked_tensors is None:
-                from . import kernels
-                _checked_tensors = kernels.checked_tensors()
-            with _checked_tensors:
+            trust = kernels._trust
+            trust.checked = True      # `_dev_ptr` takes this launch's tensors as verified
+            try:
                 compiled.plan.launch(g, bound)
+            finally:
+                trust.checked = False
         else:
             compiled.plan.launch(g, bound)
-
-
-_checked_tensors = None
 
 
 def jit(fn=None):

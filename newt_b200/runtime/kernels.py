@@ -20,6 +20,17 @@ _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 _trust = threading.local()     # .checked: the JIT launcher has verified the tensors of this launch
 
 
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+def current_device():
+    """Index of the current CUDA device (the raw getter once CUDA is up: a launch asks this for
+    every call)."""
+    if _raw_device is not None and torch.cuda.is_initialized():
+        return _raw_device()
+    return torch.cuda.current_device()
+
+
 def raw_stream():
     """The current stream of the current device as an integer handle."""
     if _raw_stream is not None:
