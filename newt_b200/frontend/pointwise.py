@@ -103,6 +103,9 @@ class _Context:
     """What all statement lists of one kernel share."""
 
     def __init__(self, trace, threads):
+        self.trace = trace
+        self._analyzer = None
+        self._unit = {}        # pointer node uid -> does it advance by one element along its last axis
         self.loops = {loop.uid: loop for loop in trace.loops}
         self.live = _live_names(trace)
         self.threads = threads
@@ -121,6 +124,23 @@ class _Context:
     def fresh(self, prefix="v"):
         self.counter += 1
         return f"{prefix}{self.counter}"
+
+    def unit_stride(self, ptr):
+        """True when the pointer block is affine in the block's indices and neighbours along its
+        last axis are neighbours in memory (the proof vector accesses need)."""
+        hit = self._unit.get(ptr.uid)
+        if hit is None:
+            from .affine import Analyzer, NotAffine, Poly
+            if self._analyzer is None:
+                self._analyzer = Analyzer(self.trace)
+            hit = False
+            try:
+                split = self._analyzer.poly(ptr).coeff_of(("ax", len(ptr.shape) - 1))
+                hit = bool(ptr.shape) and split is not None and split[0] == Poly.const(1)
+            except NotAffine:
+                pass
+            self._unit[ptr.uid] = hit
+        return hit
 
     def alloc(self, dt, count, prefix):
         """A shared-memory array of `count` elements; returns its name."""
@@ -163,6 +183,8 @@ class _Body:
         # loop variable
         self.loop_state = dict(loop_state or {})
         self.loop_final = {}    # (loop uid, name) -> offset form left by a loop emitted in this body
+        self.lanes = 0          # > 0: each trip computes this many neighbours along the last axis,
+                                # whose index is written `(nb_v + k)` for lane k
 
     def var(self, dt, expr):
         name = self.ctx.fresh()
@@ -257,6 +279,10 @@ def _emit_new(body, node, dims):
         return body.var(dt, f"{sub(ptr)} {sign} (long long)({sub(off)})")
     if op == "load":
         ptr, mask, other = node.args
+        if body.lanes:
+            packed = _emit_lanes_load(body, node, dims)
+            if packed is not None:
+                return packed
         p = sub(ptr)
         if mask is None:
             return body.var(dt, f"*{p}")
@@ -356,6 +382,83 @@ def _emit_new(body, node, dims):
         name, shape = slot
         return f"{name}[{_linear(dims, shape)}]"
     raise Unsupported(f"'{op}' has no elementwise lowering")
+
+
+
+# ---- sixteen bytes at a time ---------------------------------------------------------------
+#
+# 16-bit tensors: a thread that loads and stores one element per access moves two bytes per
+# instruction and the memory pipeline, not HBM, sets the pace (4.6 TB/s for relu(2x + y) where
+# fp32 reaches the copy rate).  When the stored block's last axis is a multiple of eight and its
+# pointer advances by one element along it, an element loop trip computes eight neighbours
+# ("lanes"): index `(nb_v + k)` for lane k.  A load whose pointer is proven unit-stride along
+# the same axis fetches its eight lanes with one 16-byte access when, at run time, the address
+# is 16-byte aligned and all eight masks hold, and lane by lane otherwise; the store does the
+# same.  Everything else about an element (arithmetic, rounding after every operation,
+# broadcasts, reductions read from shared memory) is evaluated per lane exactly as before.
+
+_LANE_BASE = "nb_v"
+
+
+def _lane_dims(dims, k):
+    return dims[:-1] + (f"({_LANE_BASE} + {k})",)
+
+
+def _lane_of(dims, lanes):
+    """Which lane the indices `dims` describe, when only the last one moves with the lane."""
+    if not dims or any(_LANE_BASE in d for d in dims[:-1]):
+        return None
+    for k in range(lanes):
+        if dims[-1] == f"({_LANE_BASE} + {k})":
+            return k
+    return None
+
+
+def _aligned16(p):
+    return f"((unsigned long long)({p}) & 15ull) == 0"
+
+
+def _emit_lanes_load(body, node, dims):
+    """All lanes of a unit-stride load at once; None when this load is not of that kind."""
+    lanes = body.lanes
+    dt = node.dtype
+    ptr, mask, other = node.args
+    if isinstance(dt, tp.pointer_type) or dt.itemsize * lanes != 16 or ptr.shape != node.shape:
+        return None
+    lane = _lane_of(dims, lanes)
+    if lane is None or not body.ctx.unit_stride(ptr):
+        return None
+
+    def at(x, k):
+        return _emit(body, x, _operand_dims(node.shape, _lane_dims(dims, k), x.shape))
+
+    p0 = at(ptr, 0)
+    masks = [at(mask, k) for k in range(lanes)] if mask is not None else None
+    if mask is None:
+        fills = None
+    elif isinstance(other, Node):
+        fills = [_convert(at(other, k), other.dtype, dt) for k in range(lanes)]
+    else:
+        fills = [_literal(other if other is not None else 0, dt)] * lanes
+    conds = [_aligned16(p0)] + (list(dict.fromkeys(masks)) if masks else [])
+    whole = body.var(tp.int1, " && ".join(conds))
+    arr = body.ctx.fresh("q")
+    ct = dt.ctype
+    body.lines.append(f"{ct} {arr}[{lanes}];")
+    body.lines.append(f"if ({whole}) {{")
+    body.lines.append(f"  const uint4 t = *reinterpret_cast<const uint4*>({p0});")
+    body.lines.append(f"  const {ct}* s = reinterpret_cast<const {ct}*>(&t);")
+    body.lines += [f"  {arr}[{k}] = s[{k}];" for k in range(lanes)]
+    body.lines.append("} else {")
+    for k in range(lanes):
+        if masks is None:
+            body.lines.append(f"  {arr}[{k}] = {p0}[{k}];")
+        else:
+            body.lines.append(f"  {arr}[{k}] = {masks[k]} ? {p0}[{k}] : {fills[k]};")
+    body.lines.append("}")
+    for k in range(lanes):
+        body.memo[(node.uid, _lane_dims(dims, k))] = f"{arr}[{k}]"
+    return f"{arr}[{lane}]"
 
 
 # ---- the expression graph, seen through loops -------------------------------------------
@@ -868,6 +971,58 @@ class _Scheduler:
         lines.append("__syncthreads();")
         return lines
 
+    def lanes_for(self, eff, state):
+        """How many neighbours a trip of this store's element loop computes: 8 for a plain store
+        of a 16-bit block whose last axis is a multiple of 8 and unit-stride in memory, with
+        nothing but elementwise arithmetic, broadcasts and materialised reductions between the
+        loads and the store; else 0 (one element per trip)."""
+        _, ptr, value, mask, _lineno = eff[:5]
+        if eff[0] != "store" or state:
+            return 0
+        elem, shape = ptr.dtype.element, ptr.shape
+        if elem.itemsize != 2 or not shape or shape[-1] % 8 or not self.ctx.unit_stride(ptr):
+            return 0
+        simple = _ELEMENTWISE + ("param", "const", "full", "pid", "nprog", "arange", "splat",
+                                 "broadcast", "expand", "load", "reduce")
+        seen, todo = set(), [r for r in (value, mask) if isinstance(r, Node)]
+        while todo:
+            n = todo.pop()
+            if n.uid in seen:
+                continue
+            seen.add(n.uid)
+            if n.op not in simple:
+                return 0
+            if n.op != "reduce":          # a reduction is read from shared memory, not recomputed
+                todo += [a for a in n.args if isinstance(a, Node)]
+        return 8
+
+    def lane_loop(self, shape, state, lanes, finish):
+        """`element_loop` with `lanes` neighbours along the last axis per trip: `finish(body,
+        dims)` gets the indices of lane 0."""
+        threads = self.ctx.threads
+        numel = 1
+        for s in shape:
+            numel *= s
+        body = _Body(self.ctx, state)
+        body.lanes = lanes
+        dims = tuple(f"i{d}" for d in range(len(shape) - 1)) + (f"({_LANE_BASE} + 0)",)
+        finish(body, dims)
+        per_row = shape[-1] // lanes
+        lines = ["#pragma unroll 2",
+                 f"for (int e = threadIdx.x; e < {numel // lanes}; e += {threads}) {{",
+                 "  int r = e;",
+                 f"  const int {_LANE_BASE} = (r % {per_row}) * {lanes};",
+                 f"  r /= {per_row};"]
+        for d in range(len(shape) - 2, 0, -1):
+            lines.append(f"  const int i{d} = r % {shape[d]};")
+            lines.append(f"  r /= {shape[d]};")
+        if len(shape) >= 2:
+            lines.append("  const int i0 = r;")
+        lines += ["  " + ln for ln in body.lines]
+        lines.append("}")
+        lines.append("__syncthreads();")
+        return lines
+
     def fill(self, array, shape, value, state, dt):
         """array[e] = value(e) for a block kept in shared memory."""
         def finish(body, dims):
@@ -962,6 +1117,28 @@ class _Scheduler:
                 raise Unsupported(f"nl.atomic_max on {elem.name}")
             body.lines.append(f"if ({guard}) {stmt}" if guard else stmt)
 
+        lanes = self.lanes_for(eff, state)
+        if lanes:
+            def finish_lanes(body, dims):
+                each = [_lane_dims(dims, k) for k in range(lanes)]
+                vals = [_convert(_emit(body, value, _operand_dims(shape, d, value.shape)),
+                                 value.dtype, elem) for d in each]
+                p0 = _emit(body, ptr, each[0])
+                guards = [_emit(body, mask, _operand_dims(shape, d, mask.shape)) for d in each] \
+                    if mask is not None else None
+                conds = [_aligned16(p0)] + (list(dict.fromkeys(guards)) if guards else [])
+                ct = elem.ctype
+                body.lines.append(f"if ({' && '.join(conds)}) {{")
+                body.lines.append(f"  __align__(16) {ct} w[{lanes}];")
+                body.lines += [f"  w[{k}] = {vals[k]};" for k in range(lanes)]
+                body.lines.append(f"  *reinterpret_cast<uint4*>({p0}) = *reinterpret_cast<const uint4*>(w);")
+                body.lines.append("} else {")
+                for k in range(lanes):
+                    stmt = f"{p0}[{k}] = {vals[k]};"
+                    body.lines.append(f"  if ({guards[k]}) {stmt}" if guards else f"  {stmt}")
+                body.lines.append("}")
+
+            return self.need(_effect_roots(eff), state) + self.lane_loop(shape, state, lanes, finish_lanes)
         return self.need(_effect_roots(eff), state) + self.element_loop(shape, state, finish)
 
     # -- statements -----------------------------------------------------------------------

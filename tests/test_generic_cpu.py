@@ -104,3 +104,32 @@ def test_control_flow_errors():
 
     with pytest.raises(newt.CompileError, match="stored to"):
         stored_then_read.specialize(F32, 4, BLOCK=64)
+
+
+def test_sixteen_bit_elementwise_gets_the_sixteen_byte_path():
+    """fp16 / bf16 blocks whose last axis is unit-stride and a multiple of eight are walked
+    eight neighbours per trip with 16-byte accesses; fp32 keeps one element per trip; a block
+    indexed through a stride argument (unit stride not provable) keeps one element per trip."""
+    import newt_b200 as newt
+    from newt_b200 import language as nl, types as tp
+    from newt_b200.runtime import nvrtc
+
+    @newt.jit
+    def scale(x_ptr, o_ptr, n, BLOCK: nl.constexpr):
+        offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        nl.store(o_ptr + offs, nl.load(x_ptr + offs, mask=offs < n, other=0.0) * 3.0, mask=offs < n)
+
+    @newt.jit
+    def strided(x_ptr, o_ptr, n, stride, BLOCK: nl.constexpr):
+        offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+        nl.store(o_ptr + offs * stride, nl.load(x_ptr + offs * stride, mask=offs < n, other=0.0),
+                 mask=offs < n)
+
+    for elem, wide in ((tp.float16, True), (tp.bfloat16, True), (tp.float32, False)):
+        p = tp.pointer_type(elem)
+        plan = scale.specialize(p, p, 1 << 20, BLOCK=1024).plan
+        assert ("uint4" in plan.source) == wide
+        nvrtc.compile_cubin(plan.source, "scale.cu")
+    p = tp.pointer_type(tp.float16)
+    assert "uint4" not in strided.specialize(p, p, 1 << 20, 2, BLOCK=1024).plan.source
+    assert "uint4" not in scale.specialize(p, p, 1 << 20, BLOCK=4).plan.source     # 4 is not a multiple of 8

@@ -8,6 +8,8 @@ import pytest
 import torch
 
 import generic_programs as gp
+import newt_b200 as newt
+from newt_b200 import language as nl
 
 pytestmark = pytest.mark.gpu
 
@@ -179,3 +181,34 @@ def test_epilogue_is_compiled_into_the_tensor_core_kernel(m, n, k, dtype):
     assert not torch.isnan(got).any()
     tol = 2 ** -8 if dtype == torch.bfloat16 else 2 ** -10
     assert ((got - want).norm() / want.norm()).item() < tol
+
+
+@newt.jit
+def _relu_axpy(x_ptr, y_ptr, o_ptr, n, BLOCK: nl.constexpr):
+    offs = nl.program_id(0) * BLOCK + nl.arange(0, BLOCK)
+    m = offs < n
+    x = nl.load(x_ptr + offs, mask=m, other=0.0)
+    y = nl.load(y_ptr + offs, mask=m, other=0.0)
+    nl.store(o_ptr + offs, nl.maximum(x * 2.0 + y, 0.0), mask=m)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,offset", [(1 << 16, 0), ((1 << 16) - 3, 0), (5000, 1), (8, 0), (7, 0)])
+def test_sixteen_bit_blocks_move_sixteen_bytes_at_a_time(dtype, n, offset):
+    """A 16-bit elementwise program: eight neighbours per trip through one 16-byte access where
+    the address is aligned and all eight masks hold, lane by lane at the ragged tail and from a
+    base off by one element; bit-exact against the same operations in torch either way, and
+    nothing written outside [0, n)."""
+    g = torch.Generator().manual_seed(n + offset)
+    x = torch.randn(n + 16, generator=g).to(dtype).cuda()
+    y = torch.randn(n + 16, generator=g).to(dtype).cuda()
+    o = torch.full((n + 16,), 7.0, device="cuda", dtype=dtype)
+    xs, ys, os_ = x[offset:offset + n], y[offset:offset + n], o[offset:offset + n]
+    block = 1024
+    _relu_axpy[(newt.cdiv(n, block),)](xs, ys, os_, n, BLOCK=block)
+    torch.cuda.synchronize()
+    plan = _relu_axpy.specialize(xs, ys, os_, n, BLOCK=block).plan
+    assert "uint4" in plan.source          # the program was given the 16-byte path
+    want = torch.relu((xs * 2.0).to(dtype) + ys)
+    assert torch.equal(os_, want)
+    assert (o[:offset] == 7.0).all() and (o[offset + n:] == 7.0).all()
