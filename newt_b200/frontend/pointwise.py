@@ -418,6 +418,31 @@ def _aligned16(p):
     return f"((unsigned long long)({p}) & 15ull) == 0"
 
 
+_LANE_SIMPLE = None
+
+
+def _simple_for_lanes(roots):
+    """(True when nothing but elementwise arithmetic, broadcasts, loads and materialised
+    reductions lies below `roots`, the 16-bit loads found)."""
+    global _LANE_SIMPLE
+    if _LANE_SIMPLE is None:
+        _LANE_SIMPLE = _ELEMENTWISE + ("param", "const", "full", "pid", "nprog", "arange", "splat",
+                                       "broadcast", "expand", "load", "reduce")
+    seen, todo, narrow = set(), [r for r in roots if isinstance(r, Node)], []
+    while todo:
+        n = todo.pop()
+        if n.uid in seen:
+            continue
+        seen.add(n.uid)
+        if n.op not in _LANE_SIMPLE:
+            return False, narrow
+        if n.op == "load" and not isinstance(n.dtype, tp.pointer_type) and n.dtype.itemsize == 2:
+            narrow.append(n)
+        if n.op != "reduce":          # a reduction is read from shared memory, not recomputed
+            todo += [a for a in n.args if isinstance(a, Node)]
+    return True, narrow
+
+
 def _emit_lanes_load(body, node, dims):
     """All lanes of a unit-stride load at once; None when this load is not of that kind."""
     lanes = body.lanes
@@ -846,6 +871,43 @@ def _materialise_reduce(node, name, threads, ctx, state=None):
     for s in out_shape:
         outs *= s
     body = _Body(ctx, state)
+    # Folding along the last axis of a block read from 16-bit tensors: eight neighbours per trip
+    # (see "sixteen bytes at a time"), when the whole block shares out the terms.
+    lanes = 0
+    if not state and outs < threads and length >= 2 * threads and length % 8 == 0 and \
+            (axis == len(shape) - 1 or (axis is None and len(shape) == 1)):
+        simple, narrow = _simple_for_lanes((x,))
+        if simple and any(ld.shape and ld.shape[-1] == length and ctx.unit_stride(ld.args[0])
+                          for ld in narrow):
+            lanes = 8
+    if lanes:
+        body.lanes = lanes
+        js = [f"j{d}" for d in range(len(out_shape))]
+        first = tuple(js[:len(shape) - 1]) + (f"({_LANE_BASE} + 0)",)
+        vals = [_convert(_emit(body, x, _lane_dims(first, k)), x.dtype, dt) for k in range(lanes)]
+        op = _REDUCE_OPS[fn]
+        init = _reduce_init(fn, dt)
+        lines = []
+        decompose = []
+        rem = "o"
+        for d in range(len(out_shape) - 1, 0, -1):
+            decompose.append(f"const int j{d} = {rem} % {out_shape[d]};")
+            decompose.append(f"const int p{d} = {rem} / {out_shape[d]};")
+            rem = f"p{d}"
+        if out_shape:
+            decompose.append(f"const int j0 = {rem};")
+        lines.append(f"for (int o = 0; o < {outs}; ++o) {{")
+        lines += ["  " + ln for ln in decompose]
+        lines.append(f"  {dt.ctype} acc = {init};")
+        lines.append(f"  for (int k = threadIdx.x; k < {length // lanes}; k += {threads}) {{")
+        lines.append(f"    const int {_LANE_BASE} = k * {lanes};")
+        lines += ["    " + ln for ln in body.lines]
+        lines += [f"    acc = nb_fold<{op}, {dt.ctype}>(acc, {v});" for v in vals]
+        lines.append("  }")
+        lines.append(f"  acc = nb_block_reduce<{op}, {dt.ctype}>(acc, reinterpret_cast<{dt.ctype}*>(nb_scratch));")
+        lines.append(f"  if (threadIdx.x == 0) {name}[o] = acc;")
+        lines.append("}")
+        return lines
     # index of x for output element (j0, j1, ...) and position k along the reduced extent
     if axis is None:
         xdims, pre, rem = [], [], "k"
@@ -982,19 +1044,7 @@ class _Scheduler:
         elem, shape = ptr.dtype.element, ptr.shape
         if elem.itemsize != 2 or not shape or shape[-1] % 8 or not self.ctx.unit_stride(ptr):
             return 0
-        simple = _ELEMENTWISE + ("param", "const", "full", "pid", "nprog", "arange", "splat",
-                                 "broadcast", "expand", "load", "reduce")
-        seen, todo = set(), [r for r in (value, mask) if isinstance(r, Node)]
-        while todo:
-            n = todo.pop()
-            if n.uid in seen:
-                continue
-            seen.add(n.uid)
-            if n.op not in simple:
-                return 0
-            if n.op != "reduce":          # a reduction is read from shared memory, not recomputed
-                todo += [a for a in n.args if isinstance(a, Node)]
-        return 8
+        return 8 if _simple_for_lanes((value, mask))[0] else 0
 
     def lane_loop(self, shape, state, lanes, finish):
         """`element_loop` with `lanes` neighbours along the last axis per trip: `finish(body,
