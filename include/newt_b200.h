@@ -148,7 +148,9 @@ int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n,
                     const nb200_gemm_config* config, void* workspace,
                     int64_t workspace_bytes, void* stream);
 
-/* nb200_gemm_tf32 for callers that cannot bring a workspace.  (No counterpart in the
+/* nb200_gemm_tf32 -- the product `nl.dot` of fp32 blocks stands for (newt/language.py:165-167:
+ * tf32 operands, fp32 accumulation; generated at newt/compiler/codegen.py:2474-2487) -- for
+ * callers that cannot bring a workspace.  (The entry point itself has no counterpart in the
  * reference, whose generated kernels never need scratch memory.)  A drop-in behind the
  * reference's launcher is such a caller: `JITFunction._run` hands a kernel nothing but the
  * user's own tensors and scalars (newt/runtime/jit.py:166-223) and the package allocates no

@@ -31,6 +31,7 @@ tracer; integer `/` is C division; math functions are the precise single-precisi
 import ctypes
 import hashlib
 import math
+import re
 
 from .. import types as tp
 from .trace import Node
@@ -124,6 +125,35 @@ class _Context:
     def fresh(self, prefix="v"):
         self.counter += 1
         return f"{prefix}{self.counter}"
+
+    def either(self, wide, narrow):
+        """The eight-lane form of a statement list when every 16-bit tensor of the launch starts
+        on a 16-byte boundary (one test per kernel: `nb_wide`), else the one-element form -- from
+        a base that is off, every 16-byte access would fall back lane by lane, which is slower
+        than never having formed the lanes."""
+        self.wide_used = True
+        out = ["if (nb_wide) {"]
+        for lines in (wide, narrow):
+            lines = list(lines)
+            if lines and lines[-1] == "__syncthreads();":
+                lines.pop()
+            out += ["  " + ln for ln in lines]
+            out.append("} else {")
+        out[-1] = "}"
+        out.append("__syncthreads();")
+        return out
+
+    def wide_declaration(self):
+        if not self.wide_used:
+            return []
+        names = [name for name, node in self.trace.params.items()
+                 if isinstance(node.dtype, tp.pointer_type)
+                 and (self.wide_all or node.dtype.element.itemsize == 2)]
+        test = " | ".join(f"(unsigned long long){n}" for n in names)
+        return [f"const bool nb_wide = (({test}) & 15ull) == 0;"]
+
+    wide_used = False
+    wide_all = False       # the test covers every tensor, not only the 16-bit ones
 
     def unit_stride(self, ptr):
         """True when the pointer block is affine in the block's indices and neighbours along its
@@ -400,18 +430,21 @@ def _emit_new(body, node, dims):
 _LANE_BASE = "nb_v"
 
 
+_LANE_TOKEN = re.compile(r"^\((nb_v\d*) \+ (\d+)\)$")
+
+
 def _lane_dims(dims, k):
-    return dims[:-1] + (f"({_LANE_BASE} + {k})",)
+    """The indices of lane k of the group `dims` belongs to."""
+    base = _LANE_TOKEN.match(dims[-1]).group(1)
+    return dims[:-1] + (f"({base} + {k})",)
 
 
 def _lane_of(dims, lanes):
     """Which lane the indices `dims` describe, when only the last one moves with the lane."""
     if not dims or any(_LANE_BASE in d for d in dims[:-1]):
         return None
-    for k in range(lanes):
-        if dims[-1] == f"({_LANE_BASE} + {k})":
-            return k
-    return None
+    m = _LANE_TOKEN.match(dims[-1])
+    return int(m.group(2)) if m and int(m.group(2)) < lanes else None
 
 
 def _aligned16(p):
@@ -448,11 +481,13 @@ def _emit_lanes_load(body, node, dims):
     lanes = body.lanes
     dt = node.dtype
     ptr, mask, other = node.args
-    if isinstance(dt, tp.pointer_type) or dt.itemsize * lanes != 16 or ptr.shape != node.shape:
+    if isinstance(dt, tp.pointer_type) or (dt.itemsize * lanes) % 16 or ptr.shape != node.shape:
         return None
     lane = _lane_of(dims, lanes)
     if lane is None or not body.ctx.unit_stride(ptr):
         return None
+    pieces = dt.itemsize * lanes // 16      # 16-byte accesses per group of lanes
+    per = lanes // pieces
 
     def at(x, k):
         return _emit(body, x, _operand_dims(node.shape, _lane_dims(dims, k), x.shape))
@@ -471,9 +506,10 @@ def _emit_lanes_load(body, node, dims):
     ct = dt.ctype
     body.lines.append(f"{ct} {arr}[{lanes}];")
     body.lines.append(f"if ({whole}) {{")
-    body.lines.append(f"  const uint4 t = *reinterpret_cast<const uint4*>({p0});")
-    body.lines.append(f"  const {ct}* s = reinterpret_cast<const {ct}*>(&t);")
-    body.lines += [f"  {arr}[{k}] = s[{k}];" for k in range(lanes)]
+    for piece in range(pieces):
+        body.lines.append(f"  const uint4 t{piece} = reinterpret_cast<const uint4*>({p0})[{piece}];")
+        body.lines.append(f"  const {ct}* s{piece} = reinterpret_cast<const {ct}*>(&t{piece});")
+        body.lines += [f"  {arr}[{piece * per + k}] = s{piece}[{k}];" for k in range(per)]
     body.lines.append("} else {")
     for k in range(lanes):
         if masks is None:
@@ -484,6 +520,44 @@ def _emit_lanes_load(body, node, dims):
     for k in range(lanes):
         body.memo[(node.uid, _lane_dims(dims, k))] = f"{arr}[{k}]"
     return f"{arr}[{lane}]"
+
+
+def _emit_lanes_store(body, ptr, value, mask, dims, lanes):
+    """The store of one group of lanes (`dims`: its lane 0): 16-byte pieces when the address is
+    aligned and every lane's mask holds, lane by lane otherwise."""
+    elem, shape = ptr.dtype.element, ptr.shape
+    each = [_lane_dims(dims, k) for k in range(lanes)]
+    vals = [_convert(_emit(body, value, _operand_dims(shape, d, value.shape)), value.dtype, elem)
+            for d in each]
+    p0 = _emit(body, ptr, each[0])
+    guards = [_emit(body, mask, _operand_dims(shape, d, mask.shape)) for d in each] \
+        if mask is not None else None
+    ct = elem.ctype
+
+    def one_by_one(indent):
+        for k in range(lanes):
+            stmt = f"{p0}[{k}] = {vals[k]};"
+            body.lines.append(f"{indent}if ({guards[k]}) {stmt}" if guards else f"{indent}{stmt}")
+
+    if (elem.itemsize * lanes) % 16 or not body.ctx.unit_stride(ptr):
+        if not body.ctx.unit_stride(ptr):        # no neighbours in memory: every lane its own pointer
+            for k, d in enumerate(each):
+                pk = _emit(body, ptr, d)
+                stmt = f"*{pk} = {vals[k]};"
+                body.lines.append(f"if ({guards[k]}) {stmt}" if guards else stmt)
+        else:
+            one_by_one("")
+        return
+    pieces = elem.itemsize * lanes // 16
+    conds = [_aligned16(p0)] + (list(dict.fromkeys(guards)) if guards else [])
+    body.lines.append(f"if ({' && '.join(conds)}) {{")
+    body.lines.append(f"  __align__(16) {ct} w[{lanes}];")
+    body.lines += [f"  w[{k}] = {vals[k]};" for k in range(lanes)]
+    body.lines += [f"  reinterpret_cast<uint4*>({p0})[{piece}] = reinterpret_cast<const uint4*>(w)[{piece}];"
+                   for piece in range(pieces)]
+    body.lines.append("} else {")
+    one_by_one("  ")
+    body.lines.append("}")
 
 
 # ---- the expression graph, seen through loops -------------------------------------------
@@ -852,7 +926,7 @@ def _reduce_init(fn, dt):
     return f"(({dt.ctype})({lo + 1}{'LL' if bits == 64 else ''} - 1))" if fn == "max" else _literal(hi, dt)
 
 
-def _materialise_reduce(node, name, threads, ctx, state=None):
+def _materialise_reduce(node, name, threads, ctx, state=None, lanes_allowed=True):
     """Statements that leave the result of reduction `node` in the shared array `name`."""
     at = dict(node.attrs)
     fn, axis = at["fn"], at["axis"]
@@ -874,7 +948,7 @@ def _materialise_reduce(node, name, threads, ctx, state=None):
     # Folding along the last axis of a block read from 16-bit tensors: eight neighbours per trip
     # (see "sixteen bytes at a time"), when the whole block shares out the terms.
     lanes = 0
-    if not state and outs < threads and length >= 2 * threads and length % 8 == 0 and \
+    if lanes_allowed and not state and outs < threads and length >= 2 * threads and length % 8 == 0 and \
             (axis == len(shape) - 1 or (axis is None and len(shape) == 1)):
         simple, narrow = _simple_for_lanes((x,))
         if simple and any(ld.shape and ld.shape[-1] == length and ctx.unit_stride(ld.args[0])
@@ -907,7 +981,7 @@ def _materialise_reduce(node, name, threads, ctx, state=None):
         lines.append(f"  acc = nb_block_reduce<{op}, {dt.ctype}>(acc, reinterpret_cast<{dt.ctype}*>(nb_scratch));")
         lines.append(f"  if (threadIdx.x == 0) {name}[o] = acc;")
         lines.append("}")
-        return lines
+        return ctx.either(lines, _materialise_reduce(node, name, threads, ctx, state, lanes_allowed=False))[:-1]
     # index of x for output element (j0, j1, ...) and position k along the reduced extent
     if axis is None:
         xdims, pre, rem = [], [], "k"
@@ -1170,25 +1244,11 @@ class _Scheduler:
         lanes = self.lanes_for(eff, state)
         if lanes:
             def finish_lanes(body, dims):
-                each = [_lane_dims(dims, k) for k in range(lanes)]
-                vals = [_convert(_emit(body, value, _operand_dims(shape, d, value.shape)),
-                                 value.dtype, elem) for d in each]
-                p0 = _emit(body, ptr, each[0])
-                guards = [_emit(body, mask, _operand_dims(shape, d, mask.shape)) for d in each] \
-                    if mask is not None else None
-                conds = [_aligned16(p0)] + (list(dict.fromkeys(guards)) if guards else [])
-                ct = elem.ctype
-                body.lines.append(f"if ({' && '.join(conds)}) {{")
-                body.lines.append(f"  __align__(16) {ct} w[{lanes}];")
-                body.lines += [f"  w[{k}] = {vals[k]};" for k in range(lanes)]
-                body.lines.append(f"  *reinterpret_cast<uint4*>({p0}) = *reinterpret_cast<const uint4*>(w);")
-                body.lines.append("} else {")
-                for k in range(lanes):
-                    stmt = f"{p0}[{k}] = {vals[k]};"
-                    body.lines.append(f"  if ({guards[k]}) {stmt}" if guards else f"  {stmt}")
-                body.lines.append("}")
+                _emit_lanes_store(body, ptr, value, mask, dims, lanes)
 
-            return self.need(_effect_roots(eff), state) + self.lane_loop(shape, state, lanes, finish_lanes)
+            return self.need(_effect_roots(eff), state) + self.ctx.either(
+                self.lane_loop(shape, state, lanes, finish_lanes),
+                self.element_loop(shape, state, finish))
         return self.need(_effect_roots(eff), state) + self.element_loop(shape, state, finish)
 
     # -- statements -----------------------------------------------------------------------
@@ -1385,6 +1445,136 @@ def _check_order(ctx, effects, written):
             written.add(_base_param(eff[1], ctx.loops))
 
 
+
+# ---- a row per program, kept in registers ------------------------------------------------------
+#
+# Programs of the softmax / layernorm family -- one 1-D block per program instance, reductions
+# over the whole block, elementwise arithmetic around them, stores of the block -- need not go
+# through memory between their passes.  Every thread owns BLOCK / threads elements (groups of
+# lanes `(g * threads + threadIdx.x) * lanes + k`, so a warp touches consecutive 16-byte pieces);
+# the program is written out as straight-line code over one statement list, so a load or an
+# `exp` that the row maximum, the row sum and the stored value all use is evaluated once per
+# element and stays in a register; a reduction folds the thread's own values, then the block's
+# (`nb_block_reduce`), and is read back from shared memory by what follows.  This is what makes
+# a log-softmax, a softmax with a temperature, an RMSNorm or a layernorm without bias -- programs
+# the tuned row kernels do not recognise -- run at one pass over HBM instead of one per
+# reduction.
+
+_RESIDENT_MAX_PER_THREAD = 32
+
+
+def _resident_shape(ctx, trace):
+    """(block extent, lanes) when the program is of that family, else None."""
+    threads = ctx.threads
+    if not trace.effects or any(eff[0] != "store" for eff in trace.effects):
+        return None
+    extent, smallest, reduces = None, 8, 0
+    seen, todo = set(), []
+    for eff in trace.effects:
+        ptr = eff[1]
+        if len(ptr.shape) != 1:
+            return None
+        if extent not in (None, ptr.shape[0]):
+            return None
+        extent = ptr.shape[0]
+        smallest = min(smallest, ptr.dtype.element.itemsize)
+        todo += [r for r in _effect_roots(eff) if isinstance(r, Node)]
+    _simple_for_lanes(())            # fills the table of operations lanes can evaluate
+    simple = _LANE_SIMPLE
+    while todo:
+        n = todo.pop()
+        if n.uid in seen:
+            continue
+        seen.add(n.uid)
+        if n.op not in simple or n.shape not in ((), (1,), (extent,)):
+            return None
+        if n.op == "reduce":
+            reduces += 1
+            if n.shape != () or n.args[0].shape != (extent,) or dict(n.attrs)["fn"] not in _REDUCE_OPS:
+                return None
+        if n.op == "load" and n.shape == (extent,) and not isinstance(n.dtype, tp.pointer_type):
+            smallest = min(smallest, n.dtype.itemsize)
+        todo += [a for a in n.args if isinstance(a, Node)]
+    if not reduces or extent % threads or extent // threads > _RESIDENT_MAX_PER_THREAD:
+        return None
+    lanes = 16 // smallest
+    if extent % (threads * lanes):
+        lanes = 1
+    return extent, lanes
+
+
+def _resident_lines(ctx, trace, extent, lanes):
+    """The whole program as straight-line code, `lanes` neighbours per group."""
+    threads = ctx.threads
+    body = _Body(ctx, {})
+    body.lanes = lanes
+    groups = extent // (threads * lanes)
+    first = []
+    for g in range(groups):
+        body.lines.append(f"const int nb_v{g} = ({g * threads} + (int)threadIdx.x) * {lanes};")
+        first.append((f"(nb_v{g} + 0)",))
+    done = set()
+
+    def fold(node):
+        at = dict(node.attrs)
+        x, dt, op = node.args[0], node.dtype, _REDUCE_OPS[at["fn"]]
+        name = ctx.alloc(dt, 1, "nb_r")
+        ctx.helpers.add("reduce")
+        acc = ctx.fresh("a")
+        terms = [_convert(_emit(body, x, _lane_dims(d, k)), x.dtype, dt)
+                 for d in first for k in range(lanes)]
+        body.lines.append(f"{dt.ctype} {acc} = {_reduce_init(at['fn'], dt)};")
+        body.lines += [f"{acc} = nb_fold<{op}, {dt.ctype}>({acc}, {t});" for t in terms]
+        body.lines.append(f"{acc} = nb_block_reduce<{op}, {dt.ctype}>({acc}, "
+                          f"reinterpret_cast<{dt.ctype}*>(nb_scratch));")
+        body.lines.append(f"if (threadIdx.x == 0) {name}[0] = {acc};")
+        body.lines.append("__syncthreads();")
+        ctx.reduced[node.uid] = (name, ())
+
+    def reductions_below(roots):
+        found, seen, todo = {}, set(), [r for r in roots if isinstance(r, Node)]
+        while todo:
+            n = todo.pop()
+            if n.uid in seen:
+                continue
+            seen.add(n.uid)
+            if n.op == "reduce" and n.uid not in done:
+                found[n.uid] = n
+            todo += [a for a in n.args if isinstance(a, Node)]
+        return [found[u] for u in sorted(found)]       # program order: operands come first
+
+    for eff in trace.effects:
+        _, ptr, value, mask, _lineno = eff[:5]
+        for node in reductions_below(_effect_roots(eff)):
+            fold(node)
+            done.add(node.uid)
+        for d in first:
+            if lanes > 1:
+                _emit_lanes_store(body, ptr, value, mask, d, lanes)
+            else:
+                p = _emit(body, ptr, d)
+                val = _convert(_emit(body, value, _operand_dims(ptr.shape, d, value.shape)),
+                               value.dtype, ptr.dtype.element)
+                guard = _emit(body, mask, _operand_dims(ptr.shape, d, mask.shape)) \
+                    if mask is not None else None
+                body.lines.append(f"if ({guard}) *{p} = {val};" if guard else f"*{p} = {val};")
+    for uid in done:          # the other form of the program folds for itself
+        del ctx.reduced[uid]
+    return ["{"] + ["  " + ln for ln in body.lines] + ["}"]
+
+
+def _resident_program(ctx, trace):
+    shape = _resident_shape(ctx, trace)
+    if shape is None:
+        return None
+    extent, lanes = shape
+    if lanes == 1:
+        return _resident_lines(ctx, trace, extent, 1)
+    ctx.wide_all = True
+    return ctx.either(_resident_lines(ctx, trace, extent, lanes),
+                      _resident_lines(ctx, trace, extent, 1))
+
+
 def generate(trace, num_warps, computed_elsewhere=None):
     """Returns (cuda_source, kernel_name, [(param name, dtype or pointer_type)], bytes of
     dynamic shared memory).
@@ -1404,7 +1594,9 @@ def generate(trace, num_warps, computed_elsewhere=None):
                for eff in trace.effects):
         raise Unsupported("the program stores nothing")
     _check_order(ctx, trace.effects, set())
-    lines = _Scheduler(ctx).run(trace.effects, {})
+    lines = None if computed_elsewhere else _resident_program(ctx, trace)
+    if lines is None:
+        lines = _Scheduler(ctx).run(trace.effects, {})
     while lines and lines[-1] == "__syncthreads();":
         lines.pop()
 
@@ -1422,7 +1614,7 @@ def generate(trace, num_warps, computed_elsewhere=None):
     if "reduce" in ctx.helpers:
         helpers += _REDUCE_HELPERS
     shared, dynamic = ctx.shared_declarations()
-    body_text = "\n  ".join(shared + lines)
+    body_text = "\n  ".join(shared + ctx.wide_declaration() + lines)
     digest = hashlib.sha1((decl + body_text).encode()).hexdigest()[:8]
     kernel_name = f"{trace.name}_{digest}"
     source = (

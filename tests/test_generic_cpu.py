@@ -133,3 +133,31 @@ def test_sixteen_bit_elementwise_gets_the_sixteen_byte_path():
     p = tp.pointer_type(tp.float16)
     assert "uint4" not in strided.specialize(p, p, 1 << 20, 2, BLOCK=1024).plan.source
     assert "uint4" not in scale.specialize(p, p, 1 << 20, BLOCK=4).plan.source     # 4 is not a multiple of 8
+
+
+def test_a_row_program_outside_the_tuned_shapes_is_written_as_one_pass():
+    """log-softmax: the row is loaded once per element and `exp` evaluated once per element
+    (the sum and nothing else uses it), although two reductions and the store all read the row;
+    blocks that do not split evenly over the threads keep the loop form."""
+    import newt_b200 as newt
+    from newt_b200 import language as nl, types as tp
+    from newt_b200.runtime import nvrtc
+
+    @newt.jit
+    def log_softmax(x_ptr, out_ptr, N, stride, BLOCK_N: nl.constexpr):
+        row = nl.program_id(0)
+        cols = nl.arange(0, BLOCK_N)
+        mask = cols < N
+        x = nl.load(x_ptr + row * stride + cols, mask=mask, other=float("-inf"))
+        z = x - nl.max(x, axis=0)
+        nl.store(out_ptr + row * stride + cols, z - nl.log(nl.sum(nl.exp(z), axis=0)), mask=mask)
+
+    p = tp.pointer_type(tp.float32)
+    plan = log_softmax.specialize(p, p, 1000, 1024, BLOCK_N=1024).plan
+    wide, narrow = plan.source.split("\n  } else {\n")       # aligned tensors / a base that is off
+    assert wide.count("expf(") == 8 and narrow.count("expf(") == 8       # 1024 / 128 threads
+    assert wide.count("const uint4 t0 = ") == 2                           # two groups of four lanes
+    assert "for (int k" not in plan.source                                 # no pass over memory per reduction
+    assert nvrtc.compile_cubin(plan.source, "log_softmax.cu")[:4] == b"\x7fELF"
+    looped = log_softmax.specialize(p, p, 60, 64, BLOCK_N=64).plan         # 64 elements, 128 threads
+    assert "nb_v0" not in looped.source

@@ -212,3 +212,96 @@ def test_sixteen_bit_blocks_move_sixteen_bytes_at_a_time(dtype, n, offset):
     want = torch.relu((xs * 2.0).to(dtype) + ys)
     assert torch.equal(os_, want)
     assert (o[:offset] == 7.0).all() and (o[offset + n:] == 7.0).all()
+
+
+# ---- rows kept in registers: programs of the softmax / layernorm family the tuned kernels do
+# ---- not recognise (a temperature, a logarithm, no mean, no bias)
+
+@newt.jit
+def _log_softmax(x_ptr, out_ptr, N, stride, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=float("-inf"))
+    z = x - nl.max(x, axis=0)
+    nl.store(out_ptr + row * stride + cols, z - nl.log(nl.sum(nl.exp(z), axis=0)), mask=mask)
+
+
+@newt.jit
+def _softmax_with_temperature(x_ptr, out_ptr, N, stride, inv_t, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=float("-inf")) * inv_t
+    e = nl.exp(x - nl.max(x, axis=0))
+    nl.store(out_ptr + row * stride + cols, e / nl.sum(e, axis=0), mask=mask)
+
+
+@newt.jit
+def _rmsnorm(x_ptr, w_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=0.0).to(nl.float32)
+    ms = nl.sum(x * x, axis=0) / N
+    y = x * nl.rsqrt(ms + eps) * nl.load(w_ptr + cols, mask=mask, other=0.0)
+    nl.store(out_ptr + row * stride + cols, y, mask=mask)
+
+
+@newt.jit
+def _layernorm_without_bias(x_ptr, w_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=0.0).to(nl.float32)
+    mean = nl.sum(x, axis=0) / N
+    d = nl.where(mask, x - mean, 0.0)
+    var = nl.sum(d * d, axis=0) / N
+    y = d * nl.rsqrt(var + eps) * nl.load(w_ptr + cols, mask=mask, other=0.0)
+    nl.store(out_ptr + row * stride + cols, y, mask=mask)
+
+
+@pytest.mark.parametrize("n,block,offset", [(1024, 1024, 0), (1000, 1024, 0), (4096, 4096, 0),
+                                            (2040, 2048, 0), (1000, 1024, 1)])
+def test_rows_of_the_softmax_family_stay_in_registers(n, block, offset):
+    """fp32 rows: whole vectors, a ragged tail (masked lanes), and a base that is off by one
+    element (the one-element form of the same program)."""
+    from newt_b200.frontend.lower import PointwisePlan
+
+    rows = 37
+    g = torch.Generator().manual_seed(n + offset)
+    pitch = block + 8
+    x = (torch.randn(rows * pitch + 8, generator=g) * 3).cuda()
+    xs = x[offset:offset + rows * pitch].view(rows, pitch)
+    for kernel, extra, want in (
+            (_log_softmax, (), torch.log_softmax(xs[:, :n].double(), -1)),
+            (_softmax_with_temperature, (0.37,), torch.softmax(xs[:, :n].double() * 0.37, -1))):
+        o = torch.full((rows * pitch + 8,), 7.0, device="cuda")
+        os_ = o[offset:offset + rows * pitch].view(rows, pitch)
+        kernel[(rows,)](xs, os_, n, pitch, *extra, BLOCK_N=block)
+        torch.cuda.synchronize()
+        plan = kernel.specialize(xs, os_, n, pitch, *extra, BLOCK_N=block).plan
+        assert isinstance(plan, PointwisePlan) and "nb_v0" in plan.source
+        torch.testing.assert_close(os_[:, :n].double().cpu(), want.cpu(), rtol=2e-5, atol=2e-6)
+        assert (os_[:, n:] == 7.0).all() and (o[:offset] == 7.0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,block", [(1024, 1024), (1000, 1024), (4096, 4096)])
+def test_rows_of_the_layernorm_family_stay_in_registers(dtype, n, block):
+    rows = 29
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(rows, block, generator=g).to(dtype).cuda()
+    w = (1 + 0.1 * torch.randn(block, generator=g)).to(dtype).cuda()
+    xd, wd = x[:, :n].double(), w[:n].double()
+    tol = {torch.float16: 2e-3, torch.bfloat16: 1.6e-2, torch.float32: 1e-5}[dtype]
+    rms = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + 1e-6) * wd
+    d = xd - xd.mean(-1, keepdim=True)
+    ln = d * torch.rsqrt((d * d).mean(-1, keepdim=True) + 1e-5) * wd
+    for kernel, eps, want in ((_rmsnorm, 1e-6, rms), (_layernorm_without_bias, 1e-5, ln)):
+        o = torch.full((rows, block), 7.0, device="cuda", dtype=dtype)
+        kernel[(rows,)](x, w, o, n, block, eps, BLOCK_N=block)
+        torch.cuda.synchronize()
+        assert "nb_v0" in kernel.specialize(x, w, o, n, block, eps, BLOCK_N=block).plan.source
+        torch.testing.assert_close(o[:, :n].double().cpu(), want.cpu(), rtol=tol, atol=tol)
+        assert (o[:, n:] == 7.0).all()
