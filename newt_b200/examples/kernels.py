@@ -66,6 +66,62 @@ def softmax(x, out=None):
     return out
 
 
+# Rows of the same family that are not the tuned programs -- a temperature, a logarithm, no
+# mean -- go through the generic lowering, which keeps such a row in registers.
+@newt.jit
+def softmax_temperature_kernel(x_ptr, out_ptr, N, stride, inv_t, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=float("-inf")) * inv_t
+    e = nl.exp(x - nl.max(x, axis=0))
+    nl.store(out_ptr + row * stride + cols, e / nl.sum(e, axis=0), mask=mask)
+
+
+@newt.jit
+def log_softmax_kernel(x_ptr, out_ptr, N, stride, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=float("-inf"))
+    z = x - nl.max(x, axis=0)
+    nl.store(out_ptr + row * stride + cols, z - nl.log(nl.sum(nl.exp(z), axis=0)), mask=mask)
+
+
+@newt.jit
+def rmsnorm_kernel(x_ptr, w_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
+    row = nl.program_id(0)
+    cols = nl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = nl.load(x_ptr + row * stride + cols, mask=mask, other=0.0).to(nl.float32)
+    ms = nl.sum(x * x, axis=0) / N
+    y = x * nl.rsqrt(ms + eps) * nl.load(w_ptr + cols, mask=mask, other=0.0)
+    nl.store(out_ptr + row * stride + cols, y, mask=mask)
+
+
+def _row_launch(kernel, x, out, *extra):
+    m, n = x.shape
+    block = newt.next_power_of_2(n)
+    kernel[(m,)](*extra[:-1], n, x.stride(0), *extra[-1], BLOCK_N=block,
+                 num_warps=4 if block < 4096 else 8)
+    return out
+
+
+def softmax_temperature(x, temperature, out=None):
+    out = torch.empty_like(x) if out is None else out
+    return _row_launch(softmax_temperature_kernel, x, out, x, out, (1.0 / temperature,))
+
+
+def log_softmax(x, out=None):
+    out = torch.empty_like(x) if out is None else out
+    return _row_launch(log_softmax_kernel, x, out, x, out, ())
+
+
+def rmsnorm(x, w, eps=1e-6, out=None):
+    out = torch.empty_like(x) if out is None else out
+    return _row_launch(rmsnorm_kernel, x, out, x, w, out, (eps,))
+
+
 @newt.jit
 def layernorm_kernel(x_ptr, w_ptr, b_ptr, out_ptr, N, stride, eps, BLOCK_N: nl.constexpr):
     row = nl.program_id(0)

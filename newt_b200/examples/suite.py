@@ -2,7 +2,7 @@
 benchmarks/results.md of the reference): vector add, fused softmax, layernorm, fp16 matmul,
 fp32/tf32 matmul, plus causal attention, each next to the torch call on the same tensors.
 
-    python -m newt_b200.examples.suite [--quick] [--kernel add|fused|softmax|layernorm|matmul|matmul_tf32|matmul_epilogue|attention]
+    python -m newt_b200.examples.suite [--quick] [--kernel add|fused|softmax|layernorm|rows|matmul|matmul_tf32|matmul_epilogue|attention]
 
 Clock and metric definitions are the reference's: `do_bench` (median, L2 flushed between
 reps); GB/s = bytes read + written / t; TFLOP/s = 2*M*N*K / t.  Prints markdown tables.
@@ -51,6 +51,13 @@ def bench_fused(quick):
         a = _bench(lambda: K.gelu_residual(x, y, o))
         b = _bench(lambda: torch.add(torch.nn.functional.gelu(x, approximate="tanh"), y, out=o))
         out.append(_row("gelu+residual fp32", n, a, b, 3 * n * 4 / 1e6))
+    n = 1 << 26                # 16-bit blocks move sixteen bytes per access
+    for dt in (torch.float16, torch.bfloat16):
+        x, y = torch.randn(n, device="cuda").to(dt), torch.randn(n, device="cuda").to(dt)
+        o = torch.empty_like(x)
+        a = _bench(lambda: K.gelu_residual(x, y, o))
+        b = _bench(lambda: torch.add(torch.nn.functional.gelu(x, approximate="tanh"), y, out=o))
+        out.append(_row(f"gelu+residual {str(dt)[6:]}", n, a, b, 3 * n * 2 / 1e6))
     return out
 
 
@@ -76,6 +83,30 @@ def bench_layernorm(quick):
         a = _bench(lambda: K.layernorm(x, w, b_, 1e-5, o))
         b = _bench(lambda: torch.nn.functional.layer_norm(x, (n,), w, b_, 1e-5))
         out.append(_row(f"layernorm {str(dt)[6:]}", f"{m}x{n}", a, b, 2 * m * n * x.element_size() / 1e6))
+    return out
+
+
+def bench_rows(quick):
+    """Rows of the softmax / layernorm family that the tuned kernels do not recognise, through
+    the generic lowering (a row kept in registers), against torch's fused calls."""
+    out = ["| kernel | M x N | newt_b200 GB/s | torch GB/s | ratio |", "|---|---|---|---|---|"]
+    for n in ([4096] if quick else [1024, 4096, 8192]):
+        x = torch.randn(4096, n, device="cuda")
+        o = torch.empty_like(x)
+        gb = 2 * 4096 * n * 4 / 1e6
+        a = _bench(lambda: K.softmax_temperature(x, 2.0, o))
+        b = _bench(lambda: torch.softmax(x * 0.5, -1, out=o))
+        out.append(_row("softmax(x / T) fp32", f"4096x{n}", a, b, gb))
+        a = _bench(lambda: K.log_softmax(x, o))
+        b = _bench(lambda: torch.log_softmax(x, -1, out=o))
+        out.append(_row("log_softmax fp32", f"4096x{n}", a, b, gb))
+    for dt in (torch.float16, torch.bfloat16):
+        x = torch.randn(8192, 4096, device="cuda").to(dt)
+        w = torch.randn(4096, device="cuda").to(dt)
+        o = torch.empty_like(x)
+        a = _bench(lambda: K.rmsnorm(x, w, 1e-6, o))
+        b = _bench(lambda: torch.nn.functional.rms_norm(x, (4096,), w, 1e-6))
+        out.append(_row(f"rmsnorm {str(dt)[6:]}", "8192x4096", a, b, 2 * x.numel() * 2 / 1e6))
     return out
 
 
@@ -146,7 +177,7 @@ def bench_attention(quick):
 
 
 SUITES = {"add": bench_add, "fused": bench_fused, "softmax": bench_softmax, "layernorm": bench_layernorm,
-          "matmul": bench_matmul, "matmul_tf32": bench_matmul_tf32,
+          "rows": bench_rows, "matmul": bench_matmul, "matmul_tf32": bench_matmul_tf32,
           "matmul_epilogue": bench_matmul_epilogue, "attention": bench_attention}
 
 

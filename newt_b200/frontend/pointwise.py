@@ -428,6 +428,7 @@ def _emit_new(body, node, dims):
 # broadcasts, reductions read from shared memory) is evaluated per lane exactly as before.
 
 _LANE_BASE = "nb_v"
+LANES_ENABLED = True        # off: every generated loop handles one element per trip (for comparisons)
 
 
 _LANE_TOKEN = re.compile(r"^\((nb_v\d*) \+ (\d+)\)$")
@@ -948,7 +949,7 @@ def _materialise_reduce(node, name, threads, ctx, state=None, lanes_allowed=True
     # Folding along the last axis of a block read from 16-bit tensors: eight neighbours per trip
     # (see "sixteen bytes at a time"), when the whole block shares out the terms.
     lanes = 0
-    if lanes_allowed and not state and outs < threads and length >= 2 * threads and length % 8 == 0 and \
+    if lanes_allowed and LANES_ENABLED and not state and outs < threads and length >= 2 * threads and length % 8 == 0 and \
             (axis == len(shape) - 1 or (axis is None and len(shape) == 1)):
         simple, narrow = _simple_for_lanes((x,))
         if simple and any(ld.shape and ld.shape[-1] == length and ctx.unit_stride(ld.args[0])
@@ -1113,7 +1114,7 @@ class _Scheduler:
         nothing but elementwise arithmetic, broadcasts and materialised reductions between the
         loads and the store; else 0 (one element per trip)."""
         _, ptr, value, mask, _lineno = eff[:5]
-        if eff[0] != "store" or state:
+        if eff[0] != "store" or state or not LANES_ENABLED:
             return 0
         elem, shape = ptr.dtype.element, ptr.shape
         if elem.itemsize != 2 or not shape or shape[-1] % 8 or not self.ctx.unit_stride(ptr):
@@ -1466,7 +1467,7 @@ _RESIDENT_MAX_PER_THREAD = 32
 def _resident_shape(ctx, trace):
     """(block extent, lanes) when the program is of that family, else None."""
     threads = ctx.threads
-    if not trace.effects or any(eff[0] != "store" for eff in trace.effects):
+    if not LANES_ENABLED or not trace.effects or any(eff[0] != "store" for eff in trace.effects):
         return None
     extent, smallest, reduces = None, 8, 0
     seen, todo = set(), []
