@@ -107,9 +107,10 @@ int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
  * with row stride ldc; innermost strides are 1.  fp16 or bf16 inputs, fp32
  * accumulation in tensor memory, one rounding to `dtype` at the store.
  * fp32 inputs run as tf32 with an fp32 result, as `nl.dot` does for fp32 blocks
- * (newt/language.py:165-167, newt/compiler/codegen.py:2195-2197); the tensor core
- * reads tf32 operands K-major only, so they go through nb200_gemm_bt or
- * nb200_gemm_tf32 below and nb200_gemm itself rejects NB200_F32.
+ * (newt/language.py:165-167, newt/compiler/codegen.py:2195-2197): like the 16-bit
+ * types, nb200_gemm reads an fp32 B in place (an MN-major operand; its base and row
+ * pitch must be 16-byte aligned, as for every operand).  nb200_gemm_tf32 below also
+ * takes a B that is not.
  *
  * The config mirrors the launch knobs of the operator API: the tile comes
  * from the kernel's BLOCK_M/BLOCK_N/BLOCK_K constexprs, `stages` from
@@ -138,10 +139,13 @@ int nb200_gemm_bt(const void* a, const void* bt, void* c, int64_t m, int64_t n,
                   const nb200_gemm_config* config, void* stream);
 
 /* fp32 C = A @ B with B as [K,N] (the layout of tests/test_matmul.py:67-70 and of
- * bench_matmul_tf32, benchmarks/bench.py:291-294): B is first transposed into `workspace`, a
- * caller-owned device buffer of at least nb200_gemm_tf32_workspace_bytes(n, k) bytes, 16-byte
- * aligned, which the call may overwrite completely; then the product runs as nb200_gemm_bt.
- * The transposing pass moves 8 bytes per element of B. */
+ * bench_matmul_tf32, benchmarks/bench.py:291-294) whatever B's base and pitch: a B that bulk
+ * tensor copies can fetch (16-byte aligned base and row pitch) is read in place, exactly as
+ * nb200_gemm does; any other is first transposed into `workspace`, a caller-owned device
+ * buffer of at least nb200_gemm_tf32_workspace_bytes(n, k) bytes, 16-byte aligned, which the
+ * call may overwrite completely, and the product then runs as nb200_gemm_bt (the transposing
+ * pass moves 8 bytes per element of B).  Knob `tf32_in_place` = 0 forces the transposing
+ * pass. */
 int64_t nb200_gemm_tf32_workspace_bytes(int64_t n, int64_t k);
 int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n,
                     int64_t k, int64_t lda, int64_t ldb, int64_t ldc,

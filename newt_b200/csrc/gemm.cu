@@ -13,9 +13,10 @@
 //     instruction) reading both operands through shared-memory descriptors;
 //     A is [M,K] row-major  -> K-major operand,
 //     B is [K,N] row-major  -> MN-major operand (no transpose pass needed), or is handed
-//     over transposed, [N,K] -> K-major operand.  tf32 operands are read K-major only (an
-//     MN-major B gives zeros), so an fp32 B as [K,N] goes through a transposing pass into a
-//     caller-provided workspace first (nb200_gemm_tf32);
+//     over transposed, [N,K] -> K-major operand.  An fp32 (tf32) B as [K,N] is MN-major too,
+//     under the 32-byte-atom form of the swizzle; one whose base or pitch bulk copies cannot
+//     fetch goes through a transposing pass into a caller-provided workspace first
+//     (nb200_gemm_tf32);
 //   * the fp32 accumulator lives in tensor memory, double-buffered, so the
 //     epilogue of tile i (tcgen05.ld -> round -> store) overlaps the MMAs of
 //     tile i+1;
@@ -151,10 +152,6 @@ int check_problem(const void* a, const void* b, const void* c, int64_t m, int64_
   if (m == 0 || n == 0) return 0;
   if (!c || (k > 0 && (!a || !b))) return fail(NB200_E_INVALID, "gemm: null tensor pointer");
   if (k == 0) return 0;  // C is cleared; A and B are never read
-  if (dtype == NB200_F32 && !b_kmajor)
-    return fail(NB200_E_UNSUPPORTED,
-                "gemm: fp32 operands run as tf32, which the tensor core reads K-major only: pass B "
-                "transposed (nb200_gemm_bt) or let nb200_gemm_tf32 transpose it into a workspace");
   if (lda < k || ldb < (b_kmajor ? k : n) || ldc < n)
     return fail(NB200_E_INVALID, "gemm: row stride smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
                 (long long)lda, (long long)ldb, (long long)ldc);
@@ -251,7 +248,8 @@ int encode_tensor_map_16bit(CUtensorMap* out, const void* base, int rank, const 
 }
 
 int encode_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int rank,
-                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      bool atom32) {
   static EncodeTiledFn encode = nullptr;
   static std::mutex mu;
   {
@@ -278,7 +276,8 @@ int encode_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int ra
   CUresult r = encode(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16,
                       (cuuint32_t)rank,
                       const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(NB200_E_INVALID, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -419,17 +418,18 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
     }
   } else {
     const int slabs = (cfg.pair ? 128 : cfg.block_n) / row_k;   // column slabs per CTA
+    const bool atom32 = eb == 4;   // an MN-major tf32 operand: the swizzle works on 32-byte atoms
     wide_b = n % row_k == 0 && slabs * ksub > 1;
     if (wide_b) {   // [N / slab, K, slab]
       const uint64_t dims[3] = {(uint64_t)row_k, (uint64_t)k, (uint64_t)(n / row_k)};
       const uint64_t strides[2] = {(uint64_t)ldb * eb, 128};
       const uint32_t box[3] = {(uint32_t)row_k, (uint32_t)(row_k * ksub), (uint32_t)slabs};
-      if (int rc = encode_tensor_map(&out->tb, b, eb, 3, dims, strides, box)) return rc;
+      if (int rc = encode_tensor_map(&out->tb, b, eb, 3, dims, strides, box, atom32)) return rc;
     } else {
       const uint64_t dims[2] = {(uint64_t)n, (uint64_t)k};
       const uint64_t strides[1] = {(uint64_t)ldb * eb};
       const uint32_t box[2] = {(uint32_t)row_k, (uint32_t)row_k};
-      if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box)) return rc;
+      if (int rc = encode_tensor_map(&out->tb, b, eb, 2, dims, strides, box, atom32)) return rc;
     }
   }
 
@@ -445,7 +445,7 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   p.k_blocks = (int)cdiv64(k, row_k);
   const int mma_m = cfg.pair ? 2 * kBlockM : kBlockM;
   p.idesc = dtype == NB200_F32
-                ? sm100::instr_desc_tf32(mma_m, cfg.block_n, false, false)
+                ? sm100::instr_desc_tf32(mma_m, cfg.block_n, false, !b_kmajor)
                 : sm100::instr_desc_f16(mma_m, cfg.block_n, dtype == NB200_BF16, false, !b_kmajor);
   p.b_kmajor = b_kmajor ? 1 : 0;
   p.wide_a = wide_a ? 1 : 0;
@@ -562,12 +562,16 @@ int64_t tf32_workspace_pitch(int64_t k) {
   return pitch % 8192 == 0 && pitch > 0 ? pitch + 32 : pitch;
 }
 
-// B [K, N] -> workspace [N, pitch]; then the K-major GEMM.
+// fp32 C = A @ B with B as [K, N].  A B that bulk tensor copies can fetch as it lies (16-byte
+// aligned base and pitch) is read in place as an MN-major tf32 operand; any other B is first
+// transposed into the workspace, [N, pitch], and read K-major.
 int gemm_tf32_via(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
                   int64_t ldb, int64_t ldc, const nb200_gemm_config* config, void* workspace,
                   cudaStream_t stream) {
   if (m < 0 || n < 0 || k < 0) return fail(NB200_E_INVALID, "gemm: negative extent");
   if (n > INT32_MAX || k > INT32_MAX) return fail(NB200_E_INVALID, "gemm: extent beyond int32");
+  if ((reinterpret_cast<uintptr_t>(b) & 15) == 0 && ldb % 4 == 0 && tuning("tf32_in_place", 1))
+    return gemm_impl(a, b, c, m, n, k, lda, ldb, ldc, NB200_F32, config, false, stream);
   const int64_t pitch = tf32_workspace_pitch(k);
   if (m > 0 && n > 0 && k > 0) {
     if (!b) return fail(NB200_E_INVALID, "gemm: null tensor pointer");

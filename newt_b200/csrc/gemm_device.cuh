@@ -116,7 +116,7 @@ struct GemmParams {
   int m_blocks, n_blocks, k_blocks;
   uint32_t idesc;
   int c_vec_ok;  // C base and row pitch are 16-byte aligned
-  int b_kmajor;  // B is given transposed ([N, K], K contiguous); always so for tf32
+  int b_kmajor;  // B is given transposed ([N, K], K contiguous)
   // One bulk copy costs its issuing thread over a hundred cycles whatever its size, so a ring
   // slot is filled with as few copies as the shapes allow.  wide_a / wide_b: the tensor map is
   // the 3-D view [K / row, rows, row] (K-major operands; needs K to be whole 128-byte rows) or
@@ -290,9 +290,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
 
   const int num_tiles = p.m_blocks * p.n_blocks;
   const int k_rounds = (p.k_blocks + KSUB - 1) / KSUB;
-  // The tensor core takes tf32 operands K-major only (an MN-major B gives zeros), so fp32
-  // always comes with B transposed; for 16-bit types it is the caller's choice.
-  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;
+  // B as [K, N] is an MN-major operand: for 16-bit types under the plain 128-byte swizzle, for
+  // tf32 under its 32-byte-atom form (see smem_desc_sw128_atom32).
+  const bool b_kmajor = p.b_kmajor != 0;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -356,7 +356,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       // A: K-major, 8-row groups 1024 B apart.  B: MN-major, 8-row K groups
       // 1024 B apart, 64-column slabs kBSlab apart.
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
-      constexpr uint64_t kBDesc = smem_desc_sw128(KSUB * kBSlab, 1024);
+      constexpr uint64_t kBDesc = DT == NB200_F32 ? smem_desc_sw128_atom32(KSUB * kBSlab, 512)
+                                                  : smem_desc_sw128(KSUB * kBSlab, 1024);
       const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
       int stage = 0;
       uint32_t phase = 0;
@@ -509,7 +510,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
   const uint32_t tmem_base = tmem_slot;
   GTRACE(0, 1, threadIdx.x == 0)      // set up
 
-  const bool b_kmajor = DT == NB200_F32 || p.b_kmajor != 0;   // see gemm_kernel
+  const bool b_kmajor = p.b_kmajor != 0;
   const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
   const int num_tiles = m_blocks2 * p.n_blocks;
   const int first = cluster_id_x(), step = cluster_count_x();
@@ -583,7 +584,8 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       const uint32_t acc_full0 = map_to_cta(smem_u32(&acc_full_bar[0]), 0);
       const uint32_t acc_full1 = map_to_cta(smem_u32(&acc_full_bar[0]), 1);
       constexpr uint64_t kADesc = smem_desc_sw128(16, 1024);
-      constexpr uint64_t kBDesc = smem_desc_sw128(KSUB * kBSlab, 1024);   // column slabs of B
+      constexpr uint64_t kBDesc = DT == NB200_F32 ? smem_desc_sw128_atom32(KSUB * kBSlab, 512)
+                                                  : smem_desc_sw128(KSUB * kBSlab, 1024);   // column slabs of B
       const uint32_t b_step = b_kmajor ? 2u : uint32_t(2 * kBK);   // descriptor units of 16 B per MMA
       int stage = 0;
       uint32_t phase = 0;

@@ -435,6 +435,14 @@ __host__ __device__ constexpr uint64_t smem_desc_sw128(uint32_t lbo_bytes, uint3
   return (uint64_t((lbo_bytes >> 4) & 0x3fff) << 16) | (uint64_t((sbo_bytes >> 4) & 0x3fff) << 32) |
          (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
+// The same for an MN-major operand of 32-bit elements (tf32): the 128-byte swizzle works on
+// 32-byte atoms there (address bits 5-6 XOR bits 7-8, a pattern of four 128-byte rows: layout
+// type 1; TMA writes it with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B), so groups of four K rows
+// are SBO = 512 bytes apart.
+__host__ __device__ constexpr uint64_t smem_desc_sw128_atom32(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t((lbo_bytes >> 4) & 0x3fff) << 16) | (uint64_t((sbo_bytes >> 4) & 0x3fff) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(1) << 61);
+}
 __device__ __forceinline__ uint64_t with_address(uint64_t desc, uint32_t smem_addr) {
   return desc | uint64_t((smem_addr >> 4) & 0x3fff);
 }
@@ -520,11 +528,13 @@ __device__ __forceinline__ float exp2_approx(float x) {
 #ifndef __CUDACC_RTC__
 // ---- host: tensor maps ---------------------------------------------------------
 
-// Encodes a tiled 16-bit tensor map with 128-byte swizzle and zero fill.
+// Encodes a tiled tensor map of 16- or 32-bit elements with 128-byte swizzle and zero fill
+// (`atom32`: the swizzle's 32-byte-atom form, for MN-major tf32 operands).
 // dims/strides are given innermost first; `strides_bytes` has rank-1 entries.
 // Returns 0 or an NB200_E_* code (message recorded).
 int encode_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int rank,
-                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      bool atom32 = false);
 int encode_tensor_map_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                             const uint64_t* strides_bytes, const uint32_t* box);
 #endif  // !__CUDACC_RTC__

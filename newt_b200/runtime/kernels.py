@@ -103,10 +103,12 @@ def gemm_bt(a, bt, c, m, n, k, lda, ldbt, ldc, config=None):
 
 
 def gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, config=None):
-    """fp32 C = A @ B (tf32 product, fp32 accumulation) with B as [K, N].  The tensor core
-    reads tf32 operands K-major only, so B is transposed into a workspace first.  The workspace
-    is a fresh tensor of torch's caching allocator: allocated and used on the current stream,
-    so the allocator's stream-ordered reuse keeps concurrent launches apart."""
+    """fp32 C = A @ B (tf32 product, fp32 accumulation) with B as [K, N].  A B whose base and
+    pitch are 16-byte aligned is read in place; any other is transposed into a workspace first,
+    a fresh tensor of torch's caching allocator: allocated and used on the current stream, so
+    the allocator's stream-ordered reuse keeps concurrent launches apart."""
+    if b.data_ptr() % 16 == 0 and int(ldb) % 4 == 0:
+        return gemm(a, b, c, m, n, k, lda, ldb, ldc, config)
     need = int(abi.load().nb200_gemm_tf32_workspace_bytes(int(n), int(k)))
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device=a.device)
     cfg = ctypes.byref(config) if config is not None else None

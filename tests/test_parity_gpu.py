@@ -5,6 +5,8 @@ Bars: bit-exact for fp32 add; rtol 1e-5 for fp32 softmax; relative Frobenius
 error <= 1e-2 against an fp32 oracle for 16-bit layernorm / matmul / attention.
 """
 
+import ctypes
+
 import pytest
 import torch
 
@@ -233,8 +235,40 @@ def test_gemm_tf32_rules():
     c = torch.zeros(64, 64, device="cuda")
     assert "multiple of 4" in kernels.gemm_check(a, b, c, 64, 64, 102, 102, 66, 64)
     assert kernels.gemm_check(a, b, c, 64, 64, 100, 104, 66, 64) is None
-    with pytest.raises(abi.UnsupportedError, match="K-major"):
-        kernels.gemm(a, b, c, 64, 64, 100, 104, 66, 64)      # fp32 with B as [K, N]: not this entry
+    with pytest.raises(abi.UnsupportedError, match="multiple of 4"):
+        kernels.gemm(a, b, c, 64, 64, 100, 104, 66, 64)      # B's pitch of 264 bytes: not in place
+
+
+@pytest.mark.parametrize("config", [dict(block_n=64), dict(block_n=128, block_k=64), dict(block_n=256),
+                                    dict(block_m=256, block_n=256),
+                                    dict(block_m=256, block_n=256, block_k=32, stages=5)])
+@pytest.mark.parametrize("m,n,k", [(128, 64, 32), (130, 72, 200), (257, 520, 132), (1024, 1024, 1024)])
+def test_gemm_tf32_reads_b_in_place(config, m, n, k):
+    """fp32 B as [K, N] with a 16-byte pitch is an MN-major tf32 operand (the swizzle on 32-byte
+    atoms): same result, bit for bit, as through the transposing pass, whose K-major product
+    sums the same terms in the same order."""
+    g = torch.Generator().manual_seed(m * 3 + n * 5 + k)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).cuda()
+    b = torch.randn(k, n, generator=g).cuda()
+    c = torch.full((m, n), float("nan"), device="cuda")
+    kernels.gemm(a, b, c, m, n, k, k, n, n, kernels.gemm_config(**config))      # in place
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    assert torch_ref.rel_frobenius(c.cpu(), a.cpu().double() @ b.cpu().double()) <= 2e-3
+    via = torch.full((m, n), float("nan"), device="cuda")
+    abi.set_tuning("tf32_in_place", 0)
+    try:
+        ws = torch.empty(int(abi.load().nb200_gemm_tf32_workspace_bytes(n, k)), dtype=torch.uint8,
+                         device="cuda")
+        abi.check(abi.load().nb200_gemm_tf32(
+            ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()),
+            ctypes.c_void_p(via.data_ptr()), m, n, k, k, n, n,
+            ctypes.byref(kernels.gemm_config(**config)), ctypes.c_void_p(ws.data_ptr()), ws.numel(),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        torch.cuda.synchronize()
+    finally:
+        abi.set_tuning("tf32_in_place", 1)
+    assert torch.equal(c, via)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
@@ -281,8 +315,6 @@ def test_gemm_cta_pair_vs_oracle(dtype, block_k, stages, m, n, k):
 def test_gemm_two_slab_slots_vs_oracle(dtype, block_n, transposed, m, n, k):
     """Ring slots of two K slabs (one copy per operand and slot where the shapes allow the wide
     tensor maps, slab by slab at ragged K or N), B as [K, N] and as [N, K]."""
-    if dtype == torch.float32 and not transposed:
-        pytest.skip("tf32 reads B K-major only")
     g = torch.Generator().manual_seed(m * 11 + n * 3 + k + block_n)
     a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype)
     b = torch.randn(k, n, generator=g).to(dtype)
@@ -339,9 +371,9 @@ def test_gemm_check_rejects_without_launching():
     c = torch.zeros(64, 64, device="cuda", dtype=torch.float16)
     assert "multiple of 8" in kernels.gemm_check(a, b, c, 64, 64, 100, 100, 64, 64)
     assert kernels.gemm_check(a, b, c, 64, 64, 96, 104, 64, 64) is None
-    af = torch.zeros(64, 64, device="cuda")
-    with pytest.raises(abi.UnsupportedError):
-        kernels.gemm(af, af, af, 64, 64, 64, 64, 64, 64)
+    af = torch.zeros(64, 66, device="cuda")          # an fp32 pitch of 264 bytes
+    with pytest.raises(abi.UnsupportedError, match="multiple of 4"):
+        kernels.gemm(af, af, af, 64, 64, 64, 66, 66, 66)
 
 
 # ---- K5 -------------------------------------------------------------------------
