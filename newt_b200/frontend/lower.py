@@ -890,9 +890,7 @@ class GemmPlan(Plan):
         if not fetchable(b, ldb, inner[self.b]):
             b, ldb = kernels.repitched("b", b, k, n, ldb, inner[self.b])
             self.repitched += 1
-        if self.row_k == 32:
-            kernels.gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, self.config())
-        elif acc32 is not None:
+        if acc32 is not None and self.row_k != 32:
             kernels.gemm_acc32(a, b, c, m, n, k, lda, ldb, ldc, False, self.config())
         else:
             kernels.gemm(a, b, c, m, n, k, lda, ldb, ldc, self.config())
@@ -1012,8 +1010,6 @@ class GemmEpiloguePlan(Plan):
         self.fused_source = None
         self.fused_reason = None
         try:
-            if gemm.row_k != 64:
-                raise pointwise.Unsupported("fp32 operands go through a transposing pass first")
             text, self.fused_params = pointwise.generate_epilogue(
                 trace, acc, store, gemm.block[:2], (gemm.pid_m, gemm.pid_n))
             self.fused_source = text
