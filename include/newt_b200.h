@@ -120,7 +120,7 @@ int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
  * at least one 256x256 tile per pair of SMs, single-CTA 128xN tiles otherwise. */
 typedef struct nb200_gemm_config {
   int32_t block_m; /* 128 (one CTA) or 256 (CTA pair)                        */
-  int32_t block_n; /* 64, 128 or 256 (256 only for a CTA pair)               */
+  int32_t block_n; /* 64, 128 or 256; a CTA pair takes 256 or 512            */
   int32_t block_k; /* 64; a CTA pair also takes 128 (default) and 192 (fp32: 32 / 64 / 96) */
   int32_t stages;  /* 1..8; snapped to a depth that fits 227 KB of shared mem */
   int32_t cta_pair;/* 0 or 1                                                 */

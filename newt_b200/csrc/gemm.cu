@@ -63,6 +63,14 @@ __global__ void __launch_bounds__(gemm::kThreads, 1)
                                                                gemm::NoEpilogueArgs{0});
 }
 
+template <int STAGES, int KSUB, int DT, int CT>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
+    gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                          const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  gemm::gemm_pair_body<STAGES, KSUB, DT, CT, gemm::NoEpilogue, 2>(tmap_a, tmap_b, p,
+                                                                  gemm::NoEpilogueArgs{0});
+}
+
 // ---- host ----------------------------------------------------------------------
 
 struct Resolved {
@@ -92,8 +100,19 @@ int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, int row_k
   if (pair) {
     if (bm != 0 && bm != 2 * kBlockM)
       return fail(NB200_E_INVALID, "block_m=%d: a CTA pair computes 256-row tiles", bm);
-    if (bn != 0 && bn != 256)
-      return fail(NB200_E_INVALID, "block_n=%d: CTA-pair tiles are 256 columns wide", bn);
+    if (bn != 0 && bn != 256 && bn != 512)
+      return fail(NB200_E_INVALID, "block_n=%d: CTA-pair tiles are 256 or 512 columns wide", bn);
+    if (bn == 512) {
+      // two 256-column MMAs per K step on one accumulator of all 512 tensor-memory columns: a
+      // third less traffic from L2 per flop, no second accumulator for the epilogue to hide behind
+      if (bk != 0 && bk != kBlockK && bk != 2 * kBlockK)
+        return fail(NB200_E_INVALID, "block_k=%d: a 512-column ring slot holds %d or %d elements of K",
+                    bk, kBlockK, 2 * kBlockK);
+      out->block_n = 512;
+      out->block_k = bk == 2 * kBlockK ? bk : kBlockK;
+      out->stages = bk == 2 * kBlockK ? 2 : 4;
+      return 0;
+    }
     if (bk != 0 && bk != kBlockK && bk != 2 * kBlockK && bk != 3 * kBlockK)
       return fail(NB200_E_INVALID,
                   "block_k=%d: a CTA-pair ring slot holds %d, %d or %d elements of K", bk, kBlockK,
@@ -205,8 +224,8 @@ int pair_clusters(const void* kern, int smem, const GemmParams& p, int* clusters
   return 0;
 }
 
-int pair_smem_bytes(int stages, int ksub) {
-  return stages * ksub * (kBlockM * 128 + 128 * 128) + 1024 + (int)gemm::kEpilogueStageBytes;
+int pair_smem_bytes(int stages, int ksub, int nsub = 1) {
+  return stages * ksub * (kBlockM * 128 + nsub * 128 * 128) + 1024 + (int)gemm::kEpilogueStageBytes;
 }
 
 template <int STAGES, int KSUB>
@@ -214,6 +233,30 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
                 bool c_f32, cudaStream_t stream) {
   const int smem = pair_smem_bytes(STAGES, KSUB);
   const void* kern = NB200_PICK(gemm_pair_kernel, STAGES, KSUB);
+  if (int rc = prepare_kernel(kern, smem)) return rc;
+  int clusters = 0;
+  if (int rc = pair_clusters(kern, smem, p, &clusters)) return rc;
+  cudaLaunchConfig_t lc = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.blockDim = dim3(kThreads);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  lc.gridDim = dim3(2 * clusters);
+  void* args[3] = {(void*)&ta, (void*)&tb, (void*)&p};
+  return cuda_check(cudaLaunchKernelExC(&lc, kern, args), "gemm pair launch");
+}
+
+template <int STAGES, int KSUB>
+int launch_pair_wide(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype,
+                bool c_f32, cudaStream_t stream) {
+  const int smem = pair_smem_bytes(STAGES, KSUB, 2);
+  const void* kern = NB200_PICK(gemm_pair_wide_kernel, STAGES, KSUB);
   if (int rc = prepare_kernel(kern, smem)) return rc;
   int clusters = 0;
   if (int rc = pair_clusters(kern, smem, p, &clusters)) return rc;
@@ -444,9 +487,10 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   p.n_blocks = (int)cdiv64(n, cfg.block_n);
   p.k_blocks = (int)cdiv64(k, row_k);
   const int mma_m = cfg.pair ? 2 * kBlockM : kBlockM;
+  const int mma_n = cfg.pair ? 256 : cfg.block_n;   // a 512-column pair tile is two MMAs wide
   p.idesc = dtype == NB200_F32
-                ? sm100::instr_desc_tf32(mma_m, cfg.block_n, false, !b_kmajor)
-                : sm100::instr_desc_f16(mma_m, cfg.block_n, dtype == NB200_BF16, false, !b_kmajor);
+                ? sm100::instr_desc_tf32(mma_m, mma_n, false, !b_kmajor)
+                : sm100::instr_desc_f16(mma_m, mma_n, dtype == NB200_BF16, false, !b_kmajor);
   p.b_kmajor = b_kmajor ? 1 : 0;
   p.wide_a = wide_a ? 1 : 0;
   p.wide_b = wide_b ? 1 : 0;
@@ -471,6 +515,9 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   const Resolved& cfg = g.cfg;
   const GemmParams& p = g.p;
 
+  if (cfg.pair && cfg.block_n == 512)
+    return cfg.block_k == 2 * g.row_k ? launch_pair_wide<2, 2>(g.ta, g.tb, p, dtype, c_f32, stream)
+                                      : launch_pair_wide<4, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
   if (cfg.pair) {
     if (cfg.block_k == 2 * g.row_k) return launch_pair<3, 2>(g.ta, g.tb, p, dtype, c_f32, stream);
     if (cfg.block_k == 3 * g.row_k) return launch_pair<2, 3>(g.ta, g.tb, p, dtype, c_f32, stream);
@@ -644,16 +691,20 @@ extern "C" int nb200_gemm_plan(const void* a, const void* b, void* c, int64_t m,
   if (g.cfg.pair) {
     // the instances the library has itself: 3 slots of two K slabs, 2 of three, 4..6 of one
     int stages = g.cfg.stages, ksub = 1;
-    if (g.cfg.block_k == 2 * g.row_k) stages = 3, ksub = 2;
+    const bool wide = g.cfg.block_n == 512;
+    if (wide) ksub = g.cfg.block_k == 2 * g.row_k ? 2 : 1;
+    else if (g.cfg.block_k == 2 * g.row_k) stages = 3, ksub = 2;
     else if (g.cfg.block_k == 3 * g.row_k) stages = 2, ksub = 3;
     else stages = stages < 4 ? 4 : (stages > 6 ? 6 : stages);
     launch->pair = 1;
     launch->stages = stages;
     launch->ksub = ksub;
     launch->cluster = 2;
-    launch->smem_bytes = pair_smem_bytes(stages, ksub);
+    launch->smem_bytes = pair_smem_bytes(stages, ksub, wide ? 2 : 1);
     // as many pairs as the device holds of the library's own instance of this shape
-    const void* twin = stages == 3 && ksub == 2 ? (const void*)gemm_pair_kernel<3, 2, NB200_BF16, NB200_BF16>
+    const void* twin = wide ? (ksub == 2 ? (const void*)gemm_pair_wide_kernel<2, 2, NB200_BF16, NB200_BF16>
+                                         : (const void*)gemm_pair_wide_kernel<4, 1, NB200_BF16, NB200_BF16>)
+                     : stages == 3 && ksub == 2 ? (const void*)gemm_pair_kernel<3, 2, NB200_BF16, NB200_BF16>
                      : stages == 2 && ksub == 3 ? (const void*)gemm_pair_kernel<2, 3, NB200_BF16, NB200_BF16>
                      : stages == 4 ? (const void*)gemm_pair_kernel<4, 1, NB200_BF16, NB200_BF16>
                      : stages == 5 ? (const void*)gemm_pair_kernel<5, 1, NB200_BF16, NB200_BF16>

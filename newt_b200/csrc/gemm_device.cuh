@@ -456,18 +456,19 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
 // epilogue warps of both CTAs, once per tile.
 // KSUB 64-element K slabs share one ring slot (one barrier round trip and one pair of
 // commits per slot).
-template <int STAGES, int KSUB, int DT, int CT, class EPI>
+template <int STAGES, int KSUB, int DT, int CT, class EPI, int NSUB = 1>
 __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmParams& p, const typename EPI::Args& ea) {
-  constexpr int BN = 256;                                // cluster tile width
+  constexpr int BN = 256 * NSUB;                         // cluster tile width: NSUB MMAs of 256 columns
+  constexpr int kAccBufs = NSUB == 1 ? 2 : 1;            // a 512-column tile takes all of tensor memory
   constexpr int kBK = Elem<DT>::kPerRow;                 // K elements per 128-byte row
   constexpr int kSlab = Elem<DT>::kPerRow;               // columns of B per slab
   constexpr uint32_t kABytes = kBlockM * 128;            // this CTA's 128 rows of A: 16 KB
   constexpr uint32_t kBSlab = kBK * 128;                 // one slab of B: 8 KB (4 KB for tf32)
-  constexpr uint32_t kBBytes = kBSlab * (128 / kSlab);   // this CTA's 128 columns of B
-  constexpr uint32_t kSlabBytes = kABytes + kBBytes;     // 32 KB per 64 elements of K
+  constexpr uint32_t kBBytes = kBSlab * (128 / kSlab);   // this CTA's 128 columns of one MMA's B
+  constexpr uint32_t kSlabBytes = kABytes + NSUB * kBBytes;   // 32 (48) KB per 64 elements of K
   constexpr uint32_t kStageBytes = KSUB * kSlabBytes;
-  constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr uint32_t kTmemCols = 512;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
@@ -526,7 +527,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
         int mb, nb;
         tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
         const int row0 = mb * 2 * kBlockM + rank * kBlockM;
-        const int col0 = nb * BN + rank * (BN / 2);
+        const int col0 = nb * BN + rank * 128;   // of the first MMA; the second is 256 further
         for (int kb = 0; kb < k_rounds; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
           if (!ok) break;
@@ -544,23 +545,28 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
             for (int sub = 0; sub < KSUB; ++sub)
               tma_load_2d_pair(a_dst + sub * kABytes, &tmap_a, (slab0 + sub) * kBK, row0, bar);
           }
-          if (b_kmajor) {   // this CTA's 128 rows of B^T, laid out like A
-            if (p.wide_b) {
-              tma_load_3d_pair(b_dst, &tmap_b, 0, col0, slab0, bar);
+#pragma unroll
+          for (int h = 0; h < NSUB; ++h) {   // this CTA's 128 columns of each 256-column MMA
+            const uint32_t bh_dst = b_dst + h * KSUB * kBBytes;
+            const int colh = col0 + h * 256;
+            if (b_kmajor) {   // 128 rows of B^T, laid out like A
+              if (p.wide_b) {
+                tma_load_3d_pair(bh_dst, &tmap_b, 0, colh, slab0, bar);
+              } else {
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub)
+                  tma_load_2d_pair(bh_dst + sub * kBBytes, &tmap_b, (slab0 + sub) * kBK, colh, bar);
+              }
+            } else if (p.wide_b) {   // both column slabs, KSUB * 64 rows of K each
+              tma_load_3d_pair(bh_dst, &tmap_b, 0, slab0 * kBK, colh / kSlab, bar);
             } else {
 #pragma unroll
-              for (int sub = 0; sub < KSUB; ++sub)
-                tma_load_2d_pair(b_dst + sub * kBBytes, &tmap_b, (slab0 + sub) * kBK, col0, bar);
+              for (int j = 0; j < 128 / kSlab; ++j)
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub)
+                  tma_load_2d_pair(bh_dst + (j * KSUB + sub) * kBSlab, &tmap_b, colh + j * kSlab,
+                                   (slab0 + sub) * kBK, bar);
             }
-          } else if (p.wide_b) {   // both column slabs, KSUB * 64 rows of K each
-            tma_load_3d_pair(b_dst, &tmap_b, 0, slab0 * kBK, col0 / kSlab, bar);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 128 / kSlab; ++j)
-#pragma unroll
-              for (int sub = 0; sub < KSUB; ++sub)
-                tma_load_2d_pair(b_dst + (j * KSUB + sub) * kBSlab, &tmap_b, col0 + j * kSlab,
-                                 (slab0 + sub) * kBK, bar);
           }
           GTRACE(0, 100 + kb, (kb & 7) == 0)     // copies of k round kb issued
           if (++stage == STAGES) {
@@ -592,12 +598,12 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       int it = 0;
       bool ok = true;
       for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
-        const int buf = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
+        const int buf = kAccBufs == 2 ? (it & 1) : 0;
+        const uint32_t acc_phase = kAccBufs == 2 ? ((it >> 1) & 1) : (it & 1);
         ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t d_tmem = tmem_base + buf * 256;
         for (int kb = 0; kb < k_rounds; ++kb) {
           ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
@@ -610,13 +616,18 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
             // K-major operands: slab `sub` is a block of its own.  B as [K, N]: a column slab
             // holds the K rows of all KSUB slabs one after the other.
             const uint64_t a_desc = with_address(kADesc, a_addr + sub * kABytes);
-            const uint64_t b_desc = b_kmajor ? with_address(kADesc, b_addr + sub * kBBytes)
-                                             : with_address(kBDesc, b_addr + sub * kBSlab);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              if (elected)
-                mma_ss_pair<DT>(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * b_step),
-                                p.idesc, (kb | sub | kk) != 0 ? 1u : 0u);
+            for (int h = 0; h < NSUB; ++h) {
+              const uint32_t bh_addr = b_addr + h * KSUB * kBBytes;
+              const uint64_t b_desc = b_kmajor ? with_address(kADesc, bh_addr + sub * kBBytes)
+                                               : with_address(kBDesc, bh_addr + sub * kBSlab);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                if (elected)
+                  mma_ss_pair<DT>(d_tmem + h * 256, a_desc + (uint64_t)(kk * 2),
+                                  b_desc + (uint64_t)(kk * b_step), p.idesc,
+                                  (kb | sub | kk) != 0 ? 1u : 0u);
+            }
           }
           // the slot is free in both CTAs once these MMAs retire
           if (elected) {
@@ -645,14 +656,14 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
     for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
       int mb, nb;
       tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
+      const int buf = kAccBufs == 2 ? (it & 1) : 0;
+      const uint32_t acc_phase = kAccBufs == 2 ? ((it >> 1) & 1) : (it & 1);
       ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
       GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
-      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * 256;
       drain_rows<BN, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
                               nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),
                               lane, ea);

@@ -17,7 +17,7 @@ import os
 import random
 import tempfile
 
-CACHE_VERSION = "sm100a-2"
+CACHE_VERSION = "sm100a-3"
 
 
 class Config(dict):
@@ -32,10 +32,10 @@ class Config(dict):
 
 def search_space(tunable, has_dot):
     """Options per knob.  A kernel with a matmul runs on tcgen05 tiles: 128-row MMAs (256 rows
-    = a CTA pair), 64..256 columns, and ring depths the GEMM has instances for; anything else
-    is a generated kernel whose tiles may be any power of two."""
+    = a CTA pair), 64..256 columns (512 for a pair), and ring depths the GEMM has instances for;
+    anything else is a generated kernel whose tiles may be any power of two."""
     if has_dot:
-        space = {name: [64, 128, 256] for name in tunable}
+        space = {name: [64, 128, 256, 512] for name in tunable}
         space["num_warps"] = [4]
         space["num_stages"] = [2, 3, 4, 5, 6]
     else:

@@ -151,6 +151,7 @@ def layernorm(x, w, b, eps=1e-5, out=None):
 # columns, 64-element K slabs per TMA stage, ring depth as num_stages.
 @newt.autotune(
     configs=[
+        newt.Config({"BLOCK_M": 256, "BLOCK_N": 512, "BLOCK_K": 64}, num_warps=4, num_stages=4),
         newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 128}, num_warps=4, num_stages=3),
         newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=6),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=4),

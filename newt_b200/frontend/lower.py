@@ -773,6 +773,8 @@ class GemmPlan(Plan):
         to issue: what small problems are bound by)."""
         bm, bn, bk = self.block
         rk = self.row_k
+        if bm == 256 and bn == 512:        # two 256-column MMAs on one 512-column accumulator
+            return ("gemm-pair-wide", 2 * rk if bk == 2 * rk else rk, 0)
         if bm == 256 and bn == 256:
             bk = bk if bk in (rk, 2 * rk, 3 * rk) else 2 * rk
             return ("gemm-pair", bk, self.num_stages if bk == rk else 0)
@@ -788,6 +790,8 @@ class GemmPlan(Plan):
             if kind == "gemm-pair":
                 self._config = kernels.gemm_config(block_m=256, block_n=256, block_k=x,
                                                    stages=stages, cta_pair=1)
+            elif kind == "gemm-pair-wide":
+                self._config = kernels.gemm_config(block_m=256, block_n=512, block_k=x, cta_pair=1)
             elif kind == "gemm-2slab":
                 self._config = kernels.gemm_config(block_n=x, block_k=2 * self.row_k)
             else:
@@ -1061,7 +1065,7 @@ class GemmEpiloguePlan(Plan):
             codes = {0: "NB200_F32", 1: "NB200_F16", 2: "NB200_BF16"}
             if launch.pair:
                 body = (f"nb200::gemm::gemm_pair_body<{launch.stages}, {launch.ksub}, {codes[dtype_code]}, "
-                        f"{codes[c_code]}, NbEpilogue>(ta, tb, p, ea);")
+                        f"{codes[c_code]}, NbEpilogue, {2 if launch.block_n == 512 else 1}>(ta, tb, p, ea);")
             else:
                 body = (f"nb200::gemm::gemm_body<{launch.block_n}, {launch.stages}, {launch.ksub}, "
                         f"{codes[dtype_code]}, "

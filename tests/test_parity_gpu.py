@@ -338,6 +338,36 @@ def test_gemm_two_slab_slots_vs_oracle(dtype, block_n, transposed, m, n, k):
     assert torch_ref.rel_frobenius(got, a.double() @ b.double()) <= tol
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("block_k", [1, 2])            # in 128-byte rows of K
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 64), (130, 72, 200), (700, 1000, 328), (512, 1024, 512),
+                                   (2048, 2048, 1024)])
+def test_gemm_wide_pair_vs_oracle(dtype, block_k, transposed, m, n, k):
+    """256 x 512 tiles per CTA pair: two 256-column MMAs per K step on one accumulator that
+    takes all of tensor memory; ragged edges in all three extents, B either way round."""
+    g = torch.Generator().manual_seed(m * 13 + n * 3 + k + block_k)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype)
+    b = torch.randn(k, n, generator=g).to(dtype)
+    kp, np_ = (k + 7) // 8 * 8, (n + 7) // 8 * 8
+    ad = torch.zeros(m, kp, dtype=dtype, device="cuda")[:, :k].copy_(a)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+    row_k = 32 if dtype == torch.float32 else 64
+    cfg = kernels.gemm_config(block_m=256, block_n=512, block_k=block_k * row_k, cta_pair=1)
+    if transposed:
+        bd = torch.zeros(n, kp, dtype=dtype, device="cuda")[:, :k].copy_(b.t())
+        kernels.gemm_bt(ad, bd, c, m, n, k, kp, kp, n, cfg)
+    else:
+        bd = torch.zeros(k, np_, dtype=dtype, device="cuda")[:, :n].copy_(b)
+        kernels.gemm(ad, bd, c, m, n, k, kp, np_, n, cfg)
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    got = c.cpu().double()
+    assert not torch.isnan(got).any()
+    tol = 2e-3 if dtype == torch.float32 else 1e-2
+    assert torch_ref.rel_frobenius(got, a.double() @ b.double()) <= tol
+
+
 def test_gemm_linearity_at_full_size():
     # size-independent property at the benchmark size: (A1 + A2) @ B == A1 @ B + A2 @ B
     # up to rounding, and a spot-checked block against the fp32 oracle
