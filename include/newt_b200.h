@@ -61,6 +61,10 @@ int nb200_read_status(uint32_t* status, uint32_t* detail);
  *   "row_items"        16-byte vectors each of those threads holds (1,2,4,8)
  *   "row_ctas_per_sm"  resident CTAs per SM of the persistent row grid
  *   "row_rpb"          rows that share one CTA (1, 2 or 4)
+ *   "row_force_slow"   1: the row kernels' element-wise path even where rows are vector-friendly
+ *   "add_variant"      K0's walk: 1 persistent grid x4 loads, 2 chunks in address order x4
+ *                      (the default), 3 chunks x8, 4 persistent x8
+ *   "tf32_in_place"    0: nb200_gemm_tf32 always transposes B into its workspace
  *   "wait_limit_us"    how long one device-side wait (an mbarrier spin of the tensor-core
  *                      kernels) may last before the kernel gives up, records a code in the
  *                      status word and returns; 2 000 000 (2 s) when unset */
