@@ -682,6 +682,12 @@ def protocol_floor_ms(ctx, nbytes, reps=20):
     return statistics.median(s.elapsed_time(e) for s, e in pairs)
 
 
+def empty_launch_ms(ctx, reps=20):
+    """What the same protocol reads for a launch that moves nothing (a 32-byte copy): the part
+    of every step time that is the launch itself, not the kernel's traffic."""
+    return protocol_floor_ms(ctx, 64, reps)
+
+
 def measure(ctx, args, wl):
     """Times one workload on this rank's GPU; rank 0 gets the record (the others None)."""
     rank, world = ctx.rank, ctx.world
@@ -737,7 +743,7 @@ def measure(ctx, args, wl):
         par["checked"] += f"; worst of {world} ranks"
 
     # ---- HBM-bound: the same steps back to back over rotating buffer sets ------
-    rotating_ms = floor_ms = None
+    rotating_ms = floor_ms = launch_only_ms = None
     if wl.bound == "hbm":
         sets = [dev] + [wl.to_device(host) for _ in range(7)]    # 8 x 128 MB > L2, no flush
         reps = max(steps, 40)
@@ -753,6 +759,7 @@ def measure(ctx, args, wl):
         rotating_ms = r0.elapsed_time(r1) / reps
         del sets
         floor_ms = protocol_floor_ms(ctx, wl.units_per_step())
+        launch_only_ms = empty_launch_ms(ctx)
     clocks = sampler.stop() if rank == 0 else None     # sampled over the device-timed regions
 
     # ---- end-to-end region: pinned host -> device, step, result -> host -------
@@ -820,6 +827,10 @@ def measure(ctx, args, wl):
             "protocol_floor_note": "torch copy_ of the same bytes (half read, half written) "
                                    "timed by the identical flush + event protocol",
             "vs_protocol_floor": floor_ms / launch_ms,
+            "empty_launch_ms": launch_only_ms,
+            "net_of_launch": {"achieved": units / max(launch_ms - launch_only_ms, 1e-6) / 1e-3 / scale,
+                              "how": "the same bytes over the step time less what an empty "
+                                     "launch reads between the same events"},
             "back_to_back": {"achieved": back_to_back, "frac": back_to_back / peak,
                              "ms_per_step": rotating_ms,
                              "how": "no flush: steps back to back over 8 rotating input/output "
