@@ -172,6 +172,49 @@ class _Context:
             self._unit[ptr.uid] = hit
         return hit
 
+    def mask_deciders(self, mask):
+        """The lanes of a group whose mask values decide the conjunction over the whole group:
+        a subset of {"first", "last"}, or None when every lane has to be looked at.  `offs < n`
+        with offs rising by one per lane holds for all lanes when it holds for the last."""
+        from .affine import NotAffine, Poly
+        if not isinstance(mask, Node):
+            return None
+        if not mask.shape or mask.shape[-1] == 1:
+            return {"first"}                      # the same value in every lane
+        if mask.op in ("broadcast", "splat"):
+            inner = mask.args[0]
+            if not isinstance(inner, Node) or not inner.shape or inner.shape[-1] == 1:
+                return {"first"}
+            return self.mask_deciders(inner) if inner.shape[-1] == mask.shape[-1] else None
+        if mask.op == "expand":
+            if dict(mask.attrs)["axis"] == len(mask.shape) - 1:
+                return {"first"}                  # the new axis is the lanes' one
+            return self.mask_deciders(mask.args[0])
+        if mask.op == "bin" and dict(mask.attrs)["fn"] == "and":
+            both = [self.mask_deciders(a) for a in mask.args]
+            return None if None in both else both[0] | both[1]
+        if mask.op != "cmp":
+            return None
+        fn = dict(mask.attrs)["fn"]
+        if self._analyzer is None:
+            from .affine import Analyzer
+            self._analyzer = Analyzer(self.trace)
+        try:
+            pa, pb = self._analyzer._aligned(mask.args[0], mask.args[1], len(mask.shape))
+            split = (pa - pb).coeff_of(("ax", len(mask.shape) - 1))
+        except NotAffine:
+            return None
+        if split is None or not split[0].is_const():
+            return None
+        rise = split[0].const_value()             # change of a - b from one lane to the next
+        if rise == 0:
+            return {"first"}
+        if fn in ("lt", "le"):
+            return {"last"} if rise > 0 else {"first"}
+        if fn in ("gt", "ge"):
+            return {"first"} if rise > 0 else {"last"}
+        return None
+
     def alloc(self, dt, count, prefix):
         """A shared-memory array of `count` elements; returns its name."""
         name = f"{prefix}{len(self.arrays)}"
@@ -477,6 +520,27 @@ def _simple_for_lanes(roots):
     return True, narrow
 
 
+def _side_body(body):
+    """A statement list for a nested block of `body`: sees what `body` has computed, keeps what
+    it computes to itself."""
+    side = _Body(body.ctx, body.loop_state)
+    side.lanes = body.lanes
+    side.memo = dict(body.memo)
+    side.loop_final = dict(body.loop_final)
+    return side
+
+
+def _whole_group(body, mask, mask_at, lanes):
+    """Conditions under which every lane of a group passes `mask`: the deciding lanes' values
+    where the mask is known to rise or fall along the lanes, else all of them."""
+    if mask is None:
+        return []
+    deciders = body.ctx.mask_deciders(mask)
+    if deciders is None:
+        return list(dict.fromkeys(mask_at(k) for k in range(lanes)))
+    return [mask_at(0 if d == "first" else lanes - 1) for d in sorted(deciders)]
+
+
 def _emit_lanes_load(body, node, dims):
     """All lanes of a unit-stride load at once; None when this load is not of that kind."""
     lanes = body.lanes
@@ -494,14 +558,7 @@ def _emit_lanes_load(body, node, dims):
         return _emit(body, x, _operand_dims(node.shape, _lane_dims(dims, k), x.shape))
 
     p0 = at(ptr, 0)
-    masks = [at(mask, k) for k in range(lanes)] if mask is not None else None
-    if mask is None:
-        fills = None
-    elif isinstance(other, Node):
-        fills = [_convert(at(other, k), other.dtype, dt) for k in range(lanes)]
-    else:
-        fills = [_literal(other if other is not None else 0, dt)] * lanes
-    conds = [_aligned16(p0)] + (list(dict.fromkeys(masks)) if masks else [])
+    conds = [_aligned16(p0)] + _whole_group(body, mask, lambda k: at(mask, k), lanes)
     whole = body.var(tp.int1, " && ".join(conds))
     arr = body.ctx.fresh("q")
     ct = dt.ctype
@@ -512,11 +569,19 @@ def _emit_lanes_load(body, node, dims):
         body.lines.append(f"  const {ct}* s{piece} = reinterpret_cast<const {ct}*>(&t{piece});")
         body.lines += [f"  {arr}[{piece * per + k}] = s{piece}[{k}];" for k in range(per)]
     body.lines.append("} else {")
+    rare = _side_body(body)         # what only the lane-by-lane path needs stays inside its braces
+
+    def rare_at(x, k):
+        return _emit(rare, x, _operand_dims(node.shape, _lane_dims(dims, k), x.shape))
+
     for k in range(lanes):
-        if masks is None:
-            body.lines.append(f"  {arr}[{k}] = {p0}[{k}];")
+        if mask is None:
+            rare.lines.append(f"{arr}[{k}] = {p0}[{k}];")
         else:
-            body.lines.append(f"  {arr}[{k}] = {masks[k]} ? {p0}[{k}] : {fills[k]};")
+            fill = _convert(rare_at(other, k), other.dtype, dt) if isinstance(other, Node) \
+                else _literal(other if other is not None else 0, dt)
+            rare.lines.append(f"{arr}[{k}] = {rare_at(mask, k)} ? {p0}[{k}] : {fill};")
+    body.lines += ["  " + ln for ln in rare.lines]
     body.lines.append("}")
     for k in range(lanes):
         body.memo[(node.uid, _lane_dims(dims, k))] = f"{arr}[{k}]"
@@ -531,33 +596,33 @@ def _emit_lanes_store(body, ptr, value, mask, dims, lanes):
     vals = [_convert(_emit(body, value, _operand_dims(shape, d, value.shape)), value.dtype, elem)
             for d in each]
     p0 = _emit(body, ptr, each[0])
-    guards = [_emit(body, mask, _operand_dims(shape, d, mask.shape)) for d in each] \
-        if mask is not None else None
     ct = elem.ctype
 
-    def one_by_one(indent):
-        for k in range(lanes):
-            stmt = f"{p0}[{k}] = {vals[k]};"
-            body.lines.append(f"{indent}if ({guards[k]}) {stmt}" if guards else f"{indent}{stmt}")
+    def guard_at(where, k):
+        return _emit(where, mask, _operand_dims(shape, each[k], mask.shape))
 
-    if (elem.itemsize * lanes) % 16 or not body.ctx.unit_stride(ptr):
-        if not body.ctx.unit_stride(ptr):        # no neighbours in memory: every lane its own pointer
-            for k, d in enumerate(each):
-                pk = _emit(body, ptr, d)
-                stmt = f"*{pk} = {vals[k]};"
-                body.lines.append(f"if ({guards[k]}) {stmt}" if guards else stmt)
-        else:
-            one_by_one("")
+    def one_by_one(where, pointer_of):
+        for k in range(lanes):
+            stmt = f"{pointer_of(k)} = {vals[k]};"
+            where.lines.append(f"if ({guard_at(where, k)}) {stmt}" if mask is not None else stmt)
+
+    if not body.ctx.unit_stride(ptr):        # no neighbours in memory: every lane its own pointer
+        one_by_one(body, lambda k: "*" + _emit(body, ptr, each[k]))
+        return
+    if (elem.itemsize * lanes) % 16:
+        one_by_one(body, lambda k: f"{p0}[{k}]")
         return
     pieces = elem.itemsize * lanes // 16
-    conds = [_aligned16(p0)] + (list(dict.fromkeys(guards)) if guards else [])
+    conds = [_aligned16(p0)] + _whole_group(body, mask, lambda k: guard_at(body, k), lanes)
     body.lines.append(f"if ({' && '.join(conds)}) {{")
     body.lines.append(f"  __align__(16) {ct} w[{lanes}];")
     body.lines += [f"  w[{k}] = {vals[k]};" for k in range(lanes)]
     body.lines += [f"  reinterpret_cast<uint4*>({p0})[{piece}] = reinterpret_cast<const uint4*>(w)[{piece}];"
                    for piece in range(pieces)]
     body.lines.append("} else {")
-    one_by_one("  ")
+    rare = _side_body(body)
+    one_by_one(rare, lambda k: f"{p0}[{k}]")
+    body.lines += ["  " + ln for ln in rare.lines]
     body.lines.append("}")
 
 
