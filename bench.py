@@ -929,7 +929,7 @@ def main():
                     help="profiler-sized variant of the workload (never a reported number)")
     ap.add_argument("--no-autotune", action="store_true",
                     help="fixed tile configuration instead of the first-call search")
-    ap.add_argument("--tile", default="256,256,128,3",
+    ap.add_argument("--tile", default="256,512,64,4",
                     help="BLOCK_M,BLOCK_N,BLOCK_K,num_stages used with --no-autotune (matmul)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=INT",
                     help="library tuning knob (nb200_set_tuning), e.g. row_tpr=256")

@@ -95,6 +95,8 @@ int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, int row_k
   if (!cfg || (bm == 0 && bn == 0 && bk == 0 && !cfg->cta_pair)) {
     // library default: CTA pairs once they fill the machine (74 pairs), else single CTAs
     pair = cdiv64(m, 2 * kBlockM) * cdiv64(n, 256) >= device_info().sm_count / 2;
+    // ... and 256 x 512 tiles once those fill it too: a third less traffic from L2 per flop
+    if (pair && cdiv64(m, 2 * kBlockM) * cdiv64(n, 512) >= device_info().sm_count / 2) bn = 512;
   }
   out->pair = pair;
   if (pair) {
@@ -493,6 +495,7 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
                 : sm100::instr_desc_f16(mma_m, mma_n, dtype == NB200_BF16, false, !b_kmajor);
   p.b_kmajor = b_kmajor ? 1 : 0;
   p.wide_a = wide_a ? 1 : 0;
+  p.group_m = tuning("gemm_group_m", 0) > 0 ? tuning("gemm_group_m", 0) : gemm::kGroupM;
   p.wide_b = wide_b ? 1 : 0;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * c_bytes) % 16 == 0) ? 1 : 0;
   p.wait_limit_ns = wait_limit_ns();

@@ -91,7 +91,7 @@ __device__ __forceinline__ void store_chunk(typename ElemType<DT>::T* crow, int 
 template <class A, class B> struct std_is_same { static constexpr bool value = false; };
 template <class A> struct std_is_same<A, A> { static constexpr bool value = true; };
 constexpr int kThreads = 192;
-constexpr int kGroupM = 8;      // row-blocks per L2 band of the tile order
+constexpr int kGroupM = 16;     // row-blocks per L2 band of the tile order
 
 // Time stamps of one CTA's roles, for development builds only (-DNB200_GEMM_TRACE; the shipped
 // library and the kernels compiled at run time have none of this).
@@ -124,6 +124,7 @@ struct GemmParams {
   // slab of the slot, or every column slab of B, at once.  Otherwise the maps are 2-D and the
   // slot is filled slab by slab, zero-filled at the ragged edges.
   int wide_a, wide_b;
+  int group_m;   // row-blocks per L2 band of the tile order
   unsigned long long wait_limit_ns;
   unsigned int* status;
 };
@@ -223,13 +224,13 @@ __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ld
   }
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int* mb,
-                                            int* nb) {
-  // bands of kGroupM row-blocks; inside a band, column-blocks advance slowest
-  const int band_tiles = kGroupM * n_blocks;
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int group_m,
+                                            int* mb, int* nb) {
+  // bands of group_m row-blocks; inside a band, column-blocks advance slowest
+  const int band_tiles = group_m * n_blocks;
   const int band = tile / band_tiles;
-  const int first_m = band * kGroupM;
-  const int rows = min(kGroupM, m_blocks - first_m);
+  const int first_m = band * group_m;
+  const int rows = min(group_m, m_blocks - first_m);
   const int in_band = tile - band * band_tiles;
   *mb = first_m + in_band % rows;
   *nb = in_band / rows;
@@ -302,7 +303,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mb, nb;
-        tile_coords(tile, p.m_blocks, p.n_blocks, &mb, &nb);
+        tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, &mb, &nb);
         for (int kb = 0; kb < k_rounds; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
           if (!ok) break;
@@ -410,7 +411,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       int mb, nb;
-      tile_coords(tile, p.m_blocks, p.n_blocks, &mb, &nb);
+      tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, &mb, &nb);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
@@ -525,7 +526,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       bool ok = true;
       for (int tile = first; tile < num_tiles && ok; tile += step) {
         int mb, nb;
-        tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
+        tile_coords(tile, m_blocks2, p.n_blocks, p.group_m, &mb, &nb);
         const int row0 = mb * 2 * kBlockM + rank * kBlockM;
         const int col0 = nb * BN + rank * 128;   // of the first MMA; the second is 256 further
         for (int kb = 0; kb < k_rounds; ++kb) {
@@ -598,12 +599,16 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       int it = 0;
       bool ok = true;
       for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
+        // Two accumulators of 256 columns take turns (NSUB = 1); the one 512-column accumulator
+        // of the wide tile is handed back in halves, acc_empty[h] for columns 256 h ..., so the
+        // first MMAs of the next tile start while the epilogue still drains the other half.
         const int buf = kAccBufs == 2 ? (it & 1) : 0;
         const uint32_t acc_phase = kAccBufs == 2 ? ((it >> 1) & 1) : (it & 1);
         ok = wait_all(&acc_empty_bar[buf], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * 256;
+        bool half1_free = NSUB == 1;
         for (int kb = 0; kb < k_rounds; ++kb) {
           ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
@@ -618,6 +623,12 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
             const uint64_t a_desc = with_address(kADesc, a_addr + sub * kABytes);
 #pragma unroll
             for (int h = 0; h < NSUB; ++h) {
+              if (NSUB == 2 && h == 1 && !half1_free) {
+                ok = wait_all(&acc_empty_bar[1], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
+                if (!ok) break;
+                tc_fence_after_sync();
+                half1_free = true;
+              }
               const uint32_t bh_addr = b_addr + h * KSUB * kBBytes;
               const uint64_t b_desc = b_kmajor ? with_address(kADesc, bh_addr + sub * kBBytes)
                                                : with_address(kBDesc, bh_addr + sub * kBSlab);
@@ -629,6 +640,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
                                   (kb | sub | kk) != 0 ? 1u : 0u);
             }
           }
+          if (!ok) break;
           // the slot is free in both CTAs once these MMAs retire
           if (elected) {
             mma_commit_pair(empty0 + stage * 8);
@@ -655,7 +667,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
     bool ok = true;
     for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
       int mb, nb;
-      tile_coords(tile, m_blocks2, p.n_blocks, &mb, &nb);
+      tile_coords(tile, m_blocks2, p.n_blocks, p.group_m, &mb, &nb);
       const int buf = kAccBufs == 2 ? (it & 1) : 0;
       const uint32_t acc_phase = kAccBufs == 2 ? ((it >> 1) & 1) : (it & 1);
       ok = mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
@@ -664,12 +676,24 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       tc_fence_after_sync();
       GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * 256;
-      drain_rows<BN, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
-                              nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),
-                              lane, ea);
+      if constexpr (NSUB == 2) {
+        drain_rows<256, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
+                                 nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),
+                                 lane, ea);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[0]), 0));
+        drain_rows<256, CT, EPI>(t_row + 256, p.c, p.ldc,
+                                 mb * 2 * kBlockM + rank * kBlockM + quarter * 32, nb * BN + 256, p.m,
+                                 p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128), lane, ea);
+      } else {
+        drain_rows<BN, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
+                                nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),
+                                lane, ea);
+      }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[buf]), 0));
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[NSUB == 2 ? 1 : buf]), 0));
       GTRACE(2, 4, threadIdx.x == 64)   // tile stored
     }
   }

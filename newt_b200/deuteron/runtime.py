@@ -204,7 +204,8 @@ class Kernel:
             say(config, f"{ms:.4f} ms")
             return ms
 
-        best, ms = tuning.Search(space, measure, plan_identity, samples=self.samples).run()
+        best, ms = tuning.Search(space, measure, plan_identity, samples=self.samples,
+                                 always=tuning.preferred(gen.tunable, gen.has_dot)).run()
         if best is None:
             raise RuntimeError(f"deuteron: no configuration of {self.__name__} both runs and matches "
                                f"its eager run (DEUTERON_VERBOSE=1 lists what was tried)")
