@@ -389,8 +389,8 @@ class MatmulWorkload(Workload):
                                  f"{self.M} (first, last, seeded draw), every column")
 
     def traffic_bytes(self):
-        # captured on the --small case (N = K = 4096) and scaled by operand bytes (x2.4)
-        return 2.4 * 221.4e6 if (self.M, self.N, self.K) == (8192, 8192, 8192) else None
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this very case
+        return 971.5e6 if (self.M, self.N, self.K) == (8192, 8192, 8192) else None
 
     def config(self, world):
         return {"workload": "bf16 matmul, one [8192,8192] block of A per GPU x B [8192,8192] "
