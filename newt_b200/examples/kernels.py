@@ -152,6 +152,7 @@ def layernorm(x, w, b, eps=1e-5, out=None):
 @newt.autotune(
     configs=[
         newt.Config({"BLOCK_M": 256, "BLOCK_N": 512, "BLOCK_K": 64}, num_warps=4, num_stages=4),
+        newt.Config({"BLOCK_M": 256, "BLOCK_N": 512, "BLOCK_K": 32}, num_warps=4, num_stages=4),   # fp32: one row of K
         newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 128}, num_warps=4, num_stages=3),
         newt.Config({"BLOCK_M": 256, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=6),
         newt.Config({"BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64}, num_warps=4, num_stages=4),
