@@ -65,6 +65,7 @@ int nb200_read_status(uint32_t* status, uint32_t* detail);
  *   "add_variant"      K0's walk: 1 persistent grid x4 loads, 2 chunks in address order x4
  *                      (the default), 3 chunks x8, 4 persistent x8
  *   "tf32_in_place"    0: nb200_gemm_tf32 always transposes B into its workspace
+ *   "gemm_group_m"     row-blocks per band of the GEMM tile order (L2 reuse of B columns; 16)
  *   "wait_limit_us"    how long one device-side wait (an mbarrier spin of the tensor-core
  *                      kernels) may last before the kernel gives up, records a code in the
  *                      status word and returns; 2 000 000 (2 s) when unset */
@@ -120,8 +121,10 @@ int nb200_layernorm(const void* x, const void* w, const void* b, void* out,
  * from the kernel's BLOCK_M/BLOCK_N/BLOCK_K constexprs, `stages` from
  * `num_stages` (depth of the TMA/mbarrier ring), `cta_pair` selects 2-CTA
  * tcgen05 (cluster of two CTAs sharing one 256-row MMA).  Zero fields mean
- * "library default": CTA pairs with 128-element K slots when the problem has
- * at least one 256x256 tile per pair of SMs, single-CTA 128xN tiles otherwise. */
+ * "library default": CTA pairs when the problem has at least one 256x256 tile
+ * per pair of SMs -- 256x512 tiles (two MMAs per K step, 64-element K slots) when
+ * the rounds those need over the resident pairs cost less than the rounds of
+ * 256x256 tiles (128-element K slots) do -- and single-CTA 128xN tiles otherwise. */
 typedef struct nb200_gemm_config {
   int32_t block_m; /* 128 (one CTA) or 256 (CTA pair)                        */
   int32_t block_n; /* 64, 128 or 256; a CTA pair takes 256 or 512            */
