@@ -66,6 +66,7 @@ int nb200_read_status(uint32_t* status, uint32_t* detail);
  *                      (the default), 3 chunks x8, 4 persistent x8
  *   "tf32_in_place"    0: nb200_gemm_tf32 always transposes B into its workspace
  *   "gemm_group_m"     row-blocks per band of the GEMM tile order (L2 reuse of B columns; 16)
+ *   "gemm_split_tail"  see nb200_gemm_split
  *   "wait_limit_us"    how long one device-side wait (an mbarrier spin of the tensor-core
  *                      kernels) may last before the kernel gives up, records a code in the
  *                      status word and returns; 2 000 000 (2 s) when unset */
@@ -183,6 +184,31 @@ int nb200_gemm_tf32(const void* a, const void* b, void* c, int64_t m, int64_t n,
 int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int64_t m, int64_t n,
                            int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
                            const nb200_gemm_config* config, void* stream);
+
+/* nb200_gemm / nb200_gemm_bt (b_transposed != 0) with a split tail.  The CTA-pair kernels hand
+ * tiles out whole, one per pair and round; when the last round would fill only part of the chip
+ * -- above all a small C with a long K: 1024 x 1024 x 16384 is 16 tiles for 74 pairs -- the
+ * tiles of that round are instead cut along K: their k steps, taken as one sequence, are divided
+ * into one equal range per pair, and a tile that ends up in several ranges is summed in fp32
+ * through `workspace` by whichever of its parts finishes last.  No part waits for another, and
+ * the sum is always taken in the same order, so results do not vary from run to run (they
+ * differ from the unsplit product by fp32 reassociation only).  The reference has no
+ * counterpart: its matmul_kernel (examples/04_matmul.py:16-45) owns one tile per program.
+ * `workspace`: 16-byte aligned device memory of at least
+ * nb200_gemm_split_workspace_bytes(m, n, k, dtype, config) bytes, the caller's; it must not be
+ * shared by launches that can overlap on the GPU.  The query returns 0 when the tiles of this
+ * problem stay whole: single-CTA tiles, a full last round, or a split that would cost more in
+ * partial sums than it saves in idle k steps (every square problem from 2048^3 up); with a null
+ * or smaller workspace the call is nb200_gemm / nb200_gemm_bt.  The call clears a few hundred
+ * bytes of counters at the start of the workspace on `stream` before the launch.  Knob
+ * "gemm_split_tail": 1 = split whenever every pair gets at least four k steps, negative =
+ * never, 0 = by the measured costs. */
+int64_t nb200_gemm_split_workspace_bytes(int64_t m, int64_t n, int64_t k, int dtype,
+                                         const nb200_gemm_config* config);
+int nb200_gemm_split(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                     int64_t lda, int64_t ldb, int64_t ldc, int dtype, int b_transposed,
+                     const nb200_gemm_config* config, void* workspace, int64_t workspace_bytes,
+                     void* stream);
 
 /* nb200_gemm / nb200_gemm_bt (b_transposed != 0) for fp16 or bf16 operands with C taking the
  * fp32 accumulator unrounded: C is float [M, N] with row stride ldc.  What a matmul with an

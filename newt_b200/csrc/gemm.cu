@@ -212,9 +212,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
   return cuda_check(cudaLaunchKernel(kern, dim3(grid), dim3(kThreads), args, smem, stream), "gemm launch");
 }
 
-// How many clusters of the pair kernel the device holds at once (asked once per device and
-// instance), never more than there are tiles.
-int pair_clusters(const void* kern, int smem, const GemmParams& p, int* clusters) {
+// How many clusters of a pair kernel the device holds at once (asked once per device and instance).
+int pair_capacity(const void* kern, int smem, int* clusters) {
   cudaLaunchConfig_t lc = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -228,6 +227,12 @@ int pair_clusters(const void* kern, int smem, const GemmParams& p, int* clusters
   lc.gridDim = dim3(2);
   if (int rc = cluster_capacity(kern, &lc, clusters)) return rc;
   if (*clusters < 1) return fail(NB200_E_CUDA, "gemm: the device cannot host a CTA pair");
+  return 0;
+}
+
+// The same, but never more than there are tiles: the grid of a launch whose tiles stay whole.
+int pair_clusters(const void* kern, int smem, const GemmParams& p, int* clusters) {
+  if (int rc = pair_capacity(kern, smem, clusters)) return rc;
   const long long tiles = (long long)cdiv64(p.m, 2 * kBlockM) * p.n_blocks;
   if (tiles < *clusters) *clusters = (int)tiles;
   return 0;
@@ -237,38 +242,40 @@ int pair_smem_bytes(int stages, int ksub, int nsub = 1) {
   return stages * ksub * (kBlockM * 128 + nsub * 128 * 128) + 1024 + (int)gemm::kEpilogueStageBytes;
 }
 
-template <int STAGES, int KSUB>
-int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype,
-                bool c_f32, cudaStream_t stream) {
-  const int smem = pair_smem_bytes(STAGES, KSUB);
-  const void* kern = NB200_PICK(gemm_pair_kernel, STAGES, KSUB);
-  if (int rc = prepare_kernel(kern, smem)) return rc;
-  int clusters = 0;
-  if (int rc = pair_clusters(kern, smem, p, &clusters)) return rc;
-  cudaLaunchConfig_t lc = {};
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  lc.blockDim = dim3(kThreads);
-  lc.dynamicSmemBytes = smem;
-  lc.stream = stream;
-  lc.attrs = attr;
-  lc.numAttrs = 1;
-  lc.gridDim = dim3(2 * clusters);
-  void* args[3] = {(void*)&ta, (void*)&tb, (void*)&p};
-  return cuda_check(cudaLaunchKernelExC(&lc, kern, args), "gemm pair launch");
+// The compiled instance of the pair kernels a resolved configuration runs on.
+struct PairInstance {
+  const void* kern;
+  int smem, ksub, nsub;
+};
+
+PairInstance pair_instance(const Resolved& cfg, int row_k, int dtype, bool c_f32) {
+  PairInstance r;
+  if (cfg.block_n == 512) {
+    r.nsub = 2;
+    r.ksub = cfg.block_k == 2 * row_k ? 2 : 1;
+    r.kern = r.ksub == 2 ? NB200_PICK(gemm_pair_wide_kernel, 2, 2) : NB200_PICK(gemm_pair_wide_kernel, 4, 1);
+    r.smem = pair_smem_bytes(r.ksub == 2 ? 2 : 4, r.ksub, 2);
+    return r;
+  }
+  r.nsub = 1;
+  int stages;
+  if (cfg.block_k == 2 * row_k) {
+    stages = 3, r.ksub = 2, r.kern = NB200_PICK(gemm_pair_kernel, 3, 2);
+  } else if (cfg.block_k == 3 * row_k) {
+    stages = 2, r.ksub = 3, r.kern = NB200_PICK(gemm_pair_kernel, 2, 3);
+  } else {
+    r.ksub = 1;
+    stages = cfg.stages == 4 || cfg.stages == 5 ? cfg.stages : 6;
+    r.kern = stages == 4 ? NB200_PICK(gemm_pair_kernel, 4, 1)
+           : stages == 5 ? NB200_PICK(gemm_pair_kernel, 5, 1)
+                         : NB200_PICK(gemm_pair_kernel, 6, 1);
+  }
+  r.smem = pair_smem_bytes(stages, r.ksub);
+  return r;
 }
 
-template <int STAGES, int KSUB>
-int launch_pair_wide(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int dtype,
-                bool c_f32, cudaStream_t stream) {
-  const int smem = pair_smem_bytes(STAGES, KSUB, 2);
-  const void* kern = NB200_PICK(gemm_pair_wide_kernel, STAGES, KSUB);
-  if (int rc = prepare_kernel(kern, smem)) return rc;
-  int clusters = 0;
-  if (int rc = pair_clusters(kern, smem, p, &clusters)) return rc;
+int launch_pair(const PairInstance& inst, const CUtensorMap& ta, const CUtensorMap& tb,
+                const GemmParams& p, int clusters, cudaStream_t stream) {
   cudaLaunchConfig_t lc = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -276,13 +283,42 @@ int launch_pair_wide(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPar
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   lc.blockDim = dim3(kThreads);
-  lc.dynamicSmemBytes = smem;
+  lc.dynamicSmemBytes = inst.smem;
   lc.stream = stream;
   lc.attrs = attr;
   lc.numAttrs = 1;
   lc.gridDim = dim3(2 * clusters);
   void* args[3] = {(void*)&ta, (void*)&tb, (void*)&p};
-  return cuda_check(cudaLaunchKernelExC(&lc, kern, args), "gemm pair launch");
+  return cuda_check(cudaLaunchKernelExC(&lc, inst.kern, args), "gemm pair launch");
+}
+
+// The split tail of a pair launch (GemmParams::sk_tiles): with `capacity` clusters resident and
+// `tiles` tiles of `k_rounds` ring slots each, how many of the last tiles are cut into equal
+// ranges of k rounds instead of being handed out whole.  Splitting saves the k rounds the idle
+// part of the chip would have sat through and costs the traffic of the partial sums, which the
+// last part of a tile reads back one after the other: measured on a B200, a k round of a
+// 256 x 256 tile takes ~0.38 us and the sums cost ~12 us + 2.6 us per part (twice that for the
+// 512-column tile).  So square problems keep their tiles whole (4096^3: 13 us saved, 20 us spent)
+// and small outputs with a long K are split (1024 x 1024 x 16384: 86 -> 59 us; 512 x 512 x 65536:
+// 297 -> 90 us).  Knob gemm_split_tail: 1 = split whenever every cluster gets four k rounds,
+// negative = never.
+int split_tail_tiles(long long tiles, int k_rounds, int capacity, int nsub) {
+  const int knob = tuning("gemm_split_tail", 0);
+  if (knob < 0 || capacity < 2) return 0;
+  const int rest = (int)(tiles % capacity);
+  if (rest == 0) return 0;
+  const long long units = (long long)rest * k_rounds;
+  if (units < 4LL * capacity) return 0;
+  if (knob > 0) return rest;
+  const long long saved = k_rounds - (units + capacity - 1) / capacity;
+  const long long parts = capacity / rest + 2;
+  return saved * 380 * nsub > 12000 + 2600 * parts * nsub ? rest : 0;
+}
+
+// Bytes of the workspace a split tail needs: 8 counters per split tile, then 2 slots per cluster.
+size_t split_counter_bytes(int sk_tiles) { return ((size_t)sk_tiles * 8 * 4 + 255) / 256 * 256; }
+size_t split_workspace_bytes(int sk_tiles, int capacity, int nsub) {
+  return split_counter_bytes(sk_tiles) + (size_t)2 * capacity * 256 * (256 * nsub) * 4;
 }
 
 }  // namespace
@@ -514,7 +550,8 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
 // C = A @ B with B given either as [K, N] (b_kmajor = false) or transposed as [N, K].
 int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
               int64_t ldb, int64_t ldc, int dtype, const nb200_gemm_config* config, bool b_kmajor,
-              cudaStream_t stream, bool c_f32 = false) {
+              cudaStream_t stream, bool c_f32 = false, void* split_ws = nullptr,
+              size_t split_ws_bytes = 0) {
   const int cb = (c_f32 || dtype == NB200_F32) ? 4 : 2;   // bytes per element of C
   PlannedGemm g;
   if (int rc = plan_gemm(a, b, c, m, n, k, lda, ldb, ldc, dtype, cb, config, b_kmajor, &g)) return rc;
@@ -525,17 +562,28 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   const Resolved& cfg = g.cfg;
   const GemmParams& p = g.p;
 
-  if (cfg.pair && cfg.block_n == 512)
-    return cfg.block_k == 2 * g.row_k ? launch_pair_wide<2, 2>(g.ta, g.tb, p, dtype, c_f32, stream)
-                                      : launch_pair_wide<4, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
   if (cfg.pair) {
-    if (cfg.block_k == 2 * g.row_k) return launch_pair<3, 2>(g.ta, g.tb, p, dtype, c_f32, stream);
-    if (cfg.block_k == 3 * g.row_k) return launch_pair<2, 3>(g.ta, g.tb, p, dtype, c_f32, stream);
-    switch (cfg.stages) {
-      case 4: return launch_pair<4, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
-      case 5: return launch_pair<5, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
-      default: return launch_pair<6, 1>(g.ta, g.tb, p, dtype, c_f32, stream);
+    const PairInstance inst = pair_instance(cfg, g.row_k, dtype, c_f32);
+    if (int rc = prepare_kernel(inst.kern, inst.smem)) return rc;
+    int capacity = 0;
+    if (int rc = pair_capacity(inst.kern, inst.smem, &capacity)) return rc;
+    const long long tiles = (long long)cdiv64(p.m, 2 * kBlockM) * p.n_blocks;
+    if (split_ws) {
+      const int k_rounds = (p.k_blocks + inst.ksub - 1) / inst.ksub;
+      const int sk = split_tail_tiles(tiles, k_rounds, capacity, inst.nsub);
+      if (sk > 0 && split_ws_bytes >= split_workspace_bytes(sk, capacity, inst.nsub) &&
+          (reinterpret_cast<uintptr_t>(split_ws) & 15) == 0) {
+        GemmParams q = p;
+        q.sk_tiles = sk;
+        q.sk_count = static_cast<unsigned int*>(split_ws);
+        q.sk_ws = reinterpret_cast<float*>(static_cast<char*>(split_ws) + split_counter_bytes(sk));
+        if (int rc = cuda_check(cudaMemsetAsync(split_ws, 0, split_counter_bytes(sk), stream),
+                                "gemm split-tail counters"))
+          return rc;
+        return launch_pair(inst, g.ta, g.tb, q, capacity, stream);
+      }
     }
+    return launch_pair(inst, g.ta, g.tb, p, (int)(tiles < capacity ? tiles : capacity), stream);
   }
   const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
   const int sms = device_info().sm_count;
@@ -659,6 +707,32 @@ extern "C" int nb200_gemm_bt(const void* a, const void* bt, void* c, int64_t m, 
                              const nb200_gemm_config* config, void* stream) {
   return gemm_impl(a, bt, c, m, n, k, lda, ldbt, ldc, dtype, config, true,
                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t nb200_gemm_split_workspace_bytes(int64_t m, int64_t n, int64_t k, int dtype,
+                                                    const nb200_gemm_config* config) {
+  if (dtype != NB200_F16 && dtype != NB200_BF16 && dtype != NB200_F32) return 0;
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  const int row_k = dtype == NB200_F32 ? 32 : 64;
+  Resolved cfg;
+  if (resolve_config(config, m, n, row_k, &cfg) != 0 || !cfg.pair) return 0;
+  const PairInstance inst = pair_instance(cfg, row_k, dtype, false);
+  int capacity = 0;
+  if (prepare_kernel(inst.kern, inst.smem) != 0 || pair_capacity(inst.kern, inst.smem, &capacity) != 0)
+    return 0;
+  const long long tiles = (long long)cdiv64(m, 2 * kBlockM) * cdiv64(n, cfg.block_n);
+  const int k_rounds = (int)cdiv64(cdiv64(k, row_k), inst.ksub);
+  const int sk = split_tail_tiles(tiles, k_rounds, capacity, inst.nsub);
+  return sk > 0 ? (int64_t)split_workspace_bytes(sk, capacity, inst.nsub) : 0;
+}
+
+extern "C" int nb200_gemm_split(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                                int64_t lda, int64_t ldb, int64_t ldc, int dtype, int b_transposed,
+                                const nb200_gemm_config* config, void* workspace,
+                                int64_t workspace_bytes, void* stream) {
+  return gemm_impl(a, b, c, m, n, k, lda, ldb, ldc, dtype, config, b_transposed != 0,
+                   static_cast<cudaStream_t>(stream), false, workspace,
+                   workspace_bytes > 0 ? (size_t)workspace_bytes : 0);
 }
 
 extern "C" int nb200_gemm_acc32(const void* a, const void* b, float* c, int64_t m, int64_t n,

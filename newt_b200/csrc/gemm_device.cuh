@@ -127,6 +127,13 @@ struct GemmParams {
   int group_m;   // row-blocks per L2 band of the tile order
   unsigned long long wait_limit_ns;
   unsigned int* status;
+  // Split tail (pair kernels): the last sk_tiles tiles are not handed out whole.  Their k rounds,
+  // taken as one sequence, are cut into one equal range per cluster, so the last round of a
+  // launch keeps every SM busy; a tile that ends up in several ranges is summed through sk_ws by
+  // whichever of its parts finishes last (see SplitTail).  0 = every tile whole.
+  int sk_tiles;
+  float* sk_ws;             // 2 slots per cluster, a slot = one fp32 accumulator tile
+  unsigned int* sk_count;   // 8 counters per split tile (CTA of the pair x epilogue warp), zero at launch
 };
 
 // What runs between the accumulator and the store.  `apply` gets 32 consecutive columns of one
@@ -143,6 +150,81 @@ struct NoEpilogue {
   static __device__ __forceinline__ void apply(float (&)[32], int, int, const Args&) {}
 };
 
+// The order in which a cluster works through a launch: its whole tiles (tile = cluster,
+// cluster + clusters, ... below dp_tiles), then its range of the split tail's k rounds, as
+// segments (tile, first k round, end k round).  The three roles of a CTA run the same sequence.
+struct SplitTail {
+  int dp_tiles, clusters, k_rounds;
+  long long units;     // sk_tiles * k_rounds
+  int next_tile;
+  long long u, u1;     // what is left of this cluster's range
+  int cluster;
+  int slot;            // of the last split segment handed out: where its partial sum goes
+
+  __device__ __forceinline__ SplitTail(const GemmParams& p, int num_tiles, int k_rounds_, int cluster_,
+                                       int clusters_)
+      : dp_tiles(num_tiles - p.sk_tiles), clusters(clusters_), k_rounds(k_rounds_),
+        units((long long)p.sk_tiles * k_rounds_), next_tile(cluster_), cluster(cluster_) {
+    u = range_start(cluster_);
+    u1 = range_start(cluster_ + 1);
+  }
+  __device__ __forceinline__ long long range_start(int c) const { return units * c / clusters; }
+  // the cluster whose range holds unit x
+  __device__ __forceinline__ int cluster_of(long long x) const {
+    return (int)(((x + 1) * clusters + units - 1) / units) - 1;
+  }
+  // Next segment; split = index of the tile inside the tail when the segment is only a part of
+  // its tile, else -1.
+  __device__ __forceinline__ bool next(int* tile, int* kb0, int* kb1, int* split) {
+    if (next_tile < dp_tiles) {
+      *tile = next_tile;
+      *kb0 = 0;
+      *kb1 = k_rounds;
+      *split = -1;
+      next_tile += clusters;
+      return true;
+    }
+    if (u >= u1) return false;
+    const int t = (int)(u / k_rounds);
+    const int b0 = (int)(u - (long long)t * k_rounds);
+    const long long left = u1 - u;
+    const int b1 = left < (long long)(k_rounds - b0) ? b0 + (int)left : k_rounds;
+    slot = 2 * cluster + (u != range_start(cluster) ? 1 : 0);
+    u += b1 - b0;
+    *tile = dp_tiles + t;
+    *kb0 = b0;
+    *kb1 = b1;
+    *split = (b0 == 0 && b1 == k_rounds) ? -1 : t;
+    return true;
+  }
+};
+
+// The parts of a split tile as one epilogue warp sees them: clusters c_lo..c_hi each hold one
+// (slot 2c, or 2c + 1 when the part is the second partial segment of its cluster, which only
+// c_lo's can be).  A slot is laid out [CTA][warp][column / 4][row] in 16-byte pieces, so a
+// warp's accesses are whole 512-byte runs.
+struct PartialSet {
+  const float* base;   // sk_ws + this warp's offset inside a slot (+ the column offset of a half);
+                       // null: the tile is whole and comes from tensor memory
+  long long slot_floats;
+  int c_lo, c_hi, lo_second;
+};
+
+template <int COLS>
+__device__ __forceinline__ void dump_rows(uint32_t t_row, float* dst, int lane) {
+#pragma unroll 1
+  for (int c0 = 0; c0 < COLS; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld_cols<32>(t_row + c0, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      __stcg(reinterpret_cast<float4*>(dst + ((c0 / 4 + j) * 32 + lane) * 4),
+             make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+  }
+}
+
 // The epilogue of one warp: its 32 rows (tensor-memory lanes) of a BN-column accumulator go
 // to C.  A thread holds one row, so storing from registers would write 16 bytes to each of 32
 // rows per instruction -- half-filled 32-byte sectors, which made the epilogue of a 128 x 256
@@ -155,7 +237,8 @@ constexpr uint32_t kEpilogueStageBytes = 4 * 32 * 128;   // four epilogue warps
 template <int BN, int CT, class EPI>
 __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ldc, int row0,
                                            int col_base, int m, int n, bool vec_ok, uint32_t stage,
-                                           int lane, const typename EPI::Args& ea) {
+                                           int lane, const typename EPI::Args& ea,
+                                           const PartialSet& ps = PartialSet{nullptr, 0, 0, -1, 0}) {
   using OutT = typename ElemType<CT>::T;
   constexpr int kPass = 128 / (int)sizeof(OutT);     // columns per pass
   constexpr int kPer16 = 16 / (int)sizeof(OutT);     // columns per 16-byte piece
@@ -165,8 +248,26 @@ __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ld
     const int col0 = col_base + c0;
     if (col0 >= n) break;   // uniform across the warp
     uint32_t r[kPass];
-    tmem_ld_cols<kPass>(t_row + c0, r);
-    tmem_ld_wait();
+    if (ps.base == nullptr) {
+      tmem_ld_cols<kPass>(t_row + c0, r);
+      tmem_ld_wait();
+    } else {   // a split tile: the sum of all its parts, always in the order of their clusters
+#pragma unroll
+      for (int j = 0; j < kPass; ++j) r[j] = 0u;
+      for (int pc = ps.c_lo; pc <= ps.c_hi; ++pc) {
+        const float* src = ps.base +
+                           (long long)(2 * pc + (pc == ps.c_lo ? ps.lo_second : 0)) * ps.slot_floats +
+                           ((c0 / 4) * 32 + lane) * 4;
+#pragma unroll
+        for (int j = 0; j < kPass / 4; ++j) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(src + j * 128));
+          r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+          r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+          r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+          r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+        }
+      }
+    }
     if constexpr (!std_is_same<EPI, NoEpilogue>::value) {
 #pragma unroll
       for (int q = 0; q < kPass / 32; ++q) {
@@ -524,12 +625,14 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = first; tile < num_tiles && ok; tile += step) {
+      SplitTail seq(p, num_tiles, k_rounds, first, step);
+      int tile, kb0, kb1, split;
+      while (ok && seq.next(&tile, &kb0, &kb1, &split)) {
         int mb, nb;
         tile_coords(tile, m_blocks2, p.n_blocks, p.group_m, &mb, &nb);
         const int row0 = mb * 2 * kBlockM + rank * kBlockM;
         const int col0 = nb * BN + rank * 128;   // of the first MMA; the second is 256 further
-        for (int kb = 0; kb < k_rounds; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, ctx, ST_WAIT_SMEM_EMPTY, tile);
           if (!ok) break;
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
@@ -598,7 +701,9 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
+      SplitTail seq(p, num_tiles, k_rounds, first, step);
+      int tile, kb0, kb1, split;
+      for (; ok && seq.next(&tile, &kb0, &kb1, &split); ++it) {
         // Two accumulators of 256 columns take turns (NSUB = 1); the one 512-column accumulator
         // of the wide tile is handed back in halves, acc_empty[h] for columns 256 h ..., so the
         // first MMAs of the next tile start while the epilogue still drains the other half.
@@ -609,7 +714,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * 256;
         bool half1_free = NSUB == 1;
-        for (int kb = 0; kb < k_rounds; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
           tc_fence_after_sync();
@@ -637,7 +742,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
                 if (elected)
                   mma_ss_pair<DT>(d_tmem + h * 256, a_desc + (uint64_t)(kk * 2),
                                   b_desc + (uint64_t)(kk * b_step), p.idesc,
-                                  (kb | sub | kk) != 0 ? 1u : 0u);
+                                  ((kb - kb0) | sub | kk) != 0 ? 1u : 0u);
             }
           }
           if (!ok) break;
@@ -665,7 +770,9 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
     const int quarter = warp & 3;
     int it = 0;
     bool ok = true;
-    for (int tile = first; tile < num_tiles && ok; tile += step, ++it) {
+    SplitTail seq(p, num_tiles, k_rounds, first, step);
+    int tile, kb0, kb1, split;
+    for (; ok && seq.next(&tile, &kb0, &kb1, &split); ++it) {
       int mb, nb;
       tile_coords(tile, m_blocks2, p.n_blocks, p.group_m, &mb, &nb);
       const int buf = kAccBufs == 2 ? (it & 1) : 0;
@@ -676,6 +783,39 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       tc_fence_after_sync();
       GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * 256;
+      if (split >= 0) {
+        // A part of a split tile: the fp32 partial sums go to this segment's slot and the
+        // accumulator is handed back at once.  The warp that finds the other parts of its 32 rows
+        // all written (a counter per tile, CTA and warp; nobody waits for anybody) adds them up
+        // in the order of their clusters and stores C.
+        constexpr long long kSlotFloats = 256LL * BN;
+        const long long warp_off = (long long)(rank * 4 + quarter) * (BN * 32);
+        dump_rows<BN>(t_row, p.sk_ws + seq.slot * kSlotFloats + warp_off, lane);
+        tc_fence_before_sync();
+        __threadfence();
+        __syncwarp();
+        unsigned int seen = 0;
+        if (lane == 0) {
+          if constexpr (NSUB == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[0]), 0));
+          mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[NSUB == 2 ? 1 : buf]), 0));
+          seen = atomicAdd(&p.sk_count[(split * 2 + (int)rank) * 4 + quarter], 1u);
+        }
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        const long long t0 = (long long)split * k_rounds;
+        const int c_lo = seq.cluster_of(t0), c_hi = seq.cluster_of(t0 + k_rounds - 1);
+        if ((int)seen == c_hi - c_lo) {
+          __threadfence();
+          const int row0 = mb * 2 * kBlockM + rank * kBlockM + quarter * 32;
+#pragma unroll
+          for (int h = 0; h < NSUB; ++h) {
+            const PartialSet ps{p.sk_ws + warp_off + h * (256 * 32), kSlotFloats, c_lo, c_hi,
+                                seq.range_start(c_lo) < t0 ? 1 : 0};
+            drain_rows<256, CT, EPI>(t_row, p.c, p.ldc, row0, nb * BN + h * 256, p.m, p.n,
+                                     p.c_vec_ok != 0, epi_stage + quarter * (32 * 128), lane, ea, ps);
+          }
+        }
+        continue;
+      }
       if constexpr (NSUB == 2) {
         drain_rows<256, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
                                  nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),

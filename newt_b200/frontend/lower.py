@@ -886,6 +886,9 @@ class GemmPlan(Plan):
             # tensor core wants anyway
             if acc32 is not None and self.row_k != 32:
                 kernels.gemm_acc32(a, b, c, m, n, k, lda, inner[self.b], ldc, True, self.config())
+            elif self._split_bytes(kernels, m, n, k, a.dtype):
+                kernels.gemm_split(a, b, c, m, n, k, lda, inner[self.b], ldc, self.config(), True,
+                                   self._split_bytes(kernels, m, n, k, a.dtype))
             else:
                 kernels.gemm_bt(a, b, c, m, n, k, lda, inner[self.b], ldc, self.config())
                 remember(abi.load().nb200_gemm_bt, a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k,
@@ -896,11 +899,27 @@ class GemmPlan(Plan):
             self.repitched += 1
         if acc32 is not None and self.row_k != 32:
             kernels.gemm_acc32(a, b, c, m, n, k, lda, ldb, ldc, False, self.config())
+        elif self._split_bytes(kernels, m, n, k, a.dtype):
+            kernels.gemm_split(a, b, c, m, n, k, lda, ldb, ldc, self.config(), False,
+                               self._split_bytes(kernels, m, n, k, a.dtype))
         else:
             kernels.gemm(a, b, c, m, n, k, lda, ldb, ldc, self.config())
             remember(abi.load().nb200_gemm, a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, lda,
                      ldb, ldc, abi.dtype_code(a.dtype), ctypes.byref(self.config()))
 
+    def _split_bytes(self, kernels, m, n, k, dtype):
+        """Workspace with which the library cuts the last round of tiles along K (a small C with
+        a long K), 0 when this problem's tiles stay whole; asked once per shape."""
+        if self._split is None:
+            self._split = {}
+        need = self._split.get((m, n, k))
+        if need is None:
+            if len(self._split) >= 256:
+                self._split.clear()
+            need = self._split[(m, n, k)] = kernels.gemm_split_bytes(m, n, k, dtype, self.config())
+        return need
+
+    _split = None
     repitched = 0       # how many operands launches of this plan had to copy first
     _scalars = None     # names of the scalar arguments, found at the first launch
 

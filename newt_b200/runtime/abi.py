@@ -72,6 +72,11 @@ SIGNATURES = {
                                               ctypes.POINTER(GemmConfig), _vp]),
     "nb200_gemm_acc32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                         ctypes.c_int, ctypes.c_int, ctypes.POINTER(GemmConfig), _vp]),
+    "nb200_gemm_split_workspace_bytes": (ctypes.c_int64, [_i64, _i64, _i64, ctypes.c_int,
+                                                          ctypes.POINTER(GemmConfig)]),
+    "nb200_gemm_split": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
+                                        ctypes.c_int, ctypes.c_int, ctypes.POINTER(GemmConfig), _vp,
+                                        _i64, _vp]),
     "nb200_gemm_params_bytes": (ctypes.c_int64, []),
     "nb200_gemm_plan": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int,
                                        ctypes.c_int, ctypes.c_int, ctypes.POINTER(GemmConfig), _vp, _vp,

@@ -102,6 +102,31 @@ def gemm_bt(a, bt, c, m, n, k, lda, ldbt, ldc, config=None):
                                        abi.dtype_code(a.dtype), cfg, _stream()))
 
 
+def gemm_split_bytes(m, n, k, dtype, config=None):
+    """Bytes of workspace with which `gemm_split` cuts the last round of tiles along K; 0 when the
+    tiles of this problem stay whole."""
+    cfg = ctypes.byref(config) if config is not None else None
+    return int(abi.load().nb200_gemm_split_workspace_bytes(int(m), int(n), int(k),
+                                                           abi.dtype_code(dtype), cfg))
+
+
+def gemm_split(a, b, c, m, n, k, lda, ldb, ldc, config=None, b_transposed=False, need=None):
+    """`gemm` / `gemm_bt` with a split tail (nb200_gemm_split): when the last round of whole tiles
+    would leave part of the chip idle, its tiles are cut along K and summed through a workspace,
+    a fresh tensor of torch's caching allocator (allocated and used on the current stream).
+    `need`: the workspace size if the caller has asked for it before."""
+    if need is None:
+        need = gemm_split_bytes(m, n, k, a.dtype, config)
+    if need == 0:
+        return (gemm_bt if b_transposed else gemm)(a, b, c, m, n, k, lda, ldb, ldc, config)
+    ws = torch.empty(need, dtype=torch.uint8, device=a.device)
+    cfg = ctypes.byref(config) if config is not None else None
+    abi.check(abi.load().nb200_gemm_split(_dev_ptr("a", a), _dev_ptr("b", b), _dev_ptr("c", c), int(m),
+                                          int(n), int(k), int(lda), int(ldb), int(ldc),
+                                          abi.dtype_code(a.dtype), 1 if b_transposed else 0, cfg,
+                                          ctypes.c_void_p(ws.data_ptr()), need, _stream()))
+
+
 def gemm_tf32(a, b, c, m, n, k, lda, ldb, ldc, config=None):
     """fp32 C = A @ B (tf32 product, fp32 accumulation) with B as [K, N].  A B whose base and
     pitch are 16-byte aligned is read in place; any other is transposed into a workspace first,

@@ -9,7 +9,7 @@ import torch
 import newt_b200 as newt
 import newt_b200.deuteron as dt
 import newt_b200.language as nl
-from newt_b200.runtime import abi
+from newt_b200.runtime import abi, kernels
 from oracle import cport, torch_ref
 
 import ref_kernels as rk
@@ -127,6 +127,27 @@ def test_matmul_bf16_and_tiles():
         a, b, c = _run_matmul(rk.matmul_kernel, 256, 512, 192, torch.bfloat16, bm=128, bn=bn,
                               bk=64, num_stages=stages)
         assert torch_ref.rel_frobenius(c.float(), torch_ref.matmul(a, b)) <= 1e-2
+
+
+def test_matmul_small_c_long_k_splits_the_tiles():
+    # 16 tiles of 256 x 256 for 74 CTA pairs, 256 k steps each: the launcher asks the library,
+    # which cuts the tiles along K and sums the parts through a workspace of the launch's own
+    m = n = 1024
+    k = 16384
+    calls = []
+    real = kernels.gemm_split
+
+    def spy(*args, **kw):
+        calls.append(args[3:6])
+        return real(*args, **kw)
+
+    kernels.gemm_split = spy
+    try:
+        a, b, c = _run_matmul(rk.matmul_kernel, m, n, k, torch.float16, bm=256, bn=256, bk=64)
+    finally:
+        kernels.gemm_split = real
+    assert calls == [(m, n, k)]
+    assert torch_ref.rel_frobenius(c.float(), torch_ref.matmul(a, b)) <= 1e-2
 
 
 def test_matmul_unmasked_kernel():

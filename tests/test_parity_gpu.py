@@ -368,6 +368,72 @@ def test_gemm_wide_pair_vs_oracle(dtype, block_k, transposed, m, n, k):
     assert torch_ref.rel_frobenius(got, a.double() @ b.double()) <= tol
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("block_n,block_k", [(256, 1), (256, 2), (512, 1), (512, 2)])   # block_k in 128-byte rows
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 40960), (700, 1000, 4104), (1024, 1024, 2048), (2560, 2304, 2048)])
+def test_gemm_split_tail_vs_oracle(dtype, block_n, block_k, transposed, m, n, k):
+    """The last round of tiles cut along K and summed through the workspace: one tile over all
+    pairs, ragged extents, a round of whole tiles before the split ones, both tile widths, B
+    either way round; the same call twice gives the same bits."""
+    g = torch.Generator().manual_seed(m * 7 + n * 5 + k + block_n + block_k)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype)
+    b = torch.randn(k, n, generator=g).to(dtype)
+    np_ = (n + 7) // 8 * 8
+    row_k = 32 if dtype == torch.float32 else 64
+    cfg = kernels.gemm_config(block_m=256, block_n=block_n, block_k=block_k * row_k, cta_pair=1)
+    ad = a.cuda()
+    bd = b.t().contiguous().cuda() if transposed else torch.zeros(k, np_, dtype=dtype, device="cuda")[:, :n].copy_(b)
+    ldb = k if transposed else np_
+    abi.set_tuning("gemm_split_tail", 1)
+    try:
+        need = kernels.gemm_split_bytes(m, n, k, dtype, cfg)
+        if need == 0:
+            pytest.skip("every pair would get fewer than four k steps")
+        outs = []
+        for _ in range(2):
+            c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+            kernels.gemm_split(ad, bd, c, m, n, k, k, ldb, n, cfg, transposed, need)
+            torch.cuda.synchronize()
+            assert abi.read_status() == (0, 0)
+            outs.append(c)
+    finally:
+        abi.set_tuning("gemm_split_tail", 0)
+    assert torch.equal(outs[0], outs[1])
+    got = outs[0].cpu().double()
+    assert not torch.isnan(got).any()
+    tol = 2e-3 if dtype == torch.float32 else 1e-2
+    assert torch_ref.rel_frobenius(got, a.double() @ b.double()) <= tol
+
+
+def test_gemm_split_tail_rule_and_small_workspace():
+    """Square problems keep their tiles whole, a small C with a long K is split; a workspace that
+    is too small means the unsplit product, not an error."""
+    assert kernels.gemm_split_bytes(4096, 4096, 4096, torch.bfloat16) == 0
+    assert kernels.gemm_split_bytes(8192, 8192, 8192, torch.bfloat16) == 0
+    assert kernels.gemm_split_bytes(1024, 1024, 1024, torch.float16) == 0
+    cfg = kernels.gemm_config(block_m=256, block_n=256, block_k=64, cta_pair=1)
+    m, n, k = 1024, 1024, 16384
+    need = kernels.gemm_split_bytes(m, n, k, torch.bfloat16, cfg)
+    assert need > 0
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = (torch.randn(m, k, device="cuda", generator=g) / k ** 0.5).bfloat16()
+    b = torch.randn(k, n, device="cuda", generator=g).bfloat16()
+    whole, split, starved = (torch.empty(m, n, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    kernels.gemm(a, b, whole, m, n, k, k, n, n, cfg)
+    kernels.gemm_split(a, b, split, m, n, k, k, n, n, cfg)
+    ws = torch.empty(4096, dtype=torch.uint8, device="cuda")
+    abi.check(abi.load().nb200_gemm_split(a.data_ptr(), b.data_ptr(), starved.data_ptr(), m, n, k, k, n, n,
+                                          abi.dtype_code(a.dtype), 0, ctypes.byref(cfg), ws.data_ptr(),
+                                          ws.numel(), kernels.raw_stream()))
+    torch.cuda.synchronize()
+    assert abi.read_status() == (0, 0)
+    assert torch.equal(starved, whole)
+    ref = a.float() @ b.float()
+    assert torch_ref.rel_frobenius(split.float().cpu(), ref.cpu()) <= 1e-2
+    assert (split.float() - whole.float()).abs().max().item() <= 0.05
+
+
 def test_gemm_linearity_at_full_size():
     # size-independent property at the benchmark size: (A1 + A2) @ B == A1 @ B + A2 @ B
     # up to rounding, and a spot-checked block against the fp32 oracle
