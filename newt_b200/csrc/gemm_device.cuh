@@ -129,11 +129,10 @@ struct GemmParams {
   unsigned int* status;
   // Split tail (pair kernels): the last sk_tiles tiles are not handed out whole.  Their k rounds,
   // taken as one sequence, are cut into one equal range per cluster, so the last round of a
-  // launch keeps every SM busy; a tile that ends up in several ranges is summed through sk_ws by
-  // whichever of its parts finishes last (see SplitTail).  0 = every tile whole.
+  // launch keeps every SM busy; a part of a tile leaves its fp32 partial sums in sk_ws and a
+  // second kernel adds the parts up (see SplitTail).  0 = every tile whole.
   int sk_tiles;
   float* sk_ws;             // 2 slots per cluster, a slot = one fp32 accumulator tile
-  unsigned int* sk_count;   // 8 counters per split tile (CTA of the pair x epilogue warp), zero at launch
 };
 
 // What runs between the accumulator and the store.  `apply` gets 32 consecutive columns of one
@@ -199,17 +198,8 @@ struct SplitTail {
   }
 };
 
-// The parts of a split tile as one epilogue warp sees them: clusters c_lo..c_hi each hold one
-// (slot 2c, or 2c + 1 when the part is the second partial segment of its cluster, which only
-// c_lo's can be).  A slot is laid out [CTA][warp][column / 4][row] in 16-byte pieces, so a
-// warp's accesses are whole 512-byte runs.
-struct PartialSet {
-  const float* base;   // sk_ws + this warp's offset inside a slot (+ the column offset of a half);
-                       // null: the tile is whole and comes from tensor memory
-  long long slot_floats;
-  int c_lo, c_hi, lo_second;
-};
-
+// A slot of the workspace is laid out [CTA of the pair][epilogue warp][column / 4][row] in
+// 16-byte pieces, so a warp's accesses are whole 512-byte runs.
 template <int COLS>
 __device__ __forceinline__ void dump_rows(uint32_t t_row, float* dst, int lane) {
 #pragma unroll 1
@@ -237,8 +227,7 @@ constexpr uint32_t kEpilogueStageBytes = 4 * 32 * 128;   // four epilogue warps
 template <int BN, int CT, class EPI>
 __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ldc, int row0,
                                            int col_base, int m, int n, bool vec_ok, uint32_t stage,
-                                           int lane, const typename EPI::Args& ea,
-                                           const PartialSet& ps = PartialSet{nullptr, 0, 0, -1, 0}) {
+                                           int lane, const typename EPI::Args& ea) {
   using OutT = typename ElemType<CT>::T;
   constexpr int kPass = 128 / (int)sizeof(OutT);     // columns per pass
   constexpr int kPer16 = 16 / (int)sizeof(OutT);     // columns per 16-byte piece
@@ -248,26 +237,8 @@ __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ld
     const int col0 = col_base + c0;
     if (col0 >= n) break;   // uniform across the warp
     uint32_t r[kPass];
-    if (ps.base == nullptr) {
-      tmem_ld_cols<kPass>(t_row + c0, r);
-      tmem_ld_wait();
-    } else {   // a split tile: the sum of all its parts, always in the order of their clusters
-#pragma unroll
-      for (int j = 0; j < kPass; ++j) r[j] = 0u;
-      for (int pc = ps.c_lo; pc <= ps.c_hi; ++pc) {
-        const float* src = ps.base +
-                           (long long)(2 * pc + (pc == ps.c_lo ? ps.lo_second : 0)) * ps.slot_floats +
-                           ((c0 / 4) * 32 + lane) * 4;
-#pragma unroll
-        for (int j = 0; j < kPass / 4; ++j) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(src + j * 128));
-          r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
-          r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
-          r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
-          r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
-        }
-      }
-    }
+    tmem_ld_cols<kPass>(t_row + c0, r);
+    tmem_ld_wait();
     if constexpr (!std_is_same<EPI, NoEpilogue>::value) {
 #pragma unroll
       for (int q = 0; q < kPass / 32; ++q) {
@@ -784,35 +755,15 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * 256;
       if (split >= 0) {
-        // A part of a split tile: the fp32 partial sums go to this segment's slot and the
-        // accumulator is handed back at once.  The warp that finds the other parts of its 32 rows
-        // all written (a counter per tile, CTA and warp; nobody waits for anybody) adds them up
-        // in the order of their clusters and stores C.
-        constexpr long long kSlotFloats = 256LL * BN;
-        const long long warp_off = (long long)(rank * 4 + quarter) * (BN * 32);
-        dump_rows<BN>(t_row, p.sk_ws + seq.slot * kSlotFloats + warp_off, lane);
+        // A part of a split tile: its fp32 partial sums go to this segment's slot and the
+        // accumulator is handed back; split_reduce_kernel adds the parts up after this kernel.
+        dump_rows<BN>(t_row, p.sk_ws + seq.slot * (256LL * BN) + (long long)(rank * 4 + quarter) * (BN * 32),
+                      lane);
         tc_fence_before_sync();
-        __threadfence();
         __syncwarp();
-        unsigned int seen = 0;
         if (lane == 0) {
           if constexpr (NSUB == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[0]), 0));
           mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[NSUB == 2 ? 1 : buf]), 0));
-          seen = atomicAdd(&p.sk_count[(split * 2 + (int)rank) * 4 + quarter], 1u);
-        }
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        const long long t0 = (long long)split * k_rounds;
-        const int c_lo = seq.cluster_of(t0), c_hi = seq.cluster_of(t0 + k_rounds - 1);
-        if ((int)seen == c_hi - c_lo) {
-          __threadfence();
-          const int row0 = mb * 2 * kBlockM + rank * kBlockM + quarter * 32;
-#pragma unroll
-          for (int h = 0; h < NSUB; ++h) {
-            const PartialSet ps{p.sk_ws + warp_off + h * (256 * 32), kSlotFloats, c_lo, c_hi,
-                                seq.range_start(c_lo) < t0 ? 1 : 0};
-            drain_rows<256, CT, EPI>(t_row, p.c, p.ldc, row0, nb * BN + h * 256, p.m, p.n,
-                                     p.c_vec_ok != 0, epi_stage + quarter * (32 * 128), lane, ea, ps);
-          }
         }
         continue;
       }

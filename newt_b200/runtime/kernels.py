@@ -2,8 +2,9 @@
 torch's current stream.  These are what the lowering plans of the JIT front end
 call; they add nothing to the arithmetic.  Like the reference launcher
 (newt/runtime/jit.py:190-223) they refuse tensors that are not on the current
-CUDA device.  Three of them need scratch memory beside the caller's tensors (the transposed
-copy of an fp32 B, a re-pitched copy of an operand bulk tensor copies cannot fetch): they take it
+CUDA device.  Some need scratch memory beside the caller's tensors (the transposed copy of an
+fp32 B, a re-pitched copy of an operand bulk tensor copies cannot fetch, the partial sums of
+tiles that were cut along K): they take it
 from torch's caching allocator per launch, on the current stream, so launches on different
 streams never share a buffer; the others never allocate.
 """
