@@ -135,18 +135,22 @@ struct GemmParams {
   float* sk_ws;             // 2 slots per cluster, a slot = one fp32 accumulator tile
 };
 
-// What runs between the accumulator and the store.  `apply` gets 32 consecutive columns of one
-// row of the fp32 accumulator (row `row`, columns `col0`..`col0 + 31` of C; entries past the
-// matrix edge are never stored) and may change them in place: a bias, an activation, a
-// scaling -- the code a kernel has after its k loop (newt/compiler/codegen.py:1854-1871 keeps it
-// in the same kernel too).  The plain product uses NoEpilogue; kernels compiled at run time
-// bring their own functor and its argument struct.
+// What runs between the accumulator and the store, in two steps.  `fetch` gets the row and
+// the first of 32 consecutive columns and reads whatever else the code needs there (a bias, a
+// residual) into a `Staged`; it runs while the accumulator's read from tensor memory is in
+// flight.  `apply` then gets those 32 columns of one row of the fp32 accumulator (row `row`,
+// columns `col0`..`col0 + 31` of C; entries past the matrix edge are never stored) and may
+// change them in place: a bias, an activation, a scaling -- the code a kernel has after its k
+// loop (newt/compiler/codegen.py:1854-1871 keeps it in the same kernel too).  The plain product
+// uses NoEpilogue; kernels compiled at run time bring their own functor and its argument struct.
 struct NoEpilogueArgs {
   int unused;
 };
 struct NoEpilogue {
   using Args = NoEpilogueArgs;
-  static __device__ __forceinline__ void apply(float (&)[32], int, int, const Args&) {}
+  struct Staged {};
+  static __device__ __forceinline__ void fetch(Staged&, int, int, const Args&) {}
+  static __device__ __forceinline__ void apply(float (&)[32], const Staged&, int, int, const Args&) {}
 };
 
 // The order in which a cluster works through a launch: its whole tiles (tile = cluster,
@@ -238,6 +242,11 @@ __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ld
     if (col0 >= n) break;   // uniform across the warp
     uint32_t r[kPass];
     tmem_ld_cols<kPass>(t_row + c0, r);
+    typename EPI::Staged staged[kPass / 32];
+    if constexpr (!std_is_same<EPI, NoEpilogue>::value) {
+#pragma unroll
+      for (int q = 0; q < kPass / 32; ++q) EPI::fetch(staged[q], row, col0 + q * 32, ea);
+    }
     tmem_ld_wait();
     if constexpr (!std_is_same<EPI, NoEpilogue>::value) {
 #pragma unroll
@@ -245,7 +254,7 @@ __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ld
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[q * 32 + j]);
-        EPI::apply(v, row, col0 + q * 32, ea);
+        EPI::apply(v, staged[q], row, col0 + q * 32, ea);
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[q * 32 + j] = __float_as_uint(v[j]);
       }

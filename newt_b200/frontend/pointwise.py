@@ -1711,35 +1711,93 @@ def generate_epilogue(trace, accumulator, store, block, axes):
     body = _Body(ctx)
     dims = ("nb_i", "nb_j")
     elem = ptr.dtype.element
-    out = _convert(_emit(body, value, _operand_dims(ptr.shape, dims, value.shape)), value.dtype, elem)
+    # The kernel's epilogue rounds the fp32 value it gets back to C's type (round to nearest, two
+    # elements per instruction), so a program's own final rounding of an fp32 value to that type
+    # is left to it: float -> 16-bit -> float -> 16-bit gives the same bits as float -> 16-bit.
+    if (value.op == "cast" and value.dtype == elem and elem in (tp.float16, tp.bfloat16)
+            and value.args[0].dtype == tp.float32 and value.args[0].shape == value.shape):
+        value = value.args[0]
+    out = _convert(_emit(body, value, _operand_dims(ptr.shape, dims, value.shape)), value.dtype,
+                   tp.float32 if value.dtype == tp.float32 else elem)
     if ctx.arrays or ctx.helpers:
         raise Unsupported("the code after the k loop needs shared memory or helper routines")
     params = [(name, node.dtype) for name, node in trace.params.items()]
     fields = "\n".join(f"    {t.ctype} {name};" for name, t in params)
     unpack = "\n".join(f"    {t.ctype} const {name} = nb_a.{name}; (void){name};" if isinstance(t, tp.pointer_type)
                        else f"    const {t.ctype} {name} = nb_a.{name}; (void){name};" for name, t in params)
-    lines = "\n".join("      " + ln for ln in body.lines)
+    early, late, staged = _split_epilogue(body.lines, out)
     bm, bn = block
+    index = (f"    const int nb_pid_m = nb_row / {bm}, nb_i = nb_row % {bm}; (void)nb_pid_m; (void)nb_i;\n"
+             "#pragma unroll\n"
+             "    for (int nb_k = 0; nb_k < 32; ++nb_k) {\n"
+             "      const int nb_col = nb_col0 + nb_k;\n"
+             f"      const int nb_pid_n = nb_col / {bn}, nb_j = nb_col % {bn}; (void)nb_pid_n; (void)nb_j;\n")
+    members = "\n".join(f"    {ctype} {name}[32];" for name, ctype in staged)
+    keep = "\n".join(f"      nb_s.{name}[nb_k] = {name};" for name, _ in staged)
+    take = "\n".join(f"      const {ctype} {name} = nb_s.{name}[nb_k];" for name, ctype in staged)
+    indent = lambda lines: "\n".join("      " + ln for ln in lines)  # noqa: E731
     text = f"""
 struct NbEpilogue {{
   struct Args {{
 {fields}
   }};
-  static __device__ __forceinline__ void apply(float (&nb_v)[32], int nb_row, int nb_col0, const Args& nb_a) {{
+  struct Staged {{
+{members}
+  }};
+  // what the code reads besides the accumulator: issued while the accumulator is on its way
+  static __device__ __forceinline__ void fetch(Staged& nb_s, int nb_row, int nb_col0, const Args& nb_a) {{
 {unpack}
-    const int nb_pid_m = nb_row / {bm}, nb_i = nb_row % {bm};
-#pragma unroll
-    for (int nb_k = 0; nb_k < 32; ++nb_k) {{
-      const int nb_col = nb_col0 + nb_k;
-      const int nb_pid_n = nb_col / {bn}, nb_j = nb_col % {bn};
-      const float nb_acc = nb_v[nb_k];
-{lines}
+{index}{indent(early)}
+{keep}
+    }}
+  }}
+  static __device__ __forceinline__ void apply(float (&nb_v)[32], const Staged& nb_s, int nb_row, int nb_col0,
+                                               const Args& nb_a) {{
+{unpack}
+{index}      const float nb_acc = nb_v[nb_k];
+{take}
+{indent(late)}
       nb_v[nb_k] = (float)({out});
     }}
   }}
 }};
 """
     return text, params
+
+
+_DECLARATION = re.compile(r"^(?P<type>(?:const\s+)?[A-Za-z_][\w:<>, ]*?(?:\s*\*)?)\s*(?:const\s+)?(?P<name>[A-Za-z_]\w*) = (?P<expr>.*);$")
+_WORD = re.compile(r"[A-Za-z_]\w*")
+
+
+def _split_epilogue(lines, out):
+    """The straight-line body of an epilogue in two parts: the statements that do not depend on
+    the accumulator (index arithmetic, the loads of a bias or a residual) and the rest.  Returns
+    (early lines, late lines, [(name, C type)] of the early values the late part or the result
+    uses).  A body with anything but plain declarations stays whole, as the late part."""
+    parsed = []
+    for ln in lines:
+        m = _DECLARATION.match(ln.strip())
+        if m is None:
+            return [], list(lines), []
+        parsed.append((ln.strip(), m.group("type").strip(), m.group("name"), set(_WORD.findall(m.group("expr")))))
+    late_names = {"nb_acc"}
+    early, late = [], []
+    for ln, ctype, name, used in parsed:
+        if used & late_names:
+            late_names.add(name)
+            late.append((ln, used))
+        else:
+            early.append((ln, ctype, name))
+    wanted = set(_WORD.findall(out))
+    for _, used in late:
+        wanted |= used
+    staged = []
+    for ln, ctype, name in early:
+        if name in wanted:
+            if "*" in ctype:      # a pointer the late part dereferences: keep the body whole
+                return [], list(lines), []
+            staged.append((name, ctype[len("const "):].strip() if ctype.startswith("const ") else ctype))
+    return [ln for ln, _, _ in early], [ln for ln, _ in late], staged
 
 
 def struct_type(params):

@@ -393,6 +393,11 @@ def test_matmul_epilogue_is_compiled_into_the_tensor_core_kernel():
     assert "struct NbEpilogue" in plan.fused_source and "fmaxf(" in plan.fused_source
     assert "nb_pid_n" in plan.fused_source and "blockIdx" not in plan.fused_source
     assert plan.hardware_key()[-1] == "fused"
+    # two steps: the bias is read in `fetch` (nothing there touches the accumulator), `apply`
+    # does the arithmetic and leaves the one rounding to bf16 to the kernel's packed conversion
+    fetch, apply = plan.fused_source.split("static __device__ __forceinline__ void apply(")
+    assert "*v" in fetch and "nb_acc" not in fetch.split("void fetch(")[1]
+    assert "nb_acc" in apply and "*v" not in apply and "__float2bfloat16_rn" not in apply
     for launch in (abi.GemmLaunch(pair=1, block_n=256, stages=7, ksub=1),
                    abi.GemmLaunch(pair=0, block_n=128, stages=4, ksub=1)):
         kernel = plan._fused_kernel(launch, abi.BF16, abi.BF16)
