@@ -186,23 +186,26 @@ int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int64_t m, int
                            const nb200_gemm_config* config, void* stream);
 
 /* nb200_gemm / nb200_gemm_bt (b_transposed != 0) with a split tail.  The CTA-pair kernels hand
- * tiles out whole, one per pair and round; when the last round would fill only part of the chip
- * -- above all a small C with a long K: 1024 x 1024 x 16384 is 16 tiles for 74 pairs -- the
- * tiles of that round are instead cut along K: their k steps, taken as one sequence, are divided
- * into one equal range per pair, a part of a tile leaves its fp32 partial sums in `workspace`,
- * and a second kernel on the same stream adds the parts of each tile and stores C.  The parts are
- * always added in the same order, so results do not vary from run to run (they differ from the
- * unsplit product by fp32 reassociation only).  Measured on a B200, bf16: 1024 x 1024 x 16384
- * 84 -> 46 us, 512 x 512 x 65536 297 -> 56 us, 256 x 256 x 65536 299 -> 34 us.  The reference has
- * no counterpart: its matmul_kernel (examples/04_matmul.py:16-45) owns one tile per program.
+ * tiles out whole, one per pair and round; when the last round would fill at most half of the
+ * chip -- above all a small C with a long K: 1024 x 1024 x 16384 is 16 tiles for 74 pairs -- the
+ * tiles of that round are instead cut along K into as many equal parts as there are pairs per
+ * tile (the same stretches of K for every tile, so pairs that read the same rows of A or columns
+ * of B run side by side and share them in L2), a part leaves its fp32 partial sums in
+ * `workspace`, and a second kernel on the same stream adds the parts of each tile and stores C.
+ * The parts are always added in the same order, so results do not vary from run to run (they
+ * differ from the unsplit product by fp32 reassociation only).  Measured on a B200, bf16, whole
+ * tiles -> split / torch.matmul, us: 1024 x 1024 x 16384  84 -> 44 / 43;  512 x 512 x 65536
+ * 297 -> 48 / 56;  256 x 256 x 65536  297 -> 32 / 38;  4096^3 in 256 x 256 tiles  96 -> 93 / 94.
+ * The reference has no counterpart: its matmul_kernel (examples/04_matmul.py:16-45) owns one
+ * tile per program.
  * `workspace`: 16-byte aligned device memory of at least
  * nb200_gemm_split_workspace_bytes(m, n, k, dtype, config) bytes, the caller's; nothing in it
  * needs clearing, and it must not be shared by launches that can overlap on the GPU.  The query
- * returns 0 when the tiles of this problem stay whole: single-CTA tiles, a full last round, or a
- * split that would cost more in partial sums than it saves in idle k steps (every square problem
- * from 1024^3 up); with a null or smaller workspace the call is nb200_gemm / nb200_gemm_bt.
- * Knob "gemm_split_tail": 1 = split whenever every pair gets at least four k steps, negative =
- * never, 0 = by the measured costs. */
+ * returns 0 when the tiles of this problem stay whole: single-CTA tiles, a last round more than
+ * half full, or a split that would cost more in partial sums than it saves in idle k steps
+ * (fewer than ~28 per pair); with a null or smaller workspace the call is nb200_gemm /
+ * nb200_gemm_bt.  Knob "gemm_split_tail": 1 = split whenever a part still has four k steps,
+ * negative = never, 0 = by the measured costs. */
 int64_t nb200_gemm_split_workspace_bytes(int64_t m, int64_t n, int64_t k, int dtype,
                                          const nb200_gemm_config* config);
 int nb200_gemm_split(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,

@@ -292,59 +292,57 @@ int launch_pair(const PairInstance& inst, const CUtensorMap& ta, const CUtensorM
   return cuda_check(cudaLaunchKernelExC(&lc, inst.kern, args), "gemm pair launch");
 }
 
-// The split tail of a pair launch (GemmParams::sk_tiles): with `capacity` clusters resident and
-// `tiles` tiles of `k_rounds` ring slots each, how many of the last tiles are cut into equal
-// ranges of k rounds instead of being handed out whole.  Splitting saves the k rounds the idle
-// part of the chip would have sat through (~0.33 us each for a 256 x 256 tile on a B200) and
-// costs the partial sums' way through L2, a second launch, and k rounds that run slower because
-// every cluster now streams a different stretch of K: 13-40 us in all, measured.  Square
-// problems therefore keep their tiles whole (4096^3 would save 13 us and come out 1 us slower)
-// and the rule asks for 76 saved k rounds, ~25 us: 1024 x 1024 x 16384 goes from 84 to 46 us,
-// 512 x 512 x 65536 from 297 to 56, 256 x 256 x 65536 from 299 to 34.  Knob gemm_split_tail:
-// 1 = split whenever every cluster gets four k rounds, negative = never.
-int split_tail_tiles(long long tiles, int k_rounds, int capacity, int nsub) {
-  (void)nsub;   // a 512-column tile doubles what a k round saves and what a partial sum costs
+// The split tail of a pair launch (GemmParams::sk_tiles ...): with `capacity` clusters resident
+// and `tiles` tiles of `k_rounds` ring slots each, the tiles of the last, partly filled round are
+// cut along K into as many equal parts as there are clusters per tile, one part per cluster.
+// Splitting saves the k rounds the idle part of the chip would have sat through (~0.33 us each
+// for a 256 x 256 tile on a B200, twice that for 512 columns) and costs the partial sums' way
+// through L2 and a second launch: 17-23 k rounds' worth, measured (4096^3 in 256 x 256 tiles saves
+// 32 and goes from 96.2 to 93.2 us; 2048^3 in 256 x 512 tiles saves 16 and loses 1 us).  The rule
+// asks for more than 28 saved k rounds.  Knob gemm_split_tail: 1 = split whenever a part still
+// has four k rounds, negative = never.
+struct SplitPlan {
+  int tiles, parts, len;   // tiles == 0: nothing is split
+};
+SplitPlan split_tail_plan(long long tiles, int k_rounds, int capacity) {
+  SplitPlan none = {0, 0, 0};
   const int knob = tuning("gemm_split_tail", 0);
-  if (knob < 0 || capacity < 2) return 0;
+  if (knob < 0) return none;
   const int rest = (int)(tiles % capacity);
-  if (rest == 0) return 0;
-  const long long units = (long long)rest * k_rounds;
-  if (units < 4LL * capacity) return 0;
-  if (knob > 0) return rest;
-  const long long saved = k_rounds - (units + capacity - 1) / capacity;
-  return saved > 76 ? rest : 0;
+  if (rest == 0 || capacity / rest < 2) return none;
+  int parts = capacity / rest;
+  if (parts > k_rounds / 4) parts = k_rounds / 4;
+  if (parts < 2) return none;
+  const int len = (k_rounds + parts - 1) / parts;
+  parts = (k_rounds + len - 1) / len;            // none of them empty
+  if (knob == 0 && k_rounds - len <= 28) return none;
+  return SplitPlan{rest, parts, len};
 }
 
-// Bytes of the workspace a split tail needs: 2 slots per cluster, a slot = one fp32 tile.
+// Bytes of the workspace a split tail needs: a slot per cluster, a slot = one fp32 tile.
 size_t split_workspace_bytes(int capacity, int nsub) {
-  return (size_t)2 * capacity * 256 * (256 * nsub) * 4;
+  return (size_t)capacity * 256 * (256 * nsub) * 4;
 }
 
 // Adds up the parts of the split tiles and stores C: what the pair kernel's epilogue does for a
-// whole tile, for the tiles whose k rounds went to several clusters.  The parts of a tile lie in
-// the slots of consecutive clusters (2c, or 2c + 1 for a cluster's second partial segment, which
-// only the first cluster of a tile can contribute).  A thread has one row and 16 columns (whole
-// 32-byte sectors of a 16-bit C); its warp the 32 rows one epilogue warp of one CTA wrote.
+// whole tile.  Part s of split tile t lies in slot s * sk_tiles + t.  A thread has one row and 16
+// columns (whole 32-byte sectors of a 16-bit C); its warp the 32 rows one epilogue warp of one
+// CTA wrote.
 // MANY = false, grid (BN / 16, split tiles): a block of 8 warps takes the 256 rows of a tile and
 // every thread adds the parts one after the other -- tiles in two to seven parts.
 // MANY = true, grid (BN / 16, 8 per split tile): a block takes 32 rows, its warp g adds parts g,
-// g + 8, ... and warp 0 adds the eight sums in order -- a small C with a long K, one part per
-// cluster.  Either way the order of the additions is fixed, so the result does not depend on
-// which part was written last.  L2-bound: 4 bytes per element and part.
+// g + 8, ... and warp 0 adds the eight sums in order -- a very small C, many parts per tile.
+// Either way the order of the additions is fixed, so the result does not depend on which part
+// was written last.  L2-bound: 4 bytes per element and part.
 template <int CT, int BN, bool MANY>
-__global__ void __launch_bounds__(256) split_reduce_kernel(const GemmParams p, int clusters, int k_rounds) {
+__global__ void __launch_bounds__(256) split_reduce_kernel(const GemmParams p) {
   using OutT = typename gemm::ElemType<CT>::T;
   __shared__ float sums[MANY ? 8 : 1][16][32];
   const int t = MANY ? blockIdx.y >> 3 : blockIdx.y;
   const int rows32 = MANY ? (blockIdx.y & 7) : (threadIdx.x >> 5);
   const int m_blocks2 = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
-  const gemm::SplitTail seq(p, m_blocks2 * p.n_blocks, k_rounds, 0, clusters);
-  const long long t0 = (long long)t * k_rounds;
-  const int c_lo = seq.cluster_of(t0), c_hi = seq.cluster_of(t0 + k_rounds - 1);
-  if (c_lo == c_hi) return;   // the tile stayed whole: the pair kernel stored it
-  const int lo_second = seq.range_start(c_lo) < t0 ? 1 : 0;
   int mb, nb;
-  gemm::tile_coords(seq.dp_tiles + t, m_blocks2, p.n_blocks, p.group_m, &mb, &nb);
+  gemm::tile_coords(m_blocks2 * p.n_blocks - p.sk_tiles + t, m_blocks2, p.n_blocks, p.group_m, &mb, &nb);
   const int g = MANY ? (threadIdx.x >> 5) : 0, lane = threadIdx.x & 31;
   const int row = mb * 2 * kBlockM + rows32 * 32 + lane;
   const int col = nb * BN + blockIdx.x * 16;
@@ -353,10 +351,9 @@ __global__ void __launch_bounds__(256) split_reduce_kernel(const GemmParams p, i
   float acc[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-  for (int pc = c_lo + g; pc <= c_hi; pc += MANY ? 8 : 1) {
+  for (int s = g; s < p.sk_parts; s += MANY ? 8 : 1) {
     const float4* src =
-        reinterpret_cast<const float4*>(p.sk_ws + (long long)(2 * pc + (pc == c_lo ? lo_second : 0)) * (256LL * BN)) +
-        piece;
+        reinterpret_cast<const float4*>(p.sk_ws + (long long)(s * p.sk_tiles + t) * (256LL * BN)) + piece;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float4 v = __ldcg(src + j * 32);
@@ -413,12 +410,12 @@ __global__ void __launch_bounds__(256) split_reduce_kernel(const GemmParams p, i
 }
 
 template <int BN>
-int launch_split_reduce(const GemmParams& p, int dtype, int clusters, int k_rounds, cudaStream_t stream) {
-  const bool many = clusters / p.sk_tiles >= 7;   // parts per tile: clusters / tiles, plus one or two
+int launch_split_reduce(const GemmParams& p, int dtype, cudaStream_t stream) {
+  const bool many = p.sk_parts >= 8;
   const dim3 grid(BN / 16, p.sk_tiles * (many ? 8 : 1));
-#define NB200_SPLIT_SUM(CT_)                                                                      \
-  if (many) split_reduce_kernel<CT_, BN, true><<<grid, 256, 0, stream>>>(p, clusters, k_rounds);  \
-  else split_reduce_kernel<CT_, BN, false><<<grid, 256, 0, stream>>>(p, clusters, k_rounds);
+#define NB200_SPLIT_SUM(CT_)                                                  \
+  if (many) split_reduce_kernel<CT_, BN, true><<<grid, 256, 0, stream>>>(p);  \
+  else split_reduce_kernel<CT_, BN, false><<<grid, 256, 0, stream>>>(p);
   if (dtype == NB200_F32) { NB200_SPLIT_SUM(NB200_F32) }
   else if (dtype == NB200_BF16) { NB200_SPLIT_SUM(NB200_BF16) }
   else { NB200_SPLIT_SUM(NB200_F16) }
@@ -675,15 +672,17 @@ int gemm_impl(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
     const long long tiles = (long long)cdiv64(p.m, 2 * kBlockM) * p.n_blocks;
     if (split_ws) {
       const int k_rounds = (p.k_blocks + inst.ksub - 1) / inst.ksub;
-      const int sk = split_tail_tiles(tiles, k_rounds, capacity, inst.nsub);
-      if (sk > 0 && split_ws_bytes >= split_workspace_bytes(capacity, inst.nsub) &&
+      const SplitPlan sp = split_tail_plan(tiles, k_rounds, capacity);
+      if (sp.tiles > 0 && split_ws_bytes >= split_workspace_bytes(capacity, inst.nsub) &&
           (reinterpret_cast<uintptr_t>(split_ws) & 15) == 0) {
         GemmParams q = p;
-        q.sk_tiles = sk;
+        q.sk_tiles = sp.tiles;
+        q.sk_parts = sp.parts;
+        q.sk_len = sp.len;
         q.sk_ws = static_cast<float*>(split_ws);
         if (int rc = launch_pair(inst, g.ta, g.tb, q, capacity, stream)) return rc;
-        return inst.nsub == 2 ? launch_split_reduce<512>(q, dtype, capacity, k_rounds, stream)
-                              : launch_split_reduce<256>(q, dtype, capacity, k_rounds, stream);
+        return inst.nsub == 2 ? launch_split_reduce<512>(q, dtype, stream)
+                              : launch_split_reduce<256>(q, dtype, stream);
       }
     }
     return launch_pair(inst, g.ta, g.tb, p, (int)(tiles < capacity ? tiles : capacity), stream);
@@ -825,8 +824,8 @@ extern "C" int64_t nb200_gemm_split_workspace_bytes(int64_t m, int64_t n, int64_
     return 0;
   const long long tiles = (long long)cdiv64(m, 2 * kBlockM) * cdiv64(n, cfg.block_n);
   const int k_rounds = (int)cdiv64(cdiv64(k, row_k), inst.ksub);
-  const int sk = split_tail_tiles(tiles, k_rounds, capacity, inst.nsub);
-  return sk > 0 ? (int64_t)split_workspace_bytes(capacity, inst.nsub) : 0;
+  return split_tail_plan(tiles, k_rounds, capacity).tiles > 0
+             ? (int64_t)split_workspace_bytes(capacity, inst.nsub) : 0;
 }
 
 extern "C" int nb200_gemm_split(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,

@@ -127,12 +127,12 @@ struct GemmParams {
   int group_m;   // row-blocks per L2 band of the tile order
   unsigned long long wait_limit_ns;
   unsigned int* status;
-  // Split tail (pair kernels): the last sk_tiles tiles are not handed out whole.  Their k rounds,
-  // taken as one sequence, are cut into one equal range per cluster, so the last round of a
-  // launch keeps every SM busy; a part of a tile leaves its fp32 partial sums in sk_ws and a
-  // second kernel adds the parts up (see SplitTail).  0 = every tile whole.
-  int sk_tiles;
-  float* sk_ws;             // 2 slots per cluster, a slot = one fp32 accumulator tile
+  // Split tail (pair kernels): the last sk_tiles tiles are not handed out whole but cut along
+  // K into sk_parts parts of sk_len k rounds, one part per cluster, so the last round of a
+  // launch keeps the chip busy; a part leaves its fp32 partial sums in sk_ws and a second kernel
+  // adds the parts up (see SplitTail).  0 = every tile whole.
+  int sk_tiles, sk_parts, sk_len;
+  float* sk_ws;             // a slot per cluster, a slot = one fp32 accumulator tile
 };
 
 // What runs between the accumulator and the store, in two steps.  `fetch` gets the row and
@@ -154,30 +154,23 @@ struct NoEpilogue {
 };
 
 // The order in which a cluster works through a launch: its whole tiles (tile = cluster,
-// cluster + clusters, ... below dp_tiles), then its range of the split tail's k rounds, as
+// cluster + clusters, ... below the split ones), then at most one part of a split tile, as
 // segments (tile, first k round, end k round).  The three roles of a CTA run the same sequence.
+// Split tile t (of sk_tiles) is cut into sk_parts stretches of sk_len k rounds, the same
+// stretches for every tile; part s of tile t goes to cluster s * sk_tiles + t, so the clusters
+// that read the same rows of A or columns of B over the same stretch of K run side by side and
+// share them in L2, as whole tiles of one round do.
 struct SplitTail {
-  int dp_tiles, clusters, k_rounds;
-  long long units;     // sk_tiles * k_rounds
-  int next_tile;
-  long long u, u1;     // what is left of this cluster's range
-  int cluster;
-  int slot;            // of the last split segment handed out: where its partial sum goes
+  int dp_tiles, clusters, k_rounds, sk_tiles, parts, len;
+  int next_tile, cluster;
+  bool part_taken;
 
   __device__ __forceinline__ SplitTail(const GemmParams& p, int num_tiles, int k_rounds_, int cluster_,
                                        int clusters_)
-      : dp_tiles(num_tiles - p.sk_tiles), clusters(clusters_), k_rounds(k_rounds_),
-        units((long long)p.sk_tiles * k_rounds_), next_tile(cluster_), cluster(cluster_) {
-    u = range_start(cluster_);
-    u1 = range_start(cluster_ + 1);
-  }
-  __device__ __forceinline__ long long range_start(int c) const { return units * c / clusters; }
-  // the cluster whose range holds unit x
-  __device__ __forceinline__ int cluster_of(long long x) const {
-    return (int)(((x + 1) * clusters + units - 1) / units) - 1;
-  }
-  // Next segment; split = index of the tile inside the tail when the segment is only a part of
-  // its tile, else -1.
+      : dp_tiles(num_tiles - p.sk_tiles), clusters(clusters_), k_rounds(k_rounds_), sk_tiles(p.sk_tiles),
+        parts(p.sk_parts), len(p.sk_len), next_tile(cluster_), cluster(cluster_), part_taken(false) {}
+  // Next segment; split = index of the tile among the split ones when the segment is a part of
+  // one (its partial sums go to slot `cluster` of the workspace), else -1.
   __device__ __forceinline__ bool next(int* tile, int* kb0, int* kb1, int* split) {
     if (next_tile < dp_tiles) {
       *tile = next_tile;
@@ -187,17 +180,13 @@ struct SplitTail {
       next_tile += clusters;
       return true;
     }
-    if (u >= u1) return false;
-    const int t = (int)(u / k_rounds);
-    const int b0 = (int)(u - (long long)t * k_rounds);
-    const long long left = u1 - u;
-    const int b1 = left < (long long)(k_rounds - b0) ? b0 + (int)left : k_rounds;
-    slot = 2 * cluster + (u != range_start(cluster) ? 1 : 0);
-    u += b1 - b0;
+    if (part_taken || cluster >= sk_tiles * parts) return false;
+    part_taken = true;
+    const int s = cluster / sk_tiles, t = cluster - s * sk_tiles;
     *tile = dp_tiles + t;
-    *kb0 = b0;
-    *kb1 = b1;
-    *split = (b0 == 0 && b1 == k_rounds) ? -1 : t;
+    *kb0 = s * len;
+    *kb1 = min(k_rounds, (s + 1) * len);
+    *split = t;
     return true;
   }
 };
@@ -766,7 +755,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       if (split >= 0) {
         // A part of a split tile: its fp32 partial sums go to this segment's slot and the
         // accumulator is handed back; split_reduce_kernel adds the parts up after this kernel.
-        dump_rows<BN>(t_row, p.sk_ws + seq.slot * (256LL * BN) + (long long)(rank * 4 + quarter) * (BN * 32),
+        dump_rows<BN>(t_row, p.sk_ws + first * (256LL * BN) + (long long)(rank * 4 + quarter) * (BN * 32),
                       lane);
         tc_fence_before_sync();
         __syncwarp();

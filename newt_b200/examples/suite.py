@@ -2,7 +2,7 @@
 benchmarks/results.md of the reference): vector add, fused softmax, layernorm, fp16 matmul,
 fp32/tf32 matmul, plus causal attention, each next to the torch call on the same tensors.
 
-    python -m newt_b200.examples.suite [--quick] [--kernel add|fused|softmax|layernorm|rows|matmul|matmul_tf32|matmul_epilogue|attention]
+    python -m newt_b200.examples.suite [--quick] [--kernel add|fused|softmax|layernorm|rows|matmul|matmul_long_k|matmul_tf32|matmul_epilogue|attention]
 
 Clock and metric definitions are the reference's: `do_bench` (median, L2 flushed between
 reps); GB/s = bytes read + written / t; TFLOP/s = 2*M*N*K / t.  Prints markdown tables.
@@ -124,6 +124,25 @@ def bench_matmul(quick):
     return out
 
 
+def bench_matmul_long_k(quick):
+    """A small C with a long K: few tiles, many k steps each.  The configurations with 256-row
+    CTA-pair tiles have the library cut the tiles along K over all pairs (nb200_gemm_split);
+    the autotuner times them next to the single-CTA tiles."""
+    out = ["| kernel | M x N x K | newt_b200 TFLOP/s | torch TFLOP/s | ratio |", "|---|---|---|---|---|"]
+    shapes = [(1024, 1024, 16384), (512, 512, 65536)]
+    if not quick:
+        shapes += [(256, 256, 65536), (2048, 1024, 16384), (1024, 1024, 65536)]
+    for m, n, k in shapes:
+        a_ = (torch.randn(m, k, device="cuda") / k ** 0.5).bfloat16()
+        b_ = torch.randn(k, n, device="cuda").bfloat16()
+        c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        a = _bench(lambda: K.matmul(a_, b_, c))     # first call autotunes
+        b = _bench(lambda: torch.matmul(a_, b_, out=c))
+        row = _row("matmul bf16", f"{m}x{n}x{k}", a, b, 2 * m * n * k / 1e9)
+        out.append(row + f" <!-- {K.matmul_kernel.best_config} -->")
+    return out
+
+
 def bench_matmul_tf32(quick):
     """fp32 operands, tf32 product (benchmarks/bench.py:291-294: torch runs with allow_tf32).
     Our time includes the pass that transposes B for the tensor core."""
@@ -177,7 +196,8 @@ def bench_attention(quick):
 
 
 SUITES = {"add": bench_add, "fused": bench_fused, "softmax": bench_softmax, "layernorm": bench_layernorm,
-          "rows": bench_rows, "matmul": bench_matmul, "matmul_tf32": bench_matmul_tf32,
+          "rows": bench_rows, "matmul": bench_matmul, "matmul_long_k": bench_matmul_long_k,
+          "matmul_tf32": bench_matmul_tf32,
           "matmul_epilogue": bench_matmul_epilogue, "attention": bench_attention}
 
 
