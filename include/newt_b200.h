@@ -204,7 +204,8 @@ int nb200_gemm_tf32_static(const void* a, const void* b, void* c, int64_t m, int
  * returns 0 when the tiles of this problem stay whole: single-CTA tiles, a last round more than
  * half full, or a split that would cost more in partial sums than it saves in idle k steps
  * (fewer than ~28 per pair); with a null or smaller workspace the call is nb200_gemm /
- * nb200_gemm_bt.  Knob "gemm_split_tail": 1 = split whenever a part still has four k steps,
+ * nb200_gemm_bt.  With `config` null or all zeros the library takes 256 x 256 pair tiles where
+ * that makes a split pay (the default of nb200_gemm gives a small C single-CTA tiles).  Knob "gemm_split_tail": 1 = split whenever a part still has four k steps,
  * negative = never, 0 = by the measured costs. */
 int64_t nb200_gemm_split_workspace_bytes(int64_t m, int64_t n, int64_t k, int dtype,
                                          const nb200_gemm_config* config);

@@ -811,11 +811,39 @@ extern "C" int nb200_gemm_bt(const void* a, const void* bt, void* c, int64_t m, 
                    static_cast<cudaStream_t>(stream));
 }
 
+namespace nb200 {
+namespace {
+// The tile a split launch runs on when the caller leaves the choice to the library: the default
+// of nb200_gemm looks at M and N only and gives a small C single-CTA tiles, which cannot be split;
+// with a K long enough for the split to pay, 256 x 256 pair tiles are the better answer.
+const nb200_gemm_config* config_for_split(const nb200_gemm_config* config, int64_t m, int64_t n,
+                                          int64_t k, int dtype, nb200_gemm_config* storage) {
+  if (config && (config->block_m || config->block_n || config->block_k || config->stages || config->cta_pair))
+    return config;
+  if (m <= 0 || n <= 0 || k <= 0) return config;
+  const int row_k = dtype == NB200_F32 ? 32 : 64;
+  const nb200_gemm_config pair256 = {256, 256, row_k, 6, 1};
+  Resolved cfg;
+  if (resolve_config(&pair256, m, n, row_k, &cfg) != 0) return config;
+  const PairInstance inst = pair_instance(cfg, row_k, dtype, false);
+  int capacity = 0;
+  if (prepare_kernel(inst.kern, inst.smem) != 0 || pair_capacity(inst.kern, inst.smem, &capacity) != 0)
+    return config;
+  const long long tiles = (long long)cdiv64(m, 2 * kBlockM) * cdiv64(n, 256);
+  if (split_tail_plan(tiles, (int)cdiv64(k, row_k), capacity).tiles == 0) return config;
+  *storage = pair256;
+  return storage;
+}
+}  // namespace
+}  // namespace nb200
+
 extern "C" int64_t nb200_gemm_split_workspace_bytes(int64_t m, int64_t n, int64_t k, int dtype,
                                                     const nb200_gemm_config* config) {
   if (dtype != NB200_F16 && dtype != NB200_BF16 && dtype != NB200_F32) return 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   const int row_k = dtype == NB200_F32 ? 32 : 64;
+  nb200_gemm_config chosen;
+  config = config_for_split(config, m, n, k, dtype, &chosen);
   Resolved cfg;
   if (resolve_config(config, m, n, row_k, &cfg) != 0 || !cfg.pair) return 0;
   const PairInstance inst = pair_instance(cfg, row_k, dtype, false);
@@ -832,6 +860,8 @@ extern "C" int nb200_gemm_split(const void* a, const void* b, void* c, int64_t m
                                 int64_t lda, int64_t ldb, int64_t ldc, int dtype, int b_transposed,
                                 const nb200_gemm_config* config, void* workspace,
                                 int64_t workspace_bytes, void* stream) {
+  nb200_gemm_config chosen;
+  if (workspace && workspace_bytes > 0) config = config_for_split(config, m, n, k, dtype, &chosen);
   return gemm_impl(a, b, c, m, n, k, lda, ldb, ldc, dtype, config, b_transposed != 0,
                    static_cast<cudaStream_t>(stream), false, workspace,
                    workspace_bytes > 0 ? (size_t)workspace_bytes : 0);

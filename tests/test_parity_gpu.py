@@ -409,7 +409,9 @@ def test_gemm_split_tail_vs_oracle(dtype, block_n, block_k, transposed, m, n, k)
 def test_gemm_split_tail_rule_and_small_workspace():
     """Square problems keep their tiles whole, a small C with a long K is split; a workspace that
     is too small means the unsplit product, not an error."""
-    assert kernels.gemm_split_bytes(4096, 4096, 4096, torch.bfloat16) == 0
+    wide = kernels.gemm_config(block_m=256, block_n=512, block_k=64, cta_pair=1)
+    assert kernels.gemm_split_bytes(4096, 4096, 4096, torch.bfloat16, wide) == 0   # 128 tiles: a round of 54
+    assert kernels.gemm_split_bytes(4096, 4096, 4096, torch.bfloat16) > 0   # left to the library: 256 x 256, 34 tiles in halves
     assert kernels.gemm_split_bytes(8192, 8192, 8192, torch.bfloat16) == 0
     assert kernels.gemm_split_bytes(1024, 1024, 1024, torch.float16) == 0
     cfg = kernels.gemm_config(block_m=256, block_n=256, block_k=64, cta_pair=1)
@@ -422,6 +424,9 @@ def test_gemm_split_tail_rule_and_small_workspace():
     whole, split, starved = (torch.empty(m, n, device="cuda", dtype=torch.bfloat16) for _ in range(3))
     kernels.gemm(a, b, whole, m, n, k, k, n, n, cfg)
     kernels.gemm_split(a, b, split, m, n, k, k, n, n, cfg)
+    assert kernels.gemm_split_bytes(m, n, k, torch.bfloat16) == need   # no config: the same tile
+    by_default = torch.empty_like(split)
+    kernels.gemm_split(a, b, by_default, m, n, k, k, n, n)
     ws = torch.empty(4096, dtype=torch.uint8, device="cuda")
     abi.check(abi.load().nb200_gemm_split(a.data_ptr(), b.data_ptr(), starved.data_ptr(), m, n, k, k, n, n,
                                           abi.dtype_code(a.dtype), 0, ctypes.byref(cfg), ws.data_ptr(),
@@ -429,6 +434,7 @@ def test_gemm_split_tail_rule_and_small_workspace():
     torch.cuda.synchronize()
     assert abi.read_status() == (0, 0)
     assert torch.equal(starved, whole)
+    assert torch.equal(by_default, split)
     ref = a.float() @ b.float()
     assert torch_ref.rel_frobenius(split.float().cpu(), ref.cpu()) <= 1e-2
     assert (split.float() - whole.float()).abs().max().item() <= 0.05
