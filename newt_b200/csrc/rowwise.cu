@@ -36,12 +36,20 @@ struct Elem<__half> {
   static constexpr int kPerVec = 8;
   __device__ static float to_f32(__half v) { return __half2float(v); }
   __device__ static __half from_f32(float v) { return __float2half_rn(v); }
+  __device__ static uint32_t pack2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
 };
 template <>
 struct Elem<__nv_bfloat16> {
   static constexpr int kPerVec = 8;
   __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
   __device__ static __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+  __device__ static uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
 };
 
 // One 16-byte vector of T, addressable both ways.
@@ -320,8 +328,16 @@ __global__ void __launch_bounds__(TPR* RPB, RowOccupancy<ITEMS * Elem<T>::kPerVe
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
       Vec<T> o;
+      if constexpr (sizeof(T) == 2) {
+        // two lanes per conversion instruction: the scalar cvt.rn.bf16.f32 issues at a fraction
+        // of the packed form's rate on sm_100a
+        uint32_t* words = reinterpret_cast<uint32_t*>(&o.raw);
 #pragma unroll
-      for (int j = 0; j < E; ++j) o.e[j] = Elem<T>::from_f32(v[i * E + j]);
+        for (int j = 0; j < E; j += 2) words[j / 2] = Elem<T>::pack2(v[i * E + j], v[i * E + j + 1]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < E; ++j) o.e[j] = Elem<T>::from_f32(v[i * E + j]);
+      }
       store_vec<T, FAST>(orow, (i * TPR + lane_in_row) * E, n, out_ok, o);
     }
   }

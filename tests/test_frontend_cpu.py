@@ -185,7 +185,7 @@ def test_block_arithmetic_is_compiled_at_run_time():
         assert f'extern "C" __global__ void __launch_bounds__(128) {c.plan.kernel_name}(' in c.plan.source
         # fp16 arithmetic is done in fp32 and rounded back after every operation
         if kernel is bias_relu:
-            assert "__float2half_rn((__half2float(" in c.plan.source
+            assert "nb_to_f16((__half2float(" in c.plan.source
         cubin = nvrtc.compile_cubin(c.plan.source, c.plan.kernel_name + ".cu")   # needs no GPU
         assert cubin[:4] == b"\x7fELF"
 
