@@ -67,6 +67,9 @@ int nb200_read_status(uint32_t* status, uint32_t* detail);
  *   "tf32_in_place"    0: nb200_gemm_tf32 always transposes B into its workspace
  *   "gemm_group_m"     row-blocks per band of the GEMM tile order (L2 reuse of B columns; 16)
  *   "gemm_split_tail"  see nb200_gemm_split
+ *   "gemm_half_tail"   256 x 512 tiles: 1 = the last ring of k steps finishes columns 0..255 first (their
+ *                      way out to C then overlaps the MMAs of columns 256..511), 2 = the first ring
+ *                      starts with them as well (the default from 32 k steps up), negative = neither
  *   "wait_limit_us"    how long one device-side wait (an mbarrier spin of the tensor-core
  *                      kernels) may last before the kernel gives up, records a code in the
  *                      status word and returns; 2 000 000 (2 s) when unset */

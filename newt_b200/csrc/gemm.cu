@@ -641,6 +641,13 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   p.b_kmajor = b_kmajor ? 1 : 0;
   p.wide_a = wide_a ? 1 : 0;
   p.group_m = tuning("gemm_group_m", 0) > 0 ? tuning("gemm_group_m", 0) : gemm::kGroupM;
+  // 512-column tiles: the last ring of k rounds ends columns 0..255 first, and with a long K the
+  // first ring starts with them as well (1622 -> 1633 -> 1643 TFLOP/s at 8192^3 bf16; the start
+  // gives nothing below ~32 k rounds).  Knob gemm_half_tail: 1 = end only, 2 = both, negative = off.
+  {
+    const int knob = tuning("gemm_half_tail", 0);
+    p.half_tail = knob < 0 ? 0 : knob > 0 ? knob : (p.k_blocks / ksub >= 32 ? 2 : 1);
+  }
   p.wide_b = wide_b ? 1 : 0;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * c_bytes) % 16 == 0) ? 1 : 0;
   p.wait_limit_ns = wait_limit_ns();

@@ -125,6 +125,7 @@ struct GemmParams {
   // slot is filled slab by slab, zero-filled at the ragged edges.
   int wide_a, wide_b;
   int group_m;   // row-blocks per L2 band of the tile order
+  int half_tail; // 512-column tile: the last ring's worth of k rounds finishes columns 0..255 first
   unsigned long long wait_limit_ns;
   unsigned int* status;
   // Split tail (pair kernels): the last sk_tiles tiles are not handed out whole but cut along
@@ -683,38 +684,80 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * 256;
         bool half1_free = NSUB == 1;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
-          if (!ok) break;
-          tc_fence_after_sync();
-          GTRACE(1, 100 + kb, elected && (kb & 7) == 0)  // k round kb landed
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint32_t b_addr = a_addr + KSUB * kABytes;
+        // the MMAs of one 256-column half over the K slabs of one ring slot
+        auto issue = [&](int h, int slot, bool first_round) {
+          const uint32_t a_addr = smem_base + slot * kStageBytes;
+          const uint32_t bh_addr = a_addr + KSUB * kABytes + h * KSUB * kBBytes;
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {
             // K-major operands: slab `sub` is a block of its own.  B as [K, N]: a column slab
             // holds the K rows of all KSUB slabs one after the other.
             const uint64_t a_desc = with_address(kADesc, a_addr + sub * kABytes);
+            const uint64_t b_desc = b_kmajor ? with_address(kADesc, bh_addr + sub * kBBytes)
+                                             : with_address(kBDesc, bh_addr + sub * kBSlab);
 #pragma unroll
-            for (int h = 0; h < NSUB; ++h) {
-              if (NSUB == 2 && h == 1 && !half1_free) {
-                ok = wait_all(&acc_empty_bar[1], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile);
-                if (!ok) break;
-                tc_fence_after_sync();
-                half1_free = true;
-              }
-              const uint32_t bh_addr = b_addr + h * KSUB * kBBytes;
-              const uint64_t b_desc = b_kmajor ? with_address(kADesc, bh_addr + sub * kBBytes)
-                                               : with_address(kBDesc, bh_addr + sub * kBSlab);
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                if (elected)
-                  mma_ss_pair<DT>(d_tmem + h * 256, a_desc + (uint64_t)(kk * 2),
-                                  b_desc + (uint64_t)(kk * b_step), p.idesc,
-                                  ((kb - kb0) | sub | kk) != 0 ? 1u : 0u);
-            }
+            for (int kk = 0; kk < 4; ++kk)
+              if (elected)
+                mma_ss_pair<DT>(d_tmem + h * 256, a_desc + (uint64_t)(kk * 2),
+                                b_desc + (uint64_t)(kk * b_step), p.idesc,
+                                (!first_round || (sub | kk) != 0) ? 1u : 0u);
           }
+        };
+        auto free_half1 = [&]() -> bool {
+          if (!half1_free) {
+            if (!wait_all(&acc_empty_bar[1], acc_phase ^ 1, ST_WAIT_ACC_EMPTY, tile)) return false;
+            tc_fence_after_sync();
+            half1_free = true;
+          }
+          return true;
+        };
+        // The wide tile has one accumulator, so the tensor core waits while the epilogue drains
+        // columns 0..255 of the tile before (every pair stores at the same moment; ~4300 cycles).
+        // The last ring's worth of k rounds is therefore issued half by half: columns 0..255 are
+        // complete, and on their way out, while the MMAs of columns 256..511 still run.
+        const int tail0 = (NSUB == 2 && p.half_tail) ? max(kb0, kb1 - STAGES) : kb1;
+        // The same at the start of a tile, the other way round: columns 256..511 of the tile
+        // before are the last to leave, so the first ring's worth of k rounds runs its columns
+        // 0..255 first.
+        const int head1 = (NSUB == 2 && p.half_tail > 1) ? min(kb0 + STAGES, tail0) : kb0;
+        if constexpr (NSUB == 2) {
+          if (head1 > kb0) {
+            int st = stage;
+            uint32_t ph = phase;
+            for (int kb = kb0; kb < head1 && ok; ++kb) {
+              ok = wait_all(&full_bar[st], ph, ST_WAIT_TMA_FULL, tile);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue(0, st, kb == kb0);
+              if (++st == STAGES) st = 0, ph ^= 1;
+            }
+            if (ok) ok = free_half1();
+            for (int kb = kb0; kb < head1 && ok; ++kb) {
+              issue(1, stage, kb == kb0);
+              if (elected) {
+                mma_commit_pair(empty0 + stage * 8);
+                mma_commit_pair(empty1 + stage * 8);
+              }
+              __syncwarp();
+              if (++stage == STAGES) {
+                stage = 0;
+                phase ^= 1;
+              }
+            }
+            if (!ok) break;
+          }
+        }
+        for (int kb = head1; kb < tail0; ++kb) {
+          ok = wait_all(&full_bar[stage], phase, ST_WAIT_TMA_FULL, tile);
           if (!ok) break;
+          tc_fence_after_sync();
+          GTRACE(1, 100 + kb, elected && (kb & 7) == 0)  // k round kb landed
+          issue(0, stage, kb == kb0);
+          if constexpr (NSUB == 2) {
+            ok = free_half1();
+            if (!ok) break;
+            issue(1, stage, kb == kb0);
+          }
           // the slot is free in both CTAs once these MMAs retire
           if (elected) {
             mma_commit_pair(empty0 + stage * 8);
@@ -726,7 +769,46 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
             phase ^= 1;
           }
         }
-        if (ok && elected) {
+        if constexpr (NSUB == 2) {
+          if (ok && tail0 < kb1) {
+            int st = stage;
+            uint32_t ph = phase;
+            for (int kb = tail0; kb < kb1 && ok; ++kb) {
+              ok = wait_all(&full_bar[st], ph, ST_WAIT_TMA_FULL, tile);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue(0, st, kb == kb0);
+              if (++st == STAGES) st = 0, ph ^= 1;
+            }
+            if (ok && elected) {
+              mma_commit_pair(acc_full0);
+              mma_commit_pair(acc_full1);
+            }
+            __syncwarp();
+            if (ok) ok = free_half1();
+            for (int kb = tail0; kb < kb1 && ok; ++kb) {
+              issue(1, stage, kb == kb0);
+              if (elected) {
+                mma_commit_pair(empty0 + stage * 8);
+                mma_commit_pair(empty1 + stage * 8);
+              }
+              __syncwarp();
+              if (++stage == STAGES) {
+                stage = 0;
+                phase ^= 1;
+              }
+            }
+            if (ok && elected) {
+              mma_commit_pair(acc_full0 + 8);
+              mma_commit_pair(acc_full1 + 8);
+            }
+          } else if (ok && elected) {   // both halves end together
+            mma_commit_pair(acc_full0);
+            mma_commit_pair(acc_full1);
+            mma_commit_pair(acc_full0 + 8);
+            mma_commit_pair(acc_full1 + 8);
+          }
+        } else if (ok && elected) {
           mma_commit_pair(acc_full0 + buf * 8);
           mma_commit_pair(acc_full1 + buf * 8);
         }
@@ -750,11 +832,22 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
+      GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete (its columns 0..255 for a wide tile)
+      // the second half of a wide tile's accumulator has a barrier of its own
+      auto second_half = [&]() -> bool {
+        bool there = mbar_wait(smem_u32(&acc_full_bar[1]), acc_phase, ctx, ST_WAIT_ACC_FULL, tile);
+        there = __all_sync(0xffffffffu, there);
+        if (there) tc_fence_after_sync();
+        return there;
+      };
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * 256;
       if (split >= 0) {
         // A part of a split tile: its fp32 partial sums go to this segment's slot and the
         // accumulator is handed back; split_reduce_kernel adds the parts up after this kernel.
+        if constexpr (NSUB == 2) {
+          ok = second_half();
+          if (!ok) break;
+        }
         dump_rows<BN>(t_row, p.sk_ws + first * (256LL * BN) + (long long)(rank * 4 + quarter) * (BN * 32),
                       lane);
         tc_fence_before_sync();
@@ -772,6 +865,8 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[0]), 0));
+        ok = second_half();
+        if (!ok) break;
         drain_rows<256, CT, EPI>(t_row + 256, p.c, p.ldc,
                                  mb * 2 * kBlockM + rank * kBlockM + quarter * 32, nb * BN + 256, p.m,
                                  p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128), lane, ea);
