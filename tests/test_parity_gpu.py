@@ -440,6 +440,36 @@ def test_gemm_split_tail_rule_and_small_workspace():
     assert (split.float() - whole.float()).abs().max().item() <= 0.05
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("block_k", [1, 2])            # in 128-byte rows of K
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 64), (512, 1024, 192), (700, 1000, 328), (1024, 2048, 4096)])
+def test_gemm_wide_pair_half_by_half_rings(dtype, block_k, m, n, k):
+    """256 x 512 tiles issue the last ring of k steps -- and, with a long K, the first -- one
+    256-column half at a time: the same MMAs per accumulator column in the same order, so the
+    bits do not depend on the knob; K shorter than a ring, a ring and a half, ragged, long."""
+    g = torch.Generator().manual_seed(m + n + k + block_k)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(dtype).cuda()
+    np_ = (n + 7) // 8 * 8
+    b = torch.zeros(k, np_, dtype=dtype, device="cuda")[:, :n].copy_(torch.randn(k, n, generator=g).to(dtype))
+    row_k = 32 if dtype == torch.float32 else 64
+    cfg = kernels.gemm_config(block_m=256, block_n=512, block_k=block_k * row_k, cta_pair=1)
+    outs = []
+    try:
+        for knob in (-1, 1, 2, 0):
+            abi.set_tuning("gemm_half_tail", knob)
+            c = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+            kernels.gemm(a, b, c, m, n, k, k, np_, n, cfg)
+            torch.cuda.synchronize()
+            assert abi.read_status() == (0, 0)
+            outs.append(c)
+    finally:
+        abi.set_tuning("gemm_half_tail", 0)
+    for c in outs[1:]:
+        assert torch.equal(c, outs[0])
+    tol = 2e-3 if dtype == torch.float32 else 1e-2
+    assert torch_ref.rel_frobenius(outs[0].cpu().double(), a.cpu().double() @ b[:, :n].cpu().double()) <= tol
+
+
 def test_gemm_linearity_at_full_size():
     # size-independent property at the benchmark size: (A1 + A2) @ B == A1 @ B + A2 @ B
     # up to rounding, and a spot-checked block against the fp32 oracle
