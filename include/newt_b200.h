@@ -67,6 +67,8 @@ int nb200_read_status(uint32_t* status, uint32_t* detail);
  *   "tf32_in_place"    0: nb200_gemm_tf32 always transposes B into its workspace
  *   "gemm_group_m"     row-blocks per band of the GEMM tile order (L2 reuse of B columns; 16)
  *   "gemm_split_tail"  see nb200_gemm_split
+ *   "gemm_c_tma"       negative: the GEMM epilogue stores C with the SMs' own 16-byte stores even where
+ *                      C could be a tensor map for the copy engine (16-byte aligned base and pitch)
  *   "gemm_half_tail"   256 x 512 tiles: 1 = the last ring of k steps finishes columns 0..255 first (their
  *                      way out to C then overlaps the MMAs of columns 256..511), 2 = the first ring
  *                      starts with them as well (the default from 32 k steps up), negative = neither

@@ -50,7 +50,7 @@ using gemm::kThreads;
 template <int BN, int STAGES, int KSUB, int DT, int CT>
 __global__ void __launch_bounds__(gemm::kThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ GemmParams p) {
   gemm::gemm_body<BN, STAGES, KSUB, DT, CT, gemm::NoEpilogue>(tmap_a, tmap_b, p,
                                                               gemm::NoEpilogueArgs{0});
 }
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(gemm::kThreads, 1)
 template <int STAGES, int KSUB, int DT, int CT>
 __global__ void __launch_bounds__(gemm::kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                     const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                     const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ GemmParams p) {
   gemm::gemm_pair_body<STAGES, KSUB, DT, CT, gemm::NoEpilogue>(tmap_a, tmap_b, p,
                                                                gemm::NoEpilogueArgs{0});
 }
@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(gemm::kThreads, 1)
 template <int STAGES, int KSUB, int DT, int CT>
 __global__ void __launch_bounds__(gemm::kThreads, 1)
     gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                          const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                          const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ GemmParams p) {
   gemm::gemm_pair_body<STAGES, KSUB, DT, CT, gemm::NoEpilogue, 2>(tmap_a, tmap_b, p,
                                                                   gemm::NoEpilogueArgs{0});
 }
@@ -130,7 +130,7 @@ int resolve_config(const nb200_gemm_config* cfg, int64_t m, int64_t n, int row_k
     if (stages != 0 && (stages < 1 || stages > 8))
       return fail(NB200_E_INVALID, "stages=%d: supported 1..8", stages);
     out->block_n = 256;
-    // ring depth: 3 slots of 128 K-elements, 2 of 192, 4..6 of 64 (the epilogue's 16 KB of
+    // ring depth: 3 slots of 128 K-elements, 2 of 192, 4..6 of 64 (the epilogue's 32 KB of
     // staging leaves no room for a seventh)
     out->stages = out->block_k == 2 * kBlockK ? 3 : (out->block_k == 3 * kBlockK ? 2 :
                   (stages == 0 ? 6 : (stages >= 6 ? 6 : (stages >= 5 ? 5 : 4))));
@@ -650,6 +650,14 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   }
   p.wide_b = wide_b ? 1 : 0;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * c_bytes) % 16 == 0) ? 1 : 0;
+  p.c_tma = 0;
+  if (p.c_vec_ok && tuning("gemm_c_tma", 0) >= 0) {
+    // C for the epilogue's copies: boxes of 32 rows x 128 bytes (one pass of one epilogue warp)
+    const uint64_t cdims[2] = {(uint64_t)n, (uint64_t)m};
+    const uint64_t cstrides[1] = {(uint64_t)ldc * (uint64_t)c_bytes};
+    const uint32_t cbox[2] = {(uint32_t)(128 / c_bytes), 32u};
+    if (encode_tensor_map(&p.tmap_c, c, c_bytes, 2, cdims, cstrides, cbox) == 0) p.c_tma = 1;
+  }
   p.wait_limit_ns = wait_limit_ns();
   p.status = device_status_ptr();
   if (!p.status) return fail(NB200_E_CUDA, "gemm: device status word is not addressable");

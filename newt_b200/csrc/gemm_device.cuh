@@ -134,6 +134,12 @@ struct GemmParams {
   // adds the parts up (see SplitTail).  0 = every tile whole.
   int sk_tiles, sk_parts, sk_len;
   float* sk_ws;             // a slot per cluster, a slot = one fp32 accumulator tile
+  // C as a tensor map with boxes of 32 rows x 128 bytes under the 128-byte swizzle -- one pass of
+  // one epilogue warp, laid out as `drain_rows` stages it -- when C can be written by the copy
+  // engine (c_tma: 16-byte aligned base and pitch).  The kernel takes this struct as a
+  // __grid_constant__ parameter, so the map is read where the launch put it.
+  int c_tma;
+  alignas(64) CUtensorMap tmap_c;
 };
 
 // What runs between the accumulator and the store, in two steps.  `fetch` gets the row and
@@ -213,15 +219,19 @@ __device__ __forceinline__ void dump_rows(uint32_t t_row, float* dst, int lane) 
 // to C.  A thread holds one row, so storing from registers would write 16 bytes to each of 32
 // rows per instruction -- half-filled 32-byte sectors, which made the epilogue of a 128 x 256
 // tile take ~4900 cycles.  Instead a pass of 128 bytes of C per row (64 columns of a 16-bit C,
-// 32 of an fp32 C) is rounded, parked in this warp's 4 KB of shared memory (16-byte pieces
-// XOR-swizzled by the row, conflict-free both ways) and written out four whole 128-byte rows
-// per instruction.  Ragged edges and unaligned C take the register path.
-constexpr uint32_t kEpilogueStageBytes = 4 * 32 * 128;   // four epilogue warps
+// 32 of an fp32 C) is rounded and parked in one of this warp's two 4 KB areas of shared memory
+// (16-byte pieces XOR-swizzled by the row: conflict-free, and the 128-byte swizzle of a tensor
+// map).  From there the copy engine writes it to C (`tmap_c`; clipped at the edges of the
+// matrix) while the warp works on the next pass in the other area; without a tensor map of C
+// the warp writes four whole 128-byte rows per instruction itself.  Ragged edges of an
+// unaligned C take the register path.
+constexpr uint32_t kEpilogueStageBytes = 4 * 2 * 32 * 128;   // four epilogue warps, two staging areas each
 
 template <int BN, int CT, class EPI>
 __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ldc, int row0,
                                            int col_base, int m, int n, bool vec_ok, uint32_t stage,
-                                           int lane, const typename EPI::Args& ea) {
+                                           int lane, const typename EPI::Args& ea,
+                                           const CUtensorMap* tmap_c = nullptr, int* flip = nullptr) {
   using OutT = typename ElemType<CT>::T;
   constexpr int kPass = 128 / (int)sizeof(OutT);     // columns per pass
   constexpr int kPer16 = 16 / (int)sizeof(OutT);     // columns per 16-byte piece
@@ -249,8 +259,17 @@ __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ld
         for (int j = 0; j < 32; ++j) r[q * 32 + j] = __float_as_uint(v[j]);
       }
     }
-    if (vec_ok && col0 + kPass <= n) {
-      const uint32_t mine = stage + lane * 128;
+    if (tmap_c != nullptr || (vec_ok && col0 + kPass <= n)) {
+      // With the copy engine doing the stores the warp's two staging areas take turns: the
+      // engine drains one (an SM writes ~32 bytes per clock towards L2: ~650 cycles for the 16 KB
+      // of a pass of the four warps) while the next pass is read, rounded and staged in the other.
+      // (`flip` runs on over calls, so the areas alternate whatever the number of passes)
+      const uint32_t area = tmap_c != nullptr ? stage + ((*flip)++ & 1) * 4096 : stage;
+      if (tmap_c != nullptr) {   // ... once the copy before last has been read out of it
+        if (lane == 0) bulk_wait_group_read<1>();
+        __syncwarp();
+      }
+      const uint32_t mine = area + lane * 128;
 #pragma unroll
       for (int pc = 0; pc < 8; ++pc) {
         uint32_t w[4];
@@ -273,13 +292,23 @@ __device__ __forceinline__ void drain_rows(uint32_t t_row, void* c, long long ld
         }
         st_shared_v4(mine + ((pc ^ (lane & 7)) << 4), w[0], w[1], w[2], w[3]);
       }
+      if (tmap_c != nullptr) {
+        // one copy of 32 rows x 128 bytes (clipped at the edges of C)
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 < m) {
+          tma_store_2d(tmap_c, area, col0, row0);
+          bulk_commit_group();
+        }
+        continue;
+      }
       __syncwarp();
       const int pc = lane & 7;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rr = i * 4 + (lane >> 3);
         uint32_t w0, w1, w2, w3;
-        ld_shared_v4(stage + rr * 128 + ((pc ^ (rr & 7)) << 4), w0, w1, w2, w3);
+        ld_shared_v4(area + rr * 128 + ((pc ^ (rr & 7)) << 4), w0, w1, w2, w3);
         if (row0 + rr < m)
           *reinterpret_cast<uint4*>(static_cast<OutT*>(c) + (long long)(row0 + rr) * ldc + col0 +
                                     pc * kPer16) = make_uint4(w0, w1, w2, w3);
@@ -478,6 +507,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const CUtensorMap* tmap_c = p.c_tma ? &p.tmap_c : nullptr;
+    int flip = 0;   // which of the warp's two staging areas the next pass takes
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -492,12 +523,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       GTRACE(2, 3, threadIdx.x == 64)   // accumulator complete
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
       drain_rows<BN, CT, EPI>(t_row, p.c, p.ldc, mb * kBlockM + quarter * 32, nb * BN, p.m, p.n,
-                              p.c_vec_ok != 0, epi_stage + quarter * (32 * 128), lane, ea);
+                              p.c_vec_ok != 0, epi_stage + quarter * (2 * 32 * 128), lane, ea, tmap_c, &flip);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buf]));
       GTRACE(2, 4, threadIdx.x == 64)   // tile stored
     }
+    if (tmap_c != nullptr && lane == 0) bulk_wait_group_all();   // this thread's copies to C are done
   }
 
   __syncthreads();
@@ -819,6 +851,8 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
   } else {
     // ---------------- epilogue: this CTA's 128 rows of the 256-row tile ----------------
     const int quarter = warp & 3;
+    const CUtensorMap* tmap_c = p.c_tma ? &p.tmap_c : nullptr;
+    int flip = 0;   // which of the warp's two staging areas the next pass takes
     int it = 0;
     bool ok = true;
     SplitTail seq(p, num_tiles, k_rounds, first, step);
@@ -860,8 +894,8 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
       }
       if constexpr (NSUB == 2) {
         drain_rows<256, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
-                                 nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),
-                                 lane, ea);
+                                 nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (2 * 32 * 128),
+                                 lane, ea, tmap_c, &flip);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[0]), 0));
@@ -869,17 +903,18 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
         if (!ok) break;
         drain_rows<256, CT, EPI>(t_row + 256, p.c, p.ldc,
                                  mb * 2 * kBlockM + rank * kBlockM + quarter * 32, nb * BN + 256, p.m,
-                                 p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128), lane, ea);
+                                 p.n, p.c_vec_ok != 0, epi_stage + quarter * (2 * 32 * 128), lane, ea, tmap_c, &flip);
       } else {
         drain_rows<BN, CT, EPI>(t_row, p.c, p.ldc, mb * 2 * kBlockM + rank * kBlockM + quarter * 32,
-                                nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (32 * 128),
-                                lane, ea);
+                                nb * BN, p.m, p.n, p.c_vec_ok != 0, epi_stage + quarter * (2 * 32 * 128),
+                                lane, ea, tmap_c, &flip);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[NSUB == 2 ? 1 : buf]), 0));
       GTRACE(2, 4, threadIdx.x == 64)   // tile stored
     }
+    if (tmap_c != nullptr && lane == 0) bulk_wait_group_all();   // this thread's copies to C are done
   }
 
   tc_fence_before_sync();

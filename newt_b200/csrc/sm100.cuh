@@ -362,6 +362,26 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_a
 }
 // TMA load into this CTA's shared memory whose completion bytes are counted on a barrier
 // that may live in the other CTA of the pair.  No multicast: each CTA fetches its own tile.
+// A tile of shared memory written out to a tensor by the copy engine (no multicast, this GPU's
+// memory): the issuing thread's writes to `src` must be behind a fence.proxy.async; the copy
+// belongs to the thread's current bulk group; boxes that reach past the tensor's edges are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the sources of all but the N newest groups of this thread have been read / all of it is done
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x,
                                                  int y, uint32_t cluster_bar) {
   asm volatile(

@@ -1095,7 +1095,7 @@ class GemmEpiloguePlan(Plan):
                 '#include "gemm_device.cuh"\n' + self.fused_source +
                 f'\nextern "C" __global__ void __launch_bounds__(192, 1) {name}(\n'
                 "    const __grid_constant__ CUtensorMap ta, const __grid_constant__ CUtensorMap tb,\n"
-                "    const nb200::gemm::GemmParams p, const NbEpilogue::Args ea) {\n"
+                "    const __grid_constant__ nb200::gemm::GemmParams p, const NbEpilogue::Args ea) {\n"
                 f"  {body}\n}}\n")
             kernel = nvrtc.Kernel(nvrtc.compile_cubin_cached(source, name + ".cu",
                                                              extra_opts=(f"-I{nvrtc.device_headers()}",)), name)
