@@ -228,9 +228,10 @@ def linear_bias_relu(a, b, bias, c=None, BLOCK_M=256, BLOCK_N=None, BLOCK_K=64, 
     m, k = a.shape
     _, n = b.shape
     if BLOCK_N is None:
-        # 256 x 512 tiles once they fill the 74 CTA pairs of a B200 (1553 against 1515 TFLOP/s at
-        # 8192^3), 256 x 256 below
-        BLOCK_N = 512 if BLOCK_M == 256 and newt.cdiv(m, 256) * newt.cdiv(n, 512) >= 74 else 256
+        # 256 x 512 tiles once they fill the 74 CTA pairs of a B200 several times over (1553 against
+        # 1515 TFLOP/s at 8192^3), 256 x 256 below (4096^3: 1425 against 1314 -- the wide tile's
+        # epilogue is not hidden behind a second accumulator, and two rounds show it twice)
+        BLOCK_N = 512 if BLOCK_M == 256 and newt.cdiv(m, 256) * newt.cdiv(n, 512) >= 4 * 74 else 256
     if num_stages is None:
         num_stages = 4 if BLOCK_N == 512 else 6
     c = torch.empty(m, n, device=a.device, dtype=a.dtype) if c is None else c
