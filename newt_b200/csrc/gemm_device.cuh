@@ -378,6 +378,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
     mbar_init_fence();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (p.c_tma) prefetch_tensormap(&p.tmap_c);
   }
   if (warp == 1) {
     __syncwarp();
@@ -603,6 +604,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmap_a, const 
     mbar_init_fence();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (p.c_tma) prefetch_tensormap(&p.tmap_c);
   }
   if (warp == 1) {
     __syncwarp();
