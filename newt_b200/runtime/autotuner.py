@@ -125,10 +125,26 @@ class Autotuner:
             except (CompileError, ValueError, RuntimeError) as e:
                 last_error = e
                 continue
-            results.append((ms, cfg))
+            results.append((ms, cfg, run))
         if not results:
             raise RuntimeError(f"autotune: no valid config for {self.__name__}") from last_error
         results.sort(key=lambda r: r[0])
+        # A run-off between the leaders when they are close: a chip at its power cap drifts by a
+        # few percent over the seconds a list of long kernels takes, which is the size of the
+        # difference between the best tiles, so the order of the list would decide.  The two are
+        # timed again, taking turns, and each keeps its best time.
+        if len(results) > 1 and results[1][0] <= 1.03 * results[0][0]:
+            best = [results[0][0], results[1][0]]
+            try:
+                for _ in range(2):
+                    for i in (1, 0):
+                        best[i] = min(best[i], do_bench(results[i][2], warmup=self.warmup, rep=self.rep))
+                results[0] = (best[0],) + results[0][1:]
+                results[1] = (best[1],) + results[1][1:]
+                results.sort(key=lambda r: r[0])
+            except (CompileError, ValueError, RuntimeError):
+                pass
+        results = [(ms, cfg) for ms, cfg, _ in results]
         self.timings = {repr(c): ms for ms, c in results}
         return results[0][1]
 
