@@ -646,7 +646,7 @@ int plan_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
   // gives nothing below ~32 k rounds).  Knob gemm_half_tail: 1 = end only, 2 = both, negative = off.
   {
     const int knob = tuning("gemm_half_tail", 0);
-    p.half_tail = knob < 0 ? 0 : knob > 0 ? knob : (p.k_blocks / ksub >= 32 ? 2 : 1);
+    p.half_tail = knob < 0 ? 0 : knob > 0 ? knob : ksub > 1 ? 0 : (p.k_blocks >= 32 ? 2 : 1);   // nothing for the two-slot ring
   }
   p.wide_b = wide_b ? 1 : 0;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * c_bytes) % 16 == 0) ? 1 : 0;
