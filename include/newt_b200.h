@@ -236,7 +236,10 @@ int nb200_gemm_acc32(const void* a, const void* b, float* c, int64_t m, int64_t 
  * `tensor_map_b` (128 bytes each, 64-byte aligned), fills `params` (the kernels' GemmParams; at
  * least nb200_gemm_params_bytes() bytes) and says in `launch` which template instance to
  * compile and how to launch it.  `c_dtype` is the element type of C (any of the three codes);
- * fp16 / bf16 operands only. */
+ * fp16 / bf16 operands only.  The kernel wrapper takes the two tensor maps and the parameter
+ * block as `const __grid_constant__` parameters: the block holds the tensor map of C that the
+ * epilogue's copies read, and a tensor map has to be read from where the launch put it, not
+ * from a thread's copy. */
 typedef struct nb200_gemm_launch {
   int32_t pair;        /* 1: gemm_pair_body<stages, ksub, ..> in clusters of two; 0: gemm_body<block_n, stages, ..> */
   int32_t block_n, stages, ksub;
